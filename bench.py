@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 weight quantisation path on the Llama-3-8B linear-weight shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = NVFP4 real quantisation + packing (global abs-max pass, then block-scale / E2M1 /
+pack pass) of every linear weight of a random-init Llama-3-8B-shaped model: 32 layers of
+q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336, bf16, Student-t(4) values
+scaled to std 0.02.  With N GPUs the 32 layers are split across the ranks (strong scaling, no
+data-path collective).  Prints one JSON line (rank 0).
+
+``--impl reference`` times the CPU restatement of the reference's torch path (oracle/) on the
+host cores for a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tensorrt-model-optimizer_b200"))
+
+LAYER_SHAPES = [("q_proj", (4096, 4096)), ("k_proj", (1024, 4096)), ("v_proj", (1024, 4096)),
+                ("o_proj", (4096, 4096)), ("gate_proj", (14336, 4096)), ("up_proj", (14336, 4096)),
+                ("down_proj", (4096, 14336))]
+N_LAYERS = 32
+ELEMS_PER_LAYER = sum(a * b for _, (a, b) in LAYER_SHAPES)
+# algorithmic bytes per element: abs-max pass reads 2 B; quantise pass reads 2 B, writes 0.5 B of
+# codes and 1/16 B of block scale
+BYTES_AMAX = 2.0
+BYTES_QUANT = 2.0 + 0.5 + 1.0 / 16
+BYTES_TOTAL = BYTES_AMAX + BYTES_QUANT
+# DRAM bytes per element of the quantise kernel from the committed ncu capture
+# (profiles/nvfp4_group_quantize_*.md), or None before one exists
+NCU_QUANT_TRAFFIC_PER_ELEM = None
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_weight(shape, seed, device):
+    """Student-t(4) scaled to std 0.02 (Var t4 = 2), bf16, from a per-tensor seed."""
+    import torch
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    z = torch.randn(shape, generator=g, device=device)
+    chi = torch.zeros(shape, device=device)
+    for _ in range(4):
+        chi += torch.randn(shape, generator=g, device=device) ** 2
+    w = z / (chi / 4).sqrt() * (0.02 / 2 ** 0.5)
+    return w.to(torch.bfloat16)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [r for t, r in self.rows if (t0 is None or t >= t0 - 0.1) and (t1 is None or t <= t1 + 0.1)]
+        if not rows:
+            rows = [r for _, r in self.rows]
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0])); smax.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------- CPU arm -------
+
+def cpu_nvfp4_sample(seconds_target: float = 15.0, threads: int | None = None):
+    """Time the oracle's NVFP4 quantisation (the reference's torch-path arithmetic, numpy) on host
+    cores over row chunks of k_proj-shaped weights; returns (GB/s of algorithmic bytes, info)."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+
+    from oracle import quant_oracle as qo
+
+    threads = threads or os.cpu_count() or 1
+    rng = np.random.default_rng(0)
+    rows, cols = 1024, 4096
+    w = rng.standard_t(4, size=(rows, cols)).astype(np.float32) * np.float32(0.02 / 2 ** 0.5)
+    w = qo.round_bf16(w)
+    chunks = np.array_split(np.arange(rows), threads * 2)
+
+    def one_pass():
+        amax = qo.reduce_amax(w)
+        s2 = qo.nvfp4_scale2(amax)
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(lambda idx: qo.nvfp4_quantize(w[idx[0]:idx[-1] + 1], 16, s2=s2), chunks))
+
+    one_pass()
+    t0 = time.perf_counter()
+    one_pass()
+    dt1 = time.perf_counter() - t0
+    reps = max(1, min(50, int(seconds_target / max(dt1, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        one_pass()
+    dt = (time.perf_counter() - t0) / reps
+    gbs = rows * cols * BYTES_TOTAL / dt / 1e9
+    return gbs, {"cores": threads, "kind": "port",
+                 "sample": f"{reps} passes over one k_proj-shaped weight [{rows},{cols}] bf16 "
+                           f"({dt * 1e3:.1f} ms per pass), numpy oracle, {threads} threads"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    per_step = max(2.0, min(20.0, 120.0 / (steps + warm)))
+    vals = []
+    info = None
+    for i in range(steps + warm):
+        gbs, info = cpu_nvfp4_sample(per_step)
+        if i >= warm:
+            vals.append(gbs)
+    v = statistics.mean(vals)
+    ms_full = N_LAYERS * ELEMS_PER_LAYER * BYTES_TOTAL / (v * 1e9) * 1e3
+    line = {
+        "impl": "reference", "metric": "nvfp4_weight_quantize_hbm_gbps", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": ms_full,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "llama3-8b-shape linear weights, NVFP4 quantize+pack (block 16)",
+                   "note": "ms_per_step extrapolated from the sample to the full 32-layer model"},
+        "cpu_baseline": {"value": v, "unit": "GB/s", **info},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------- GPU arm -------
+
+def split_layers(n_layers: int, world: int, rank: int):
+    per = n_layers // world
+    extra = n_layers % world
+    lo = rank * per + min(rank, extra)
+    return list(range(lo, lo + per + (1 if rank < extra else 0)))
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from b200q.ops import NvFp4Group
+    from b200q.pipeline import HostNvFp4Packer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the kernels)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    layers = split_layers(args.layers, world, rank)
+
+    # ---- resident inputs ---------------------------------------------------------------------
+    weights = []
+    for l in layers:
+        for k, (_, shape) in enumerate(LAYER_SHAPES):
+            weights.append(make_weight(shape, l * len(LAYER_SHAPES) + k, dev))
+    group = NvFp4Group(weights) if weights else None
+    my_elems = sum(w.numel() for w in weights)
+    total_elems = args.layers * ELEMS_PER_LAYER
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        if group is not None:
+            group.run()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.25)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    from b200q._cabi import call
+    from b200q.ops import _DT
+    barrier()
+    t_wall0 = time.perf_counter()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        if group is None:
+            continue
+        # same two launches as group.run(), with an event between them so that each kernel's
+        # duration is known
+        st = torch.cuda.current_stream().cuda_stream
+        group.amax.zero_()
+        ev[i][0].record()
+        call("b200q_nvfp4_group_amax", group._descs.data_ptr(), group.n, group.total_tiles, _DT[group.dtype], st)
+        ev[i][1].record()
+        call("b200q_nvfp4_group_quantize", group._descs.data_ptr(), group.n, group.total_tiles, _DT[group.dtype], st)
+        ev[i][2].record()
+    end.record()
+    barrier()
+    t_wall1 = time.perf_counter()
+    ms = start.elapsed_time(end)
+    clocks = sampler.stop(t_wall0, t_wall1)
+    amax_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev) if group is not None else 0.0
+    quant_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev) if group is not None else 0.0
+    if world > 1:
+        t = torch.tensor([ms, amax_ms, quant_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, amax_ms, quant_ms = t.tolist()
+    ms_per_step = ms / args.steps
+    value = total_elems * BYTES_TOTAL / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: pinned host weights in, packed bytes out, through the public packer -----
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, weights, layers, dev, world, total_elems, barrier)
+
+    # ---- CPU baseline (rank 0, N=1 only) ---------------------------------------------------
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        gbs, info = cpu_nvfp4_sample(12.0)
+        cpu = {"value": gbs, "unit": "GB/s", **info}
+
+    if rank == 0:
+        peak, which = peaks()
+        per_rank_elems = my_elems  # rank 0's share; shares are equal when world divides the layers
+        achieved = per_rank_elems * BYTES_QUANT / (quant_ms * 1e-3) / 1e9 if quant_ms else None
+        achieved_amax = per_rank_elems * BYTES_AMAX / (amax_ms * 1e-3) / 1e9 if amax_ms else None
+        line = {
+            "metric": "nvfp4_weight_quantize_hbm_gbps", "value": value, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "llama3-8b-shape linear weights (224 tensors, 6.98e9 elements), NVFP4 "
+                                   "real quantize + pack: fp32 global scale, E4M3 scale per 16, E2M1 nibbles",
+                       "layers": args.layers, "sharding": f"layers split over {world} rank(s)",
+                       "l2": "inputs (>=1.7 GB per rank) are larger than L2; no flush needed",
+                       "bytes_per_element": BYTES_TOTAL, "ptq_seconds": ms_per_step * 1e-3},
+            "roofline": {"bound": "hbm", "kernel": "nvfp4_group_quantize_kernel", "achieved": achieved,
+                         "peak": peak, "peak_source": f"of {which}", "unit": "GB/s",
+                         "frac": achieved / peak if achieved else None,
+                         "traffic": NCU_QUANT_TRAFFIC_PER_ELEM * per_rank_elems
+                         if NCU_QUANT_TRAFFIC_PER_ELEM else None,
+                         "algorithmic_bytes_per_launch": per_rank_elems * BYTES_QUANT,
+                         "ms_per_launch": quant_ms,
+                         "amax_kernel": {"achieved": achieved_amax, "frac": achieved_amax / peak
+                                         if achieved_amax else None, "ms_per_launch": amax_ms}},
+            "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": 2 * args.steps,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
+    import torch
+    import torch.distributed as dist
+
+    from b200q.pipeline import HostNvFp4Packer
+
+    shapes = [s for _, s in LAYER_SHAPES]
+    try:
+        packer = HostNvFp4Packer(shapes, torch.bfloat16, dev)
+        host_in = []
+        for li in range(len(layers)):
+            host_in.append([torch.empty(s, dtype=torch.bfloat16).pin_memory() for s in shapes])
+            for k in range(len(shapes)):
+                host_in[li][k].copy_(weights[li * len(shapes) + k])
+        host_out = packer.alloc_host_outputs(len(layers))
+    except RuntimeError as e:  # pinned allocation refused
+        return {"value": None, "unit": "GB/s", "error": str(e)[:200]}
+    torch.cuda.synchronize()
+    steps = max(1, min(args.steps, args.e2e_steps))
+    packer.pack(host_in, host_out)  # warm-up
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        packer.pack(host_in, host_out)
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    if world > 1:
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = t.item()
+    h2d = len(layers) * packer.in_bytes
+    d2h = len(layers) * (packer.packed_bytes + packer.scale_bytes + 4 * len(shapes))
+    return {"value": total_elems * BYTES_TOTAL / dt / 1e9, "unit": "GB/s", "seconds_per_step": dt,
+            "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "api": "b200q.pipeline.HostNvFp4Packer.pack (pinned host weights -> pinned host NVFP4)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

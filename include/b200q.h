@@ -1,0 +1,198 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) quantize / calibrate kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA stream it is
+ * given (a cudaStream_t passed as void*; NULL = legacy default stream), allocates nothing and
+ * never synchronises.  The return value is B200Q_OK (0) or a negative b200q_status; on an
+ * error nothing has been launched.  Pointers must be 16-byte aligned unless stated otherwise.
+ *
+ * The comment above each declaration names the interface of the reference (ModelOpt 0.40,
+ * paths relative to the reference project root) that the entry point stands in for.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element type of floating tensors ("T" below) */
+typedef enum { B200Q_F32 = 0, B200Q_F16 = 1, B200Q_BF16 = 2 } b200q_dtype;
+
+typedef enum {
+  B200Q_OK = 0,
+  B200Q_ERR_NULL = -1,        /* a required pointer is NULL */
+  B200Q_ERR_DTYPE = -2,       /* dtype code not one of b200q_dtype */
+  B200Q_ERR_ALIGN = -3,       /* pointer not 16-byte aligned */
+  B200Q_ERR_SHAPE = -4,       /* size not positive / not divisible by the block size */
+  B200Q_ERR_ARG = -5,         /* other argument out of range (bits, flags, ...) */
+  B200Q_ERR_CUDA = -6,        /* the CUDA runtime reported an error at launch */
+  B200Q_ERR_UNSUPPORTED = -7, /* valid request the kernels do not cover */
+  B200Q_ERR_TIMEOUT = -8      /* a bounded device-side wait ran out (see b200q_last_device_status) */
+} b200q_status;
+
+const char* b200q_strerror(int status);
+int b200q_version(void);
+/* number of SMs of the current device (grid sizing is a multiple of it) */
+int b200q_sm_count(void);
+
+/* ---------------------------------------------------------------- amax reductions --------- */
+
+/* Running per-tensor abs-max: *amax_io = max(*amax_io, max|x|) as fp32 (zero it for a fresh
+ * amax).  NaN in x makes the result NaN.  Replaces reduce_amax(axis=None)
+ * (modelopt/torch/quantization/utils.py:155-188) and the running max of MaxCalibrator.collect
+ * (modelopt/torch/quantization/calib/max.py:52-86). */
+int b200q_amax_tensor(const void* x, int64_t n, int dtype, float* amax_io, void* stream);
+
+/* Running abs-max over the outer and inner dimensions of x viewed as [outer, axis, inner]
+ * (row-major): amax_io[a] = max(amax_io[a], max_{o,i} |x[o,a,i]|).  Replaces reduce_amax with a
+ * reduce-axis list (utils.py:137-188) as used by per-channel MaxCalibrator (calib/max.py:62-63). */
+int b200q_amax_axis(const void* x, int64_t outer, int64_t axis, int64_t inner, int dtype,
+                    float* amax_io, void* stream);
+
+/* Abs-max of each run of `block` contiguous elements: amax_out[b] (fp32, overwritten).
+ * Replaces reduce_block_amax with block_sizes={-1: block} (utils.py:52-98). */
+int b200q_amax_blocks(const void* x, int64_t nblocks, int block, int dtype, float* amax_out,
+                      void* stream);
+
+/* ---------------------------------------------------------------- integer fake quant ------ */
+
+/* y = clamp(rint(x*scale), lo, bound)/scale with scale = bound/amax, bound = 2^(bits-1+unsigned)-1,
+ * lo = -(bound + !narrow_range); amax < 2^-24 gives 0.  One fp32 amax for the whole tensor.
+ * Replaces fake_tensor_quant of modelopt_cuda_ext
+ * (modelopt/torch/quantization/src/tensor_quant_gpu.cu:43-98). */
+int b200q_fake_int_tensor(const void* x, void* y, int64_t n, int dtype, const float* amax,
+                          int num_bits, int is_unsigned, int narrow_range, void* stream);
+
+/* Same arithmetic with amax[a] chosen by the middle index of x viewed as [outer, axis, inner].
+ * Replaces fake_tensor_quant_with_axis (src/tensor_quant_gpu.cu:100-140). */
+int b200q_fake_int_axis(const void* x, void* y, int64_t outer, int64_t axis, int64_t inner,
+                        int dtype, const float* amax, int num_bits, int is_unsigned,
+                        int narrow_range, void* stream);
+
+/* Fused dynamic per-row quantisation of x[rows, cols]: the row abs-max is taken on chip and
+ * used as amax of that row in the same pass; amax_out (fp32 [rows], may be NULL) receives it.
+ * Replaces the reduce_amax + fake_tensor_quant_with_axis pair that TensorQuantizer issues for
+ * dynamic / per-row / per-block integer quantisers
+ * (modelopt/torch/quantization/nn/modules/tensor_quantizer.py:505-514,633-686). */
+int b200q_fake_int_rows_dynamic(const void* x, void* y, int64_t rows, int64_t cols, int dtype,
+                                float* amax_out, int num_bits, int is_unsigned,
+                                int narrow_range, void* stream);
+
+/* ---------------------------------------------------------------- FP8 E4M3 fake quant ----- */
+
+/* y = T(float(e4m3_rn_satfinite(float(x)*scale))*inv), scale = 448/amax, inv = 1/scale;
+ * amax == NULL casts without scaling.  Replaces fake_e4m3fy
+ * (modelopt/torch/quantization/src/tensor_quant_gpu_fp8.cu:35-45,86-101). */
+int b200q_fake_e4m3_tensor(const void* x, void* y, int64_t n, int dtype, const float* amax,
+                           void* stream);
+
+/* Per-channel form, x viewed as [outer, axis, inner].  Replaces fake_e4m3fy_with_axis
+ * (src/tensor_quant_gpu_fp8.cu:47-84). */
+int b200q_fake_e4m3_axis(const void* x, void* y, int64_t outer, int64_t axis, int64_t inner,
+                         int dtype, const float* amax, void* stream);
+
+/* ---------------------------------------------------------------- NVFP4 ------------------- */
+
+/* flags for b200q_nvfp4_quantize */
+enum {
+  B200Q_NVFP4_GLOBAL_IS_SCALE2 = 1 /* `global` holds weights_scaling_factor_2, not amax */
+};
+
+/* Two-level-scale NVFP4 real quantisation of nblocks runs of 16 contiguous elements:
+ *   s2 = amax/2688 (or *global itself with B200Q_NVFP4_GLOBAL_IS_SCALE2), written to *s2_out
+ *   scales[b] = e4m3(block_amax/(6*s2)) (0 -> 1.0; torch cast rule: >464 -> NaN code 0x7F),
+ *               or scales_in[b] when scales_in != NULL
+ *   code = sign<<3 | e2m1_rne(|x/(float(scales[b])*s2)|),  packed[j] = code[2j+1]<<4 | code[2j]
+ * Replaces NVFP4QTensor.quantize / get_weights_scaling_factor / _cast_fp4
+ * (modelopt/torch/quantization/qtensor/nvfp4_tensor.py:62-97,119-232). */
+int b200q_nvfp4_quantize(const void* x, int64_t nblocks, int dtype, const float* global,
+                         const uint8_t* scales_in, uint8_t* packed, uint8_t* scales,
+                         float* s2_out, int flags, void* stream);
+
+/* y = T(lut[code] * (float(scales[b]) * *s2)).  Replaces NVFP4QTensor.dequantize
+ * (nvfp4_tensor.py:234-297) and the Triton fp4_dequantize
+ * (modelopt/torch/quantization/triton/fp4_kernel.py:211-383). */
+int b200q_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* s2,
+                           void* y, int64_t nblocks, int dtype, void* stream);
+
+/* NVFP4 fake quantisation: y = dequantize(quantize(x)) with the arithmetic above, block scale
+ * cast saturating (min(.,448)), one pass, nothing stored but y.  Stands in for
+ * dynamic_block_quantize_op with (2,1)/(4,3) formats
+ * (modelopt/torch/quantization/tensor_quant.py:158-198; Triton fp4_fake_quant_block,
+ * triton/fp4_kernel.py:45-208; fused_amax_convert, src/tensor_quant_mx.cu:239-391). */
+int b200q_nvfp4_fake(const void* x, void* y, int64_t nblocks, int dtype, const float* amax,
+                     void* stream);
+
+/* One tensor of a grouped NVFP4 launch.  All pointers are device pointers. */
+typedef struct {
+  const void* x;        /* T [nblocks*16] */
+  uint8_t* packed;      /* [nblocks*8]  */
+  uint8_t* scales;      /* [nblocks]    */
+  float* amax;          /* running abs-max slot of this tensor (in/out) */
+  float* s2;            /* weights_scaling_factor_2 out */
+  int64_t nblocks;      /* 16-element blocks in this tensor */
+  int64_t tile_begin;   /* first tile of this tensor in the launch-wide tile numbering */
+} b200q_nvfp4_desc;
+
+/* elements one CTA tile of the grouped kernels covers (tile_begin is counted in these) */
+int b200q_nvfp4_group_tile_elems(void);
+
+/* Grouped launches over a device-resident descriptor table (n entries, tile_begin ascending,
+ * total_tiles = tiles of all tensors).  `_amax` folds max|x| of each tensor into desc.amax;
+ * `_quantize` then quantises every tensor from its desc.amax.  Two launches replace the
+ * per-weight loop of pack_real_quantize_weight
+ * (modelopt/torch/quantization/qtensor/base_qtensor.py:196-229). */
+int b200q_nvfp4_group_amax(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles, int dtype,
+                           void* stream);
+int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles,
+                               int dtype, void* stream);
+
+/* ---------------------------------------------------------------- INT4 block -------------- */
+
+/* INT4 (AWQ) block quantise + pack, arithmetic in T as the reference kernel does:
+ *   scale = T(T(1/amax_T(block))*7) (or scales_in[b]);  u = roundf(clamp(x*scale,-8,7)+8)
+ *   packed[j] = u[2j]<<4 | u[2j+1];  scales_out[b] = scale (T, may alias nothing, may be NULL).
+ * Replaces INT4QTensor.quantize + INT4_quantize
+ * (modelopt/torch/quantization/qtensor/int4_tensor.py:39-88; src/tensor_quant_gpu.cu:310-366). */
+int b200q_int4_quantize(const void* x, int64_t nblocks, int block, int dtype,
+                        const void* scales_in, void* scales_out, uint8_t* packed, void* stream);
+
+/* y[2j] = T(hi-8)/scale, y[2j+1] = T(lo-8)/scale.  Replaces INT4_dequantize
+ * (src/tensor_quant_gpu.cu:261-308). */
+int b200q_int4_dequantize(const uint8_t* packed, const void* scales, void* y, int64_t nblocks,
+                          int block, int dtype, void* stream);
+
+/* ---------------------------------------------------------------- FP8 / INT8 real quant --- */
+
+/* q = e4m3fn_torch_cast(T(x / scale[a])) over x viewed as [outer, axis, inner]; scales are T;
+ * axis == 1 means one scale.  Replaces FP8QTensor.quantize
+ * (modelopt/torch/quantization/qtensor/fp8_tensor.py:41-113). */
+int b200q_fp8_quantize(const void* x, const void* scales, uint8_t* q, int64_t outer,
+                       int64_t axis, int64_t inner, int dtype, void* stream);
+
+/* q = int8(clamp(round_half_even(T(x / scale[a])), -128, 127)).  Replaces INT8QTensor.quantize
+ * (modelopt/torch/quantization/qtensor/int8_tensor.py:35-89). */
+int b200q_int8_quantize(const void* x, const void* scales, int8_t* q, int64_t outer,
+                        int64_t axis, int64_t inner, int dtype, void* stream);
+
+/* ---------------------------------------------------------------- histogram calibration --- */
+
+/* counts[bin] += #{ i : bin = min(int(|x_i| * nbins / range_max), nbins-1), |x_i| <= range_max }
+ * with 64-bit counters (|x| taken in fp32).  Replaces the abs/float/histc chain of
+ * HistogramCalibrator.collect (modelopt/torch/quantization/calib/histogram.py:77-130). */
+int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
+                       unsigned long long* counts, void* stream);
+
+/* *amax_out = edge of the first bin whose cumulative share (float64 running sum of count/total)
+ * reaches percentile/100: edges[i] when edges (fp32 [nbins+1]) is given, else bin_width*i.
+ * Replaces _compute_amax_percentile (calib/histogram.py:328-343). */
+int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,
+                          float bin_width, double percentile, float* amax_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

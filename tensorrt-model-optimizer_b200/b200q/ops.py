@@ -1,0 +1,363 @@
+"""Tensor-level wrappers over the C ABI.
+
+Each function takes CUDA tensors, allocates the outputs with torch (plumbing only), and launches
+the kernel on torch's current stream of the tensor's device.  CPU tensors are rejected: there is
+no fallback implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _cabi
+from ._cabi import call
+
+_DT = {torch.float32: _cabi.F32, torch.float16: _cabi.F16, torch.bfloat16: _cabi.BF16}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"b200q kernels take float32/float16/bfloat16 tensors, got {t.dtype}") from None
+
+
+def _cuda(t: torch.Tensor, what="input") -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"b200q: {what} must be a CUDA tensor (no CPU path exists)")
+    return t
+
+
+def _prep(x: torch.Tensor, align: int = 16) -> torch.Tensor:
+    """Contiguous, aligned view of x (copies only when it has to)."""
+    _cuda(x)
+    x = x.contiguous()
+    if x.data_ptr() % align:
+        x = x.clone(memory_format=torch.contiguous_format)
+    return x
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _amax_f32(amax: torch.Tensor, device) -> torch.Tensor:
+    return amax.detach().to(device=device, dtype=torch.float32).contiguous()
+
+
+# --------------------------------------------------------------------------- amax --------------
+
+def amax_tensor(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 0-dim abs-max of x; with ``out`` (fp32, 1 element) the running max is updated in place."""
+    x = _prep(x)
+    if out is None:
+        out = torch.zeros((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        call("b200q_amax_tensor", x.data_ptr(), x.numel(), dtype_code(x), out.data_ptr(), _stream(x))
+    return out
+
+
+def amax_axis3(x: torch.Tensor, outer: int, axis: int, inner: int,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 [axis] abs-max of contiguous x viewed as [outer, axis, inner]."""
+    x = _prep(x)
+    assert x.numel() == outer * axis * inner
+    if out is None:
+        out = torch.zeros(axis, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        call("b200q_amax_axis", x.data_ptr(), outer, axis, inner, dtype_code(x), out.data_ptr(), _stream(x))
+    return out
+
+
+def amax_blocks(x: torch.Tensor, block: int) -> torch.Tensor:
+    """fp32 [numel/block] abs-max of each run of ``block`` contiguous elements."""
+    x = _prep(x)
+    n = x.numel()
+    if n % block:
+        raise ValueError(f"numel {n} is not divisible by block {block}")
+    out = torch.empty(n // block, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        call("b200q_amax_blocks", x.data_ptr(), n // block, block, dtype_code(x), out.data_ptr(), _stream(x))
+    return out
+
+
+# --------------------------------------------------------------------------- fake quant --------
+
+def _axis_view(x: torch.Tensor, amax: torch.Tensor):
+    """(outer, axis, inner) of the single dimension along which ``amax`` varies."""
+    n = amax.numel()
+    shape = list(amax.shape)
+    if len(shape) == x.dim() and n in shape:
+        ax = shape.index(n)
+    elif amax.dim() == 1 and n in x.shape:
+        ax = list(x.shape).index(n)
+    else:
+        raise ValueError(f"amax of shape {tuple(amax.shape)} does not select one axis of {tuple(x.shape)}")
+    if x.shape[ax] != n:
+        raise ValueError(f"amax has {n} elements but input dim {ax} has {x.shape[ax]}")
+    outer = 1
+    for d in x.shape[:ax]:
+        outer *= d
+    inner = 1
+    for d in x.shape[ax + 1:]:
+        inner *= d
+    return outer, n, inner
+
+
+def fake_int(x: torch.Tensor, amax: torch.Tensor, num_bits: int = 8, unsigned: bool = False,
+             narrow_range: bool = True) -> torch.Tensor:
+    x = _prep(x)
+    y = torch.empty_like(x)
+    if x.numel() == 0:
+        return y
+    am = _amax_f32(amax, x.device)
+    with torch.cuda.device(x.device):
+        if am.numel() == 1:
+            call("b200q_fake_int_tensor", x.data_ptr(), y.data_ptr(), x.numel(), dtype_code(x),
+                 am.data_ptr(), num_bits, int(unsigned), int(narrow_range), _stream(x))
+        else:
+            outer, axis, inner = _axis_view(x, amax)
+            call("b200q_fake_int_axis", x.data_ptr(), y.data_ptr(), outer, axis, inner, dtype_code(x),
+                 am.data_ptr(), num_bits, int(unsigned), int(narrow_range), _stream(x))
+    return y
+
+
+def fake_int_rows_dynamic(x: torch.Tensor, num_bits: int = 8, unsigned: bool = False,
+                          narrow_range: bool = True, return_amax: bool = False):
+    """Per-row dynamic fake quant of a 2-D tensor; the row amax is found in the same pass."""
+    x = _prep(x)
+    if x.dim() != 2:
+        raise ValueError("expected a 2-D tensor [rows, cols]")
+    rows, cols = x.shape
+    y = torch.empty_like(x)
+    am = torch.empty(rows, dtype=torch.float32, device=x.device) if return_amax else None
+    with torch.cuda.device(x.device):
+        call("b200q_fake_int_rows_dynamic", x.data_ptr(), y.data_ptr(), rows, cols, dtype_code(x),
+             am.data_ptr() if am is not None else None, num_bits, int(unsigned), int(narrow_range),
+             _stream(x))
+    return (y, am) if return_amax else y
+
+
+def fake_e4m3(x: torch.Tensor, amax: torch.Tensor | None) -> torch.Tensor:
+    x = _prep(x)
+    y = torch.empty_like(x)
+    if x.numel() == 0:
+        return y
+    with torch.cuda.device(x.device):
+        if amax is None:
+            call("b200q_fake_e4m3_tensor", x.data_ptr(), y.data_ptr(), x.numel(), dtype_code(x), None, _stream(x))
+            return y
+        am = _amax_f32(amax, x.device)
+        if am.numel() == 1:
+            call("b200q_fake_e4m3_tensor", x.data_ptr(), y.data_ptr(), x.numel(), dtype_code(x),
+                 am.data_ptr(), _stream(x))
+        else:
+            outer, axis, inner = _axis_view(x, amax)
+            call("b200q_fake_e4m3_axis", x.data_ptr(), y.data_ptr(), outer, axis, inner, dtype_code(x),
+                 am.data_ptr(), _stream(x))
+    return y
+
+
+# --------------------------------------------------------------------------- NVFP4 -------------
+
+def nvfp4_quantize(x: torch.Tensor, amax: torch.Tensor | None = None, scale2: torch.Tensor | None = None,
+                   scales_in: torch.Tensor | None = None):
+    """x [..., K] with K % 16 == 0 -> (packed uint8 [..., K/2], scales float8_e4m3fn [..., K/16],
+    scale2 fp32 0-dim).  ``amax`` (any float dtype, 1 element) or ``scale2`` may be given; with
+    neither the tensor's own abs-max is used."""
+    x = _prep(x, 32)
+    K = x.shape[-1]
+    if K % 16:
+        raise ValueError("last dimension must be a multiple of 16 (pad first)")
+    nblocks = x.numel() // 16
+    dev = x.device
+    packed = torch.empty((*x.shape[:-1], K // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((*x.shape[:-1], K // 16), dtype=torch.uint8, device=dev)
+    s2 = torch.empty((), dtype=torch.float32, device=dev)
+    flags = 0
+    if scale2 is not None:
+        glob = _amax_f32(scale2, dev).reshape(())
+        flags = 1
+    elif amax is not None:
+        glob = _amax_f32(amax, dev).reshape(())
+    else:
+        glob = amax_tensor(x)
+    sin = None
+    if scales_in is not None:
+        sin = _cuda(scales_in, "scales_in").contiguous().view(torch.uint8)
+        assert sin.numel() == nblocks
+    with torch.cuda.device(dev):
+        call("b200q_nvfp4_quantize", x.data_ptr(), nblocks, dtype_code(x), glob.data_ptr(),
+             sin.data_ptr() if sin is not None else None, packed.data_ptr(), scales.data_ptr(),
+             s2.data_ptr(), flags, _stream(x))
+    return packed, scales.view(torch.float8_e4m3fn), s2
+
+
+def nvfp4_dequantize(packed: torch.Tensor, scales: torch.Tensor, scale2: torch.Tensor,
+                     dtype: torch.dtype) -> torch.Tensor:
+    packed = _cuda(packed).contiguous()
+    scales = _cuda(scales).contiguous().view(torch.uint8)
+    s2 = _amax_f32(scale2, packed.device).reshape(())
+    y = torch.empty((*packed.shape[:-1], packed.shape[-1] * 2), dtype=dtype, device=packed.device)
+    nblocks = y.numel() // 16
+    assert scales.numel() == nblocks
+    with torch.cuda.device(packed.device):
+        call("b200q_nvfp4_dequantize", packed.data_ptr(), scales.data_ptr(), s2.data_ptr(), y.data_ptr(),
+             nblocks, _DT[dtype], _stream(packed))
+    return y
+
+
+def nvfp4_fake(x: torch.Tensor, amax: torch.Tensor | None = None) -> torch.Tensor:
+    """NVFP4 fake quant along the last dimension (numel % 16 == 0)."""
+    x = _prep(x, 32)
+    if x.numel() % 16:
+        raise ValueError("numel must be a multiple of 16 (pad first)")
+    y = torch.empty_like(x)
+    am = amax_tensor(x) if amax is None else _amax_f32(amax, x.device)
+    if am.numel() != 1:
+        am = am.amax()
+    with torch.cuda.device(x.device):
+        call("b200q_nvfp4_fake", x.data_ptr(), y.data_ptr(), x.numel() // 16, dtype_code(x), am.data_ptr(),
+             _stream(x))
+    return y
+
+
+class NvFp4Group:
+    """A list of same-dtype weight tensors quantised by two grouped launches (amax, quantise).
+
+    The descriptor table lives in device memory and is built once; ``run()`` only zeroes the
+    amax slots and launches, so it can be repeated (and timed) without host work per tensor.
+    """
+
+    def __init__(self, tensors: list[torch.Tensor]):
+        if not tensors:
+            raise ValueError("empty tensor list")
+        self.tensors = [_prep(t, 32) for t in tensors]
+        dev, dt = self.tensors[0].device, self.tensors[0].dtype
+        tile = call("b200q_nvfp4_group_tile_elems")
+        n = len(self.tensors)
+        self.device, self.dtype, self.n = dev, dt, n
+        total_packed = sum(t.numel() // 2 for t in self.tensors)
+        total_scales = sum(t.numel() // 16 for t in self.tensors)
+        # one allocation per output kind; 32-byte aligned slices
+        self._packed = torch.empty(total_packed + 32 * n, dtype=torch.uint8, device=dev)
+        self._scales = torch.empty(total_scales + 32 * n, dtype=torch.uint8, device=dev)
+        self.amax = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.scale2 = torch.empty(n, dtype=torch.float32, device=dev)
+        descs = (_cabi.NvFp4Desc * n)()
+        self.packed, self.scales = [], []
+        po = so = 0
+        tiles = 0
+        for i, t in enumerate(self.tensors):
+            if t.device != dev or t.dtype != dt:
+                raise ValueError("all tensors of a group must share device and dtype")
+            if t.shape[-1] % 16:
+                raise ValueError("last dimension must be a multiple of 16")
+            K = t.shape[-1]
+            p = self._packed[po:po + t.numel() // 2].view(*t.shape[:-1], K // 2)
+            s = self._scales[so:so + t.numel() // 16].view(*t.shape[:-1], K // 16)
+            self.packed.append(p)
+            self.scales.append(s.view(torch.float8_e4m3fn))
+            d = descs[i]
+            d.x, d.packed, d.scales = t.data_ptr(), p.data_ptr(), s.data_ptr()
+            d.amax = self.amax.data_ptr() + 4 * i
+            d.s2 = self.scale2.data_ptr() + 4 * i
+            d.nblocks = t.numel() // 16
+            d.tile_begin = tiles
+            tiles += (t.numel() + tile - 1) // tile
+            po += (t.numel() // 2 + 31) // 32 * 32
+            so += (t.numel() // 16 + 31) // 32 * 32
+        self.total_tiles = tiles
+        raw = bytes(descs)
+        host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+        self._descs = host.to(dev)
+        self.elements = sum(t.numel() for t in self.tensors)
+
+    def run(self, amax_pass: bool = True):
+        dc = _DT[self.dtype]
+        with torch.cuda.device(self.device):
+            st = torch.cuda.current_stream(self.device).cuda_stream
+            if amax_pass:
+                self.amax.zero_()
+                call("b200q_nvfp4_group_amax", self._descs.data_ptr(), self.n, self.total_tiles, dc, st)
+            call("b200q_nvfp4_group_quantize", self._descs.data_ptr(), self.n, self.total_tiles, dc, st)
+        return self.packed, self.scales, self.scale2
+
+
+# --------------------------------------------------------------------------- INT4 --------------
+
+def int4_quantize(x: torch.Tensor, block: int, scales_in: torch.Tensor | None = None):
+    """Flat contiguous x (numel % block == 0) -> (packed uint8 [numel/2], scales T [numel/block, 1])."""
+    x = _prep(x)
+    n = x.numel()
+    if n % block or block % 2:
+        raise ValueError("numel must be a multiple of an even block size (pad first)")
+    nb = n // block
+    packed = torch.empty(n // 2, dtype=torch.uint8, device=x.device)
+    if scales_in is not None:
+        scales = _cuda(scales_in, "scales").to(x.dtype).contiguous().view(nb, 1)
+        sin, sout = scales.data_ptr(), None
+    else:
+        scales = torch.empty((nb, 1), dtype=x.dtype, device=x.device)
+        sin, sout = None, scales.data_ptr()
+    with torch.cuda.device(x.device):
+        call("b200q_int4_quantize", x.data_ptr(), nb, block, dtype_code(x), sin, sout, packed.data_ptr(),
+             _stream(x))
+    return packed, scales
+
+
+def int4_dequantize(packed: torch.Tensor, scales: torch.Tensor, block: int) -> torch.Tensor:
+    packed = _cuda(packed).contiguous().view(-1)
+    scales = _cuda(scales, "scales").contiguous()
+    n = packed.numel() * 2
+    y = torch.empty(n, dtype=scales.dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        call("b200q_int4_dequantize", packed.data_ptr(), scales.data_ptr(), y.data_ptr(), n // block, block,
+             dtype_code(scales), _stream(packed))
+    return y
+
+
+# --------------------------------------------------------------------------- FP8 / INT8 --------
+
+def _q8(name: str, x: torch.Tensor, scales: torch.Tensor, outer: int, axis: int, inner: int, out_dtype):
+    x = _prep(x)
+    s = _cuda(scales, "scales").to(x.dtype).contiguous()
+    assert s.numel() == axis and x.numel() == outer * axis * inner
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        call(name, x.data_ptr(), s.data_ptr(), q.data_ptr(), outer, axis, inner, dtype_code(x), _stream(x))
+    return q.view(out_dtype)
+
+
+def fp8_quantize(x, scales, outer, axis, inner):
+    return _q8("b200q_fp8_quantize", x, scales, outer, axis, inner, torch.float8_e4m3fn)
+
+
+def int8_quantize(x, scales, outer, axis, inner):
+    return _q8("b200q_int8_quantize", x, scales, outer, axis, inner, torch.int8)
+
+
+# --------------------------------------------------------------------------- histogram ---------
+
+def hist_collect(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_max: float):
+    """counts (int64 [>= nbins], CUDA) += histogram of |x| over [0, range_max] with nbins bins."""
+    x = _prep(x)
+    assert counts.dtype == torch.int64 and counts.is_cuda and counts.numel() >= nbins
+    with torch.cuda.device(x.device):
+        call("b200q_hist_collect", x.data_ptr(), x.numel(), dtype_code(x), nbins,
+             ctypes.c_float(range_max), counts.data_ptr(), _stream(x))
+    return counts
+
+
+def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None, width: float,
+                    percentile: float) -> torch.Tensor:
+    out = torch.empty((), dtype=torch.float32, device=counts.device)
+    e = None
+    if edges is not None:
+        e = edges.to(device=counts.device, dtype=torch.float32).contiguous()
+        assert e.numel() >= nbins + 1
+    with torch.cuda.device(counts.device):
+        call("b200q_hist_percentile", counts.data_ptr(), nbins, e.data_ptr() if e is not None else None,
+             ctypes.c_float(width), ctypes.c_double(percentile), out.data_ptr(), _stream(counts))
+    return out

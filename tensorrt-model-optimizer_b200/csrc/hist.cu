@@ -1,0 +1,120 @@
+// Histogram calibration: fixed-range, equal-width binning of |x| with 64-bit global counters,
+// and the percentile read-out.
+//
+// Each CTA bins into shared-memory 32-bit counters (several replicas chosen by lane, so that the
+// lanes of a warp that hit the same hot bin do not serialise on one address), then adds its
+// non-zero bins to the global 64-bit counters once.  Bins beyond the shared range go to global
+// atomics directly.  Integer sums make the result independent of the order of batches and ranks.
+#include "numerics.cuh"
+
+namespace b200q {
+
+constexpr int kHistThreads = 512;
+constexpr int kHistSmemWords = 16384;  // 64 KB of 32-bit counters per CTA
+
+template <typename T>
+__global__ void __launch_bounds__(kHistThreads)
+hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, int smem_bins,
+                    int replicas, unsigned long long* __restrict__ counts) {
+  using E = Elem<T>;
+  constexpr int P = E::kPerPack;
+  extern __shared__ uint32_t sh[];
+  for (int i = threadIdx.x; i < smem_bins * replicas; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  uint32_t* mine = sh + (threadIdx.x & (replicas - 1)) * smem_bins;
+  const float fbins = static_cast<float>(nbins);
+
+  auto bin_one = [&](float v) {
+    const float a = fabsf(v);
+    if (!(a <= range_max)) return;  // out of range or NaN: not counted
+    int b = static_cast<int>(__fdiv_rn(a * fbins, range_max));
+    if (b >= nbins) b = nbins - 1;
+    if (b < smem_bins) atomicAdd(mine + b, 1u);
+    else atomicAdd(counts + b, 1ull);
+  };
+
+  const int64_t npack = n / P;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + stride < npack; i += 2 * stride) {
+    const uint4 v0 = ld_stream(xv + i), v1 = ld_stream(xv + i + stride);
+    float f[P];
+    E::unpack(v0, f);
+#pragma unroll
+    for (int k = 0; k < P; ++k) bin_one(f[k]);
+    E::unpack(v1, f);
+#pragma unroll
+    for (int k = 0; k < P; ++k) bin_one(f[k]);
+  }
+  for (; i < npack; i += stride) {
+    float f[P];
+    E::unpack(ld_stream(xv + i), f);
+#pragma unroll
+    for (int k = 0; k < P; ++k) bin_one(f[k]);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - npack * P) bin_one(E::to_float(x[npack * P + threadIdx.x]));
+  __syncthreads();
+  for (int b = threadIdx.x; b < smem_bins; b += blockDim.x) {
+    unsigned long long c = 0;
+    for (int r = 0; r < replicas; ++r) c += sh[r * smem_bins + b];
+    if (c) atomicAdd(counts + b, c);
+  }
+}
+
+// One thread walks the bins in order so that the running sum rounds exactly as a sequential
+// float64 cumulative sum does.
+__global__ void hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
+                                       const float* __restrict__ edges, float bin_width,
+                                       double frac, float* __restrict__ amax_out) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  unsigned long long total = 0;
+  for (int i = 0; i < nbins; ++i) total += counts[i];
+  const double dt = static_cast<double>(total);
+  double cdf = 0.0;
+  int idx = nbins;
+  for (int i = 0; i < nbins; ++i) {
+    cdf += static_cast<double>(counts[i]) / dt;
+    if (cdf >= frac) { idx = i; break; }
+  }
+  *amax_out = edges ? edges[idx] : bin_width * static_cast<float>(idx);
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
+                                  unsigned long long* counts, void* stream) {
+  B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(counts);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x);
+  if (n <= 0 || nbins <= 0) return B200Q_ERR_SHAPE;
+  if (!(range_max > 0.f)) return B200Q_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // shared bins: all of them when they fit, replicated as often as the budget allows (<= 8)
+  int smem_bins = nbins < kHistSmemWords ? nbins : kHistSmemWords;
+  int replicas = 1;
+  while (replicas < 8 && smem_bins * replicas * 2 <= kHistSmemWords) replicas <<= 1;
+  const size_t smem = static_cast<size_t>(smem_bins) * replicas * sizeof(uint32_t);
+  return B200Q_DISPATCH(dtype, [&] {
+    auto kern = hist_collect_kernel<T>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kHistSmemWords * 4) != cudaSuccess)
+      return static_cast<int>(B200Q_ERR_CUDA);
+    int grid = grid_for(n / Elem<T>::kPerPack, kHistThreads * 2, 2);
+    kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x), n, nbins, range_max, smem_bins,
+                                          replicas, counts);
+    return launch_status();
+  });
+}
+
+extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,
+                                     float bin_width, double percentile, float* amax_out,
+                                     void* stream) {
+  B200Q_REQUIRE_PTR(counts); B200Q_REQUIRE_PTR(amax_out);
+  if (nbins <= 0) return B200Q_ERR_SHAPE;
+  if (!(percentile >= 0.0 && percentile <= 100.0)) return B200Q_ERR_ARG;
+  hist_percentile_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts, nbins, edges, bin_width, percentile / 100.0, amax_out);
+  return launch_status();
+}

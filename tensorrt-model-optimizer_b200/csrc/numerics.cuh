@@ -1,0 +1,79 @@
+// Numeric primitives shared by every kernel.  All fp32 arithmetic here is IEEE round-to-nearest:
+// the translation units are compiled without fast-math, and divisions use __fdiv_rn explicitly.
+#pragma once
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace b200q {
+
+// ---- E4M3 ------------------------------------------------------------------------------------
+// Two fp32 -> two E4M3 bytes (lo in bits 0-7), round-to-nearest-even, saturating to +-448, NaN -> 0x7F.
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2_sat(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t f32_to_e4m3_sat(float x) { return f32x2_to_e4m3x2_sat(x, 0.f) & 0xffu; }
+
+// torch's float32 -> float8_e4m3fn cast: RNE, |x| up to 464 rounds to 448, larger magnitudes and
+// NaN become the NaN code 0x7F with the sign bit kept.
+__device__ __forceinline__ uint32_t f32_to_e4m3_torch(float x) {
+  uint32_t c = f32_to_e4m3_sat(x);
+  if (fabsf(x) > 464.f) c = 0x7fu | ((__float_as_uint(x) >> 24) & 0x80u);
+  return c;
+}
+
+// E4M3 byte -> fp32 (exact).  The 7 magnitude bits dropped at bit 20 of an fp32 pattern give
+// 2^(E-127)(1+m/8) (or the matching subnormal), which 2^120 rebiases to 2^(E-7); 0x7F/0xFF -> NaN.
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
+  uint32_t mag = b & 0x7fu;
+  float f = __uint_as_float(mag << 20) * 1.329227995784916e36f;  // 2^120
+  if (mag == 0x7fu) f = __uint_as_float(0x7fc00000u);
+  return __uint_as_float(__float_as_uint(f) | ((b & 0x80u) << 24));
+}
+
+// Two E4M3 bytes -> two fp32 through the hardware conversion (exact).
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(v)));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
+// ---- E2M1 ------------------------------------------------------------------------------------
+// Two fp32 -> one byte of two E2M1 codes (`even` in the low nibble), RNE, saturating to +-6,
+// NaN -> +6 (0x7).  The sign bit follows the sign bit of the input, so callers that need
+// "negative zero only for inputs below zero" canonicalise the input first.
+__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float even, float odd) {
+  return __nv_cvt_float2_to_fp4x2(make_float2(even, odd), __NV_E2M1, cudaRoundNearest);
+}
+
+// magnitude of an E2M1 code (bits 0-2): 0,.5,1,1.5,2,3,4,6 ; bit 3 is the sign
+__device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
+  const uint32_t m = code & 7u;
+  // m < 2: m*0.5 ; else (2 + (m&1)) * 2^((m>>1)-2)
+  float v = (m < 2u) ? 0.5f * static_cast<float>(m)
+                     : __uint_as_float(((126u + (m >> 1)) << 23) | ((m & 1u) << 22));
+  return (code & 8u) ? -v : v;
+}
+
+// ---- integer fake quant ------------------------------------------------------------------------
+struct IntQ {
+  float bound, lo;
+};
+__host__ __device__ inline IntQ make_intq(int num_bits, int is_unsigned, int narrow) {
+  IntQ q;
+  q.bound = static_cast<float>((1 << (num_bits - 1 + (is_unsigned ? 1 : 0))) - 1);
+  q.lo = -(q.bound + (narrow ? 0.f : 1.f));
+  return q;
+}
+// scale = bound/amax is formed once per amax; amax < 2^-24 maps everything to 0.
+__device__ __forceinline__ float intq_apply(float x, float scale, bool live, const IntQ& q) {
+  float r = rintf(x * scale);
+  r = r > q.bound ? q.bound : r;
+  r = r < q.lo ? q.lo : r;
+  return live ? __fdiv_rn(r, scale) : 0.f;
+}
+
+}  // namespace b200q

@@ -1,0 +1,424 @@
+// NVFP4: two-level scaling (fp32 per-tensor scale, E4M3 scale per 16 elements) and E2M1 values
+// packed two per byte.  Real quantisation (codes + scales), dequantisation, fake quantisation,
+// and grouped launches that cover a whole list of weight tensors with one grid.
+//
+// One thread owns one 16-element block: the block arrives with 256-bit loads (one for half/bf16,
+// two for fp32), the block abs-max never leaves registers, and the eight packed bytes leave as
+// one 8-byte store, so a warp reads 1 KB and writes 256 B + 32 B, all contiguous.
+#include "numerics.cuh"
+
+namespace b200q {
+
+constexpr int kNvThreads = 256;
+constexpr int kNvUnroll = 2;                              // blocks in flight per thread
+constexpr int kNvTileBlocks = kNvThreads * kNvUnroll;     // 16-element blocks per CTA tile
+constexpr int kNvTileElems = kNvTileBlocks * 16;
+
+struct u32x8 { uint32_t w[8]; };
+
+__device__ __forceinline__ u32x8 ld256_stream(const void* p) {
+  u32x8 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]),
+                 "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p));
+  return v;
+}
+// same, asking L2 to keep the line: the quantise pass reads the tensor again right after
+__device__ __forceinline__ u32x8 ld256_keep(const void* p) {
+  u32x8 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_last.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]),
+                 "=r"(v.w[5]), "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st256_stream(void* p, const u32x8& v) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.w[0]),
+               "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]),
+               "r"(v.w[7])
+               : "memory");
+}
+
+// Raw storage of one 16-element block and its decoding.
+template <typename T> struct Block16;
+template <> struct Block16<float> {
+  u32x8 a, b;
+  __device__ __forceinline__ void load(const float* p) { a = ld256_stream(p); b = ld256_stream(p + 8); }
+  __device__ __forceinline__ void load_keep(const float* p) { a = ld256_keep(p); b = ld256_keep(p + 8); }
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a.w[i] = b.w[i] = 0;
+  }
+  __device__ __forceinline__ uint32_t amax_f32bits() const {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = max(m, max(a.w[i] & 0x7fffffffu, b.w[i] & 0x7fffffffu));
+    return m;
+  }
+  __device__ __forceinline__ void decode(float* f) const {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { f[i] = __uint_as_float(a.w[i]); f[8 + i] = __uint_as_float(b.w[i]); }
+  }
+};
+template <> struct Block16<__nv_bfloat16> {
+  u32x8 a;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = ld256_stream(p); }
+  __device__ __forceinline__ void load_keep(const __nv_bfloat16* p) { a = ld256_keep(p); }
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a.w[i] = 0;
+  }
+  __device__ __forceinline__ uint32_t amax_f32bits() const {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = __vmaxu2(m, a.w[i] & 0x7fff7fffu);
+    return max(m & 0xffffu, m >> 16) << 16;
+  }
+  __device__ __forceinline__ void decode(float* f) const {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      f[2 * i] = __uint_as_float(a.w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(a.w[i] & 0xffff0000u);
+    }
+  }
+};
+template <> struct Block16<__half> {
+  u32x8 a;
+  __device__ __forceinline__ void load(const __half* p) { a = ld256_stream(p); }
+  __device__ __forceinline__ void load_keep(const __half* p) { a = ld256_keep(p); }
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a.w[i] = 0;
+  }
+  __device__ __forceinline__ uint32_t amax_f32bits() const {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = __vmaxu2(m, a.w[i] & 0x7fff7fffu);
+    uint16_t h = static_cast<uint16_t>(max(m & 0xffffu, m >> 16));
+    return __float_as_uint(__half2float(__ushort_as_half(h)));
+  }
+  __device__ __forceinline__ void decode(float* f) const {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&a.w[i]));
+      f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+  }
+};
+
+// ---- per-block arithmetic ----------------------------------------------------------------------
+// block scale code from the block abs-max; c = 6*s2
+template <bool kTorchCast>
+__device__ __forceinline__ uint32_t nvfp4_scale_code(float bamax, float c) {
+  float t = __fdiv_rn(bamax, c);
+  if (t == 0.f) t = 1.f;
+  return kTorchCast ? f32_to_e4m3_torch(t) : f32_to_e4m3_sat(t);
+}
+
+// 16 values -> 8 bytes of E2M1 codes under divisor d.  x/d is the IEEE quotient; adding +0
+// turns a negative-zero quotient into +0 so that only values below zero carry the sign bit.
+__device__ __forceinline__ uint2 nvfp4_encode16(const float* f, float d) {
+  uint32_t w[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float e = __fdiv_rn(f[8 * h + 2 * j], d) + 0.f;
+      const float o = __fdiv_rn(f[8 * h + 2 * j + 1], d) + 0.f;
+      acc |= f32x2_to_e2m1x2(e, o) << (8 * j);
+    }
+    w[h] = acc;
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+// 8 bytes of codes -> 16 values times d, with +0 for the negative-zero code as the table has
+__device__ __forceinline__ void nvfp4_decode16(uint2 codes, float d, float* f) {
+  const uint32_t w[2] = {codes.x, codes.y};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t c = (w[i >> 3] >> (4 * (i & 7))) & 0xfu;
+    f[i] = e2m1_to_f32(c) * d + 0.f;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store16(T* y, const float* f);
+template <> __device__ __forceinline__ void store16<float>(float* y, const float* f) {
+  u32x8 a, b;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { a.w[i] = __float_as_uint(f[i]); b.w[i] = __float_as_uint(f[8 + i]); }
+  st256_stream(y, a); st256_stream(y + 8, b);
+}
+template <> __device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* y, const float* f) {
+  u32x8 a;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a.w[i] = Elem<__nv_bfloat16>::pack2(f[2 * i], f[2 * i + 1]);
+  st256_stream(y, a);
+}
+template <> __device__ __forceinline__ void store16<__half>(__half* y, const float* f) {
+  u32x8 a;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) a.w[i] = Elem<__half>::pack2(f[2 * i], f[2 * i + 1]);
+  st256_stream(y, a);
+}
+
+// Quantise one loaded block and store codes + scale.
+template <typename T>
+__device__ __forceinline__ void nvfp4_quant_block(const Block16<T>& blk, int64_t b, float s2, float c,
+                                                  const uint8_t* __restrict__ scales_in,
+                                                  uint8_t* __restrict__ packed,
+                                                  uint8_t* __restrict__ scales) {
+  uint32_t code;
+  if (scales_in) code = scales_in[b];
+  else code = nvfp4_scale_code<true>(__uint_as_float(blk.amax_f32bits()), c);
+  const float d = e4m3_to_f32(code) * s2;
+  float f[16];
+  blk.decode(f);
+  st_stream(packed + 8 * b, nvfp4_encode16(f, d));
+  if (scales) scales[b] = static_cast<uint8_t>(code);
+}
+
+// ---- single-tensor kernels ---------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kNvThreads)
+nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __restrict__ global,
+                      bool global_is_s2, const uint8_t* __restrict__ scales_in,
+                      uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                      float* __restrict__ s2_out) {
+  const float g = __ldg(global);
+  const float s2 = global_is_s2 ? g : __fdiv_rn(g, 2688.f);
+  const float c = 6.f * s2;
+  if (s2_out && blockIdx.x == 0 && threadIdx.x == 0) *s2_out = s2;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t b0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b0 < nblocks;
+       b0 += kNvUnroll * stride) {
+    Block16<T> blk[kNvUnroll];
+#pragma unroll
+    for (int u = 0; u < kNvUnroll; ++u) {
+      const int64_t b = b0 + u * stride;
+      if (b < nblocks) blk[u].load(x + 16 * b);
+    }
+#pragma unroll
+    for (int u = 0; u < kNvUnroll; ++u) {
+      const int64_t b = b0 + u * stride;
+      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, s2, c, scales_in, packed, scales);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNvThreads)
+nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
+                  const float* __restrict__ amax) {
+  const float s2 = __fdiv_rn(__ldg(amax), 2688.f);
+  const float c = 6.f * s2;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t b0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b0 < nblocks;
+       b0 += kNvUnroll * stride) {
+    Block16<T> blk[kNvUnroll];
+#pragma unroll
+    for (int u = 0; u < kNvUnroll; ++u) {
+      const int64_t b = b0 + u * stride;
+      if (b < nblocks) blk[u].load(x + 16 * b);
+    }
+#pragma unroll
+    for (int u = 0; u < kNvUnroll; ++u) {
+      const int64_t b = b0 + u * stride;
+      if (b < nblocks) {
+        const uint32_t code = nvfp4_scale_code<false>(__uint_as_float(blk[u].amax_f32bits()), c);
+        const float d = e4m3_to_f32(code) * s2;
+        float f[16];
+        blk[u].decode(f);
+        const uint2 q = nvfp4_encode16(f, d);
+        nvfp4_decode16(q, d, f);
+        store16<T>(y + 16 * b, f);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNvThreads)
+nvfp4_dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                        const float* __restrict__ s2p, T* __restrict__ y, int64_t nblocks) {
+  const float s2 = __ldg(s2p);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
+    const uint2 q = *reinterpret_cast<const uint2*>(packed + 8 * b);
+    const float d = e4m3_to_f32(scales[b]) * s2;
+    float f[16];
+    nvfp4_decode16(q, d, f);
+    store16<T>(y + 16 * b, f);
+  }
+}
+
+// ---- grouped kernels -----------------------------------------------------------------------------
+// Tiles of kNvTileBlocks blocks are numbered across all tensors; a CTA takes a contiguous run of
+// tiles so that it crosses few tensor boundaries (one amax atomic per tensor it touches).
+__device__ __forceinline__ int find_tensor(const b200q_nvfp4_desc* __restrict__ d, int n, int64_t tile) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (d[mid].tile_begin <= tile) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNvThreads)
+nvfp4_group_amax_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, int64_t total_tiles) {
+  __shared__ uint32_t red[32];
+  const int64_t per = (total_tiles + gridDim.x - 1) / gridDim.x;
+  const int64_t t0 = blockIdx.x * per, t1 = min(total_tiles, t0 + per);
+  if (t0 >= t1) return;
+  int ti = find_tensor(descs, n, t0);
+  int64_t t = t0;
+  while (t < t1) {
+    const b200q_nvfp4_desc d = descs[ti];
+    const int64_t tensor_tiles = (d.nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
+    const int64_t tend = min(t1, d.tile_begin + tensor_tiles);
+    const T* x = static_cast<const T*>(d.x);
+    uint32_t m = 0;
+    for (; t < tend; ++t) {
+      const int64_t tb = (t - d.tile_begin) * kNvTileBlocks;
+      Block16<T> blk[kNvUnroll];
+#pragma unroll
+      for (int u = 0; u < kNvUnroll; ++u) {
+        const int64_t b = tb + u * kNvThreads + threadIdx.x;
+        if (b < d.nblocks) blk[u].load_keep(x + 16 * b); else blk[u].zero();
+      }
+#pragma unroll
+      for (int u = 0; u < kNvUnroll; ++u) m = max(m, blk[u].amax_f32bits());
+    }
+    m = cta_max_u32(m, red);
+    if (threadIdx.x == 0 && m != 0) {
+      uint32_t* slot = reinterpret_cast<uint32_t*>(d.amax);
+      if (*reinterpret_cast<volatile uint32_t*>(slot) < m) atomicMax(slot, m);
+    }
+    ++ti;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNvThreads)
+nvfp4_group_quantize_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, int64_t total_tiles) {
+  const int64_t per = (total_tiles + gridDim.x - 1) / gridDim.x;
+  const int64_t t0 = blockIdx.x * per, t1 = min(total_tiles, t0 + per);
+  if (t0 >= t1) return;
+  int ti = find_tensor(descs, n, t0);
+  int64_t t = t0;
+  while (t < t1) {
+    const b200q_nvfp4_desc d = descs[ti];
+    const int64_t tensor_tiles = (d.nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
+    const int64_t tend = min(t1, d.tile_begin + tensor_tiles);
+    const T* x = static_cast<const T*>(d.x);
+    const float s2 = __fdiv_rn(*d.amax, 2688.f);
+    const float c = 6.f * s2;
+    if (t == d.tile_begin && threadIdx.x == 0 && d.s2) *d.s2 = s2;
+    for (; t < tend; ++t) {
+      const int64_t tb = (t - d.tile_begin) * kNvTileBlocks;
+      Block16<T> blk[kNvUnroll];
+#pragma unroll
+      for (int u = 0; u < kNvUnroll; ++u) {
+        const int64_t b = tb + u * kNvThreads + threadIdx.x;
+        if (b < d.nblocks) blk[u].load(x + 16 * b);
+      }
+#pragma unroll
+      for (int u = 0; u < kNvUnroll; ++u) {
+        const int64_t b = tb + u * kNvThreads + threadIdx.x;
+        if (b < d.nblocks) nvfp4_quant_block<T>(blk[u], b, s2, c, nullptr, d.packed, d.scales);
+      }
+    }
+    ++ti;
+  }
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+#define B200Q_REQUIRE_ALIGNED32(p) \
+  do {                             \
+    if ((reinterpret_cast<uintptr_t>(p) & 31u) != 0) return B200Q_ERR_ALIGN; \
+  } while (0)
+
+extern "C" int b200q_nvfp4_group_tile_elems(void) { return kNvTileElems; }
+
+extern "C" int b200q_nvfp4_quantize(const void* x, int64_t nblocks, int dtype, const float* global,
+                                    const uint8_t* scales_in, uint8_t* packed, uint8_t* scales,
+                                    float* s2_out, int flags, void* stream) {
+  B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(global); B200Q_REQUIRE_PTR(packed);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED32(x);
+  if ((reinterpret_cast<uintptr_t>(packed) & 7u) != 0) return B200Q_ERR_ALIGN;
+  if (nblocks <= 0) return B200Q_ERR_SHAPE;
+  if (flags & ~B200Q_NVFP4_GLOBAL_IS_SCALE2) return B200Q_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(nblocks, kNvTileBlocks, 8);
+    nvfp4_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(
+        static_cast<const T*>(x), nblocks, global, (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0,
+        scales_in, packed, scales, s2_out);
+    return launch_status();
+  });
+}
+
+extern "C" int b200q_nvfp4_fake(const void* x, void* y, int64_t nblocks, int dtype, const float* amax,
+                                void* stream) {
+  B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(y); B200Q_REQUIRE_PTR(amax);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED32(x); B200Q_REQUIRE_ALIGNED32(y);
+  if (nblocks <= 0) return B200Q_ERR_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(nblocks, kNvTileBlocks, 8);
+    nvfp4_fake_kernel<T><<<grid, kNvThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y),
+                                                     nblocks, amax);
+    return launch_status();
+  });
+}
+
+extern "C" int b200q_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* s2,
+                                      void* y, int64_t nblocks, int dtype, void* stream) {
+  B200Q_REQUIRE_PTR(packed); B200Q_REQUIRE_PTR(scales); B200Q_REQUIRE_PTR(s2); B200Q_REQUIRE_PTR(y);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED32(y);
+  if ((reinterpret_cast<uintptr_t>(packed) & 7u) != 0) return B200Q_ERR_ALIGN;
+  if (nblocks <= 0) return B200Q_ERR_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(nblocks, kNvThreads, 8);
+    nvfp4_dequantize_kernel<T><<<grid, kNvThreads, 0, s>>>(packed, scales, s2, static_cast<T*>(y), nblocks);
+    return launch_status();
+  });
+}
+
+static int check_group(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles, int dtype) {
+  B200Q_REQUIRE_PTR(descs);
+  B200Q_REQUIRE_DTYPE(dtype);
+  if ((reinterpret_cast<uintptr_t>(descs) & 7u) != 0) return B200Q_ERR_ALIGN;
+  if (n <= 0 || total_tiles <= 0) return B200Q_ERR_SHAPE;
+  return B200Q_OK;
+}
+
+extern "C" int b200q_nvfp4_group_amax(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles,
+                                      int dtype, void* stream) {
+  if (int e = check_group(descs, n, total_tiles, dtype)) return e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(total_tiles, 1, 8);
+    nvfp4_group_amax_kernel<T><<<grid, kNvThreads, 0, s>>>(descs, n, total_tiles);
+    return launch_status();
+  });
+}
+
+extern "C" int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles,
+                                          int dtype, void* stream) {
+  if (int e = check_group(descs, n, total_tiles, dtype)) return e;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(total_tiles, 1, 8);
+    nvfp4_group_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(descs, n, total_tiles);
+    return launch_status();
+  });
+}

@@ -1,0 +1,256 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE itself on CPU.
+
+Run in a container that has the reference checkout (default /root/reference):
+
+    python tests/golden/make_golden.py [--ref /path/to/TensorRT-Model-Optimizer]
+
+The reference is imported unmodified with three shims (it cannot be pip-installed offline):
+its distribution version is supplied, the optional ``pulp`` / ``torchprofile`` imports are
+stubbed, and ``fp4_compatible`` is forced False so that NVFP4QTensor.quantize does not probe for
+a GPU.  Inputs are seeded; every file stores inputs and the reference outputs as raw bit
+patterns (uint16 for half/bf16, uint8 for fp8) so that nothing is lost in storage.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.metadata as md
+import sys
+import types
+import warnings
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def import_reference(ref_root: str):
+    real_version = md.version
+
+    def version(name):
+        return "0.40.0" if name == "nvidia-modelopt" else real_version(name)
+
+    md.version = version
+
+    class _Stub(types.ModuleType):
+        def __getattr__(self, k):
+            if k.startswith("__"):
+                raise AttributeError(k)
+            return type(k, (), {})
+
+    for m in ("pulp", "torchprofile", "torchprofile.profile"):
+        sys.modules.setdefault(m, _Stub(m))
+    sys.path.insert(0, ref_root)
+    warnings.filterwarnings("ignore")
+    import modelopt.torch.quantization as mtq  # noqa: F401
+    import modelopt.torch.quantization.qtensor.nvfp4_tensor as nv
+
+    nv.fp4_compatible = lambda: False
+    return mtq
+
+
+TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    """Raw storage of a tensor as a numpy integer array."""
+    t = t.detach().contiguous().cpu()
+    if t.dtype == torch.float32:
+        return t.numpy().copy()
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16).copy()
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy().copy()
+    return t.numpy().copy()
+
+
+def gen(shape, T, seed, scale=1.0, heavy=False):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g)
+    if heavy:  # Student-t(4) like weights with outliers
+        chi = torch.randn((4, *shape), generator=g).pow(2).sum(0) / 4
+        x = x / chi.sqrt()
+    return (x * scale).to(TD[T])
+
+
+def golden_fake_int(out):
+    from modelopt.torch.quantization.tensor_quant import fake_tensor_quant
+    from modelopt.torch.quantization.utils import reduce_amax
+
+    cases = {}
+    i = 0
+    for T in ("f32", "f16", "bf16"):
+        for bits_ in (3, 4, 5, 7, 8, 11):
+            for unsigned in (False, True):
+                for narrow in (True, False):
+                    x = gen((6, 32), T, 100 + i, scale=0.7)
+                    if unsigned:
+                        x = x.abs()
+                    for axis in (None, 0, 1):
+                        if axis is None:
+                            amax = reduce_amax(x) * 0.8
+                        else:
+                            red = [d for d in range(2) if d != axis]
+                            amax = reduce_amax(x, axis=red) * 0.8
+                        y = fake_tensor_quant(x, amax.float(), None, bits_, unsigned, narrow)
+                        k = f"{T}_b{bits_}_u{int(unsigned)}_n{int(narrow)}_a{axis}"
+                        cases[k + "_x"] = bits(x)
+                        cases[k + "_amax"] = bits(amax.float())
+                        cases[k + "_y"] = bits(y)
+                    i += 1
+    # tiny amax -> zeros (epsilon rule), per-channel amax with one dead channel
+    x = gen((8, 32), "f32", 7)
+    amax = torch.full((8, 1), 0.5)
+    amax[3] = 1e-9
+    cases["tiny_x"] = bits(x)
+    cases["tiny_amax"] = bits(amax)
+    cases["tiny_y"] = bits(fake_tensor_quant(x, amax, None, 8, False, True))
+    np.savez_compressed(out / "fake_int.npz", **cases)
+
+
+def golden_fake_e4m3(out):
+    from modelopt.torch.quantization.tensor_quant import scaled_e4m3
+    from modelopt.torch.quantization.utils import reduce_amax
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        x = gen((32, 128), T, 200 + i, scale=3.0)
+        amax = reduce_amax(x)  # in range: the eager cast equals the saturating kernel here
+        cases[f"{T}_x"] = bits(x)
+        cases[f"{T}_amax"] = bits(amax.float())
+        cases[f"{T}_y"] = bits(scaled_e4m3(x, amax, None, 4, 3))
+        cases[f"{T}_y_noamax"] = bits(scaled_e4m3(x, None, None, 4, 3))
+        for axis in (0, 1):
+            am = reduce_amax(x, axis=[1 - axis])
+            cases[f"{T}_amax_a{axis}"] = bits(am.float())
+            cases[f"{T}_y_a{axis}"] = bits(scaled_e4m3(x, am, None, 4, 3))
+    np.savez_compressed(out / "fake_e4m3.npz", **cases)
+
+
+def golden_nvfp4(out):
+    from modelopt.torch.quantization.qtensor import NVFP4QTensor
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        for j, (shape, sc, heavy) in enumerate([((16, 64), 0.02, True), ((8, 48), 1.0, False),
+                                                ((4, 40), 5.0, False)]):
+            x = gen(shape, T, 300 + 10 * i + j, scale=sc, heavy=heavy)
+            if j == 1:
+                x[0, :16] = 0  # an all-zero block
+                x[1, 3] = -0.0
+            q, s, s2 = NVFP4QTensor.quantize(x.clone(), 16)
+            k = f"{T}_{j}"
+            cases[k + "_x"] = bits(x)
+            cases[k + "_packed"] = bits(q._quantized_data)
+            cases[k + "_scales"] = bits(s)
+            cases[k + "_s2"] = bits(s2.reshape(1))
+            if shape[-1] % 16 == 0:  # the reference's dequantize cannot undo its own padding
+                d = q.dequantize(scale=s, double_scale=s2, block_sizes={-1: 16})
+                cases[k + "_deq"] = bits(d)
+            # externally supplied (clipped) amax: block scales may overflow the E4M3 cast
+            s2c = NVFP4QTensor.get_weights_scaling_factor_2(x) * 0.5
+            q2, sb2, _ = NVFP4QTensor.quantize(x.clone(), 16, weights_scaling_factor_2=s2c)
+            cases[k + "_clip_s2"] = bits(s2c.reshape(1))
+            cases[k + "_clip_packed"] = bits(q2._quantized_data)
+            cases[k + "_clip_scales"] = bits(sb2)
+    # _cast_fp4 at and around every rounding boundary, both signs
+    pts = []
+    for b in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.0, 0.5, 1, 1.5, 2, 3, 4, 6, 7.5, 100.0):
+        for d in (0.0, 1e-3, -1e-3, 6e-8, -6e-8):
+            pts += [b + d, -(b + d)]
+    v = torch.tensor(pts + [float("nan"), float("inf"), -float("inf"), -0.0, -1e-30, 1e-30],
+                     dtype=torch.float32)
+    cases["cast_v"] = bits(v)
+    cases["cast_code"] = bits(NVFP4QTensor._cast_fp4(v.clone()))
+    np.savez_compressed(out / "nvfp4.npz", **cases)
+
+
+def golden_int4(out):
+    from modelopt.torch.quantization.qtensor import INT4QTensor
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        for j, (shape, block) in enumerate([((8, 256), 128), ((6, 40), 16), ((2, 24), 32)]):
+            x = gen(shape, T, 400 + 10 * i + j, scale=0.05)
+            q, s = INT4QTensor.quantize(x, block)  # CPU branch of the reference
+            k = f"{T}_{j}"
+            cases[k + "_x"] = bits(x)
+            cases[k + "_block"] = np.array(block)
+            cases[k + "_packed"] = bits(q._quantized_data)
+            cases[k + "_scales"] = bits(s)
+            cases[k + "_deq"] = bits(q.dequantize(scale=s, block_sizes={-1: block}))
+    np.savez_compressed(out / "int4.npz", **cases)
+
+
+def golden_q8(out):
+    from modelopt.torch.quantization.qtensor import FP8QTensor, INT8QTensor
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        x = gen((16, 96), T, 500 + i, scale=2.0)
+        cases[f"{T}_x"] = bits(x)
+        for name, cls in (("fp8", FP8QTensor), ("int8", INT8QTensor)):
+            for tag, kw in (("t", {}), ("a0", {"axis": 0}), ("blk", {"block_sizes": {-1: 32}})):
+                q, s = cls.quantize(x, **kw)
+                cases[f"{T}_{name}_{tag}_q"] = bits(q._quantized_data)
+                cases[f"{T}_{name}_{tag}_s"] = bits(s.reshape(-1))
+    np.savez_compressed(out / "q8.npz", **cases)
+
+
+def golden_amax(out):
+    from modelopt.torch.quantization.calib import MaxCalibrator
+    from modelopt.torch.quantization.utils import reduce_amax, reduce_block_amax
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        x = gen((4, 12, 64), T, 600 + i)
+        cases[f"{T}_x"] = bits(x)
+        cases[f"{T}_all"] = bits(reduce_amax(x).reshape(1))
+        for axis in (0, 1, 2, -1):
+            red = [d for d in range(3) if d != axis % 3]
+            cases[f"{T}_ax{axis}"] = bits(reduce_amax(x, axis=red).reshape(-1))
+        for blk in (16, 32):
+            cases[f"{T}_blk{blk}"] = bits(reduce_block_amax(x, {-1: blk}).reshape(-1))
+        cal = MaxCalibrator(8, 1, False)
+        for b in range(3):
+            cal.collect(gen((4, 12, 64), T, 650 + 3 * i + b, scale=1.0 + b))
+        cases[f"{T}_cal_ax1"] = bits(cal.compute_amax().reshape(-1))
+    np.savez_compressed(out / "amax.npz", **cases)
+
+
+def golden_hist(out):
+    from modelopt.torch.quantization.calib import HistogramCalibrator
+
+    cases = {}
+    cal = HistogramCalibrator(8, None, False, num_bins=2048)
+    for b in range(3):
+        x = gen((64, 512), "bf16", 700 + b, scale=1.0 + 0.6 * b)
+        cases[f"x{b}"] = bits(x)
+        cal.collect(x)
+        cases[f"hist{b}"] = cal._calib_hist.cpu().numpy().astype(np.int64)
+        cases[f"edges{b}"] = cal._calib_bin_edges.cpu().numpy().astype(np.float32)
+    for p in (99.0, 99.9, 99.99, 100.0):
+        cases[f"pct_{p}"] = np.array(cal.compute_amax("percentile", percentile=p).item(), dtype=np.float32)
+    cases["entropy"] = np.array(cal.compute_amax("entropy").item(), dtype=np.float32)
+    np.savez_compressed(out / "hist.npz", **cases)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    import_reference(args.ref)
+    torch.manual_seed(0)
+    fns = {"fake_int": golden_fake_int, "fake_e4m3": golden_fake_e4m3, "nvfp4": golden_nvfp4,
+           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist}
+    for name, fn in fns.items():
+        if args.only and name not in args.only.split(","):
+            continue
+        fn(HERE)
+        print("wrote", name)
+
+
+if __name__ == "__main__":
+    main()

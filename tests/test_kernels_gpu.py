@@ -1,0 +1,385 @@
+"""CUDA kernels (through the C ABI) against the CPU oracle and the reference's golden vectors."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant_oracle as qo
+from _util import f32_from_tensor, load, same_bits, same_values, tensor_from_f32, to_f32, torch_dtype
+
+pytestmark = pytest.mark.gpu
+TS = ("f32", "f16", "bf16")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from b200q import ops as _ops
+
+    return _ops
+
+
+def rnd(shape, T, seed, scale=1.0, heavy=False):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(shape).astype(np.float32)
+    if heavy:
+        x = x / np.sqrt(rng.chisquare(4, shape) / 4).astype(np.float32)
+    return qo.round_to((x * np.float32(scale)).astype(np.float32), T)
+
+
+# ----------------------------------------------------------------------------- amax ------------
+
+@pytest.mark.parametrize("T", TS)
+def test_amax_tensor_axis_blocks_golden(ops, T):
+    g = load("amax")
+    x = to_f32(g[f"{T}_x"], T)
+    xt = tensor_from_f32(x, T)
+    assert same_bits(f32_from_tensor(ops.amax_tensor(xt)).reshape(1), to_f32(g[f"{T}_all"], T))
+    shape = x.shape
+    for axis in (0, 1, 2):
+        outer = int(np.prod(shape[:axis])); inner = int(np.prod(shape[axis + 1:]))
+        got = f32_from_tensor(ops.amax_axis3(xt, outer, shape[axis], inner))
+        assert same_bits(got, to_f32(g[f"{T}_ax{axis}"], T)), axis
+    for blk in (16, 32):
+        assert same_bits(f32_from_tensor(ops.amax_blocks(xt, blk)), to_f32(g[f"{T}_blk{blk}"], T))
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("n", [1, 7, 8, 1000, 4096 * 33 + 5, 1 << 22])
+def test_amax_tensor_sizes(ops, T, n):
+    x = rnd((n,), T, n)
+    got = f32_from_tensor(ops.amax_tensor(tensor_from_f32(x, T)))
+    assert got == np.abs(x).max()
+
+
+def test_amax_running_and_nan(ops):
+    a = tensor_from_f32(rnd((4096,), "bf16", 1), "bf16")
+    b = tensor_from_f32(rnd((4096,), "bf16", 2, scale=3.0), "bf16")
+    out = ops.amax_tensor(a)
+    ops.amax_tensor(b, out=out)
+    assert out.item() == max(a.abs().max().item(), b.abs().max().item())
+    c = a.clone(); c[17] = float("nan")
+    assert torch.isnan(ops.amax_tensor(c))
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8192, 512, 1), (3, 40, 24), (2, 5, 7), (300, 1024, 1),
+                                   (1, 3, 100000)])
+def test_amax_axis_shapes(ops, T, shape):
+    x = rnd(shape, T, sum(shape))
+    got = f32_from_tensor(ops.amax_axis3(tensor_from_f32(x, T), *shape))
+    assert same_bits(got, np.abs(x).max(axis=(0, 2)))
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("block", [8, 16, 32, 128, 256, 24, 4096])
+def test_amax_blocks(ops, T, block):
+    x = rnd((37 * block,), T, block)
+    got = f32_from_tensor(ops.amax_blocks(tensor_from_f32(x, T), block))
+    assert same_bits(got, np.abs(x.reshape(-1, block)).max(-1))
+
+
+# ----------------------------------------------------------------------------- int fake quant --
+
+def test_fake_int_golden_grid(ops):
+    """Reference grid: bits x signed/unsigned x narrow x dtype x {per tensor, axis 0, axis 1}."""
+    g = load("fake_int")
+    for T in TS:
+        for bits in (3, 4, 5, 7, 8, 11):
+            for u in (0, 1):
+                for nr in (0, 1):
+                    for axis in (None, 0, 1):
+                        k = f"{T}_b{bits}_u{u}_n{nr}_a{axis}"
+                        x = to_f32(g[k + "_x"], T)
+                        amax = torch.from_numpy(g[k + "_amax"]).cuda()
+                        y = ops.fake_int(tensor_from_f32(x, T), amax, bits, bool(u), bool(nr))
+                        assert same_values(f32_from_tensor(y), to_f32(g[k + "_y"], T)), k
+                        want = qo.fake_int(x, g[k + "_amax"], bits, bool(u), bool(nr), T)
+                        assert same_bits(f32_from_tensor(y), want), k
+
+
+def test_fake_int_tiny_amax_is_zero(ops):
+    g = load("fake_int")
+    y = ops.fake_int(torch.from_numpy(g["tiny_x"]).cuda(), torch.from_numpy(g["tiny_amax"]).cuda(), 8, False, True)
+    assert same_values(f32_from_tensor(y), g["tiny_y"])
+    x = torch.randn(1000, device="cuda")
+    assert torch.all(ops.fake_int(x, torch.tensor(1e-9, device="cuda")) == 0)
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("shape,axis", [((1024, 4096), 0), ((512, 1024), 1), ((33, 100), 0), ((33, 100), 1),
+                                        ((4, 64, 24), 1), ((1, 5, 3), 2), ((7, 1037), None)])
+def test_fake_int_layouts(ops, T, shape, axis):
+    x = rnd(shape, T, 11 + len(shape), scale=0.02)
+    if axis is None:
+        amax = np.float32(np.abs(x).max() * 0.9).reshape(())
+    else:
+        red = tuple(d for d in range(len(shape)) if d != axis)
+        amax = (np.abs(x).max(axis=red, keepdims=True) * np.float32(0.9)).astype(np.float32)
+    y = ops.fake_int(tensor_from_f32(x, T), torch.from_numpy(np.asarray(amax)).cuda(), 8, False, True)
+    assert same_bits(f32_from_tensor(y), qo.fake_int(x, amax, 8, False, True, T))
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("rows,cols,bits,narrow", [(4096, 4096, 8, True), (1000, 128, 4, False), (77, 16, 4, False),
+                                                   (5, 1024, 8, True), (9, 8200, 8, True), (3, 32768, 8, True),
+                                                   (64, 24, 4, False)])
+def test_fake_int_rows_dynamic(ops, T, rows, cols, bits, narrow):
+    x = rnd((rows, cols), T, rows + cols, scale=0.02)
+    if T == "f32" and cols > 32768 // 1:
+        pytest.skip("row too long for the fused kernel")
+    y, am = ops.fake_int_rows_dynamic(tensor_from_f32(x, T), bits, False, narrow, return_amax=True)
+    amax = np.abs(x).max(-1, keepdims=True)
+    assert same_bits(f32_from_tensor(am), amax.reshape(-1))
+    assert same_bits(f32_from_tensor(y), qo.fake_int(x, amax, bits, False, narrow, T))
+
+
+# ----------------------------------------------------------------------------- FP8 fake --------
+
+@pytest.mark.parametrize("T", TS)
+def test_fake_e4m3_golden(ops, T):
+    """In-range data: the reference's eager path and the saturating kernel agree except for the
+    last-bit difference of reciprocal-times-448 vs 448/amax, which the oracle models both ways."""
+    g = load("fake_e4m3")
+    x = to_f32(g[f"{T}_x"], T)
+    xt = tensor_from_f32(x, T)
+    y = ops.fake_e4m3(xt, None)
+    assert same_bits(f32_from_tensor(y), to_f32(g[f"{T}_y_noamax"], T))
+    amax = g[f"{T}_amax"]
+    y = ops.fake_e4m3(xt, torch.from_numpy(amax).cuda())
+    assert same_bits(f32_from_tensor(y), qo.fake_e4m3(x, amax, T))
+    for axis in (0, 1):
+        am = g[f"{T}_amax_a{axis}"]
+        y = ops.fake_e4m3(xt, torch.from_numpy(am).cuda())
+        assert same_bits(f32_from_tensor(y), qo.fake_e4m3(x, am, T)), axis
+
+
+@pytest.mark.parametrize("T", TS)
+def test_fake_e4m3_saturates_and_all_codes(ops, T):
+    # every E4M3 value and every midpoint between neighbours, both signs, plus out-of-range values
+    vals = qo.e4m3_decode(np.arange(0, 127, dtype=np.uint8)).astype(np.float64)
+    mids = (vals[1:] + vals[:-1]) / 2
+    pts = np.concatenate([vals, mids, mids * (1 + 2 ** -12), mids * (1 - 2 ** -12), [470, 1000, 3e38, 0]])
+    pts = np.concatenate([pts, -pts]).astype(np.float32)
+    x = qo.round_to(pts, T)
+    pad = (-x.size) % 16
+    x = np.concatenate([x, np.zeros(pad, np.float32)])
+    y = ops.fake_e4m3(tensor_from_f32(x, T), None)
+    assert same_bits(f32_from_tensor(y), qo.fake_e4m3(x, None, T))
+    amax = np.float32(300.0)  # calibrated amax below the data: the kernel saturates at +-amax-ish
+    y = ops.fake_e4m3(tensor_from_f32(x, T), torch.tensor(300.0, device="cuda"))
+    want = qo.fake_e4m3(x, amax, T)
+    assert same_bits(f32_from_tensor(y), want)
+    assert np.isfinite(want[np.isfinite(x)]).all()
+
+
+def test_fake_e4m3_config2_shape_bf16(ops):
+    g = torch.Generator().manual_seed(1000)
+    x = torch.randn(8192, 4096, generator=g)
+    idx = torch.randperm(4096, generator=torch.Generator().manual_seed(7))[:4]
+    x[:, idx] *= 50
+    x = x.bfloat16()
+    xt = x.cuda()
+    amax = ops.amax_tensor(xt)
+    assert amax.item() == x.float().abs().max().item()
+    y = ops.fake_e4m3(xt, amax)
+    want = qo.fake_e4m3(x.float().numpy(), np.float32(amax.item()), "bf16")
+    assert same_bits(f32_from_tensor(y), want)
+
+
+# ----------------------------------------------------------------------------- NVFP4 -----------
+
+@pytest.mark.parametrize("T", TS)
+def test_nvfp4_golden(ops, T):
+    g = load("nvfp4")
+    for j in range(3):
+        k = f"{T}_{j}"
+        x = to_f32(g[k + "_x"], T)
+        x = qo.pad_last(x, 16)
+        xt = tensor_from_f32(x, T)
+        packed, scales, s2 = ops.nvfp4_quantize(xt)
+        assert np.array_equal(packed.cpu().numpy(), g[k + "_packed"]), k
+        assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), g[k + "_scales"]), k
+        assert same_bits(f32_from_tensor(s2).reshape(1), g[k + "_s2"]), k
+        if k + "_deq" in g:
+            d = ops.nvfp4_dequantize(packed, scales, s2, torch_dtype(T))
+            assert same_bits(f32_from_tensor(d), to_f32(g[k + "_deq"], T)), k
+        s2c = torch.from_numpy(g[k + "_clip_s2"]).cuda()
+        p2, sc2, _ = ops.nvfp4_quantize(xt, scale2=s2c)
+        assert np.array_equal(sc2.view(torch.uint8).cpu().numpy(), g[k + "_clip_scales"]), k
+        assert np.array_equal(p2.cpu().numpy(), g[k + "_clip_packed"]), k
+
+
+def test_nvfp4_every_rounding_boundary(ops):
+    """_cast_fp4 golden points: with amax = 2688 the global scale is 1 and a block whose max is 6
+    gets block scale 1, so the codes are those of the raw values."""
+    g = load("nvfp4")
+    v = g["cast_v"]
+    v = v[np.isfinite(v) & (np.abs(v) <= 6)]
+    code = qo.e2m1_encode(v)
+    blocks = []
+    for i in range(0, v.size, 15):
+        chunk = v[i:i + 15]
+        blocks.append(np.concatenate([chunk, np.zeros(15 - chunk.size, np.float32), [6.0]]))
+    x = np.stack(blocks).astype(np.float32)
+    packed, scales, s2 = ops.nvfp4_quantize(torch.from_numpy(x).cuda(), amax=torch.tensor(2688.0))
+    assert s2.item() == 1.0 and (scales.float() == 1).all()
+    p = packed.cpu().numpy()
+    got = np.stack([p & 15, p >> 4], -1).reshape(x.shape)
+    want = qo.e2m1_encode(x)
+    assert np.array_equal(got, want)
+    assert np.array_equal(got[:, :15].reshape(-1)[: v.size], code)
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("shape,scale,heavy", [((1024, 4096), 0.02, True), ((333, 48), 1.0, False),
+                                               ((1, 16), 3.0, False), ((4096, 14336), 0.02, True)])
+def test_nvfp4_quantize_vs_oracle(ops, T, shape, scale, heavy):
+    if shape[0] * shape[1] > 2 ** 24 and T != "bf16":
+        pytest.skip("large case only in bf16")
+    x = rnd(shape, T, shape[1], scale, heavy)
+    packed, scales, s2 = ops.nvfp4_quantize(tensor_from_f32(x, T))
+    wp, ws, ws2 = qo.nvfp4_quantize(x, 16)
+    assert s2.item() == ws2
+    assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), ws)
+    assert np.array_equal(packed.cpu().numpy(), wp)
+    d = ops.nvfp4_dequantize(packed, scales, s2, torch_dtype(T))
+    assert same_bits(f32_from_tensor(d), qo.nvfp4_dequantize(wp, ws, ws2, 16, T))
+
+
+@pytest.mark.parametrize("T", TS)
+def test_nvfp4_fake_vs_oracle(ops, T):
+    x = rnd((512, 1024), T, 5, 1.0)
+    x[0, :16] = 0
+    x[1, :16] = 1e-9  # tiny block: keeps its (tiny) scale in the canonical definition
+    x[2, 5] = -0.0
+    xt = tensor_from_f32(x, T)
+    amax = np.float32(np.abs(x).max())
+    y = ops.nvfp4_fake(xt, torch.tensor(float(amax)))
+    assert same_bits(f32_from_tensor(y), qo.nvfp4_fake(x, amax, 16, T))
+    # calibrated amax below the data: block scales saturate at 448 instead of becoming NaN
+    y = ops.nvfp4_fake(xt, torch.tensor(float(amax) / 4))
+    want = qo.nvfp4_fake(x, amax / 4, 16, T)
+    assert np.isfinite(want).all()
+    assert same_bits(f32_from_tensor(y), want)
+
+
+def test_nvfp4_supplied_block_scales(ops):
+    x = rnd((64, 256), "bf16", 9, 0.02, True)
+    xt = tensor_from_f32(x, "bf16")
+    _, scales, s2 = ops.nvfp4_quantize(xt)
+    sc = scales.view(torch.uint8).clone()
+    sc[:, ::2] = torch.clamp(sc[:, ::2].int() - 3, min=1).to(torch.uint8)  # perturb: forces saturation
+    packed, sc_out, _ = ops.nvfp4_quantize(xt, scale2=s2, scales_in=sc)
+    wp, _, _ = qo.nvfp4_quantize(x, 16, s2=np.float32(s2.item()), scales=sc.cpu().numpy())
+    assert np.array_equal(packed.cpu().numpy(), wp)
+    assert torch.equal(sc_out.view(torch.uint8), sc)
+
+
+def test_nvfp4_group_matches_single(ops):
+    shapes = [(256, 4096), (64, 4096), (1024, 1024), (48, 16), (4096, 1440)]
+    ts = [tensor_from_f32(rnd(s, "bf16", i + 40, 0.02, True), "bf16") for i, s in enumerate(shapes)]
+    grp = ops.NvFp4Group(ts)
+    packed, scales, s2 = grp.run()
+    torch.cuda.synchronize()
+    for i, t in enumerate(ts):
+        p1, sc1, s21 = ops.nvfp4_quantize(t)
+        assert torch.equal(packed[i], p1), i
+        assert torch.equal(scales[i].view(torch.uint8), sc1.view(torch.uint8)), i
+        assert s2[i].item() == s21.item(), i
+        assert grp.amax[i].item() == t.abs().max().item()
+    # a second run gives the same bytes (amax slots are reset, nothing accumulates)
+    before = [p.clone() for p in packed]
+    grp.run()
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(before, grp.packed))
+
+
+# ----------------------------------------------------------------------------- INT4 ------------
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("n,block", [(4096 * 128, 128), (77 * 16, 16), (13 * 32, 32), (5 * 24, 24), (3 * 1024, 1024)])
+def test_int4_quantize_vs_oracle(ops, T, n, block):
+    x = rnd((n,), T, n % 1000, 0.05)
+    packed, scales = ops.int4_quantize(tensor_from_f32(x, T), block)
+    wp, ws = qo.int4_quantize(x, block, T, flavour="kernel")
+    assert same_bits(f32_from_tensor(scales), ws)
+    assert np.array_equal(packed.cpu().numpy(), wp)
+    d = ops.int4_dequantize(packed, scales, block)
+    assert same_bits(f32_from_tensor(d), qo.int4_dequantize(wp, ws, block, T))
+
+
+def test_int4_known_answers(ops):
+    x = np.zeros(16, dtype=np.float32)
+    x[:8] = [7, -7, 0.5, -0.5, 1.5, 2.5, -2.5, 6.5]
+    p, s = ops.int4_quantize(torch.from_numpy(x).cuda(), 16)
+    codes = np.stack([p.cpu().numpy() >> 4, p.cpu().numpy() & 15], -1).reshape(-1)[:8]
+    assert list(codes) == [15, 1, 9, 8, 10, 11, 6, 15]
+    x2 = np.zeros(16, dtype=np.float32); x2[0], x2[1] = 7.0, 0.484375
+    p2, _ = ops.int4_quantize(torch.from_numpy(x2).cuda().bfloat16(), 16)
+    assert p2[0].item() == ((15 << 4) | 9)
+
+
+@pytest.mark.parametrize("T", TS)
+def test_int4_golden_where_kernel_and_cpu_branch_agree(ops, T):
+    """The reference's CPU branch pins scales exactly and codes wherever no .5 tie / T rounding of
+    y+8 is involved (the oracle's two flavours mark those positions)."""
+    g = load("int4")
+    for j in range(3):
+        k = f"{T}_{j}"
+        x = to_f32(g[k + "_x"], T)
+        block = int(g[k + "_block"])
+        xp = qo.pad_last(x.reshape(-1), block)
+        packed, scales = ops.int4_quantize(tensor_from_f32(xp, T), block)
+        assert same_bits(f32_from_tensor(scales).reshape(-1), to_f32(g[k + "_scales"], T).reshape(-1)), k
+        pk, _ = qo.int4_quantize(x, block, T, flavour="kernel")
+        pc, _ = qo.int4_quantize(x, block, T, flavour="cpu")
+        got = packed.cpu().numpy()
+        assert np.array_equal(got, pk), k
+        agree = pk == pc
+        assert np.array_equal(got[agree], g[k + "_packed"].reshape(-1)[agree]), k
+
+
+# ----------------------------------------------------------------------------- FP8 / INT8 ------
+
+@pytest.mark.parametrize("T", TS)
+def test_q8_golden(ops, T):
+    g = load("q8")
+    x = to_f32(g[f"{T}_x"], T)
+    xt = tensor_from_f32(x, T)
+    for name, fn in (("fp8", ops.fp8_quantize), ("int8", ops.int8_quantize)):
+        for tag, (outer, axis, inner) in (("t", (1, 1, x.size)), ("a0", (1, 16, 96)), ("blk", (1, 48, 32))):
+            s = tensor_from_f32(to_f32(g[f"{T}_{name}_{tag}_s"], T), T)
+            q = fn(xt, s, outer, axis, inner)
+            assert np.array_equal(q.view(torch.uint8).cpu().numpy().reshape(-1),
+                                  g[f"{T}_{name}_{tag}_q"].view(np.uint8).reshape(-1)), (name, tag)
+
+
+# ----------------------------------------------------------------------------- histogram -------
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("nbins", [128, 2048, 5000, 20000])
+def test_hist_collect_vs_oracle(ops, T, nbins):
+    x = rnd((1 << 20,), T, nbins, 1.0, heavy=True)
+    xt = tensor_from_f32(x, T)
+    rmax = float(np.abs(x).max()) * 0.7  # some samples fall outside and are dropped
+    counts = torch.zeros(nbins, dtype=torch.int64, device="cuda")
+    ops.hist_collect(xt, counts, nbins, rmax)
+    want = qo.hist_bins(x, nbins, rmax)
+    assert np.array_equal(counts.cpu().numpy(), want)
+    ops.hist_collect(xt, counts, nbins, rmax)  # accumulates
+    assert np.array_equal(counts.cpu().numpy(), 2 * want)
+
+
+def test_hist_golden_and_percentile(ops):
+    g = load("hist")
+    x = to_f32(g["x0"], "bf16")
+    counts = torch.zeros(2048, dtype=torch.int64, device="cuda")
+    rmax = float(np.abs(x).max())
+    ops.hist_collect(tensor_from_f32(x, "bf16"), counts, 2048, rmax)
+    ref = g["hist0"]
+    got = counts.cpu().numpy()
+    assert got.sum() == ref.sum()
+    assert np.abs(got - ref).sum() <= 2e-3 * ref.sum()
+    for p in (99.0, 99.9, 99.99, 100.0):
+        want, _ = qo.percentile_amax(got, g["edges0"], p)
+        a = ops.hist_percentile(counts, 2048, torch.from_numpy(g["edges0"]), 0.0, p)
+        assert a.item() == want

@@ -1,0 +1,165 @@
+"""The CPU oracle against golden vectors produced by the reference itself (CPU, no GPU needed)."""
+import numpy as np
+import pytest
+
+from oracle import quant_oracle as qo
+from _util import load, same_bits, same_values, to_f32
+
+TS = ("f32", "f16", "bf16")
+
+
+def test_fake_int_matches_reference_cpu_path():
+    g = load("fake_int")
+    n = 0
+    for T in TS:
+        for bits in (3, 4, 5, 7, 8, 11):
+            for u in (0, 1):
+                for nr in (0, 1):
+                    for axis in (None, 0, 1):
+                        k = f"{T}_b{bits}_u{u}_n{nr}_a{axis}"
+                        x = to_f32(g[k + "_x"], T)
+                        amax = g[k + "_amax"]
+                        y = qo.fake_int(x, amax, bits, bool(u), bool(nr), T, cpu_flavour=True)
+                        assert same_values(y, to_f32(g[k + "_y"], T)), k
+                        # kernel flavour differs only in the epsilon rule and the unsigned floor
+                        y2 = qo.fake_int(x, amax, bits, bool(u), bool(nr), T)
+                        assert same_values(y2, y), k
+                        n += 1
+    assert n == 216
+    y = qo.fake_int(g["tiny_x"], g["tiny_amax"], 8, False, True, "f32", cpu_flavour=True)
+    assert same_values(y, g["tiny_y"])
+    assert np.all(y[3] == 0)
+
+
+def test_fake_e4m3_matches_reference_eager():
+    g = load("fake_e4m3")
+    for T in TS:
+        x = to_f32(g[f"{T}_x"], T)
+        assert same_bits(qo.fake_e4m3(x, g[f"{T}_amax"], T, eager=True), to_f32(g[f"{T}_y"], T)), T
+        assert same_bits(qo.fake_e4m3(x, None, T), to_f32(g[f"{T}_y_noamax"], T)), T
+        for axis in (0, 1):
+            y = qo.fake_e4m3(x, g[f"{T}_amax_a{axis}"], T, eager=True)
+            assert same_bits(y, to_f32(g[f"{T}_y_a{axis}"], T)), (T, axis)
+
+
+def test_e4m3_encode_edges():
+    v = np.array([448, 463, 464, 465, 480, 1000, np.nan, -465, -448, 0, -0.0, 2 ** -9, 2 ** -10,
+                  1.5 * 2 ** -10, 0.0009765625 * 3], dtype=np.float32)
+    t = qo.e4m3_encode(v, "torch")
+    assert list(t[:9]) == [126, 126, 126, 127, 127, 127, 127, 255, 254]
+    s = qo.e4m3_encode(v, "sat")
+    assert list(s[:9]) == [126, 126, 126, 126, 126, 126, 127, 254, 254]
+    # smallest subnormal 2^-9; half of it ties to even (0); 1.5*2^-10 rounds up
+    assert list(s[9:14]) == [0, 0x80, 1, 0, 1]
+    # round trip of every code
+    codes = np.arange(256, dtype=np.uint8)
+    vals = qo.e4m3_decode(codes)
+    ok = ~np.isnan(vals)
+    back = qo.e4m3_encode(vals[ok], "sat")
+    assert np.array_equal(back, codes[ok])
+
+
+def test_nvfp4_matches_reference():
+    g = load("nvfp4")
+    assert np.array_equal(qo.e2m1_encode(g["cast_v"]), g["cast_code"])
+    for T in TS:
+        for j in range(3):
+            k = f"{T}_{j}"
+            x = to_f32(g[k + "_x"], T)
+            packed, scales, s2 = qo.nvfp4_quantize(x, 16)
+            assert np.array_equal(packed, g[k + "_packed"]), k
+            assert np.array_equal(scales, g[k + "_scales"]), k
+            assert same_bits(np.array([s2]), g[k + "_s2"]), k
+            if k + "_deq" in g:
+                d = qo.nvfp4_dequantize(packed, scales, s2, 16, T)
+                assert same_bits(d, to_f32(g[k + "_deq"], T)), k
+            p2, sc2, _ = qo.nvfp4_quantize(x, 16, s2=g[k + "_clip_s2"][0])
+            assert np.array_equal(sc2, g[k + "_clip_scales"]), k
+            assert np.array_equal(p2, g[k + "_clip_packed"]), k
+    # the clipped case really exercises the overflowing block-scale cast
+    assert any((g[f"{T}_{j}_clip_scales"] == 0x7F).any() for T in TS for j in range(3))
+
+
+def test_int4_cpu_flavour_matches_reference_and_kernel_flavour_differs_only_at_ties():
+    g = load("int4")
+    for T in TS:
+        for j in range(3):
+            k = f"{T}_{j}"
+            x = to_f32(g[k + "_x"], T)
+            block = int(g[k + "_block"])
+            packed, scales = qo.int4_quantize(x, block, T, flavour="cpu")
+            assert same_bits(scales.reshape(-1), to_f32(g[k + "_scales"], T).reshape(-1)), k
+            assert np.array_equal(packed, g[k + "_packed"].reshape(-1)), k
+            deq = qo.int4_dequantize(packed, scales, block, T)[: x.size]
+            assert same_values(deq, to_f32(g[k + "_deq"], T).reshape(-1)), k
+            pk, _ = qo.int4_quantize(x, block, T, flavour="kernel")
+            hi = lambda p: (p >> 4).astype(int)  # noqa: E731
+            lo = lambda p: (p & 15).astype(int)  # noqa: E731
+            assert np.abs(hi(pk) - hi(packed)).max() <= 1 and np.abs(lo(pk) - lo(packed)).max() <= 1
+            assert (pk != packed).mean() < (0.2 if T == "bf16" else 0.02), k
+
+
+def test_int4_kernel_flavour_known_answers():
+    # scale 1: values straight onto the grid; .5 ties round away from zero; bf16 rounds y+8 first
+    x = np.zeros(16, dtype=np.float32)
+    x[:8] = [7, -7, 0.5, -0.5, 1.5, 2.5, -2.5, 6.5]
+    pk, sc = qo.int4_quantize(x, 16, "f32", flavour="kernel")
+    assert sc[0, 0] == 1.0
+    codes = np.stack([pk >> 4, pk & 15], -1).reshape(-1)[:8]
+    assert list(codes) == [15, 1, 9, 8, 10, 11, 6, 15]
+    # bf16: 0.484375 + 8 = 8.484375 -> bf16 spacing 1/16 -> 8.5 -> roundf -> 9 (exact math gives 8)
+    x2 = np.zeros(16, dtype=np.float32)
+    x2[0], x2[1] = 7.0, 0.484375
+    pk2, _ = qo.int4_quantize(x2, 16, "bf16", flavour="kernel")
+    assert pk2[0] == ((15 << 4) | 9)
+    pk3, _ = qo.int4_quantize(x2, 16, "f32", flavour="kernel")
+    assert pk3[0] == ((15 << 4) | 8)
+
+
+def test_q8_matches_reference():
+    g = load("q8")
+    for T in TS:
+        x = to_f32(g[f"{T}_x"], T)
+        for name, fn in (("fp8", qo.fp8_quantize), ("int8", qo.int8_quantize)):
+            s = to_f32(g[f"{T}_{name}_t_s"], T)
+            q = fn(x, s.reshape(()), T)
+            assert np.array_equal(q.view(np.uint8), g[f"{T}_{name}_t_q"].view(np.uint8)), (T, name)
+            s = to_f32(g[f"{T}_{name}_a0_s"], T)
+            q = fn(x, s.reshape(-1, 1), T)
+            assert np.array_equal(q.view(np.uint8), g[f"{T}_{name}_a0_q"].view(np.uint8)), (T, name)
+            s = to_f32(g[f"{T}_{name}_blk_s"], T)
+            q = fn(x.reshape(16, 3, 32), s.reshape(16, 3, 1), T).reshape(16, 96)
+            assert np.array_equal(q.view(np.uint8), g[f"{T}_{name}_blk_q"].view(np.uint8)), (T, name)
+
+
+def test_amax_matches_reference():
+    g = load("amax")
+    for T in TS:
+        x = to_f32(g[f"{T}_x"], T)
+        assert same_bits(qo.reduce_amax(x).reshape(1), to_f32(g[f"{T}_all"], T))
+        for axis in (0, 1, 2, -1):
+            red = qo.quant_axis_to_reduce_axis(3, axis)
+            assert same_bits(qo.reduce_amax(x, red).reshape(-1), to_f32(g[f"{T}_ax{axis}"], T))
+        for blk in (16, 32):
+            assert same_bits(qo.reduce_block_amax(x, blk).reshape(-1), to_f32(g[f"{T}_blk{blk}"], T))
+
+
+def test_histogram_matches_reference_within_tolerance():
+    """Counts are tolerance-compared: the reference ran torch's CPU histc here, whose edge
+    placement differs from the CUDA formula the oracle restates by a few samples per edge."""
+    g = load("hist")
+    h = qo.HistogramOracle(2048)
+    for b in range(3):
+        x = to_f32(g[f"x{b}"], "bf16")
+        h.collect(x)
+        ref = g[f"hist{b}"]
+        assert h.hist.size == ref.size, b
+        assert h.hist.sum() == ref.sum(), b
+        assert np.abs(h.hist - ref).sum() <= 2e-3 * ref.sum(), b
+        assert np.allclose(h.edges, g[f"edges{b}"], rtol=1e-5, atol=0), b
+    for p in (99.0, 99.9, 99.99, 100.0):
+        amax, _ = qo.percentile_amax(h.hist, h.edges, p)
+        assert abs(amax - g[f"pct_{p}"]) <= 1e-3 * g[f"pct_{p}"], p
+    # entropy on the reference's own histogram: exact same algorithm -> same edge
+    amax = qo.entropy_amax(g["hist2"], g["edges2"], 8, False)
+    assert abs(amax - g["entropy"]) <= 1e-3 * g["entropy"]
