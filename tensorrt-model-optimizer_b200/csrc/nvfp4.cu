@@ -108,28 +108,86 @@ template <> struct Block16<__half> {
 };
 
 // ---- per-block arithmetic ----------------------------------------------------------------------
-// block scale code from the block abs-max; c = 6*s2
+// Correctly rounded a/d for two lanes at once, given y = RN(1/d) and nd = -d.  The first product
+// is within 1.5 ulp of the quotient; one residual correction makes it faithful and, by Markstein's
+// theorem (y correctly rounded, quotient faithful, residual exact in an FMA), the second correction
+// rounds to RN(a/d).  Callers guarantee d, a/d in the normal range with no overflow.  A zero
+// numerator of either sign comes out as +0 ((+0) + (-0) = +0 in the corrections).
+__device__ __forceinline__ float2 div2_rn(float2 a, float2 nd, float2 y) {
+  float2 q = __fmul2_rn(a, y);
+  float2 e = __ffma2_rn(q, nd, a);
+  q = __ffma2_rn(e, y, q);
+  e = __ffma2_rn(q, nd, a);
+  return __ffma2_rn(e, y, q);
+}
+__device__ __forceinline__ float div1_rn(float a, float d, float y) {
+  float q = a * y;
+  float e = fmaf(-q, d, a);
+  q = fmaf(e, y, q);
+  e = fmaf(-q, d, a);
+  return fmaf(e, y, q);
+}
+
+constexpr float kTwoP60 = 1152921504606846976.f;        // 2^60
+constexpr float kTwoM60 = 8.673617379884035e-19f;       // 2^-60
+
+// Per-tensor constants of the two-level scaling.
+struct Nvfp4Tensor {
+  float s2;    // weights_scaling_factor_2
+  float c;     // 6 * s2
+  float rc;    // RN(1/c) when c is in the safe range
+  bool c_ok;
+  __device__ __forceinline__ explicit Nvfp4Tensor(float s2_) : s2(s2_) {
+    c = 6.f * s2;
+    c_ok = c >= kTwoM60 && c <= kTwoP60;
+    rc = __frcp_rn(c);
+  }
+};
+
+// block scale code from the block abs-max: t = bamax/c (IEEE quotient), 0 -> 1, cast to E4M3
 template <bool kTorchCast>
-__device__ __forceinline__ uint32_t nvfp4_scale_code(float bamax, float c) {
-  float t = __fdiv_rn(bamax, c);
+__device__ __forceinline__ uint32_t nvfp4_scale_code(float bamax, const Nvfp4Tensor& tn) {
+  float t;
+  if (tn.c_ok && (bamax == 0.f || (bamax >= kTwoM60 && bamax <= kTwoP60)))
+    t = div1_rn(bamax, tn.c, tn.rc);
+  else
+    t = __fdiv_rn(bamax, tn.c);
   if (t == 0.f) t = 1.f;
   return kTorchCast ? f32_to_e4m3_torch(t) : f32_to_e4m3_sat(t);
 }
 
-// 16 values -> 8 bytes of E2M1 codes under divisor d.  x/d is the IEEE quotient; adding +0
-// turns a negative-zero quotient into +0 so that only values below zero carry the sign bit.
-__device__ __forceinline__ uint2 nvfp4_encode16(const float* f, float d) {
+// 16 values -> 8 bytes of E2M1 codes under divisor d = float(block scale) * s2.
+// Fast path (16-bit inputs, divisor and block abs-max in a safe range — every ordinary block):
+// quotients through div2_rn with one reciprocal per block.  Otherwise the IEEE division per
+// element, with +0 added so that a negative-zero quotient does not set the sign bit.
+template <bool kAllowFast>
+__device__ __forceinline__ uint2 nvfp4_encode16(const float* f, float d, float bamax) {
   uint32_t w[2];
+  if (kAllowFast && d >= kTwoM60 && d <= 65536.f && bamax <= kTwoP60) {
+    const float r = __frcp_rn(d);
+    const float2 y = make_float2(r, r), nd = make_float2(-d, -d);
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    uint32_t acc = 0;
+    for (int h = 0; h < 2; ++h) {
+      uint32_t acc = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float e = __fdiv_rn(f[8 * h + 2 * j], d) + 0.f;
-      const float o = __fdiv_rn(f[8 * h + 2 * j + 1], d) + 0.f;
-      acc |= f32x2_to_e2m1x2(e, o) << (8 * j);
+      for (int j = 0; j < 4; ++j) {
+        const float2 q = div2_rn(make_float2(f[8 * h + 2 * j], f[8 * h + 2 * j + 1]), nd, y);
+        acc |= f32x2_to_e2m1x2(q.x, q.y) << (8 * j);
+      }
+      w[h] = acc;
     }
-    w[h] = acc;
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float e = __fdiv_rn(f[8 * h + 2 * j], d) + 0.f;
+        const float o = __fdiv_rn(f[8 * h + 2 * j + 1], d) + 0.f;
+        acc |= f32x2_to_e2m1x2(e, o) << (8 * j);
+      }
+      w[h] = acc;
+    }
   }
   return make_uint2(w[0], w[1]);
 }
@@ -167,17 +225,18 @@ template <> __device__ __forceinline__ void store16<__half>(__half* y, const flo
 
 // Quantise one loaded block and store codes + scale.
 template <typename T>
-__device__ __forceinline__ void nvfp4_quant_block(const Block16<T>& blk, int64_t b, float s2, float c,
+__device__ __forceinline__ void nvfp4_quant_block(const Block16<T>& blk, int64_t b, const Nvfp4Tensor& tn,
                                                   const uint8_t* __restrict__ scales_in,
                                                   uint8_t* __restrict__ packed,
                                                   uint8_t* __restrict__ scales) {
+  const float bamax = __uint_as_float(blk.amax_f32bits());
   uint32_t code;
   if (scales_in) code = scales_in[b];
-  else code = nvfp4_scale_code<true>(__uint_as_float(blk.amax_f32bits()), c);
-  const float d = e4m3_to_f32(code) * s2;
+  else code = nvfp4_scale_code<true>(bamax, tn);
+  const float d = e4m3_to_f32(code) * tn.s2;
   float f[16];
   blk.decode(f);
-  st_stream(packed + 8 * b, nvfp4_encode16(f, d));
+  st_stream(packed + 8 * b, nvfp4_encode16<sizeof(T) == 2>(f, d, bamax));
   if (scales) scales[b] = static_cast<uint8_t>(code);
 }
 
@@ -189,9 +248,8 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __r
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
                       float* __restrict__ s2_out) {
   const float g = __ldg(global);
-  const float s2 = global_is_s2 ? g : __fdiv_rn(g, 2688.f);
-  const float c = 6.f * s2;
-  if (s2_out && blockIdx.x == 0 && threadIdx.x == 0) *s2_out = s2;
+  const Nvfp4Tensor tn(global_is_s2 ? g : __fdiv_rn(g, 2688.f));
+  if (s2_out && blockIdx.x == 0 && threadIdx.x == 0) *s2_out = tn.s2;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t b0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b0 < nblocks;
        b0 += kNvUnroll * stride) {
@@ -204,7 +262,7 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __r
 #pragma unroll
     for (int u = 0; u < kNvUnroll; ++u) {
       const int64_t b = b0 + u * stride;
-      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, s2, c, scales_in, packed, scales);
+      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, tn, scales_in, packed, scales);
     }
   }
 }
@@ -213,8 +271,7 @@ template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
                   const float* __restrict__ amax) {
-  const float s2 = __fdiv_rn(__ldg(amax), 2688.f);
-  const float c = 6.f * s2;
+  const Nvfp4Tensor tn(__fdiv_rn(__ldg(amax), 2688.f));
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t b0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b0 < nblocks;
        b0 += kNvUnroll * stride) {
@@ -228,11 +285,12 @@ nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
     for (int u = 0; u < kNvUnroll; ++u) {
       const int64_t b = b0 + u * stride;
       if (b < nblocks) {
-        const uint32_t code = nvfp4_scale_code<false>(__uint_as_float(blk[u].amax_f32bits()), c);
-        const float d = e4m3_to_f32(code) * s2;
+        const float bamax = __uint_as_float(blk[u].amax_f32bits());
+        const uint32_t code = nvfp4_scale_code<false>(bamax, tn);
+        const float d = e4m3_to_f32(code) * tn.s2;
         float f[16];
         blk[u].decode(f);
-        const uint2 q = nvfp4_encode16(f, d);
+        const uint2 q = nvfp4_encode16<sizeof(T) == 2>(f, d, bamax);
         nvfp4_decode16(q, d, f);
         store16<T>(y + 16 * b, f);
       }
@@ -315,9 +373,8 @@ nvfp4_group_quantize_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, i
     const int64_t tensor_tiles = (d.nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
     const int64_t tend = min(t1, d.tile_begin + tensor_tiles);
     const T* x = static_cast<const T*>(d.x);
-    const float s2 = __fdiv_rn(*d.amax, 2688.f);
-    const float c = 6.f * s2;
-    if (t == d.tile_begin && threadIdx.x == 0 && d.s2) *d.s2 = s2;
+    const Nvfp4Tensor tn(__fdiv_rn(*d.amax, 2688.f));
+    if (t == d.tile_begin && threadIdx.x == 0 && d.s2) *d.s2 = tn.s2;
     for (; t < tend; ++t) {
       const int64_t tb = (t - d.tile_begin) * kNvTileBlocks;
       Block16<T> blk[kNvUnroll];
@@ -329,7 +386,7 @@ nvfp4_group_quantize_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, i
 #pragma unroll
       for (int u = 0; u < kNvUnroll; ++u) {
         const int64_t b = tb + u * kNvThreads + threadIdx.x;
-        if (b < d.nblocks) nvfp4_quant_block<T>(blk[u], b, s2, c, nullptr, d.packed, d.scales);
+        if (b < d.nblocks) nvfp4_quant_block<T>(blk[u], b, tn, nullptr, d.packed, d.scales);
       }
     }
     ++ti;

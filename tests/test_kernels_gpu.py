@@ -383,3 +383,19 @@ def test_hist_golden_and_percentile(ops):
         want, _ = qo.percentile_amax(got, g["edges0"], p)
         a = ops.hist_percentile(counts, 2048, torch.from_numpy(g["edges0"]), 0.0, p)
         assert a.item() == want
+
+
+def test_nvfp4_every_bf16_value_under_many_divisors(ops):
+    """All finite bf16 bit patterns quantised under 160 per-tensor scales spread over 12 decades:
+    the reciprocal-and-correct quotient of the kernel must give the codes of the IEEE division."""
+    pat = np.arange(65536, dtype=np.uint32)
+    vals = (pat << 16).view(np.float32)
+    vals = vals[np.isfinite(vals)]
+    rng = np.random.default_rng(123)
+    for i in range(160):
+        x = rng.permutation(vals)[: (vals.size // 16) * 16].reshape(-1, 16)
+        s2 = np.float32(10.0 ** rng.uniform(-8, 4))
+        packed, scales, s2o = ops.nvfp4_quantize(tensor_from_f32(x, "bf16"), scale2=torch.tensor(float(s2)))
+        wp, ws, _ = qo.nvfp4_quantize(x, 16, s2=s2)
+        assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), ws), i
+        assert np.array_equal(packed.cpu().numpy(), wp), i
