@@ -192,6 +192,24 @@ int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float ran
 int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,
                           float bin_width, double percentile, float* amax_out, void* stream);
 
+/* ---------------------------------------------------------------- awq_lite search ---------- */
+
+/* One candidate of the awq_lite search, weight side: for w[rows, cols] and s[cols] (both T),
+ *   v = T(w * s[col]);  amax = max|v| over each run of `block` elements of a row;
+ *   y = T(fake_int(v, amax, num_bits, ...))      (integer fake quant as b200q_fake_int_tensor)
+ * in one pass.  Replaces the pre_quant_scale multiply, block reshape, dynamic amax and
+ * fake_tensor_quant_with_axis chain that TensorQuantizer.forward runs per alpha
+ * (modelopt/torch/quantization/model_calib.py:671-685;
+ *  nn/modules/tensor_quantizer.py:882-883,505-514,633-686). */
+int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, int64_t rows, int64_t cols,
+                             int block, int dtype, int num_bits, int is_unsigned, int narrow_range,
+                             void* stream);
+
+/* *sum_io += sum_i float(T(a_i - b_i))^2 (float64 accumulator): the numerator of the awq_lite
+ * loss (out - out_actual).float().pow(2).mean() (model_calib.py:623-627). */
+int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double* sum_io,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

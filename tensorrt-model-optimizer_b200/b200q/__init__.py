@@ -2,5 +2,12 @@
 quantize / calibrate path.  ``import b200q as mtq`` gives the reference's entry points
 (``quantize``, ``calibrate``, ``compress``, the ``*_CFG`` dictionaries) for this path."""
 from . import _cabi, ops  # noqa: F401  (loading the library is part of importing the package)
+from . import calib, dist, nn, qtensor, tensor_quant, utils  # noqa: F401
+from .config import *  # noqa: F401,F403
+from .conversion import (replace_quant_module, set_quantizer_attribute, set_quantizer_by_cfg,  # noqa: F401
+                         set_quantizer_by_cfg_context)
+from .model_calib import awq_lite, max_calibrate  # noqa: F401
+from .model_quant import (calibrate, compress, disable_quantizer, enable_quantizer, fold_weight,  # noqa: F401
+                          modelopt_state, print_quant_summary, quantize)
 
 __version__ = "0.1.0"

@@ -1,0 +1,171 @@
+"""Quantisation format dictionaries and the quantiser attribute record, with the names and
+contents of ``modelopt/torch/quantization/config.py`` (formats :147-388, attributes :661-955,
+algorithm options :958-1150) for the formats this package accelerates."""
+from __future__ import annotations
+
+import copy
+from dataclasses import dataclass, field, fields
+from typing import Any
+
+__all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG",
+           "INT4_BLOCKWISE_WEIGHT_ONLY_CFG", "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG",
+           "choices", "need_calibration"]
+
+_default_disabled_quantizer_cfg = {
+    "nn.BatchNorm1d": {"*": {"enable": False}},
+    "nn.BatchNorm2d": {"*": {"enable": False}},
+    "nn.BatchNorm3d": {"*": {"enable": False}},
+    "nn.LeakyReLU": {"*": {"enable": False}},
+    "*lm_head*": {"enable": False},
+    "*proj_out.*": {"enable": False},
+    "*block_sparse_moe.gate*": {"enable": False},
+    "*router*": {"enable": False},
+    "*mlp.gate.*": {"enable": False},
+    "*mlp.shared_expert_gate.*": {"enable": False},
+    "*linear_attn.conv1d*": {"enable": False},
+    "*mixer.conv1d*": {"enable": False},
+    "*output_layer*": {"enable": False},
+    "output.*": {"enable": False},
+    "default": {"enable": False},
+}
+
+INT8_DEFAULT_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": {"num_bits": 8, "axis": 0},
+        "*input_quantizer": {"num_bits": 8, "axis": None},
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": "max",
+}
+
+INT8_WEIGHT_ONLY_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": {"num_bits": 8, "axis": 0},
+        "*input_quantizer": {"enable": False},
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": "max",
+}
+
+FP8_DEFAULT_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": {"num_bits": (4, 3), "axis": None},
+        "*input_quantizer": {"num_bits": (4, 3), "axis": None},
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": "max",
+}
+
+INT4_BLOCKWISE_WEIGHT_ONLY_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": {"num_bits": 4, "block_sizes": {-1: 128}, "enable": True},
+        "*input_quantizer": {"enable": False},
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": "max",
+}
+
+INT4_AWQ_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": {"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+        "*input_quantizer": {"enable": False},
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": {"method": "awq_lite", "alpha_step": 0.1},
+}
+
+_nvfp4 = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
+          "axis": None, "enable": True}
+
+NVFP4_DEFAULT_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": copy.deepcopy(_nvfp4),
+        "*input_quantizer": copy.deepcopy(_nvfp4),
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": "max",
+}
+
+NVFP4_AWQ_LITE_CFG = {
+    "quant_cfg": {
+        "*weight_quantizer": copy.deepcopy(_nvfp4),
+        "*input_quantizer": copy.deepcopy(_nvfp4),
+        **_default_disabled_quantizer_cfg,
+    },
+    "algorithm": "awq_lite",
+}
+
+choices = {"INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
+           "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG"}
+
+
+@dataclass
+class QuantizerAttributeConfig:
+    """Attributes of one TensorQuantizer (same field names and defaults as the reference record)."""
+
+    enable: bool = True
+    num_bits: Any = 8                     # int, or (E, M) for floating formats
+    axis: Any = None                      # kept (quantisation) axis / axes; None = per tensor
+    fake_quant: bool = True
+    unsigned: bool = False
+    narrow_range: bool = False
+    learn_amax: bool = False
+    type: str = "static"                  # "static" | "dynamic"
+    block_sizes: dict | None = None       # {dim: size, "type": ..., "scale_bits": ...}
+    bias: dict | None = None
+    trt_high_precision_dtype: str = "Float"
+    calibrator: Any = "max"               # "max" | "histogram" | (class, args, kwargs) | instance
+    rotate: bool = False
+    pass_through_bwd: bool = False
+
+    def __post_init__(self):
+        if isinstance(self.num_bits, list):
+            self.num_bits = tuple(self.num_bits)
+        if isinstance(self.num_bits, int):
+            if self.num_bits < 1:
+                raise ValueError("num_bits must be a positive integer or a tuple of positive integers.")
+        elif not (isinstance(self.num_bits, tuple) and len(self.num_bits) == 2):
+            raise ValueError("num_bits must be a positive integer or a tuple of positive integers.")
+        if self.learn_amax:
+            raise ValueError("learn_amax is deprecated and reserved for backward compatibility.")
+        if self.type not in ("static", "dynamic"):
+            raise ValueError("type must be 'static' or 'dynamic'")
+        if self.block_sizes is not None:
+            if self.axis is not None:
+                raise ValueError("axis must be None when block_sizes is not None.")
+            bs = {}
+            for k, v in self.block_sizes.items():
+                if isinstance(k, str) and k.lstrip("-").isdigit():
+                    k = int(k)
+                if isinstance(k, str):
+                    if k not in ("type", "scale_bits", "scale_block_sizes"):
+                        raise ValueError(f"Unknown block_sizes key {k!r}")
+                    if k == "scale_bits" and isinstance(v, list):
+                        v = tuple(v)
+                bs[k] = v
+            self.block_sizes = bs
+
+    @staticmethod
+    def _get_block_quant_axes_and_sizes(block_sizes):
+        if block_sizes is None:
+            return None
+        return {k: v for k, v in block_sizes.items() if isinstance(k, int) and v is not None}
+
+    def dict(self):
+        return {f.name: getattr(self, f.name) for f in fields(self)}
+
+
+def need_calibration(config) -> bool:
+    """True when some enabled static quantiser of ``config`` needs calibration data."""
+    if config.get("algorithm") not in ("max", None):
+        return True
+    for name, cfg in config.get("quant_cfg", {}).items():
+        cfgs = cfg if isinstance(cfg, (list, tuple)) else [cfg]
+        for c in cfgs:
+            if not isinstance(c, dict) or "*" in c:
+                continue
+            if c.get("enable", True) and "weight_quantizer" not in name:
+                bs = c.get("block_sizes") or {}
+                if c.get("type", "static") != "dynamic" and bs.get("type", "static") != "dynamic":
+                    return True
+    return False

@@ -1,0 +1,112 @@
+"""Model conversion: class-patch ``nn.Linear`` into ``QuantLinear`` and configure the quantisers
+from a wildcard dictionary (reference: modelopt/torch/quantization/conversion.py:56-301)."""
+from __future__ import annotations
+
+import fnmatch
+from contextlib import contextmanager
+
+from torch import nn
+
+from .config import QuantizerAttributeConfig
+from .nn import QuantLinear, QuantModule, SequentialQuantizer, TensorQuantizer
+
+__all__ = ["replace_quant_module", "set_quantizer_by_cfg", "set_quantizer_attribute",
+           "set_quantizer_by_cfg_context", "convert_to_quantized_model"]
+
+
+def replace_quant_module(model: nn.Module):
+    """Convert every ``nn.Linear`` (exact type or subclass not yet converted) in place."""
+    for m in list(model.modules()):
+        if isinstance(m, nn.Linear) and not isinstance(m, QuantModule):
+            QuantLinear.convert(m)
+    return model
+
+
+def _match(pattern, name: str) -> bool:
+    if callable(pattern):
+        return bool(pattern(name))
+    return fnmatch.fnmatch(name, pattern)
+
+
+def set_quantizer_attribute(model: nn.Module, wildcard_or_filter, attribute, parent_class=None):
+    """Apply ``attribute`` (a dict / QuantizerAttributeConfig, or a list of them for a
+    SequentialQuantizer) to every quantiser whose full name matches."""
+    for name, module in list(model.named_modules()):
+        if not isinstance(module, (TensorQuantizer, SequentialQuantizer)) or not _match(wildcard_or_filter, name):
+            continue
+        if parent_class is not None:
+            parent = model.get_submodule(name.rpartition(".")[0]) if "." in name else model
+            if not isinstance(parent, parent_class):
+                continue
+        if isinstance(attribute, (list, tuple)):
+            if not isinstance(module, SequentialQuantizer):
+                parent = model.get_submodule(name.rpartition(".")[0]) if "." in name else model
+                seq = SequentialQuantizer(*(TensorQuantizer() for _ in attribute))
+                seq.to(next(iter(module.buffers()), None).device if list(module.buffers()) else "cpu")
+                setattr(parent, name.rpartition(".")[2], seq)
+                module = seq
+            module.set_from_attribute_config([_as_cfg(a, None) for a in attribute])
+        else:
+            if isinstance(module, SequentialQuantizer):
+                parent = model.get_submodule(name.rpartition(".")[0]) if "." in name else model
+                module = TensorQuantizer()
+                setattr(parent, name.rpartition(".")[2], module)
+            module.set_from_attribute_config(_as_cfg(attribute, module))
+
+
+def _as_cfg(attribute, module):
+    if isinstance(attribute, QuantizerAttributeConfig):
+        return attribute
+    attribute = dict(attribute)
+    if set(attribute) == {"enable"} and module is not None:
+        # a bare enable/disable keeps the quantiser's other attributes
+        cfg = QuantizerAttributeConfig(
+            enable=attribute["enable"], num_bits=module._num_bits, axis=module._axis,
+            fake_quant=module._fake_quant, unsigned=module._unsigned, narrow_range=module._narrow_range,
+            type="dynamic" if module._dynamic else "static", block_sizes=module._block_sizes,
+            calibrator=module._calibrator if module._calibrator is not None else "max")
+        return cfg
+    return QuantizerAttributeConfig(**attribute)
+
+
+def set_quantizer_by_cfg(model: nn.Module, quant_cfg: dict):
+    """``quant_cfg`` maps wildcards (or ``nn.<Class>`` names) to attribute dictionaries; the
+    ``"default"`` entry is applied first, then the others in order."""
+    quant_cfg = dict(quant_cfg)
+    if "default" in quant_cfg:
+        set_quantizer_attribute(model, "*", quant_cfg["default"])
+        quant_cfg.pop("default")
+    for pattern, cfg in quant_cfg.items():
+        if isinstance(pattern, str) and pattern.startswith("nn."):
+            cls = getattr(nn, pattern[3:], None)
+            if cls is None:
+                continue
+            for sub_pattern, sub_cfg in cfg.items():
+                set_quantizer_attribute(model, sub_pattern, sub_cfg, parent_class=cls)
+        else:
+            set_quantizer_attribute(model, pattern, cfg)
+
+
+@contextmanager
+def set_quantizer_by_cfg_context(model: nn.Module, quant_cfg: dict):
+    """Temporarily apply ``quant_cfg`` (only switches and attributes; buffers are kept)."""
+    saved = {}
+    for name, m in model.named_modules():
+        if isinstance(m, TensorQuantizer):
+            saved[name] = {k: v for k, v in m.__dict__.items() if k.startswith("_") and k not in
+                           ("_parameters", "_buffers", "_modules") and not k.startswith("_forward")
+                           and not k.startswith("_backward") and not k.startswith("_state_dict")
+                           and not k.startswith("_load_state") and k != "_non_persistent_buffers_set"}
+    set_quantizer_by_cfg(model, quant_cfg)
+    try:
+        yield
+    finally:
+        for name, m in model.named_modules():
+            if name in saved:
+                m.__dict__.update(saved[name])
+
+
+def convert_to_quantized_model(model: nn.Module, config: dict):
+    replace_quant_module(model)
+    set_quantizer_by_cfg(model, config.get("quant_cfg", {}))
+    return model

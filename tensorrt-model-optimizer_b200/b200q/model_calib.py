@@ -1,0 +1,287 @@
+"""Calibration algorithms (reference: modelopt/torch/quantization/model_calib.py): ``max_calibrate``
+(:65-185) and ``awq_lite`` (:530-785) with their helpers.
+
+Differences in execution, not in results: amax collection is one kernel per quantiser call with
+no host synchronisation, the data-parallel amax exchange is one all-reduce over a flat buffer
+(``b200q.dist.sync_amax``) instead of one per quantiser, and the AWQ search evaluates each alpha
+with a fused scale+block-quantise kernel feeding the GEMM.
+"""
+from __future__ import annotations
+
+import warnings
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+from . import dist as qdist
+from . import ops
+from .nn import QuantModule, SequentialQuantizer, TensorQuantizer, is_quantized_linear
+
+__all__ = ["max_calibrate", "awq_lite", "awq", "enable_stats_collection", "finish_stats_collection",
+           "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]
+
+
+def enable_stats_collection(model: nn.Module):
+    for _, m in model.named_modules():
+        if isinstance(m, TensorQuantizer) and not m._disabled:
+            if m._calibrator is not None:
+                m.disable_quant()
+                m.enable_calib()
+            else:
+                m.disable()
+
+
+def finish_stats_collection(model: nn.Module, method: str | None = None):
+    for _, m in model.named_modules():
+        if not isinstance(m, TensorQuantizer) or m._disabled:
+            continue
+        cal = getattr(m, "_calibrator", None)
+        if cal and not m._dynamic:
+            if method in {"mse", "entropy"}:
+                if cal.compute_amax(method) is not None:
+                    m.load_calib_amax(method)
+            elif cal.compute_amax() is not None:
+                m.load_calib_amax()
+        m.enable_quant()
+        m.disable_calib()
+
+
+def weight_only_quantize(model: nn.Module):
+    """Run every weight through its weight quantiser once (collects weight statistics)."""
+    seen = set()
+    for _, m in model.named_modules():
+        if m in seen:
+            continue
+        if hasattr(m, "weight_quantizer") and getattr(m, "weight", None) is not None:
+            m.weight_quantizer(m.weight)
+        seen.add(m)
+
+
+@torch.no_grad()
+def max_calibrate(model: nn.Module, forward_loop=None, distributed_sync=True):
+    """Max calibration: collect abs-max statistics while ``forward_loop(model)`` runs (or over the
+    weights only when no loop is given), load them into the ``_amax`` buffers and take the MAX
+    over the data-parallel group."""
+    enable_stats_collection(model)
+    if forward_loop is None:
+        weight_only_quantize(model)
+    else:
+        forward_loop(model)
+    finish_stats_collection(model)
+    if distributed_sync and dist.is_available() and dist.is_initialized():
+        qdist.sync_amax(model)
+
+
+# --------------------------------------------------------------------------------- AWQ lite ----
+
+def _awq_block_size(weight, quantizer):
+    bs = quantizer.block_sizes
+    if bs is None:
+        return None
+    b = bs.get(-1) or bs.get(weight.dim() - 1)
+    return b
+
+
+def get_weight_scale(weight, block_size=None):
+    """mean over rows of |W| / (block amax + tiny), reduced in the weight's dtype, then fp32
+    (reference model_calib.py:588-603)."""
+    org_shape = weight.shape
+    sl = None
+    if block_size:
+        if org_shape[-1] % block_size:
+            sl = slice(org_shape[-1])
+            weight = F.pad(weight, (0, block_size - org_shape[-1] % block_size), "constant", 0)
+            org_shape = weight.shape
+        weight = weight.contiguous().view(-1, block_size)
+    amax = weight.abs().amax(dim=1, keepdim=True)
+    scale = (weight.abs() / (amax + torch.finfo(weight.dtype).tiny)).view(org_shape)
+    if sl is not None:
+        scale = scale[..., sl]
+    return scale.mean(0).to(torch.float32)
+
+
+def get_act_scale(x):
+    return x.abs().contiguous().view(-1, x.shape[-1]).mean(0).to(torch.float32)
+
+
+def get_scale(x_max, w_max, alpha):
+    """s = clamp(a^alpha / (w^(1-alpha) + tiny), 1e-4, 1e4) / sqrt(max(s) * min(s))."""
+    s = (x_max.pow(alpha) / (w_max.to(x_max.device).pow(1 - alpha) + torch.finfo(torch.float32).tiny)
+         ).clamp(min=1e-4, max=1e4).view(-1)
+    return (s / (s.max() * s.min()).sqrt()).view(-1)
+
+
+@torch.no_grad()
+def apply_pre_quant_scale_and_smooth(linear, pre_quant_scale):
+    """Set ``input_quantizer.pre_quant_scale`` and fold its inverse into the weight, then
+    re-calibrate the weight amax (reference model_calib.py:344-408)."""
+    assert is_quantized_linear(linear), "Only quantized linear modules are supported"
+    assert linear.input_quantizer.pre_quant_scale is None, "pre_quant_scale should be None first!"
+    assert torch.all(pre_quant_scale > 0), "pre_quant_scale should be positive"
+    pqs = pre_quant_scale.to(torch.float32)
+    linear.input_quantizer._enable_pre_quant_scale = True
+    linear.input_quantizer.pre_quant_scale = pqs.to(linear.weight.dtype)
+    inv = 1.0 / pqs
+    linear.weight.data.copy_((linear.weight * inv.to(linear.weight.device).squeeze()[None, :]).to(linear.weight.dtype))
+    linear.weight_quantizer.reset_amax()
+    max_calibrate(linear, lambda lin: lin.weight_quantizer(lin.weight), distributed_sync=False)
+    if linear.input_quantizer.amax is not None:
+        assert hasattr(linear.input_quantizer, "_amax_for_smoothing")
+        dev, dt = linear.weight.device, linear.weight.dtype
+        a = linear.input_quantizer._amax_for_smoothing.to(device=dev, dtype=dt)
+        linear.input_quantizer.amax = (a * pqs.to(dev)).amax().to(dt)
+
+
+class _AWQLiteState:
+    def __init__(self, module, name, alpha_step):
+        self.name = name
+        self.module = module
+        self.act_scale = 0.0
+        self.num_cache_steps = 0
+        self.num_search_steps = 0
+        self.block_size = _awq_block_size(module.weight, module.weight_quantizer)
+        self.weight_scale = get_weight_scale(module.weight, self.block_size)
+        self.loss = {k.item(): torch.zeros((), device=module.weight.device, dtype=torch.float32)
+                     for k in torch.arange(0, 1.0 + alpha_step, alpha_step)}
+        self.best_scale = None
+        self.best_alpha = None
+        self.is_input_quantized = module.input_quantizer.is_enabled
+        self.is_enabled = True
+
+
+def _evaluate_alpha(module, st, x2d, out_actual, alpha):
+    """loss contribution of one alpha for one batch: mean((x/s) @ fq(W*s)^T - x @ W^T)^2."""
+    s = get_scale(st.act_scale, st.weight_scale, alpha)
+    dt = module.weight.dtype
+    w_s, x_s = s.to(dt), (1 / s).to(dt)
+    wq = module.weight_quantizer
+    fast = (wq._fake_quant and isinstance(wq._num_bits, int) and st.block_size
+            and module.weight.shape[-1] % st.block_size == 0 and wq._block_sizes.get("type", "static") == "static")
+    if fast:
+        # (W * s) rounded to the weight dtype, per-block abs-max, integer fake quant: one kernel
+        wfq = ops.awq_scale_fake_int(module.weight, w_s, st.block_size, wq._num_bits, wq._unsigned, wq._narrow_range)
+    else:
+        wq._enable_pre_quant_scale = True
+        wq.pre_quant_scale = w_s
+        wfq = wq(module.weight)
+        delattr(wq, "_pre_quant_scale")
+    xin = x2d * x_s
+    if module.input_quantizer.is_enabled:
+        xin = module.input_quantizer(xin)
+    out = F.linear(xin, wfq, module.bias)
+    return ops.mse_loss(out, out_actual)
+
+
+def _awq_forward(self, input, *args, **kwargs):
+    st = self.awq_lite
+    for q in (self.input_quantizer, self.weight_quantizer):
+        if hasattr(q, "_pre_quant_scale"):
+            delattr(q, "_pre_quant_scale")
+    out_actual = F.linear(self.input_quantizer(input) if st.cache_mode_ref[0] else input, self.weight, self.bias)
+    if input.numel() == 0 or not st.is_enabled:
+        return out_actual
+    if st.cache_mode_ref[0]:
+        st.act_scale = st.act_scale + get_act_scale(input)
+        st.num_cache_steps += 1
+        if st.is_input_quantized:
+            self.input_quantizer._calibrator.collect(input)
+        return out_actual
+    for alpha in st.loss:
+        st.loss[alpha] += _evaluate_alpha(self, st, input, out_actual, alpha)
+    st.num_search_steps += 1
+    return out_actual
+
+
+@torch.no_grad()
+def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: bool = False, **kwargs):
+    """AWQ-lite: per linear layer, search the exponent alpha of the per-input-channel scale
+    s = act_scale^alpha / weight_scale^(1-alpha) that minimises the output error of the
+    block-quantised layer, then fold the best scale into the weight and the input quantiser."""
+    if forward_loop is None:
+        warnings.warn("forward_loop must be provided for awq_lite; skipping awq_lite")
+        return
+    cache_mode = [True]
+    layers = []
+    for name, m in model.named_modules():
+        if is_quantized_linear(m) and m.weight_quantizer.is_enabled:
+            st = _AWQLiteState(m, name, alpha_step)
+            st.cache_mode_ref = cache_mode
+            m.awq_lite = st
+            if m.input_quantizer.is_enabled:
+                m.input_quantizer.disable()
+                if m.input_quantizer.axis not in (None, -1):
+                    st.is_enabled = False
+                else:
+                    m.input_quantizer.axis = -1
+            m._forward_no_awq = m.forward
+            m.forward = _awq_forward.__get__(m, type(m))
+            layers.append((name, m))
+
+    # pass 1: activation statistics
+    forward_loop(model)
+    for name, m in layers:
+        st = m.awq_lite
+        if st.is_input_quantized and st.num_cache_steps > 0:
+            m.input_quantizer.load_calib_amax()
+    if dist.is_available() and dist.is_initialized():
+        qdist.sync_amax(model)
+    for name, m in layers:
+        st = m.awq_lite
+        if st.num_cache_steps > 0:
+            st.act_scale = st.act_scale / st.num_cache_steps
+            has_nan = bool(torch.any(torch.isnan(st.act_scale)) or torch.any(torch.isnan(st.weight_scale)))
+            if dist.is_available() and dist.is_initialized():
+                flags = [None] * dist.get_world_size()
+                dist.all_gather_object(flags, has_nan)
+                has_nan = any(flags)
+            if has_nan:
+                st.is_enabled = False
+            elif dist.is_available() and dist.is_initialized():
+                dist.all_reduce(st.act_scale, op=dist.ReduceOp.SUM)
+                st.act_scale /= dist.get_world_size()
+
+    # pass 2: search
+    cache_mode[0] = False
+    forward_loop(model)
+
+    for name, m in layers:
+        st = m.awq_lite
+        m.forward = m._forward_no_awq
+        del m._forward_no_awq
+        if st.num_cache_steps == 0:
+            st.is_enabled = False
+        elif st.num_search_steps == 0:
+            st.is_enabled = False
+            warnings.warn(f"awq_lite: the second forward_loop(model) did not reach {name}.")
+        if st.is_enabled:
+            st.loss = {k: float(v) for k, v in st.loss.items()}
+            st.best_alpha = min(st.loss, key=st.loss.get)
+            st.best_scale = get_scale(st.act_scale, st.weight_scale, st.best_alpha)
+        for q in (m.weight_quantizer, m.input_quantizer):
+            if hasattr(q, "_pre_quant_scale"):
+                delattr(q, "_pre_quant_scale")
+        if st.is_input_quantized and m.input_quantizer.amax is not None:
+            act_amax = m.input_quantizer.amax
+            m.input_quantizer._amax_for_smoothing = act_amax.cpu()
+            m.input_quantizer.reset_amax()
+            m.input_quantizer.axis = None
+            m.input_quantizer.amax = act_amax.amax()
+            m.input_quantizer.enable()
+        if st.is_enabled:
+            apply_pre_quant_scale_and_smooth(m, 1.0 / st.best_scale)
+        else:
+            warnings.warn(f"awq_lite: Disabling for {name}, quantizing with max calibration.")
+            max_calibrate(m, lambda mod: mod.weight_quantizer(mod.weight), distributed_sync=False)
+        if not debug:
+            delattr(m, "awq_lite")
+
+
+def awq(model, forward_loop=None, algorithm="awq_lite", **kwargs):
+    """AWQ entry point (reference model_calib.py:499-526); only the lite search is built."""
+    if algorithm not in ("awq_lite",):
+        raise NotImplementedError(f"AWQ variant {algorithm!r} is outside the accelerated path")
+    with SequentialQuantizer.convert_to_single_quantizer(model):
+        awq_lite(model, forward_loop, **kwargs)
+    max_calibrate(model, lambda m: None)

@@ -1,0 +1,116 @@
+"""User entry points: ``quantize``, ``calibrate``, ``compress`` and helpers (reference:
+modelopt/torch/quantization/model_quant.py:53-231,499-523; compress.py:53-222)."""
+from __future__ import annotations
+
+import fnmatch
+
+import torch
+from torch import nn
+
+from .conversion import convert_to_quantized_model, set_quantizer_attribute
+from .model_calib import awq, max_calibrate
+from .nn import QuantLinear, RealQuantLinear, SequentialQuantizer, TensorQuantizer
+from .qtensor import pack_real_quantize_weight
+
+__all__ = ["quantize", "calibrate", "compress", "disable_quantizer", "enable_quantizer",
+           "print_quant_summary", "fold_weight", "modelopt_state"]
+
+_ALGORITHMS = {"max": max_calibrate, "awq_lite": awq}
+
+
+def calibrate(model: nn.Module, algorithm="max", forward_loop=None) -> nn.Module:
+    """Run a calibration algorithm on a converted model.
+
+    ``algorithm``: ``"max"``, ``"awq_lite"``, ``None`` (skip), or a dict
+    ``{"method": name, **options}``.  ``forward_loop(model)`` must push the calibration data
+    through the model; it may be called more than once."""
+    if algorithm is None:
+        return model
+    opts = {}
+    if isinstance(algorithm, dict):
+        opts = {k: v for k, v in algorithm.items() if k != "method"}
+        algorithm = algorithm["method"]
+    fn = _ALGORITHMS.get(algorithm)
+    if fn is None:
+        raise NotImplementedError(f"calibration algorithm {algorithm!r} is outside the accelerated path "
+                                  f"(built: {sorted(_ALGORITHMS)})")
+    was_training = model.training
+    model.eval()
+    fn(model, forward_loop, **opts) if algorithm != "max" else fn(model, forward_loop, **opts)
+    model.train(was_training)
+    _record_mode(model, f"{algorithm}_calibrate" if algorithm != "awq_lite" else "awq_lite_calibrate")
+    return model
+
+
+def quantize(model: nn.Module, config: dict, forward_loop=None) -> nn.Module:
+    """Convert ``model`` in place (``nn.Linear`` -> ``QuantLinear``), configure its quantisers from
+    ``config["quant_cfg"]`` and calibrate with ``config["algorithm"]``."""
+    convert_to_quantized_model(model, config)
+    _record_mode(model, "quantize", config)
+    return calibrate(model, config.get("algorithm", "max"), forward_loop)
+
+
+def compress(model: nn.Module, config=None) -> nn.Module:
+    """Real-quantise the weights: every enabled weight quantiser that supports it is switched to
+    real-quant mode and the weight is replaced by its packed form (``QTensorWrapper``); scales are
+    kept as ``_scale`` / ``_double_scale`` buffers of the quantiser.
+
+    ``config`` may carry ``{"compress": {pattern: bool}}`` to choose layers by name."""
+    patterns = (config or {}).get("compress", {"default": True}) if isinstance(config, dict) else {"default": True}
+    with SequentialQuantizer.convert_to_single_quantizer(model):
+        for name, m in model.named_modules():
+            if not isinstance(m, QuantLinear):
+                continue
+            wq = m.weight_quantizer
+            chosen = patterns.get("default", False)
+            for p, v in patterns.items():
+                if p != "default" and fnmatch.fnmatch(name, p):
+                    chosen = v
+            if not (chosen and wq.is_enabled and wq._is_real_quantize_support()):
+                continue
+            m.__class__ = RealQuantLinear
+            wq._fake_quant = False
+            wq._dequantize = False
+        pack_real_quantize_weight(model)
+    _record_mode(model, "real_quantize")
+    return model
+
+
+def disable_quantizer(model: nn.Module, wildcard_or_filter_func):
+    set_quantizer_attribute(model, wildcard_or_filter_func, {"enable": False})
+
+
+def enable_quantizer(model: nn.Module, wildcard_or_filter_func):
+    set_quantizer_attribute(model, wildcard_or_filter_func, {"enable": True})
+
+
+def print_quant_summary(model: nn.Module):
+    count = 0
+    for name, m in model.named_modules():
+        if isinstance(m, TensorQuantizer):
+            print(f"{name:80} {m}")
+            count += 1
+    print(f"{count} TensorQuantizers found in model")
+
+
+@torch.no_grad()
+def fold_weight(model: nn.Module):
+    """Replace each weight by its fake-quantised value and disable the weight quantiser."""
+    for _, m in model.named_modules():
+        if isinstance(m, QuantLinear) and m.weight_quantizer.is_enabled and m.weight_quantizer._fake_quant:
+            m.weight.data.copy_(m.weight_quantizer(m.weight).to(m.weight.dtype))
+            m.weight_quantizer.disable()
+
+
+def _record_mode(model, mode, config=None):
+    st = model.__dict__.setdefault("_b200q_state", [])
+    st.append((mode, config))
+
+
+def modelopt_state(model: nn.Module) -> dict:
+    """Modes applied so far plus the per-quantiser Python state (buffers are in ``state_dict()``)."""
+    return {
+        "modelopt_state_dict": list(model.__dict__.get("_b200q_state", [])),
+        "quantizer_state": {n: m.get_modelopt_state() for n, m in model.named_modules()
+                            if isinstance(m, TensorQuantizer)},
+    }

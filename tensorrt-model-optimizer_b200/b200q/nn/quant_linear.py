@@ -1,0 +1,82 @@
+"""Quantised linear layer (reference: modelopt/torch/quantization/nn/modules/quant_linear.py:38-312
+and quant_module.py:102-169).
+
+``QuantLinear.convert`` patches the class of an existing ``nn.Linear`` in place (same parameters,
+same state-dict keys) and adds ``input_quantizer``, ``weight_quantizer`` and ``output_quantizer``
+children.  The forward is ``F.linear(input_quantizer(x), weight_quantizer(W), b)``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ..config import QuantizerAttributeConfig
+from ..qtensor import QTensorWrapper
+from .tensor_quantizer import SequentialQuantizer, TensorQuantizer
+
+__all__ = ["QuantModule", "QuantLinear", "RealQuantLinear", "is_quantized_linear"]
+
+
+class QuantModule(nn.Module):
+    """Marker base class of converted modules."""
+
+
+class QuantLinear(nn.Linear, QuantModule):
+    default_quant_desc_input = QuantizerAttributeConfig(num_bits=8)
+    default_quant_desc_weight = QuantizerAttributeConfig(num_bits=8, axis=0)
+    default_quant_desc_output = QuantizerAttributeConfig(num_bits=8)
+
+    @classmethod
+    def convert(cls, module: nn.Linear) -> "QuantLinear":
+        """Turn ``module`` into a QuantLinear in place and return it."""
+        assert isinstance(module, nn.Linear)
+        module._original_cls = type(module)
+        module.__class__ = cls
+        module._setup()
+        return module
+
+    def _setup(self):
+        self.input_quantizer = TensorQuantizer(self.default_quant_desc_input)
+        self.weight_quantizer = TensorQuantizer(self.default_quant_desc_weight)
+        self.output_quantizer = TensorQuantizer(self.default_quant_desc_output)
+        self.output_quantizer.disable()
+        dev = self.weight.device
+        if dev.type != "meta":
+            for q in (self.input_quantizer, self.weight_quantizer, self.output_quantizer):
+                q.to(dev)
+
+    def restore(self) -> nn.Linear:
+        """Undo :meth:`convert` (drops the quantisers)."""
+        for n in ("input_quantizer", "weight_quantizer", "output_quantizer"):
+            delattr(self, n)
+        self.__class__ = self._original_cls
+        return self
+
+    def _quantized_weight(self):
+        w = self.weight
+        if isinstance(w, QTensorWrapper):
+            return self.weight_quantizer(w)
+        return self.weight_quantizer(w)
+
+    def forward(self, input, *args, **kwargs):
+        x = self.input_quantizer(input)
+        out = F.linear(x, self._quantized_weight(), self.bias)
+        return self.output_quantizer(out)
+
+
+class RealQuantLinear(QuantLinear):
+    """QuantLinear whose weight is stored packed (after ``compress``); the forward dequantises it
+    through the weight quantiser."""
+
+    def _quantized_weight(self):
+        w = self.weight
+        if isinstance(w, QTensorWrapper):
+            return self.weight_quantizer(w)
+        return super()._quantized_weight()
+
+
+def is_quantized_linear(module) -> bool:
+    return (isinstance(module, QuantModule) and isinstance(getattr(module, "input_quantizer", None), TensorQuantizer)
+            and hasattr(module, "weight_quantizer") and getattr(module, "weight", None) is not None
+            and module.weight.dim() == 2)

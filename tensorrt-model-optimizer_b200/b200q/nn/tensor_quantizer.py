@@ -1,0 +1,510 @@
+"""TensorQuantizer: the per-tensor quantisation module (reference:
+modelopt/torch/quantization/nn/modules/tensor_quantizer.py:65-1225).
+
+It holds the quantiser attributes and the ``_amax`` / ``_pre_quant_scale`` / ``_scale`` /
+``_double_scale`` buffers (same buffer names as the reference, so its state dicts load), feeds the
+calibrator during calibration and dispatches fake or real quantisation to the CUDA kernels.
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import warnings
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+from .. import calib, ops
+from ..config import QuantizerAttributeConfig
+from ..qtensor import (BaseQuantizedTensor, FP8QTensor, INT4QTensor, INT8QTensor, NVFP4QTensor,
+                       QTensorWrapper)
+from ..tensor_quant import dynamic_block_quant, fake_tensor_quant, scaled_e4m3
+from ..utils import convert_quantization_axis_to_reduce_axis, reduce_amax
+
+__all__ = ["TensorQuantizer", "SequentialQuantizer"]
+
+
+class TensorQuantizer(nn.Module):
+    """Quantises one tensor (a weight, or the activations entering a layer).
+
+    Args:
+        quant_attribute_cfg: a :class:`QuantizerAttributeConfig` (default: 8-bit per tensor).
+        if_quant: quantise in ``forward``.
+        if_calib: feed the calibrator in ``forward``.
+        amax: optional initial amax.
+    """
+
+    def __init__(self, quant_attribute_cfg=None, if_quant=True, if_calib=False, amax=None):
+        super().__init__()
+        cfg = quant_attribute_cfg if quant_attribute_cfg is not None else QuantizerAttributeConfig()
+        if amax is not None:
+            self.amax = amax
+        self.set_from_attribute_config(cfg)
+        self._if_quant = if_quant
+        self._if_calib = if_calib
+        self._enable_pre_quant_scale = True
+        self._dequantize = False
+        self._input_dtype = None
+
+    # ---- configuration --------------------------------------------------------------------
+    def set_from_attribute_config(self, attribute_cfg):
+        if isinstance(attribute_cfg, dict):
+            attribute_cfg = QuantizerAttributeConfig(**attribute_cfg)
+        c = attribute_cfg
+        self._disabled = not c.enable
+        self._num_bits = c.num_bits
+        self._axis = c.axis
+        self._fake_quant = c.fake_quant
+        self._unsigned = c.unsigned
+        self._narrow_range = c.narrow_range
+        self._dynamic = c.type == "dynamic"
+        self._block_sizes = dict(c.block_sizes) if c.block_sizes else None
+        self._bias = c.bias
+        self._trt_high_precision_dtype = c.trt_high_precision_dtype
+        self._rotate = c.rotate
+        self._pass_through_bwd = c.pass_through_bwd
+        if self._bias is not None or self._rotate:
+            raise NotImplementedError("bias calibration and rotation are not part of the accelerated path")
+        self._calibrator = self._make_calibrator(c.calibrator)
+        for attr in ("_block_reshape_size", "_padding", "_slices", "_original_shape", "_amax_shape_for_export"):
+            if hasattr(self, attr):
+                delattr(self, attr)
+
+    def _make_calibrator(self, spec):
+        if isinstance(spec, calib._Calibrator):
+            return spec
+        if isinstance(spec, str):
+            cls = {"max": calib.MaxCalibrator, "histogram": calib.HistogramCalibrator}.get(spec)
+            if cls is None:
+                raise ValueError(f"Unknown calibrator: {spec}")
+            return cls(self._num_bits, self._axis, self._unsigned)
+        if isinstance(spec, (tuple, list)):  # (class, args, kwargs)
+            cls, args, kwargs = (list(spec) + [(), {}])[:3]
+            return cls(*args, **(kwargs or {}))
+        if isinstance(spec, type):
+            return spec(self._num_bits, self._axis, self._unsigned)
+        raise ValueError(f"Unknown calibrator: {spec}")
+
+    # ---- properties ------------------------------------------------------------------------
+    num_bits = property(lambda self: self._num_bits)
+    unsigned = property(lambda self: self._unsigned)
+    narrow_range = property(lambda self: self._narrow_range)
+    fake_quant = property(lambda self: self._fake_quant)
+    block_sizes = property(lambda self: self._block_sizes)
+    is_enabled = property(lambda self: not self._disabled)
+
+    @num_bits.setter
+    def num_bits(self, v):
+        self._num_bits = v
+        if self._calibrator is not None:
+            self._calibrator._num_bits = v
+
+    @block_sizes.setter
+    def block_sizes(self, v):
+        self._axis = None
+        self._block_sizes = v
+
+    @property
+    def axis(self):
+        return self._axis
+
+    @axis.setter
+    def axis(self, v):
+        self._axis = v
+        if self._calibrator is not None:
+            self._calibrator._axis = v
+
+    @property
+    def maxbound(self):
+        if self._num_bits == (4, 3):
+            return 448.0
+        if self._num_bits == (2, 1) and self._block_sizes and self._block_sizes.get("scale_bits") == (4, 3):
+            return 6.0
+        if isinstance(self._num_bits, tuple):
+            raise NotImplementedError(f"maxbound of format {self._num_bits}")
+        return (1 << (self._num_bits - 1 + int(self._unsigned))) - 1
+
+    @property
+    def is_mx_format(self):
+        return (self._block_sizes is not None and self._block_sizes.get("type") == "dynamic"
+                and self._block_sizes.get("scale_bits") == (8, 0))
+
+    @property
+    def is_static_block_quant(self):
+        return (self._block_sizes is not None and self._block_sizes.get("type", "static") == "static"
+                and self._fake_quant)
+
+    @property
+    def pre_quant_scale(self):
+        if not hasattr(self, "_pre_quant_scale") or not self._enable_pre_quant_scale:
+            return None
+        return self._pre_quant_scale
+
+    @pre_quant_scale.setter
+    def pre_quant_scale(self, value):
+        assert value is not None, "pre_quant_scale cannot be set to None."
+        assert self._enable_pre_quant_scale, "pre_quant_scale is disabled"
+        value = value.clone().detach() if isinstance(value, torch.Tensor) else torch.tensor(value)
+        if hasattr(self, "_pre_quant_scale"):
+            if self._pre_quant_scale.shape != value.shape:
+                raise RuntimeError("Changing shape when setting pre_quant_scale is not allowed.")
+            self._pre_quant_scale.data.copy_(value.to(self._pre_quant_scale.device))
+        else:
+            self.register_buffer("_pre_quant_scale", value)
+
+    @property
+    def amax(self):
+        return getattr(self, "_amax", None)
+
+    @amax.setter
+    def amax(self, value):
+        assert value is not None, "amax cannot be set to None."
+        if not isinstance(value, torch.Tensor):
+            value = torch.tensor(value)
+        if not hasattr(self, "_amax"):
+            self.register_buffer("_amax", value.clone().detach())
+        else:
+            if self._amax.shape != value.shape:
+                raise RuntimeError("Changing shape when setting amax is not allowed.")
+            self._amax.data.copy_(value.clone().detach().to(self._amax.device))
+
+    def reset_amax(self):
+        if hasattr(self, "_amax"):
+            delattr(self, "_amax")
+        if self._calibrator is not None:
+            self._calibrator.reset()
+
+    @property
+    def step_size(self):
+        if not hasattr(self, "_amax"):
+            warnings.warn("step_size is undefined under dynamic amax mode!")
+            return None
+        assert isinstance(self._num_bits, int), "Step size is not defined for non-integer quantization."
+        return self._amax / (2.0 ** (self._num_bits - 1 + int(self._unsigned)) - 1.0)
+
+    # ---- switches ----------------------------------------------------------------------------
+    def disable(self):
+        self._disabled = True
+
+    def enable(self):
+        self._disabled = False
+
+    def disable_calib(self):
+        self._if_calib = False
+
+    def enable_calib(self):
+        if self._calibrator is None:
+            raise ValueError("Calibrator was not created, cannot enable calibration.")
+        self._if_calib = not self._dynamic
+
+    def disable_quant(self):
+        self._if_quant = False
+
+    def enable_quant(self):
+        self._if_quant = True
+
+    def _set_buffer(self, key, value):
+        if hasattr(self, key):
+            delattr(self, key)
+        self.register_buffer(key, value)
+
+    # ---- calibration -------------------------------------------------------------------------
+    def collect(self, inputs):
+        self._calibrator.collect(inputs)
+
+    def load_calib_amax(self, *args, **kwargs):
+        """Fetch the amax from the calibrator into the ``_amax`` buffer."""
+        assert self._calibrator is not None, "Calibrator not created."
+        calib_amax = self._calibrator.compute_amax(*args, **kwargs)
+        if calib_amax is None:
+            raise RuntimeError("Calibrator returned None. This usually happens when calibrator hasn't seen any tensor.")
+        self.validate_attr(attr_value=calib_amax, attr_name="_amax", raise_error=True)
+        if not hasattr(self, "_amax"):
+            self.register_buffer("_amax", calib_amax.clone().detach())
+        else:
+            self._amax.data.copy_(calib_amax.clone().detach().to(self._amax.device))
+
+    def validate_attr(self, attr_value=None, attr_name="_amax", raise_error=False, warn_error=False, name=""):
+        attr_value = attr_value if attr_value is not None else getattr(self, attr_name, None)
+        if attr_value is None or (isinstance(attr_value, torch.Tensor) and attr_value.is_meta):
+            return True
+        bad = bool(torch.any(attr_value < 0)) if attr_name == "_amax" else False
+        bad = bad or bool(torch.any(torch.isinf(attr_value) | torch.isnan(attr_value)))
+        if bad:
+            msg = f"{name} {attr_name} contains invalid values: {attr_value}"
+            if raise_error:
+                raise ValueError(msg)
+            if warn_error:
+                warnings.warn(msg)
+        return not bad
+
+    def sync_amax_across_distributed_group(self, parallel_group):
+        """MAX all-reduce of ``_amax`` over a process group (one collective for this quantiser;
+        ``b200q.dist.sync_amax`` batches all quantisers of a model into one)."""
+        group = getattr(parallel_group, "group", parallel_group)
+        if dist.is_initialized() and getattr(self, "_amax", None) is not None:
+            try:
+                dist.all_reduce(self._amax, op=dist.ReduceOp.MAX, group=group)
+            except RuntimeError as e:
+                warnings.warn(f"Failed to synchronize amax: {e}")
+
+    # ---- amax / block helpers ---------------------------------------------------------------
+    def _get_amax(self, inputs):
+        if hasattr(self, "_amax"):
+            return self._amax.data
+        red = convert_quantization_axis_to_reduce_axis(inputs, self._axis)
+        return reduce_amax(inputs, axis=red, keepdims=True).detach()
+
+    def _block_sizes_to_axis(self, x):
+        bs = self._block_sizes
+        if bs is None:
+            return
+        if all(v is None for k, v in bs.items() if isinstance(k, int)):
+            assert self._axis is None, "Axis and block_sizes are both set."
+            ax = tuple(k if k >= 0 else k + x.dim() for k in bs if isinstance(k, int))
+            self.axis = tuple(i for i in range(x.dim()) if i not in ax) or None
+            self._block_sizes = None
+
+    def _setup_for_blockquant(self, inputs):
+        if hasattr(self, "_block_reshape_size"):
+            return
+        axes = QuantizerAttributeConfig._get_block_quant_axes_and_sizes(self._block_sizes)
+        last = self._block_sizes.get(inputs.dim() - 1) or self._block_sizes.get(-1)
+        if not (last and len(axes) == 1):
+            raise NotImplementedError("static block quantisation is built for a single last-dimension block size")
+        self._original_shape = inputs.shape
+        rem = inputs.shape[-1] % last
+        if rem:
+            self._padding = (0, last - rem)
+            self._slices = (*(slice(None),) * (inputs.dim() - 1), slice(inputs.shape[-1]))
+            self._original_shape = F.pad(inputs, self._padding, "constant", 0).shape
+        self.axis = (0,)
+        self._block_reshape_size = torch.Size((-1, last))
+        self._amax_shape_for_export = (*inputs.shape[:-1], -1)
+
+    def _process_for_blockquant(self, inputs):
+        if hasattr(self, "_padding"):
+            inputs = F.pad(inputs, self._padding, "constant", 0)
+        if inputs.shape != self._original_shape:
+            raise ValueError(f"Input shape has changed from {self._original_shape} to {inputs.shape}."
+                             " Block-quantization requires a fixed input shape.")
+        return inputs.reshape(self._block_reshape_size)
+
+    def _reset_to_original_shape(self, outputs):
+        outputs = outputs.reshape(self._original_shape)
+        if hasattr(self, "_slices"):
+            outputs = outputs[self._slices]
+        return outputs
+
+    def export_amax(self):
+        if self._block_sizes is not None and self._block_sizes.get("type") == "dynamic":
+            return self.amax
+        if self.amax is None:
+            return None
+        amax = self.amax if not hasattr(self, "_amax_shape_for_export") else self.amax.reshape(self._amax_shape_for_export)
+        amax = amax.clone()
+        amax[amax == 0] = self.maxbound
+        amax = torch.nan_to_num(amax, nan=self.maxbound)
+        fi = torch.finfo(amax.dtype)
+        amax = amax.clamp(min=fi.tiny, max=fi.max)
+        self.validate_attr(attr_name="_amax", attr_value=amax)
+        if self._block_sizes is None:
+            if self._axis is None:
+                amax = amax.unsqueeze(0)
+            elif isinstance(self._axis, int) or (isinstance(self._axis, (list, tuple)) and len(self._axis) == 1):
+                amax = amax.squeeze()
+        return amax
+
+    # ---- quantisation ------------------------------------------------------------------------
+    def _fake_quantize(self, inputs):
+        bs = self._block_sizes
+        if bs is not None and bs.get("type", "static") == "dynamic":
+            block = bs.get(-1) or bs.get(inputs.dim() - 1)
+            if block is None:
+                raise ValueError("block size for dynamic quantization not found.")
+            amax = None if self.is_mx_format else self._get_amax(inputs)
+            return dynamic_block_quant(inputs, block, amax, None, self._num_bits, bs.get("scale_bits"),
+                                       self._trt_high_precision_dtype, "dynamic", self._pass_through_bwd)
+        if isinstance(self._num_bits, tuple):
+            E, M = self._num_bits  # noqa: N806
+            return scaled_e4m3(inputs, self._get_amax(inputs), None, E, M, self._trt_high_precision_dtype,
+                               self._pass_through_bwd)
+        if (not hasattr(self, "_amax") and inputs.dim() == 2 and self._axis in ((0,), 0, [0])
+                and not inputs.requires_grad):
+            # dynamic per-row amax (static block quantisation before calibration, per-row weights):
+            # abs-max and quantisation fused in one pass
+            try:
+                return ops.fake_int_rows_dynamic(inputs, self._num_bits, self._unsigned, self._narrow_range)
+            except ops._cabi.B200QError as e:  # row shape outside the fused kernel: two passes below
+                if e.status != -7:
+                    raise
+        return fake_tensor_quant(inputs, self._get_amax(inputs), None, self._num_bits, self._unsigned,
+                                 self._narrow_range, self._trt_high_precision_dtype, self._pass_through_bwd,
+                                 bs.get(-1) if bs else None,
+                                 self._axis[0] if isinstance(self._axis, tuple) else self._axis)
+
+    def _is_real_quantize_support(self):
+        return (self._num_bits in ((2, 1), (4, 3), 8)
+                or (self._num_bits == 4 and self._block_sizes is not None))
+
+    def _real_quantize(self, inputs):
+        assert self._is_real_quantize_support(), "Real quantization not supported for this format."
+        bufs = {}
+        bs = self._block_sizes or {}
+        blocks_only = {k: v for k, v in bs.items() if isinstance(k, int)} or None
+        if self._num_bits == (4, 3):
+            use_amax = self.amax is not None and not (blocks_only and self.amax.numel() == 1)
+            outputs, scale = FP8QTensor.quantize(inputs, axis=self._axis, block_sizes=blocks_only,
+                                                 scales=self.amax / 448.0 if use_amax else None)
+            bufs["_scale"] = scale
+        elif self._num_bits == 8:
+            outputs, scale = INT8QTensor.quantize(inputs, axis=self._axis, block_sizes=blocks_only)
+            bufs["_scale"] = scale
+        elif bs.get("scale_bits") == (4, 3):
+            outputs, s, s2 = NVFP4QTensor.quantize(
+                inputs, bs[-1],
+                weights_scaling_factor_2=self.amax.float() / (448.0 * 6.0) if self.amax is not None else None)
+            bufs["_scale"], bufs["_double_scale"] = s, s2
+        else:
+            outputs, scale = INT4QTensor.quantize(inputs, bs[-1])
+            bufs["_scale"] = scale
+        for k, v in bufs.items():
+            self._set_buffer(k, v)
+        self._dequantize = True
+        return outputs
+
+    def dequantize(self, inputs):
+        qtensor = inputs.get_qtensor() if isinstance(inputs, QTensorWrapper) else inputs
+        assert isinstance(qtensor, BaseQuantizedTensor), "Expected input as real quantized tensors."
+        kwarg = {"scale": self._scale, "block_sizes": self._block_sizes,
+                 "double_scale": getattr(self, "_double_scale", None),
+                 "scale_zeros": getattr(self, "_scale_zeros", None)}
+        return qtensor.dequantize(**kwarg)
+
+    def forward(self, inputs):
+        if isinstance(inputs, (BaseQuantizedTensor, QTensorWrapper)):
+            assert self._dequantize, "No dequantization stats in the tensor quantizer."
+            return self.dequantize(inputs)
+        if inputs.numel() == 0:
+            return inputs
+        if self.pre_quant_scale is not None:
+            inputs = inputs * self.pre_quant_scale
+        if self._disabled:
+            self._input_dtype = inputs.dtype
+            return inputs
+        if self._block_sizes is not None and self._fake_quant:
+            self._block_sizes_to_axis(inputs)
+        static_block = self.is_static_block_quant
+        if static_block:
+            self._setup_for_blockquant(inputs)
+            inputs = self._process_for_blockquant(inputs)
+        outputs = inputs
+        if self._if_calib and not self._dynamic:
+            if self._calibrator is None:
+                raise RuntimeError("Calibrator was not created.")
+            self.collect(inputs)
+        if self._if_quant:
+            if not inputs.is_contiguous():
+                inputs = inputs.contiguous()
+            if self._fake_quant:
+                outputs = self._fake_quantize(inputs)
+            elif not self._dequantize:
+                outputs = self._real_quantize(inputs)
+            else:
+                raise ValueError("self._dequantize is True and self.fake_quant is False. "
+                                 "This case should have been handled.")
+        if static_block:
+            outputs = self._reset_to_original_shape(outputs)
+        return outputs
+
+    # ---- repr / state ------------------------------------------------------------------------
+    def _short_amax(self, fmt=".4f"):
+        if self.is_mx_format:
+            return "None"
+        if not hasattr(self, "_amax"):
+            return "dynamic"
+        if self._amax.is_meta:
+            return "meta"
+        if self._amax.numel() == 1:
+            return f"{self._amax.item():{fmt}}"
+        return f"[{self._amax.min().item():{fmt}}, {self._amax.max().item():{fmt}}]({self._amax.numel()})"
+
+    def extra_repr(self):
+        if self._disabled:
+            return "disabled"
+        s = f"{'unsigned ' if self._unsigned else ''}{self._num_bits} bit"
+        s += " narrow" if self._narrow_range else ""
+        s += " fake" if self._fake_quant else " real"
+        s += f" block_sizes={self._block_sizes}," if self._block_sizes else f" axis={self._axis}" if self._axis is not None else " per-tensor"
+        s += f" amax={self._short_amax()}"
+        s += " pre_quant_scale" if self.pre_quant_scale is not None else ""
+        s += f" calibrator={self._calibrator.__class__.__name__}" if self._calibrator is not None else ""
+        s += " quant" if self._if_quant else ""
+        s += " calib" if self._if_calib else ""
+        return s
+
+    def get_modelopt_state(self, properties_only=False):
+        """Python-side state needed to rebuild the quantiser (buffers travel in the state dict)."""
+        skip = {"_calibrator", "_original_shape", "_block_reshape_size", "_padding", "_slices",
+                "_amax_shape_for_export", "_input_dtype"}
+        state = {k: v for k, v in self.__dict__.items()
+                 if k.startswith("_") and k not in skip and k not in nn.Module().__dict__
+                 and not isinstance(v, (torch.Tensor, nn.Module))}
+        state["_calibrator_type"] = type(self._calibrator).__name__ if self._calibrator else None
+        if not properties_only:
+            state["_pytorch_state_metadata"] = {
+                "buffers": {k: {"shape": v.shape, "dtype": v.dtype} for k, v in self._buffers.items()
+                            if v is not None}}
+        return state
+
+    def set_from_modelopt_state(self, state):
+        for k, v in state.items():
+            if k in ("_pytorch_state_metadata", "_calibrator_type"):
+                continue
+            setattr(self, k, v)
+        for k, meta in state.get("_pytorch_state_metadata", {}).get("buffers", {}).items():
+            if not hasattr(self, k):
+                self.register_buffer(k, torch.empty(meta["shape"], dtype=meta["dtype"]))
+
+
+class SequentialQuantizer(nn.Sequential):
+    """Several quantisers applied one after the other (e.g. INT4 block then FP8 for W4A8)."""
+
+    def __init__(self, *quantizers):
+        assert all(isinstance(q, TensorQuantizer) for q in quantizers)
+        super().__init__(*quantizers)
+
+    def get_modelopt_state(self):
+        return {"num_quantizers": len(self), "is_sequential_quantizer": True}
+
+    def disable(self):
+        for q in self:
+            q.disable()
+
+    def reset_amax(self):
+        for q in self:
+            q.reset_amax()
+
+    def set_from_attribute_config(self, attributes):
+        if not isinstance(attributes, (list, tuple)):
+            attributes = [attributes] * len(self)
+        for cfg, q in zip(attributes, self):
+            q.set_from_attribute_config(cfg)
+
+    @staticmethod
+    @contextlib.contextmanager
+    def convert_to_single_quantizer(model, indx: int = 0):
+        """Temporarily replace every SequentialQuantizer of ``model`` by its ``indx``-th member."""
+        swapped = []
+        for m in model.modules():
+            for name, child in list(m.named_children()):
+                if isinstance(child, SequentialQuantizer):
+                    swapped.append((m, name, child))
+                    setattr(m, name, child[indx])
+        try:
+            yield
+        finally:
+            for m, name, seq in swapped:
+                setattr(m, name, seq)

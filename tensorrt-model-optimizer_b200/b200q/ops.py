@@ -361,3 +361,28 @@ def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None
         call("b200q_hist_percentile", counts.data_ptr(), nbins, e.data_ptr() if e is not None else None,
              ctypes.c_float(width), ctypes.c_double(percentile), out.data_ptr(), _stream(counts))
     return out
+
+
+# --------------------------------------------------------------------------- awq_lite ----------
+
+def awq_scale_fake_int(w: torch.Tensor, s: torch.Tensor, block: int, num_bits: int = 4,
+                       unsigned: bool = False, narrow_range: bool = False) -> torch.Tensor:
+    """fake_int over blocks of ``block`` along the last dim of T(w * s), s broadcast over rows."""
+    w = _prep(w)
+    s = _prep(s.to(w.dtype))
+    assert w.dim() == 2 and s.numel() == w.shape[1]
+    y = torch.empty_like(w)
+    with torch.cuda.device(w.device):
+        call("b200q_awq_scale_fake_int", w.data_ptr(), s.data_ptr(), y.data_ptr(), w.shape[0], w.shape[1],
+             block, dtype_code(w), num_bits, int(unsigned), int(narrow_range), _stream(w))
+    return y
+
+
+def mse_loss(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """mean(float(a - b)^2) with the difference rounded to the tensors' dtype first; fp32 0-dim."""
+    a, b = _prep(a), _prep(b)
+    assert a.shape == b.shape and a.dtype == b.dtype
+    acc = torch.zeros((), dtype=torch.float64, device=a.device)
+    with torch.cuda.device(a.device):
+        call("b200q_sq_diff_sum", a.data_ptr(), b.data_ptr(), a.numel(), dtype_code(a), acc.data_ptr(), _stream(a))
+    return (acc / a.numel()).to(torch.float32)

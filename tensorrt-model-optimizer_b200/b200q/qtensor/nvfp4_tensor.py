@@ -1,0 +1,79 @@
+"""NVFP4 quantised tensor (reference: modelopt/torch/quantization/qtensor/nvfp4_tensor.py:31-297):
+E2M1 values packed two per byte, an E4M3 scale per 16 elements, an fp32 scale per tensor."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..utils import reduce_amax, reduce_block_padding
+from .base_qtensor import BaseQuantizedTensor
+
+__all__ = ["NVFP4QTensor"]
+
+
+class NVFP4QTensor(BaseQuantizedTensor):
+    @classmethod
+    def get_weights_scaling_factor_2_from_quantizer(cls, weight_quantizer):
+        assert hasattr(weight_quantizer, "_amax"), "Weight quantizer does not have attribute amax"
+        return weight_quantizer._amax.float() / (6.0 * 448.0)
+
+    @classmethod
+    def get_weights_scaling_factor_2(cls, input: torch.Tensor):
+        """amax / (6 * 448) as fp32."""
+        return reduce_amax(input).float() / (6.0 * 448.0)
+
+    @classmethod
+    def get_weights_scaling_factor(cls, input, block_size, weights_scaling_factor_2=None,
+                                   keep_high_precision=False):
+        """(per-block scale as float8_e4m3fn [..., K/block], weights_scaling_factor_2)."""
+        assert block_size == 16, "the NVFP4 kernels are built for block size 16"
+        assert input.shape[-1] % block_size == 0, (
+            "Weight shape is not divisible for block size for block quantization.")
+        if weights_scaling_factor_2 is None:
+            weights_scaling_factor_2 = cls.get_weights_scaling_factor_2(input)
+        if keep_high_precision:
+            amax = ops.amax_blocks(input, block_size).reshape(*input.shape[:-1], -1)
+            s = amax / (6.0 * weights_scaling_factor_2.to(amax.device))
+            s[s == 0] = 1.0
+            return s, weights_scaling_factor_2
+        _, scales, _ = ops.nvfp4_quantize(input, scale2=weights_scaling_factor_2)
+        return scales, weights_scaling_factor_2
+
+    @classmethod
+    def get_activation_scaling_factor(cls, quantizer):
+        if not quantizer.is_enabled:
+            return None
+        amax = quantizer.export_amax()
+        if amax is None:
+            return None
+        s = amax.float() / (quantizer.maxbound * 448.0)
+        assert torch.all(s > 0), f" activation scaling factor {s} not positive."
+        return s
+
+    @classmethod
+    def quantize(cls, input, block_size, weights_scaling_factor=None, weights_scaling_factor_2=None,
+                 keep_high_precision=False, try_tensorrt=False):
+        """-> (NVFP4QTensor, per-block scale float8_e4m3fn, per-tensor scale fp32).  One fused
+        kernel (plus the abs-max pass when no per-tensor scale is given)."""
+        if keep_high_precision:
+            raise NotImplementedError("keep_high_precision is not part of the accelerated path")
+        assert block_size == 16, "the NVFP4 kernels are built for block size 16"
+        shape, dtype = input.shape, input.dtype
+        x = reduce_block_padding(input, {-1: block_size})
+        packed, scales, s2 = ops.nvfp4_quantize(x, scale2=weights_scaling_factor_2,
+                                                scales_in=weights_scaling_factor)
+        if weights_scaling_factor is not None:
+            scales = weights_scaling_factor
+        if weights_scaling_factor_2 is not None:
+            s2 = weights_scaling_factor_2
+        return cls(shape, dtype, packed), scales, s2
+
+    def dequantize(self, dtype=None, fast=False, **kwarg):
+        """Needs ``scale`` (E4M3 per block), ``double_scale`` (fp32) and ``block_sizes``."""
+        dtype = dtype or self.metadata["dtype"]
+        assert kwarg["block_sizes"][-1] == 16
+        out = ops.nvfp4_dequantize(self._quantized_data, kwarg["scale"], kwarg["double_scale"], dtype)
+        shape = self.metadata["shape"]
+        if out.shape[-1] != shape[-1]:
+            out = out[..., : shape[-1]]
+        return out.reshape(shape)

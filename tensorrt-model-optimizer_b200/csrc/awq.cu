@@ -1,0 +1,139 @@
+// Kernels of the awq_lite search loop: per-input-channel scaling fused with per-block dynamic
+// integer fake quantisation of the weight, and the squared-error reduction between two GEMM
+// outputs.  The GEMM itself runs between them.
+#include "numerics.cuh"
+
+namespace b200q {
+
+template <typename T> __device__ __forceinline__ float round_t(float v) {
+  return Elem<T>::to_float(Elem<T>::from_float(v));
+}
+
+// w [rows, cols] row-major, s [cols] in T.  For every run of `block` elements along a row:
+//   v = T(w * s[col]);  amax = max|v|;  y = T(fake_int(v, amax))
+// `lanes` adjacent lanes (power of two <= 32) own one block, PPL packs each.
+template <typename T, int PPL>
+__global__ void __launch_bounds__(256)
+awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restrict__ y,
+                    int64_t nblocks, int lanes, int packs_per_row, IntQ q) {
+  using E = Elem<T>;
+  constexpr int P = E::kPerPack;
+  const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t total = nblocks * lanes;
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  const uint4* sv = reinterpret_cast<const uint4*>(s);
+  uint4* yv = reinterpret_cast<uint4*>(y);
+  for (int64_t t = gthread; t < ((total + 31) / 32) * 32; t += nthreads) {
+    const bool valid = t < total;
+    float v[PPL][P];
+    uint32_t bits = 0;
+#pragma unroll
+    for (int p = 0; p < PPL; ++p) {
+      const int64_t pk = t * PPL + p;
+      uint4 a = valid ? ld_stream(wv + pk) : make_uint4(0, 0, 0, 0);
+      uint4 b = valid ? __ldg(sv + (pk % packs_per_row)) : make_uint4(0, 0, 0, 0);
+      float fa[P], fb[P];
+      E::unpack(a, fa);
+      E::unpack(b, fb);
+#pragma unroll
+      for (int k = 0; k < P; ++k) {
+        v[p][k] = round_t<T>(fa[k] * fb[k]);
+        bits = max(bits, __float_as_uint(fabsf(v[p][k])));
+      }
+    }
+    for (int o = lanes >> 1; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+    const float amax = __uint_as_float(bits);
+    const bool live = !(amax < 5.9604644775390625e-8f);
+    const float scale = __fdiv_rn(q.bound, amax);
+    if (valid) {
+#pragma unroll
+      for (int p = 0; p < PPL; ++p) {
+#pragma unroll
+        for (int k = 0; k < P; ++k) v[p][k] = intq_apply(v[p][k], scale, live, q);
+        st_stream(yv + t * PPL + p, E::pack(v[p]));
+      }
+    }
+  }
+}
+
+// sum over i of float(T(a_i - b_i))^2, added to a double accumulator
+template <typename T>
+__global__ void __launch_bounds__(256)
+sq_diff_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, int64_t n, double* __restrict__ out) {
+  using E = Elem<T>;
+  constexpr int P = E::kPerPack;
+  __shared__ float red[8];
+  const int64_t npack = n / P;
+  const uint4* av = reinterpret_cast<const uint4*>(a);
+  const uint4* bv = reinterpret_cast<const uint4*>(b);
+  float acc = 0.f;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < npack; i += stride) {
+    float fa[P], fb[P];
+    E::unpack(ld_stream(av + i), fa);
+    E::unpack(ld_stream(bv + i), fb);
+#pragma unroll
+    for (int k = 0; k < P; ++k) {
+      const float d = round_t<T>(fa[k] - fb[k]);
+      acc = fmaf(d, d, acc);
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - npack * P) {
+    const int64_t j = npack * P + threadIdx.x;
+    const float d = round_t<T>(E::to_float(a[j]) - E::to_float(b[j]));
+    acc = fmaf(d, d, acc);
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double s = 0.0;
+    for (int i = 0; i < 8; ++i) s += static_cast<double>(red[i]);
+    atomicAdd(out, s);
+  }
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, int64_t rows, int64_t cols,
+                                        int block, int dtype, int num_bits, int is_unsigned,
+                                        int narrow_range, void* stream) {
+  B200Q_REQUIRE_PTR(w); B200Q_REQUIRE_PTR(s); B200Q_REQUIRE_PTR(y);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(w); B200Q_REQUIRE_ALIGNED(s); B200Q_REQUIRE_ALIGNED(y);
+  if (rows <= 0 || cols <= 0 || block <= 0 || cols % block) return B200Q_ERR_SHAPE;
+  if (num_bits < 1 || num_bits + (is_unsigned ? 1 : 0) > 24) return B200Q_ERR_ARG;
+  const IntQ q = make_intq(num_bits, is_unsigned, narrow_range);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&]() -> int {
+    constexpr int P = Elem<T>::kPerPack;
+    const int packs = block / P;
+    if (block % P || packs <= 0 || (packs & (packs - 1)) || packs > 64) return B200Q_ERR_UNSUPPORTED;
+    const int ppl = packs >= 2 ? 2 : 1;
+    const int lanes = packs / ppl;
+    const int64_t nblocks = rows * (cols / block);
+    int grid = grid_for(nblocks * lanes, 256, 8);
+    const T* wp = static_cast<const T*>(w);
+    const T* sp = static_cast<const T*>(s);
+    T* yp = static_cast<T*>(y);
+    const int ppr = static_cast<int>(cols / P);
+    if (ppl == 2) awq_scale_fq_kernel<T, 2><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, ppr, q);
+    else awq_scale_fq_kernel<T, 1><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, ppr, q);
+    return launch_status();
+  });
+}
+
+extern "C" int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double* sum_io,
+                                 void* stream) {
+  B200Q_REQUIRE_PTR(a); B200Q_REQUIRE_PTR(b); B200Q_REQUIRE_PTR(sum_io);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(a); B200Q_REQUIRE_ALIGNED(b);
+  if (n <= 0) return B200Q_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(n / Elem<T>::kPerPack, 256 * 4, 8);
+    sq_diff_sum_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), n, sum_io);
+    return launch_status();
+  });
+}

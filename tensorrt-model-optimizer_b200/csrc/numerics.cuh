@@ -49,6 +49,20 @@ __device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float even, float odd) {
   return __nv_cvt_float2_to_fp4x2(make_float2(even, odd), __NV_E2M1, cudaRoundNearest);
 }
 
+// Eight fp32 (four even/odd pairs) -> four bytes of E2M1 codes, first pair in the low byte.
+__device__ __forceinline__ uint32_t f32x8_to_e2m1x8(float2 p0, float2 p1, float2 p2, float2 p3) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+      "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+      : "=r"(r)
+      : "f"(p0.x), "f"(p0.y), "f"(p1.x), "f"(p1.y), "f"(p2.x), "f"(p2.y), "f"(p3.x), "f"(p3.y));
+  return r;
+}
+
 // magnitude of an E2M1 code (bits 0-2): 0,.5,1,1.5,2,3,4,6 ; bit 3 is the sign
 __device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
   const uint32_t m = code & 7u;

@@ -168,13 +168,11 @@ __device__ __forceinline__ uint2 nvfp4_encode16(const float* f, float d, float b
     const float2 y = make_float2(r, r), nd = make_float2(-d, -d);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      uint32_t acc = 0;
+      float2 q[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 q = div2_rn(make_float2(f[8 * h + 2 * j], f[8 * h + 2 * j + 1]), nd, y);
-        acc |= f32x2_to_e2m1x2(q.x, q.y) << (8 * j);
-      }
-      w[h] = acc;
+      for (int j = 0; j < 4; ++j)
+        q[j] = div2_rn(make_float2(f[8 * h + 2 * j], f[8 * h + 2 * j + 1]), nd, y);
+      w[h] = f32x8_to_e2m1x8(q[0], q[1], q[2], q[3]);
     }
   } else {
 #pragma unroll
