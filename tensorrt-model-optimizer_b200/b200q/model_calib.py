@@ -179,7 +179,7 @@ def _awq_forward(self, input, *args, **kwargs):
     for q in (self.input_quantizer, self.weight_quantizer):
         if hasattr(q, "_pre_quant_scale"):
             delattr(q, "_pre_quant_scale")
-    out_actual = F.linear(self.input_quantizer(input) if st.cache_mode_ref[0] else input, self.weight, self.bias)
+    out_actual = F.linear(input, self.weight, self.bias)
     if input.numel() == 0 or not st.is_enabled:
         return out_actual
     if st.cache_mode_ref[0]:
@@ -215,8 +215,8 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
                     st.is_enabled = False
                 else:
                     m.input_quantizer.axis = -1
-            m._forward_no_awq = m.forward
-            m.forward = _awq_forward.__get__(m, type(m))
+            m.__dict__["_forward_no_awq"] = m.forward
+            m.__dict__["forward"] = _awq_forward.__get__(m, type(m))
             layers.append((name, m))
 
     # pass 1: activation statistics
@@ -248,8 +248,8 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
 
     for name, m in layers:
         st = m.awq_lite
-        m.forward = m._forward_no_awq
-        del m._forward_no_awq
+        del m.__dict__["forward"]
+        del m.__dict__["_forward_no_awq"]
         if st.num_cache_steps == 0:
             st.is_enabled = False
         elif st.num_search_steps == 0:

@@ -357,7 +357,8 @@ class TensorQuantizer(nn.Module):
         if self._num_bits == (4, 3):
             use_amax = self.amax is not None and not (blocks_only and self.amax.numel() == 1)
             outputs, scale = FP8QTensor.quantize(inputs, axis=self._axis, block_sizes=blocks_only,
-                                                 scales=self.amax / 448.0 if use_amax else None)
+                                                 scales=self.amax / torch.full((), 448.0, dtype=self.amax.dtype, device=self.amax.device)
+                                                 if use_amax else None)
             bufs["_scale"] = scale
         elif self._num_bits == 8:
             outputs, scale = INT8QTensor.quantize(inputs, axis=self._axis, block_sizes=blocks_only)
@@ -365,7 +366,8 @@ class TensorQuantizer(nn.Module):
         elif bs.get("scale_bits") == (4, 3):
             outputs, s, s2 = NVFP4QTensor.quantize(
                 inputs, bs[-1],
-                weights_scaling_factor_2=self.amax.float() / (448.0 * 6.0) if self.amax is not None else None)
+                weights_scaling_factor_2=NVFP4QTensor.get_weights_scaling_factor_2_from_quantizer(self)
+                if self.amax is not None else None)
             bufs["_scale"], bufs["_double_scale"] = s, s2
         else:
             outputs, scale = INT4QTensor.quantize(inputs, bs[-1])

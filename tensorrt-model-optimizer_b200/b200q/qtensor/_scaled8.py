@@ -18,7 +18,8 @@ def prepare(input, scales, axis, block_sizes, divisor):
             amax = reduce_block_amax(x, block_sizes)
         else:
             amax = reduce_amax(x, axis=convert_quantization_axis_to_reduce_axis(x, axis))
-        scales = amax / divisor
+        # tensor divisor: a true division on every device (see nvfp4_tensor._scale2_from_amax)
+        scales = amax / torch.full((), divisor, dtype=amax.dtype, device=amax.device)
     if block_sizes:
         expected = list(x.shape)
         for dim, b in block_sizes.items():

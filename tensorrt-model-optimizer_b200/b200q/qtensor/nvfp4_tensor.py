@@ -11,16 +11,24 @@ from .base_qtensor import BaseQuantizedTensor
 __all__ = ["NVFP4QTensor"]
 
 
+def _scale2_from_amax(amax: torch.Tensor) -> torch.Tensor:
+    """amax / (6 * 448) in fp32 as a true division.  (Dividing a CUDA tensor by a Python number is
+    evaluated by torch as a multiplication with the rounded reciprocal, which can differ from the
+    quotient in the last bit; a tensor divisor keeps the IEEE division on every device.)"""
+    a = amax.float()
+    return a / torch.full((), 6.0 * 448.0, dtype=torch.float32, device=a.device)
+
+
 class NVFP4QTensor(BaseQuantizedTensor):
     @classmethod
     def get_weights_scaling_factor_2_from_quantizer(cls, weight_quantizer):
         assert hasattr(weight_quantizer, "_amax"), "Weight quantizer does not have attribute amax"
-        return weight_quantizer._amax.float() / (6.0 * 448.0)
+        return _scale2_from_amax(weight_quantizer._amax)
 
     @classmethod
     def get_weights_scaling_factor_2(cls, input: torch.Tensor):
         """amax / (6 * 448) as fp32."""
-        return reduce_amax(input).float() / (6.0 * 448.0)
+        return _scale2_from_amax(reduce_amax(input))
 
     @classmethod
     def get_weights_scaling_factor(cls, input, block_size, weights_scaling_factor_2=None,

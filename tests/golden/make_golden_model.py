@@ -1,0 +1,133 @@
+"""Model-level golden vectors: run the REFERENCE's mtq.quantize / mtq.compress on CPU for a small
+MLP and store what it produced (amax buffers, AWQ losses and scales, packed weights).
+
+    python tests/golden/make_golden_model.py [--ref /path/to/TensorRT-Model-Optimizer]
+
+Uses the same import shims as make_golden.py.
+"""
+from __future__ import annotations
+
+import argparse
+import copy
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+from torch import nn
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+from make_golden import bits, import_reference  # noqa: E402
+
+
+class MLP(nn.Module):
+    """Llama-style MLP names so that the wildcard patterns behave as on a real model."""
+
+    def __init__(self, hidden=128, inter=256):
+        super().__init__()
+        self.up_proj = nn.Linear(hidden, inter, bias=False)
+        self.down_proj = nn.Linear(inter, hidden, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(torch.nn.functional.silu(self.up_proj(x)))
+
+
+def make_model(seed, dtype):
+    torch.manual_seed(seed)
+    m = MLP()
+    with torch.no_grad():
+        for p in m.parameters():
+            p.copy_(torch.randn_like(p) * 0.05)
+    return m.to(dtype)
+
+
+def make_batches(seed, n, dtype, hidden=128, tokens=48):
+    g = torch.Generator().manual_seed(seed)
+    mag = torch.exp(torch.randn(hidden, generator=g))
+    return [(torch.randn(tokens, hidden, generator=g) * mag).to(dtype) for _ in range(n)]
+
+
+def golden_awq(mtq, out):
+    cases = {}
+    for tag, dtype in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        model = make_model(11, dtype)
+        batches = make_batches(12, 2, dtype)
+        cases[f"{tag}_w_up"] = bits(model.up_proj.weight)
+        cases[f"{tag}_w_down"] = bits(model.down_proj.weight)
+        for i, b in enumerate(batches):
+            cases[f"{tag}_x{i}"] = bits(b)
+        cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+        cfg["algorithm"] = {"method": "awq_lite", "alpha_step": 0.05, "debug": True}
+
+        def loop(m):
+            for b in batches:
+                m(b)
+
+        mtq.quantize(model, cfg, loop)
+        for name in ("up_proj", "down_proj"):
+            lin = getattr(model, name)
+            st = lin.awq_lite
+            cases[f"{tag}_{name}_alphas"] = np.array(list(st.loss.keys()), dtype=np.float64)
+            cases[f"{tag}_{name}_losses"] = np.array([float(v) for v in st.loss.values()], dtype=np.float64)
+            cases[f"{tag}_{name}_best_alpha"] = np.array(st.best_alpha, dtype=np.float64)
+            cases[f"{tag}_{name}_best_scale"] = st.best_scale.float().numpy()
+            cases[f"{tag}_{name}_act_scale"] = st.act_scale.float().numpy()
+            cases[f"{tag}_{name}_weight_scale"] = st.weight_scale.float().numpy()
+            cases[f"{tag}_{name}_pqs"] = bits(lin.input_quantizer._pre_quant_scale)
+            cases[f"{tag}_{name}_w_folded"] = bits(lin.weight)
+            cases[f"{tag}_{name}_w_amax"] = bits(lin.weight_quantizer._amax)
+        y = model(batches[0])
+        cases[f"{tag}_y_fake"] = bits(y)
+    np.savez_compressed(out / "awq.npz", **cases)
+
+
+def golden_flows(mtq, out):
+    """INT8 / FP8 / NVFP4 max calibration: the amax buffers the reference ends up with, and the
+    packed weights of mtq.compress for NVFP4."""
+    cases = {}
+    dtype = torch.bfloat16
+    batches = make_batches(22, 3, dtype)
+    for i, b in enumerate(batches):
+        cases[f"x{i}"] = bits(b)
+    base = make_model(21, dtype)
+    cases["w_up"] = bits(base.up_proj.weight)
+    cases["w_down"] = bits(base.down_proj.weight)
+
+    def loop(m):
+        for b in batches:
+            m(b)
+
+    for tag, cfg in (("int8", mtq.INT8_DEFAULT_CFG), ("fp8", mtq.FP8_DEFAULT_CFG), ("nvfp4", mtq.NVFP4_DEFAULT_CFG)):
+        model = copy.deepcopy(base)
+        mtq.quantize(model, copy.deepcopy(cfg), loop)
+        for name in ("up_proj", "down_proj"):
+            lin = getattr(model, name)
+            cases[f"{tag}_{name}_in_amax"] = bits(lin.input_quantizer._amax.float().reshape(-1))
+            cases[f"{tag}_{name}_w_amax"] = bits(lin.weight_quantizer._amax.float().reshape(-1))
+        if tag != "nvfp4":  # the reference has no CPU kernel for NVFP4 fake quant
+            cases[f"{tag}_y"] = bits(model(batches[0]))
+        else:
+            mtq.compress(model)
+            for name in ("up_proj", "down_proj"):
+                lin = getattr(model, name)
+                cases[f"nvfp4_{name}_packed"] = bits(lin.weight.data)
+                cases[f"nvfp4_{name}_scale"] = bits(lin.weight_quantizer._scale)
+                cases[f"nvfp4_{name}_double_scale"] = bits(lin.weight_quantizer._double_scale.reshape(1))
+            cases["nvfp4_state_keys"] = np.array(sorted(model.state_dict().keys()))
+    np.savez_compressed(out / "flows.npz", **cases)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    mtq = import_reference(args.ref)
+    golden_awq(mtq, HERE)
+    print("wrote awq")
+    golden_flows(mtq, HERE)
+    print("wrote flows")
+
+
+if __name__ == "__main__":
+    main()

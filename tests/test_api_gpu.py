@@ -1,0 +1,237 @@
+"""The modelopt-style API (quantize / calibrate / compress, TensorQuantizer, calibrators, QTensors)
+on the GPU against golden results of the reference run on CPU and against the oracle."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from oracle import quant_oracle as qo
+from _util import f32_from_tensor, load, same_bits, tensor_from_f32, to_f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mtq():
+    import b200q
+
+    return b200q
+
+
+class MLP(nn.Module):
+    def __init__(self, hidden=128, inter=256):
+        super().__init__()
+        self.up_proj = nn.Linear(hidden, inter, bias=False)
+        self.down_proj = nn.Linear(inter, hidden, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(torch.nn.functional.silu(self.up_proj(x)))
+
+
+def build(g, prefix, T, dtype):
+    m = MLP().to(dtype).cuda()
+    with torch.no_grad():
+        m.up_proj.weight.copy_(tensor_from_f32(to_f32(g[prefix + "w_up"], T), T))
+        m.down_proj.weight.copy_(tensor_from_f32(to_f32(g[prefix + "w_down"], T), T))
+    return m
+
+
+def bits_of(t):
+    t = t.detach().contiguous().cpu()
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy()
+    return t.numpy()
+
+
+@pytest.mark.parametrize("fmt", ["int8", "fp8", "nvfp4"])
+def test_quantize_max_calibration_matches_reference(mtq, fmt):
+    g = load("flows")
+    model = build(g, "", "bf16", torch.bfloat16)
+    batches = [tensor_from_f32(to_f32(g[f"x{i}"], "bf16"), "bf16") for i in range(3)]
+    cfg = {"int8": mtq.INT8_DEFAULT_CFG, "fp8": mtq.FP8_DEFAULT_CFG, "nvfp4": mtq.NVFP4_DEFAULT_CFG}[fmt]
+
+    def loop(m):
+        for b in batches:
+            m(b)
+
+    mtq.quantize(model, copy.deepcopy(cfg), loop)
+    for name in ("up_proj", "down_proj"):
+        lin = getattr(model, name)
+        assert lin.input_quantizer._amax.dtype == torch.bfloat16
+        assert same_bits(lin.input_quantizer._amax.float().reshape(-1).cpu().numpy(), g[f"{fmt}_{name}_in_amax"])
+        assert same_bits(lin.weight_quantizer._amax.float().reshape(-1).cpu().numpy(), g[f"{fmt}_{name}_w_amax"])
+    y = model(batches[0])
+    assert torch.isfinite(y).all()
+    if fmt != "nvfp4":
+        ref = to_f32(g[f"{fmt}_y"], "bf16")
+        # GEMMs accumulate in a different order on the two devices: outputs agree to bf16 noise
+        assert np.allclose(f32_from_tensor(y), ref, rtol=5e-2, atol=5e-3 * np.abs(ref).max())
+    else:
+        mtq.compress(model)
+        assert np.array_equal(np.array(sorted(model.state_dict().keys())), g["nvfp4_state_keys"])
+        for name in ("up_proj", "down_proj"):
+            lin = getattr(model, name)
+            assert type(lin).__name__ == "RealQuantLinear"
+            assert np.array_equal(bits_of(lin.weight.data), g[f"nvfp4_{name}_packed"]), name
+            assert np.array_equal(bits_of(lin.weight_quantizer._scale), g[f"nvfp4_{name}_scale"]), name
+            assert same_bits(lin.weight_quantizer._double_scale.reshape(1).cpu().numpy(),
+                             g[f"nvfp4_{name}_double_scale"]), name
+        y2 = model(batches[0])  # forward through dequantised packed weights
+        assert torch.isfinite(y2).all()
+        assert np.allclose(f32_from_tensor(y2), f32_from_tensor(y), rtol=5e-2, atol=1e-2 * float(y.abs().max()))
+
+
+@pytest.mark.parametrize("T,dtype", [("bf16", torch.bfloat16), ("f32", torch.float32)])
+def test_awq_lite_matches_reference(mtq, T, dtype):
+    g = load("awq")
+    p = T + "_"
+    model = build(g, p, T, dtype)
+    batches = [tensor_from_f32(to_f32(g[f"{p}x{i}"], T), T) for i in range(2)]
+    cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+    cfg["algorithm"] = {"method": "awq_lite", "alpha_step": 0.05, "debug": True}
+
+    def loop(m):
+        for b in batches:
+            m(b)
+
+    mtq.quantize(model, cfg, loop)
+    for name in ("up_proj", "down_proj"):
+        lin = getattr(model, name)
+        st = lin.awq_lite
+        k = f"{p}{name}_"
+        assert np.array_equal(np.array(list(st.loss.keys()), dtype=np.float64), g[k + "alphas"])  # 21 fp32 keys
+        # statistics are reduced in the tensor dtype: equal up to a bf16 rounding flip in rare channels
+        tol = 1e-2 if T == "bf16" else 1e-5
+        assert np.allclose(st.weight_scale.cpu().numpy(), g[k + "weight_scale"], rtol=tol)
+        assert np.allclose(st.act_scale.cpu().numpy(), g[k + "act_scale"], rtol=tol)
+        losses = np.array([float(v) for v in st.loss.values()])
+        ref = g[k + "losses"]
+        assert np.allclose(losses, ref, rtol=5e-2), (losses / ref)
+        # selected alpha: equal, or a neighbour whose reference loss is within 2 % of the minimum
+        if st.best_alpha != float(g[k + "best_alpha"]):
+            i = list(st.loss.keys()).index(st.best_alpha)
+            assert ref[i] <= ref.min() * 1.02, (st.best_alpha, float(g[k + "best_alpha"]))
+        else:
+            assert np.allclose(st.best_scale.cpu().numpy(), g[k + "best_scale"], rtol=max(tol, 1e-3))
+            pqs = lin.input_quantizer._pre_quant_scale.float().cpu().numpy()
+            assert np.allclose(pqs, to_f32(g[k + "pqs"], T), rtol=2e-2 if T == "bf16" else 1e-3)
+            wf = f32_from_tensor(lin.weight)
+            ref_w = to_f32(g[k + "w_folded"], T)
+            assert np.mean(wf != ref_w) < (0.02 if T == "bf16" else 1.0)
+            assert np.allclose(wf, ref_w, rtol=2e-2, atol=1e-6)
+        assert lin.weight_quantizer._amax.shape == g[k + "w_amax"].shape
+    assert torch.isfinite(model(batches[0])).all()
+    mtq.compress(model)
+    assert model.up_proj.weight.dtype == torch.uint8
+    assert model.up_proj.weight.shape == (256, 64)
+    assert torch.isfinite(model(batches[0])).all()
+
+
+def test_awq_scale_fake_int_kernel_vs_oracle(mtq):
+    from b200q import ops
+
+    rng = np.random.default_rng(3)
+    for T in ("bf16", "f16", "f32"):
+        w = qo.round_to(rng.standard_normal((96, 512)).astype(np.float32) * 0.02, T)
+        s = qo.round_to(np.exp(rng.standard_normal(512)).astype(np.float32), T)
+        y = ops.awq_scale_fake_int(tensor_from_f32(w, T), tensor_from_f32(s, T), 128, 4, False, False)
+        v = qo.round_to((w * s[None, :]).astype(np.float32), T).reshape(-1, 128)
+        amax = np.abs(v).max(-1, keepdims=True)
+        want = qo.fake_int(v, amax, 4, False, False, T).reshape(w.shape)
+        assert same_bits(f32_from_tensor(y), want), T
+        a = tensor_from_f32(w, T)
+        b = tensor_from_f32(want, T)
+        d = qo.round_to((w - want).astype(np.float32), T).astype(np.float64)
+        got = ops.mse_loss(a, b).item()
+        assert abs(got - (d ** 2).mean()) <= 1e-6 * (d ** 2).mean()
+
+
+def test_tensor_quantizer_block_quant_with_padding_matches_oracle(mtq):
+    from b200q.nn import TensorQuantizer
+
+    x = qo.round_bf16(np.random.default_rng(0).standard_normal((24, 200)).astype(np.float32))
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=4, block_sizes={-1: 128})).cuda()
+    xt = tensor_from_f32(x, "bf16")
+    y = q(xt)                                   # dynamic block amax (fused kernel), padded to 256
+    xp = qo.pad_last(x, 128).reshape(-1, 128)
+    want = qo.fake_int(xp, np.abs(xp).max(-1, keepdims=True), 4, False, False, "bf16").reshape(24, 256)[:, :200]
+    assert y.shape == xt.shape and same_bits(f32_from_tensor(y), want)
+    # calibrated: amax buffer per block, same result; export shape follows the reference
+    mtq.max_calibrate(q, lambda m: m(xt), distributed_sync=False)
+    assert q._amax.shape == (48, 1)
+    assert same_bits(f32_from_tensor(q(xt)), want)
+    assert q.export_amax().shape == (24, 2)
+
+
+def test_tensor_quantizer_pre_quant_scale_and_per_channel(mtq):
+    from b200q.nn import TensorQuantizer
+
+    x = qo.round_bf16(np.random.default_rng(1).standard_normal((64, 256)).astype(np.float32))
+    xt = tensor_from_f32(x, "bf16")
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8, axis=0, narrow_range=True)).cuda()
+    mtq.max_calibrate(q, lambda m: m(xt), distributed_sync=False)
+    amax = np.abs(x).max(-1, keepdims=True)
+    assert same_bits(q._amax.float().cpu().numpy(), amax)
+    assert same_bits(f32_from_tensor(q(xt)), qo.fake_int(x, amax, 8, False, True, "bf16"))
+    pqs = qo.round_bf16(np.linspace(0.5, 2, 256).astype(np.float32))
+    q2 = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=(4, 3))).cuda()
+    q2.pre_quant_scale = tensor_from_f32(pqs, "bf16")
+    xs = qo.round_bf16(x * pqs[None, :])
+    q2.amax = torch.tensor(float(np.abs(xs).max()), device="cuda")
+    assert same_bits(f32_from_tensor(q2(xt)), qo.fake_e4m3(xs, np.float32(np.abs(xs).max()), "bf16"))
+
+
+def test_histogram_calibrator_matches_reference_sequence(mtq):
+    g = load("hist")
+    cal = mtq.calib.HistogramCalibrator(8, None, False, num_bins=2048)
+    for b in range(3):
+        cal.collect(tensor_from_f32(to_f32(g[f"x{b}"], "bf16"), "bf16"))
+        ref = g[f"hist{b}"]
+        got = cal.hist.cpu().numpy()
+        assert got.size == ref.size and got.sum() == ref.sum(), b
+        assert np.abs(got - ref).sum() <= 2e-3 * ref.sum(), b
+        assert np.allclose(cal._calib_bin_edges.cpu().numpy(), g[f"edges{b}"], rtol=1e-5)
+    for p in (99.0, 99.9, 99.99, 100.0):
+        a = cal.compute_amax("percentile", percentile=p).item()
+        assert abs(a - g[f"pct_{p}"]) <= 1e-3 * g[f"pct_{p}"], p
+    e = cal.compute_amax("entropy").item()
+    assert abs(e - g["entropy"]) <= 1e-3 * g["entropy"] + 2 * float(cal._calib_bin_edges[1])
+    q = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8, calibrator="histogram")).cuda()
+    q.enable_calib(); q.disable_quant()
+    for b in range(3):
+        q(tensor_from_f32(to_f32(g[f"x{b}"], "bf16"), "bf16"))
+    q.load_calib_amax("percentile", percentile=99.99)
+    assert abs(q.amax.item() - g["pct_99.99"]) <= 1e-3 * g["pct_99.99"]
+
+
+def test_qtensor_classes_roundtrip(mtq):
+    from b200q.qtensor import FP8QTensor, INT4QTensor, INT8QTensor, NVFP4QTensor
+
+    x = qo.round_bf16(np.random.default_rng(2).standard_normal((32, 200)).astype(np.float32) * 0.05)
+    xt = tensor_from_f32(x, "bf16")
+    q, s, s2 = NVFP4QTensor.quantize(xt, 16)                       # pads 200 -> 208
+    wp, ws, ws2 = qo.nvfp4_quantize(x, 16)
+    assert np.array_equal(q._quantized_data.cpu().numpy(), wp) and s2.item() == ws2
+    d = q.dequantize(scale=s, double_scale=s2, block_sizes={-1: 16})
+    assert d.shape == xt.shape
+    assert same_bits(f32_from_tensor(d), qo.nvfp4_dequantize(wp, ws, ws2, 16, "bf16")[:, :200])
+    qi, si = INT4QTensor.quantize(xt, 128)
+    pk, sc = qo.int4_quantize(x, 128, "bf16")
+    assert np.array_equal(qi._quantized_data.cpu().numpy().reshape(-1), pk)
+    di = qi.dequantize(scale=si, block_sizes={-1: 128})
+    assert same_bits(f32_from_tensor(di).reshape(-1), qo.int4_dequantize(pk, sc, 128, "bf16")[: x.size])
+    for cls, fn, div in ((FP8QTensor, qo.fp8_quantize, 448.0), (INT8QTensor, qo.int8_quantize, 127.0)):
+        for kw, view in (({}, None), ({"axis": 0}, (-1, 1)), ({"block_sizes": {-1: 40}}, None)):
+            qq, ss = cls.quantize(xt, **kw)
+            sf = ss.float().cpu().numpy()
+            if "block_sizes" in kw:
+                want = fn(x.reshape(32, 5, 40), sf.reshape(32, 5, 1), "bf16").reshape(32, 200)
+            else:
+                want = fn(x, sf.reshape(view) if view else sf.reshape(()), "bf16")
+            assert np.array_equal(qq._quantized_data.view(torch.uint8).cpu().numpy(), want.view(np.uint8)), (cls, kw)
+            dd = qq.dequantize(scale=ss, **({"block_sizes": kw["block_sizes"]} if "block_sizes" in kw else {}))
+            assert dd.shape == xt.shape and torch.isfinite(dd).all()

@@ -1,0 +1,225 @@
+"""Host-side logic that needs no GPU: configuration matching, module conversion, state-dict
+names, quantiser bookkeeping and the batched data-parallel exchanges over gloo (2 CPU ranks)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+from torch import nn
+
+import b200q as mtq
+from b200q.calib import HistogramCalibrator
+from b200q.nn import QuantLinear, SequentialQuantizer, TensorQuantizer
+
+
+class MLP(nn.Module):
+    def __init__(self, hidden=32, inter=64):
+        super().__init__()
+        self.up_proj = nn.Linear(hidden, inter, bias=False)
+        self.down_proj = nn.Linear(inter, hidden, bias=False)
+        self.lm_head = nn.Linear(hidden, 10, bias=False)
+
+    def forward(self, x):
+        return self.lm_head(self.down_proj(torch.relu(self.up_proj(x))))
+
+
+def test_convert_and_configure_by_wildcards():
+    m = MLP()
+    keys_before = list(m.state_dict().keys())
+    mtq.replace_quant_module(m)
+    assert isinstance(m.up_proj, QuantLinear) and isinstance(m.lm_head, QuantLinear)
+    assert list(m.state_dict().keys()) == keys_before  # no buffers until calibrated
+    mtq.set_quantizer_by_cfg(m, mtq.NVFP4_DEFAULT_CFG["quant_cfg"])
+    q = m.up_proj.weight_quantizer
+    assert q.is_enabled and q.num_bits == (2, 1) and q.block_sizes[-1] == 16
+    assert q.block_sizes["scale_bits"] == (4, 3) and q.maxbound == 6.0
+    assert m.up_proj.input_quantizer.is_enabled
+    assert not m.up_proj.output_quantizer.is_enabled          # "default": disabled
+    assert not m.lm_head.weight_quantizer.is_enabled          # "*lm_head*": disabled
+    assert not m.lm_head.input_quantizer.is_enabled
+
+
+def test_int4_awq_config_and_sequential():
+    m = MLP()
+    mtq.replace_quant_module(m)
+    mtq.set_quantizer_by_cfg(m, mtq.INT4_AWQ_CFG["quant_cfg"])
+    q = m.down_proj.weight_quantizer
+    assert q.num_bits == 4 and q.block_sizes == {-1: 128, "type": "static"} and q.is_static_block_quant
+    assert not m.down_proj.input_quantizer.is_enabled
+    assert q.maxbound == 7 and not q.narrow_range
+    # a list of attribute dicts makes a SequentialQuantizer
+    mtq.set_quantizer_attribute(m, "*up_proj.weight_quantizer",
+                                [{"num_bits": 4, "block_sizes": {-1: 128}}, {"num_bits": (4, 3)}])
+    assert isinstance(m.up_proj.weight_quantizer, SequentialQuantizer) and len(m.up_proj.weight_quantizer) == 2
+    with SequentialQuantizer.convert_to_single_quantizer(m):
+        assert isinstance(m.up_proj.weight_quantizer, TensorQuantizer)
+    assert isinstance(m.up_proj.weight_quantizer, SequentialQuantizer)
+
+
+def test_enable_disable_keeps_attributes():
+    m = MLP()
+    mtq.replace_quant_module(m)
+    mtq.set_quantizer_by_cfg(m, mtq.INT8_DEFAULT_CFG["quant_cfg"])
+    mtq.disable_quantizer(m, "*up_proj*")
+    assert not m.up_proj.weight_quantizer.is_enabled and m.up_proj.weight_quantizer.axis == 0
+    mtq.enable_quantizer(m, "*up_proj.weight_quantizer")
+    assert m.up_proj.weight_quantizer.is_enabled and not m.up_proj.input_quantizer.is_enabled
+
+
+def test_quantizer_attribute_validation_and_amax_rules():
+    with pytest.raises(ValueError):
+        mtq.QuantizerAttributeConfig(num_bits=0)
+    with pytest.raises(ValueError):
+        mtq.QuantizerAttributeConfig(axis=0, block_sizes={-1: 16})
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8, axis=0))
+    q.amax = torch.ones(4, 1)
+    with pytest.raises(RuntimeError):
+        q.amax = torch.ones(5, 1)          # shape change is refused, as in the reference
+    assert "_amax" in q.state_dict()
+    q.reset_amax()
+    assert q.amax is None
+    with pytest.raises(ValueError):         # negative amax is rejected where it is produced
+        q.validate_attr(attr_value=torch.tensor([-1.0]), raise_error=True)
+    e = q.export_amax()
+    assert e is None
+
+
+def test_export_amax_shapes():
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8))
+    q.amax = torch.tensor(0.0)
+    assert q.export_amax().shape == (1,) and q.export_amax().item() == 127   # 0 -> maxbound
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8, axis=0))
+    q.amax = torch.rand(6, 1) + 0.1
+    assert q.export_amax().shape == (6,)
+
+
+def test_kernels_refuse_cpu_tensors():
+    from b200q import ops
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.amax_tensor(torch.randn(64))
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8))
+    q.amax = torch.tensor(1.0)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        q(torch.randn(4, 16))
+
+
+def test_awq_scale_formula_matches_reference_definition():
+    from b200q.model_calib import get_scale
+
+    a = torch.tensor([1.0, 4.0, 0.25, 9.0])
+    w = torch.tensor([0.5, 0.5, 1.0, 0.1])
+    s = get_scale(a, w, 0.5)
+    raw = (a.pow(0.5) / (w.pow(0.5) + torch.finfo(torch.float32).tiny)).clamp(1e-4, 1e4)
+    assert torch.allclose(s, raw / (raw.max() * raw.min()).sqrt())
+    assert torch.allclose(s.max() * s.min(), torch.tensor(1.0))
+
+
+# ------------------------------------------------------------------------------- gloo ranks ----
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _spawn(fn, world=2):
+    port = _free_port()
+    mp.spawn(_entry, args=(world, port, fn), nprocs=world, join=True)
+
+
+def _entry(rank, world, port, fn):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        fn(rank, world)
+    finally:
+        dist.destroy_process_group()
+
+
+def _amax_job(rank, world):
+    torch.manual_seed(0)
+    m = MLP()
+    mtq.replace_quant_module(m)
+    mtq.set_quantizer_by_cfg(m, mtq.INT8_DEFAULT_CFG["quant_cfg"])
+    g = torch.Generator().manual_seed(100 + rank)      # different data per data-parallel rank
+    local = {}
+    for name, q in m.named_modules():
+        if isinstance(q, TensorQuantizer) and q.is_enabled:
+            shape = (64, 1) if name == "up_proj.weight_quantizer" else (32, 1) if "weight" in name else ()
+            q.amax = torch.rand(shape, generator=g) + rank
+            local[name] = q.amax.clone()
+    n = mtq.dist.sync_amax(m)
+    assert n == 1, "all amaxes must travel in one collective"
+    for name, q in m.named_modules():
+        if name in local:
+            gathered = [torch.zeros_like(local[name]) for _ in range(world)]
+            dist.all_gather(gathered, local[name])
+            assert torch.equal(q.amax, torch.stack(gathered).amax(0)), name
+    # a second sync changes nothing (MAX is idempotent) — the reference's own DP invariant
+    before = {n_: q.amax.clone() for n_, q in m.named_modules() if n_ in local}
+    mtq.dist.sync_amax(m)
+    assert all(torch.equal(before[n_], q.amax) for n_, q in m.named_modules() if n_ in local)
+
+
+def test_sync_amax_two_gloo_ranks():
+    _spawn(_amax_job)
+
+
+def _hist_job(rank, world):
+    m = MLP()
+    mtq.replace_quant_module(m)
+    cfg = {"*input_quantizer": {"num_bits": 8, "axis": None, "calibrator": "histogram"},
+           "*weight_quantizer": {"enable": False}, "default": {"enable": False}}
+    mtq.set_quantizer_by_cfg(m, cfg)
+    cals = [(n, q._calibrator) for n, q in m.named_modules()
+            if isinstance(q, TensorQuantizer) and q.is_enabled]
+    assert len(cals) == 3 and all(isinstance(c, HistogramCalibrator) for _, c in cals)
+    # rank 0's first-batch maxima define the common bin width
+    first_max = {n: 1.0 + i + 10.0 * rank for i, (n, _) in enumerate(cals)}
+    mtq.dist.agree_histogram_ranges(m, first_max, torch.device("cpu"))
+    rng = np.random.default_rng(5 + rank)
+    mine = []
+    for i, (n, c) in enumerate(cals):
+        assert abs(float(c._calib_bin_edges[-1]) - (1.0 + i)) < 1e-6     # rank 0's value everywhere
+        nb = 2048 + (300 * rank if i == 1 else 0)                          # rank 1 grew one histogram
+        h = torch.from_numpy(rng.integers(0, 1000, nb))
+        c._calib_hist, c._num_bins = h.clone(), nb
+        if nb != 2048:
+            w = c._calib_bin_edges[1] - c._calib_bin_edges[0]
+            c._calib_bin_edges = torch.arange(nb + 1, dtype=torch.float32) * w
+        mine.append(h)
+    assert mtq.dist.sync_histograms(m) == 2
+    for i, (n, c) in enumerate(cals):
+        nb = 2048 + (300 if i == 1 else 0)
+        assert c._num_bins == nb and c._calib_hist.numel() == nb and c._calib_bin_edges.numel() == nb + 1
+        pad = torch.zeros(nb, dtype=torch.int64)
+        pad[: mine[i].numel()] = mine[i]
+        gathered = [torch.zeros_like(pad) for _ in range(world)]
+        dist.all_gather(gathered, pad)
+        assert torch.equal(c._calib_hist, sum(gathered)), n
+
+
+def test_sync_histograms_two_gloo_ranks():
+    _spawn(_hist_job)
+
+
+def _failing_rank_job(rank, world):
+    """A rank that never joins the exchange: the others get an error from the collective's
+    timeout instead of hanging (host-side failure, no GPU involved)."""
+    import datetime
+
+    pg = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=2))
+    q = TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8))
+    q.amax = torch.tensor(float(rank + 1))
+    if rank == 1:
+        return                              # leaves between steps, nothing in flight
+    with pytest.raises(RuntimeError):
+        mtq.dist.flat_all_reduce([q._amax], dist.ReduceOp.MAX, group=pg)
+
+
+def test_missing_rank_surfaces_as_error():
+    _spawn(_failing_rank_job)
