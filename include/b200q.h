@@ -30,7 +30,8 @@ typedef enum {
   B200Q_ERR_ARG = -5,         /* other argument out of range (bits, flags, ...) */
   B200Q_ERR_CUDA = -6,        /* the CUDA runtime reported an error at launch */
   B200Q_ERR_UNSUPPORTED = -7, /* valid request the kernels do not cover */
-  B200Q_ERR_TIMEOUT = -8      /* a bounded device-side wait ran out (see b200q_last_device_status) */
+  B200Q_ERR_TIMEOUT = -8,     /* a bounded device-side wait ran out */
+  B200Q_ERR_CAPACITY = -9     /* request larger than the library's built-in scratch */
 } b200q_status;
 
 const char* b200q_strerror(int status);
@@ -149,6 +150,25 @@ int b200q_nvfp4_group_amax(const b200q_nvfp4_desc* descs, int n, int64_t total_t
                            void* stream);
 int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles,
                                int dtype, void* stream);
+
+/* Grouped NVFP4 quantisation (abs-max pass + quantise pass, same results as the two calls above)
+ * for callers that are not allowed to allocate device memory where they quantise — an
+ * inference-engine plugin inside its enqueue call, a service whose memory is handed out once at
+ * start-up, a process under a hard memory cap.  This entry point has no counterpart in the
+ * reference.  It calls no allocator of any kind: the descriptor table and the per-tensor abs-max
+ * slots, which the other grouped calls expect from the caller, live in an array built into the
+ * library (about 62 KB on every GPU that loads it, until the process exits).
+ *   host_descs: HOST array of n descriptors; x, packed, scales, s2, nblocks are read (device
+ *               pointers the caller owns), amax and tile_begin are ignored.
+ *   n:          at most b200q_nvfp4_group_max_tensors_noalloc() (1024); more is refused with
+ *               B200Q_ERR_CAPACITY and nothing is launched.
+ * The first call made on a device looks up the array's device address; make that call before any
+ * stream capture begins.  All calls on a device share the one array: the table is rewritten and
+ * the abs-max slots cleared by every call, and two calls whose GPU work overlaps (different
+ * streams, different threads) race on it — serialise them. */
+int b200q_nvfp4_group_quantize_noalloc(const b200q_nvfp4_desc* host_descs, int n, int dtype,
+                                       void* stream);
+int b200q_nvfp4_group_max_tensors_noalloc(void);
 
 /* ---------------------------------------------------------------- INT4 block -------------- */
 

@@ -41,6 +41,8 @@ SIGNATURES = {
     "b200q_nvfp4_group_tile_elems": [],
     "b200q_nvfp4_group_amax": [_p, _i, _i64, _i, _p],
     "b200q_nvfp4_group_quantize": [_p, _i, _i64, _i, _p],
+    "b200q_nvfp4_group_quantize_noalloc": [_p, _i, _i, _p],
+    "b200q_nvfp4_group_max_tensors_noalloc": [],
     "b200q_int4_quantize": [_p, _i64, _i, _i, _p, _p, _p, _p],
     "b200q_int4_dequantize": [_p, _p, _p, _i64, _i, _i, _p],
     "b200q_fp8_quantize": [_p, _p, _p, _i64, _i64, _i64, _i, _p],
@@ -51,7 +53,8 @@ SIGNATURES = {
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
 }
 _RESTYPES = {"b200q_strerror": C.c_char_p}
-_NO_STATUS = {"b200q_strerror", "b200q_version", "b200q_sm_count", "b200q_nvfp4_group_tile_elems"}
+_NO_STATUS = {"b200q_strerror", "b200q_version", "b200q_sm_count", "b200q_nvfp4_group_tile_elems",
+              "b200q_nvfp4_group_max_tensors_noalloc"}
 
 
 def _load() -> C.CDLL:

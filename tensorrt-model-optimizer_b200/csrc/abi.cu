@@ -12,6 +12,7 @@ extern "C" const char* b200q_strerror(int status) {
     case B200Q_ERR_CUDA: return "CUDA runtime error at launch";
     case B200Q_ERR_UNSUPPORTED: return "request not covered by the kernels";
     case B200Q_ERR_TIMEOUT: return "bounded device-side wait ran out";
+    case B200Q_ERR_CAPACITY: return "request exceeds the scratch capacity built into the library";
     default: return "unknown status";
   }
 }

@@ -477,3 +477,81 @@ extern "C" int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, 
     return launch_status();
   });
 }
+
+// ---- grouped quantisation without any allocation -------------------------------------------------
+// Some hosts may not allocate device memory at the point where they quantise: an inference-engine
+// plugin inside its enqueue call, a service whose memory is handed out once at start-up by a
+// budgeting allocator, a process sharing the GPU under a hard memory cap.  The grouped kernels need
+// scratch the caller would otherwise have to provide (the descriptor table in device memory and one
+// abs-max slot per tensor), so this variant keeps that scratch in the library image itself.
+//
+// The array below is part of every CUDA context that loads the library (about 62 KB per GPU, held
+// until the process exits).  Its name is only a host-side handle: the device address is fetched per
+// device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+namespace b200q {
+
+constexpr int kNoAllocMaxTensors = 1024;
+constexpr size_t kNoAllocDescBytes = sizeof(b200q_nvfp4_desc) * kNoAllocMaxTensors;
+constexpr size_t kNoAllocAmaxOffset = (kNoAllocDescBytes + 255) / 256 * 256;
+constexpr size_t kNoAllocBytes = kNoAllocAmaxOffset + sizeof(float) * kNoAllocMaxTensors;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+static unsigned char* g_noalloc_ptr[kMaxDevices] = {};   // device address of the array, per device
+
+// Device address of the scratch array on the current device (looked up on the first call made
+// with that device current; a benign race between threads stores the same value twice).
+static int noalloc_scratch(unsigned char** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200Q_ERR_CUDA;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return B200Q_ERR_CUDA;
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return B200Q_OK;
+}
+
+}  // namespace b200q
+
+extern "C" int b200q_nvfp4_group_max_tensors_noalloc(void) { return kNoAllocMaxTensors; }
+
+extern "C" int b200q_nvfp4_group_quantize_noalloc(const b200q_nvfp4_desc* host_descs, int n, int dtype,
+                                                  void* stream) {
+  B200Q_REQUIRE_PTR(host_descs);
+  B200Q_REQUIRE_DTYPE(dtype);
+  if (n <= 0) return B200Q_ERR_SHAPE;
+  if (n > kNoAllocMaxTensors) return B200Q_ERR_CAPACITY;
+  unsigned char* scratch = nullptr;
+  if (int e = noalloc_scratch(&scratch)) return e;
+  b200q_nvfp4_desc* d_descs = reinterpret_cast<b200q_nvfp4_desc*>(scratch);
+  float* d_amax = reinterpret_cast<float*>(scratch + kNoAllocAmaxOffset);
+
+  // host copy of the table on the stack: abs-max slots redirected into the scratch, tiles numbered
+  b200q_nvfp4_desc table[kNoAllocMaxTensors];
+  int64_t tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    table[i] = host_descs[i];
+    if (table[i].x == nullptr || table[i].packed == nullptr) return B200Q_ERR_NULL;
+    if (table[i].nblocks <= 0) return B200Q_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(table[i].x) & 31u) || (reinterpret_cast<uintptr_t>(table[i].packed) & 7u))
+      return B200Q_ERR_ALIGN;
+    table[i].amax = d_amax + i;
+    table[i].tile_begin = tiles;
+    tiles += (table[i].nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the table is overwritten and the abs-max
+  // slots, which the first kernel only ever raises, are cleared.
+  if (cudaMemcpyAsync(d_descs, table, sizeof(b200q_nvfp4_desc) * n, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return B200Q_ERR_CUDA;
+  if (cudaMemsetAsync(d_amax, 0, sizeof(float) * n, s) != cudaSuccess) return B200Q_ERR_CUDA;
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(tiles, 1, 8);
+    nvfp4_group_amax_kernel<T><<<grid, kNvThreads, 0, s>>>(d_descs, n, tiles);
+    nvfp4_group_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(d_descs, n, tiles);
+    return launch_status();
+  });
+}
