@@ -123,22 +123,21 @@ def cpu_nvfp4_sample(seconds_target: float = 15.0, threads: int | None = None):
     """Time the oracle's NVFP4 quantisation (the reference's torch-path arithmetic, numpy) on host
     cores over row chunks of k_proj-shaped weights; returns (GB/s of algorithmic bytes, info)."""
     import numpy as np
-    from concurrent.futures import ThreadPoolExecutor
 
+    from oracle import cref
     from oracle import quant_oracle as qo
 
     threads = threads or os.cpu_count() or 1
+    lib = cref.load()
     rng = np.random.default_rng(0)
-    rows, cols = 1024, 4096
+    rows, cols = 14336, 4096
     w = rng.standard_t(4, size=(rows, cols)).astype(np.float32) * np.float32(0.02 / 2 ** 0.5)
-    w = qo.round_bf16(w)
-    chunks = np.array_split(np.arange(rows), threads * 2)
+    bits = (qo.round_bf16(w).view(np.uint32) >> 16).astype(np.uint16).reshape(-1)
+    out = (np.empty(bits.size // 2, np.uint8), np.empty(bits.size // 16, np.uint8))
 
     def one_pass():
-        amax = qo.reduce_amax(w)
-        s2 = qo.nvfp4_scale2(amax)
-        with ThreadPoolExecutor(threads) as ex:
-            list(ex.map(lambda idx: qo.nvfp4_quantize(w[idx[0]:idx[-1] + 1], 16, s2=s2), chunks))
+        # abs-max pass + quantise/pack pass, as the reference's NVFP4QTensor.quantize does
+        cref.nvfp4_quantize_bf16(lib, bits, -1.0, threads, out)
 
     one_pass()
     t0 = time.perf_counter()
@@ -151,8 +150,9 @@ def cpu_nvfp4_sample(seconds_target: float = 15.0, threads: int | None = None):
     dt = (time.perf_counter() - t0) / reps
     gbs = rows * cols * BYTES_TOTAL / dt / 1e9
     return gbs, {"cores": threads, "kind": "port",
-                 "sample": f"{reps} passes over one k_proj-shaped weight [{rows},{cols}] bf16 "
-                           f"({dt * 1e3:.1f} ms per pass), numpy oracle, {threads} threads"}
+                 "sample": f"{reps} passes over one gate_proj-shaped weight [{rows},{cols}] bf16 "
+                           f"({dt * 1e3:.1f} ms per pass), C restatement of the reference's torch path "
+                           f"(oracle/nvfp4_ref.c), {threads} threads"}
 
 
 def run_reference(args):

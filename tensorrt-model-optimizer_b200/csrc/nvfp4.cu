@@ -9,8 +9,18 @@
 
 namespace b200q {
 
-constexpr int kNvThreads = 256;
-constexpr int kNvUnroll = 2;                              // blocks in flight per thread
+#ifndef B200Q_NV_THREADS
+#define B200Q_NV_THREADS 256
+#endif
+#ifndef B200Q_NV_UNROLL
+#define B200Q_NV_UNROLL 2
+#endif
+#ifndef B200Q_NV_CTAS
+#define B200Q_NV_CTAS 8
+#endif
+constexpr int kNvCtasPerSm = B200Q_NV_CTAS;
+constexpr int kNvThreads = B200Q_NV_THREADS;
+constexpr int kNvUnroll = B200Q_NV_UNROLL;                // blocks in flight per thread
 constexpr int kNvTileBlocks = kNvThreads * kNvUnroll;     // 16-element blocks per CTA tile
 constexpr int kNvTileElems = kNvTileBlocks * 16;
 
@@ -70,9 +80,21 @@ template <> struct Block16<__nv_bfloat16> {
     for (int i = 0; i < 8; ++i) a.w[i] = 0;
   }
   __device__ __forceinline__ uint32_t amax_f32bits() const {
+#ifdef B200Q_NV_HMAX
+    // |x| max as packed bf16 arithmetic (NaN-propagating), tree of 7 ops
+    __nv_bfloat162 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&a.w[i]));
+#pragma unroll
+    for (int s = 4; s > 0; s >>= 1)
+#pragma unroll
+      for (int i = 0; i < s; ++i) v[i] = __hmax2_nan(v[i], v[i + s]);
+    const uint32_t m = *reinterpret_cast<uint32_t*>(&v[0]);
+#else
     uint32_t m = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) m = __vmaxu2(m, a.w[i] & 0x7fff7fffu);
+#endif
     return max(m & 0xffffu, m >> 16) << 16;
   }
   __device__ __forceinline__ void decode(float* f) const {
@@ -461,7 +483,7 @@ extern "C" int b200q_nvfp4_group_amax(const b200q_nvfp4_desc* descs, int n, int6
   if (int e = check_group(descs, n, total_tiles, dtype)) return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return B200Q_DISPATCH(dtype, [&] {
-    int grid = grid_for(total_tiles, 1, 8);
+    int grid = grid_for(total_tiles, 1, kNvCtasPerSm);
     nvfp4_group_amax_kernel<T><<<grid, kNvThreads, 0, s>>>(descs, n, total_tiles);
     return launch_status();
   });
@@ -472,7 +494,7 @@ extern "C" int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, 
   if (int e = check_group(descs, n, total_tiles, dtype)) return e;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return B200Q_DISPATCH(dtype, [&] {
-    int grid = grid_for(total_tiles, 1, 8);
+    int grid = grid_for(total_tiles, 1, kNvCtasPerSm);
     nvfp4_group_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(descs, n, total_tiles);
     return launch_status();
   });

@@ -163,3 +163,25 @@ def test_histogram_matches_reference_within_tolerance():
     # entropy on the reference's own histogram: exact same algorithm -> same edge
     amax = qo.entropy_amax(g["hist2"], g["edges2"], 8, False)
     assert abs(amax - g["entropy"]) <= 1e-3 * g["entropy"]
+
+
+def test_c_restatement_matches_numpy_oracle_and_golden():
+    """oracle/nvfp4_ref.c (the CPU baseline that bench.py times) gives the reference's bytes."""
+    from oracle import cref
+
+    lib = cref.load()
+    g = load("nvfp4")
+    for j in (0, 1):
+        x = g[f"bf16_{j}_x"]
+        packed, scales, s2 = cref.nvfp4_quantize_bf16(lib, x.reshape(-1))
+        assert np.array_equal(packed, g[f"bf16_{j}_packed"].reshape(-1))
+        assert np.array_equal(scales, g[f"bf16_{j}_scales"].reshape(-1))
+        assert same_bits(np.array([s2]), g[f"bf16_{j}_s2"])
+    rng = np.random.default_rng(0)
+    x = qo.round_bf16((rng.standard_t(4, size=(256, 512)) * 0.02).astype(np.float32))
+    x[3, :16] = 0
+    bits = (x.view(np.uint32) >> 16).astype(np.uint16)
+    for amax in (-1.0, float(np.abs(x).max()) / 3):     # own amax, and a clipped one (NaN scale codes)
+        packed, scales, s2 = cref.nvfp4_quantize_bf16(lib, bits.reshape(-1), amax, threads=3)
+        wp, ws, ws2 = qo.nvfp4_quantize(x, 16, amax=None if amax < 0 else np.float32(amax))
+        assert np.array_equal(packed, wp.reshape(-1)) and np.array_equal(scales, ws.reshape(-1)) and s2 == ws2
