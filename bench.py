@@ -278,6 +278,12 @@ def run_b200(args):
         gbs, info = cpu_nvfp4_sample(12.0)
         cpu = {"value": gbs, "unit": "GB/s", **info}
 
+    formats = None
+    if world == 1 and not args.no_formats:
+        del group, weights
+        torch.cuda.empty_cache()
+        formats = run_formats(dev, peaks()[0])
+
     if rank == 0:
         peak, which = peaks()
         per_rank_elems = my_elems  # rank 0's share; shares are equal when world divides the layers
@@ -303,10 +309,68 @@ def run_b200(args):
                          "amax_kernel": {"achieved": achieved_amax, "frac": achieved_amax / peak
                                          if achieved_amax else None, "ms_per_launch": amax_ms}},
             "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": 2 * args.steps,
+            "formats": formats,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_formats(dev, peak):
+    """Achieved algorithmic GB/s of the other formats' kernels (BASELINE configs 1, 2, 4 and the
+    histogram pass of config 5), each over inputs larger than L2 (several distinct tensors used
+    in turn), timed with CUDA events after 3 warm-up passes."""
+    import torch
+
+    from b200q import ops
+
+    def timed(fn, n_bytes, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        gbs = n_bytes / (ms * 1e-3) / 1e9
+        return {"gbps": gbs, "frac_of_measured_peak": gbs / peak, "ms": ms, "algorithmic_bytes": n_bytes}
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(0)
+    # config 1: INT8 per-row (axis 0, narrow) fake quant of fp32 [4096,4096] fused with the row amax
+    w32 = [torch.randn(4096, 4096, generator=g, device=dev) * 0.02 for _ in range(8)]
+    out["int8_per_row_fused_amax_fp32_4096x4096"] = timed(
+        lambda: [ops.fake_int_rows_dynamic(w, 8, False, True) for w in w32], 8 * 4096 * 4096 * 8)
+    del w32
+    # config 2: FP8 per-tensor, 16 batches of bf16 [8192,4096] with outlier channels
+    idx = torch.randperm(4096, generator=torch.Generator().manual_seed(7))[:4].to(dev)
+    xs = []
+    for b in range(16):
+        x = torch.randn(8192, 4096, generator=torch.Generator(device=dev).manual_seed(1000 + b), device=dev)
+        x[:, idx] *= 50
+        xs.append(x.bfloat16())
+    amax = torch.zeros((), device=dev)
+    n = 16 * 8192 * 4096
+    out["fp8_max_calibration_bf16_16x8192x4096"] = timed(lambda: [ops.amax_tensor(x, out=amax) for x in xs], n * 2)
+    out["fp8_per_tensor_fake_quant_bf16_16x8192x4096"] = timed(lambda: [ops.fake_e4m3(x, amax) for x in xs], n * 4)
+    out["nvfp4_fake_quant_bf16_16x8192x4096"] = timed(lambda: [ops.nvfp4_fake(x, amax) for x in xs], n * 4)
+    # histogram pass of config 5 (2048 bins) on the same activations
+    counts = torch.zeros(2048, dtype=torch.int64, device=dev)
+    rmax = float(amax)
+    out["histogram_2048_bins_bf16_16x8192x4096"] = timed(lambda: [ops.hist_collect(x, counts, 2048, rmax) for x in xs], n * 2)
+    del xs
+    # config 4: INT4 block-128 amax + pack, and the per-alpha weight-side kernel of awq_lite
+    ws = [(torch.randn(14336, 4096, generator=g, device=dev) * 0.02).bfloat16() for _ in range(3)]
+    s = torch.exp(torch.randn(4096, generator=g, device=dev)).bfloat16()
+    n = 3 * 14336 * 4096
+    out["int4_block128_quantize_pack_bf16_14336x4096"] = timed(
+        lambda: [ops.int4_quantize(w.reshape(-1), 128) for w in ws], int(n * (2 + 0.5 + 2 / 128)))
+    out["awq_scale_fake_int4_bf16_14336x4096"] = timed(
+        lambda: [ops.awq_scale_fake_int(w, s, 128, 4, False, False) for w in ws], n * 4)
+    return out
 
 
 def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
@@ -356,6 +420,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-formats", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -3,5 +3,6 @@
 from .calibrator import _Calibrator
 from .histogram import HistogramCalibrator, calibrate_weights
 from .max import MaxCalibrator
+from .mse import MseCalibrator
 
-__all__ = ["_Calibrator", "MaxCalibrator", "HistogramCalibrator", "calibrate_weights"]
+__all__ = ["_Calibrator", "MaxCalibrator", "MseCalibrator", "HistogramCalibrator", "calibrate_weights"]

@@ -17,9 +17,10 @@ from torch import nn
 
 from . import dist as qdist
 from . import ops
+from .calib import MseCalibrator
 from .nn import QuantModule, SequentialQuantizer, TensorQuantizer, is_quantized_linear
 
-__all__ = ["max_calibrate", "awq_lite", "awq", "enable_stats_collection", "finish_stats_collection",
+__all__ = ["max_calibrate", "mse_calibrate", "awq_lite", "awq", "enable_stats_collection", "finish_stats_collection",
            "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]
 
 
@@ -39,7 +40,10 @@ def finish_stats_collection(model: nn.Module, method: str | None = None):
             continue
         cal = getattr(m, "_calibrator", None)
         if cal and not m._dynamic:
-            if method in {"mse", "entropy"}:
+            if isinstance(cal, MseCalibrator):
+                if cal.compute_amax() is not None:
+                    m.load_calib_amax()
+            elif method in {"mse", "entropy"}:
                 if cal.compute_amax(method) is not None:
                     m.load_calib_amax(method)
             elif cal.compute_amax() is not None:
@@ -72,6 +76,42 @@ def max_calibrate(model: nn.Module, forward_loop=None, distributed_sync=True):
     finish_stats_collection(model)
     if distributed_sync and dist.is_available() and dist.is_initialized():
         qdist.sync_amax(model)
+
+
+@torch.no_grad()
+def mse_calibrate(model: nn.Module, forward_loop=None, distributed_sync=True, num_steps: int = 10,
+                  start_multiplier: float = 0.25, stop_multiplier: float = 4.0):
+    """Max calibration first, then per quantiser an amax search over
+    ``amax * linspace(start, stop, num_steps)`` minimising the fake-quantisation error
+    (reference model_calib.py:188-269)."""
+    max_calibrate(model, forward_loop, distributed_sync)
+    for name, m in model.named_modules():
+        if not isinstance(m, TensorQuantizer) or m._disabled:
+            continue
+        if m.is_static_block_quant:
+            raise ValueError("MSE calibration does not support static block quantization. "
+                             f"Found static block quantization at {name}.")
+        if m._calibrator is not None and not m._dynamic and hasattr(m, "_amax"):
+            def quant_func(x, amax, q=m):
+                saved = q._amax
+                if_quant, if_calib, fake = q._if_quant, q._if_calib, q._fake_quant
+                q._amax = amax
+                q._if_quant, q._if_calib, q._fake_quant = True, False, True
+                try:
+                    return q(x)
+                finally:
+                    q._amax = saved
+                    q._if_quant, q._if_calib, q._fake_quant = if_quant, if_calib, fake
+
+            m._calibrator = MseCalibrator(amax=m._amax.clone().detach(), axis=m._calibrator._axis,
+                                          num_steps=num_steps, start_multiplier=start_multiplier,
+                                          stop_multiplier=stop_multiplier, quant_func=quant_func)
+    enable_stats_collection(model)
+    if forward_loop is None:
+        weight_only_quantize(model)
+    else:
+        forward_loop(model)
+    finish_stats_collection(model, method="mse")
 
 
 # --------------------------------------------------------------------------------- AWQ lite ----

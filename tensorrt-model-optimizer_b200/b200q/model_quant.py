@@ -8,14 +8,14 @@ import torch
 from torch import nn
 
 from .conversion import convert_to_quantized_model, set_quantizer_attribute
-from .model_calib import awq, max_calibrate
+from .model_calib import awq, max_calibrate, mse_calibrate
 from .nn import QuantLinear, RealQuantLinear, SequentialQuantizer, TensorQuantizer
 from .qtensor import pack_real_quantize_weight
 
 __all__ = ["quantize", "calibrate", "compress", "disable_quantizer", "enable_quantizer",
            "print_quant_summary", "fold_weight", "modelopt_state"]
 
-_ALGORITHMS = {"max": max_calibrate, "awq_lite": awq}
+_ALGORITHMS = {"max": max_calibrate, "mse": mse_calibrate, "awq_lite": awq}
 
 
 def calibrate(model: nn.Module, algorithm="max", forward_loop=None) -> nn.Module:

@@ -115,6 +115,15 @@ def golden_flows(mtq, out):
                 cases[f"nvfp4_{name}_scale"] = bits(lin.weight_quantizer._scale)
                 cases[f"nvfp4_{name}_double_scale"] = bits(lin.weight_quantizer._double_scale.reshape(1))
             cases["nvfp4_state_keys"] = np.array(sorted(model.state_dict().keys()))
+    for tag, cfg in (("int8", mtq.INT8_DEFAULT_CFG), ("fp8", mtq.FP8_DEFAULT_CFG)):
+        model = copy.deepcopy(base)
+        c = copy.deepcopy(cfg)
+        c["algorithm"] = "mse"
+        mtq.quantize(model, c, loop)
+        for name in ("up_proj", "down_proj"):
+            lin = getattr(model, name)
+            cases[f"{tag}_mse_{name}_in_amax"] = bits(lin.input_quantizer._amax.float().reshape(-1))
+            cases[f"{tag}_mse_{name}_w_amax"] = bits(lin.weight_quantizer._amax.float().reshape(-1))
     np.savez_compressed(out / "flows.npz", **cases)
 
 
