@@ -34,7 +34,11 @@ class MseCalibrator(_Calibrator):
                                      device=x.device)
         red = convert_quantization_axis_to_reduce_axis(x, self._axis)
         for step, m in enumerate(multipliers):
-            cand = self._initial_amax * m
+            # candidate = initial * multiplier with the rounding the reference gets on CPU: the
+            # product is formed in fp32 and rounded to the amax dtype (a 0-dim amax promotes to fp32).
+            # (On CUDA torch would first round the 0-dim multiplier to the amax dtype.)
+            a = self._initial_amax
+            cand = a.float() * m if a.dim() == 0 else (a.float() * m).to(a.dtype)
             xq = self._quant_func(x, cand)
             err = self._error_func(x, xq) if self._error_func is not None else F.mse_loss(x, xq, reduction="none")
             loss = err.sum() if red is None else err.sum(dim=red)

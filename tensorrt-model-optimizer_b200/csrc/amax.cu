@@ -176,7 +176,7 @@ amax_blocks_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, float* _
     }
     uint32_t bits = E::acc_to_f32bits(acc);
     for (int o = lanes >> 1; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
-    if (t < total && (t % lanes) == 0) out[t / lanes] = __uint_as_float(bits);
+    if (t < total && (t & (lanes - 1)) == 0) out[t >> (__ffs(lanes) - 1)] = __uint_as_float(bits);
   }
 }
 

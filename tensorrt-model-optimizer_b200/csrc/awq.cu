@@ -15,42 +15,44 @@ template <typename T> __device__ __forceinline__ float round_t(float v) {
 template <typename T, int PPL>
 __global__ void __launch_bounds__(256)
 awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restrict__ y,
-                    int64_t nblocks, int lanes, int packs_per_row, IntQ q) {
+                    int64_t nblocks, int lanes, FastDiv blocks_per_row, IntQ q) {
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t total = nblocks * lanes;
+  const int lane_shift = __ffs(lanes) - 1;
   const uint4* wv = reinterpret_cast<const uint4*>(w);
   const uint4* sv = reinterpret_cast<const uint4*>(s);
   uint4* yv = reinterpret_cast<uint4*>(y);
   for (int64_t t = gthread; t < ((total + 31) / 32) * 32; t += nthreads) {
     const bool valid = t < total;
+    // column of this lane's first pack: (block index within its row) * packs per block + lane offset
+    uint32_t rowq, colblk;
+    blocks_per_row.divmod(static_cast<uint32_t>(valid ? (t >> lane_shift) : 0), rowq, colblk);   // nblocks < 2^31
+    const uint32_t spack = (colblk * lanes + static_cast<uint32_t>(t & (lanes - 1))) * PPL;
     float v[PPL][P];
     uint32_t bits = 0;
 #pragma unroll
     for (int p = 0; p < PPL; ++p) {
-      const int64_t pk = t * PPL + p;
-      uint4 a = valid ? ld_stream(wv + pk) : make_uint4(0, 0, 0, 0);
-      uint4 b = valid ? __ldg(sv + (pk % packs_per_row)) : make_uint4(0, 0, 0, 0);
+      uint4 a = valid ? ld_stream(wv + t * PPL + p) : make_uint4(0, 0, 0, 0);
+      uint4 b = valid ? __ldg(sv + spack + p) : make_uint4(0, 0, 0, 0);
       float fa[P], fb[P];
       E::unpack(a, fa);
       E::unpack(b, fb);
 #pragma unroll
       for (int k = 0; k < P; ++k) {
         v[p][k] = round_t<T>(fa[k] * fb[k]);
-        bits = max(bits, __float_as_uint(fabsf(v[p][k])));
+        bits = max(bits, __float_as_uint(v[p][k]) & 0x7fffffffu);
       }
     }
     for (int o = lanes >> 1; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
-    const float amax = __uint_as_float(bits);
-    const bool live = !(amax < 5.9604644775390625e-8f);
-    const float scale = __fdiv_rn(q.bound, amax);
+    const IntScale sc = make_int_scale(q, __uint_as_float(bits));
     if (valid) {
 #pragma unroll
       for (int p = 0; p < PPL; ++p) {
 #pragma unroll
-        for (int k = 0; k < P; ++k) v[p][k] = intq_apply(v[p][k], scale, live, q);
+        for (int k = 0; k < P; ++k) v[p][k] = intq_apply(v[p][k], sc, q);
         st_stream(yv + t * PPL + p, E::pack(v[p]));
       }
     }
@@ -114,13 +116,14 @@ extern "C" int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, i
     const int ppl = packs >= 2 ? 2 : 1;
     const int lanes = packs / ppl;
     const int64_t nblocks = rows * (cols / block);
+    if (nblocks > kFastDivLimit) return B200Q_ERR_UNSUPPORTED;
+    const FastDiv bpr(static_cast<uint32_t>(cols / block));
     int grid = grid_for(nblocks * lanes, 256, 8);
     const T* wp = static_cast<const T*>(w);
     const T* sp = static_cast<const T*>(s);
     T* yp = static_cast<T*>(y);
-    const int ppr = static_cast<int>(cols / P);
-    if (ppl == 2) awq_scale_fq_kernel<T, 2><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, ppr, q);
-    else awq_scale_fq_kernel<T, 1><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, ppr, q);
+    if (ppl == 2) awq_scale_fq_kernel<T, 2><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
+    else awq_scale_fq_kernel<T, 1><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
     return launch_status();
   });
 }

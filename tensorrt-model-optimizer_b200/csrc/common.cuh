@@ -173,4 +173,28 @@ inline int grid_for(int64_t work_items, int per_cta, int ctas_per_sm) {
   return static_cast<int>(need < cap ? need : cap);
 }
 
+// Division of a 31-bit index by a launch-invariant divisor as multiply-high + shift (the divisor's
+// magic number is computed once on the host): 2 integer instructions instead of the ~50 of a
+// 64-bit division in the index arithmetic of every 16-byte pack.
+struct FastDiv {
+  uint32_t d, mul, shr;
+  FastDiv() : d(1), mul(0), shr(0) {}
+  explicit FastDiv(uint32_t divisor) : d(divisor), mul(0), shr(0) {
+    if (d > 1) {
+      uint32_t lg = 0;
+      while ((1ull << lg) < d) ++lg;                      // ceil(log2 d)
+      const uint32_t p = 31 + lg;
+      mul = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+      shr = p - 32;
+    }
+  }
+  // n < 2^31
+  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : __umulhi(n, mul) >> shr; }
+  __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
+    q = div(n);
+    r = n - q * d;
+  }
+};
+constexpr int64_t kFastDivLimit = (1ll << 31) - 1;
+
 }  // namespace b200q

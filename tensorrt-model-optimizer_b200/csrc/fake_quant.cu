@@ -15,14 +15,10 @@ constexpr int kEwUnroll = 4;
 // A functor is built once per thread from the per-tensor amax, or once per pack from the channel amax.
 struct IntFq {
   IntQ q;
-  float scale;
-  bool live;
+  IntScale s;
   __device__ __forceinline__ IntFq() {}
-  __device__ __forceinline__ IntFq(const IntQ& q_, float amax) : q(q_) {
-    live = !(amax < 5.9604644775390625e-8f);  // 2^-24
-    scale = __fdiv_rn(q.bound, amax);
-  }
-  __device__ __forceinline__ float operator()(float x) const { return intq_apply(x, scale, live, q); }
+  __device__ __forceinline__ IntFq(const IntQ& q_, float amax) : q(q_), s(make_int_scale(q_, amax)) {}
+  __device__ __forceinline__ float operator()(float x) const { return intq_apply(x, s, q); }
   template <int N> __device__ __forceinline__ void apply(float* f) const {
 #pragma unroll
     for (int i = 0; i < N; ++i) f[i] = (*this)(f[i]);
@@ -118,8 +114,8 @@ e4m3_cast_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n) {
 // ---- amax per channel, inner a multiple of the pack: a pack lies inside one channel ------------
 template <typename T, typename F>
 __global__ void __launch_bounds__(kEwThreads)
-fq_axis_inner_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t npack, int64_t axis,
-                     int64_t inner_packs, const float* __restrict__ amax, IntQ q) {
+fq_axis_inner_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t npack, FastDiv axis,
+                     FastDiv inner_packs, const float* __restrict__ amax, IntQ q) {
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -134,7 +130,9 @@ fq_axis_inner_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t npack, 
       const int64_t j = i + u * stride;
       if (j < npack) {
         v[u] = ld_stream(xv + j);
-        am[u] = __ldg(amax + (j / inner_packs) % axis);
+        uint32_t row = inner_packs.div(static_cast<uint32_t>(j)), oq, ch;   // npack < 2^31 here
+        axis.divmod(row, oq, ch);
+        am[u] = __ldg(amax + ch);
       }
     }
 #pragma unroll
@@ -305,10 +303,11 @@ static int launch_fq_axis(const void* x, void* y, int64_t outer, int64_t axis, i
     const T* xp = static_cast<const T*>(x);
     T* yp = static_cast<T*>(y);
     const int64_t n = outer * axis * inner;
-    if (inner % P == 0) {
+    if (inner % P == 0 && n / P <= kFastDivLimit) {
       const int64_t npack = n / P;
       int grid = grid_for(npack, kEwThreads * kEwUnroll, 8);
-      fq_axis_inner_kernel<T, F><<<grid, kEwThreads, 0, s>>>(xp, yp, npack, axis, inner / P, amax, q);
+      fq_axis_inner_kernel<T, F><<<grid, kEwThreads, 0, s>>>(
+          xp, yp, npack, FastDiv(static_cast<uint32_t>(axis)), FastDiv(static_cast<uint32_t>(inner / P)), amax, q);
     } else if (inner == 1 && axis % P == 0) {
       const int64_t cpacks = axis / P;
       const int bx = static_cast<int>((cpacks + kEwThreads - 1) / kEwThreads);

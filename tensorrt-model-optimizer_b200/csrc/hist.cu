@@ -23,11 +23,16 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
   __syncthreads();
   uint32_t* mine = sh + (threadIdx.x & (replicas - 1)) * smem_bins;
   const float fbins = static_cast<float>(nbins);
+  // bin = int(RN(|x| * nbins / range_max)): the quotient through one reciprocal per thread; tiny
+  // quotients may lose bits there but stay below 1 (bin 0)
+  const bool fast = div_safe(range_max);
+  const float rcp_range = __frcp_rn(range_max);
 
   auto bin_one = [&](float v) {
     const float a = fabsf(v);
     if (!(a <= range_max)) return;  // out of range or NaN: not counted
-    int b = static_cast<int>(__fdiv_rn(a * fbins, range_max));
+    const float num = a * fbins;
+    int b = static_cast<int>(fast ? div_rn_rcp(num, range_max, rcp_range) : __fdiv_rn(num, range_max));
     if (b >= nbins) b = nbins - 1;
     if (b < smem_bins) atomicAdd(mine + b, 1u);
     else atomicAdd(counts + b, 1ull);

@@ -56,6 +56,7 @@ int4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes,
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t total = nblocks * lanes;
+  const int lane_shift = __ffs(lanes) - 1;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   for (int64_t t = gthread; t < ((total + 31) / 32) * 32; t += nthreads) {
     const bool valid = t < total;
@@ -64,7 +65,7 @@ int4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes,
 #pragma unroll
     for (int p = 0; p < PPL; ++p) v[p] = valid ? ld_stream(xv + t * PPL + p) : make_uint4(0, 0, 0, 0);
     float scale;
-    const int64_t b = t / lanes;
+    const int64_t b = t >> lane_shift;   // lanes is a power of two
     if (scales_in) {
       scale = valid ? E::to_float(scales_in[b]) : 0.f;
     } else {
@@ -75,7 +76,7 @@ int4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes,
       scale = int4_scale_from_amax<T>(__uint_as_float(bits));
     }
     if (valid) {
-      if (scales_out && (t % lanes) == 0) scales_out[b] = E::from_float(scale);
+      if (scales_out && (t & (lanes - 1)) == 0) scales_out[b] = E::from_float(scale);
 #pragma unroll
       for (int p = 0; p < PPL; ++p)
         store_codes<T>(packed + (t * PPL + p) * (P / 2), int4_pack<T>(v[p], scale));

@@ -72,6 +72,30 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t code) {
   return (code & 8u) ? -v : v;
 }
 
+// ---- correctly rounded division through a reciprocal ---------------------------------------------
+// RN(a/d) given y = RN(1/d).  The first product is within 1.5 ulp of the quotient; one residual
+// correction makes it faithful and, by Markstein's theorem (y correctly rounded, quotient
+// faithful, residual exact in an FMA), the second correction rounds to RN(a/d).  Callers guarantee
+// that d and a/d are in the normal range and nothing overflows (see div_safe).  A zero numerator
+// of either sign comes out as +0 ((+0) + (-0) = +0 in the corrections).
+__device__ __forceinline__ float div_rn_rcp(float a, float d, float y) {
+  float q = a * y;
+  float e = fmaf(-q, d, a);
+  q = fmaf(e, y, q);
+  e = fmaf(-q, d, a);
+  return fmaf(e, y, q);
+}
+// the same for two lanes with packed fp32x2 instructions; nd = -d
+__device__ __forceinline__ float2 div2_rn_rcp(float2 a, float2 nd, float2 y) {
+  float2 q = __fmul2_rn(a, y);
+  float2 e = __ffma2_rn(q, nd, a);
+  q = __ffma2_rn(e, y, q);
+  e = __ffma2_rn(q, nd, a);
+  return __ffma2_rn(e, y, q);
+}
+// divisor (or numerator bound) inside [2^-40, 2^40]: with both there, quotients stay normal
+__device__ __forceinline__ bool div_safe(float v) { return v >= 9.094947017729282e-13f && v <= 1099511627776.f; }
+
 // ---- integer fake quant ------------------------------------------------------------------------
 struct IntQ {
   float bound, lo;
@@ -88,6 +112,29 @@ __device__ __forceinline__ float intq_apply(float x, float scale, bool live, con
   r = r > q.bound ? q.bound : r;
   r = r < q.lo ? q.lo : r;
   return live ? __fdiv_rn(r, scale) : 0.f;
+}
+
+// The same with the division by `scale` done through its reciprocal once per amax.
+struct IntScale {
+  float scale, y;
+  bool live, fast;
+};
+__device__ __forceinline__ IntScale make_int_scale(const IntQ& q, float amax) {
+  IntScale s;
+  s.live = !(amax < 5.9604644775390625e-8f);  // 2^-24
+  s.scale = __fdiv_rn(q.bound, amax);
+  s.fast = div_safe(s.scale);
+  s.y = __frcp_rn(s.scale);
+  return s;
+}
+__device__ __forceinline__ float intq_apply(float x, const IntScale& s, const IntQ& q) {
+  float r = rintf(x * s.scale);
+  r = r > q.bound ? q.bound : r;
+  r = r < q.lo ? q.lo : r;
+  // |r| is 0 or an integer in [1, 2^24]: the quotient is normal whenever scale is div_safe
+  float o = s.fast ? div_rn_rcp(r, s.scale, s.y) : __fdiv_rn(r, s.scale);
+  o = (r == 0.f) ? r : o;  // a zero quotient keeps the sign of the rounded value
+  return s.live ? o : 0.f;
 }
 
 }  // namespace b200q

@@ -212,13 +212,22 @@ __device__ __forceinline__ uint2 nvfp4_encode16(const float* f, float d, float b
   return make_uint2(w[0], w[1]);
 }
 
-// 8 bytes of codes -> 16 values times d, with +0 for the negative-zero code as the table has
+// 8 bytes of codes -> 16 values times d.  The hardware conversion gives -0 for the negative-zero
+// code; the fused multiply-add with +0 turns the product into +0 as the reference's table has it.
 __device__ __forceinline__ void nvfp4_decode16(uint2 codes, float d, float* f) {
   const uint32_t w[2] = {codes.x, codes.y};
+  const float2 dd = make_float2(d, d), zz = make_float2(0.f, 0.f);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t c = (w[i >> 3] >> (4 * (i & 7))) & 0xfu;
-    f[i] = e2m1_to_f32(c) * d + 0.f;
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(
+          static_cast<__nv_fp4x2_storage_t>((w[h] >> (8 * j)) & 0xffu), __NV_E2M1);
+      const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      const float2 r = __ffma2_rn(v, dd, zz);
+      f[8 * h + 2 * j] = r.x;
+      f[8 * h + 2 * j + 1] = r.y;
+    }
   }
 }
 

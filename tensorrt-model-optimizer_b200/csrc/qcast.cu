@@ -26,7 +26,7 @@ struct ToInt8 {
 template <typename T, typename C>
 __global__ void __launch_bounds__(256)
 qcast_inner_kernel(const T* __restrict__ x, const T* __restrict__ scales, uint8_t* __restrict__ q,
-                   int64_t npack, int64_t axis, int64_t inner_packs) {
+                   int64_t npack, FastDiv axis, FastDiv inner_packs) {
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -35,8 +35,11 @@ qcast_inner_kernel(const T* __restrict__ x, const T* __restrict__ scales, uint8_
     const int64_t j1 = i + stride;
     const uint4 v0 = ld_stream(xv + i);
     const uint4 v1 = j1 < npack ? ld_stream(xv + j1) : v0;
-    const float s0 = E::to_float(scales[(i / inner_packs) % axis]);
-    const float s1 = j1 < npack ? E::to_float(scales[(j1 / inner_packs) % axis]) : s0;
+    uint32_t oq, c0, c1;
+    axis.divmod(inner_packs.div(static_cast<uint32_t>(i)), oq, c0);        // npack < 2^31 here
+    axis.divmod(inner_packs.div(static_cast<uint32_t>(j1 < npack ? j1 : i)), oq, c1);
+    const float s0 = E::to_float(scales[c0]);
+    const float s1 = E::to_float(scales[c1]);
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const int64_t j = u ? j1 : i;
@@ -78,10 +81,11 @@ static int launch_qcast(const void* x, const void* scales, uint8_t* q, int64_t o
     // a single scale can be treated as one channel spanning the whole tensor
     int64_t ax = axis, in = inner;
     if (axis == 1) { in = outer * inner; }
-    if (in % P == 0 && (reinterpret_cast<uintptr_t>(q) & 7u) == 0) {
+    if (in % P == 0 && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && n / P <= kFastDivLimit) {
       const int64_t npack = n / P;
       int grid = grid_for(npack, 512, 8);
-      qcast_inner_kernel<T, C><<<grid, 256, 0, s>>>(xp, sp, q, npack, ax, in / P);
+      qcast_inner_kernel<T, C><<<grid, 256, 0, s>>>(xp, sp, q, npack, FastDiv(static_cast<uint32_t>(ax)),
+                                                    FastDiv(static_cast<uint32_t>(in / P)));
     } else {
       int grid = grid_for(n, 256, 8);
       qcast_generic_kernel<T, C><<<grid, 256, 0, s>>>(xp, sp, q, n, ax, in);
