@@ -40,7 +40,7 @@ BYTES_QUANT = 2.0 + 0.5 + 1.0 / 16
 BYTES_TOTAL = BYTES_AMAX + BYTES_QUANT
 # DRAM bytes per element of the quantise kernel from the committed ncu capture
 # (profiles/nvfp4_group_quantize_*.md), or None before one exists
-NCU_QUANT_TRAFFIC_PER_ELEM = None
+NCU_QUANT_TRAFFIC_PER_ELEM = 2.478
 
 
 def peaks():
