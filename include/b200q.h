@@ -230,6 +230,16 @@ int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, int64_t rows
 int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double* sum_io,
                       void* stream);
 
+/* One candidate of the awq_lite search, evaluation side, on the tensor cores (tcgen05, TMEM):
+ *   *sum_io += sum_{m,n} float(bf16(bf16(sum_k a[m,k]*b[n,k]) - ref[m,n]))^2
+ * a [m,k], b [n,k], ref [m,n] bf16 row-major; m, n multiples of 128, k a multiple of 64 (other
+ * shapes return B200Q_ERR_UNSUPPORTED).  The product is never written unless c_out (fp32 [m,n],
+ * may be NULL) is given.  *status_io (device word, caller zeroes it) receives error bits if a
+ * bounded wait inside the kernel ran out.  Replaces F.linear + update_loss of the search loop
+ * (modelopt/torch/quantization/model_calib.py:623-627,671-685). */
+int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
+                         int64_t k, double* sum_io, float* c_out, uint32_t* status_io, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

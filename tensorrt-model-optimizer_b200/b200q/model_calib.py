@@ -174,6 +174,10 @@ def apply_pre_quant_scale_and_smooth(linear, pre_quant_scale):
         linear.input_quantizer.amax = (a * pqs.to(dev)).amax().to(dt)
 
 
+# evaluate awq_lite candidates with the fused tcgen05 GEMM + loss kernel where its shape rules allow
+USE_TENSOR_CORE_EVAL = True
+
+
 class _AWQLiteState:
     def __init__(self, module, name, alpha_step):
         self.name = name
@@ -189,6 +193,9 @@ class _AWQLiteState:
         self.best_alpha = None
         self.is_input_quantized = module.input_quantizer.is_enabled
         self.is_enabled = True
+        # error bits of the evaluation kernel's bounded waits (checked once, after the search)
+        self.gemm_status = (torch.zeros((), dtype=torch.int32, device=module.weight.device)
+                            if module.weight.is_cuda else None)
 
 
 def _evaluate_alpha(module, st, x2d, out_actual, alpha):
@@ -210,6 +217,13 @@ def _evaluate_alpha(module, st, x2d, out_actual, alpha):
     xin = x2d * x_s
     if module.input_quantizer.is_enabled:
         xin = module.input_quantizer(xin)
+    x2 = xin.reshape(-1, xin.shape[-1])
+    ref2 = out_actual.reshape(-1, out_actual.shape[-1])
+    if USE_TENSOR_CORE_EVAL and module.bias is None and ops.awq_gemm_supported(x2, wfq):
+        # GEMM and squared-error reduction in one tcgen05 kernel: the product never reaches memory
+        acc = torch.zeros((), dtype=torch.float64, device=x2.device)
+        ops.awq_gemm_sqerr(x2, wfq, ref2, acc, st.gemm_status)
+        return (acc / ref2.numel()).to(torch.float32)
     out = F.linear(xin, wfq, module.bias)
     return ops.mse_loss(out, out_actual)
 
@@ -295,6 +309,8 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
         elif st.num_search_steps == 0:
             st.is_enabled = False
             warnings.warn(f"awq_lite: the second forward_loop(model) did not reach {name}.")
+        if st.gemm_status is not None and int(st.gemm_status) != 0:
+            raise RuntimeError(f"awq_lite: the evaluation kernel timed out in {name} (status {int(st.gemm_status)})")
         if st.is_enabled:
             st.loss = {k: float(v) for k, v in st.loss.items()}
             st.best_alpha = min(st.loss, key=st.loss.get)

@@ -386,3 +386,24 @@ def mse_loss(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     with torch.cuda.device(a.device):
         call("b200q_sq_diff_sum", a.data_ptr(), b.data_ptr(), a.numel(), dtype_code(a), acc.data_ptr(), _stream(a))
     return (acc / a.numel()).to(torch.float32)
+
+
+def awq_gemm_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Shapes / dtype the tensor-core evaluation kernel covers."""
+    return (a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+            and a.shape[0] % 128 == 0 and b.shape[0] % 128 == 0 and a.shape[1] % 64 == 0
+            and a.shape[1] == b.shape[1])
+
+
+def awq_gemm_sqerr(a: torch.Tensor, b: torch.Tensor, ref: torch.Tensor, acc: torch.Tensor,
+                   status: torch.Tensor, c_out: torch.Tensor | None = None):
+    """acc (float64, 1 element) += sum of squared bf16 differences between bf16(a @ b.T) and ref.
+    ``status`` is an int32 device word that collects error bits of the kernel's bounded waits."""
+    a, b, ref = _prep(a), _prep(b), _prep(ref)
+    m, k = a.shape
+    n = b.shape[0]
+    assert ref.shape == (m, n) and ref.dtype == torch.bfloat16 and acc.dtype == torch.float64
+    with torch.cuda.device(a.device):
+        call("b200q_awq_gemm_sqerr", a.data_ptr(), b.data_ptr(), ref.data_ptr(), m, n, k, acc.data_ptr(),
+             c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(a))
+    return acc

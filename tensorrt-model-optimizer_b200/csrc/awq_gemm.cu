@@ -1,0 +1,276 @@
+// awq_lite evaluation GEMM on the 5th-generation tensor cores, fused with the loss:
+//
+//     loss_sum += sum_{m,n} float( bf16( bf16(sum_k A[m,k] * B[n,k]) - R[m,n] ) )^2
+//
+// A = scaled activations [M, K], B = fake-quantised scaled weights [N, K], R = the unquantised
+// layer output [M, N], all bf16 with K (resp. N for R) contiguous.  The product never goes to
+// memory: accumulators live in tensor memory and the epilogue reduces the squared error.
+//
+// One CTA computes one 128 x 128 output tile.  Warp 0 streams 128 x 64 operand tiles into a
+// 4-stage shared-memory ring with TMA (128-byte swizzle), one thread of warp 1 issues
+// tcgen05.mma (UMMA 128x128x16, bf16 -> fp32 in TMEM) and frees ring slots with tcgen05.commit,
+// warps 2-5 read the accumulator with tcgen05.ld and do the epilogue.
+//
+// Every mbarrier wait is bounded: when a wait runs out, an error bit is set in the caller's status
+// word, the CTA stops waiting anywhere else, lets its outstanding work drain, frees its TMEM and
+// returns.
+#include <cuda.h>
+
+#include "numerics.cuh"
+
+namespace b200q {
+
+constexpr int kGM = 128, kGN = 128, kGK = 64;        // CTA tile; kGK bf16 = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr uint32_t kTileBytesA = kGM * kGK * 2, kTileBytesB = kGN * kGK * 2;
+constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
+constexpr uint32_t kTmemCols = 128;                   // fp32 accumulator columns (= kGN)
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+enum : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4 };
+
+struct GemmSmem {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t accum;
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and records `code`) when the limit is hit or the CTA has given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, GemmSmem* sm, uint32_t* status,
+                                          uint32_t code) {
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if (*reinterpret_cast<volatile uint32_t*>(&sm->abort)) return false;
+    if (it > 128) __nanosleep(64);
+  }
+  *reinterpret_cast<volatile uint32_t*>(&sm->abort) = 1;
+  atomicOr(status, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// shared-memory matrix descriptor: K-major operand tile, 128-byte swizzle, rows 128 B apart,
+// 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);         // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                          // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                  // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                          // descriptor version
+  d |= static_cast<uint64_t>(2) << 61;                          // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kGN >> 3) << 17) | ((kGM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __nv_bfloat16* __restrict__ ref, int64_t N, int num_k_blocks,
+                      double* __restrict__ sum_io, float* __restrict__ c_out, uint32_t* __restrict__ status) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // operand ring first (1024-byte aligned for the swizzle), control block after it
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmSmem* sm = reinterpret_cast<GemmSmem*>(ring + kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kGM, n0 = blockIdx.x * kGN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    mbar_init(&sm->accum, 1);
+    sm->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sm->tmem_base);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_k_blocks; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t ph = (kb / kStages) & 1;
+        if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, status, kErrProducerWait)) break;
+        uint8_t* a = ring + s * kStageBytes;
+        mbar_expect_tx(&sm->full[s], kStageBytes);
+        tma_load_2d(a, &map_a, &sm->full[s], kb * kGK, m0);
+        tma_load_2d(a + kTileBytesA, &map_b, &sm->full[s], kb * kGK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < num_k_blocks && ok; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t ph = (kb / kStages) & 1;
+        ok = mbar_wait(&sm->full[s], ph, sm, status, kErrMmaWait);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(ring + s * kStageBytes);
+        const uint64_t da = umma_desc(a), db = umma_desc(a + kTileBytesA);
+#pragma unroll
+        for (int k = 0; k < kGK / kUmmaK; ++k) {
+          // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+          umma_bf16(tmem, da + 2 * k, db + 2 * k, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&sm->empty[s]);   // the slot is free once these MMAs have read it
+      }
+      umma_commit(&sm->accum);        // fires when every MMA issued above has completed
+    }
+  } else {
+    // epilogue warps 2..5: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read
+    const int quarter = warp & 3;
+    const bool ok = mbar_wait(&sm->accum, 0, sm, status, kErrEpilogueWait);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float sq = 0.f;
+    if (ok) {
+      const int64_t row = m0 + quarter * 32 + lane;
+      const __nv_bfloat16* rrow = ref + row * N + n0;
+#pragma unroll 1
+      for (int c = 0; c < kGN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, acc);
+        const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 r4 = __ldg(rp + v);
+          float rf[8];
+          Elem<__nv_bfloat16>::unpack(r4, rf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float a = __uint_as_float(acc[8 * v + j]);
+            const float o = __bfloat162float(__float2bfloat16_rn(a));
+            const float d = __bfloat162float(__float2bfloat16_rn(o - rf[j]));
+            sq = fmaf(d, d, sq);
+          }
+        }
+        if (c_out) {
+          float* cp = c_out + row * N + n0 + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cp[j] = __uint_as_float(acc[j]);
+        }
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if (lane == 0 && ok) atomicAdd(sum_io, static_cast<double>(sq));
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, k] with k contiguous; boxes of kGK x box_rows, 128-byte swizzle
+static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kGK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
+                                    int64_t k, double* sum_io, float* c_out, uint32_t* status_io,
+                                    void* stream) {
+  B200Q_REQUIRE_PTR(a); B200Q_REQUIRE_PTR(b); B200Q_REQUIRE_PTR(ref); B200Q_REQUIRE_PTR(sum_io);
+  B200Q_REQUIRE_PTR(status_io);
+  B200Q_REQUIRE_ALIGNED(a); B200Q_REQUIRE_ALIGNED(b); B200Q_REQUIRE_ALIGNED(ref);
+  if (m <= 0 || n <= 0 || k <= 0) return B200Q_ERR_SHAPE;
+  if (m % kGM || n % kGN || k % kGK || m / kGM > 65535) return B200Q_ERR_UNSUPPORTED;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, kGN)) return B200Q_ERR_CUDA;
+  const size_t smem = kStages * kStageBytes + sizeof(GemmSmem) + 1024;
+  if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return B200Q_ERR_CUDA;
+  dim3 grid(static_cast<unsigned>(n / kGN), static_cast<unsigned>(m / kGM));
+  awq_gemm_sqerr_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
+      status_io);
+  return launch_status();
+}
