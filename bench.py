@@ -370,6 +370,32 @@ def run_formats(dev, peak):
         lambda: [ops.int4_quantize(w.reshape(-1), 128) for w in ws], int(n * (2 + 0.5 + 2 / 128)))
     out["awq_scale_fake_int4_bf16_14336x4096"] = timed(
         lambda: [ops.awq_scale_fake_int(w, s, 128, 4, False, False) for w in ws], n * 4)
+    # config 4: the awq_lite search of one layer (up_proj shape): 21 candidates, each = fused
+    # scale + INT4 block fake quant of W, then the tcgen05 GEMM with the squared-error epilogue
+    x = (torch.randn(512, 4096, generator=g, device=dev) * torch.exp(torch.randn(4096, generator=g, device=dev))).bfloat16()
+    w = ws[0]
+    ref = torch.nn.functional.linear(x, w)
+    acc = torch.zeros((), dtype=torch.float64, device=dev)
+    status = torch.zeros((), dtype=torch.int32, device=dev)
+    scales = [torch.exp(0.05 * i * torch.randn(4096, generator=g, device=dev)).bfloat16() for i in range(21)]
+
+    def search():
+        for sc in scales:
+            wfq = ops.awq_scale_fake_int(w, sc, 128, 4, False, False)
+            ops.awq_gemm_sqerr(x, wfq, ref, acc, status)
+
+    flops = 21 * 2.0 * 512 * 4096 * 14336
+    r = timed(search, 21 * 14336 * 4096 * 4, reps=3)
+    out["awq_lite_search_21_alphas_up_proj_512tok"] = {
+        "ms": r["ms"], "gemm_tflops_incl_quant_kernel": flops / (r["ms"] * 1e-3) / 1e12}
+    wfq = ops.awq_scale_fake_int(w, scales[1], 128, 4, False, False)
+    r = timed(lambda: [ops.awq_gemm_sqerr(x, wfq, ref, acc, status) for _ in range(21)], 1, reps=3)
+    tf = flops / (r["ms"] * 1e-3) / 1e12
+    out["awq_gemm_sqerr_tcgen05_512x14336x4096"] = {"ms_per_gemm": r["ms"] / 21, "tflops": tf,
+                                                    "kernel_status": int(status)}
+    r = timed(lambda: [torch.nn.functional.linear(x, wfq) for _ in range(21)], 1, reps=3)
+    out["cublas_linear_512x14336x4096_for_comparison"] = {"ms_per_gemm": r["ms"] / 21,
+                                                          "tflops": flops / (r["ms"] * 1e-3) / 1e12}
     return out
 
 

@@ -37,13 +37,29 @@ awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restr
     for (int p = 0; p < PPL; ++p) {
       uint4 a = valid ? ld_stream(wv + t * PPL + p) : make_uint4(0, 0, 0, 0);
       uint4 b = valid ? __ldg(sv + spack + p) : make_uint4(0, 0, 0, 0);
-      float fa[P], fb[P];
-      E::unpack(a, fa);
-      E::unpack(b, fb);
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        // packed bf16 multiply = the product rounded to bf16, two elements per instruction
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t acc16 = 0;
 #pragma unroll
-      for (int k = 0; k < P; ++k) {
-        v[p][k] = round_t<T>(fa[k] * fb[k]);
-        bits = max(bits, __float_as_uint(v[p][k]) & 0x7fffffffu);
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 pr = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]),
+                                            *reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+          const uint32_t pw = *reinterpret_cast<const uint32_t*>(&pr);
+          v[p][2 * i] = __uint_as_float(pw << 16);
+          v[p][2 * i + 1] = __uint_as_float(pw & 0xffff0000u);
+          acc16 = __vmaxu2(acc16, pw & 0x7fff7fffu);
+        }
+        bits = max(bits, max(acc16 & 0xffffu, acc16 >> 16) << 16);
+      } else {
+        float fa[P], fb[P];
+        E::unpack(a, fa);
+        E::unpack(b, fb);
+#pragma unroll
+        for (int k = 0; k < P; ++k) {
+          v[p][k] = round_t<T>(fa[k] * fb[k]);
+          bits = max(bits, __float_as_uint(v[p][k]) & 0x7fffffffu);
+        }
       }
     }
     for (int o = lanes >> 1; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
@@ -51,8 +67,7 @@ awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restr
     if (valid) {
 #pragma unroll
       for (int p = 0; p < PPL; ++p) {
-#pragma unroll
-        for (int k = 0; k < P; ++k) v[p][k] = intq_apply(v[p][k], sc, q);
+        intq_apply_n<P>(v[p], sc, q);
         st_stream(yv + t * PPL + p, E::pack(v[p]));
       }
     }

@@ -6,34 +6,46 @@
 // layer output [M, N], all bf16 with K (resp. N for R) contiguous.  The product never goes to
 // memory: accumulators live in tensor memory and the epilogue reduces the squared error.
 //
-// One CTA computes one 128 x 128 output tile.  Warp 0 streams 128 x 64 operand tiles into a
-// 4-stage shared-memory ring with TMA (128-byte swizzle), one thread of warp 1 issues
-// tcgen05.mma (UMMA 128x128x16, bf16 -> fp32 in TMEM) and frees ring slots with tcgen05.commit,
-// warps 2-5 read the accumulator with tcgen05.ld and do the epilogue.
+// One CTA computes one 128 x BN output tile (BN = 128 or 256).  Warp 0 streams 128 x 64 and
+// BN x 64 operand tiles into a shared-memory ring with TMA (128-byte swizzle), one thread of warp 1
+// issues tcgen05.mma (UMMA 128 x BN x 16, bf16 -> fp32 in TMEM) and frees ring slots with
+// tcgen05.commit, warps 2-5 read the accumulator with tcgen05.ld and do the epilogue.
 //
 // Every mbarrier wait is bounded: when a wait runs out, an error bit is set in the caller's status
 // word, the CTA stops waiting anywhere else, lets its outstanding work drain, frees its TMEM and
 // returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "numerics.cuh"
 
 namespace b200q {
 
-constexpr int kGM = 128, kGN = 128, kGK = 64;        // CTA tile; kGK bf16 = one 128-byte swizzle row
-constexpr int kStages = 4;
+constexpr int kGM = 128, kGK = 64;                   // CTA tile rows; kGK bf16 = one 128-byte swizzle row
+constexpr int kMaxStages = 4;
 constexpr int kUmmaK = 16;
-constexpr uint32_t kTileBytesA = kGM * kGK * 2, kTileBytesB = kGN * kGK * 2;
-constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
-constexpr uint32_t kTmemCols = 128;                   // fp32 accumulator columns (= kGN)
+constexpr uint32_t kTileBytesA = kGM * kGK * 2;
 constexpr int kGemmThreads = 192;
+// Two tile widths: 128 x 128 with a 3-deep ring (96 KB, two CTAs per SM, so one CTA's epilogue
+// overlaps the other's main loop) and 128 x 256 with a 4-deep ring (192 KB, one CTA per SM, a
+// third less operand traffic per FLOP).
+template <int BN> struct GemmCfg {
+  static constexpr int kStages = BN == 128 ? 3 : 4;
+  static constexpr uint32_t kTileBytesB = BN * kGK * 2;
+  static constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
+  static constexpr uint32_t kTmemCols = BN;            // fp32 accumulator columns
+  static constexpr int kCtasPerSm = BN == 128 ? 2 : 1;
+  // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
+  static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((kGM >> 4) << 24);
+};
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 enum : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4 };
 
 struct GemmSmem {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t accum;
   uint32_t tmem_base;
   uint32_t abort;
@@ -89,15 +101,13 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
   d |= static_cast<uint64_t>(2) << 61;                          // SWIZZLE_128B
   return d;
 }
-// instruction descriptor: D fp32, A/B bf16, both K-major, N = 128, M = 128
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kGN >> 3) << 17) | ((kGM >> 4) << 24);
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                          uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -116,16 +126,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN>::kCtasPerSm)
 awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __nv_bfloat16* __restrict__ ref, int64_t N, int num_k_blocks,
                       double* __restrict__ sum_io, float* __restrict__ c_out, uint32_t* __restrict__ status) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr uint32_t kStageBytes = Cfg::kStageBytes, kTmemCols = Cfg::kTmemCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // operand ring first (1024-byte aligned for the swizzle), control block after it
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmSmem* sm = reinterpret_cast<GemmSmem*>(ring + kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kGM, n0 = blockIdx.x * kGN;
+  const int m0 = blockIdx.y * kGM, n0 = blockIdx.x * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
@@ -168,7 +182,7 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
         for (int k = 0; k < kGK / kUmmaK; ++k) {
           // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-          umma_bf16(tmem, da + 2 * k, db + 2 * k, (kb | k) != 0 ? 1u : 0u);
+          umma_bf16(tmem, da + 2 * k, db + 2 * k, Cfg::kIdesc, (kb | k) != 0 ? 1u : 0u);
         }
         umma_commit(&sm->empty[s]);   // the slot is free once these MMAs have read it
       }
@@ -184,7 +198,7 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int64_t row = m0 + quarter * 32 + lane;
       const __nv_bfloat16* rrow = ref + row * N + n0;
 #pragma unroll 1
-      for (int c = 0; c < kGN / 32; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t acc[32];
         tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, acc);
         const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
@@ -261,16 +275,29 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
   B200Q_REQUIRE_PTR(status_io);
   B200Q_REQUIRE_ALIGNED(a); B200Q_REQUIRE_ALIGNED(b); B200Q_REQUIRE_ALIGNED(ref);
   if (m <= 0 || n <= 0 || k <= 0) return B200Q_ERR_SHAPE;
-  if (m % kGM || n % kGN || k % kGK || m / kGM > 65535) return B200Q_ERR_UNSUPPORTED;
+  if (m % kGM || n % 128 || k % kGK || m / kGM > 65535) return B200Q_ERR_UNSUPPORTED;
+  // wide tiles when they still give every SM at least ~1.4 tiles, else narrow tiles on two CTAs per SM
+  int bn = 128;
+  if (n % 256 == 0 && (m / kGM) * (n / 256) * 10 >= static_cast<int64_t>(sm_count_cached()) * 14) bn = 256;
+  if (const char* e = getenv("B200Q_AWQ_GEMM_BN")) {
+    const int v = atoi(e);
+    if ((v == 128 || v == 256) && n % v == 0) bn = v;
+  }
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, kGN)) return B200Q_ERR_CUDA;
-  const size_t smem = kStages * kStageBytes + sizeof(GemmSmem) + 1024;
-  if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem)) != cudaSuccess)
-    return B200Q_ERR_CUDA;
-  dim3 grid(static_cast<unsigned>(n / kGN), static_cast<unsigned>(m / kGM));
-  awq_gemm_sqerr_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
-      status_io);
-  return launch_status();
+  if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, bn)) return B200Q_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto launch = [&](auto tag) -> int {
+    constexpr int BN = decltype(tag)::value;
+    using Cfg = GemmCfg<BN>;
+    const size_t smem = Cfg::kStages * Cfg::kStageBytes + sizeof(GemmSmem) + 1024;
+    if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return B200Q_ERR_CUDA;
+    dim3 grid(static_cast<unsigned>(n / BN), static_cast<unsigned>(m / kGM));
+    awq_gemm_sqerr_kernel<BN><<<grid, kGemmThreads, smem, st>>>(
+        map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
+        status_io);
+    return launch_status();
+  };
+  return bn == 256 ? launch(std::integral_constant<int, 256>{}) : launch(std::integral_constant<int, 128>{});
 }

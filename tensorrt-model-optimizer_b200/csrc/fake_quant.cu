@@ -19,10 +19,7 @@ struct IntFq {
   __device__ __forceinline__ IntFq() {}
   __device__ __forceinline__ IntFq(const IntQ& q_, float amax) : q(q_), s(make_int_scale(q_, amax)) {}
   __device__ __forceinline__ float operator()(float x) const { return intq_apply(x, s, q); }
-  template <int N> __device__ __forceinline__ void apply(float* f) const {
-#pragma unroll
-    for (int i = 0; i < N; ++i) f[i] = (*this)(f[i]);
-  }
+  template <int N> __device__ __forceinline__ void apply(float* f) const { intq_apply_n<N>(f, s, q); }
 };
 
 struct E4m3Fq {

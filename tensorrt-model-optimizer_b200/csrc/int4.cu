@@ -33,6 +33,28 @@ template <typename T> __device__ __forceinline__ uint32_t int4_pack(const uint4&
     out |= ((int4_code<T>(f[2 * j], scale) << 4) | int4_code<T>(f[2 * j + 1], scale)) << (8 * j);
   return out;
 }
+// bf16: the multiply, clamp and +8 are the packed bf16 instructions themselves (each rounds to
+// bf16 exactly as the step-by-step form does); z >= 0, so roundf(z) = floor(z + 0.5), read from the
+// low mantissa bits after a round-toward-zero add of 2^23.
+template <> __device__ __forceinline__ uint32_t int4_pack<__nv_bfloat16>(const uint4& v, float scale) {
+  const __nv_bfloat162 s2 = __float2bfloat162_rn(scale);
+  const __nv_bfloat162 hi7 = __float2bfloat162_rn(7.f), lo8 = __float2bfloat162_rn(-8.f),
+                       off8 = __float2bfloat162_rn(8.f);
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t out = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 y = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]), s2);
+    y = __hmax2(lo8, __hmin2(hi7, y));
+    const __nv_bfloat162 z = __hadd2(y, off8);
+    const uint32_t zw = *reinterpret_cast<const uint32_t*>(&z);
+    const float z0 = __uint_as_float(zw << 16), z1 = __uint_as_float(zw & 0xffff0000u);
+    const uint32_t u0 = __float_as_uint(__fadd_rz(z0 + 0.5f, 8388608.f)) & 0xfu;
+    const uint32_t u1 = __float_as_uint(__fadd_rz(z1 + 0.5f, 8388608.f)) & 0xfu;
+    out |= ((u0 << 4) | u1) << (8 * j);
+  }
+  return out;
+}
 
 template <typename T> __device__ __forceinline__ void store_codes(uint8_t* dst, uint32_t codes);
 template <> __device__ __forceinline__ void store_codes<float>(uint8_t* dst, uint32_t c) {

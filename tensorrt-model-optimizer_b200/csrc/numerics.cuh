@@ -137,4 +137,44 @@ __device__ __forceinline__ float intq_apply(float x, const IntScale& s, const In
   return s.live ? o : 0.f;
 }
 
+// NaN-propagating min / max (one instruction each), so that the clamp keeps a NaN input as the
+// reference's compare-and-select does
+__device__ __forceinline__ float fmin_nan(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+// Two elements at once on the fast path (scale div_safe, amax live): packed multiply and packed
+// reciprocal-and-correct division.  Same results as intq_apply, element by element.
+__device__ __forceinline__ float2 intq_apply2_fast(float2 x, const IntScale& s, const IntQ& q) {
+  const float2 t = __fmul2_rn(x, make_float2(s.scale, s.scale));
+  float2 r;
+  r.x = fmax_nan(fmin_nan(rintf(t.x), q.bound), q.lo);
+  r.y = fmax_nan(fmin_nan(rintf(t.y), q.bound), q.lo);
+  float2 o = div2_rn_rcp(r, make_float2(-s.scale, -s.scale), make_float2(s.y, s.y));
+  o.x = (r.x == 0.f) ? r.x : o.x;
+  o.y = (r.y == 0.f) ? r.y : o.y;
+  return o;
+}
+// N (even) elements in place
+template <int N>
+__device__ __forceinline__ void intq_apply_n(float* f, const IntScale& s, const IntQ& q) {
+  if (s.live && s.fast) {
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      const float2 o = intq_apply2_fast(make_float2(f[i], f[i + 1]), s, q);
+      f[i] = o.x;
+      f[i + 1] = o.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = intq_apply(f[i], s, q);
+  }
+}
+
 }  // namespace b200q

@@ -43,3 +43,45 @@ def test_awq_gemm_unsupported_shapes_are_refused():
         ops.awq_gemm_sqerr(a, b, torch.zeros(100, 128, device="cuda", dtype=torch.bfloat16),
                            torch.zeros((), dtype=torch.float64, device="cuda"),
                            torch.zeros((), dtype=torch.int32, device="cuda"))
+
+
+def test_awq_lite_search_same_result_with_and_without_tensor_core_kernel():
+    """The search picks the same alpha and scales whether candidates are evaluated by the fused
+    tcgen05 kernel or by F.linear + the squared-error kernel (losses agree to 1e-3)."""
+    import copy
+
+    import b200q as mtq
+    from b200q import model_calib
+
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up_proj = torch.nn.Linear(256, 512, bias=False)
+            self.down_proj = torch.nn.Linear(512, 256, bias=False)
+
+        def forward(self, x):
+            return self.down_proj(torch.nn.functional.silu(self.up_proj(x)))
+
+    torch.manual_seed(0)
+    base = MLP().cuda().bfloat16()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    mag = torch.exp(torch.randn(256, generator=g, device="cuda"))
+    batches = [(torch.randn(256, 256, generator=g, device="cuda") * mag).bfloat16() for _ in range(2)]
+    results = []
+    for use in (True, False):
+        model_calib.USE_TENSOR_CORE_EVAL = use
+        try:
+            m = copy.deepcopy(base)
+            cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+            cfg["algorithm"] = {"method": "awq_lite", "alpha_step": 0.1, "debug": True}
+            mtq.quantize(m, cfg, lambda mod: [mod(b) for b in batches])
+            results.append({n: (getattr(m, n).awq_lite.loss, getattr(m, n).awq_lite.best_alpha,
+                                getattr(m, n).awq_lite.best_scale) for n in ("up_proj", "down_proj")})
+        finally:
+            model_calib.USE_TENSOR_CORE_EVAL = True
+    for n in ("up_proj", "down_proj"):
+        la, aa, sa = results[0][n]
+        lb, ab, sb = results[1][n]
+        for k in la:
+            assert abs(la[k] - lb[k]) <= 1e-3 * lb[k], (n, k, la[k], lb[k])
+        assert aa == ab and torch.equal(sa, sb)
