@@ -9,9 +9,14 @@
 
 namespace b200q {
 
-constexpr int kHistThreads = 512;
-constexpr int kHistSmemWords = 16384;  // 64 KB of 32-bit counters per CTA
+constexpr int kHistThreads = 1024;
+constexpr int kHistSmemBytes = 200 * 1024;   // shared-memory budget for the replicated counters
 
+// Shared counters are replicated `replicas` times (a power of two <= 32) and a lane always uses
+// replica (lane % replicas).  Replica r starts at word r * (smem_bins + 1): the odd stride puts the
+// same bin of different replicas into different banks, so lanes of a warp that hit one hot bin —
+// the normal case for activations, whose range is set by a few outliers — neither collide on an
+// address nor on a bank.
 template <typename T>
 __global__ void __launch_bounds__(kHistThreads)
 hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, int smem_bins,
@@ -19,50 +24,57 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   extern __shared__ uint32_t sh[];
-  for (int i = threadIdx.x; i < smem_bins * replicas; i += blockDim.x) sh[i] = 0;
+  const int stride_r = smem_bins + 1;
+  for (int i = threadIdx.x; i < stride_r * replicas; i += blockDim.x) sh[i] = 0;
   __syncthreads();
-  uint32_t* mine = sh + (threadIdx.x & (replicas - 1)) * smem_bins;
+  uint32_t* mine = sh + (threadIdx.x & (replicas - 1)) * stride_r;
   const float fbins = static_cast<float>(nbins);
   // bin = int(RN(|x| * nbins / range_max)): the quotient through one reciprocal per thread; tiny
   // quotients may lose bits there but stay below 1 (bin 0)
   const bool fast = div_safe(range_max);
   const float rcp_range = __frcp_rn(range_max);
+  const float2 y2 = make_float2(rcp_range, rcp_range), nd2 = make_float2(-range_max, -range_max);
 
-  auto bin_one = [&](float v) {
-    const float a = fabsf(v);
+  auto count = [&](float a, float quot) {
     if (!(a <= range_max)) return;  // out of range or NaN: not counted
-    const float num = a * fbins;
-    int b = static_cast<int>(fast ? div_rn_rcp(num, range_max, rcp_range) : __fdiv_rn(num, range_max));
+    int b = static_cast<int>(quot);
     if (b >= nbins) b = nbins - 1;
     if (b < smem_bins) atomicAdd(mine + b, 1u);
     else atomicAdd(counts + b, 1ull);
+  };
+  auto bin_pack = [&](const uint4& v) {
+    float f[P];
+    E::unpack(v, f);
+#pragma unroll
+    for (int k = 0; k < P; k += 2) {
+      const float a0 = fabsf(f[k]), a1 = fabsf(f[k + 1]);
+      const float2 num = __fmul2_rn(make_float2(a0, a1), make_float2(fbins, fbins));
+      float2 q;
+      if (fast) q = div2_rn_rcp(num, nd2, y2);
+      else q = make_float2(__fdiv_rn(num.x, range_max), __fdiv_rn(num.y, range_max));
+      count(a0, q.x);
+      count(a1, q.y);
+    }
   };
 
   const int64_t npack = n / P;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  for (; i + stride < npack; i += 2 * stride) {
-    const uint4 v0 = ld_stream(xv + i), v1 = ld_stream(xv + i + stride);
-    float f[P];
-    E::unpack(v0, f);
-#pragma unroll
-    for (int k = 0; k < P; ++k) bin_one(f[k]);
-    E::unpack(v1, f);
-#pragma unroll
-    for (int k = 0; k < P; ++k) bin_one(f[k]);
+  for (; i + 3 * stride < npack; i += 4 * stride) {
+    const uint4 v0 = ld_stream(xv + i), v1 = ld_stream(xv + i + stride), v2 = ld_stream(xv + i + 2 * stride),
+                v3 = ld_stream(xv + i + 3 * stride);
+    bin_pack(v0); bin_pack(v1); bin_pack(v2); bin_pack(v3);
   }
-  for (; i < npack; i += stride) {
-    float f[P];
-    E::unpack(ld_stream(xv + i), f);
-#pragma unroll
-    for (int k = 0; k < P; ++k) bin_one(f[k]);
+  for (; i < npack; i += stride) bin_pack(ld_stream(xv + i));
+  if (blockIdx.x == 0 && threadIdx.x < n - npack * P) {
+    const float a = fabsf(E::to_float(x[npack * P + threadIdx.x]));
+    count(a, __fdiv_rn(a * fbins, range_max));
   }
-  if (blockIdx.x == 0 && threadIdx.x < n - npack * P) bin_one(E::to_float(x[npack * P + threadIdx.x]));
   __syncthreads();
   for (int b = threadIdx.x; b < smem_bins; b += blockDim.x) {
     unsigned long long c = 0;
-    for (int r = 0; r < replicas; ++r) c += sh[r * smem_bins + b];
+    for (int r = 0; r < replicas; ++r) c += sh[r * stride_r + b];
     if (c) atomicAdd(counts + b, c);
   }
 }
@@ -96,17 +108,17 @@ extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins
   if (n <= 0 || nbins <= 0) return B200Q_ERR_SHAPE;
   if (!(range_max > 0.f)) return B200Q_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // shared bins: all of them when they fit, replicated as often as the budget allows (<= 8)
-  int smem_bins = nbins < kHistSmemWords ? nbins : kHistSmemWords;
+  // shared bins: all of them when they fit, replicated as often as the budget allows (<= 32)
+  const int max_words = kHistSmemBytes / 4;
+  int smem_bins = nbins + 1 <= max_words ? nbins : max_words - 1;
   int replicas = 1;
-  while (replicas < 8 && smem_bins * replicas * 2 <= kHistSmemWords) replicas <<= 1;
-  const size_t smem = static_cast<size_t>(smem_bins) * replicas * sizeof(uint32_t);
+  while (replicas < 32 && static_cast<int64_t>(smem_bins + 1) * replicas * 2 <= max_words) replicas <<= 1;
+  const size_t smem = static_cast<size_t>(smem_bins + 1) * replicas * sizeof(uint32_t);
   return B200Q_DISPATCH(dtype, [&] {
     auto kern = hist_collect_kernel<T>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kHistSmemWords * 4) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistSmemBytes) != cudaSuccess)
       return static_cast<int>(B200Q_ERR_CUDA);
-    int grid = grid_for(n / Elem<T>::kPerPack, kHistThreads * 2, 2);
+    int grid = grid_for(n / Elem<T>::kPerPack, kHistThreads * 4, 1);
     kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x), n, nbins, range_max, smem_bins,
                                           replicas, counts);
     return launch_status();
