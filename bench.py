@@ -399,6 +399,40 @@ def run_formats(dev, peak):
     return out
 
 
+def run_profile_kernels():
+    """A few launches of each secondary kernel on small inputs (larger than L2, < 1 GB on the
+    device) — the program the committed ncu summaries of these kernels were captured from."""
+    import torch
+
+    from b200q import ops
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    m, n, k = 512, 14336, 4096
+    a = torch.randn(m, k, generator=g, device=dev).bfloat16()
+    w = (torch.randn(n, k, generator=g, device=dev) * 0.02).bfloat16()
+    s = torch.exp(torch.randn(k, generator=g, device=dev)).bfloat16()
+    ref = torch.nn.functional.linear(a, w)
+    acc = torch.zeros((), dtype=torch.float64, device=dev)
+    status = torch.zeros((), dtype=torch.int32, device=dev)
+    x = torch.randn(2, 8192, 4096, generator=g, device=dev).bfloat16()
+    x[:, :, :4] *= 50
+    w32 = torch.randn(2, 4096, 4096, generator=g, device=dev) * 0.02
+    counts = torch.zeros(2048, dtype=torch.int64, device=dev)
+    amax = ops.amax_tensor(x)
+    rmax = float(amax)
+    for i in range(4):
+        wfq = ops.awq_scale_fake_int(w, s, 128, 4, False, False)
+        ops.awq_gemm_sqerr(a, wfq, ref, acc, status)
+        ops.hist_collect(x[i % 2], counts, 2048, rmax)
+        ops.fake_e4m3(x[i % 2], amax)
+        ops.nvfp4_fake(x[i % 2], amax)
+        ops.fake_int_rows_dynamic(w32[i % 2], 8, False, True)
+        ops.int4_quantize(w.reshape(-1), 128)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_kernels": "done", "gemm_status": int(status)}))
+
+
 def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
     import torch
     import torch.distributed as dist
@@ -447,9 +481,13 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-formats", action="store_true")
+    ap.add_argument("--profile-kernels", action="store_true",
+                    help="run a few launches of the secondary kernels and exit (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    if args.impl == "reference":
+    if args.profile_kernels:
+        run_profile_kernels()
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

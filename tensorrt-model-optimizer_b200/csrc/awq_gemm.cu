@@ -139,7 +139,9 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   GemmSmem* sm = reinterpret_cast<GemmSmem*>(ring + kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kGM, n0 = blockIdx.x * BN;
+  // the (few) row tiles are the fast grid dimension: CTAs that share a B tile run together, so
+  // the tile comes from DRAM once and from L2 for the others
+  const int m0 = blockIdx.x * kGM, n0 = blockIdx.y * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
@@ -275,7 +277,7 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
   B200Q_REQUIRE_PTR(status_io);
   B200Q_REQUIRE_ALIGNED(a); B200Q_REQUIRE_ALIGNED(b); B200Q_REQUIRE_ALIGNED(ref);
   if (m <= 0 || n <= 0 || k <= 0) return B200Q_ERR_SHAPE;
-  if (m % kGM || n % 128 || k % kGK || m / kGM > 65535) return B200Q_ERR_UNSUPPORTED;
+  if (m % kGM || n % 128 || k % kGK || n / 128 > 65535) return B200Q_ERR_UNSUPPORTED;
   // wide tiles when they still give every SM at least ~1.4 tiles, else narrow tiles on two CTAs per SM
   int bn = 128;
   if (n % 256 == 0 && (m / kGM) * (n / 256) * 10 >= static_cast<int64_t>(sm_count_cached()) * 14) bn = 256;
@@ -293,7 +295,7 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
     if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return B200Q_ERR_CUDA;
-    dim3 grid(static_cast<unsigned>(n / BN), static_cast<unsigned>(m / kGM));
+    dim3 grid(static_cast<unsigned>(m / kGM), static_cast<unsigned>(n / BN));
     awq_gemm_sqerr_kernel<BN><<<grid, kGemmThreads, smem, st>>>(
         map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
         status_io);

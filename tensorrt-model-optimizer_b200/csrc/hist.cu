@@ -17,7 +17,8 @@ constexpr int kHistSmemBytes = 200 * 1024;   // shared-memory budget for the rep
 // same bin of different replicas into different banks, so lanes of a warp that hit one hot bin —
 // the normal case for activations, whose range is set by a few outliers — neither collide on an
 // address nor on a bank.
-template <typename T>
+// kAllShared: every bin has a shared counter (the usual case), so no global-atomic path is compiled.
+template <typename T, bool kAllShared>
 __global__ void __launch_bounds__(kHistThreads)
 hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, int smem_bins,
                     int replicas, unsigned long long* __restrict__ counts) {
@@ -34,27 +35,36 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
   const bool fast = div_safe(range_max);
   const float rcp_range = __frcp_rn(range_max);
   const float2 y2 = make_float2(rcp_range, rcp_range), nd2 = make_float2(-range_max, -range_max);
+  const uint32_t last = static_cast<uint32_t>(nbins - 1);
 
+  // a = |x| (non-negative); quot = RN(a * nbins / range_max) < 2^22: its integer part is read from
+  // the low mantissa bits after a round-toward-zero add of 2^23 (no float->int conversion)
   auto count = [&](float a, float quot) {
-    if (!(a <= range_max)) return;  // out of range or NaN: not counted
-    int b = static_cast<int>(quot);
-    if (b >= nbins) b = nbins - 1;
-    if (b < smem_bins) atomicAdd(mine + b, 1u);
-    else atomicAdd(counts + b, 1ull);
+    uint32_t b = __float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu;
+    b = min(b, last);
+    if (a <= range_max) {  // false for out-of-range values and NaN: not counted
+      if (kAllShared || b < static_cast<uint32_t>(smem_bins)) atomicAdd(mine + b, 1u);
+      else atomicAdd(counts + b, 1ull);
+    }
   };
-  auto bin_pack = [&](const uint4& v) {
+  auto bin_pair = [&](float a0, float a1) {
+    const float2 num = __fmul2_rn(make_float2(a0, a1), make_float2(fbins, fbins));
+    float2 q;
+    if (fast) q = div2_rn_rcp(num, nd2, y2);
+    else q = make_float2(__fdiv_rn(num.x, range_max), __fdiv_rn(num.y, range_max));
+    count(a0, q.x);
+    count(a1, q.y);
+  };
+  auto bin_pack = [&](uint4 v) {
+    if (sizeof(T) == 2) {  // clear both sign bits of a 16-bit pair with one instruction
+      v.x &= 0x7fff7fffu; v.y &= 0x7fff7fffu; v.z &= 0x7fff7fffu; v.w &= 0x7fff7fffu;
+    } else {
+      v.x &= 0x7fffffffu; v.y &= 0x7fffffffu; v.z &= 0x7fffffffu; v.w &= 0x7fffffffu;
+    }
     float f[P];
     E::unpack(v, f);
 #pragma unroll
-    for (int k = 0; k < P; k += 2) {
-      const float a0 = fabsf(f[k]), a1 = fabsf(f[k + 1]);
-      const float2 num = __fmul2_rn(make_float2(a0, a1), make_float2(fbins, fbins));
-      float2 q;
-      if (fast) q = div2_rn_rcp(num, nd2, y2);
-      else q = make_float2(__fdiv_rn(num.x, range_max), __fdiv_rn(num.y, range_max));
-      count(a0, q.x);
-      count(a1, q.y);
-    }
+    for (int k = 0; k < P; k += 2) bin_pair(f[k], f[k + 1]);
   };
 
   const int64_t npack = n / P;
@@ -115,7 +125,7 @@ extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins
   while (replicas < 32 && static_cast<int64_t>(smem_bins + 1) * replicas * 2 <= max_words) replicas <<= 1;
   const size_t smem = static_cast<size_t>(smem_bins + 1) * replicas * sizeof(uint32_t);
   return B200Q_DISPATCH(dtype, [&] {
-    auto kern = hist_collect_kernel<T>;
+    auto kern = smem_bins == nbins ? hist_collect_kernel<T, true> : hist_collect_kernel<T, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistSmemBytes) != cudaSuccess)
       return static_cast<int>(B200Q_ERR_CUDA);
     int grid = grid_for(n / Elem<T>::kPerPack, kHistThreads * 4, 1);
