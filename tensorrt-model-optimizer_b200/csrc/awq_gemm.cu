@@ -30,12 +30,14 @@ constexpr int kGemmThreads = 192;
 // Two tile widths: 128 x 128 with a 3-deep ring (96 KB, two CTAs per SM, so one CTA's epilogue
 // overlaps the other's main loop) and 128 x 256 with a 4-deep ring (192 KB, one CTA per SM, a
 // third less operand traffic per FLOP).
-template <int BN> struct GemmCfg {
-  static constexpr int kStages = BN == 128 ? 3 : 4;
+// MT = 2 stacks two 128-row tiles on one B tile (256 x 256 per CTA, all 512 TMEM columns): the
+// least operand traffic per FLOP, used when the problem still yields enough CTAs.
+template <int BN, int MT> struct GemmCfg {
+  static constexpr int kStages = (BN == 128 || MT == 2) ? 3 : 4;
   static constexpr uint32_t kTileBytesB = BN * kGK * 2;
-  static constexpr uint32_t kStageBytes = kTileBytesA + kTileBytesB;
-  static constexpr uint32_t kTmemCols = BN;            // fp32 accumulator columns
-  static constexpr int kCtasPerSm = BN == 128 ? 2 : 1;
+  static constexpr uint32_t kStageBytes = MT * kTileBytesA + kTileBytesB;
+  static constexpr uint32_t kTmemCols = BN * MT;       // fp32 accumulator columns
+  static constexpr int kCtasPerSm = (BN == 128 && MT == 1) ? 2 : 1;
   // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((kGM >> 4) << 24);
 };
@@ -126,12 +128,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN>::kCtasPerSm)
+template <int BN, int MT>
+__global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN, MT>::kCtasPerSm)
 awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __nv_bfloat16* __restrict__ ref, int64_t N, int num_k_blocks,
                       double* __restrict__ sum_io, float* __restrict__ c_out, uint32_t* __restrict__ status) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, MT>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes, kTmemCols = Cfg::kTmemCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -141,7 +143,7 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the (few) row tiles are the fast grid dimension: CTAs that share a B tile run together, so
   // the tile comes from DRAM once and from L2 for the others
-  const int m0 = blockIdx.x * kGM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * kGM * MT, n0 = blockIdx.y * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
@@ -166,8 +168,9 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (!mbar_wait(&sm->empty[s], ph ^ 1, sm, status, kErrProducerWait)) break;
         uint8_t* a = ring + s * kStageBytes;
         mbar_expect_tx(&sm->full[s], kStageBytes);
-        tma_load_2d(a, &map_a, &sm->full[s], kb * kGK, m0);
-        tma_load_2d(a + kTileBytesA, &map_b, &sm->full[s], kb * kGK, n0);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * kTileBytesA, &map_a, &sm->full[s], kb * kGK, m0 + mt * kGM);
+        tma_load_2d(a + MT * kTileBytesA, &map_b, &sm->full[s], kb * kGK, n0);
       }
     }
   } else if (warp == 1) {
@@ -180,11 +183,15 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a = smem_u32(ring + s * kStageBytes);
-        const uint64_t da = umma_desc(a), db = umma_desc(a + kTileBytesA);
+        const uint64_t db = umma_desc(a + MT * kTileBytesA);
 #pragma unroll
-        for (int k = 0; k < kGK / kUmmaK; ++k) {
-          // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-          umma_bf16(tmem, da + 2 * k, db + 2 * k, Cfg::kIdesc, (kb | k) != 0 ? 1u : 0u);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint64_t da = umma_desc(a + mt * kTileBytesA);
+#pragma unroll
+          for (int k = 0; k < kGK / kUmmaK; ++k) {
+            // advancing 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+            umma_bf16(tmem + mt * BN, da + 2 * k, db + 2 * k, Cfg::kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(&sm->empty[s]);   // the slot is free once these MMAs have read it
       }
@@ -197,30 +204,33 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float sq = 0.f;
     if (ok) {
-      const int64_t row = m0 + quarter * 32 + lane;
-      const __nv_bfloat16* rrow = ref + row * N + n0;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, acc);
-        const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
+      for (int mt = 0; mt < MT; ++mt) {
+        const int64_t row = m0 + mt * kGM + quarter * 32 + lane;
+        const __nv_bfloat16* rrow = ref + row * N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);
+          const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const uint4 r4 = __ldg(rp + v);
-          float rf[8];
-          Elem<__nv_bfloat16>::unpack(r4, rf);
+          for (int v = 0; v < 4; ++v) {
+            const uint4 r4 = __ldg(rp + v);
+            float rf[8];
+            Elem<__nv_bfloat16>::unpack(r4, rf);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float a = __uint_as_float(acc[8 * v + j]);
-            const float o = __bfloat162float(__float2bfloat16_rn(a));
-            const float d = __bfloat162float(__float2bfloat16_rn(o - rf[j]));
-            sq = fmaf(d, d, sq);
+            for (int j = 0; j < 8; ++j) {
+              const float a = __uint_as_float(acc[8 * v + j]);
+              const float o = __bfloat162float(__float2bfloat16_rn(a));
+              const float d = __bfloat162float(__float2bfloat16_rn(o - rf[j]));
+              sq = fmaf(d, d, sq);
+            }
           }
-        }
-        if (c_out) {
-          float* cp = c_out + row * N + n0 + c * 32;
+          if (c_out) {
+            float* cp = c_out + row * N + n0 + c * 32;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) cp[j] = __uint_as_float(acc[j]);
+            for (int j = 0; j < 32; ++j) cp[j] = __uint_as_float(acc[j]);
+          }
         }
       }
     }
@@ -278,28 +288,40 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
   B200Q_REQUIRE_ALIGNED(a); B200Q_REQUIRE_ALIGNED(b); B200Q_REQUIRE_ALIGNED(ref);
   if (m <= 0 || n <= 0 || k <= 0) return B200Q_ERR_SHAPE;
   if (m % kGM || n % 128 || k % kGK || n / 128 > 65535) return B200Q_ERR_UNSUPPORTED;
-  // wide tiles when they still give every SM at least ~1.4 tiles, else narrow tiles on two CTAs per SM
-  int bn = 128;
-  if (n % 256 == 0 && (m / kGM) * (n / 256) * 10 >= static_cast<int64_t>(sm_count_cached()) * 14) bn = 256;
-  if (const char* e = getenv("B200Q_AWQ_GEMM_BN")) {
+  // Tile choice: 256 x 256 per CTA when that still gives ~3/4 of the SMs a tile (least operand
+  // traffic per FLOP — the kernel is bound by L2 -> SM bandwidth); else 128 x 256 when every SM gets
+  // 0.4 tiles or more (fewer, faster CTAs beat more CTAs here); else 128 x 128 on two CTAs per SM.
+  const int64_t sms = sm_count_cached();
+  int bn = 128, mt = 1;
+  if (n % 256 == 0 && (m / kGM) * (n / 256) * 10 >= sms * 4) bn = 256;
+  if (n % 256 == 0 && m % 256 == 0 && (m / 256) * (n / 256) * 4 >= sms * 3) { bn = 256; mt = 2; }
+  if (const char* e = getenv("B200Q_AWQ_GEMM_TILE")) {   // "128", "256" or "512" (= 256 x 256)
     const int v = atoi(e);
-    if ((v == 128 || v == 256) && n % v == 0) bn = v;
+    if (v == 128) { bn = 128; mt = 1; }
+    if (v == 256 && n % 256 == 0) { bn = 256; mt = 1; }
+    if (v == 512 && n % 256 == 0 && m % 256 == 0) { bn = 256; mt = 2; }
   }
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, bn)) return B200Q_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  auto launch = [&](auto tag) -> int {
-    constexpr int BN = decltype(tag)::value;
-    using Cfg = GemmCfg<BN>;
+  auto launch = [&](auto bn_tag, auto mt_tag) -> int {
+    constexpr int BN = decltype(bn_tag)::value, MT = decltype(mt_tag)::value;
+    using Cfg = GemmCfg<BN, MT>;
     const size_t smem = Cfg::kStages * Cfg::kStageBytes + sizeof(GemmSmem) + 1024;
-    if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return B200Q_ERR_CUDA;
-    dim3 grid(static_cast<unsigned>(m / kGM), static_cast<unsigned>(n / BN));
-    awq_gemm_sqerr_kernel<BN><<<grid, kGemmThreads, smem, st>>>(
+    dim3 grid(static_cast<unsigned>(m / (kGM * MT)), static_cast<unsigned>(n / BN));
+    awq_gemm_sqerr_kernel<BN, MT><<<grid, kGemmThreads, smem, st>>>(
         map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
         status_io);
     return launch_status();
   };
-  return bn == 256 ? launch(std::integral_constant<int, 256>{}) : launch(std::integral_constant<int, 128>{});
+  using I1 = std::integral_constant<int, 1>;
+  using I2 = std::integral_constant<int, 2>;
+  using I128 = std::integral_constant<int, 128>;
+  using I256 = std::integral_constant<int, 256>;
+  if (bn == 256 && mt == 2) return launch(I256{}, I2{});
+  if (bn == 256) return launch(I256{}, I1{});
+  return launch(I128{}, I1{});
 }
