@@ -240,6 +240,16 @@ int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double
 int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
                          int64_t k, double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* ---------------------------------------------------------------- export packers ------------ */
+
+/* INT4 weights in the checkpoint layout: q = clamp(round_half_even(w / scale[r, c/block]), -8, 7)
+ * as a signed nibble, byte [r, c] of out[rows/2, cols] = q[2r, c] | q[2r+1, c] << 4.  scales is
+ * [rows, cols/block], fp32 (scales_are_f32 != 0: the quotient is an fp32 division) or of type T
+ * (the quotient is rounded to T).  Replaces pack_int4_in_uint8
+ * (modelopt/torch/export/quant_utils.py:697-738). */
+int b200q_int4_export_pack(const void* w, const void* scales, int scales_are_f32, uint8_t* out,
+                           int64_t rows, int64_t cols, int block, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -412,3 +412,33 @@ def _kl(pk: np.ndarray, qk: np.ndarray) -> float:
         t = np.where(pk > 0, pk * np.log(pk / qk), 0.0)
     t = np.where((pk > 0) & (qk == 0), np.inf, t)
     return float(t.sum())
+
+
+# --------------------------------------------------------------------------- export packers ----
+
+def export_scaling_factor(w: np.ndarray, group: int) -> np.ndarray:
+    """get_scaling_factor_from_weight (modelopt/torch/export/quant_utils.py:68-91): fp32 amax/7 per
+    (row, group) when group > 0, amax/127 per row when group == 0; zeros become 1."""
+    w = np.asarray(w, dtype=F32)
+    if group:
+        amax = np.abs(w.reshape(w.shape[0], -1, group)).max(-1)
+        s = (amax / F32(7.0)).astype(F32)
+    else:
+        s = (np.abs(w).max(-1) / F32(127.0)).astype(F32)
+    s[s == 0] = 1.0
+    return s
+
+
+def pack_int4_export(w: np.ndarray, scales: np.ndarray, T="f32", scales_in_T=False) -> np.ndarray:
+    """pack_int4_in_uint8 (quant_utils.py:697-738) for 2-D weights: signed nibbles
+    clamp(round_half_even(w/scale), -8, 7), byte [r, c] = q[2r, c] & 15 | (q[2r+1, c] & 15) << 4."""
+    w = np.asarray(w, dtype=F32)
+    block = w.shape[1] // scales.shape[1]
+    se = np.repeat(np.asarray(scales, dtype=F32), block, axis=1)
+    q = (w / se).astype(F32)
+    if scales_in_T:
+        q = round_to(q, T)
+    q = np.clip(np.rint(q), -8, 7).astype(np.int8)
+    lo = q[0::2].astype(np.uint8) & 0x0F
+    hi = q[1::2].astype(np.uint8) & 0x0F
+    return (lo | (hi << 4)).astype(np.uint8)

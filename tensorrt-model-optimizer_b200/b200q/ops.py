@@ -407,3 +407,19 @@ def awq_gemm_sqerr(a: torch.Tensor, b: torch.Tensor, ref: torch.Tensor, acc: tor
         call("b200q_awq_gemm_sqerr", a.data_ptr(), b.data_ptr(), ref.data_ptr(), m, n, k, acc.data_ptr(),
              c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(a))
     return acc
+
+
+def int4_export_pack(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """w [rows, cols], scales [rows, cols/block] (fp32 or w.dtype) -> uint8 [rows/2, cols]."""
+    w = _prep(w)
+    assert w.dim() == 2 and scales.dim() == 2 and scales.shape[0] == w.shape[0]
+    rows, cols = w.shape
+    block = cols // scales.shape[1]
+    sc = _cuda(scales, "scales").contiguous()
+    if sc.dtype not in (torch.float32, w.dtype):
+        sc = sc.float()
+    out = torch.empty((rows // 2, cols), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        call("b200q_int4_export_pack", w.data_ptr(), sc.data_ptr(), int(sc.dtype == torch.float32),
+             out.data_ptr(), rows, cols, block, dtype_code(w), _stream(w))
+    return out

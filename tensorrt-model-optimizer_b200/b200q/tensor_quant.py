@@ -154,3 +154,27 @@ class DynamicBlockQuantizationFunction(Function):
 fake_tensor_quant = FakeTensorQuantFunction.apply
 scaled_e4m3 = ScaledE4M3Function.apply
 dynamic_block_quant = DynamicBlockQuantizationFunction.apply
+
+
+def _register_reference_op_names():
+    """Also expose the two ops under the reference's names (``tensorrt::quantize_op``,
+    ``tensorrt::dynamic_block_quantize_op``, tensor_quant.py:226-273) so that code and exported
+    graphs that refer to ``torch.ops.tensorrt.*`` resolve to these kernels.  Skipped when that
+    namespace already defines them (the reference itself is imported in the same process)."""
+    try:
+        lib = torch.library.Library("tensorrt", "FRAGMENT")
+        lib.define("quantize_op(Tensor input, Tensor amax, int num_bits, int exponent_bits, "
+                   "bool unsigned, bool narrow_range) -> Tensor")
+        lib.define("dynamic_block_quantize_op(Tensor input, int block_size, Tensor amax, int num_bits, "
+                   "int exponent_bits, int scale_num_bits, int scale_exponent_bits) -> Tensor")
+        lib.impl("quantize_op", lambda i, a, nb, eb, u, nr: quantize_op(i, a, nb, eb, u, nr), "CUDA")
+        lib.impl("dynamic_block_quantize_op",
+                 lambda i, bs, a, nb, eb, snb, seb: dynamic_block_quantize_op(i, bs, a, nb, eb, snb, seb), "CUDA")
+        lib.impl("quantize_op", lambda i, a, nb, eb, u, nr: torch.empty_like(i), "Meta")
+        lib.impl("dynamic_block_quantize_op", lambda i, bs, a, nb, eb, snb, seb: torch.empty_like(i), "Meta")
+        return lib
+    except RuntimeError:
+        return None
+
+
+_tensorrt_lib = _register_reference_op_names()

@@ -236,6 +236,32 @@ def golden_hist(out):
     np.savez_compressed(out / "hist.npz", **cases)
 
 
+def golden_export(out):
+    from modelopt.torch.export.quant_utils import (get_scaling_factor_from_weight, pack_int4_in_uint8,
+                                                   to_quantized_weight)
+    from modelopt.torch.quantization.qtensor import NVFP4QTensor
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        w = gen((64, 256), T, 800 + i, scale=0.05)
+        cases[f"{T}_w"] = bits(w)
+        s4 = get_scaling_factor_from_weight(w, 128)
+        cases[f"{T}_int4_scale"] = bits(s4)
+        cases[f"{T}_int4_packed"] = bits(pack_int4_in_uint8(w, s4))
+        s8 = get_scaling_factor_from_weight(w, 0)
+        cases[f"{T}_int8_scale"] = bits(s8)
+        cases[f"{T}_int8_q"] = bits(to_quantized_weight(w, s8, "int8_sq"))
+        sf = w.abs().amax().float() / 448.0
+        cases[f"{T}_fp8_scale"] = bits(sf.reshape(1))
+        cases[f"{T}_fp8_q"] = bits(to_quantized_weight(w, sf, "fp8"))
+        wsf2 = NVFP4QTensor.get_weights_scaling_factor_2(w)
+        wsf, _ = NVFP4QTensor.get_weights_scaling_factor(w, 16, wsf2)
+        cases[f"{T}_nvfp4_wsf"] = bits(wsf)
+        cases[f"{T}_nvfp4_wsf2"] = bits(wsf2.reshape(1))
+        cases[f"{T}_nvfp4_packed"] = bits(to_quantized_weight(w, wsf, "nvfp4", wsf2, 16))
+    np.savez_compressed(out / "export.npz", **cases)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -244,7 +270,7 @@ def main():
     import_reference(args.ref)
     torch.manual_seed(0)
     fns = {"fake_int": golden_fake_int, "fake_e4m3": golden_fake_e4m3, "nvfp4": golden_nvfp4,
-           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist}
+           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export}
     for name, fn in fns.items():
         if args.only and name not in args.only.split(","):
             continue

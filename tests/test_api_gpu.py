@@ -256,3 +256,70 @@ def test_mse_calibration_matches_reference_int8(mtq):
         assert np.mean(got_w != ref_w) <= 0.02, name      # a near-tie between two candidates may flip
     from b200q.calib import MseCalibrator
     assert isinstance(model.up_proj.weight_quantizer._calibrator, MseCalibrator)
+
+
+def test_reference_op_names_resolve_to_these_kernels(mtq):
+    x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
+    amax = x.abs().amax().float()
+    a = torch.ops.tensorrt.quantize_op(x, amax, 8, 4, False, False)
+    b = torch.ops.b200q.quantize_op(x, amax, 8, 4, False, False)
+    assert torch.equal(a, b)
+    c = torch.ops.tensorrt.dynamic_block_quantize_op(x, 16, amax, 4, 2, 8, 4)
+    assert torch.equal(c, mtq.ops.nvfp4_fake(x, amax))
+    assert torch.ops.tensorrt.quantize_op(x.to("meta"), amax.to("meta"), 8, 0, False, True).shape == x.shape
+
+
+def test_batched_exchanges_over_nccl_single_rank(mtq):
+    """The flat amax / histogram exchanges on GPU tensors through NCCL (world of one rank: the
+    collectives run, the values must come back unchanged)."""
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        pytest.skip("a process group already exists")
+    dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29631", rank=0, world_size=1,
+                            device_id=torch.device("cuda", 0))
+    try:
+        m = MLP().cuda().bfloat16()
+        mtq.replace_quant_module(m)
+        cfg = {"*input_quantizer": {"num_bits": 8, "axis": None, "calibrator": "histogram"},
+               "*weight_quantizer": {"num_bits": 8, "axis": 0}, "default": {"enable": False}}
+        mtq.set_quantizer_by_cfg(m, cfg)
+        x = torch.randn(64, 128, device="cuda", dtype=torch.bfloat16)
+        for q in (m.up_proj.input_quantizer, m.down_proj.input_quantizer):
+            q._calibrator.collect(x)
+        m.up_proj.weight_quantizer.amax = m.up_proj.weight.abs().amax(1, keepdim=True)
+        m.down_proj.weight_quantizer.amax = m.down_proj.weight.abs().amax(1, keepdim=True)
+        before = m.up_proj.weight_quantizer.amax.clone()
+        assert mtq.dist.sync_amax(m) == 1
+        assert torch.equal(before, m.up_proj.weight_quantizer.amax)
+        h = m.up_proj.input_quantizer._calibrator.hist.clone()
+        assert mtq.dist.sync_histograms(m) == 2
+        assert torch.equal(h, m.up_proj.input_quantizer._calibrator.hist)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("T", ["f32", "f16", "bf16"])
+def test_export_packers_match_reference(mtq, T):
+    from b200q import export
+
+    g = load("export")
+    w = to_f32(g[f"{T}_w"], T)
+    wt = tensor_from_f32(w, T)
+    s4 = export.get_scaling_factor_from_weight(wt, 128)
+    assert same_bits(s4.cpu().numpy(), g[f"{T}_int4_scale"])
+    assert np.array_equal(export.to_quantized_weight(wt, s4, "int4_awq").cpu().numpy(), g[f"{T}_int4_packed"])
+    # scales given in the weight's own type: the quotient is rounded to that type first
+    s4t = tensor_from_f32(qo.round_to(s4.cpu().numpy(), T), T)
+    got = export.pack_int4_in_uint8(wt, s4t).cpu().numpy()
+    assert np.array_equal(got, qo.pack_int4_export(w, qo.round_to(s4.cpu().numpy(), T), T, scales_in_T=True))
+    s8 = export.get_scaling_factor_from_weight(wt, 0)
+    assert same_bits(s8.cpu().numpy(), g[f"{T}_int8_scale"])
+    assert np.array_equal(export.to_quantized_weight(wt, s8, "int8_sq").cpu().numpy(), g[f"{T}_int8_q"])
+    sf = torch.from_numpy(g[f"{T}_fp8_scale"]).cuda().reshape(())
+    q = export.to_quantized_weight(wt, sf, "fp8")
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), g[f"{T}_fp8_q"])
+    wsf = torch.from_numpy(g[f"{T}_nvfp4_wsf"]).cuda().view(torch.float8_e4m3fn)
+    wsf2 = torch.from_numpy(g[f"{T}_nvfp4_wsf2"]).cuda().reshape(())
+    p = export.to_quantized_weight(wt, wsf, "nvfp4", wsf2, 16)
+    assert np.array_equal(p.cpu().numpy(), g[f"{T}_nvfp4_packed"])

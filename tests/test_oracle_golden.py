@@ -185,3 +185,19 @@ def test_c_restatement_matches_numpy_oracle_and_golden():
         packed, scales, s2 = cref.nvfp4_quantize_bf16(lib, bits.reshape(-1), amax, threads=3)
         wp, ws, ws2 = qo.nvfp4_quantize(x, 16, amax=None if amax < 0 else np.float32(amax))
         assert np.array_equal(packed, wp.reshape(-1)) and np.array_equal(scales, ws.reshape(-1)) and s2 == ws2
+
+
+def test_export_packers_match_reference():
+    g = load("export")
+    for T in TS:
+        w = to_f32(g[f"{T}_w"], T)
+        s4 = qo.export_scaling_factor(w, 128)
+        assert same_bits(s4, g[f"{T}_int4_scale"]), T
+        assert np.array_equal(qo.pack_int4_export(w, s4, T), g[f"{T}_int4_packed"]), T
+        s8 = qo.export_scaling_factor(w, 0)
+        assert same_bits(s8, g[f"{T}_int8_scale"]), T
+        assert np.array_equal(qo.int8_quantize(w, s8[:, None], "f32"), g[f"{T}_int8_q"]), T
+        # a 0-dim fp32 scale does not promote a 16-bit weight: the quotient is rounded to T
+        assert np.array_equal(qo.fp8_quantize(w, g[f"{T}_fp8_scale"].reshape(()), T), g[f"{T}_fp8_q"]), T
+        p, _, _ = qo.nvfp4_quantize(w, 16, s2=g[f"{T}_nvfp4_wsf2"][0], scales=g[f"{T}_nvfp4_wsf"])
+        assert np.array_equal(p, g[f"{T}_nvfp4_packed"]), T
