@@ -240,6 +240,26 @@ int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double
 int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
                          int64_t k, double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* ---------------------------------------------------------------- MX (E8M0-scaled) formats -- */
+
+/* element formats of b200q_mx_fake (numbering of the reference's Types enum) */
+enum { B200Q_MX_E4M3 = 0, B200Q_MX_E5M2 = 1, B200Q_MX_INT8 = 2, B200Q_MX_E2M1 = 6, B200Q_MX_E3M2 = 7,
+       B200Q_MX_E2M3 = 8 };
+
+/* MX fake quantisation over nblocks runs of `block` contiguous elements:
+ *   unscale = 2^clamp(ceil(log2(block_amax / format_max)), -127, 127) (1 for amax 0/inf/NaN),
+ *   y = T(sign(x) * round_to_format(|x| / unscale) * unscale), rounding to nearest even, saturating.
+ * Replaces fused_amax_convert with an E8M0 scale format
+ * (modelopt/torch/quantization/src/tensor_quant_mx.cu:36-54,105-137,239-294). */
+int b200q_mx_fake(const void* x, void* y, int64_t nblocks, int block, int dtype, int elem_format,
+                  void* stream);
+
+/* MXFP4 real quantisation: scale byte = 127 + ceil(max(log2(block_amax/6), -127)), code =
+ * (x > 0 ? 0 : 8) + number of E2M1 bounds strictly below |x / 2^e|, even element in the low nibble.
+ * Replaces MXFP4QTensor.quantize (modelopt/torch/quantization/qtensor/mxfp4_tensor.py:38-81). */
+int b200q_mxfp4_quantize(const void* x, int64_t nblocks, int block, int dtype, uint8_t* packed,
+                         uint8_t* scales, void* stream);
+
 /* ---------------------------------------------------------------- export packers ------------ */
 
 /* INT4 weights in the checkpoint layout: q = clamp(round_half_even(w / scale[r, c/block]), -8, 7)

@@ -442,3 +442,84 @@ def pack_int4_export(w: np.ndarray, scales: np.ndarray, T="f32", scales_in_T=Fal
     lo = q[0::2].astype(np.uint8) & 0x0F
     hi = q[1::2].astype(np.uint8) & 0x0F
     return (lo | (hi << 4)).astype(np.uint8)
+
+
+# --------------------------------------------------------------------------- MX formats --------
+# Element formats: name -> (exponent bits, mantissa bits, bias, max); "int8" handled apart.
+MX_FORMATS = {"e4m3": (4, 3, 7, 448.0), "e5m2": (5, 2, 15, 57344.0), "e2m1": (2, 1, 1, 6.0),
+              "e3m2": (3, 2, 3, 28.0), "e2m3": (2, 3, 1, 7.5), "int8": (0, 0, 0, 127.0)}
+
+
+def minifloat_round(a: np.ndarray, fmt: str) -> np.ndarray:
+    """Non-negative fp32 -> nearest value of the format (ties to even), saturating at its max.
+    Restates convert_to_types (modelopt/torch/quantization/src/tensor_quant_mx.h:72-186): the
+    table formats' bounds are the midpoints and its tie rule picks the even mantissa."""
+    a = np.asarray(a, np.float32)
+    _, mbits, bias, fmax = MX_FORMATS[fmt]
+    if fmt == "int8":
+        return np.clip(np.rint(a), -127, 127).astype(np.float32)
+    _, ex = np.frexp(a)                       # a = m * 2^ex, m in [0.5, 1)
+    e = np.maximum(ex - 1, 1 - bias)          # subnormals share the smallest normal exponent
+    quantum = np.ldexp(np.float32(1), (e - mbits).astype(np.int32)).astype(np.float32)
+    r = (np.rint(a / quantum) * quantum).astype(np.float32)
+    r = np.where(np.isnan(a) | (r > fmax), np.float32(fmax), r)
+    return r.astype(np.float32)
+
+
+def mx_unscale_exponent(amax: np.ndarray, fmt: str) -> np.ndarray:
+    """clamp(ceil(log2(amax / format_max))) read from the bits of the fp32 quotient
+    (compute_scale_e8m0_NV, modelopt/torch/quantization/src/tensor_quant_mx.cu:105-137)."""
+    ratio = (np.asarray(amax, np.float32) / np.float32(MX_FORMATS[fmt][3])).astype(np.float32)
+    u = ratio.view(np.uint32)
+    ef = ((u >> 23) & 0xFF).astype(np.int32)
+    sf = (u & 0x7FFFFF).astype(np.int64)
+    up = (sf > 0) & (ef != 0xFE) & ~((ef == 0) & (sf <= 0x400000))
+    return np.where(up, ef - 126, ef - 127).astype(np.int32)
+
+
+def mx_fake(x: np.ndarray, block: int, fmt: str, T="f32") -> np.ndarray:
+    """MX fake quantisation over the last dim (amax_and_convert_kernel + quantize,
+    modelopt/torch/quantization/src/tensor_quant_mx.cu:36-54,239-294); ragged tails are padded
+    with zeros for the block amax.  A zero input gives +0 here (the reference leaves its sign
+    variable unset for x == 0)."""
+    x = np.asarray(x, np.float32)
+    k = x.shape[-1]
+    xp = pad_last(x, block)
+    blocks = xp.reshape(-1, block)
+    amax = np.abs(blocks).max(axis=1)
+    e = mx_unscale_exponent(amax, fmt)
+    e = np.where((amax == 0) | ~np.isfinite(amax), 0, e)
+    scale = np.ldexp(np.float32(1), -e).astype(np.float32)[:, None]
+    unscale = np.ldexp(np.float32(1), e).astype(np.float32)[:, None]
+    with np.errstate(over="ignore", invalid="ignore"):
+        q = minifloat_round((np.abs(blocks) * scale).astype(np.float32), fmt)
+        y = np.copysign((q * unscale).astype(np.float32), blocks)
+    y = y.reshape(xp.shape)[..., :k]
+    return round_to(y, T)
+
+
+def mxfp4_quantize(x: np.ndarray, block=32):
+    """-> (packed uint8 [..., K/2], scale bytes [numel/block, 1]); MXFP4QTensor.quantize
+    (modelopt/torch/quantization/qtensor/mxfp4_tensor.py:38-81): ties go to the smaller
+    magnitude and every value that is not > 0 carries the sign bit."""
+    x = np.asarray(x, np.float32)
+    b = x.reshape(-1, block)
+    amax = np.abs(b).max(axis=1, keepdims=True)
+    with np.errstate(divide="ignore"):
+        e = np.ceil(np.maximum(np.log2((amax / np.float32(6.0)).astype(np.float32)), np.float32(-127)))
+    q = (b / np.exp2(e).astype(np.float32)).astype(np.float32)
+    bounds = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], np.float32)
+    code = (np.abs(q)[..., None] > bounds).sum(-1).astype(np.uint8)
+    code = code + np.where(q > 0, 0, 8).astype(np.uint8)
+    code = code.reshape(*x.shape[:-1], x.shape[-1] // 2, 2)
+    packed = (code[..., 0] | (code[..., 1] << 4)).astype(np.uint8)
+    return packed, (e + 127).astype(np.uint8)
+
+
+def mxfp4_dequantize(packed: np.ndarray, scales: np.ndarray, block=32, T="f32") -> np.ndarray:
+    """MXFP4QTensor.dequantize (modelopt/torch/quantization/qtensor/mxfp4_tensor.py:83-143)."""
+    codes = np.stack([packed & 0xF, packed >> 4], axis=-1).reshape(*packed.shape[:-1], -1)
+    mags = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6], np.float32)[codes & 7]
+    v = np.where(codes & 8, -mags, mags).astype(np.float32)
+    v = v.reshape(-1, block) * np.exp2(scales.reshape(-1, 1).astype(np.float32) - 127).astype(np.float32)
+    return round_to(v.reshape(codes.shape).astype(np.float32), T)

@@ -53,6 +53,8 @@ SIGNATURES = {
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],
     "b200q_int4_export_pack": [_p, _p, _i, _p, _i64, _i64, _i, _i, _p],
+    "b200q_mx_fake": [_p, _p, _i64, _i, _i, _i, _p],
+    "b200q_mxfp4_quantize": [_p, _i64, _i, _i, _p, _p, _p],
 }
 _RESTYPES = {"b200q_strerror": C.c_char_p}
 _NO_STATUS = {"b200q_strerror", "b200q_version", "b200q_sm_count", "b200q_nvfp4_group_tile_elems",

@@ -9,6 +9,7 @@ from typing import Any
 
 __all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG",
            "INT4_BLOCKWISE_WEIGHT_ONLY_CFG", "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG",
+           "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG",
            "choices", "need_calibration"]
 
 _default_disabled_quantizer_cfg = {
@@ -95,7 +96,20 @@ NVFP4_AWQ_LITE_CFG = {
     "algorithm": "awq_lite",
 }
 
-choices = {"INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
+def _mx(num_bits):
+    return {"num_bits": num_bits, "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (8, 0)}, "enable": True}
+
+
+MXFP8_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx((4, 3)), "*input_quantizer": _mx((4, 3)),
+                                   **_default_disabled_quantizer_cfg}, "algorithm": None}
+MXFP6_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx((3, 2)), "*input_quantizer": _mx((3, 2)),
+                                   **_default_disabled_quantizer_cfg}, "algorithm": None}
+MXFP4_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx((2, 1)), "*input_quantizer": _mx((2, 1)),
+                                   **_default_disabled_quantizer_cfg}, "algorithm": None}
+MXINT8_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx(8), "*input_quantizer": _mx(8),
+                                    **_default_disabled_quantizer_cfg}, "algorithm": None}
+
+choices = {"MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG","INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
            "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG"}
 
 

@@ -18,8 +18,8 @@ from torch import nn
 
 from .. import calib, ops
 from ..config import QuantizerAttributeConfig
-from ..qtensor import (BaseQuantizedTensor, FP8QTensor, INT4QTensor, INT8QTensor, NVFP4QTensor,
-                       QTensorWrapper)
+from ..qtensor import (BaseQuantizedTensor, FP8QTensor, INT4QTensor, INT8QTensor, MXFP4QTensor,
+                       NVFP4QTensor, QTensorWrapper)
 from ..tensor_quant import dynamic_block_quant, fake_tensor_quant, scaled_e4m3
 from ..utils import convert_quantization_axis_to_reduce_axis, reduce_amax
 
@@ -362,6 +362,11 @@ class TensorQuantizer(nn.Module):
             bufs["_scale"] = scale
         elif self._num_bits == 8:
             outputs, scale = INT8QTensor.quantize(inputs, axis=self._axis, block_sizes=blocks_only)
+            bufs["_scale"] = scale
+        elif bs.get("scale_bits") == (8, 0) and bs.get("type") == "dynamic":
+            if self._num_bits != (2, 1):
+                raise ValueError(f"Real quantization for MX {self._num_bits} format is not supported.")
+            outputs, scale = MXFP4QTensor.quantize(inputs, bs[-1])
             bufs["_scale"] = scale
         elif bs.get("scale_bits") == (4, 3):
             outputs, s, s2 = NVFP4QTensor.quantize(

@@ -423,3 +423,35 @@ def int4_export_pack(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
         call("b200q_int4_export_pack", w.data_ptr(), sc.data_ptr(), int(sc.dtype == torch.float32),
              out.data_ptr(), rows, cols, block, dtype_code(w), _stream(w))
     return out
+
+
+# --------------------------------------------------------------------------- MX formats --------
+
+MX_FORMATS = {(4, 3): 0, (5, 2): 1, 8: 2, (2, 1): 6, (3, 2): 7, (2, 3): 8}
+
+
+def mx_fake(x: torch.Tensor, block: int, num_bits) -> torch.Tensor:
+    """MX fake quant along the last dim (blocks of ``block``, E8M0 scale); pads like the reference."""
+    fmt = MX_FORMATS[tuple(num_bits) if isinstance(num_bits, (tuple, list)) else num_bits]
+    shape = x.shape
+    pad = (-shape[-1]) % block
+    xx = torch.nn.functional.pad(x, (0, pad)) if pad else x
+    xx = _prep(xx)
+    y = torch.empty_like(xx)
+    with torch.cuda.device(xx.device):
+        call("b200q_mx_fake", xx.data_ptr(), y.data_ptr(), xx.numel() // block, block, dtype_code(xx), fmt,
+             _stream(xx))
+    return y[..., : shape[-1]].contiguous() if pad else y
+
+
+def mxfp4_quantize(x: torch.Tensor, block: int = 32):
+    """-> (packed uint8 [..., K/2], e8m0 scale bytes uint8 [numel/block, 1])."""
+    x = _prep(x)
+    n = x.numel()
+    assert n % block == 0
+    packed = torch.empty((*x.shape[:-1], x.shape[-1] // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((n // block, 1), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        call("b200q_mxfp4_quantize", x.data_ptr(), n // block, block, dtype_code(x), packed.data_ptr(),
+             scales.data_ptr(), _stream(x))
+    return packed, scales

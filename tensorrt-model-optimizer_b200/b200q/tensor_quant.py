@@ -53,9 +53,13 @@ def dynamic_block_quantize_op(input: torch.Tensor, block_size: int, amax: torch.
             x = torch.nn.functional.pad(x, (0, pad))
         y = ops.nvfp4_fake(x, amax)
         return y[..., : shape[-1]].contiguous() if pad else y
+    if scale_fmt == (8, 0):  # MX formats: power-of-two block scales, no global amax
+        key = num_bits if exponent_bits == 0 else fmt
+        if key in ops.MX_FORMATS:
+            return ops.mx_fake(input, block_size, key)
     raise NotImplementedError(
         f"Unsupported num_bits: {fmt}, scale_bits: {scale_fmt}, block {block_size} for dynamic block "
-        "quantization (NVFP4 = (2,1) values, (4,3) scales, block 16 is built).")
+        "quantization (built: NVFP4 = (2,1)/(4,3)/16 and the MX formats with (8,0) scales).")
 
 
 @dynamic_block_quantize_op.register_fake
@@ -141,8 +145,9 @@ class DynamicBlockQuantizationFunction(Function):
             exponent_bits, nb = 0, num_bits
         else:
             exponent_bits, nb = num_bits[0], num_bits[0] + num_bits[1] + 1
-        if amax is None:
-            amax = ops.amax_tensor(inputs)
+        if amax is None:  # MX formats carry no global amax; the op needs a tensor argument
+            amax = (ops.amax_tensor(inputs) if tuple(scale_bits) != (8, 0)
+                    else torch.zeros((), dtype=torch.float32, device=inputs.device))
         return dynamic_block_quantize_op(inputs, block_size, _as_tensor(amax, inputs), nb, exponent_bits,
                                          scale_bits[0] + scale_bits[1] + 1, scale_bits[0])
 

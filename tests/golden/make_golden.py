@@ -262,6 +262,60 @@ def golden_export(out):
     np.savez_compressed(out / "export.npz", **cases)
 
 
+def golden_mxfp4(out):
+    from modelopt.torch.quantization.qtensor import MXFP4QTensor
+
+    cases = {}
+    for i, T in enumerate(("f32", "f16", "bf16")):
+        for j, (shape, block) in enumerate([((8, 128), 32), ((3, 5, 64), 32), ((4, 64), 16)]):
+            x = gen(shape, T, 900 + 10 * i + j, scale=(0.02, 1.0, 40.0)[j], heavy=(j == 1))
+            if j == 0:
+                x[0, :32] = 0          # an all-zero block
+                x[1, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0]).to(x.dtype)  # ties
+                x[1, 8:32] = 0
+            q, s = MXFP4QTensor.quantize(x, block)
+            k = f"{T}_{j}"
+            cases[k + "_x"] = bits(x)
+            cases[k + "_block"] = np.array(block)
+            cases[k + "_packed"] = bits(q._quantized_data)
+            cases[k + "_scales"] = bits(s)
+            cases[k + "_deq"] = bits(q.dequantize(scale=s, block_sizes={-1: block}))
+    np.savez_compressed(out / "mxfp4.npz", **cases)
+
+
+def golden_mx_known_answers(out, ref_root):
+    """The known-answer tables of the reference's MX tests, read from the test source as data
+    (tests/gpu/torch/quantization/test_quantize_mxformats_cuda.py: test_mxfp4, test_mxfp6,
+    test_mxfp8, test_mxint8); those tests need a GPU and the compiled extension, their tables
+    do not."""
+    import ast
+
+    src = (Path(ref_root) / "tests/gpu/torch/quantization/test_quantize_mxformats_cuda.py").read_text()
+    plan = {"test_mxfp4": (["e2m1"], 8), "test_mxfp6": (["e3m2", "e2m3"], 16),
+            "test_mxfp8": (["e4m3", "e5m2"], 8), "test_mxint8": (["int8"], 8)}
+    cases = {}
+    for fn in ast.parse(src).body:
+        if not isinstance(fn, ast.FunctionDef) or fn.name not in plan:
+            continue
+        fmts, block = plan[fn.name]
+        test_in, outs = None, []
+        for node in ast.walk(fn):
+            if isinstance(node, ast.Assign) and isinstance(node.targets[0], ast.Name) \
+                    and node.targets[0].id in ("test_in", "test_out"):
+                table = np.array(ast.literal_eval(node.value.args[0]), dtype=np.float32)
+                if node.targets[0].id == "test_in":
+                    test_in = table
+                else:
+                    outs.append((node.lineno, table))
+        outs = [t for _, t in sorted(outs, key=lambda p: p[0])]
+        assert test_in is not None and len(outs) == len(fmts), fn.name
+        for fmt, t in zip(fmts, outs):
+            assert t.shape == test_in.shape
+            cases[f"{fmt}_in"], cases[f"{fmt}_out"], cases[f"{fmt}_block"] = test_in, t, np.array(block)
+    assert len(cases) == 18
+    np.savez_compressed(out / "mx_known_answers.npz", **cases)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -270,12 +324,15 @@ def main():
     import_reference(args.ref)
     torch.manual_seed(0)
     fns = {"fake_int": golden_fake_int, "fake_e4m3": golden_fake_e4m3, "nvfp4": golden_nvfp4,
-           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export}
+           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export, "mxfp4": golden_mxfp4}
     for name, fn in fns.items():
         if args.only and name not in args.only.split(","):
             continue
         fn(HERE)
         print("wrote", name)
+    if not args.only or "mx_known_answers" in args.only.split(","):
+        golden_mx_known_answers(HERE, args.ref)
+        print("wrote mx_known_answers")
 
 
 if __name__ == "__main__":

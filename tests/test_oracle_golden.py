@@ -201,3 +201,66 @@ def test_export_packers_match_reference():
         assert np.array_equal(qo.fp8_quantize(w, g[f"{T}_fp8_scale"].reshape(()), T), g[f"{T}_fp8_q"]), T
         p, _, _ = qo.nvfp4_quantize(w, 16, s2=g[f"{T}_nvfp4_wsf2"][0], scales=g[f"{T}_nvfp4_wsf"])
         assert np.array_equal(p, g[f"{T}_nvfp4_packed"]), T
+
+
+# ------------------------------------------------------------------------------- MX formats ----
+MX_FMTS = ("e2m1", "e3m2", "e2m3", "e4m3", "e5m2", "int8")
+
+
+def test_mx_fake_matches_reference_known_answers():
+    """The tables of the reference's own MX tests (same tolerances as those tests use)."""
+    g = load("mx_known_answers")
+    for fmt in MX_FMTS:
+        x, want, block = g[fmt + "_in"], g[fmt + "_out"], int(g[fmt + "_block"])
+        for sign in (1.0, -1.0):
+            y = qo.mx_fake(x * np.float32(sign), block, fmt)
+            atol = 1e-8 if fmt == "e2m1" else 1e-3
+            assert np.allclose(y, want * np.float32(sign), rtol=1e-5, atol=atol), fmt
+        if fmt == "e2m1":  # the reference runs this table at blocks 8, 16 and 32
+            for b in (16, 32):
+                y = qo.mx_fake(np.tile(x, (1, b // 8)), b, fmt)
+                assert np.allclose(y, np.tile(want, (1, b // 8)), rtol=1e-5, atol=1e-8), b
+
+
+def test_minifloat_round_against_value_tables():
+    """Round-to-nearest-even against tables built from the format definitions: every value is a
+    fixed point, every midpoint goes to the neighbour with an even mantissa."""
+    for fmt in ("e2m1", "e3m2", "e2m3"):
+        ebits, mbits, bias, fmax = qo.MX_FORMATS[fmt]
+        vals = []
+        for e in range(1 << ebits):
+            for m in range(1 << mbits):
+                vals.append((m / (1 << mbits)) * 2.0 ** (1 - bias) if e == 0
+                            else (1 + m / (1 << mbits)) * 2.0 ** (e - bias))
+        vals = np.array(vals, np.float32)
+        assert vals[-1] == fmax and np.all(np.diff(vals) > 0)
+        assert np.array_equal(qo.minifloat_round(vals, fmt), vals)
+        mid = (vals[:-1] + vals[1:]) / 2
+        want = np.where(np.arange(len(mid)) % 2 == 0, vals[:-1], vals[1:])
+        assert np.array_equal(qo.minifloat_round(mid, fmt), want)
+        assert np.array_equal(qo.minifloat_round(np.nextafter(mid, np.float32(0)), fmt), vals[:-1])
+        assert np.array_equal(qo.minifloat_round(np.nextafter(mid, np.float32(1e9)), fmt), vals[1:])
+        assert qo.minifloat_round(np.float32([fmax * 4, np.inf, np.nan]), fmt).tolist() == [fmax] * 3
+
+
+def test_mx_scale_exponent_edges():
+    # exact powers of two keep their exponent, anything above moves up, 2^127 is the clamp
+    e = qo.mx_unscale_exponent(np.float32([6, 6.0000005, 12, 3, 0.75, 6 * 2.0 ** -126, 3.0e38]), "e2m1")
+    assert e.tolist() == [0, 1, 1, -1, -3, -126, 126]
+    y = qo.mx_fake(np.zeros((1, 32), np.float32), 32, "e4m3")
+    assert np.all(y == 0)
+    y = qo.mx_fake(np.float32([[np.inf] + [1.0] * 7]), 8, "e2m1")   # invalid amax: unscaled
+    assert y[0, 1:].tolist() == [1.0] * 7 and y[0, 0] == 6.0
+
+
+def test_mxfp4_qtensor_matches_reference_cpu_path():
+    g = load("mxfp4")
+    for T in TS:
+        for j in range(3):
+            k = f"{T}_{j}"
+            x, block = to_f32(g[k + "_x"], T), int(g[k + "_block"])
+            packed, scales = qo.mxfp4_quantize(x, block)
+            assert np.array_equal(packed, g[k + "_packed"]), k
+            assert np.array_equal(scales, g[k + "_scales"]), k
+            deq = qo.mxfp4_dequantize(packed, scales, block, T)
+            assert same_bits(deq, to_f32(g[k + "_deq"], T)), k
