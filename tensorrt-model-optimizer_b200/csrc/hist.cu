@@ -1,10 +1,20 @@
 // Histogram calibration: fixed-range, equal-width binning of |x| with 64-bit global counters,
 // and the percentile read-out.
 //
-// Each CTA bins into shared-memory 32-bit counters (several replicas chosen by lane, so that the
-// lanes of a warp that hit the same hot bin do not serialise on one address), then adds its
-// non-zero bins to the global 64-bit counters once.  Bins beyond the shared range go to global
-// atomics directly.  Integer sums make the result independent of the order of batches and ranks.
+// 16-bit inputs (the activations that calibration sees) have at most 32768 distinct magnitudes, so
+// a CTA first counts VALUES: the 15 magnitude bits of an element are the index of a shared 32-bit
+// counter (two bit operations and one shared reduction per element, no float arithmetic).  When
+// its share of the input is done it maps the values that occurred to bins with the exact reference
+// arithmetic (a few thousand divisions per CTA), adds them into shared bin counters and adds the
+// non-zero bins to the global 64-bit counters once.
+//
+// fp32 inputs bin directly: each CTA bins into shared-memory 32-bit counters (several replicas
+// chosen by lane, so that the lanes of a warp that hit the same hot bin do not serialise on one
+// address), then adds its non-zero bins to the global counters.  Bins beyond the shared range go
+// to global atomics directly.  Integer sums make the result independent of the order of batches
+// and ranks.
+#include <cstring>
+
 #include "numerics.cuh"
 
 namespace b200q {
@@ -89,6 +99,131 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
   }
 }
 
+// ---- 16-bit inputs: value counting -------------------------------------------------------------
+// Non-negative 16-bit floats order like their bit patterns.  With `hi` the largest pattern whose
+// value is <= range_max and `lo` a pattern whose value is <= range_max / (2 nbins) (everything at
+// or below it lands in bin 0), an element's counter index is clamp(pattern, lo, hi + 1) - lo:
+// index 0 collects all the tiny values, the last index everything beyond the range (NaN and inf
+// included), which is dropped.  That leaves about 128 * (log2(nbins) + 1) counters for bf16,
+// few enough for `1 << rshift` replicas chosen by lane: with 16 replicas the word of a counter is
+// index * 16 + lane % 16, so two lanes of a warp meet in a bank only when they are 16 apart and
+// their values have the same parity.
+constexpr int kHist16SmemWords = 227 * 1024 / 4;   // the whole shared memory of an SM
+constexpr int kHist16MaxSmemBins = 8192;
+
+struct Hist16Layout {
+  uint32_t lo, hi1;   // patterns: lower clamp, upper clamp (= hi + 1)
+  int values;         // counters per replica: hi1 - lo + 1, padded to a multiple of 4
+  int rshift;         // log2(replicas)
+  int smem_bins;      // bins with a shared counter
+};
+
+__device__ __forceinline__ void red_shared_inc(uint32_t addr) {
+  asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(1u) : "memory");
+}
+template <typename T> __device__ __forceinline__ float value_of_bits16(uint32_t idx);
+template <> __device__ __forceinline__ float value_of_bits16<__nv_bfloat16>(uint32_t idx) {
+  return __uint_as_float(idx << 16);
+}
+template <> __device__ __forceinline__ float value_of_bits16<__half>(uint32_t idx) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(idx)));
+}
+
+// sh = [values << rshift value counters][smem_bins bin counters]
+template <typename T>
+__global__ void __launch_bounds__(kHistThreads)
+hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, Hist16Layout lay,
+                      unsigned long long* __restrict__ counts) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  extern __shared__ uint32_t sh[];
+  uint4* sh4 = reinterpret_cast<uint4*>(sh);
+  const int vwords = lay.values << lay.rshift;             // a multiple of 4 (host pads `values`)
+
+  // Four packs per step, loaded one step ahead (the first step before shared memory is cleared).
+  // A pack beyond the end reads as all-ones: NaN patterns, which clamp to the dropped index.
+  const int64_t npack = n / 8;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const uint4 none = make_uint4(~0u, ~0u, ~0u, ~0u);
+  auto load4 = [&](int64_t at, uint4* v) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = at + k * stride < npack ? ld_stream(xv + at + k * stride) : none;
+  };
+  uint4 cur[4], nxt[4];
+  load4(i, cur);
+
+  for (int j = threadIdx.x; j < (vwords + lay.smem_bins + 3) / 4; j += blockDim.x) sh4[j] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  const uint32_t rmask = (1u << lay.rshift) - 1u;
+  const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(sh));
+  // byte address of counter (index, my replica) = index * (4 << rshift) + cbase
+  const uint32_t bytes_per_value = 4u << lay.rshift;
+  const uint32_t cbase = base + ((threadIdx.x & rmask) << 2) - lay.lo * bytes_per_value;
+  const uint32_t lo2 = lay.lo | (lay.lo << 16), hi2 = lay.hi1 | (lay.hi1 << 16);
+
+  auto count_word = [&](uint32_t w) {  // two elements
+    const uint32_t t = __vmaxu2(__vminu2(w & 0x7fff7fffu, hi2), lo2);
+    red_shared_inc((t & 0xffffu) * bytes_per_value + cbase);
+    red_shared_inc((t >> 16) * bytes_per_value + cbase);
+  };
+  auto count_pack = [&](const uint4& v) { count_word(v.x); count_word(v.y); count_word(v.z); count_word(v.w); };
+
+  for (; i < npack; i += 4 * stride) {
+    load4(i + 4 * stride, nxt);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) count_pack(cur[k]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - npack * 8) {
+    const uint32_t w = reinterpret_cast<const unsigned short*>(x)[npack * 8 + threadIdx.x] & 0x7fffu;
+    red_shared_inc(max(min(w, lay.hi1), lay.lo) * bytes_per_value + cbase);
+  }
+  __syncthreads();
+
+  // values -> bins with the reference arithmetic: bin = int(RN(RN(a * nbins) / range)), the right
+  // edge in the last bin.  Thread v sums the replicas of value v starting at its own lane's
+  // replica, so that the lanes of a warp read different banks.
+  uint32_t* bins = sh + vwords;
+  const float fbins = static_cast<float>(nbins);
+  const uint32_t last = static_cast<uint32_t>(nbins - 1);
+  const int in_range = static_cast<int>(lay.hi1 - lay.lo);   // index hi1 - lo holds what is out of range
+  for (int v = threadIdx.x; v < in_range; v += blockDim.x) {
+    const uint32_t* row = sh + (v << lay.rshift);
+    uint32_t c = 0;
+    for (uint32_t k = 0; k <= rmask; ++k) c += row[(k + threadIdx.x) & rmask];
+    if (c == 0) continue;
+    const float a = value_of_bits16<T>(lay.lo + v);
+    if (!(a <= range_max)) continue;   // cannot happen by construction of hi1; kept as a guard
+    const float quot = __fdiv_rn(a * fbins, range_max);
+    uint32_t b = quot < 8388608.f ? (__float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu) : last;
+    b = min(b, last);
+    if (b < static_cast<uint32_t>(lay.smem_bins)) atomicAdd(bins + b, c);
+    else atomicAdd(counts + b, static_cast<unsigned long long>(c));
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < lay.smem_bins; b += blockDim.x) {
+    const uint32_t c = bins[b];
+    if (c) atomicAdd(counts + b, static_cast<unsigned long long>(c));
+  }
+}
+
+// largest 16-bit pattern of type `dtype` whose value is <= v (v >= 0), capped at the largest finite
+static uint32_t floor_bits16(float v, int dtype) {
+  if (dtype == B200Q_BF16) {
+    uint32_t u;
+    memcpy(&u, &v, 4);
+    u >>= 16;   // truncation rounds a non-negative value down
+    return u > 0x7f7fu ? 0x7f7fu : u;
+  }
+  if (!(v < 65504.f)) return 0x7bffu;
+  const __half h = __float2half_rd(v);
+  unsigned short r;
+  memcpy(&r, &h, 2);
+  return r;
+}
+
 // One thread walks the bins in order so that the running sum rounds exactly as a sequential
 // float64 cumulative sum does.
 __global__ void hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
@@ -118,21 +253,52 @@ extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins
   if (n <= 0 || nbins <= 0) return B200Q_ERR_SHAPE;
   if (!(range_max > 0.f)) return B200Q_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // shared bins: all of them when they fit, replicated as often as the budget allows (<= 32)
+  // 32-bit shared counters: one launch bins at most 2^36 elements (< 2^32 per CTA)
+  const int64_t chunk = int64_t{1} << 36;
+  if (dtype != B200Q_F32) {
+    Hist16Layout lay;
+    lay.hi1 = floor_bits16(range_max, dtype) + 1;
+    lay.lo = floor_bits16(range_max / (2.f * static_cast<float>(nbins)), dtype);
+    if (lay.lo >= lay.hi1) lay.lo = lay.hi1 - 1;
+    lay.values = static_cast<int>(lay.hi1 - lay.lo + 1);
+    lay.values = (lay.values + 3) & ~3;   // padding counters are never addressed
+    lay.smem_bins = nbins < kHist16MaxSmemBins ? nbins : kHist16MaxSmemBins;
+    lay.rshift = 4;   // 16 replicas: 32 are conflict-free but measured no faster, and double the clearing
+    while (lay.rshift > 0 && (static_cast<int64_t>(lay.values) << lay.rshift) + lay.smem_bins + 3 > kHist16SmemWords)
+      --lay.rshift;
+    const size_t smem = ((static_cast<size_t>(lay.values) << lay.rshift) + ((lay.smem_bins + 3) & ~3)) * sizeof(uint32_t);
+    return B200Q_DISPATCH(dtype, [&]() -> int {
+      if constexpr (sizeof(T) == 2) {
+        auto kern = hist16_collect_kernel<T>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHist16SmemWords * 4) != cudaSuccess)
+          return B200Q_ERR_CUDA;
+        for (int64_t off = 0; off < n; off += chunk) {
+          const int64_t len = n - off < chunk ? n - off : chunk;
+          const int grid = grid_for(len / 8, kHistThreads * 4, 1);
+          kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x) + off, len, nbins, range_max, lay, counts);
+        }
+        return launch_status();
+      } else {
+        return B200Q_ERR_DTYPE;
+      }
+    });
+  }
+  // fp32: shared bins, all of them when they fit, replicated as often as the budget allows (<= 32)
   const int max_words = kHistSmemBytes / 4;
   int smem_bins = nbins + 1 <= max_words ? nbins : max_words - 1;
   int replicas = 1;
   while (replicas < 32 && static_cast<int64_t>(smem_bins + 1) * replicas * 2 <= max_words) replicas <<= 1;
   const size_t smem = static_cast<size_t>(smem_bins + 1) * replicas * sizeof(uint32_t);
-  return B200Q_DISPATCH(dtype, [&] {
-    auto kern = smem_bins == nbins ? hist_collect_kernel<T, true> : hist_collect_kernel<T, false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistSmemBytes) != cudaSuccess)
-      return static_cast<int>(B200Q_ERR_CUDA);
-    int grid = grid_for(n / Elem<T>::kPerPack, kHistThreads * 4, 1);
-    kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x), n, nbins, range_max, smem_bins,
+  auto kern = smem_bins == nbins ? hist_collect_kernel<float, true> : hist_collect_kernel<float, false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistSmemBytes) != cudaSuccess)
+    return B200Q_ERR_CUDA;
+  for (int64_t off = 0; off < n; off += chunk) {
+    const int64_t len = n - off < chunk ? n - off : chunk;
+    const int grid = grid_for(len / 4, kHistThreads * 4, 1);
+    kern<<<grid, kHistThreads, smem, s>>>(static_cast<const float*>(x) + off, len, nbins, range_max, smem_bins,
                                           replicas, counts);
-    return launch_status();
-  });
+  }
+  return launch_status();
 }
 
 extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,

@@ -369,6 +369,32 @@ def test_hist_collect_vs_oracle(ops, T, nbins):
     assert np.array_equal(counts.cpu().numpy(), 2 * want)
 
 
+@pytest.mark.parametrize("nbins", [2048, 1500, 30000, 120000])
+def test_hist_bin_edges_and_specials(ops, nbins):
+    """Samples on and one ulp around every bin edge, the range end, NaN, inf and every finite bf16
+    value: the bracketed bin index must fall back to the exact division wherever it matters."""
+    rng = np.random.default_rng(nbins)
+    for rmax in (np.float32(1.0), np.float32(7.3125), np.float32(rng.uniform(0.01, 300.0)), np.float32(3.0e-3)):
+        k = np.arange(nbins + 2, dtype=np.float64)
+        edges = (k * float(rmax) / nbins).astype(np.float32)
+        x = np.concatenate([edges, np.nextafter(edges, np.float32(0)), np.nextafter(edges, np.float32(1e30)),
+                            -edges, np.float32([rmax, -rmax, np.nan, np.inf, -np.inf, 0.0, -0.0, 1e-45, 1e38]),
+                            rng.uniform(0, float(rmax), 100003).astype(np.float32)])
+        counts = torch.zeros(nbins, dtype=torch.int64, device="cuda")
+        ops.hist_collect(tensor_from_f32(x, "f32"), counts, nbins, float(rmax))
+        assert np.array_equal(counts.cpu().numpy(), qo.hist_bins(x, nbins, rmax)), float(rmax)
+    pat = np.arange(65536, dtype=np.uint32)
+    vals = (pat << 16).view(np.float32)
+    h16 = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float32)
+    for rmax in (np.float32(2.0), np.float32(448.0), np.float32(rng.uniform(0.5, 50.0)), np.float32(1e-3),
+                 np.float32(7e4), np.float32(3e30)):
+        for T, v in (("bf16", vals), ("f16", h16)):
+            v = np.concatenate([v, v[: 12345]])  # a ragged length and repeated values
+            counts = torch.zeros(nbins, dtype=torch.int64, device="cuda")
+            ops.hist_collect(tensor_from_f32(v, T), counts, nbins, float(rmax))
+            assert np.array_equal(counts.cpu().numpy(), qo.hist_bins(v, nbins, rmax)), (T, float(rmax))
+
+
 def test_hist_golden_and_percentile(ops):
     g = load("hist")
     x = to_f32(g["x0"], "bf16")
