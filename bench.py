@@ -470,6 +470,168 @@ def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
             "api": "b200q.pipeline.HostNvFp4Packer.pack (pinned host weights -> pinned host NVFP4)"}
 
 
+# ---------------------------------------------------------------- 70B-shape calibration --------
+L70 = {"hidden": 8192, "kv": 1024, "inter": 28672, "layers": 80}
+
+
+def run_calib70b(args):
+    """Data-parallel NVFP4 activation calibration on Llama-3-70B shapes, then the NVFP4 weight
+    quantisation of this rank's layers.
+
+    Every linear's input quantiser (7 per layer) is a TensorQuantizer with a 2048-bin
+    HistogramCalibrator.  The forward GEMMs that would produce the activations are not part of
+    this path, so each kind of activation (attention input, o_proj input, MLP input, down_proj
+    input) is one seeded synthetic buffer of [tokens, dim] per rank (larger than L2), fed
+    ``--batches`` times per layer.  Steps: first-batch abs-max of every quantiser -> one
+    broadcast fixes the common bin width -> histogram collection -> one SUM all-reduce of all
+    histograms (plus a MAX of their lengths) -> percentile amax on every rank -> NVFP4 weight
+    quantisation of the rank's share of the layers.  Activation work per rank is fixed (weak
+    scaling in the batch dimension), weight work is split by layer.
+    """
+    import torch
+    import torch.distributed as dist
+
+    from b200q import dist as qdist
+    from b200q.nn import TensorQuantizer
+    from b200q.ops import NvFp4Group
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the kernels)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_layers = args.layers if args.layers != N_LAYERS else L70["layers"]
+    tokens, batches = args.tokens, args.batches
+    H, KV, I = L70["hidden"], L70["kv"], L70["inter"]
+    kinds = [("attn_in", H, ("q_proj", "k_proj", "v_proj")), ("o_in", H, ("o_proj",)),
+             ("mlp_in", H, ("gate_proj", "up_proj")), ("down_in", I, ("down_proj",))]
+    acts = {}
+    for k, (name, dim, _) in enumerate(kinds):
+        g = torch.Generator(device=dev).manual_seed(50_000 + 16 * rank + k)
+        ch = torch.exp(torch.randn(dim, generator=g, device=dev))          # lognormal(0,1) channel magnitudes
+        acts[name] = (torch.randn(tokens, dim, generator=g, device=dev) * ch).bfloat16()
+    qcfg = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
+            "axis": None, "enable": True, "calibrator": "histogram"}
+    model = torch.nn.ModuleDict()
+    for l in range(n_layers):
+        for _, _, lins in kinds:
+            for lin in lins:
+                q = TensorQuantizer(dict(qcfg))
+                q.disable_quant(); q.enable_calib()
+                model[f"l{l}_{lin}"] = q
+    n_quant = len(model)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def phase(fn):
+        barrier()
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = t.item()
+        return dt
+
+    from b200q import ops
+    for name in acts:           # warm-up: kernels, and the communicator's collectives
+        for _ in range(3):
+            ops.amax_tensor(acts[name])
+    if world > 1:
+        for op in (dist.ReduceOp.MAX, dist.ReduceOp.SUM):
+            for _ in range(3):
+                dist.all_reduce(torch.zeros(1 << 20, dtype=torch.int64, device=dev), op=op)
+        dist.broadcast(torch.zeros(1024, device=dev), src=0)
+    first = {}
+
+    def ranges():
+        for l in range(n_layers):
+            for name, _, lins in kinds:
+                for lin in lins:
+                    first[f"l{l}_{lin}"] = ops.amax_tensor(acts[name])
+        vals = torch.stack(list(first.values())).tolist()      # one device->host copy
+        qdist.agree_histogram_ranges(model, dict(zip(first.keys(), vals)), dev)
+
+    def collect():
+        for l in range(n_layers):
+            for _ in range(batches):
+                for name, _, lins in kinds:
+                    for lin in lins:
+                        model[f"l{l}_{lin}"](acts[name])
+
+    def exchange():
+        qdist.sync_histograms(model)
+
+    def readout():
+        for q in model.values():
+            q.load_calib_amax("percentile", percentile=99.99)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_wall0 = time.perf_counter()
+    t_ranges = phase(ranges)
+    t_collect = phase(collect)
+    t_exchange = phase(exchange)
+    t_readout = phase(readout)
+
+    # weights of one layer, reused for every layer of this rank's share
+    shapes = [(H, H), (KV, H), (KV, H), (H, H), (I, H), (I, H), (H, I)]
+    my_layers = split_layers(n_layers, world, rank)
+    weights = [make_weight(sh, 7000 + k, dev) for k, sh in enumerate(shapes)]
+    group = NvFp4Group(weights)
+    group.run()
+
+    def quantize():
+        for _ in my_layers:
+            group.run()
+
+    t_weights = phase(quantize)
+    t_wall1 = time.perf_counter()
+    clocks = sampler.stop(t_wall0, t_wall1)
+    amaxes = torch.stack([q._amax.float().reshape(()) for q in model.values()])
+    same = True
+    if world > 1:
+        lo, hi = amaxes.clone(), amaxes.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool(torch.equal(lo, hi))
+    if rank == 0:
+        peak, which = peaks()
+        elems_per_pass = n_layers * batches * tokens * (6 * H + I)        # per rank
+        act_bytes = world * elems_per_pass * 2                              # one binning pass over bf16
+        w_elems = n_layers * sum(a * b for a, b in shapes)
+        total = t_ranges + t_collect + t_exchange + t_readout + t_weights
+        print(json.dumps({
+            "metric": "nvfp4_calibration_70b_shape_seconds", "value": total, "unit": "s", "n_gpus": world,
+            "higher_is_better": False, "scaling": "weak (activation batches per rank fixed); weights split by layer",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama3-70b-shape NVFP4 calibration: 2048-bin histogram of every linear input, "
+                                   "percentile 99.99 amax, then NVFP4 weight quantisation",
+                       "layers": n_layers, "quantizers": n_quant, "tokens_per_batch": tokens,
+                       "batches_per_rank_per_layer": batches,
+                       "full_size_note": "the named configuration is 4096x1024 tokens over 8 GPUs = 64 batches of "
+                                         "8192 tokens per rank per layer"},
+            "seconds": {"ranges": t_ranges, "collect": t_collect, "exchange": t_exchange, "readout": t_readout,
+                        "weights": t_weights},
+            "collect_gbps_all_ranks": act_bytes / t_collect / 1e9,
+            "collect_frac_of_peak_per_gpu": act_bytes / world / t_collect / 1e9 / peak,
+            "weights_gbps_all_ranks": w_elems * BYTES_TOTAL / t_weights / 1e9,
+            "collectives": {"broadcast": 1, "all_reduce": 2, "histogram_bytes": n_quant * 2048 * 8},
+            "amax_identical_on_all_ranks": same, "amax_range": [float(amaxes.min()), float(amaxes.max())],
+            "peak_source": f"of {which}", "clocks": clocks,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -481,6 +643,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-formats", action="store_true")
+    ap.add_argument("--workload", default="ptq8b", choices=["ptq8b", "calib70b"],
+                    help="ptq8b: NVFP4 weight quantisation on 8B shapes (the headline line); "
+                         "calib70b: data-parallel histogram calibration on 70B shapes")
+    ap.add_argument("--tokens", type=int, default=8192, help="calib70b: tokens per batch")
+    ap.add_argument("--batches", type=int, default=2, help="calib70b: batches per rank per layer")
     ap.add_argument("--profile-kernels", action="store_true",
                     help="run a few launches of the secondary kernels and exit (for ncu captures)")
     args = ap.parse_args()
@@ -489,6 +656,8 @@ def main():
         run_profile_kernels()
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload == "calib70b":
+        run_calib70b(args)
     else:
         run_b200(args)
 

@@ -206,6 +206,15 @@ int b200q_int8_quantize(const void* x, const void* scales, int8_t* q, int64_t ou
 int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
                        unsigned long long* counts, void* stream);
 
+/* Open-ended collection for a calibrator whose range grows: bins continue past nbins - 1 at the
+ * same width (range_max / nbins) up to `capacity` bins, so that later batches with larger values
+ * need neither a new range nor a host round trip.  Samples beyond capacity bins, NaN and inf are
+ * not binned; their number is added to *overflow.  counts has room for `capacity` bins.
+ * Stands in for the range-extension branch of HistogramCalibrator.collect
+ * (modelopt/torch/quantization/calib/histogram.py:119-130). */
+int b200q_hist_collect_open(const void* x, int64_t n, int dtype, int nbins, float range_max, int capacity,
+                            unsigned long long* counts, unsigned long long* overflow, void* stream);
+
 /* *amax_out = edge of the first bin whose cumulative share (float64 running sum of count/total)
  * reaches percentile/100: edges[i] when edges (fp32 [nbins+1]) is given, else bin_width*i.
  * Replaces _compute_amax_percentile (calib/histogram.py:328-343). */

@@ -342,6 +342,23 @@ def hist_bins(x: np.ndarray, nbins: int, range_max) -> np.ndarray:
     return np.bincount(b, minlength=nbins).astype(np.int64)
 
 
+def hist_bins_open(x: np.ndarray, nbins: int, range_max, capacity: int):
+    """Open-ended variant of hist_bins: bin width range_max / nbins, bins continue to `capacity`;
+    returns (int64 counts [capacity], number of samples beyond the last bin or not finite).
+    Same arithmetic as the reference applies after it has extended its range
+    (modelopt/torch/quantization/calib/histogram.py:119-130), with the first batch's (nbins, range)."""
+    a = np.abs(np.asarray(x, dtype=F32)).reshape(-1)
+    rm = F32(range_max)
+    cap_range = F32(np.float64(rm) * capacity / nbins) if capacity != nbins else rm
+    with np.errstate(invalid="ignore"):
+        ok = a <= cap_range
+    beyond = int((~ok).sum())
+    a = a[ok]
+    b = ((a * F32(nbins)).astype(F32) / rm).astype(F32).astype(np.int64)
+    b = np.where(a <= rm, np.minimum(b, nbins - 1), np.minimum(b, capacity - 1))
+    return np.bincount(b, minlength=capacity).astype(np.int64), beyond
+
+
 class HistogramOracle:
     """HistogramCalibrator.collect with torch_hist=True (calib/histogram.py:77-130) — range set by
     the first batch, later batches extend the bin count at the first batch's width."""

@@ -1,10 +1,14 @@
 """Histogram calibrator (reference: modelopt/torch/quantization/calib/histogram.py:35-343).
 
-``collect`` keeps the reference's range rules — the first batch fixes the bin width
-(max / num_bins), later batches that exceed the range extend the number of bins at that width —
-but runs as two single-pass kernels (abs-max, then binning of |x| into 64-bit device counters)
-instead of the abs / float / max / histc chain.  Integer counters make the result independent of
-batch order and summable across data-parallel ranks (``b200q.dist.sync_histograms``).
+The reference fixes the bin width with the first batch (max / num_bins) and, when a later batch
+exceeds the range, extends the number of bins at that width before binning it.  Here the first
+batch fixes the width the same way (one abs-max pass), and every batch is binned by ONE kernel
+into an open-ended histogram of ``CAPACITY_FACTOR * num_bins`` 64-bit device counters of that
+width: a larger later batch simply lands in higher bins, with no range pass and no host round
+trip per batch.  How many bins are live (the reference's ``_num_bins``) is read from the counters
+when they are needed.  Samples beyond the capacity, NaN and inf are counted apart and make the
+read-out raise.  Integer counters make the result independent of batch order and summable across
+data-parallel ranks (``b200q.dist.sync_histograms``).
 
 ``compute_amax`` offers "percentile" (on the GPU), and "entropy" / "mse" on the host from the
 copied counts.  "mse" follows the algorithm the reference documents (minimise the count-weighted
@@ -26,6 +30,8 @@ __all__ = ["HistogramCalibrator", "calibrate_weights"]
 
 
 class HistogramCalibrator(_Calibrator):
+    CAPACITY_FACTOR = 16   # later batches may reach 16x the first batch's maximum
+
     def __init__(self, num_bits=8, axis=None, unsigned=False, num_bins=2048, grow_method=None,
                  skip_zeros=False, torch_hist=True):
         super().__init__(num_bits, axis, unsigned)
@@ -33,53 +39,92 @@ class HistogramCalibrator(_Calibrator):
             raise NotImplementedError("Calibrator histogram collection only supports per tensor scaling")
         if skip_zeros:
             raise NotImplementedError("skip_zeros is not supported by the CUDA histogram")
-        self._num_bins = num_bins
+        self._init_bins = num_bins     # bins of the first batch's range
+        self._num_bins = num_bins      # live bins (grows; refreshed by _resolve)
         self._calib_hist = None        # int64 [capacity] on the device; first _num_bins are live
         self._calib_bin_edges = None   # fp32 [_num_bins + 1] on the device
-        self._width = None             # python float, fixed by the first batch (or by set_range)
+        self._range0 = None            # python float: right edge of bin _init_bins - 1
+        self._overflow = None          # int64 [1] on the device
+        self._stale = False            # counters changed since _num_bins was last read from them
 
     # ---- range management ------------------------------------------------------------------
     def set_range(self, x_max: float, device):
-        """Fix the histogram range before the first batch (used to give all data-parallel ranks
-        the same bin width)."""
+        """Fix the bin width (x_max / num_bins) before the first batch — also the way all
+        data-parallel ranks get the same width."""
         assert self._calib_hist is None, "range already set"
-        self._calib_hist = torch.zeros(self._num_bins, dtype=torch.int64, device=device)
-        self._calib_bin_edges = torch.linspace(0, x_max, self._num_bins + 1, device=device)
-        self._width = float(self._calib_bin_edges[1] - self._calib_bin_edges[0])
+        self._calib_hist = torch.zeros(self._init_bins * self.CAPACITY_FACTOR, dtype=torch.int64, device=device)
+        self._overflow = torch.zeros(1, dtype=torch.int64, device=device)
+        self._calib_bin_edges = torch.linspace(0, x_max, self._init_bins + 1, device=device)
+        self._range0 = float(self._calib_bin_edges[-1])
+        self._num_bins = self._init_bins
 
-    def _grow(self, x_max_t: torch.Tensor):
-        width = self._calib_bin_edges[1] - self._calib_bin_edges[0]
-        self._num_bins = int((x_max_t / width).ceil().item())
-        self._calib_bin_edges = torch.arange(0, float(x_max_t + width), float(width),
-                                             device=self._calib_hist.device, dtype=torch.float32)
-        if self._calib_hist.numel() < self._num_bins:
-            bigger = torch.zeros(max(self._num_bins, 2 * self._calib_hist.numel()), dtype=torch.int64,
-                                 device=self._calib_hist.device)
-            bigger[: self._calib_hist.numel()] = self._calib_hist
-            self._calib_hist = bigger
+    @property
+    def _width(self):
+        return None if self._calib_bin_edges is None else float(self._calib_bin_edges[1] - self._calib_bin_edges[0])
+
+    def _resolve(self):
+        """Bring ``_num_bins`` / ``_calib_bin_edges`` up to date with the device counters."""
+        if not self._stale:
+            return
+        self._stale = False
+        # one device->host copy: the overflow count and the number of live bins past _num_bins
+        tail = self._calib_hist[self._num_bins:]
+        if tail.numel():
+            live = ((tail != 0) * torch.arange(1, tail.numel() + 1, device=tail.device)).max()
+        else:
+            live = torch.zeros((), dtype=torch.int64, device=self._calib_hist.device)
+        overflow, live = torch.stack([self._overflow[0], live]).tolist()
+        if overflow > 0:
+            raise RuntimeError(
+                f"HistogramCalibrator: {overflow} samples were NaN, inf or beyond "
+                f"{self.CAPACITY_FACTOR}x the range of the first batch ({self._range0}); they were not binned.")
+        if live:
+            n = self._num_bins + live
+            width = self._calib_bin_edges[1] - self._calib_bin_edges[0]
+            self._calib_bin_edges = torch.arange(n + 1, device=self._calib_hist.device, dtype=torch.float32) * width
+            self._num_bins = n
+
+    def _load_counts(self, counts: torch.Tensor):
+        """Replace the live counters (used after a cross-rank sum); bins beyond stay empty."""
+        n = counts.numel()
+        if n > self._num_bins:
+            width = self._calib_bin_edges[1] - self._calib_bin_edges[0]
+            self._calib_bin_edges = torch.arange(n + 1, device=counts.device, dtype=torch.float32) * width
+            self._num_bins = n
+        if self._calib_hist.numel() < n:
+            self._calib_hist = torch.zeros(n, dtype=torch.int64, device=counts.device)
+        self._calib_hist.zero_()
+        self._calib_hist[:n] = counts
+        self._stale = False
 
     @torch.no_grad()
     def collect(self, x):
         x = x.detach()
-        x_max_t = ops.amax_tensor(x)
         if self._calib_hist is None:
-            self.set_range(float(x_max_t), x.device)
-        elif bool(x_max_t > self._calib_bin_edges[-1]):
-            self._grow(x_max_t)
-        ops.hist_collect(x, self._calib_hist, self._num_bins, float(self._calib_bin_edges[-1]))
+            self.set_range(float(ops.amax_tensor(x)), x.device)
+        ops.hist_collect_open(x, self._calib_hist, self._init_bins, self._range0, self._overflow)
+        self._stale = True
 
     def reset(self):
         self._calib_bin_edges = None
         self._calib_hist = None
+        self._overflow = None
+        self._range0 = None
+        self._num_bins = self._init_bins
+        self._stale = False
 
     # ---- read-out -------------------------------------------------------------------------------
     @property
     def hist(self):
-        return None if self._calib_hist is None else self._calib_hist[: self._num_bins]
+        if self._calib_hist is None:
+            return None
+        self._resolve()
+        return self._calib_hist[: self._num_bins]
 
     def compute_amax(self, method: str, *, stride: int = 1, start_bin: int = 128, percentile: float = 99.99):
         if self._calib_hist is None:
             return None
+        self._resolve()
         if method == "percentile":
             if percentile < 0 or percentile > 100:
                 raise ValueError("Invalid percentile. Must be in range 0 <= percentile <= 100.")

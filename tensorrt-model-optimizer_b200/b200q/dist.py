@@ -98,6 +98,8 @@ def sync_histograms(model: nn.Module, group=None) -> int:
     if not cals or not (dist.is_available() and dist.is_initialized()):
         return 0
     dev = cals[0][1]._calib_hist.device
+    for _, c in cals:
+        c._resolve()
     lens = torch.tensor([c._num_bins for _, c in cals], dtype=torch.int64, device=dev)
     dist.all_reduce(lens, op=dist.ReduceOp.MAX, group=group)
     lens = lens.tolist()
@@ -109,10 +111,6 @@ def sync_histograms(model: nn.Module, group=None) -> int:
     dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
     off = 0
     for (_, c), n in zip(cals, lens):
-        if n != c._num_bins:
-            width = c._calib_bin_edges[1] - c._calib_bin_edges[0]
-            c._calib_bin_edges = torch.arange(n + 1, device=dev, dtype=torch.float32) * width
-            c._num_bins = n
-        c._calib_hist = flat[off:off + n].clone()
+        c._load_counts(flat[off:off + n])
         off += n
     return 2

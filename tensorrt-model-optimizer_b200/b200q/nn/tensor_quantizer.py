@@ -230,8 +230,10 @@ class TensorQuantizer(nn.Module):
         attr_value = attr_value if attr_value is not None else getattr(self, attr_name, None)
         if attr_value is None or (isinstance(attr_value, torch.Tensor) and attr_value.is_meta):
             return True
-        bad = bool(torch.any(attr_value < 0)) if attr_name == "_amax" else False
-        bad = bad or bool(torch.any(torch.isinf(attr_value) | torch.isnan(attr_value)))
+        flags = torch.isinf(attr_value) | torch.isnan(attr_value)
+        if attr_name == "_amax":
+            flags = flags | (attr_value < 0)
+        bad = bool(torch.any(flags))   # one device->host read
         if bad:
             msg = f"{name} {attr_name} contains invalid values: {attr_value}"
             if raise_error:

@@ -350,6 +350,19 @@ def hist_collect(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_max: f
     return counts
 
 
+def hist_collect_open(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_max: float,
+                      overflow: torch.Tensor):
+    """counts (int64 [capacity]) += histogram of |x| with bin width range_max / nbins, open-ended: bins
+    run on past nbins - 1 up to counts.numel(); samples beyond that (and NaN / inf) add to overflow."""
+    x = _prep(x)
+    assert counts.dtype == torch.int64 and counts.is_cuda and counts.numel() >= nbins
+    assert overflow.dtype == torch.int64 and overflow.is_cuda and overflow.numel() >= 1
+    with torch.cuda.device(x.device):
+        call("b200q_hist_collect_open", x.data_ptr(), x.numel(), dtype_code(x), nbins, ctypes.c_float(range_max),
+             counts.numel(), counts.data_ptr(), overflow.data_ptr(), _stream(x))
+    return counts
+
+
 def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None, width: float,
                     percentile: float) -> torch.Tensor:
     out = torch.empty((), dtype=torch.float32, device=counts.device)

@@ -28,10 +28,20 @@ constexpr int kHistSmemBytes = 200 * 1024;   // shared-memory budget for the rep
 // the normal case for activations, whose range is set by a few outliers — neither collide on an
 // address nor on a bank.
 // kAllShared: every bin has a shared counter (the usual case), so no global-atomic path is compiled.
+//
+// Open-ended collection: bins continue past nbins - 1 at the same width up to `capacity` bins
+// (range `cap_range`); what lies beyond that, NaN and inf are not binned but counted in
+// `*overflow` when that is given.  capacity == nbins is the closed histogram of torch.histc.
+struct HistOpen {
+  int capacity;
+  float cap_range;
+  unsigned long long* overflow;
+};
+
 template <typename T, bool kAllShared>
 __global__ void __launch_bounds__(kHistThreads)
-hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, int smem_bins,
-                    int replicas, unsigned long long* __restrict__ counts) {
+hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
+                    int smem_bins, int replicas, unsigned long long* __restrict__ counts) {
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   extern __shared__ uint32_t sh[];
@@ -49,12 +59,16 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
 
   // a = |x| (non-negative); quot = RN(a * nbins / range_max) < 2^22: its integer part is read from
   // the low mantissa bits after a round-toward-zero add of 2^23 (no float->int conversion)
+  const uint32_t cap_last = static_cast<uint32_t>(open.capacity - 1);
+  uint32_t beyond = 0;
   auto count = [&](float a, float quot) {
     uint32_t b = __float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu;
-    b = min(b, last);
-    if (a <= range_max) {  // false for out-of-range values and NaN: not counted
+    if (a <= open.cap_range) {  // false for values beyond the last bin and for NaN
+      b = min(b, a <= range_max ? last : cap_last);
       if (kAllShared || b < static_cast<uint32_t>(smem_bins)) atomicAdd(mine + b, 1u);
       else atomicAdd(counts + b, 1ull);
+    } else {
+      ++beyond;
     }
   };
   auto bin_pair = [&](float a0, float a1) {
@@ -97,6 +111,9 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
     for (int r = 0; r < replicas; ++r) c += sh[r * stride_r + b];
     if (c) atomicAdd(counts + b, c);
   }
+  beyond = __reduce_add_sync(0xffffffffu, beyond);
+  if (open.overflow != nullptr && beyond != 0 && (threadIdx.x & 31) == 0)
+    atomicAdd(open.overflow, static_cast<unsigned long long>(beyond));
 }
 
 // ---- 16-bit inputs: value counting -------------------------------------------------------------
@@ -132,23 +149,22 @@ template <> __device__ __forceinline__ float value_of_bits16<__half>(uint32_t id
 // sh = [values << rshift value counters][smem_bins bin counters]
 template <typename T>
 __global__ void __launch_bounds__(kHistThreads)
-hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, Hist16Layout lay,
-                      unsigned long long* __restrict__ counts) {
+hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
+                      Hist16Layout lay, unsigned long long* __restrict__ counts) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
   extern __shared__ uint32_t sh[];
   uint4* sh4 = reinterpret_cast<uint4*>(sh);
   const int vwords = lay.values << lay.rshift;             // a multiple of 4 (host pads `values`)
 
   // Four packs per step, loaded one step ahead (the first step before shared memory is cleared).
-  // A pack beyond the end reads as all-ones: NaN patterns, which clamp to the dropped index.
   const int64_t npack = n / 8;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const uint4 none = make_uint4(~0u, ~0u, ~0u, ~0u);
   auto load4 = [&](int64_t at, uint4* v) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = at + k * stride < npack ? ld_stream(xv + at + k * stride) : none;
+    for (int k = 0; k < 4; ++k)
+      if (at + k * stride < npack) v[k] = ld_stream(xv + at + k * stride);
   };
   uint4 cur[4], nxt[4];
   load4(i, cur);
@@ -172,7 +188,8 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   for (; i < npack; i += 4 * stride) {
     load4(i + 4 * stride, nxt);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) count_pack(cur[k]);
+    for (int k = 0; k < 4; ++k)
+      if (i + k * stride < npack) count_pack(cur[k]);
 #pragma unroll
     for (int k = 0; k < 4; ++k) cur[k] = nxt[k];
   }
@@ -187,7 +204,7 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   // replica, so that the lanes of a warp read different banks.
   uint32_t* bins = sh + vwords;
   const float fbins = static_cast<float>(nbins);
-  const uint32_t last = static_cast<uint32_t>(nbins - 1);
+  const uint32_t last = static_cast<uint32_t>(nbins - 1), cap_last = static_cast<uint32_t>(open.capacity - 1);
   const int in_range = static_cast<int>(lay.hi1 - lay.lo);   // index hi1 - lo holds what is out of range
   for (int v = threadIdx.x; v < in_range; v += blockDim.x) {
     const uint32_t* row = sh + (v << lay.rshift);
@@ -195,12 +212,16 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
     for (uint32_t k = 0; k <= rmask; ++k) c += row[(k + threadIdx.x) & rmask];
     if (c == 0) continue;
     const float a = value_of_bits16<T>(lay.lo + v);
-    if (!(a <= range_max)) continue;   // cannot happen by construction of hi1; kept as a guard
+    if (!(a <= open.cap_range)) continue;   // cannot happen by construction of hi1; kept as a guard
     const float quot = __fdiv_rn(a * fbins, range_max);
-    uint32_t b = quot < 8388608.f ? (__float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu) : last;
-    b = min(b, last);
+    uint32_t b = quot < 8388608.f ? (__float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu) : cap_last;
+    b = min(b, a <= range_max ? last : cap_last);
     if (b < static_cast<uint32_t>(lay.smem_bins)) atomicAdd(bins + b, c);
     else atomicAdd(counts + b, static_cast<unsigned long long>(c));
+  }
+  if (open.overflow != nullptr && threadIdx.x <= rmask) {   // the index that holds what is out of range
+    const uint32_t c = sh[(in_range << lay.rshift) + threadIdx.x];
+    if (c) atomicAdd(open.overflow, static_cast<unsigned long long>(c));
   }
   __syncthreads();
   for (int b = threadIdx.x; b < lay.smem_bins; b += blockDim.x) {
@@ -224,45 +245,81 @@ static uint32_t floor_bits16(float v, int dtype) {
   return r;
 }
 
-// One thread walks the bins in order so that the running sum rounds exactly as a sequential
-// float64 cumulative sum does.
-__global__ void hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
-                                       const float* __restrict__ edges, float bin_width,
-                                       double frac, float* __restrict__ amax_out) {
-  if (blockIdx.x != 0 || threadIdx.x != 0) return;
-  unsigned long long total = 0;
-  for (int i = 0; i < nbins; ++i) total += counts[i];
-  const double dt = static_cast<double>(total);
-  double cdf = 0.0;
-  int idx = nbins;
-  for (int i = 0; i < nbins; ++i) {
-    cdf += static_cast<double>(counts[i]) / dt;
-    if (cdf >= frac) { idx = i; break; }
+// Percentile read-out.  The quotients count / total are formed by all threads; one thread then adds
+// them in bin order, so that the running sum rounds exactly as a sequential float64 cumulative sum.
+constexpr int kPctThreads = 1024;
+constexpr int kPctChunk = 4096;   // quotients staged per round (32 KB of shared memory)
+
+__global__ void __launch_bounds__(kPctThreads)
+hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
+                       const float* __restrict__ edges, float bin_width, double frac,
+                       float* __restrict__ amax_out) {
+  __shared__ double q[kPctChunk];
+  __shared__ unsigned long long warp_sums[kPctThreads / 32];
+  __shared__ unsigned long long total_s;
+  __shared__ double cdf_s;
+  __shared__ int idx_s;
+  unsigned long long part = 0;
+  for (int i = threadIdx.x; i < nbins; i += blockDim.x) part += counts[i];
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long t = 0;
+    for (int w = 0; w < kPctThreads / 32; ++w) t += warp_sums[w];
+    total_s = t; cdf_s = 0.0; idx_s = -1;
   }
-  *amax_out = edges ? edges[idx] : bin_width * static_cast<float>(idx);
+  __syncthreads();
+  const double dt = static_cast<double>(total_s);
+  for (int base = 0; base < nbins; base += kPctChunk) {
+    const int len = min(kPctChunk, nbins - base);
+    for (int i = threadIdx.x; i < len; i += blockDim.x) q[i] = static_cast<double>(counts[base + i]) / dt;
+    __syncthreads();
+    if (threadIdx.x == 0 && idx_s < 0) {
+      double cdf = cdf_s;
+      for (int i = 0; i < len; ++i) {
+        cdf += q[i];
+        if (cdf >= frac) { idx_s = base + i; break; }
+      }
+      cdf_s = cdf;
+    }
+    __syncthreads();
+    if (idx_s >= 0) break;
+  }
+  if (threadIdx.x == 0) {
+    const int idx = idx_s < 0 ? nbins : idx_s;
+    *amax_out = edges ? edges[idx] : bin_width * static_cast<float>(idx);
+  }
 }
 
 }  // namespace b200q
 
 using namespace b200q;
 
-extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
-                                  unsigned long long* counts, void* stream) {
+static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, float range_max, int capacity,
+                             unsigned long long* counts, unsigned long long* overflow, void* stream) {
   B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(counts);
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x);
-  if (n <= 0 || nbins <= 0) return B200Q_ERR_SHAPE;
+  if (n <= 0 || nbins <= 0 || capacity < nbins || capacity > (1 << 22)) return B200Q_ERR_SHAPE;
   if (!(range_max > 0.f)) return B200Q_ERR_ARG;
+  HistOpen open;
+  open.capacity = capacity;
+  // right end of the last bin; for the closed histogram exactly range_max
+  open.cap_range = capacity == nbins ? range_max
+                                     : static_cast<float>(static_cast<double>(range_max) * capacity / nbins);
+  if (!(open.cap_range < 3.0e38f)) return B200Q_ERR_ARG;
+  open.overflow = overflow;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // 32-bit shared counters: one launch bins at most 2^36 elements (< 2^32 per CTA)
   const int64_t chunk = int64_t{1} << 36;
   if (dtype != B200Q_F32) {
     Hist16Layout lay;
-    lay.hi1 = floor_bits16(range_max, dtype) + 1;
+    lay.hi1 = floor_bits16(open.cap_range, dtype) + 1;
     lay.lo = floor_bits16(range_max / (2.f * static_cast<float>(nbins)), dtype);
     if (lay.lo >= lay.hi1) lay.lo = lay.hi1 - 1;
     lay.values = static_cast<int>(lay.hi1 - lay.lo + 1);
     lay.values = (lay.values + 3) & ~3;   // padding counters are never addressed
-    lay.smem_bins = nbins < kHist16MaxSmemBins ? nbins : kHist16MaxSmemBins;
+    lay.smem_bins = capacity < kHist16MaxSmemBins ? capacity : kHist16MaxSmemBins;
     lay.rshift = 4;   // 16 replicas: 32 are conflict-free but measured no faster, and double the clearing
     while (lay.rshift > 0 && (static_cast<int64_t>(lay.values) << lay.rshift) + lay.smem_bins + 3 > kHist16SmemWords)
       --lay.rshift;
@@ -275,7 +332,7 @@ extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins
         for (int64_t off = 0; off < n; off += chunk) {
           const int64_t len = n - off < chunk ? n - off : chunk;
           const int grid = grid_for(len / 8, kHistThreads * 4, 1);
-          kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x) + off, len, nbins, range_max, lay, counts);
+          kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x) + off, len, nbins, range_max, open, lay, counts);
         }
         return launch_status();
       } else {
@@ -289,16 +346,28 @@ extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins
   int replicas = 1;
   while (replicas < 32 && static_cast<int64_t>(smem_bins + 1) * replicas * 2 <= max_words) replicas <<= 1;
   const size_t smem = static_cast<size_t>(smem_bins + 1) * replicas * sizeof(uint32_t);
-  auto kern = smem_bins == nbins ? hist_collect_kernel<float, true> : hist_collect_kernel<float, false>;
+  auto kern = smem_bins == capacity ? hist_collect_kernel<float, true> : hist_collect_kernel<float, false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHistSmemBytes) != cudaSuccess)
     return B200Q_ERR_CUDA;
   for (int64_t off = 0; off < n; off += chunk) {
     const int64_t len = n - off < chunk ? n - off : chunk;
     const int grid = grid_for(len / 4, kHistThreads * 4, 1);
-    kern<<<grid, kHistThreads, smem, s>>>(static_cast<const float*>(x) + off, len, nbins, range_max, smem_bins,
+    kern<<<grid, kHistThreads, smem, s>>>(static_cast<const float*>(x) + off, len, nbins, range_max, open, smem_bins,
                                           replicas, counts);
   }
   return launch_status();
+}
+
+extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
+                                  unsigned long long* counts, void* stream) {
+  return hist_collect_impl(x, n, dtype, nbins, range_max, nbins, counts, nullptr, stream);
+}
+
+extern "C" int b200q_hist_collect_open(const void* x, int64_t n, int dtype, int nbins, float range_max,
+                                       int capacity, unsigned long long* counts, unsigned long long* overflow,
+                                       void* stream) {
+  B200Q_REQUIRE_PTR(overflow);
+  return hist_collect_impl(x, n, dtype, nbins, range_max, capacity, counts, overflow, stream);
 }
 
 extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,
@@ -307,7 +376,7 @@ extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins
   B200Q_REQUIRE_PTR(counts); B200Q_REQUIRE_PTR(amax_out);
   if (nbins <= 0) return B200Q_ERR_SHAPE;
   if (!(percentile >= 0.0 && percentile <= 100.0)) return B200Q_ERR_ARG;
-  hist_percentile_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  hist_percentile_kernel<<<1, kPctThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       counts, nbins, edges, bin_width, percentile / 100.0, amax_out);
   return launch_status();
 }

@@ -187,20 +187,17 @@ def _hist_job(rank, world):
         assert abs(float(c._calib_bin_edges[-1]) - (1.0 + i)) < 1e-6     # rank 0's value everywhere
         nb = 2048 + (300 * rank if i == 1 else 0)                          # rank 1 grew one histogram
         h = torch.from_numpy(rng.integers(0, 1000, nb))
-        c._calib_hist, c._num_bins = h.clone(), nb
-        if nb != 2048:
-            w = c._calib_bin_edges[1] - c._calib_bin_edges[0]
-            c._calib_bin_edges = torch.arange(nb + 1, dtype=torch.float32) * w
+        c._load_counts(h.clone())
         mine.append(h)
     assert mtq.dist.sync_histograms(m) == 2
     for i, (n, c) in enumerate(cals):
         nb = 2048 + (300 if i == 1 else 0)
-        assert c._num_bins == nb and c._calib_hist.numel() == nb and c._calib_bin_edges.numel() == nb + 1
+        assert c._num_bins == nb and c.hist.numel() == nb and c._calib_bin_edges.numel() == nb + 1
         pad = torch.zeros(nb, dtype=torch.int64)
         pad[: mine[i].numel()] = mine[i]
         gathered = [torch.zeros_like(pad) for _ in range(world)]
         dist.all_gather(gathered, pad)
-        assert torch.equal(c._calib_hist, sum(gathered)), n
+        assert torch.equal(c.hist, sum(gathered)), n
 
 
 def test_sync_histograms_two_gloo_ranks():

@@ -395,6 +395,29 @@ def test_hist_bin_edges_and_specials(ops, nbins):
             assert np.array_equal(counts.cpu().numpy(), qo.hist_bins(v, nbins, rmax)), (T, float(rmax))
 
 
+@pytest.mark.parametrize("T", TS)
+def test_hist_collect_open_vs_oracle(ops, T):
+    """Open-ended collection: later, larger batches land in bins past the first range; what is
+    beyond the capacity, NaN and inf are counted apart."""
+    nbins, cap = 2048, 2048 * 16
+    x0 = rnd((1 << 18,), T, 11, 1.0, heavy=True)
+    rmax = float(np.abs(x0).max())
+    counts = torch.zeros(cap, dtype=torch.int64, device="cuda")
+    over = torch.zeros(1, dtype=torch.int64, device="cuda")
+    want = np.zeros(cap, np.int64)
+    beyond = 0
+    for i, scale in enumerate((1.0, 3.0, 12.0, 40.0)):
+        x = rnd((1 << 18,) if i else x0.shape, T, 11 + i, scale, heavy=True) if i else x0
+        x = x.copy()
+        x[5] = np.nan; x[77] = np.inf; x[78] = -np.inf
+        ops.hist_collect_open(tensor_from_f32(x, T), counts, nbins, rmax, over)
+        w, b = qo.hist_bins_open(x, nbins, np.float32(rmax), cap)
+        want += w; beyond += b
+        assert np.array_equal(counts.cpu().numpy(), want), scale
+        assert int(over) == beyond
+    assert beyond > 3 * 4 and want[nbins:].sum() > 0
+
+
 def test_hist_golden_and_percentile(ops):
     g = load("hist")
     x = to_f32(g["x0"], "bf16")
