@@ -249,6 +249,17 @@ int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double
 int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
                          int64_t k, double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* awq_clip block search.  w [rows, cols], x [ntok, cols] (the sampled calibration tokens) and
+ * w_amax [rows * cols/block] (block abs-max, row-major) in `dtype`; ratios: nratios (<= 15) clip ratios
+ * in device memory, fp32.  For every ratio r, row and block:
+ *   loss[r][row][blk] += mean over tokens of float(T(cur - org))^2, where org / cur are the block's
+ *   partial dot products T(sum_j T(x*w)) with the weights as they are / fake quantised (integer,
+ *   num_bits) with block amax T(amax * ratio_r).  loss is fp32 [nratios, rows, cols/block], device.
+ * Replaces the per-ratio loop of _clip_search (modelopt/torch/quantization/model_calib.py:875-915). */
+int b200q_awq_clip_loss(const void* w, const void* x, const void* w_amax, const float* ratios, int nratios,
+                        float* loss, int64_t rows, int64_t cols, int block, int ntok, int dtype,
+                        int num_bits, int is_unsigned, int narrow_range, void* stream);
+
 /* ---------------------------------------------------------------- MX (E8M0-scaled) formats -- */
 
 /* element formats of b200q_mx_fake (numbering of the reference's Types enum) */

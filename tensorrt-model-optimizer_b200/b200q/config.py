@@ -9,6 +9,7 @@ from typing import Any
 
 __all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG",
            "INT4_BLOCKWISE_WEIGHT_ONLY_CFG", "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG",
+           "INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG",
            "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG",
            "choices", "need_calibration"]
 
@@ -96,6 +97,21 @@ NVFP4_AWQ_LITE_CFG = {
     "algorithm": "awq_lite",
 }
 
+INT8_SMOOTHQUANT_CFG = {
+    "quant_cfg": {"*weight_quantizer": {"num_bits": 8, "axis": 0}, "*input_quantizer": {"num_bits": 8, "axis": None},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": "smoothquant",
+}
+
+_nvfp4 = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}, "axis": None,
+          "enable": True}
+NVFP4_AWQ_CLIP_CFG = {"quant_cfg": {"*weight_quantizer": dict(_nvfp4), "*input_quantizer": dict(_nvfp4),
+                                    **_default_disabled_quantizer_cfg}, "algorithm": {"method": "awq_clip"}}
+NVFP4_AWQ_FULL_CFG = {"quant_cfg": {"*weight_quantizer": dict(_nvfp4), "*input_quantizer": dict(_nvfp4),
+                                    **_default_disabled_quantizer_cfg},
+                      "algorithm": {"method": "awq_full", "alpha_step": 0.1}}
+
+
 def _mx(num_bits):
     return {"num_bits": num_bits, "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (8, 0)}, "enable": True}
 
@@ -109,7 +125,7 @@ MXFP4_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx((2, 1)), "*input_qua
 MXINT8_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx(8), "*input_quantizer": _mx(8),
                                     **_default_disabled_quantizer_cfg}, "algorithm": None}
 
-choices = {"MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG","INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
+choices = {"INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG", "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG","INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
            "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG"}
 
 

@@ -20,7 +20,7 @@ from . import ops
 from .calib import MseCalibrator
 from .nn import QuantModule, SequentialQuantizer, TensorQuantizer, is_quantized_linear
 
-__all__ = ["max_calibrate", "mse_calibrate", "awq_lite", "awq", "enable_stats_collection", "finish_stats_collection",
+__all__ = ["max_calibrate", "mse_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection",
            "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]
 
 
@@ -334,10 +334,189 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
             delattr(m, "awq_lite")
 
 
+# --------------------------------------------------------------------------------- AWQ clip ----
+
+class _AWQClipState:
+    """Search state of one linear layer (reference model_calib.py:807-849)."""
+
+    def __init__(self, module, min_clip_ratio, shrink_step):
+        self.num_tokens = 0
+        self.block_size = _awq_block_size(module.weight, module.weight_quantizer)
+        wq = module.weight_quantizer
+        wq.reset_amax()
+        enable_stats_collection(wq)
+        wq(module.weight)
+        finish_stats_collection(wq)
+        self.w_amax = wq.amax.clone()
+        self.ratios = [round(float(k), 2) for k in torch.arange(min_clip_ratio, 1.0, shrink_step)] + [1.0]
+        co, ci = module.weight.shape
+        dev = module.weight.device
+        self.per_tensor = self._is_per_tensor_clip(wq)
+        if self.per_tensor:
+            self.loss_t = torch.zeros(len(self.ratios), dtype=torch.float32, device=dev)
+        else:
+            if ci % self.block_size:
+                raise NotImplementedError("awq_clip: in_features must be a multiple of the block size")
+            self.loss_t = torch.zeros((len(self.ratios), co, ci // self.block_size), dtype=torch.float32, device=dev)
+            self.ratios_t = torch.tensor(self.ratios, dtype=torch.float32, device=dev)
+        self.best_clip_val = None
+        self.best_loss = None
+        self.is_input_quantized = module.input_quantizer.is_enabled
+        wq.disable()
+
+    @staticmethod
+    def _is_per_tensor_clip(q):
+        bs = q.block_sizes
+        dynamic_per_tensor = bs is not None and bs.get("type", None) == "dynamic" and q.axis is None
+        return dynamic_per_tensor or (q.axis is None and bs is None)
+
+    @property
+    def loss(self):
+        """{clip ratio: loss} like the reference's dictionary."""
+        return {r: self.loss_t[i] for i, r in enumerate(self.ratios)}
+
+
+def _clip_search(module, st, inputs, max_tokens):
+    wq = module.weight_quantizer
+    wq.enable()
+    if st.per_tensor:
+        # only the per-tensor amax is clipped (NVFP4): whole-layer output error per ratio
+        x2 = inputs.reshape(-1, inputs.shape[-1])
+        out_actual = F.linear(x2, module.weight)
+        original = wq.amax.clone()
+        st.num_tokens += inputs.shape[0]
+        for i, shrink in enumerate(st.ratios):
+            wq.amax = original * shrink
+            out = F.linear(x2, wq(module.weight))
+            st.loss_t[i] += ops.mse_loss(out, out_actual)
+        wq.amax = original
+        return
+    x2 = inputs.reshape(-1, inputs.shape[-1])
+    x2 = x2[0:: max(1, x2.shape[0] // max_tokens)].contiguous()
+    st.num_tokens += x2.shape[0]
+    ops.awq_clip_loss(module.weight, x2.to(module.weight.dtype), st.w_amax, st.ratios_t, st.loss_t,
+                      st.block_size, wq._num_bits, wq._unsigned, wq._narrow_range)
+
+
+def _awq_clip_forward(self, input, *args, **kwargs):
+    st = self.awq_clip
+    if st.is_input_quantized:
+        self.input_quantizer.enable()
+        max_calibrate(self.input_quantizer, lambda q: q(input), distributed_sync=False)
+        self.input_quantizer.disable()
+    _clip_search(self, st, self.input_quantizer(input), st.max_tokens)
+    self.weight_quantizer.disable()
+    return self._forward_no_awq(input, *args, **kwargs)
+
+
+@torch.no_grad()
+def awq_clip(model: nn.Module, forward_loop, max_co_batch_size: int = 1024, max_tokens_per_batch: int = 64,
+             min_clip_ratio: float = 0.5, shrink_step: float = 0.05, debug: bool = False, **kwargs):
+    """AWQ-clip (reference model_calib.py:788-997): per weight block, pick the clip ratio of the
+    block amax whose fake-quantised block changes the block's partial outputs least on a sample
+    of the calibration tokens.  ``max_co_batch_size`` (the reference's memory knob) is accepted
+    and unused: the search kernel never materialises the per-ratio products."""
+    assert forward_loop is not None, "forward_loop must be provided for awq_clip"
+    layers = []
+    for name, m in model.named_modules():
+        if is_quantized_linear(m) and m.weight_quantizer.is_enabled and m.weight_quantizer.block_sizes is not None:
+            wq = m.weight_quantizer
+            if not isinstance(wq._num_bits, int) and not _AWQClipState._is_per_tensor_clip(wq):
+                raise NotImplementedError("awq_clip: block-wise search is built for integer weight formats")
+            st = _AWQClipState(m, min_clip_ratio, shrink_step)
+            st.max_tokens = max_tokens_per_batch
+            m.awq_clip = st
+            m.__dict__["_forward_no_awq"] = m.forward
+            m.__dict__["forward"] = _awq_clip_forward.__get__(m, type(m))
+            layers.append((name, m))
+    enable_stats_collection(model)
+    forward_loop(model)
+    max_calibrate(model, lambda mod: None)
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    for name, m in layers:
+        st = m.awq_clip
+        del m.__dict__["forward"]
+        del m.__dict__["_forward_no_awq"]
+        if st.num_tokens > 0:
+            if world > 1 and not st.per_tensor:   # the reference averages every block loss over the DP group
+                dist.all_reduce(st.loss_t, op=dist.ReduceOp.SUM)
+                st.loss_t /= world
+            best_loss = torch.full_like(st.w_amax, float("inf"), dtype=torch.float32)
+            best_clip = torch.zeros_like(st.w_amax)
+            for i, shrink in enumerate(st.ratios):
+                loss = st.loss_t[i].reshape(st.w_amax.shape)
+                better = loss < best_loss
+                best_loss = torch.where(better, loss, best_loss)
+                best_clip = torch.where(better, st.w_amax * shrink, best_clip)
+            st.best_loss, st.best_clip_val = best_loss, best_clip
+            m.weight_quantizer.amax = best_clip
+            m.weight_quantizer.enable()
+            if st.is_input_quantized:
+                m.input_quantizer.enable()
+        if not debug:
+            delattr(m, "awq_clip")
+
+
+# --------------------------------------------------------------------------------- SmoothQuant --
+
+@torch.no_grad()
+def smoothquant(model: nn.Module, forward_loop=None, alpha: float = 1.0):
+    """SmoothQuant for INT8 linears (reference model_calib.py:411-496): per-input-channel activation
+    amax from a max calibration with ``axis=-1``, smoothing scale
+    ``s = w_max^(1-alpha) / a_max^alpha`` folded into the weight (and its inverse into the input
+    quantiser's pre-quant scale), then per-tensor activation quantisation."""
+    assert forward_loop is not None, "forward_loop must be provided for smoothquant"
+    from .utils import reduce_amax
+
+    for _, m in model.named_modules():
+        if is_quantized_linear(m) and m.input_quantizer.is_enabled and m.input_quantizer.axis is None:
+            m.input_quantizer.axis = -1
+    max_calibrate(model, forward_loop)
+    smoothed = 0
+    for name, m in model.named_modules():
+        if not is_quantized_linear(m):
+            continue
+        iq, wq = m.input_quantizer, m.weight_quantizer
+        if not hasattr(iq, "_amax"):
+            warnings.warn(f"{name} is not calibrated, skip smoothing")
+            continue
+        if iq.num_bits != 8 or wq.num_bits != 8:
+            warnings.warn(f"Only int8 smoothing is supported, skip {name}")
+            continue
+        if iq.axis != -1:
+            warnings.warn(f"Only per-channel smoothing is supported, skip {name}")
+            continue
+        assert iq._amax.numel() > 1, f"Error: {name} has only one channel to smooth"
+        act_amax = iq.amax.float()
+        weight_scale = reduce_amax(m.weight, axis=0, keepdims=True)
+        dev, dt = m.weight.device, m.weight.dtype
+        scale_a = (weight_scale.pow(1 - alpha) / act_amax.pow(alpha)).squeeze()
+        iq._amax_for_smoothing = act_amax.cpu()
+        iq.reset_amax()
+        iq.axis = None
+        iq.amax = act_amax.amax().to(dtype=dt, device=dev)
+        epsilon = 1.0 / (1 << 31)
+        if scale_a.min() <= epsilon:   # channels that never fired
+            scale_a[(act_amax <= epsilon).reshape(scale_a.shape)] = 1
+        scale_a = scale_a.clamp(min=1e-4, max=1e4)
+        apply_pre_quant_scale_and_smooth(m, scale_a)
+        smoothed += 1
+    return smoothed
+
+
 def awq(model, forward_loop=None, algorithm="awq_lite", **kwargs):
-    """AWQ entry point (reference model_calib.py:499-526); only the lite search is built."""
-    if algorithm not in ("awq_lite",):
+    """AWQ entry point (reference model_calib.py:499-526): ``awq_lite``, ``awq_clip`` or
+    ``awq_full`` (lite, then clip)."""
+    if algorithm not in ("awq_lite", "awq_clip", "awq_full"):
         raise NotImplementedError(f"AWQ variant {algorithm!r} is outside the accelerated path")
+    lite_kw = {k: v for k, v in kwargs.items() if k in ("alpha_step", "debug")}
+    clip_kw = {k: v for k, v in kwargs.items()
+               if k in ("max_co_batch_size", "max_tokens_per_batch", "min_clip_ratio", "shrink_step", "debug")}
     with SequentialQuantizer.convert_to_single_quantizer(model):
-        awq_lite(model, forward_loop, **kwargs)
-    max_calibrate(model, lambda m: None)
+        if algorithm in ("awq_full", "awq_lite"):
+            awq_lite(model, forward_loop, **lite_kw)
+        if algorithm in ("awq_full", "awq_clip"):
+            awq_clip(model, forward_loop, **clip_kw)
+    for _, m in model.named_modules():
+        if is_quantized_linear(m) and isinstance(m.weight_quantizer, SequentialQuantizer):
+            max_calibrate(m, lambda lin: lin.weight_quantizer(lin.weight), distributed_sync=False)

@@ -8,20 +8,29 @@ import torch
 from torch import nn
 
 from .conversion import convert_to_quantized_model, set_quantizer_attribute
-from .model_calib import awq, max_calibrate, mse_calibrate
+from .model_calib import awq, max_calibrate, mse_calibrate, smoothquant
 from .nn import QuantLinear, RealQuantLinear, SequentialQuantizer, TensorQuantizer
 from .qtensor import pack_real_quantize_weight
 
 __all__ = ["quantize", "calibrate", "compress", "disable_quantizer", "enable_quantizer",
            "print_quant_summary", "fold_weight", "modelopt_state"]
 
-_ALGORITHMS = {"max": max_calibrate, "mse": mse_calibrate, "awq_lite": awq}
+def _awq_variant(variant):
+    def run(model, forward_loop=None, **opts):
+        return awq(model, forward_loop, algorithm=variant, **opts)
+    return run
+
+
+_ALGORITHMS = {"max": max_calibrate, "mse": mse_calibrate, "smoothquant": smoothquant,
+               "awq_lite": _awq_variant("awq_lite"), "awq_clip": _awq_variant("awq_clip"),
+               "awq_full": _awq_variant("awq_full")}
 
 
 def calibrate(model: nn.Module, algorithm="max", forward_loop=None) -> nn.Module:
     """Run a calibration algorithm on a converted model.
 
-    ``algorithm``: ``"max"``, ``"awq_lite"``, ``None`` (skip), or a dict
+    ``algorithm``: ``"max"``, ``"mse"``, ``"smoothquant"``, ``"awq_lite"``, ``"awq_clip"``,
+    ``"awq_full"``, ``None`` (skip), or a dict
     ``{"method": name, **options}``.  ``forward_loop(model)`` must push the calibration data
     through the model; it may be called more than once."""
     if algorithm is None:
@@ -36,9 +45,9 @@ def calibrate(model: nn.Module, algorithm="max", forward_loop=None) -> nn.Module
                                   f"(built: {sorted(_ALGORITHMS)})")
     was_training = model.training
     model.eval()
-    fn(model, forward_loop, **opts) if algorithm != "max" else fn(model, forward_loop, **opts)
+    fn(model, forward_loop, **opts)
     model.train(was_training)
-    _record_mode(model, f"{algorithm}_calibrate" if algorithm != "awq_lite" else "awq_lite_calibrate")
+    _record_mode(model, f"{algorithm}_calibrate")
     return model
 
 

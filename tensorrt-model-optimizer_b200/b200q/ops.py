@@ -468,3 +468,26 @@ def mxfp4_quantize(x: torch.Tensor, block: int = 32):
         call("b200q_mxfp4_quantize", x.data_ptr(), n // block, block, dtype_code(x), packed.data_ptr(),
              scales.data_ptr(), _stream(x))
     return packed, scales
+
+
+# --------------------------------------------------------------------------- awq_clip ----------
+
+def awq_clip_loss(w: torch.Tensor, x: torch.Tensor, w_amax: torch.Tensor, ratios: torch.Tensor,
+                  loss: torch.Tensor, block: int, num_bits: int = 4, unsigned: bool = False,
+                  narrow_range: bool = False) -> torch.Tensor:
+    """loss[r, row, blk] (fp32, CUDA) += block-wise output error of clipping the block amax to
+    ``w_amax * ratios[r]`` (see ``b200q_awq_clip_loss``).  w [rows, cols], x [tokens, cols], w_amax
+    [rows * cols / block] share one dtype; ratios is an fp32 CUDA tensor."""
+    w, x = _prep(w), _prep(x)
+    w_amax = _prep(w_amax.to(w.dtype))
+    rows, cols = w.shape
+    assert x.dim() == 2 and x.shape[1] == cols and x.dtype == w.dtype
+    assert w_amax.numel() == rows * (cols // block)
+    assert ratios.dtype == torch.float32 and ratios.is_cuda and ratios.is_contiguous()
+    assert loss.dtype == torch.float32 and loss.is_cuda and loss.is_contiguous()
+    assert loss.numel() == ratios.numel() * rows * (cols // block)
+    with torch.cuda.device(w.device):
+        call("b200q_awq_clip_loss", w.data_ptr(), x.data_ptr(), w_amax.data_ptr(), ratios.data_ptr(),
+             ratios.numel(), loss.data_ptr(), rows, cols, block, x.shape[0], dtype_code(w), num_bits,
+             int(unsigned), int(narrow_range), _stream(w))
+    return loss

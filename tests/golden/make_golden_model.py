@@ -127,15 +127,74 @@ def golden_flows(mtq, out):
     np.savez_compressed(out / "flows.npz", **cases)
 
 
+def golden_clip_smooth(mtq, out):
+    """awq_clip / awq_full on INT4 block-32 weights (losses per clip ratio and block, the chosen
+    block amax) and INT8 smoothquant (pre-quant scale, smoothed weight, amax buffers)."""
+    cases = {}
+    for tag, dtype in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        batches = make_batches(32, 2, dtype, tokens=80)      # 80 tokens: the sampler keeps every token
+        for i, b in enumerate(batches):
+            cases[f"{tag}_x{i}"] = bits(b)
+
+        def loop(m):
+            for b in batches:
+                m(b)
+
+        for method in ("awq_clip", "awq_full"):
+            model = make_model(31, dtype)
+            if method == "awq_clip":
+                cases[f"{tag}_w_up"] = bits(model.up_proj.weight)
+                cases[f"{tag}_w_down"] = bits(model.down_proj.weight)
+            cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+            cfg["quant_cfg"]["*weight_quantizer"]["block_sizes"] = {-1: 32, "type": "static"}
+            cfg["algorithm"] = {"method": method, "debug": True, "max_tokens_per_batch": 32}
+            if method == "awq_full":
+                cfg["algorithm"]["alpha_step"] = 0.1
+            mtq.quantize(model, cfg, loop)
+            for name in ("up_proj", "down_proj"):
+                lin = getattr(model, name)
+                st = lin.awq_clip
+                k = f"{tag}_{method}_{name}"
+                cases[k + "_ratios"] = np.array(list(st.loss.keys()), dtype=np.float64)
+                cases[k + "_losses"] = np.stack([v.float().numpy() for v in st.loss.values()])
+                cases[k + "_w_amax"] = bits(st.w_amax)
+                cases[k + "_best_clip"] = bits(lin.weight_quantizer._amax)
+                cases[k + "_num_tokens"] = np.array(st.num_tokens)
+                if method == "awq_full":
+                    cases[k + "_pqs"] = bits(lin.input_quantizer._pre_quant_scale)
+                    cases[k + "_best_alpha"] = np.array(lin.awq_lite.best_alpha, dtype=np.float64)
+            cases[f"{tag}_{method}_y"] = bits(model(batches[0]))
+
+        model = make_model(31, dtype)
+        mtq.quantize(model, copy.deepcopy(mtq.INT8_SMOOTHQUANT_CFG), loop)
+        for name in ("up_proj", "down_proj"):
+            lin = getattr(model, name)
+            k = f"{tag}_sq_{name}"
+            cases[k + "_pqs"] = bits(lin.input_quantizer._pre_quant_scale)
+            cases[k + "_in_amax"] = bits(lin.input_quantizer._amax.reshape(-1))
+            cases[k + "_w_amax"] = bits(lin.weight_quantizer._amax.reshape(-1))
+            cases[k + "_w"] = bits(lin.weight)
+            cases[k + "_amax_for_smoothing"] = lin.input_quantizer._amax_for_smoothing.float().numpy()
+        cases[f"{tag}_sq_y"] = bits(model(batches[0]))
+    np.savez_compressed(out / "clip_smooth.npz", **cases)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--only", default="")
     args = ap.parse_args()
     mtq = import_reference(args.ref)
+    if args.only == "clip_smooth":
+        golden_clip_smooth(mtq, HERE)
+        print("wrote clip_smooth")
+        return
     golden_awq(mtq, HERE)
     print("wrote awq")
     golden_flows(mtq, HERE)
     print("wrote flows")
+    golden_clip_smooth(mtq, HERE)
+    print("wrote clip_smooth")
 
 
 if __name__ == "__main__":
