@@ -30,13 +30,16 @@ awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restr
     // column of this lane's first pack: (block index within its row) * packs per block + lane offset
     uint32_t rowq, colblk;
     blocks_per_row.divmod(static_cast<uint32_t>(valid ? (t >> lane_shift) : 0), rowq, colblk);   // nblocks < 2^31
-    const uint32_t spack = (colblk * lanes + static_cast<uint32_t>(t & (lanes - 1))) * PPL;
+    // lane l of a block takes packs l, l + lanes, ...: whole sectors per load instruction
+    const uint32_t spack = colblk * lanes * PPL + static_cast<uint32_t>(t & (lanes - 1));
+    const int64_t wpack = (t >> lane_shift) * (lanes * PPL) + (t & (lanes - 1));
+    const int pstride = lanes;
     float v[PPL][P];
     uint32_t bits = 0;
 #pragma unroll
     for (int p = 0; p < PPL; ++p) {
-      uint4 a = valid ? ld_stream(wv + t * PPL + p) : make_uint4(0, 0, 0, 0);
-      uint4 b = valid ? __ldg(sv + spack + p) : make_uint4(0, 0, 0, 0);
+      uint4 a = valid ? ld_stream(wv + wpack + p * pstride) : make_uint4(0, 0, 0, 0);
+      uint4 b = valid ? __ldg(sv + spack + p * pstride) : make_uint4(0, 0, 0, 0);
       if constexpr (std::is_same<T, __nv_bfloat16>::value) {
         // packed bf16 multiply = the product rounded to bf16, two elements per instruction
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
@@ -68,7 +71,7 @@ awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restr
 #pragma unroll
       for (int p = 0; p < PPL; ++p) {
         intq_apply_n<P>(v[p], sc, q);
-        st_stream(yv + t * PPL + p, E::pack(v[p]));
+        st_stream(yv + wpack + p * pstride, E::pack(v[p]));
       }
     }
   }
@@ -128,7 +131,7 @@ extern "C" int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, i
     constexpr int P = Elem<T>::kPerPack;
     const int packs = block / P;
     if (block % P || packs <= 0 || (packs & (packs - 1)) || packs > 64) return B200Q_ERR_UNSUPPORTED;
-    const int ppl = packs >= 2 ? 2 : 1;
+    const int ppl = packs >= 4 ? 4 : packs >= 2 ? 2 : 1;
     const int lanes = packs / ppl;
     const int64_t nblocks = rows * (cols / block);
     if (nblocks > kFastDivLimit) return B200Q_ERR_UNSUPPORTED;
@@ -137,7 +140,8 @@ extern "C" int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, i
     const T* wp = static_cast<const T*>(w);
     const T* sp = static_cast<const T*>(s);
     T* yp = static_cast<T*>(y);
-    if (ppl == 2) awq_scale_fq_kernel<T, 2><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
+    if (ppl == 4) awq_scale_fq_kernel<T, 4><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
+    else if (ppl == 2) awq_scale_fq_kernel<T, 2><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
     else awq_scale_fq_kernel<T, 1><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
     return launch_status();
   });

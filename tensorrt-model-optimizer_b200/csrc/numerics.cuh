@@ -157,8 +157,9 @@ __device__ __forceinline__ float2 intq_apply2_fast(float2 x, const IntScale& s, 
   r.x = fmax_nan(fmin_nan(rintf(t.x), q.bound), q.lo);
   r.y = fmax_nan(fmin_nan(rintf(t.y), q.bound), q.lo);
   float2 o = div2_rn_rcp(r, make_float2(-s.scale, -s.scale), make_float2(s.y, s.y));
-  o.x = (r.x == 0.f) ? r.x : o.x;
-  o.y = (r.y == 0.f) ? r.y : o.y;
+  // the quotient has the sign of the rounded value (scale > 0); only a zero quotient can have lost it
+  o.x = __uint_as_float(__float_as_uint(o.x) | (__float_as_uint(r.x) & 0x80000000u));
+  o.y = __uint_as_float(__float_as_uint(o.y) | (__float_as_uint(r.y) & 0x80000000u));
   return o;
 }
 // N (even) elements in place
