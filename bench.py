@@ -421,14 +421,24 @@ def run_profile_kernels():
     counts = torch.zeros(2048, dtype=torch.int64, device=dev)
     amax = ops.amax_tensor(x)
     rmax = float(amax)
+    counts_open = torch.zeros(2048 * 16, dtype=torch.int64, device=dev)
+    overflow = torch.zeros(1, dtype=torch.int64, device=dev)
+    xs = a[:64].contiguous()                                    # awq_clip: 64 sampled tokens
+    w_amax = w.reshape(n, k // 128, 128).abs().amax(-1).reshape(-1, 1)
+    ratios = torch.tensor([0.5 + 0.05 * i for i in range(10)] + [1.0], device=dev)
+    clip_loss = torch.zeros(11, n, k // 128, device=dev)
     for i in range(4):
         wfq = ops.awq_scale_fake_int(w, s, 128, 4, False, False)
         ops.awq_gemm_sqerr(a, wfq, ref, acc, status)
         ops.hist_collect(x[i % 2], counts, 2048, rmax)
+        ops.hist_collect_open(x[i % 2], counts_open, 2048, rmax / 4, overflow)
         ops.fake_e4m3(x[i % 2], amax)
         ops.nvfp4_fake(x[i % 2], amax)
         ops.fake_int_rows_dynamic(w32[i % 2], 8, False, True)
         ops.int4_quantize(w.reshape(-1), 128)
+        ops.mx_fake(x[i % 2], 32, (4, 3))
+        ops.mxfp4_quantize(x[i % 2], 32)
+        ops.awq_clip_loss(w, xs, w_amax, ratios, clip_loss, 128, 4, False, False)
     torch.cuda.synchronize()
     print(json.dumps({"profile_kernels": "done", "gemm_status": int(status)}))
 

@@ -249,6 +249,18 @@ int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double
 int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
                          int64_t k, double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* NVFP4 with a block size other than 16 (any even size; NVFP4QTensor.quantize and
+ * dynamic_block_quant take the block size as an argument, modelopt/torch/quantization/qtensor/
+ * nvfp4_tensor.py:142-232, tensor_quant.py:158-198).  Same arithmetic and argument meaning as
+ * b200q_nvfp4_quantize / _fake / _dequantize; one thread per block, no alignment requirement. */
+int b200q_nvfp4_quantize_blocks(const void* x, int64_t nblocks, int block, int dtype, const float* global,
+                                const uint8_t* scales_in, uint8_t* packed, uint8_t* scales, float* s2_out,
+                                int flags, void* stream);
+int b200q_nvfp4_fake_blocks(const void* x, void* y, int64_t nblocks, int block, int dtype, const float* amax,
+                            void* stream);
+int b200q_nvfp4_dequantize_blocks(const uint8_t* packed, const uint8_t* scales, const float* s2, void* y,
+                                  int64_t nblocks, int block, int dtype, void* stream);
+
 /* awq_clip block search.  w [rows, cols], x [ntok, cols] (the sampled calibration tokens) and
  * w_amax [rows * cols/block] (block abs-max, row-major) in `dtype`; ratios: nratios (<= 15) clip ratios
  * in device memory, fp32.  For every ratio r, row and block:

@@ -54,6 +54,9 @@ SIGNATURES = {
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],
     "b200q_int4_export_pack": [_p, _p, _i, _p, _i64, _i64, _i, _i, _p],
+    "b200q_nvfp4_quantize_blocks": [_p, _i64, _i, _i, _p, _p, _p, _p, _p, _i, _p],
+    "b200q_nvfp4_fake_blocks": [_p, _p, _i64, _i, _i, _p, _p],
+    "b200q_nvfp4_dequantize_blocks": [_p, _p, _p, _p, _i64, _i, _i, _p],
     "b200q_awq_clip_loss": [_p, _p, _p, _p, _i, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _p],
     "b200q_mx_fake": [_p, _p, _i64, _i, _i, _i, _p],
     "b200q_mxfp4_quantize": [_p, _i64, _i, _i, _p, _p, _p],

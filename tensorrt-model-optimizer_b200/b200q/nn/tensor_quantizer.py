@@ -270,21 +270,41 @@ class TensorQuantizer(nn.Module):
             self._block_sizes = None
 
     def _setup_for_blockquant(self, inputs):
+        """Static block quantisation = per-row quantisation of a [blocks, block elements] view.
+        Blocks along the last dimension only are a plain reshape; blocks over several dimensions
+        (e.g. 2-D tiles) go through a permuted copy (reference tensor_quantizer.py:705-780)."""
         if hasattr(self, "_block_reshape_size"):
             return
-        axes = QuantizerAttributeConfig._get_block_quant_axes_and_sizes(self._block_sizes)
-        last = self._block_sizes.get(inputs.dim() - 1) or self._block_sizes.get(-1)
-        if not (last and len(axes) == 1):
-            raise NotImplementedError("static block quantisation is built for a single last-dimension block size")
-        self._original_shape = inputs.shape
-        rem = inputs.shape[-1] % last
-        if rem:
-            self._padding = (0, last - rem)
-            self._slices = (*(slice(None),) * (inputs.dim() - 1), slice(inputs.shape[-1]))
-            self._original_shape = F.pad(inputs, self._padding, "constant", 0).shape
+        nd = inputs.dim()
+        sizes = {(k if k >= 0 else k + nd): v for k, v in self._block_sizes.items() if isinstance(k, int) and v}
+        if not sizes:
+            raise ValueError("block_sizes holds no block dimension")
         self.axis = (0,)
-        self._block_reshape_size = torch.Size((-1, last))
-        self._amax_shape_for_export = (*inputs.shape[:-1], -1)
+        if list(sizes) == [nd - 1]:
+            last = sizes[nd - 1]
+            self._original_shape = inputs.shape
+            rem = inputs.shape[-1] % last
+            if rem:
+                self._padding = (0, last - rem)
+                self._slices = (*(slice(None),) * (nd - 1), slice(inputs.shape[-1]))
+                self._original_shape = F.pad(inputs, self._padding, "constant", 0).shape
+            self._block_reshape_size = torch.Size((-1, last))
+            self._amax_shape_for_export = (*inputs.shape[:-1], -1)
+            return
+        blocks = [sizes.get(d, 1) for d in range(nd)]
+        pads = [(-n) % b for n, b in zip(inputs.shape, blocks)]
+        if any(pads):
+            self._padding = tuple(v for p in reversed(pads) for v in (0, p))
+            self._slices = tuple(slice(n) for n in inputs.shape)
+        padded = [n + p for n, p in zip(inputs.shape, pads)]
+        self._original_shape = torch.Size(padded)
+        self._nd_split = [v for n, b in zip(padded, blocks) for v in (n // b, b)]      # [n0/b0, b0, n1/b1, b1, ..]
+        self._nd_perm = [2 * d for d in range(nd)] + [2 * d + 1 for d in range(nd)]   # outer dims, then blocks
+        block_elems = 1
+        for b in blocks:
+            block_elems *= b
+        self._block_reshape_size = torch.Size((-1, block_elems))
+        self._amax_shape_for_export = tuple(n // b for n, b in zip(padded, blocks))
 
     def _process_for_blockquant(self, inputs):
         if hasattr(self, "_padding"):
@@ -292,9 +312,15 @@ class TensorQuantizer(nn.Module):
         if inputs.shape != self._original_shape:
             raise ValueError(f"Input shape has changed from {self._original_shape} to {inputs.shape}."
                              " Block-quantization requires a fixed input shape.")
+        if hasattr(self, "_nd_split"):
+            inputs = inputs.reshape(self._nd_split).permute(self._nd_perm).contiguous()
         return inputs.reshape(self._block_reshape_size)
 
     def _reset_to_original_shape(self, outputs):
+        if hasattr(self, "_nd_split"):
+            permuted = [self._nd_split[i] for i in self._nd_perm]
+            inverse = [self._nd_perm.index(i) for i in range(len(self._nd_perm))]
+            outputs = outputs.reshape(permuted).permute(inverse)
         outputs = outputs.reshape(self._original_shape)
         if hasattr(self, "_slices"):
             outputs = outputs[self._slices]

@@ -162,18 +162,18 @@ def fake_e4m3(x: torch.Tensor, amax: torch.Tensor | None) -> torch.Tensor:
 # --------------------------------------------------------------------------- NVFP4 -------------
 
 def nvfp4_quantize(x: torch.Tensor, amax: torch.Tensor | None = None, scale2: torch.Tensor | None = None,
-                   scales_in: torch.Tensor | None = None):
-    """x [..., K] with K % 16 == 0 -> (packed uint8 [..., K/2], scales float8_e4m3fn [..., K/16],
+                   scales_in: torch.Tensor | None = None, block: int = 16):
+    """x [..., K] with K % block == 0 -> (packed uint8 [..., K/2], scales float8_e4m3fn [..., K/block],
     scale2 fp32 0-dim).  ``amax`` (any float dtype, 1 element) or ``scale2`` may be given; with
-    neither the tensor's own abs-max is used."""
-    x = _prep(x, 32)
+    neither the tensor's own abs-max is used.  block 16 (the format's own) runs the fast kernels."""
+    x = _prep(x, 32 if block == 16 else 16)
     K = x.shape[-1]
-    if K % 16:
-        raise ValueError("last dimension must be a multiple of 16 (pad first)")
-    nblocks = x.numel() // 16
+    if K % block or block % 2:
+        raise ValueError(f"last dimension must be a multiple of the (even) block size {block} (pad first)")
+    nblocks = x.numel() // block
     dev = x.device
     packed = torch.empty((*x.shape[:-1], K // 2), dtype=torch.uint8, device=dev)
-    scales = torch.empty((*x.shape[:-1], K // 16), dtype=torch.uint8, device=dev)
+    scales = torch.empty((*x.shape[:-1], K // block), dtype=torch.uint8, device=dev)
     s2 = torch.empty((), dtype=torch.float32, device=dev)
     flags = 0
     if scale2 is not None:
@@ -188,38 +188,51 @@ def nvfp4_quantize(x: torch.Tensor, amax: torch.Tensor | None = None, scale2: to
         sin = _cuda(scales_in, "scales_in").contiguous().view(torch.uint8)
         assert sin.numel() == nblocks
     with torch.cuda.device(dev):
-        call("b200q_nvfp4_quantize", x.data_ptr(), nblocks, dtype_code(x), glob.data_ptr(),
-             sin.data_ptr() if sin is not None else None, packed.data_ptr(), scales.data_ptr(),
-             s2.data_ptr(), flags, _stream(x))
+        if block == 16:
+            call("b200q_nvfp4_quantize", x.data_ptr(), nblocks, dtype_code(x), glob.data_ptr(),
+                 sin.data_ptr() if sin is not None else None, packed.data_ptr(), scales.data_ptr(),
+                 s2.data_ptr(), flags, _stream(x))
+        else:
+            call("b200q_nvfp4_quantize_blocks", x.data_ptr(), nblocks, block, dtype_code(x), glob.data_ptr(),
+                 sin.data_ptr() if sin is not None else None, packed.data_ptr(), scales.data_ptr(),
+                 s2.data_ptr(), flags, _stream(x))
     return packed, scales.view(torch.float8_e4m3fn), s2
 
 
 def nvfp4_dequantize(packed: torch.Tensor, scales: torch.Tensor, scale2: torch.Tensor,
-                     dtype: torch.dtype) -> torch.Tensor:
+                     dtype: torch.dtype, block: int = 16) -> torch.Tensor:
     packed = _cuda(packed).contiguous()
     scales = _cuda(scales).contiguous().view(torch.uint8)
     s2 = _amax_f32(scale2, packed.device).reshape(())
     y = torch.empty((*packed.shape[:-1], packed.shape[-1] * 2), dtype=dtype, device=packed.device)
-    nblocks = y.numel() // 16
+    nblocks = y.numel() // block
     assert scales.numel() == nblocks
     with torch.cuda.device(packed.device):
-        call("b200q_nvfp4_dequantize", packed.data_ptr(), scales.data_ptr(), s2.data_ptr(), y.data_ptr(),
-             nblocks, _DT[dtype], _stream(packed))
+        if block == 16:
+            call("b200q_nvfp4_dequantize", packed.data_ptr(), scales.data_ptr(), s2.data_ptr(), y.data_ptr(),
+                 nblocks, _DT[dtype], _stream(packed))
+        else:
+            call("b200q_nvfp4_dequantize_blocks", packed.data_ptr(), scales.data_ptr(), s2.data_ptr(),
+                 y.data_ptr(), nblocks, block, _DT[dtype], _stream(packed))
     return y
 
 
-def nvfp4_fake(x: torch.Tensor, amax: torch.Tensor | None = None) -> torch.Tensor:
-    """NVFP4 fake quant along the last dimension (numel % 16 == 0)."""
-    x = _prep(x, 32)
-    if x.numel() % 16:
-        raise ValueError("numel must be a multiple of 16 (pad first)")
+def nvfp4_fake(x: torch.Tensor, amax: torch.Tensor | None = None, block: int = 16) -> torch.Tensor:
+    """NVFP4 fake quant along the last dimension (last dimension % block == 0)."""
+    x = _prep(x, 32 if block == 16 else 16)
+    if x.shape[-1] % block or block % 2:
+        raise ValueError(f"last dimension must be a multiple of the (even) block size {block} (pad first)")
     y = torch.empty_like(x)
     am = amax_tensor(x) if amax is None else _amax_f32(amax, x.device)
     if am.numel() != 1:
         am = am.amax()
     with torch.cuda.device(x.device):
-        call("b200q_nvfp4_fake", x.data_ptr(), y.data_ptr(), x.numel() // 16, dtype_code(x), am.data_ptr(),
-             _stream(x))
+        if block == 16:
+            call("b200q_nvfp4_fake", x.data_ptr(), y.data_ptr(), x.numel() // 16, dtype_code(x), am.data_ptr(),
+                 _stream(x))
+        else:
+            call("b200q_nvfp4_fake_blocks", x.data_ptr(), y.data_ptr(), x.numel() // block, block, dtype_code(x),
+                 am.data_ptr(), _stream(x))
     return y
 
 

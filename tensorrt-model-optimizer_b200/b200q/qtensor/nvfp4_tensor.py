@@ -34,7 +34,6 @@ class NVFP4QTensor(BaseQuantizedTensor):
     def get_weights_scaling_factor(cls, input, block_size, weights_scaling_factor_2=None,
                                    keep_high_precision=False):
         """(per-block scale as float8_e4m3fn [..., K/block], weights_scaling_factor_2)."""
-        assert block_size == 16, "the NVFP4 kernels are built for block size 16"
         assert input.shape[-1] % block_size == 0, (
             "Weight shape is not divisible for block size for block quantization.")
         if weights_scaling_factor_2 is None:
@@ -44,7 +43,7 @@ class NVFP4QTensor(BaseQuantizedTensor):
             s = amax / (6.0 * weights_scaling_factor_2.to(amax.device))
             s[s == 0] = 1.0
             return s, weights_scaling_factor_2
-        _, scales, _ = ops.nvfp4_quantize(input, scale2=weights_scaling_factor_2)
+        _, scales, _ = ops.nvfp4_quantize(input, scale2=weights_scaling_factor_2, block=block_size)
         return scales, weights_scaling_factor_2
 
     @classmethod
@@ -65,11 +64,10 @@ class NVFP4QTensor(BaseQuantizedTensor):
         kernel (plus the abs-max pass when no per-tensor scale is given)."""
         if keep_high_precision:
             raise NotImplementedError("keep_high_precision is not part of the accelerated path")
-        assert block_size == 16, "the NVFP4 kernels are built for block size 16"
         shape, dtype = input.shape, input.dtype
         x = reduce_block_padding(input, {-1: block_size})
         packed, scales, s2 = ops.nvfp4_quantize(x, scale2=weights_scaling_factor_2,
-                                                scales_in=weights_scaling_factor)
+                                                scales_in=weights_scaling_factor, block=block_size)
         if weights_scaling_factor is not None:
             scales = weights_scaling_factor
         if weights_scaling_factor_2 is not None:
@@ -79,8 +77,8 @@ class NVFP4QTensor(BaseQuantizedTensor):
     def dequantize(self, dtype=None, fast=False, **kwarg):
         """Needs ``scale`` (E4M3 per block), ``double_scale`` (fp32) and ``block_sizes``."""
         dtype = dtype or self.metadata["dtype"]
-        assert kwarg["block_sizes"][-1] == 16
-        out = ops.nvfp4_dequantize(self._quantized_data, kwarg["scale"], kwarg["double_scale"], dtype)
+        out = ops.nvfp4_dequantize(self._quantized_data, kwarg["scale"], kwarg["double_scale"], dtype,
+                                   block=kwarg["block_sizes"][-1])
         shape = self.metadata["shape"]
         if out.shape[-1] != shape[-1]:
             out = out[..., : shape[-1]]

@@ -45,13 +45,13 @@ def dynamic_block_quantize_op(input: torch.Tensor, block_size: int, amax: torch.
                               scale_exponent_bits: int) -> torch.Tensor:
     fmt = (exponent_bits, num_bits - exponent_bits - 1)
     scale_fmt = (scale_exponent_bits, scale_num_bits - scale_exponent_bits - 1)
-    if fmt == (2, 1) and scale_fmt == (4, 3) and block_size == 16:
+    if fmt == (2, 1) and scale_fmt == (4, 3) and block_size % 2 == 0:
         shape = input.shape
         x = input
-        pad = (-shape[-1]) % 16
+        pad = (-shape[-1]) % block_size
         if pad:
             x = torch.nn.functional.pad(x, (0, pad))
-        y = ops.nvfp4_fake(x, amax)
+        y = ops.nvfp4_fake(x, amax, block=block_size)
         return y[..., : shape[-1]].contiguous() if pad else y
     if scale_fmt == (8, 0):  # MX formats: power-of-two block scales, no global amax
         key = num_bits if exponent_bits == 0 else fmt
@@ -59,7 +59,7 @@ def dynamic_block_quantize_op(input: torch.Tensor, block_size: int, amax: torch.
             return ops.mx_fake(input, block_size, key)
     raise NotImplementedError(
         f"Unsupported num_bits: {fmt}, scale_bits: {scale_fmt}, block {block_size} for dynamic block "
-        "quantization (built: NVFP4 = (2,1)/(4,3)/16 and the MX formats with (8,0) scales).")
+        "quantization (built: NVFP4 = (2,1) values with (4,3) scales, and the MX formats with (8,0) scales).")
 
 
 @dynamic_block_quantize_op.register_fake

@@ -120,7 +120,8 @@ mxfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, uint8
     for (int o = lanes >> 1; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
     const float descale = __fdiv_rn(__uint_as_float(bits), 6.f);
     const float e = ceilf(fmaxf(log2f(descale), -127.f));
-    const float div = exp2f(e);
+    // x / 2^e as x * 2^-e: both are exact scalings by a power of two (2^-e is finite for e >= -127)
+    const float mul = exp2f(-e);
     if (!valid) continue;
     if ((t & (lanes - 1)) == 0) scales[t / lanes] = static_cast<uint8_t>(static_cast<int>(e + 127.f));
 #pragma unroll
@@ -130,7 +131,7 @@ mxfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, uint8
       uint32_t out = 0;
 #pragma unroll
       for (int k = 0; k < P; ++k) {
-        const float q = __fdiv_rn(f[k], div);
+        const float q = f[k] * mul;
         const float a = fabsf(q);
         uint32_t code = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.f);
         code |= (q > 0.f) ? 0u : 8u;

@@ -316,6 +316,83 @@ def golden_mx_known_answers(out, ref_root):
     np.savez_compressed(out / "mx_known_answers.npz", **cases)
 
 
+def golden_reference_test_tables(out, ref_root):
+    """Known answers held by the reference's own GPU tests, taken from their source as data:
+
+    * tests/gpu/torch/quantization/test_qtensor_cuda.py, test_qtensor_accuracy: (num_bits,
+      block_sizes, axis, input, dequantised output) rows for INT4 / INT8 / FP8 real quantisation
+      (the NF4 rows belong to a format outside this package; the MXFP4 row has no expected output);
+    * the same file, test_cast_fp4_equivalence and test_nvfp4_quantize: inputs, with the codes /
+      packed bytes / scales produced by the reference's NVFP4QTensor on CPU;
+    * tests/gpu/torch/quantization/test_tensor_quant_cuda.py, Testfp4.test_cuda_ext_fp4: the
+      E2M1 value and tie tables for NVFP4 fake quantisation (block 16, global amax = max|x|).
+    """
+    import ast
+
+    from modelopt.torch.quantization.qtensor import NVFP4QTensor
+
+    cases = {}
+    src = (Path(ref_root) / "tests/gpu/torch/quantization/test_qtensor_cuda.py").read_text()
+    tree = ast.parse(src)
+
+    def params_of(fn_name, first_arg):
+        for node in ast.walk(tree):
+            if isinstance(node, ast.FunctionDef) and node.name == fn_name:
+                for dec in node.decorator_list:
+                    if isinstance(dec, ast.Call) and dec.args and \
+                            ast.unparse(dec.args[0]).replace("'", '"').startswith(first_arg):
+                        return eval(compile(ast.Expression(dec.args[1]), "<ref-test-data>", "eval"), {"torch": torch})
+        raise KeyError(fn_name)
+
+    rows = params_of("test_qtensor_accuracy", '("num_bits"')
+    n = 0
+    for num_bits, block_sizes, axis, x, y in rows:
+        if y is None or (block_sizes and "scale_block_sizes" in block_sizes):
+            continue
+        k = f"acc{n}_"
+        cases[k + "num_bits"] = np.array(num_bits)
+        cases[k + "blocks"] = np.array(sorted((block_sizes or {}).items()), dtype=np.int64).reshape(-1, 2)
+        cases[k + "axis"] = np.array(-99 if axis is None else axis)
+        cases[k + "x"] = bits(x)
+        cases[k + "y"] = bits(y)
+        n += 1
+    cases["acc_count"] = np.array(n)
+
+    for i, x in enumerate(params_of("test_cast_fp4_equivalence", '"test_input"')[1:]):   # [0] is randn
+        cases[f"cast{i}_x"] = x.numpy().copy()   # the reference casts in place
+        cases[f"cast{i}_codes"] = NVFP4QTensor._cast_fp4(x).numpy()
+    cases["cast_count"] = np.array(i + 1)
+
+    for i, x in enumerate(params_of("test_nvfp4_quantize", '"test_input"')):
+        if x.shape[-1] % 8:
+            x = torch.nn.functional.pad(x, (0, 8 - x.shape[-1] % 8))        # the reference pads to the block
+        for T in ("f32", "f16", "bf16"):
+            xt = x.to(TD[T])
+            q, s, s2 = NVFP4QTensor.quantize(xt, 8)
+            k = f"nvq{i}_{T}_"
+            cases[k + "x"] = bits(xt)
+            cases[k + "packed"] = bits(q._quantized_data)
+            cases[k + "scales"] = bits(s)
+            cases[k + "scale2"] = bits(s2.reshape(1))
+    cases["nvq_count"] = np.array(i + 1)
+
+    src = (Path(ref_root) / "tests/gpu/torch/quantization/test_tensor_quant_cuda.py").read_text()
+    fn = next(nd for nd in ast.walk(ast.parse(src)) if isinstance(nd, ast.FunctionDef) and nd.name == "test_cuda_ext_fp4")
+    lits = []
+    for node in ast.walk(fn):
+        if isinstance(node, ast.Call) and ast.unparse(node.func) == "torch.tensor" and isinstance(node.args[0], ast.List):
+            lits.append((node.lineno, np.array(ast.literal_eval(node.args[0]), dtype=np.float32)))
+    lits = [t for _, t in sorted(lits, key=lambda p: p[0])]
+    assert len(lits) == 8 and all(t.shape == (1, 8) for t in lits)
+    # the test perturbs the third and fourth inputs by -0.1 / +0.1 (all but the last element)
+    below, above = lits[4].copy(), lits[6].copy()
+    below[:, :-1] -= np.float32(0.1)
+    above[:, :-1] += np.float32(0.1)
+    for i, (x, y) in enumerate([(lits[0], lits[1]), (lits[2], lits[3]), (below, lits[5]), (above, lits[7])]):
+        cases[f"fp4fake{i}_x"], cases[f"fp4fake{i}_y"] = x, y
+    np.savez_compressed(out / "reference_test_tables.npz", **cases)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -330,6 +407,9 @@ def main():
             continue
         fn(HERE)
         print("wrote", name)
+    if not args.only or "reference_test_tables" in args.only.split(","):
+        golden_reference_test_tables(HERE, args.ref)
+        print("wrote reference_test_tables")
     if not args.only or "mx_known_answers" in args.only.split(","):
         golden_mx_known_answers(HERE, args.ref)
         print("wrote mx_known_answers")
