@@ -100,6 +100,8 @@ class HistogramCalibrator(_Calibrator):
     @torch.no_grad()
     def collect(self, x):
         x = x.detach()
+        if not x.is_floating_point() or x.dtype == torch.float64:
+            x = x.float()
         if self._calib_hist is None:
             self.set_range(float(ops.amax_tensor(x)), x.device)
         ops.hist_collect_open(x, self._calib_hist, self._init_bins, self._range0, self._overflow)

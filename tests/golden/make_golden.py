@@ -233,6 +233,23 @@ def golden_hist(out):
     for p in (99.0, 99.9, 99.99, 100.0):
         cases[f"pct_{p}"] = np.array(cal.compute_amax("percentile", percentile=p).item(), dtype=np.float32)
     cases["entropy"] = np.array(cal.compute_amax("entropy").item(), dtype=np.float32)
+    # the sequence of the reference's own test_torch_hist (tests/unit/torch/quantization/
+    # test_calibrator.py:141-181): 19 bins, 15-element batches, the second kind forces growth
+    torch.manual_seed(0)
+    x_1 = torch.rand(15)
+    x_1[0] = 0
+    x_2 = torch.rand(15) + 1
+    x_2[1] = 0
+    small = HistogramCalibrator(8, None, False, num_bins=19, torch_hist=True)
+    small.collect(x_1)
+    cases["small_x1"], cases["small_x2"] = x_1.numpy().copy(), x_2.numpy().copy()
+    cases["small_hist0"] = small._calib_hist.cpu().numpy().astype(np.int64)
+    for r in range(3):
+        small.collect(x_2)
+        small.collect(x_1)
+        cases[f"small_hist{r + 1}"] = small._calib_hist.cpu().numpy().astype(np.int64)
+        cases[f"small_edges{r + 1}"] = small._calib_bin_edges.cpu().numpy().astype(np.float32)
+        cases[f"small_pct{r + 1}"] = np.array(small.compute_amax("percentile", percentile=99.99).item(), np.float32)
     np.savez_compressed(out / "hist.npz", **cases)
 
 

@@ -323,3 +323,54 @@ def test_export_packers_match_reference(mtq, T):
     wsf2 = torch.from_numpy(g[f"{T}_nvfp4_wsf2"]).cuda().reshape(())
     p = export.to_quantized_weight(wt, wsf, "nvfp4", wsf2, 16)
     assert np.array_equal(p.cpu().numpy(), g[f"{T}_nvfp4_packed"])
+
+
+def test_histogram_calibrator_small_sequence_of_the_reference_test(mtq):
+    """The 19-bin, 15-sample sequence of the reference's test_torch_hist (growth on every other
+    batch), plus its integer-input and outlier property tests."""
+    g = load("hist")
+    x1, x2 = torch.from_numpy(g["small_x1"]).cuda(), torch.from_numpy(g["small_x2"]).cuda()
+    cal = mtq.calib.HistogramCalibrator(8, None, False, num_bins=19)
+    cal.collect(x1)
+    assert np.array_equal(cal.hist.cpu().numpy(), g["small_hist0"])
+    for r in range(3):
+        cal.collect(x2)
+        cal.collect(x1)
+        got, ref = cal.hist.cpu().numpy(), g[f"small_hist{r + 1}"]
+        assert got.sum() == ref.sum() and got.size == ref.size
+        # x1's maximum IS the first range's right edge: the reference puts it in bin 18 while the range is
+        # [0, max] and in bin 19 once the range has grown; here it stays in bin 18.  Everything else is equal.
+        merged = lambda h: np.concatenate([h[:18], [h[18] + h[19]], h[20:]])  # noqa: E731
+        assert np.array_equal(merged(got), merged(ref)), (got, ref)
+        assert cal.hist.numel() == cal._calib_bin_edges.numel() - 1
+        assert np.allclose(cal._calib_bin_edges.cpu().numpy(), g[f"small_edges{r + 1}"], rtol=1e-5)
+        a = cal.compute_amax("percentile", percentile=99.99).item()
+        assert abs(a - g[f"small_pct{r + 1}"]) <= float(cal._calib_bin_edges[1]) + 1e-6
+    # integer inputs, a second batch one past the range (reference test_grow)
+    cal = mtq.calib.HistogramCalibrator(8, None, False, num_bins=2048)
+    cal.collect(torch.tensor([0, 255, 255, 255, 255, 255]).cuda())
+    cal.collect(torch.tensor([0, 255, 255, 255, 255, 256]).cuda())
+    assert abs(cal.compute_amax("mse", start_bin=128).item() - 255.0) < 0.5
+    # one outlier among uniform samples is discarded by the entropy method (reference TestEntropyCalibrator)
+    torch.manual_seed(1)
+    for unsigned in (False, True):
+        cal = mtq.calib.HistogramCalibrator(8, None, unsigned, num_bins=2048)
+        x = torch.rand(11, 7, 3, 3).cuda()
+        x[1, 1, 1, 1] = 10.0
+        cal.collect(x)
+        cal.collect(torch.rand(11, 7, 3, 3).cuda())
+        assert cal.compute_amax("entropy", start_bin=128).item() < 1.1
+
+
+def test_scales_from_quantizer_amax_like_the_reference_test(mtq):
+    """reference test_amax_from_tensor_quantizer: with amax preset to 1.1 the NVFP4 per-tensor scale
+    is amax/448/6 and the FP8 scale amax/448."""
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        for num_bits, blocks, attr, want in (
+                ((2, 1), {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}, "_double_scale", 1.1 / 448.0 / 6.0),
+                ((4, 3), None, "_scale", 1.1 / 448.0)):
+            q = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=num_bits, block_sizes=blocks,
+                                                                    fake_quant=False)).cuda()
+            q.amax = torch.tensor(1.1, device="cuda")
+            q(torch.rand(32, 32, device="cuda").to(dtype))
+            assert torch.allclose(getattr(q, attr).float().reshape(()), torch.tensor(want, device="cuda"))
