@@ -9,6 +9,9 @@ from . import ops
 from .qtensor import FP8QTensor, NVFP4QTensor, QTensorWrapper
 
 __all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized_weight",
+           "get_quantization_format", "get_weight_block_size", "get_scaling_factor", "get_activation_scaling_factor",
+           "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
+           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict",
            "QUANTIZATION_FP8", "QUANTIZATION_INT8_SQ", "QUANTIZATION_INT8_WO", "QUANTIZATION_INT4_AWQ",
            "QUANTIZATION_W4A8_AWQ", "QUANTIZATION_NVFP4", "QUANTIZATION_NVFP4_AWQ", "QUANTIZATION_FP8_PB_WO",
            "QUANTIZATION_FP8_PC_PT"]
@@ -101,3 +104,201 @@ def to_quantized_weight(weight, weights_scaling_factor, quantization: str, weigh
         return NVFP4QTensor.quantize(weight, block_size, weights_scaling_factor,
                                      weights_scaling_factor2)[0]._quantized_data
     raise NotImplementedError(f"quantization format {quantization} not supported")
+
+
+# ---------------------------------------------------------------- per-layer checkpoint export --
+# Reference: modelopt/torch/export/quant_utils.py:214-321,412-533,860-983 and
+# modelopt/torch/export/unified_export_hf.py:233-392 (for nn.Linear-like modules with the
+# ``weight`` / ``weight_quantizer`` / ``input_quantizer`` attribute names).
+
+QUANTIZATION_NONE = None
+
+
+def get_quantization_format(module):
+    """The checkpoint format name implied by a layer's quantisers (None if not quantised)."""
+    from .nn import SequentialQuantizer
+
+    wq = getattr(module, "weight_quantizer", None)
+    iq = getattr(module, "input_quantizer", None)
+    if wq is not None and wq.is_enabled:
+        if isinstance(wq, SequentialQuantizer):
+            assert len(wq) == 2 and wq[0].num_bits == 4 and wq[1].num_bits == (4, 3), \
+                "Unsupported SequentialQuantizer configuration"
+            return QUANTIZATION_W4A8_AWQ
+        if wq.num_bits == 4:
+            assert wq.block_sizes and wq.block_sizes[-1] > 0, "Invalid block_sizes for INT4 quantizer"
+            return QUANTIZATION_INT4_AWQ
+        if wq.num_bits == 8:
+            return QUANTIZATION_INT8_SQ if iq is not None and iq.is_enabled else QUANTIZATION_INT8_WO
+        if wq.num_bits == (4, 3):
+            if wq.block_sizes:
+                if not wq.fake_quant:
+                    raise NotImplementedError("export of real-quantised per-block FP8 weights")
+                return QUANTIZATION_FP8_PB_WO
+            return QUANTIZATION_FP8_PC_PT if wq.axis == 0 else QUANTIZATION_FP8
+        if wq.num_bits == (2, 1):
+            scale_bits = wq.block_sizes.get("scale_bits")
+            if iq is not None and hasattr(iq, "_pre_quant_scale"):
+                return QUANTIZATION_NVFP4_AWQ
+            if scale_bits == (4, 3):
+                return QUANTIZATION_NVFP4
+        raise NotImplementedError(f"Unsupported quantizer with num_bits: {wq.num_bits}")
+    for _, child in module.named_children():
+        fmt = get_quantization_format(child)
+        if fmt is not QUANTIZATION_NONE:
+            return fmt
+    return QUANTIZATION_NONE
+
+
+def get_weight_block_size(module) -> int:
+    from .nn import SequentialQuantizer
+
+    wq = getattr(module, "weight_quantizer", None)
+    if wq is None:
+        return 0
+    if isinstance(wq, SequentialQuantizer):
+        wq = wq[0]
+    if not wq.is_enabled or not wq.block_sizes:
+        return 0
+    return wq.block_sizes[-1]
+
+
+def get_scaling_factor(quantizer):
+    """fp32 scaling factor of a quantiser: amax / maxbound (amax / (6 * 448) for NVFP4)."""
+    if not quantizer.is_enabled:
+        return None
+    amax = quantizer.export_amax()
+    if amax is None:
+        return None
+    if quantizer.num_bits == (2, 1):
+        s = NVFP4QTensor.get_weights_scaling_factor_2_from_quantizer(quantizer)
+    else:
+        s = _true_div(amax.float(), float(quantizer.maxbound))
+    assert torch.all(s > 0), f"scaling factor {s} not positive."
+    return s
+
+
+def get_activation_scaling_factor(module):
+    iq = getattr(module, "input_quantizer", None)
+    if iq is None:
+        return None
+    if get_quantization_format(module) in (QUANTIZATION_NVFP4, QUANTIZATION_NVFP4_AWQ):
+        return NVFP4QTensor.get_activation_scaling_factor(iq)
+    return get_scaling_factor(iq)
+
+
+def get_weight_scaling_factor(module):
+    from .nn import SequentialQuantizer
+
+    wq = getattr(module, "weight_quantizer", None)
+    if wq is None:
+        return None
+    if isinstance(wq, SequentialQuantizer):
+        return get_scaling_factor(wq[0])
+    if get_quantization_format(module) in (QUANTIZATION_NVFP4, QUANTIZATION_NVFP4_AWQ):
+        s2 = NVFP4QTensor.get_weights_scaling_factor_2_from_quantizer(wq)
+        return NVFP4QTensor.get_weights_scaling_factor(module.weight, wq.block_sizes[-1], s2.to(module.weight.device))[0]
+    return get_scaling_factor(wq)
+
+
+def get_weight_scaling_factor_2(module):
+    from .nn import SequentialQuantizer
+
+    wq = getattr(module, "weight_quantizer", None)
+    if wq is None:
+        return None
+    if get_quantization_format(module) in (QUANTIZATION_NVFP4, QUANTIZATION_NVFP4_AWQ):
+        return NVFP4QTensor.get_weights_scaling_factor_2_from_quantizer(wq)
+    if not isinstance(wq, SequentialQuantizer) or not wq[-1].is_enabled:
+        return None
+    assert len(wq) == 2, "only 2 sequential quantization layers are supported"
+    return get_scaling_factor(wq[-1])
+
+
+def get_prequant_scaling_factor(module):
+    iq = getattr(module, "input_quantizer", None)
+    s = iq._pre_quant_scale.squeeze() if iq is not None and hasattr(iq, "_pre_quant_scale") else None
+    if s is not None:
+        assert torch.all(s > 0), f"prequant scaling factor {s} not positive."
+    return s
+
+
+@torch.no_grad()
+def export_quantized_weight(module, dtype: torch.dtype):
+    """Replace ``module.weight`` by its packed checkpoint form and register ``weight_scale``,
+    ``weight_scale_2`` and ``input_scale`` buffers, as the reference's per-layer export does."""
+    fmt = get_quantization_format(module)
+    if fmt is QUANTIZATION_NONE:
+        return
+    block_size = get_weight_block_size(module)
+    wq, iq = module.weight_quantizer, getattr(module, "input_quantizer", None)
+    weight = module.weight
+    if fmt == QUANTIZATION_FP8:
+        wq._amax = wq._amax.to(torch.float32)
+        if wq._amax.dim() == 1:
+            ws = torch.tensor(wq.amax.item() / wq.maxbound)
+        else:
+            ws = _true_div(wq.amax, float(wq.maxbound)).clone()
+        module.register_buffer("weight_scale", ws)
+        if iq is not None and hasattr(iq, "_amax"):
+            iq._amax = iq._amax.to(torch.float32)
+            module.register_buffer("input_scale", get_activation_scaling_factor(module).squeeze())
+    else:
+        module.register_buffer("weight_scale", get_weight_scaling_factor(module))
+        if iq is not None and iq.is_enabled and iq.amax is not None:
+            module.register_buffer("input_scale", get_activation_scaling_factor(module).squeeze())
+    if fmt in (QUANTIZATION_NVFP4_AWQ, QUANTIZATION_NVFP4, QUANTIZATION_W4A8_AWQ):
+        module.register_buffer("weight_scale_2", get_weight_scaling_factor_2(module).squeeze())
+    weight_scale = getattr(module, "weight_scale", None)
+    weight_scale_2 = getattr(module, "weight_scale_2", None)
+    if fmt in (QUANTIZATION_NVFP4, QUANTIZATION_NVFP4_AWQ):
+        weight_scale = NVFP4QTensor.get_weights_scaling_factor(weight, block_size, weight_scale_2)[0]
+    packed = to_quantized_weight(weight.to(dtype), weight_scale, fmt, weight_scale_2, block_size)
+    module.weight = torch.nn.Parameter(packed, requires_grad=False)
+    if weight_scale is not None:
+        module.register_buffer("weight_scale", weight_scale)
+
+
+def postprocess_state_dict(state_dict: dict) -> dict:
+    """Drop quantiser state (``_amax``, output quantisers, real-quant scale buffers), rename
+    ``input_quantizer._pre_quant_scale`` to ``pre_quant_scale`` and squeeze ``[1, a, b]`` scales."""
+    from .nn import RealQuantLinear
+
+    skip = ("output_quantizer", "_amax", "_bias_value", "input_quantizer._pre_quant_scale")
+    old, new = "input_quantizer._pre_quant_scale", "pre_quant_scale"
+    out = {}
+    for key, value in state_dict.items():
+        if all(s not in key for s in skip):
+            out[key] = value
+        elif key.endswith(old):
+            out[key[: -len(old)] + new] = value
+    for key, value in list(out.items()):
+        if "scale" in key and isinstance(value, torch.Tensor) and value.dim() == 3 and value.shape[0] == 1:
+            out[key] = value.squeeze(0)
+    scale_names = getattr(RealQuantLinear, "list_of_scale_tensors", ["_scale", "_double_scale", "_scale_zeros"])
+    for key in [k for k in out if any(k.endswith("weight_quantizer." + q) for q in scale_names)]:
+        del out[key]
+    seen = {}
+    for key in list(out):
+        v = out[key]
+        if isinstance(v, torch.Tensor):
+            if v.data_ptr() in seen and v.numel() > 0:
+                del out[key]          # a tied weight: keep the first name
+            else:
+                seen[v.data_ptr()] = key
+    return out
+
+
+@torch.no_grad()
+def export_hf_state_dict(model, dtype: torch.dtype | None = None) -> dict:
+    """Packed state dict of a quantised model with the checkpoint's names (``weight``,
+    ``weight_scale``, ``weight_scale_2``, ``input_scale``, ``pre_quant_scale``).  The model's
+    linear layers are converted in place."""
+    from .nn import is_quantized_linear
+
+    if dtype is None:
+        dtype = next(p.dtype for p in model.parameters() if p.is_floating_point())
+    for _, m in model.named_modules():
+        if is_quantized_linear(m) and get_quantization_format(m) is not QUANTIZATION_NONE:
+            export_quantized_weight(m, dtype)
+    return postprocess_state_dict(model.state_dict())

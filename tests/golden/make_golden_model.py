@@ -127,6 +127,43 @@ def golden_flows(mtq, out):
     np.savez_compressed(out / "flows.npz", **cases)
 
 
+def golden_export_layers(mtq, out):
+    """Per-layer checkpoint export of the reference (_export_quantized_weight + postprocess_state_dict)
+    after mtq.quantize, for FP8, INT8 SmoothQuant, INT4 AWQ and NVFP4."""
+    from modelopt.torch.export.quant_utils import get_quantization_format, postprocess_state_dict
+    from modelopt.torch.export.unified_export_hf import _export_quantized_weight
+
+    cases = {}
+    dtype = torch.bfloat16
+    batches = make_batches(42, 2, dtype)
+    for i, b in enumerate(batches):
+        cases[f"x{i}"] = bits(b)
+    base = make_model(41, dtype)
+    cases["w_up"] = bits(base.up_proj.weight)
+    cases["w_down"] = bits(base.down_proj.weight)
+
+    def loop(m):
+        for b in batches:
+            m(b)
+
+    int4 = copy.deepcopy(mtq.INT4_AWQ_CFG)
+    int4["quant_cfg"]["*weight_quantizer"]["block_sizes"] = {-1: 32, "type": "static"}
+    for tag, cfg in (("fp8", mtq.FP8_DEFAULT_CFG), ("int8_sq", mtq.INT8_SMOOTHQUANT_CFG), ("int4_awq", int4),
+                     ("nvfp4", mtq.NVFP4_DEFAULT_CFG)):
+        model = copy.deepcopy(base)
+        mtq.quantize(model, copy.deepcopy(cfg), loop)
+        for name in ("up_proj", "down_proj"):
+            lin = getattr(model, name)
+            cases[f"{tag}_{name}_format"] = np.array(get_quantization_format(lin))
+            _export_quantized_weight(lin, dtype)
+        sd = postprocess_state_dict(model.state_dict(), 448.0, None)
+        cases[f"{tag}_keys"] = np.array(sorted(sd.keys()))
+        for k, v in sd.items():
+            cases[f"{tag}_sd_{k}"] = bits(v)
+            cases[f"{tag}_dt_{k}"] = np.array(str(v.dtype))
+    np.savez_compressed(out / "export_layers.npz", **cases)
+
+
 def golden_clip_smooth(mtq, out):
     """awq_clip / awq_full on INT4 block-32 weights (losses per clip ratio and block, the chosen
     block amax) and INT8 smoothquant (pre-quant scale, smoothed weight, amax buffers)."""
@@ -185,6 +222,10 @@ def main():
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     mtq = import_reference(args.ref)
+    if args.only == "export_layers":
+        golden_export_layers(mtq, HERE)
+        print("wrote export_layers")
+        return
     if args.only == "clip_smooth":
         golden_clip_smooth(mtq, HERE)
         print("wrote clip_smooth")
@@ -195,6 +236,8 @@ def main():
     print("wrote flows")
     golden_clip_smooth(mtq, HERE)
     print("wrote clip_smooth")
+    golden_export_layers(mtq, HERE)
+    print("wrote export_layers")
 
 
 if __name__ == "__main__":
