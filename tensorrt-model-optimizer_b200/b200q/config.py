@@ -10,6 +10,8 @@ from typing import Any
 __all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG",
            "INT4_BLOCKWISE_WEIGHT_ONLY_CFG", "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG",
            "INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG",
+           "FP8_PER_CHANNEL_PER_TOKEN_CFG", "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG", "W4A8_AWQ_BETA_CFG", "W4A8_NVFP4_FP8_CFG",
+           "W4A8_MXFP4_FP8_CFG", "NVFP4_MLP_WEIGHT_ONLY_CFG", "NVFP4_MLP_ONLY_CFG", "MXFP4_MLP_WEIGHT_ONLY_CFG",
            "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG",
            "choices", "need_calibration"]
 
@@ -112,6 +114,59 @@ NVFP4_AWQ_FULL_CFG = {"quant_cfg": {"*weight_quantizer": dict(_nvfp4), "*input_q
                       "algorithm": {"method": "awq_full", "alpha_step": 0.1}}
 
 
+FP8_PER_CHANNEL_PER_TOKEN_CFG = {
+    "quant_cfg": {"*weight_quantizer": {"num_bits": (4, 3), "axis": 0},
+                  "*input_quantizer": {"num_bits": (4, 3), "type": "dynamic", "block_sizes": {-1: None}},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": "max",
+}
+FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG = {
+    "quant_cfg": {"*weight_quantizer": {"num_bits": (4, 3), "block_sizes": {-1: 128, -2: 128}, "enable": True},
+                  "*input_quantizer": {"enable": False}, **_default_disabled_quantizer_cfg},
+    "algorithm": "max",
+}
+W4A8_AWQ_BETA_CFG = {
+    "quant_cfg": {"*weight_quantizer": [{"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+                                        {"num_bits": (4, 3), "axis": None, "enable": True}],
+                  "*input_quantizer": {"num_bits": (4, 3), "axis": None, "enable": True},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": "awq_lite",
+}
+W4A8_NVFP4_FP8_CFG = {
+    "quant_cfg": {"*weight_quantizer": {"num_bits": (2, 1), "axis": None, "enable": True,
+                                        "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (4, 3)}},
+                  "*input_quantizer": {"num_bits": (4, 3), "axis": None, "enable": True},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": "max",
+}
+W4A8_MXFP4_FP8_CFG = {
+    "quant_cfg": {"*weight_quantizer": {"num_bits": (2, 1), "enable": True,
+                                        "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (8, 0)}},
+                  "*input_quantizer": {"num_bits": (4, 3), "axis": None}, **_default_disabled_quantizer_cfg},
+    "algorithm": None,
+}
+NVFP4_MLP_WEIGHT_ONLY_CFG = {
+    "quant_cfg": {"*mlp*weight_quantizer": {"num_bits": (2, 1), "enable": True, "pass_through_bwd": True,
+                                            "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (4, 3)}},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": "max",
+}
+NVFP4_MLP_ONLY_CFG = {
+    "quant_cfg": {"*mlp*weight_quantizer": {"num_bits": (2, 1), "enable": True, "pass_through_bwd": True,
+                                            "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}},
+                  "*mlp*input_quantizer": {"num_bits": (2, 1), "enable": True, "pass_through_bwd": True,
+                                           "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": "max",
+}
+MXFP4_MLP_WEIGHT_ONLY_CFG = {
+    "quant_cfg": {"*mlp*weight_quantizer": {"num_bits": (2, 1), "enable": True, "pass_through_bwd": True,
+                                            "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (8, 0)}},
+                  **_default_disabled_quantizer_cfg},
+    "algorithm": None,
+}
+
+
 def _mx(num_bits):
     return {"num_bits": num_bits, "block_sizes": {-1: 32, "type": "dynamic", "scale_bits": (8, 0)}, "enable": True}
 
@@ -125,7 +180,8 @@ MXFP4_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx((2, 1)), "*input_qua
 MXINT8_DEFAULT_CFG = {"quant_cfg": {"*weight_quantizer": _mx(8), "*input_quantizer": _mx(8),
                                     **_default_disabled_quantizer_cfg}, "algorithm": None}
 
-choices = {"INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG", "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG","INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
+choices = {"FP8_PER_CHANNEL_PER_TOKEN_CFG", "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG", "W4A8_AWQ_BETA_CFG", "W4A8_NVFP4_FP8_CFG", "W4A8_MXFP4_FP8_CFG", "NVFP4_MLP_WEIGHT_ONLY_CFG", "NVFP4_MLP_ONLY_CFG", "MXFP4_MLP_WEIGHT_ONLY_CFG",
+           "INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG", "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG","INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG", "INT4_BLOCKWISE_WEIGHT_ONLY_CFG",
            "INT4_AWQ_CFG", "NVFP4_DEFAULT_CFG", "NVFP4_AWQ_LITE_CFG"}
 
 

@@ -253,20 +253,25 @@ template <> __device__ __forceinline__ void store16<__half>(__half* y, const flo
 }
 
 // Quantise one loaded block and store codes + scale.
+// `pair`: scale blocks of 32 elements = two adjacent 16-element units held by adjacent lanes, which
+// share one abs-max and one scale (unit count even, so both lanes of a pair are always active).
 template <typename T>
 __device__ __forceinline__ void nvfp4_quant_block(const Block16<T>& blk, int64_t b, const Nvfp4Tensor& tn,
                                                   const uint8_t* __restrict__ scales_in,
                                                   uint8_t* __restrict__ packed,
-                                                  uint8_t* __restrict__ scales) {
-  const float bamax = __uint_as_float(blk.amax_f32bits());
+                                                  uint8_t* __restrict__ scales, bool pair = false) {
+  uint32_t abits = blk.amax_f32bits();
+  if (pair) abits = max(abits, __shfl_xor_sync(__activemask(), abits, 1));
+  const float bamax = __uint_as_float(abits);
+  const int64_t sb = pair ? (b >> 1) : b;
   uint32_t code;
-  if (scales_in) code = scales_in[b];
+  if (scales_in) code = scales_in[sb];
   else code = nvfp4_scale_code<true>(bamax, tn);
   const float d = e4m3_to_f32(code) * tn.s2;
   float f[16];
   blk.decode(f);
   st_stream(packed + 8 * b, nvfp4_encode16<sizeof(T) == 2>(f, d, bamax));
-  if (scales) scales[b] = static_cast<uint8_t>(code);
+  if (scales && !(pair && (b & 1))) scales[sb] = static_cast<uint8_t>(code);
 }
 
 // ---- single-tensor kernels ---------------------------------------------------------------------
@@ -275,7 +280,7 @@ __global__ void __launch_bounds__(kNvThreads)
 nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __restrict__ global,
                       bool global_is_s2, const uint8_t* __restrict__ scales_in,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                      float* __restrict__ s2_out) {
+                      float* __restrict__ s2_out, bool pair) {
   const float g = __ldg(global);
   const Nvfp4Tensor tn(global_is_s2 ? g : __fdiv_rn(g, 2688.f));
   if (s2_out && blockIdx.x == 0 && threadIdx.x == 0) *s2_out = tn.s2;
@@ -291,7 +296,7 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __r
 #pragma unroll
     for (int u = 0; u < kNvUnroll; ++u) {
       const int64_t b = b0 + u * stride;
-      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, tn, scales_in, packed, scales);
+      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, tn, scales_in, packed, scales, pair);
     }
   }
 }
@@ -299,7 +304,7 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __r
 template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
-                  const float* __restrict__ amax) {
+                  const float* __restrict__ amax, bool pair) {
   const Nvfp4Tensor tn(__fdiv_rn(__ldg(amax), 2688.f));
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t b0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b0 < nblocks;
@@ -314,7 +319,9 @@ nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
     for (int u = 0; u < kNvUnroll; ++u) {
       const int64_t b = b0 + u * stride;
       if (b < nblocks) {
-        const float bamax = __uint_as_float(blk[u].amax_f32bits());
+        uint32_t abits = blk[u].amax_f32bits();
+        if (pair) abits = max(abits, __shfl_xor_sync(__activemask(), abits, 1));
+        const float bamax = __uint_as_float(abits);
         const uint32_t code = nvfp4_scale_code<false>(bamax, tn);
         const float d = e4m3_to_f32(code) * tn.s2;
         float f[16];
@@ -330,12 +337,12 @@ nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
 template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
-                        const float* __restrict__ s2p, T* __restrict__ y, int64_t nblocks) {
+                        const float* __restrict__ s2p, T* __restrict__ y, int64_t nblocks, bool pair) {
   const float s2 = __ldg(s2p);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
     const uint2 q = *reinterpret_cast<const uint2*>(packed + 8 * b);
-    const float d = e4m3_to_f32(scales[b]) * s2;
+    const float d = e4m3_to_f32(scales[pair ? (b >> 1) : b]) * s2;
     float f[16];
     nvfp4_decode16(q, d, f);
     store16<T>(y + 16 * b, f);
@@ -433,6 +440,42 @@ using namespace b200q;
 
 extern "C" int b200q_nvfp4_group_tile_elems(void) { return kNvTileElems; }
 
+// Launchers shared with the other-block-size entry points: `pair` = scale blocks of 32 elements.
+namespace b200q {
+
+int nvfp4_launch_quantize(const void* x, int64_t nunits, int dtype, const float* global,
+                          const uint8_t* scales_in, uint8_t* packed, uint8_t* scales, float* s2_out,
+                          int flags, bool pair, cudaStream_t s) {
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(nunits, kNvTileBlocks, 8);
+    nvfp4_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(
+        static_cast<const T*>(x), nunits, global, (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0,
+        scales_in, packed, scales, s2_out, pair);
+    return launch_status();
+  });
+}
+
+int nvfp4_launch_fake(const void* x, void* y, int64_t nunits, int dtype, const float* amax, bool pair,
+                      cudaStream_t s) {
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(nunits, kNvTileBlocks, 8);
+    nvfp4_fake_kernel<T><<<grid, kNvThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), nunits, amax,
+                                                     pair);
+    return launch_status();
+  });
+}
+
+int nvfp4_launch_dequantize(const uint8_t* packed, const uint8_t* scales, const float* s2, void* y,
+                            int64_t nunits, int dtype, bool pair, cudaStream_t s) {
+  return B200Q_DISPATCH(dtype, [&] {
+    int grid = grid_for(nunits, kNvThreads, 8);
+    nvfp4_dequantize_kernel<T><<<grid, kNvThreads, 0, s>>>(packed, scales, s2, static_cast<T*>(y), nunits, pair);
+    return launch_status();
+  });
+}
+
+}  // namespace b200q
+
 extern "C" int b200q_nvfp4_quantize(const void* x, int64_t nblocks, int dtype, const float* global,
                                     const uint8_t* scales_in, uint8_t* packed, uint8_t* scales,
                                     float* s2_out, int flags, void* stream) {
@@ -441,14 +484,8 @@ extern "C" int b200q_nvfp4_quantize(const void* x, int64_t nblocks, int dtype, c
   if ((reinterpret_cast<uintptr_t>(packed) & 7u) != 0) return B200Q_ERR_ALIGN;
   if (nblocks <= 0) return B200Q_ERR_SHAPE;
   if (flags & ~B200Q_NVFP4_GLOBAL_IS_SCALE2) return B200Q_ERR_ARG;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return B200Q_DISPATCH(dtype, [&] {
-    int grid = grid_for(nblocks, kNvTileBlocks, 8);
-    nvfp4_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(
-        static_cast<const T*>(x), nblocks, global, (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0,
-        scales_in, packed, scales, s2_out);
-    return launch_status();
-  });
+  return nvfp4_launch_quantize(x, nblocks, dtype, global, scales_in, packed, scales, s2_out, flags, false,
+                               static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200q_nvfp4_fake(const void* x, void* y, int64_t nblocks, int dtype, const float* amax,
@@ -456,13 +493,7 @@ extern "C" int b200q_nvfp4_fake(const void* x, void* y, int64_t nblocks, int dty
   B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(y); B200Q_REQUIRE_PTR(amax);
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED32(x); B200Q_REQUIRE_ALIGNED32(y);
   if (nblocks <= 0) return B200Q_ERR_SHAPE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return B200Q_DISPATCH(dtype, [&] {
-    int grid = grid_for(nblocks, kNvTileBlocks, 8);
-    nvfp4_fake_kernel<T><<<grid, kNvThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y),
-                                                     nblocks, amax);
-    return launch_status();
-  });
+  return nvfp4_launch_fake(x, y, nblocks, dtype, amax, false, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200q_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scales, const float* s2,
@@ -471,12 +502,7 @@ extern "C" int b200q_nvfp4_dequantize(const uint8_t* packed, const uint8_t* scal
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED32(y);
   if ((reinterpret_cast<uintptr_t>(packed) & 7u) != 0) return B200Q_ERR_ALIGN;
   if (nblocks <= 0) return B200Q_ERR_SHAPE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return B200Q_DISPATCH(dtype, [&] {
-    int grid = grid_for(nblocks, kNvThreads, 8);
-    nvfp4_dequantize_kernel<T><<<grid, kNvThreads, 0, s>>>(packed, scales, s2, static_cast<T*>(y), nblocks);
-    return launch_status();
-  });
+  return nvfp4_launch_dequantize(packed, scales, s2, y, nblocks, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
 static int check_group(const b200q_nvfp4_desc* descs, int n, int64_t total_tiles, int dtype) {

@@ -6,6 +6,17 @@
 
 namespace b200q {
 
+// the 16-element-unit kernels; pair = two adjacent units share one scale (block 32)
+int nvfp4_launch_quantize(const void* x, int64_t nunits, int dtype, const float* global,
+                          const uint8_t* scales_in, uint8_t* packed, uint8_t* scales, float* s2_out,
+                          int flags, bool pair, cudaStream_t s);
+int nvfp4_launch_fake(const void* x, void* y, int64_t nunits, int dtype, const float* amax, bool pair,
+                      cudaStream_t s);
+int nvfp4_launch_dequantize(const uint8_t* packed, const uint8_t* scales, const float* s2, void* y,
+                            int64_t nunits, int dtype, bool pair, cudaStream_t s);
+
+static bool aligned_to(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
 // kTorchCast: the block-scale cast of torch (NaN code above 464); otherwise saturating (fake quant)
 template <bool kTorchCast>
 __device__ __forceinline__ uint32_t nv_block_scale_code(float bamax, float s2) {
@@ -78,6 +89,8 @@ extern "C" int b200q_nvfp4_quantize_blocks(const void* x, int64_t nblocks, int b
   if (nblocks <= 0 || block <= 0 || (block & 1)) return B200Q_ERR_SHAPE;
   if (flags & ~B200Q_NVFP4_GLOBAL_IS_SCALE2) return B200Q_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (block == 32 && aligned_to(x, 32) && aligned_to(packed, 8))   // block 32 on the fast kernels
+    return nvfp4_launch_quantize(x, nblocks * 2, dtype, global, scales_in, packed, scales, s2_out, flags, true, s);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nblocks, 128, 16);
     nvfp4_blocks_kernel<T, 0><<<grid, 128, 0, s>>>(static_cast<const T*>(x), nblocks, block, global,
@@ -93,6 +106,8 @@ extern "C" int b200q_nvfp4_fake_blocks(const void* x, void* y, int64_t nblocks, 
   B200Q_REQUIRE_DTYPE(dtype);
   if (nblocks <= 0 || block <= 0 || (block & 1)) return B200Q_ERR_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (block == 32 && aligned_to(x, 32) && aligned_to(y, 32))
+    return nvfp4_launch_fake(x, y, nblocks * 2, dtype, amax, true, s);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nblocks, 128, 16);
     nvfp4_blocks_kernel<T, 1><<<grid, 128, 0, s>>>(static_cast<const T*>(x), nblocks, block, amax, false, nullptr,
@@ -107,6 +122,8 @@ extern "C" int b200q_nvfp4_dequantize_blocks(const uint8_t* packed, const uint8_
   B200Q_REQUIRE_DTYPE(dtype);
   if (nblocks <= 0 || block <= 0 || (block & 1)) return B200Q_ERR_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (block == 32 && aligned_to(y, 32) && aligned_to(packed, 8))
+    return nvfp4_launch_dequantize(packed, scales, s2, y, nblocks * 2, dtype, true, s);
   return B200Q_DISPATCH(dtype, [&] {
     const int64_t nbytes = nblocks * (block / 2);
     int grid = grid_for(nbytes, 256, 8);

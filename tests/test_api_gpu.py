@@ -374,3 +374,48 @@ def test_scales_from_quantizer_amax_like_the_reference_test(mtq):
             q.amax = torch.tensor(1.1, device="cuda")
             q(torch.rand(32, 32, device="cuda").to(dtype))
             assert torch.allclose(getattr(q, attr).float().reshape(()), torch.tensor(want, device="cuda"))
+
+
+@pytest.mark.parametrize("T", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("block", [8, 32, 64])
+def test_nvfp4_other_block_sizes_vs_oracle(mtq, T, block):
+    """NVFP4 with the reference's other block sizes (8 in its tests, 32 in its W4A8 / MLP-only
+    configs): packed bytes, scales, dequantised and fake-quantised values against the oracle."""
+    from b200q import ops
+    from test_kernels_gpu import rnd
+
+    x = rnd((48, 256), T, 900 + block, 0.3, heavy=True)
+    xt = tensor_from_f32(x, T)
+    packed, scales, s2 = ops.nvfp4_quantize(xt, block=block)
+    wp, ws, w2 = qo.nvfp4_quantize(x, block)
+    assert np.array_equal(packed.cpu().numpy(), wp) and np.array_equal(scales.view(torch.uint8).cpu().numpy(), ws)
+    assert float(s2) == float(w2)
+    deq = ops.nvfp4_dequantize(packed, scales, s2, xt.dtype, block=block)
+    assert same_bits(f32_from_tensor(deq), qo.nvfp4_dequantize(wp, ws, w2, block, T))
+    fq = ops.nvfp4_fake(xt, block=block)
+    assert same_bits(f32_from_tensor(fq), qo.nvfp4_fake(x, np.abs(x).max(), block, T))
+
+
+@pytest.mark.parametrize("name", ["FP8_PER_CHANNEL_PER_TOKEN_CFG", "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG",
+                                  "W4A8_AWQ_BETA_CFG", "W4A8_NVFP4_FP8_CFG", "W4A8_MXFP4_FP8_CFG",
+                                  "INT4_BLOCKWISE_WEIGHT_ONLY_CFG", "INT8_WEIGHT_ONLY_CFG"])
+def test_more_reference_configs_quantize_and_run(mtq, name):
+    """Every further configuration of the reference that is made of the built formats converts,
+    calibrates and runs; the quantised output stays close to the unquantised one."""
+    torch.manual_seed(5)
+    model = MLP().to(torch.bfloat16).cuda()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.mul_(0.5)
+    x = [torch.randn(32, 128, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    ref = model(x[0]).float()
+
+    def loop(m):
+        for b in x:
+            m(b)
+
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), loop)
+    y = model(x[0]).float()
+    assert torch.isfinite(y).all()
+    rel = (y - ref).abs().mean() / ref.abs().mean()
+    assert rel < (0.35 if "W4" in name or "INT4" in name else 0.1), float(rel)
