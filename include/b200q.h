@@ -206,6 +206,24 @@ int b200q_int8_quantize(const void* x, const void* scales, int8_t* q, int64_t ou
 int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
                        unsigned long long* counts, void* stream);
 
+/* Entropy (KL-divergence) calibration on the device.  For every candidate i = start_bin, start_bin +
+ * stride, ... <= nbins the first i bins are re-quantised into num_levels (a power of two,
+ * 2^(bits-1+unsigned)) levels and KL(reference || candidate) is written to divergences[k]
+ * (device, (nbins-start_bin)/stride + 1 doubles); *amax_out = edges[i*] (or i* x bin_width when
+ * edges is NULL) for the LAST minimum i*.  Replaces _compute_amax_entropy
+ * (modelopt/torch/quantization/calib/histogram.py:210-282), a host loop over scipy.stats.entropy. */
+int b200q_hist_entropy(const unsigned long long* counts, int nbins, int num_levels, int start_bin, int stride,
+                       const float* edges, float bin_width, double* divergences, float* amax_out,
+                       void* stream);
+
+/* Mean-squared-error calibration from a histogram: for every candidate i = start_bin, start_bin +
+ * stride, ... < nbins the clip point is the centre of bin i, every bin centre is fake quantised to
+ * +-bound integer levels and errors[k] = mean over bins of count * (q - centre)^2; *amax_out = the
+ * centre of the FIRST minimum.  The documented algorithm of _compute_amax_mse
+ * (modelopt/torch/quantization/calib/histogram.py:285-325). */
+int b200q_hist_mse(const unsigned long long* counts, int nbins, const float* edges, double bound, int start_bin,
+                   int stride, double* errors, float* amax_out, void* stream);
+
 /* Open-ended collection for a calibrator whose range grows: bins continue past nbins - 1 at the
  * same width (range_max / nbins) up to `capacity` bins, so that later batches with larger values
  * need neither a new range nor a host round trip.  Samples beyond capacity bins, NaN and inf are

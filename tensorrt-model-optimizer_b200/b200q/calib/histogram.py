@@ -10,8 +10,9 @@ when they are needed.  Samples beyond the capacity, NaN and inf are counted apar
 read-out raise.  Integer counters make the result independent of batch order and summable across
 data-parallel ranks (``b200q.dist.sync_histograms``).
 
-``compute_amax`` offers "percentile" (on the GPU), and "entropy" / "mse" on the host from the
-copied counts.  "mse" follows the algorithm the reference documents (minimise the count-weighted
+``compute_amax`` offers "percentile", "entropy" and "mse" on the GPU (one CTA per candidate clip point
+for the searches the reference runs as host loops), and all three on the host for counters held
+in CPU memory.  "mse" follows the algorithm the reference documents (minimise the count-weighted
 squared error of fake-quantised bin centres); the reference's own implementation passes its
 arguments to ``fake_tensor_quant`` in the wrong slots (histogram.py:308) and is not reproduced.
 """
@@ -131,6 +132,17 @@ class HistogramCalibrator(_Calibrator):
             if percentile < 0 or percentile > 100:
                 raise ValueError("Invalid percentile. Must be in range 0 <= percentile <= 100.")
             return ops.hist_percentile(self._calib_hist, self._num_bins, self._calib_bin_edges, 0.0, percentile)
+        if method == "entropy" and self._calib_hist.is_cuda:
+            if isinstance(self._num_bits, tuple):
+                raise TypeError("entropy calibration needs an integer num_bits")
+            levels = 1 << (self._num_bits - 1 + int(self._unsigned))
+            return ops.hist_entropy(self._calib_hist, self._num_bins, self._calib_bin_edges, levels,
+                                    start_bin, stride)[0]
+        if method == "mse" and self._calib_hist.is_cuda:
+            if isinstance(self._num_bits, tuple):
+                raise TypeError("mse calibration from a histogram needs an integer num_bits")
+            bound = 2.0 ** (self._num_bits - 1 + int(self._unsigned)) - 1
+            return ops.hist_mse(self._calib_hist, self._num_bins, self._calib_bin_edges, bound, start_bin, stride)[0]
         counts = self.hist.cpu().numpy()
         edges = self._calib_bin_edges.cpu().numpy()
         if method == "entropy":

@@ -376,6 +376,34 @@ def hist_collect_open(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_m
     return counts
 
 
+def hist_entropy(counts: torch.Tensor, nbins: int, edges: torch.Tensor, num_levels: int, start_bin: int = 128,
+                 stride: int = 1):
+    """Entropy-calibrated amax (0-dim fp32 tensor) and the per-candidate divergences (fp64)."""
+    ncand = (nbins - start_bin) // stride + 1
+    divs = torch.empty(ncand, dtype=torch.float64, device=counts.device)
+    out = torch.empty((), dtype=torch.float32, device=counts.device)
+    e = edges.to(device=counts.device, dtype=torch.float32).contiguous()
+    assert e.numel() >= nbins + 1 and counts.dtype == torch.int64
+    with torch.cuda.device(counts.device):
+        call("b200q_hist_entropy", counts.data_ptr(), nbins, num_levels, start_bin, stride, e.data_ptr(),
+             ctypes.c_float(0.0), divs.data_ptr(), out.data_ptr(), _stream(counts))
+    return out, divs
+
+
+def hist_mse(counts: torch.Tensor, nbins: int, edges: torch.Tensor, bound: float, start_bin: int = 128,
+             stride: int = 1):
+    """MSE-calibrated amax (0-dim fp32 tensor) and the per-candidate errors (fp64)."""
+    ncand = (nbins - 1 - start_bin) // stride + 1
+    errs = torch.empty(ncand, dtype=torch.float64, device=counts.device)
+    out = torch.empty((), dtype=torch.float32, device=counts.device)
+    e = edges.to(device=counts.device, dtype=torch.float32).contiguous()
+    assert e.numel() >= nbins + 1 and counts.dtype == torch.int64
+    with torch.cuda.device(counts.device):
+        call("b200q_hist_mse", counts.data_ptr(), nbins, e.data_ptr(), ctypes.c_double(bound), start_bin, stride,
+             errs.data_ptr(), out.data_ptr(), _stream(counts))
+    return out, errs
+
+
 def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None, width: float,
                     percentile: float) -> torch.Tensor:
     out = torch.empty((), dtype=torch.float32, device=counts.device)

@@ -292,6 +292,127 @@ hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
   }
 }
 
+// ---- entropy (KL-divergence) read-out -------------------------------------------------------------
+// One CTA per candidate clip point i (the first i bins kept): the kept bins are merged into
+// `nlev` equal-width levels, each level's mass spread evenly over its non-empty bins, and
+// KL(reference || candidate) taken with the clipped tail added to the reference's last bin
+// (reference calib/histogram.py:210-282; bin 0 takes the count of bin 1 first).  Counts are
+// integers, so level masses and totals are exact; the divergence is summed in fp64.
+constexpr int kEntThreads = 256;
+constexpr int kEntMaxLevels = 1 << 12;
+
+__device__ __forceinline__ unsigned long long ent_count(const unsigned long long* c, int j) {
+  return c[j == 0 ? 1 : j];   // the reference overwrites bin 0 by bin 1
+}
+
+__global__ void __launch_bounds__(kEntThreads)
+hist_entropy_kernel(const unsigned long long* __restrict__ counts, int nbins, int nlev, int start_bin,
+                    int stride, double* __restrict__ divs) {
+  extern __shared__ unsigned long long ent_sh[];   // [nlev] mass | [nlev] non-empty bins (as u64)
+  unsigned long long* mass = ent_sh;
+  unsigned long long* cnt = ent_sh + nlev;
+  __shared__ double red[kEntThreads / 32];
+  __shared__ unsigned long long redu[kEntThreads / 32];
+  const int i = start_bin + static_cast<int>(blockIdx.x) * stride;   // bins kept
+  for (int l = threadIdx.x; l < 2 * nlev; l += blockDim.x) ent_sh[l] = 0;
+  __syncthreads();
+  // level of bin j: floor(j * nlev / i)  (nlev is a power of two: the reference's linspace edges are exact)
+  unsigned long long tail = 0;
+  for (int j = threadIdx.x; j < nbins; j += blockDim.x) {
+    const unsigned long long c = ent_count(counts, j);
+    if (j < i) {
+      if (c) {
+        const int l = static_cast<int>((static_cast<long long>(j) * nlev) / i);
+        atomicAdd(mass + l, c);
+        atomicAdd(cnt + l, 1ull);
+      }
+    } else {
+      tail += c;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) tail += __shfl_xor_sync(0xffffffffu, tail, o);
+  if ((threadIdx.x & 31) == 0) redu[threadIdx.x >> 5] = tail;
+  __syncthreads();
+  tail = 0;
+  for (int w = 0; w < kEntThreads / 32; ++w) tail += redu[w];
+  unsigned long long head = 0;   // sum of the kept bins = sum of the level masses
+  for (int l = 0; l < nlev; ++l) head += mass[l];   // nlev <= 4096: cheap, same order in every thread
+  const double total = static_cast<double>(head + tail), dhead = static_cast<double>(head);
+  double kl = 0.0;
+  bool infinite = false;
+  for (int j = threadIdx.x; j < i; j += blockDim.x) {
+    const unsigned long long c = ent_count(counts, j);
+    unsigned long long r = c + (j == i - 1 ? tail : 0ull);
+    if (r == 0) continue;
+    if (c == 0) { infinite = true; continue; }   // reference mass where the candidate has none
+    const int l = static_cast<int>((static_cast<long long>(j) * nlev) / i);
+    const double p = static_cast<double>(r) / total;
+    const double q = (static_cast<double>(mass[l]) / static_cast<double>(cnt[l])) / dhead;
+    kl += p * log(p / q);
+  }
+  for (int o = 16; o > 0; o >>= 1) kl += __shfl_xor_sync(0xffffffffu, kl, o);
+  const bool any_inf = __syncthreads_or(infinite);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = kl;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double sum = 0.0;
+    for (int w = 0; w < kEntThreads / 32; ++w) sum += red[w];
+    divs[blockIdx.x] = any_inf ? __longlong_as_double(0x7ff0000000000000ll) : sum;
+  }
+}
+
+// last minimum of divs -> amax = edges[index * stride + start_bin]
+__global__ void hist_entropy_pick_kernel(const double* __restrict__ divs, int ncand, int start_bin, int stride,
+                                         const float* __restrict__ edges, float bin_width,
+                                         float* __restrict__ amax_out) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  int best = 0;
+  double bv = divs[0];
+  for (int k = 1; k < ncand; ++k)
+    if (divs[k] <= bv) { bv = divs[k]; best = k; }
+  const int idx = best * stride + start_bin;
+  *amax_out = edges ? edges[idx] : bin_width * static_cast<float>(idx);
+}
+
+// ---- mean-squared-error read-out ---------------------------------------------------------------------
+// One CTA per candidate clip point i: amax = centre of bin i, every bin centre is fake quantised to
+// `bound` integer levels with that amax and the count-weighted squared error is averaged (fp64).
+// The FIRST minimum wins.
+__global__ void __launch_bounds__(kEntThreads)
+hist_mse_kernel(const unsigned long long* __restrict__ counts, int nbins, const float* __restrict__ edges,
+                double bound, int start_bin, int stride, double* __restrict__ errs) {
+  __shared__ double red[kEntThreads / 32];
+  const int i = start_bin + static_cast<int>(blockIdx.x) * stride;
+  const double amax = (static_cast<double>(edges[i + 1]) + static_cast<double>(edges[i])) / 2.0;
+  const double scale = bound / amax;
+  double acc = 0.0;
+  for (int j = threadIdx.x; j < nbins; j += blockDim.x) {
+    const double c = (static_cast<double>(edges[j + 1]) + static_cast<double>(edges[j])) / 2.0;
+    double q = rint(c * scale);
+    q = fmin(fmax(q, -bound), bound) / scale;
+    acc += (q - c) * (q - c) * static_cast<double>(counts[j]);
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double sum = 0.0;
+    for (int w = 0; w < kEntThreads / 32; ++w) sum += red[w];
+    errs[blockIdx.x] = sum / static_cast<double>(nbins);
+  }
+}
+
+__global__ void hist_mse_pick_kernel(const double* __restrict__ errs, int ncand, int start_bin, int stride,
+                                     const float* __restrict__ edges, float* __restrict__ amax_out) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  int best = 0;
+  double bv = errs[0];
+  for (int k = 1; k < ncand; ++k)
+    if (errs[k] < bv) { bv = errs[k]; best = k; }
+  const int i = best * stride + start_bin;
+  *amax_out = static_cast<float>((static_cast<double>(edges[i + 1]) + static_cast<double>(edges[i])) / 2.0);
+}
+
 }  // namespace b200q
 
 using namespace b200q;
@@ -378,5 +499,31 @@ extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins
   if (!(percentile >= 0.0 && percentile <= 100.0)) return B200Q_ERR_ARG;
   hist_percentile_kernel<<<1, kPctThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       counts, nbins, edges, bin_width, percentile / 100.0, amax_out);
+  return launch_status();
+}
+
+extern "C" int b200q_hist_entropy(const unsigned long long* counts, int nbins, int num_levels, int start_bin,
+                                  int stride, const float* edges, float bin_width, double* divergences,
+                                  float* amax_out, void* stream) {
+  B200Q_REQUIRE_PTR(counts); B200Q_REQUIRE_PTR(divergences); B200Q_REQUIRE_PTR(amax_out);
+  if (nbins < 2 || start_bin < 1 || start_bin > nbins || stride < 1) return B200Q_ERR_SHAPE;
+  if (num_levels < 1 || num_levels > kEntMaxLevels || (num_levels & (num_levels - 1))) return B200Q_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int ncand = (nbins - start_bin) / stride + 1;
+  hist_entropy_kernel<<<ncand, kEntThreads, 2 * num_levels * sizeof(unsigned long long), s>>>(
+      counts, nbins, num_levels, start_bin, stride, divergences);
+  hist_entropy_pick_kernel<<<1, 32, 0, s>>>(divergences, ncand, start_bin, stride, edges, bin_width, amax_out);
+  return launch_status();
+}
+
+extern "C" int b200q_hist_mse(const unsigned long long* counts, int nbins, const float* edges, double bound,
+                              int start_bin, int stride, double* errors, float* amax_out, void* stream) {
+  B200Q_REQUIRE_PTR(counts); B200Q_REQUIRE_PTR(edges); B200Q_REQUIRE_PTR(errors); B200Q_REQUIRE_PTR(amax_out);
+  if (nbins < 2 || start_bin < 0 || start_bin >= nbins || stride < 1) return B200Q_ERR_SHAPE;
+  if (!(bound >= 1.0)) return B200Q_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int ncand = (nbins - 1 - start_bin) / stride + 1;
+  hist_mse_kernel<<<ncand, kEntThreads, 0, s>>>(counts, nbins, edges, bound, start_bin, stride, errors);
+  hist_mse_pick_kernel<<<1, 32, 0, s>>>(errors, ncand, start_bin, stride, edges, amax_out);
   return launch_status();
 }

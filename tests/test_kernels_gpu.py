@@ -448,3 +448,40 @@ def test_nvfp4_every_bf16_value_under_many_divisors(ops):
         wp, ws, _ = qo.nvfp4_quantize(x, 16, s2=s2)
         assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), ws), i
         assert np.array_equal(packed.cpu().numpy(), wp), i
+
+
+@pytest.mark.parametrize("num_bits,unsigned", [(8, False), (8, True), (4, False)])
+def test_hist_entropy_kernel_vs_host_search(ops, num_bits, unsigned):
+    """The device KL search against the numpy restatement of the reference's host loop: same
+    divergences (fp64 sums in another order) and the same chosen clip point."""
+    from b200q.calib.histogram import _entropy_amax
+
+    rng = np.random.default_rng(7 + num_bits)
+    for nbins, start, stride in ((2048, 128, 1), (2048, 128, 3), (700, 128, 1), (4600, 256, 7)):
+        x = np.abs(rng.standard_normal(400_000)).astype(np.float32)
+        x[:50] *= 30.0                                          # outliers: a long, mostly empty tail
+        counts, edges = np.histogram(x, bins=nbins, range=(0, float(x.max())))
+        c = torch.from_numpy(counts.astype(np.int64)).cuda()
+        e = torch.from_numpy(edges.astype(np.float32)).cuda()
+        levels = 1 << (num_bits - 1 + int(unsigned))
+        amax, divs = ops.hist_entropy(c, nbins, e, levels, start, stride)
+        want = _entropy_amax(counts, edges.astype(np.float32), num_bits, unsigned, stride, start)
+        assert amax.item() == np.float32(want), (nbins, start, stride)
+        assert torch.isfinite(divs).any()
+
+
+def test_hist_mse_kernel_vs_host_search(ops):
+    from b200q.calib.histogram import _mse_amax
+
+    rng = np.random.default_rng(21)
+    for nbins, start, stride, bits, unsigned in ((2048, 128, 1, 8, False), (2048, 128, 5, 8, True), (300, 16, 1, 4, False)):
+        x = np.abs(rng.standard_normal(300_000)).astype(np.float32)
+        x[:20] *= 25.0
+        counts, edges = np.histogram(x, bins=nbins, range=(0, float(x.max())))
+        edges = edges.astype(np.float32)
+        bound = 2.0 ** (bits - 1 + int(unsigned)) - 1
+        amax, errs = ops.hist_mse(torch.from_numpy(counts.astype(np.int64)).cuda(), nbins,
+                                  torch.from_numpy(edges).cuda(), bound, start, stride)
+        want = _mse_amax(counts, edges, bits, unsigned, stride, start)
+        assert abs(amax.item() - want) <= 1e-6 * want, (nbins, amax.item(), want)
+        assert torch.isfinite(errs).all()
