@@ -324,17 +324,21 @@ def run_formats(dev, peak):
 
     from b200q import ops
 
-    def timed(fn, n_bytes, reps=5):
+    def timed(fn, n_bytes, reps=5, groups=5):
+        """median over `groups` of the mean time of `reps` back-to-back passes (CUDA events)"""
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / reps
+        times = []
+        for _ in range(groups):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / reps)
+        ms = statistics.median(times)
         gbs = n_bytes / (ms * 1e-3) / 1e9
         return {"gbps": gbs, "frac_of_measured_peak": gbs / peak, "ms": ms, "algorithmic_bytes": n_bytes}
 
@@ -385,15 +389,15 @@ def run_formats(dev, peak):
             ops.awq_gemm_sqerr(x, wfq, ref, acc, status)
 
     flops = 21 * 2.0 * 512 * 4096 * 14336
-    r = timed(search, 21 * 14336 * 4096 * 4, reps=3)
+    r = timed(search, 21 * 14336 * 4096 * 4, reps=3, groups=3)
     out["awq_lite_search_21_alphas_up_proj_512tok"] = {
         "ms": r["ms"], "gemm_tflops_incl_quant_kernel": flops / (r["ms"] * 1e-3) / 1e12}
     wfq = ops.awq_scale_fake_int(w, scales[1], 128, 4, False, False)
-    r = timed(lambda: [ops.awq_gemm_sqerr(x, wfq, ref, acc, status) for _ in range(21)], 1, reps=3)
+    r = timed(lambda: [ops.awq_gemm_sqerr(x, wfq, ref, acc, status) for _ in range(21)], 1, reps=3, groups=3)
     tf = flops / (r["ms"] * 1e-3) / 1e12
     out["awq_gemm_sqerr_tcgen05_512x14336x4096"] = {"ms_per_gemm": r["ms"] / 21, "tflops": tf,
                                                     "kernel_status": int(status)}
-    r = timed(lambda: [torch.nn.functional.linear(x, wfq) for _ in range(21)], 1, reps=3)
+    r = timed(lambda: [torch.nn.functional.linear(x, wfq) for _ in range(21)], 1, reps=3, groups=3)
     out["cublas_linear_512x14336x4096_for_comparison"] = {"ms_per_gemm": r["ms"] / 21,
                                                           "tflops": flops / (r["ms"] * 1e-3) / 1e12}
     return out

@@ -28,6 +28,7 @@ template <typename T>
 __global__ void __launch_bounds__(kAmaxThreads)
 amax_tensor_kernel(const T* __restrict__ x, int64_t n, uint32_t* __restrict__ amax_bits) {
   using E = Elem<T>;
+  pdl_prologue();
   __shared__ uint32_t red[32];
   const int64_t npack = n / E::kPerPack;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -57,6 +58,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 amax_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t axis, int64_t inner,
                  int slices_per_row, uint32_t* __restrict__ amax_bits) {
+  pdl_prologue();
   using E = Elem<T>;
   __shared__ uint32_t red[32];
   const int64_t total = rows * slices_per_row;
@@ -97,6 +99,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 amax_cols_kernel(const T* __restrict__ x, int64_t outer, int64_t axis, int rows_per_band,
                  uint32_t* __restrict__ amax_bits) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t cpack = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -148,6 +151,7 @@ amax_cols_kernel(const T* __restrict__ x, int64_t outer, int64_t axis, int rows_
 template <typename T>
 __global__ void amax_axis_generic_kernel(const T* __restrict__ x, int64_t n, int64_t axis,
                                          int64_t inner, uint32_t* __restrict__ amax_bits) {
+  pdl_prologue();
   using E = Elem<T>;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -160,6 +164,7 @@ __global__ void amax_axis_generic_kernel(const T* __restrict__ x, int64_t n, int
 template <typename T, int PPL>
 __global__ void __launch_bounds__(256)
 amax_blocks_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, float* __restrict__ out) {
+  pdl_prologue();
   using E = Elem<T>;
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -183,6 +188,7 @@ amax_blocks_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, float* _
 template <typename T>
 __global__ void amax_blocks_generic_kernel(const T* __restrict__ x, int64_t nblocks, int block,
                                            float* __restrict__ out) {
+  pdl_prologue();
   using E = Elem<T>;
   for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblocks;
        b += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -205,8 +211,8 @@ extern "C" int b200q_amax_tensor(const void* x, int64_t n, int dtype, float* ama
   return B200Q_DISPATCH(dtype, [&] {
     const int64_t npack = n / Elem<T>::kPerPack;
     int grid = grid_for(npack, kAmaxThreads * kAmaxUnroll, 4);
-    amax_tensor_kernel<T><<<grid, kAmaxThreads, 0, s>>>(static_cast<const T*>(x), n,
-                                                        reinterpret_cast<uint32_t*>(amax_io));
+    launch_pdl(amax_tensor_kernel<T>, grid, kAmaxThreads, 0, s, static_cast<const T*>(x), n,
+               reinterpret_cast<uint32_t*>(amax_io));
     return launch_status();
   });
 }
@@ -230,7 +236,7 @@ extern "C" int b200q_amax_axis(const void* x, int64_t outer, int64_t axis, int64
       if (bands > 65535) bands = 65535;
       const int rpb = static_cast<int>((outer + bands - 1) / bands);
       dim3 grid(bx, static_cast<unsigned>((outer + rpb - 1) / rpb));
-      amax_cols_kernel<T><<<grid, 256, 0, s>>>(xp, outer, axis, rpb, out);
+      launch_pdl(amax_cols_kernel<T>, grid, 256, 0, s, xp, outer, axis, rpb, out);
     } else if (inner >= 64 && (inner % P == 0 || inner >= 4096)) {
       const int64_t rows = outer * axis;
       // split long rows so that at least ~4 CTAs per SM have work
@@ -243,11 +249,11 @@ extern "C" int b200q_amax_axis(const void* x, int64_t outer, int64_t axis, int64
         slices = static_cast<int>(sp < max_sp ? sp : max_sp);
       }
       int grid = grid_for(rows * slices, 1, 8);
-      amax_rows_kernel<T><<<grid, 256, 0, s>>>(xp, rows, axis, inner, slices, out);
+      launch_pdl(amax_rows_kernel<T>, grid, 256, 0, s, xp, rows, axis, inner, slices, out);
     } else {
       const int64_t n = outer * axis * inner;
       int grid = grid_for(n, 256, 8);
-      amax_axis_generic_kernel<T><<<grid, 256, 0, s>>>(xp, n, axis, inner, out);
+      launch_pdl(amax_axis_generic_kernel<T>, grid, 256, 0, s, xp, n, axis, inner, out);
     }
     return launch_status();
   });
@@ -270,12 +276,12 @@ extern "C" int b200q_amax_blocks(const void* x, int64_t nblocks, int block, int 
       const int lanes = packs / ppl;
       int grid = grid_for(nblocks * lanes, 256, 8);
       if (ppl == 2)
-        amax_blocks_kernel<T, 2><<<grid, 256, 0, s>>>(xp, nblocks, lanes, amax_out);
+        launch_pdl(amax_blocks_kernel<T, 2>, grid, 256, 0, s, xp, nblocks, lanes, amax_out);
       else
-        amax_blocks_kernel<T, 1><<<grid, 256, 0, s>>>(xp, nblocks, lanes, amax_out);
+        launch_pdl(amax_blocks_kernel<T, 1>, grid, 256, 0, s, xp, nblocks, lanes, amax_out);
     } else {
       int grid = grid_for(nblocks, 256, 8);
-      amax_blocks_generic_kernel<T><<<grid, 256, 0, s>>>(xp, nblocks, block, amax_out);
+      launch_pdl(amax_blocks_generic_kernel<T>, grid, 256, 0, s, xp, nblocks, block, amax_out);
     }
     return launch_status();
   });

@@ -16,6 +16,7 @@ template <typename T, int PPL>
 __global__ void __launch_bounds__(256)
 awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restrict__ y,
                     int64_t nblocks, int lanes, FastDiv blocks_per_row, IntQ q) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -81,6 +82,7 @@ awq_scale_fq_kernel(const T* __restrict__ w, const T* __restrict__ s, T* __restr
 template <typename T>
 __global__ void __launch_bounds__(256)
 sq_diff_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, int64_t n, double* __restrict__ out) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   __shared__ float red[8];
@@ -140,9 +142,9 @@ extern "C" int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, i
     const T* wp = static_cast<const T*>(w);
     const T* sp = static_cast<const T*>(s);
     T* yp = static_cast<T*>(y);
-    if (ppl == 4) awq_scale_fq_kernel<T, 4><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
-    else if (ppl == 2) awq_scale_fq_kernel<T, 2><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
-    else awq_scale_fq_kernel<T, 1><<<grid, 256, 0, st>>>(wp, sp, yp, nblocks, lanes, bpr, q);
+    if (ppl == 4) launch_pdl(awq_scale_fq_kernel<T, 4>, grid, 256, 0, st, wp, sp, yp, nblocks, lanes, bpr, q);
+    else if (ppl == 2) launch_pdl(awq_scale_fq_kernel<T, 2>, grid, 256, 0, st, wp, sp, yp, nblocks, lanes, bpr, q);
+    else launch_pdl(awq_scale_fq_kernel<T, 1>, grid, 256, 0, st, wp, sp, yp, nblocks, lanes, bpr, q);
     return launch_status();
   });
 }
@@ -155,7 +157,7 @@ extern "C" int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dt
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(n / Elem<T>::kPerPack, 256 * 4, 8);
-    sq_diff_sum_kernel<T><<<grid, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), n, sum_io);
+    launch_pdl(sq_diff_sum_kernel<T>, grid, 256, 0, st, static_cast<const T*>(a), static_cast<const T*>(b), n, sum_io);
     return launch_status();
   });
 }

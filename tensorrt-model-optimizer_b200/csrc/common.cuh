@@ -27,6 +27,34 @@ namespace b200q {
 
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? B200Q_OK : B200Q_ERR_CUDA; }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// Streaming kernels are launched with programmatic stream serialisation and open with
+// pdl_prologue(): they let the NEXT kernel of the stream become resident while their own tail
+// drains, and then wait until the PREVIOUS kernel has completed and its writes are visible before
+// touching global memory.  Results and ordering are those of plain stream order; what overlaps is
+// launch latency, block scheduling and per-CTA set-up.  A predecessor that never signals (any
+// kernel of another library) simply completes first, as without the attribute.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
 int sm_count_cached();
 
 // Dispatch a generic lambda on the element type.

@@ -24,6 +24,7 @@ template <typename T, bool kScaleIsT>
 __global__ void __launch_bounds__(256)
 int4_export_pack_kernel(const T* __restrict__ w, const void* __restrict__ scales, uint8_t* __restrict__ out,
                         int64_t row_pairs, FastDiv packs_per_row, int packs_per_block, int blocks_per_row) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t total = row_pairs * packs_per_row.d;
@@ -85,10 +86,10 @@ extern "C" int b200q_int4_export_pack(const void* w, const void* scales, int sca
     int grid = grid_for(total, 256, 8);
     const T* wp = static_cast<const T*>(w);
     if (scales_are_f32)
-      int4_export_pack_kernel<T, false><<<grid, 256, 0, s>>>(wp, scales, out, rows / 2, ppr, block / P,
+      launch_pdl(int4_export_pack_kernel<T, false>, grid, 256, 0, s, wp, scales, out, rows / 2, ppr, block / P,
                                                              static_cast<int>(cols / block));
     else
-      int4_export_pack_kernel<T, true><<<grid, 256, 0, s>>>(wp, scales, out, rows / 2, ppr, block / P,
+      launch_pdl(int4_export_pack_kernel<T, true>, grid, 256, 0, s, wp, scales, out, rows / 2, ppr, block / P,
                                                             static_cast<int>(cols / block));
     return launch_status();
   });

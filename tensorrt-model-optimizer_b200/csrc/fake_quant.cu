@@ -55,6 +55,7 @@ fq_tensor_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n,
                  const float* __restrict__ amax, IntQ q) {
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
+  pdl_prologue();
   const F f = amax ? F(q, __ldg(amax)) : F(q, 1.f);
   const int64_t npack = n / P;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -89,6 +90,7 @@ fq_tensor_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n,
 template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
 e4m3_cast_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const E4m3Fq f;
@@ -113,6 +115,7 @@ template <typename T, typename F>
 __global__ void __launch_bounds__(kEwThreads)
 fq_axis_inner_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t npack, FastDiv axis,
                      FastDiv inner_packs, const float* __restrict__ amax, IntQ q) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -152,6 +155,7 @@ template <typename T, typename F>
 __global__ void __launch_bounds__(kEwThreads)
 fq_axis_cols_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t outer, int64_t axis,
                     int rows_per_band, const float* __restrict__ amax, IntQ q) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t cpack = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -187,6 +191,7 @@ template <typename T, typename F>
 __global__ void fq_axis_generic_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t n,
                                        int64_t axis, int64_t inner,
                                        const float* __restrict__ amax, IntQ q) {
+  pdl_prologue();
   using E = Elem<T>;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -201,6 +206,7 @@ template <typename T, int PPL>
 __global__ void __launch_bounds__(kEwThreads)
 fq_rows_warp_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int np, int G,
                     float* __restrict__ amax_out, IntQ q) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int lane_in_group = threadIdx.x & (G - 1);
@@ -248,6 +254,7 @@ template <typename T, int PPL>
 __global__ void __launch_bounds__(1024)
 fq_rows_cta_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int np,
                    float* __restrict__ amax_out, IntQ q) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   __shared__ uint32_t red[32];
@@ -286,8 +293,8 @@ static int launch_fq_tensor(const void* x, void* y, int64_t n, int dtype, const 
                             cudaStream_t s) {
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(n / Elem<T>::kPerPack, kEwThreads * kEwUnroll, 8);
-    fq_tensor_kernel<T, F><<<grid, kEwThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), n,
-                                                       amax, q);
+    launch_pdl(fq_tensor_kernel<T, F>, grid, kEwThreads, 0, s, static_cast<const T*>(x), static_cast<T*>(y), n,
+               amax, q);
     return launch_status();
   });
 }
@@ -303,8 +310,7 @@ static int launch_fq_axis(const void* x, void* y, int64_t outer, int64_t axis, i
     if (inner % P == 0 && n / P <= kFastDivLimit) {
       const int64_t npack = n / P;
       int grid = grid_for(npack, kEwThreads * kEwUnroll, 8);
-      fq_axis_inner_kernel<T, F><<<grid, kEwThreads, 0, s>>>(
-          xp, yp, npack, FastDiv(static_cast<uint32_t>(axis)), FastDiv(static_cast<uint32_t>(inner / P)), amax, q);
+      launch_pdl(fq_axis_inner_kernel<T, F>, grid, kEwThreads, 0, s, xp, yp, npack, FastDiv(static_cast<uint32_t>(axis)), FastDiv(static_cast<uint32_t>(inner / P)), amax, q);
     } else if (inner == 1 && axis % P == 0) {
       const int64_t cpacks = axis / P;
       const int bx = static_cast<int>((cpacks + kEwThreads - 1) / kEwThreads);
@@ -313,10 +319,10 @@ static int launch_fq_axis(const void* x, void* y, int64_t outer, int64_t axis, i
       if (bands > 65535) bands = 65535;
       const int rpb = static_cast<int>((outer + bands - 1) / bands);
       dim3 grid(bx, static_cast<unsigned>((outer + rpb - 1) / rpb));
-      fq_axis_cols_kernel<T, F><<<grid, kEwThreads, 0, s>>>(xp, yp, outer, axis, rpb, amax, q);
+      launch_pdl(fq_axis_cols_kernel<T, F>, grid, kEwThreads, 0, s, xp, yp, outer, axis, rpb, amax, q);
     } else {
       int grid = grid_for(n, 256, 8);
-      fq_axis_generic_kernel<T, F><<<grid, 256, 0, s>>>(xp, yp, n, axis, inner, amax, q);
+      launch_pdl(fq_axis_generic_kernel<T, F>, grid, 256, 0, s, xp, yp, n, axis, inner, amax, q);
     }
     return launch_status();
   });
@@ -377,18 +383,18 @@ extern "C" int b200q_fake_int_rows_dynamic(const void* x, void* y, int64_t rows,
       const int ppl = (np + G - 1) / G;
       const int64_t groups = rows;
       int grid = grid_for(groups * G, kEwThreads, 8);
-      if (ppl <= 1) fq_rows_warp_kernel<T, 1><<<grid, kEwThreads, 0, s>>>(xp, yp, rows, np, G, amax_out, q);
-      else if (ppl <= 2) fq_rows_warp_kernel<T, 2><<<grid, kEwThreads, 0, s>>>(xp, yp, rows, np, G, amax_out, q);
-      else fq_rows_warp_kernel<T, 4><<<grid, kEwThreads, 0, s>>>(xp, yp, rows, np, G, amax_out, q);
+      if (ppl <= 1) launch_pdl(fq_rows_warp_kernel<T, 1>, grid, kEwThreads, 0, s, xp, yp, rows, np, G, amax_out, q);
+      else if (ppl <= 2) launch_pdl(fq_rows_warp_kernel<T, 2>, grid, kEwThreads, 0, s, xp, yp, rows, np, G, amax_out, q);
+      else launch_pdl(fq_rows_warp_kernel<T, 4>, grid, kEwThreads, 0, s, xp, yp, rows, np, G, amax_out, q);
     } else {
       int threads = 256;
       while (threads < 1024 && threads * 4 < np) threads <<= 1;
       const int ppl = (np + threads - 1) / threads;
       int grid = grid_for(rows, 1, 2048 / threads);
-      if (ppl <= 1) fq_rows_cta_kernel<T, 1><<<grid, threads, 0, s>>>(xp, yp, rows, np, amax_out, q);
-      else if (ppl <= 2) fq_rows_cta_kernel<T, 2><<<grid, threads, 0, s>>>(xp, yp, rows, np, amax_out, q);
-      else if (ppl <= 4) fq_rows_cta_kernel<T, 4><<<grid, threads, 0, s>>>(xp, yp, rows, np, amax_out, q);
-      else fq_rows_cta_kernel<T, 8><<<grid, threads, 0, s>>>(xp, yp, rows, np, amax_out, q);
+      if (ppl <= 1) launch_pdl(fq_rows_cta_kernel<T, 1>, grid, threads, 0, s, xp, yp, rows, np, amax_out, q);
+      else if (ppl <= 2) launch_pdl(fq_rows_cta_kernel<T, 2>, grid, threads, 0, s, xp, yp, rows, np, amax_out, q);
+      else if (ppl <= 4) launch_pdl(fq_rows_cta_kernel<T, 4>, grid, threads, 0, s, xp, yp, rows, np, amax_out, q);
+      else launch_pdl(fq_rows_cta_kernel<T, 8>, grid, threads, 0, s, xp, yp, rows, np, amax_out, q);
     }
     return launch_status();
   });
@@ -403,7 +409,7 @@ extern "C" int b200q_fake_e4m3_tensor(const void* x, void* y, int64_t n, int dty
   if (amax) return launch_fq_tensor<E4m3Fq>(x, y, n, dtype, amax, IntQ{0.f, 0.f}, s);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(n / Elem<T>::kPerPack, kEwThreads, 8);
-    e4m3_cast_kernel<T><<<grid, kEwThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), n);
+    launch_pdl(e4m3_cast_kernel<T>, grid, kEwThreads, 0, s, static_cast<const T*>(x), static_cast<T*>(y), n);
     return launch_status();
   });
 }

@@ -42,6 +42,7 @@ template <typename T, bool kAllShared>
 __global__ void __launch_bounds__(kHistThreads)
 hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
                     int smem_bins, int replicas, unsigned long long* __restrict__ counts) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   extern __shared__ uint32_t sh[];
@@ -152,6 +153,7 @@ __global__ void __launch_bounds__(kHistThreads)
 hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
                       Hist16Layout lay, unsigned long long* __restrict__ counts) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
+  pdl_prologue();
   extern __shared__ uint32_t sh[];
   uint4* sh4 = reinterpret_cast<uint4*>(sh);
   const int vwords = lay.values << lay.rshift;             // a multiple of 4 (host pads `values`)
@@ -254,6 +256,7 @@ __global__ void __launch_bounds__(kPctThreads)
 hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
                        const float* __restrict__ edges, float bin_width, double frac,
                        float* __restrict__ amax_out) {
+  pdl_prologue();
   __shared__ double q[kPctChunk];
   __shared__ unsigned long long warp_sums[kPctThreads / 32];
   __shared__ unsigned long long total_s;
@@ -308,6 +311,7 @@ __device__ __forceinline__ unsigned long long ent_count(const unsigned long long
 __global__ void __launch_bounds__(kEntThreads)
 hist_entropy_kernel(const unsigned long long* __restrict__ counts, int nbins, int nlev, int start_bin,
                     int stride, double* __restrict__ divs) {
+  pdl_prologue();
   extern __shared__ unsigned long long ent_sh[];   // [nlev] mass | [nlev] non-empty bins (as u64)
   unsigned long long* mass = ent_sh;
   unsigned long long* cnt = ent_sh + nlev;
@@ -381,6 +385,7 @@ __global__ void hist_entropy_pick_kernel(const double* __restrict__ divs, int nc
 __global__ void __launch_bounds__(kEntThreads)
 hist_mse_kernel(const unsigned long long* __restrict__ counts, int nbins, const float* __restrict__ edges,
                 double bound, int start_bin, int stride, double* __restrict__ errs) {
+  pdl_prologue();
   __shared__ double red[kEntThreads / 32];
   const int i = start_bin + static_cast<int>(blockIdx.x) * stride;
   const double amax = (static_cast<double>(edges[i + 1]) + static_cast<double>(edges[i])) / 2.0;
@@ -453,7 +458,8 @@ static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, flo
         for (int64_t off = 0; off < n; off += chunk) {
           const int64_t len = n - off < chunk ? n - off : chunk;
           const int grid = grid_for(len / 8, kHistThreads * 4, 1);
-          kern<<<grid, kHistThreads, smem, s>>>(static_cast<const T*>(x) + off, len, nbins, range_max, open, lay, counts);
+          launch_pdl(kern, grid, kHistThreads, smem, s, static_cast<const T*>(x) + off, len, nbins, range_max, open,
+                     lay, counts);
         }
         return launch_status();
       } else {
@@ -473,7 +479,7 @@ static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, flo
   for (int64_t off = 0; off < n; off += chunk) {
     const int64_t len = n - off < chunk ? n - off : chunk;
     const int grid = grid_for(len / 4, kHistThreads * 4, 1);
-    kern<<<grid, kHistThreads, smem, s>>>(static_cast<const float*>(x) + off, len, nbins, range_max, open, smem_bins,
+    launch_pdl(kern, grid, kHistThreads, smem, s, static_cast<const float*>(x) + off, len, nbins, range_max, open, smem_bins,
                                           replicas, counts);
   }
   return launch_status();

@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(256)
 int4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes,
                      const T* __restrict__ scales_in, T* __restrict__ scales_out,
                      uint8_t* __restrict__ packed) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -115,6 +116,7 @@ template <typename T>
 __global__ void int4_quantize_generic_kernel(const T* __restrict__ x, int64_t nblocks, int block,
                                              const T* __restrict__ scales_in,
                                              T* __restrict__ scales_out, uint8_t* __restrict__ packed) {
+  pdl_prologue();
   using E = Elem<T>;
   for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblocks;
        b += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -141,6 +143,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 int4_dequantize_kernel(const uint8_t* __restrict__ packed, const T* __restrict__ scales,
                        T* __restrict__ y, int64_t nbytes, int bytes_per_block) {
+  pdl_prologue();
   using E = Elem<T>;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < nbytes; j += stride) {
@@ -177,11 +180,11 @@ extern "C" int b200q_int4_quantize(const void* x, int64_t nblocks, int block, in
       const int ppl = packs >= 2 ? 2 : 1;
       const int lanes = packs / ppl;
       int grid = grid_for(nblocks * lanes, 256, 8);
-      if (ppl == 2) int4_quantize_kernel<T, 2><<<grid, 256, 0, s>>>(xp, nblocks, lanes, sin, sout, packed);
-      else int4_quantize_kernel<T, 1><<<grid, 256, 0, s>>>(xp, nblocks, lanes, sin, sout, packed);
+      if (ppl == 2) launch_pdl(int4_quantize_kernel<T, 2>, grid, 256, 0, s, xp, nblocks, lanes, sin, sout, packed);
+      else launch_pdl(int4_quantize_kernel<T, 1>, grid, 256, 0, s, xp, nblocks, lanes, sin, sout, packed);
     } else {
       int grid = grid_for(nblocks, 128, 16);
-      int4_quantize_generic_kernel<T><<<grid, 128, 0, s>>>(xp, nblocks, block, sin, sout, packed);
+      launch_pdl(int4_quantize_generic_kernel<T>, grid, 128, 0, s, xp, nblocks, block, sin, sout, packed);
     }
     return launch_status();
   });
@@ -196,7 +199,7 @@ extern "C" int b200q_int4_dequantize(const uint8_t* packed, const void* scales, 
   return B200Q_DISPATCH(dtype, [&] {
     const int64_t nbytes = nblocks * (block / 2);
     int grid = grid_for(nbytes, 256, 8);
-    int4_dequantize_kernel<T><<<grid, 256, 0, s>>>(packed, static_cast<const T*>(scales),
+    launch_pdl(int4_dequantize_kernel<T>, grid, 256, 0, s, packed, static_cast<const T*>(scales),
                                                    static_cast<T*>(y), nbytes, block / 2);
     return launch_status();
   });

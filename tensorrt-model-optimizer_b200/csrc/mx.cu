@@ -58,6 +58,7 @@ template <int FMT> __device__ __forceinline__ float2 mx_round2(float a, float b)
 template <typename T, int FMT, int PPL>
 __global__ void __launch_bounds__(256)
 mx_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks, int lanes) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -101,6 +102,7 @@ template <typename T, int PPL>
 __global__ void __launch_bounds__(256)
 mxfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, uint8_t* __restrict__ packed,
                       uint8_t* __restrict__ scales) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -152,8 +154,8 @@ static int launch_mx_fake(const T* x, T* y, int64_t nblocks, int block, cudaStre
   const int ppl = packs >= 2 ? 2 : 1;
   const int lanes = packs / ppl;
   int grid = grid_for(nblocks * lanes, 256, 8);
-  if (ppl == 2) mx_fake_kernel<T, FMT, 2><<<grid, 256, 0, s>>>(x, y, nblocks, lanes);
-  else mx_fake_kernel<T, FMT, 1><<<grid, 256, 0, s>>>(x, y, nblocks, lanes);
+  if (ppl == 2) launch_pdl(mx_fake_kernel<T, FMT, 2>, grid, 256, 0, s, x, y, nblocks, lanes);
+  else launch_pdl(mx_fake_kernel<T, FMT, 1>, grid, 256, 0, s, x, y, nblocks, lanes);
   return launch_status();
 }
 
@@ -197,8 +199,8 @@ extern "C" int b200q_mxfp4_quantize(const void* x, int64_t nblocks, int block, i
     const int lanes = packs / ppl;
     int grid = grid_for(nblocks * lanes, 256, 8);
     const T* xp = static_cast<const T*>(x);
-    if (ppl == 2) mxfp4_quantize_kernel<T, 2><<<grid, 256, 0, s>>>(xp, nblocks, lanes, packed, scales);
-    else mxfp4_quantize_kernel<T, 1><<<grid, 256, 0, s>>>(xp, nblocks, lanes, packed, scales);
+    if (ppl == 2) launch_pdl(mxfp4_quantize_kernel<T, 2>, grid, 256, 0, s, xp, nblocks, lanes, packed, scales);
+    else launch_pdl(mxfp4_quantize_kernel<T, 1>, grid, 256, 0, s, xp, nblocks, lanes, packed, scales);
     return launch_status();
   });
 }

@@ -281,6 +281,7 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __r
                       bool global_is_s2, const uint8_t* __restrict__ scales_in,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
                       float* __restrict__ s2_out, bool pair) {
+  pdl_prologue();
   const float g = __ldg(global);
   const Nvfp4Tensor tn(global_is_s2 ? g : __fdiv_rn(g, 2688.f));
   if (s2_out && blockIdx.x == 0 && threadIdx.x == 0) *s2_out = tn.s2;
@@ -305,6 +306,7 @@ template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_fake_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t nblocks,
                   const float* __restrict__ amax, bool pair) {
+  pdl_prologue();
   const Nvfp4Tensor tn(__fdiv_rn(__ldg(amax), 2688.f));
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t b0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b0 < nblocks;
@@ -338,6 +340,7 @@ template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                         const float* __restrict__ s2p, T* __restrict__ y, int64_t nblocks, bool pair) {
+  pdl_prologue();
   const float s2 = __ldg(s2p);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
@@ -364,6 +367,7 @@ __device__ __forceinline__ int find_tensor(const b200q_nvfp4_desc* __restrict__ 
 template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_group_amax_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, int64_t total_tiles) {
+  pdl_prologue();
   __shared__ uint32_t red[32];
   const int64_t per = (total_tiles + gridDim.x - 1) / gridDim.x;
   const int64_t t0 = blockIdx.x * per, t1 = min(total_tiles, t0 + per);
@@ -399,6 +403,7 @@ nvfp4_group_amax_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, int64
 template <typename T>
 __global__ void __launch_bounds__(kNvThreads)
 nvfp4_group_quantize_kernel(const b200q_nvfp4_desc* __restrict__ descs, int n, int64_t total_tiles) {
+  pdl_prologue();
   const int64_t per = (total_tiles + gridDim.x - 1) / gridDim.x;
   const int64_t t0 = blockIdx.x * per, t1 = min(total_tiles, t0 + per);
   if (t0 >= t1) return;
@@ -448,9 +453,8 @@ int nvfp4_launch_quantize(const void* x, int64_t nunits, int dtype, const float*
                           int flags, bool pair, cudaStream_t s) {
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nunits, kNvTileBlocks, 8);
-    nvfp4_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(
-        static_cast<const T*>(x), nunits, global, (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0,
-        scales_in, packed, scales, s2_out, pair);
+    launch_pdl(nvfp4_quantize_kernel<T>, grid, kNvThreads, 0, s, static_cast<const T*>(x), nunits, global,
+               (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0, scales_in, packed, scales, s2_out, pair);
     return launch_status();
   });
 }
@@ -459,8 +463,8 @@ int nvfp4_launch_fake(const void* x, void* y, int64_t nunits, int dtype, const f
                       cudaStream_t s) {
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nunits, kNvTileBlocks, 8);
-    nvfp4_fake_kernel<T><<<grid, kNvThreads, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(y), nunits, amax,
-                                                     pair);
+    launch_pdl(nvfp4_fake_kernel<T>, grid, kNvThreads, 0, s, static_cast<const T*>(x), static_cast<T*>(y), nunits,
+               amax, pair);
     return launch_status();
   });
 }
@@ -469,7 +473,7 @@ int nvfp4_launch_dequantize(const uint8_t* packed, const uint8_t* scales, const 
                             int64_t nunits, int dtype, bool pair, cudaStream_t s) {
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nunits, kNvThreads, 8);
-    nvfp4_dequantize_kernel<T><<<grid, kNvThreads, 0, s>>>(packed, scales, s2, static_cast<T*>(y), nunits, pair);
+    launch_pdl(nvfp4_dequantize_kernel<T>, grid, kNvThreads, 0, s, packed, scales, s2, static_cast<T*>(y), nunits, pair);
     return launch_status();
   });
 }
@@ -519,7 +523,7 @@ extern "C" int b200q_nvfp4_group_amax(const b200q_nvfp4_desc* descs, int n, int6
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(total_tiles, 1, kNvCtasPerSm);
-    nvfp4_group_amax_kernel<T><<<grid, kNvThreads, 0, s>>>(descs, n, total_tiles);
+    launch_pdl(nvfp4_group_amax_kernel<T>, grid, kNvThreads, 0, s, descs, n, total_tiles);
     return launch_status();
   });
 }
@@ -530,7 +534,7 @@ extern "C" int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(total_tiles, 1, kNvCtasPerSm);
-    nvfp4_group_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(descs, n, total_tiles);
+    launch_pdl(nvfp4_group_quantize_kernel<T>, grid, kNvThreads, 0, s, descs, n, total_tiles);
     return launch_status();
   });
 }
@@ -607,8 +611,8 @@ extern "C" int b200q_nvfp4_group_quantize_noalloc(const b200q_nvfp4_desc* host_d
   if (cudaMemsetAsync(d_amax, 0, sizeof(float) * n, s) != cudaSuccess) return B200Q_ERR_CUDA;
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(tiles, 1, 8);
-    nvfp4_group_amax_kernel<T><<<grid, kNvThreads, 0, s>>>(d_descs, n, tiles);
-    nvfp4_group_quantize_kernel<T><<<grid, kNvThreads, 0, s>>>(d_descs, n, tiles);
+    launch_pdl(nvfp4_group_amax_kernel<T>, grid, kNvThreads, 0, s, d_descs, n, tiles);
+    launch_pdl(nvfp4_group_quantize_kernel<T>, grid, kNvThreads, 0, s, d_descs, n, tiles);
     return launch_status();
   });
 }

@@ -31,6 +31,7 @@ __global__ void __launch_bounds__(128)
 nvfp4_blocks_kernel(const T* __restrict__ x, int64_t nblocks, int block, const float* __restrict__ global,
                     bool global_is_s2, const uint8_t* __restrict__ scales_in, uint8_t* __restrict__ packed,
                     uint8_t* __restrict__ scales, float* __restrict__ s2_out, T* __restrict__ y) {
+  pdl_prologue();
   using E = Elem<T>;
   const float g = __ldg(global);
   const float s2 = global_is_s2 ? g : __fdiv_rn(g, 2688.f);
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(256)
 nvfp4_blocks_dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                                const float* __restrict__ s2p, T* __restrict__ y, int64_t nbytes,
                                int bytes_per_block) {
+  pdl_prologue();
   using E = Elem<T>;
   const float s2 = __ldg(s2p);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -93,7 +95,7 @@ extern "C" int b200q_nvfp4_quantize_blocks(const void* x, int64_t nblocks, int b
     return nvfp4_launch_quantize(x, nblocks * 2, dtype, global, scales_in, packed, scales, s2_out, flags, true, s);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nblocks, 128, 16);
-    nvfp4_blocks_kernel<T, 0><<<grid, 128, 0, s>>>(static_cast<const T*>(x), nblocks, block, global,
+    launch_pdl(nvfp4_blocks_kernel<T, 0>, grid, 128, 0, s, static_cast<const T*>(x), nblocks, block, global,
                                                    (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0, scales_in, packed,
                                                    scales, s2_out, nullptr);
     return launch_status();
@@ -110,7 +112,7 @@ extern "C" int b200q_nvfp4_fake_blocks(const void* x, void* y, int64_t nblocks, 
     return nvfp4_launch_fake(x, y, nblocks * 2, dtype, amax, true, s);
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nblocks, 128, 16);
-    nvfp4_blocks_kernel<T, 1><<<grid, 128, 0, s>>>(static_cast<const T*>(x), nblocks, block, amax, false, nullptr,
+    launch_pdl(nvfp4_blocks_kernel<T, 1>, grid, 128, 0, s, static_cast<const T*>(x), nblocks, block, amax, false, nullptr,
                                                    nullptr, nullptr, nullptr, static_cast<T*>(y));
     return launch_status();
   });
@@ -127,7 +129,7 @@ extern "C" int b200q_nvfp4_dequantize_blocks(const uint8_t* packed, const uint8_
   return B200Q_DISPATCH(dtype, [&] {
     const int64_t nbytes = nblocks * (block / 2);
     int grid = grid_for(nbytes, 256, 8);
-    nvfp4_blocks_dequantize_kernel<T><<<grid, 256, 0, s>>>(packed, scales, s2, static_cast<T*>(y), nbytes, block / 2);
+    launch_pdl(nvfp4_blocks_dequantize_kernel<T>, grid, 256, 0, s, packed, scales, s2, static_cast<T*>(y), nbytes, block / 2);
     return launch_status();
   });
 }

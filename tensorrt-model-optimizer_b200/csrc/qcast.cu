@@ -27,6 +27,7 @@ template <typename T, typename C>
 __global__ void __launch_bounds__(256)
 qcast_inner_kernel(const T* __restrict__ x, const T* __restrict__ scales, uint8_t* __restrict__ q,
                    int64_t npack, FastDiv axis, FastDiv inner_packs) {
+  pdl_prologue();
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
@@ -62,6 +63,7 @@ qcast_inner_kernel(const T* __restrict__ x, const T* __restrict__ scales, uint8_
 template <typename T, typename C>
 __global__ void qcast_generic_kernel(const T* __restrict__ x, const T* __restrict__ scales,
                                      uint8_t* __restrict__ q, int64_t n, int64_t axis, int64_t inner) {
+  pdl_prologue();
   using E = Elem<T>;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -84,11 +86,11 @@ static int launch_qcast(const void* x, const void* scales, uint8_t* q, int64_t o
     if (in % P == 0 && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && n / P <= kFastDivLimit) {
       const int64_t npack = n / P;
       int grid = grid_for(npack, 512, 8);
-      qcast_inner_kernel<T, C><<<grid, 256, 0, s>>>(xp, sp, q, npack, FastDiv(static_cast<uint32_t>(ax)),
+      launch_pdl(qcast_inner_kernel<T, C>, grid, 256, 0, s, xp, sp, q, npack, FastDiv(static_cast<uint32_t>(ax)),
                                                     FastDiv(static_cast<uint32_t>(in / P)));
     } else {
       int grid = grid_for(n, 256, 8);
-      qcast_generic_kernel<T, C><<<grid, 256, 0, s>>>(xp, sp, q, n, ax, in);
+      launch_pdl(qcast_generic_kernel<T, C>, grid, 256, 0, s, xp, sp, q, n, ax, in);
     }
     return launch_status();
   });
