@@ -514,13 +514,30 @@ class SequentialQuantizer(nn.Sequential):
     def get_modelopt_state(self):
         return {"num_quantizers": len(self), "is_sequential_quantizer": True}
 
+    # the first member answers for the container; setting writes through to every member
+    @property
+    def is_enabled(self):
+        return self[0].is_enabled
+
+    @property
+    def fake_quant(self):
+        return self[0].fake_quant
+
     def disable(self):
         for q in self:
             q.disable()
 
+    def enable(self):
+        for q in self:
+            q.enable()
+
     def reset_amax(self):
         for q in self:
             q.reset_amax()
+
+    def load_calib_amax(self, *args, **kwargs):
+        for q in self:
+            q.load_calib_amax(*args, **kwargs)
 
     def set_from_attribute_config(self, attributes):
         if not isinstance(attributes, (list, tuple)):

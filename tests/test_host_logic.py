@@ -220,3 +220,64 @@ def _failing_rank_job(rank, world):
 
 def test_missing_rank_surfaces_as_error():
     _spawn(_failing_rank_job)
+
+
+def test_export_format_detection_and_state_dict_postprocess():
+    """Host-only parts of the checkpoint export: format names from quantiser attributes, state-dict
+    key filtering and renaming (no kernels involved)."""
+    from b200q import export
+    from b200q.nn import QuantLinear, SequentialQuantizer
+
+    def lin(wcfg, icfg):
+        m = torch.nn.Sequential(torch.nn.Linear(32, 16, bias=False))
+        mtq.replace_quant_module(m)
+        mtq.set_quantizer_by_cfg(m, {"*weight_quantizer": wcfg, "*input_quantizer": icfg, "default": {"enable": False}})
+        assert isinstance(m[0], QuantLinear)
+        return m[0]
+
+    nv = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}, "enable": True}
+    cases = [
+        ({"num_bits": (4, 3), "axis": None}, {"num_bits": (4, 3), "axis": None}, "fp8"),
+        ({"num_bits": (4, 3), "axis": 0}, {"enable": False}, "fp8_pc_pt"),
+        ({"num_bits": (4, 3), "block_sizes": {-1: 128, -2: 128}}, {"enable": False}, "fp8_pb_wo"),
+        ({"num_bits": 8, "axis": 0}, {"num_bits": 8, "axis": None}, "int8_sq"),
+        ({"num_bits": 8, "axis": 0}, {"enable": False}, "int8_wo"),
+        ({"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}}, {"enable": False}, "int4_awq"),
+        (nv, nv, "nvfp4"),
+        ({"enable": False}, {"enable": False}, None),
+    ]
+    for wcfg, icfg, want in cases:
+        m = lin(wcfg, icfg)
+        assert export.get_quantization_format(m) == want, (wcfg, want)
+    m = lin({"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}}, {"enable": False})
+    assert export.get_weight_block_size(m) == 128
+    m = lin(nv, nv)
+    m.input_quantizer.register_buffer("_pre_quant_scale", torch.ones(32))
+    assert export.get_quantization_format(m) == "nvfp4_awq"
+    w4a8 = lin([{"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+                {"num_bits": (4, 3), "axis": None, "enable": True}], {"num_bits": (4, 3), "axis": None})
+    assert isinstance(w4a8.weight_quantizer, SequentialQuantizer)
+    assert export.get_quantization_format(w4a8) == "w4a8_awq" and export.get_weight_block_size(w4a8) == 128
+
+    t = torch.arange(4.0)
+    sd = {"a.weight": t.clone(), "a.weight_scale": torch.ones(1, 2, 3), "a.input_quantizer._amax": t.clone(),
+          "a.input_quantizer._pre_quant_scale": t.clone() + 1, "a.weight_quantizer._amax": t.clone(),
+          "a.weight_quantizer._scale": t.clone(), "a.output_quantizer._amax": t.clone(), "b.weight": t.clone() + 2}
+    sd["b.tied"] = sd["b.weight"]
+    out = export.postprocess_state_dict(sd)
+    assert sorted(out) == ["a.pre_quant_scale", "a.weight", "a.weight_scale", "b.weight"]
+    assert out["a.weight_scale"].shape == (2, 3) and torch.equal(out["a.pre_quant_scale"], t + 1)
+
+
+def test_every_config_converts_a_model_on_cpu():
+    """Conversion (module replacement and quantiser attributes) is host logic: every named
+    configuration applies to a small model without a GPU."""
+    for name in sorted(mtq.config.choices):
+        m = MLP()
+        mtq.replace_quant_module(m)
+        cfg = getattr(mtq, name)
+        mtq.set_quantizer_by_cfg(m, cfg["quant_cfg"])
+        qs = [q for _, q in m.named_modules() if isinstance(q, TensorQuantizer)]
+        assert qs, name
+        algo = cfg["algorithm"]
+        assert algo is None or isinstance(algo, (str, dict)), name
