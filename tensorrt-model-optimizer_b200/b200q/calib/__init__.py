@@ -1,8 +1,9 @@
 """Calibrators with the collect / compute_amax / reset contract of
 ``modelopt/torch/quantization/calib/``."""
+from .bias import BiasCalibrator
 from .calibrator import _Calibrator
 from .histogram import HistogramCalibrator, calibrate_weights
 from .max import MaxCalibrator
 from .mse import MseCalibrator
 
-__all__ = ["_Calibrator", "MaxCalibrator", "MseCalibrator", "HistogramCalibrator", "calibrate_weights"]
+__all__ = ["_Calibrator", "BiasCalibrator", "MaxCalibrator", "MseCalibrator", "HistogramCalibrator", "calibrate_weights"]

@@ -12,6 +12,7 @@ __all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG
            "INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG",
            "FP8_PER_CHANNEL_PER_TOKEN_CFG", "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG", "W4A8_AWQ_BETA_CFG", "W4A8_NVFP4_FP8_CFG",
            "W4A8_MXFP4_FP8_CFG", "NVFP4_MLP_WEIGHT_ONLY_CFG", "NVFP4_MLP_ONLY_CFG", "MXFP4_MLP_WEIGHT_ONLY_CFG",
+           "FP8_KV_CFG", "FP8_AFFINE_KV_CFG", "NVFP4_KV_CFG", "NVFP4_AFFINE_KV_CFG",
            "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG",
            "choices", "need_calibration"]
 
@@ -165,6 +166,22 @@ MXFP4_MLP_WEIGHT_ONLY_CFG = {
                   **_default_disabled_quantizer_cfg},
     "algorithm": None,
 }
+
+
+# KV-cache quantisers (`*[kv]_bmm_quantizer`) exist on attention modules converted by a model
+# plugin; on models without them these patterns match nothing.
+FP8_KV_CFG = {"quant_cfg": {"*[kv]_bmm_quantizer": {"num_bits": (4, 3), "axis": None, "enable": True},
+                            "default": {"enable": False}}, "algorithm": "max"}
+FP8_AFFINE_KV_CFG = {"quant_cfg": {"*[kv]_bmm_quantizer": {"num_bits": (4, 3), "axis": None,
+                                                           "bias": {-2: None, -4: None, "type": "static"}},
+                                   "default": {"enable": False}}, "algorithm": "max"}
+NVFP4_KV_CFG = {"quant_cfg": {"*[kv]_bmm_quantizer": {"num_bits": (2, 1), "axis": None, "enable": True,
+                                                      "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}},
+                              "default": {"enable": False}}, "algorithm": "max"}
+NVFP4_AFFINE_KV_CFG = {"quant_cfg": {"*[kv]_bmm_quantizer": {"num_bits": (2, 1), "axis": None, "enable": True,
+                                                             "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
+                                                             "bias": {-2: None, -4: None, "type": "static"}},
+                                     "default": {"enable": False}}, "algorithm": "max"}
 
 
 def _mx(num_bits):

@@ -48,6 +48,8 @@ def finish_stats_collection(model: nn.Module, method: str | None = None):
                     m.load_calib_amax(method)
             elif cal.compute_amax() is not None:
                 m.load_calib_amax()
+        if m.bias_calibrator is not None and m.bias_type == "static":
+            m.load_calib_bias()
         m.enable_quant()
         m.disable_calib()
 

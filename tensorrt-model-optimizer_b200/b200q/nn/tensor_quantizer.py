@@ -65,8 +65,9 @@ class TensorQuantizer(nn.Module):
         self._trt_high_precision_dtype = c.trt_high_precision_dtype
         self._rotate = c.rotate
         self._pass_through_bwd = c.pass_through_bwd
-        if self._bias is not None or self._rotate:
-            raise NotImplementedError("bias calibration and rotation are not part of the accelerated path")
+        if self._rotate:
+            raise NotImplementedError("rotation is not part of the accelerated path")
+        self._bias_calibrator = None
         self._calibrator = self._make_calibrator(c.calibrator)
         for attr in ("_block_reshape_size", "_padding", "_slices", "_original_shape", "_amax_shape_for_export"):
             if hasattr(self, attr):
@@ -175,6 +176,7 @@ class TensorQuantizer(nn.Module):
             delattr(self, "_amax")
         if self._calibrator is not None:
             self._calibrator.reset()
+        self.reset_bias()
 
     @property
     def step_size(self):
@@ -183,6 +185,66 @@ class TensorQuantizer(nn.Module):
             return None
         assert isinstance(self._num_bits, int), "Step size is not defined for non-integer quantization."
         return self._amax / (2.0 ** (self._num_bits - 1 + int(self._unsigned)) - 1.0)
+
+    # ---- affine quantisation: a bias subtracted before and added back after quantisation ------
+    # (reference tensor_quantizer.py:262-378,491-549,1098-1108)
+    @property
+    def bias(self):
+        return self._bias
+
+    @property
+    def bias_method(self):
+        return None if self._bias is None else self._bias.get("method", "mean")
+
+    @property
+    def bias_type(self):
+        return None if self._bias is None else self._bias.get("type", "static")
+
+    @property
+    def bias_value(self):
+        return getattr(self, "_bias_value", None)
+
+    @bias_value.setter
+    def bias_value(self, value):
+        assert value is not None, "bias cannot be set to None."
+        if not isinstance(value, torch.Tensor):
+            value = torch.tensor(value)
+        if not hasattr(self, "_bias_value"):
+            self.register_buffer("_bias_value", value.clone().detach())
+        else:
+            if self._bias_value.shape != value.shape:
+                raise RuntimeError("Changing shape when setting bias is not allowed.")
+            self._bias_value.data.copy_(value.clone().detach().to(self._bias_value.device))
+
+    @property
+    def bias_calibrator(self):
+        if self._bias_calibrator is None and self._bias is not None:
+            self._bias_axis = tuple(k for k in self._bias if isinstance(k, int))
+            self._bias_calibrator = calib.BiasCalibrator(method=self.bias_method, axis=self._bias_axis)
+        return self._bias_calibrator
+
+    def reset_bias(self):
+        if hasattr(self, "_bias_value"):
+            delattr(self, "_bias_value")
+        if self._bias_calibrator is not None:
+            self._bias_calibrator.reset()
+
+    def load_calib_bias(self, *args, **kwargs):
+        assert self.bias_calibrator is not None, "Bias calibrator not created."
+        b = self.bias_calibrator.compute_bias(*args, **kwargs)
+        if b is None:
+            raise RuntimeError("Bias calibrator returned None. This usually happens when bias calibrator "
+                               "hasn't seen any tensor.")
+        self.bias_value = b
+
+    def _get_bias(self, inputs):
+        if self.bias_calibrator is None:
+            return None
+        if self.bias_type == "static":
+            return getattr(self, "_bias_value", None)
+        if self.bias_type == "dynamic":
+            return self.bias_calibrator.compute_dynamic_bias(inputs)
+        raise ValueError(f"Unsupported bias type: {self.bias_type}")
 
     # ---- switches ----------------------------------------------------------------------------
     def disable(self):
@@ -212,6 +274,9 @@ class TensorQuantizer(nn.Module):
 
     # ---- calibration -------------------------------------------------------------------------
     def collect(self, inputs):
+        if self.bias_calibrator is not None and self.bias_type == "static":
+            self.bias_calibrator.collect(inputs)
+            inputs = inputs - self.bias_calibrator.compute_bias()
         self._calibrator.collect(inputs)
 
     def load_calib_amax(self, *args, **kwargs):
@@ -353,13 +418,13 @@ class TensorQuantizer(nn.Module):
             if block is None:
                 raise ValueError("block size for dynamic quantization not found.")
             amax = None if self.is_mx_format else self._get_amax(inputs)
-            return dynamic_block_quant(inputs, block, amax, None, self._num_bits, bs.get("scale_bits"),
+            return dynamic_block_quant(inputs, block, amax, self._get_bias(inputs), self._num_bits, bs.get("scale_bits"),
                                        self._trt_high_precision_dtype, "dynamic", self._pass_through_bwd)
         if isinstance(self._num_bits, tuple):
             E, M = self._num_bits  # noqa: N806
-            return scaled_e4m3(inputs, self._get_amax(inputs), None, E, M, self._trt_high_precision_dtype,
-                               self._pass_through_bwd)
-        if (not hasattr(self, "_amax") and inputs.dim() == 2 and self._axis in ((0,), 0, [0])
+            return scaled_e4m3(inputs, self._get_amax(inputs), self._get_bias(inputs), E, M,
+                               self._trt_high_precision_dtype, self._pass_through_bwd)
+        if (self._bias is None and not hasattr(self, "_amax") and inputs.dim() == 2 and self._axis in ((0,), 0, [0])
                 and not inputs.requires_grad):
             # dynamic per-row amax (static block quantisation before calibration, per-row weights):
             # abs-max and quantisation fused in one pass
@@ -368,7 +433,7 @@ class TensorQuantizer(nn.Module):
             except ops._cabi.B200QError as e:  # row shape outside the fused kernel: two passes below
                 if e.status != -7:
                     raise
-        return fake_tensor_quant(inputs, self._get_amax(inputs), None, self._num_bits, self._unsigned,
+        return fake_tensor_quant(inputs, self._get_amax(inputs), self._get_bias(inputs), self._num_bits, self._unsigned,
                                  self._narrow_range, self._trt_high_precision_dtype, self._pass_through_bwd,
                                  bs.get(-1) if bs else None,
                                  self._axis[0] if isinstance(self._axis, tuple) else self._axis)

@@ -333,6 +333,34 @@ def golden_mx_known_answers(out, ref_root):
     np.savez_compressed(out / "mx_known_answers.npz", **cases)
 
 
+def golden_bias(out):
+    """Affine (bias) quantisation through the reference's TensorQuantizer on CPU: static mean,
+    static max_min and dynamic bias, INT8 and FP8, two calibration batches of a 4-D tensor."""
+    from modelopt.torch.quantization.config import QuantizerAttributeConfig
+    from modelopt.torch.quantization.nn import TensorQuantizer
+
+    cases = {}
+    xs = [gen((2, 3, 8, 16), "f32", 1200 + i, scale=1.0 + i) + 0.75 * (i + 1) for i in range(2)]
+    for i, x in enumerate(xs):
+        cases[f"x{i}"] = bits(x)
+    cfgs = {"fp8_mean": dict(num_bits=(4, 3), axis=None, bias={-2: None, -4: None, "type": "static"}),
+            "int8_maxmin": dict(num_bits=8, axis=None, bias={-1: None, "type": "static", "method": "max_min"}),
+            "int8_dynamic": dict(num_bits=8, axis=None, bias={-2: None, "type": "dynamic"})}
+    for tag, kw in cfgs.items():
+        q = TensorQuantizer(QuantizerAttributeConfig(**kw))
+        q.enable_calib(); q.disable_quant()
+        for x in xs:
+            q(x)
+        q.load_calib_amax()
+        if q.bias_type == "static":
+            q.load_calib_bias()
+            cases[f"{tag}_bias"] = bits(q._bias_value)
+        q.enable_quant(); q.disable_calib()
+        cases[f"{tag}_amax"] = bits(q._amax.reshape(-1))
+        cases[f"{tag}_y"] = bits(q(xs[1]))
+    np.savez_compressed(out / "bias.npz", **cases)
+
+
 def golden_reference_test_tables(out, ref_root):
     """Known answers held by the reference's own GPU tests, taken from their source as data:
 
@@ -418,7 +446,7 @@ def main():
     import_reference(args.ref)
     torch.manual_seed(0)
     fns = {"fake_int": golden_fake_int, "fake_e4m3": golden_fake_e4m3, "nvfp4": golden_nvfp4,
-           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export, "mxfp4": golden_mxfp4}
+           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export, "mxfp4": golden_mxfp4, "bias": golden_bias}
     for name, fn in fns.items():
         if args.only and name not in args.only.split(","):
             continue

@@ -419,3 +419,29 @@ def test_more_reference_configs_quantize_and_run(mtq, name):
     assert torch.isfinite(y).all()
     rel = (y - ref).abs().mean() / ref.abs().mean()
     assert rel < (0.35 if "W4" in name or "INT4" in name else 0.1), float(rel)
+
+
+def test_affine_bias_quantization_matches_reference(mtq):
+    """Static mean / static mid-range / dynamic bias through TensorQuantizer (calibrate on two
+    batches, then quantise) against the reference's CPU results."""
+    g = load("bias")
+    xs = [torch.from_numpy(g[f"x{i}"]).cuda() for i in range(2)]
+    cfgs = {"fp8_mean": dict(num_bits=(4, 3), axis=None, bias={-2: None, -4: None, "type": "static"}),
+            "int8_maxmin": dict(num_bits=8, axis=None, bias={-1: None, "type": "static", "method": "max_min"}),
+            "int8_dynamic": dict(num_bits=8, axis=None, bias={-2: None, "type": "dynamic"})}
+    for tag, kw in cfgs.items():
+        q = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(**kw)).cuda()
+        q.enable_calib(); q.disable_quant()
+        for x in xs:
+            q(x)
+        q.load_calib_amax()
+        if q.bias_type == "static":
+            q.load_calib_bias()
+            assert np.allclose(q._bias_value.cpu().numpy(), g[f"{tag}_bias"], rtol=1e-6, atol=1e-7), tag
+        q.enable_quant(); q.disable_calib()
+        assert np.allclose(q._amax.float().cpu().numpy().reshape(-1), g[f"{tag}_amax"], rtol=1e-6), tag
+        y = q(xs[1]).cpu().numpy()
+        ref = g[f"{tag}_y"]
+        # the bias is a mean formed in another summation order: a last-bit difference of the bias can move
+        # single elements across a rounding boundary of the quantiser
+        assert np.mean(np.abs(y - ref) > 1e-5) < 2e-3 and np.abs(y - ref).max() < 0.1, tag

@@ -281,3 +281,25 @@ def test_every_config_converts_a_model_on_cpu():
         assert qs, name
         algo = cfg["algorithm"]
         assert algo is None or isinstance(algo, (str, dict)), name
+
+
+def test_bias_calibrator_matches_reference_values():
+    """Running-mean and running-mid-range bias over two batches against the reference's values
+    (tests/golden/bias.npz); the calibrator is plain tensor arithmetic, so this runs on CPU."""
+    from b200q.calib import BiasCalibrator
+
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "bias.npz"))
+    xs = [torch.from_numpy(g["x0"]), torch.from_numpy(g["x1"])]
+    mean = BiasCalibrator("mean", (-2, -4))
+    mid = BiasCalibrator("max_min", (-1,))
+    for x in xs:
+        mean.collect(x)
+        mid.collect(x)
+    assert mean.compute_bias().shape == (1, 3, 1, 16) and mid.compute_bias().shape == (2, 3, 8, 1)
+    assert torch.allclose(mean.compute_bias(), torch.from_numpy(g["fp8_mean_bias"]), rtol=1e-6, atol=1e-7)
+    assert torch.equal(mid.compute_bias(), torch.from_numpy(g["int8_maxmin_bias"]))
+    assert torch.equal(mid.compute_dynamic_bias(xs[0]), (xs[0].amax(-1, keepdim=True) + xs[0].amin(-1, keepdim=True)) / 2)
+    mean.reset()
+    assert mean.compute_bias() is None
+    with pytest.raises(ValueError):
+        BiasCalibrator("median")
