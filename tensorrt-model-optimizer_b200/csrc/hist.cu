@@ -153,12 +153,16 @@ __global__ void __launch_bounds__(kHistThreads)
 hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
                       Hist16Layout lay, unsigned long long* __restrict__ counts) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
-  pdl_prologue();
+  pdl_launch_dependents();
   extern __shared__ uint32_t sh[];
   uint4* sh4 = reinterpret_cast<uint4*>(sh);
   const int vwords = lay.values << lay.rshift;             // a multiple of 4 (host pads `values`)
+  // clearing the (CTA-private) counters overlaps the previous kernel's tail; global memory is
+  // touched only after pdl_wait()
+  for (int j = threadIdx.x; j < (vwords + lay.smem_bins + 3) / 4; j += blockDim.x) sh4[j] = make_uint4(0, 0, 0, 0);
+  pdl_wait();
 
-  // Four packs per step, loaded one step ahead (the first step before shared memory is cleared).
+  // Four packs per step, loaded one step ahead.
   const int64_t npack = n / 8;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -170,8 +174,6 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   };
   uint4 cur[4], nxt[4];
   load4(i, cur);
-
-  for (int j = threadIdx.x; j < (vwords + lay.smem_bins + 3) / 4; j += blockDim.x) sh4[j] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   const uint32_t rmask = (1u << lay.rshift) - 1u;
   const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(sh));
