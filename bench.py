@@ -40,7 +40,7 @@ BYTES_QUANT = 2.0 + 0.5 + 1.0 / 16
 BYTES_TOTAL = BYTES_AMAX + BYTES_QUANT
 # DRAM bytes per element of the quantise kernel from the committed ncu capture
 # (profiles/nvfp4_group_quantize_*.md), or None before one exists
-NCU_QUANT_TRAFFIC_PER_ELEM = 2.478
+NCU_QUANT_TRAFFIC_PER_ELEM = 2.477
 
 
 def peaks():
@@ -383,14 +383,39 @@ def run_formats(dev, peak):
     status = torch.zeros((), dtype=torch.int32, device=dev)
     scales = [torch.exp(0.05 * i * torch.randn(4096, generator=g, device=dev)).bfloat16() for i in range(21)]
 
-    def search():
+    def search_sequential():
         for sc in scales:
             wfq = ops.awq_scale_fake_int(w, sc, 128, 4, False, False)
             ops.awq_gemm_sqerr(x, wfq, ref, acc, status)
 
+    # what awq_lite runs (b200q.model_calib._search_pipelined): the weight-side kernel of candidate
+    # i+1 on a second stream while the GEMM of candidate i runs, two weight-sized buffers
+    side = torch.cuda.Stream(dev)
+    bufs = [torch.empty_like(w), torch.empty_like(w)]
+
+    def search():
+        main = torch.cuda.current_stream(dev)
+        side.wait_stream(main)
+        done_q = [torch.cuda.Event() for _ in scales]
+        done_g = [torch.cuda.Event() for _ in scales]
+        for i, sc in enumerate(scales):
+            with torch.cuda.stream(side):
+                if i >= 2:
+                    side.wait_event(done_g[i - 2])
+                ops.awq_scale_fake_int(w, sc, 128, 4, False, False, out=bufs[i % 2])
+                done_q[i].record(side)
+            main.wait_event(done_q[i])
+            ops.awq_gemm_sqerr(x, bufs[i % 2], ref, acc, status)
+            done_g[i].record(main)
+        side.wait_stream(main)
+
     flops = 21 * 2.0 * 512 * 4096 * 14336
     r = timed(search, 21 * 14336 * 4096 * 4, reps=3, groups=3)
     out["awq_lite_search_21_alphas_up_proj_512tok"] = {
+        "ms": r["ms"], "gemm_tflops_incl_quant_kernel": flops / (r["ms"] * 1e-3) / 1e12,
+        "schedule": "scale+quantise kernel of candidate i+1 on a second stream under the GEMM of candidate i"}
+    r = timed(search_sequential, 21 * 14336 * 4096 * 4, reps=3, groups=3)
+    out["awq_lite_search_21_alphas_one_stream"] = {
         "ms": r["ms"], "gemm_tflops_incl_quant_kernel": flops / (r["ms"] * 1e-3) / 1e12}
     wfq = ops.awq_scale_fake_int(w, scales[1], 128, 4, False, False)
     r = timed(lambda: [ops.awq_gemm_sqerr(x, wfq, ref, acc, status) for _ in range(21)], 1, reps=3, groups=3)

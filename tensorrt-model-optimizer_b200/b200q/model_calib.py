@@ -198,6 +198,8 @@ class _AWQLiteState:
         # error bits of the evaluation kernel's bounded waits (checked once, after the search)
         self.gemm_status = (torch.zeros((), dtype=torch.int32, device=module.weight.device)
                             if module.weight.is_cuda else None)
+        self.side_stream = None   # second stream and two weight-sized buffers of the pipelined search
+        self.wfq_bufs = None
 
 
 def _evaluate_alpha(module, st, x2d, out_actual, alpha):
@@ -230,6 +232,59 @@ def _evaluate_alpha(module, st, x2d, out_actual, alpha):
     return ops.mse_loss(out, out_actual)
 
 
+# run the weight-side kernel of candidate i+1 on a second stream while the GEMM of candidate i runs
+PIPELINE_AWQ_SEARCH = True
+
+
+def _search_pipelined(module, st, x2d, out_actual) -> bool:
+    """All candidates of one batch with the two kernels of consecutive candidates overlapped: the
+    scale + block-quantise kernel (HBM and ALU bound) of candidate i+1 runs on a side stream into
+    the other of two weight-sized buffers while the tcgen05 GEMM (tensor pipe, operands from L2)
+    of candidate i runs on the current stream.  Same kernels, inputs and results as
+    ``_evaluate_alpha``; returns False when the layer is outside what the two kernels cover."""
+    wq = module.weight_quantizer
+    w = module.weight
+    fast = (wq._fake_quant and isinstance(wq._num_bits, int) and st.block_size
+            and w.shape[-1] % st.block_size == 0 and wq._block_sizes.get("type", "static") == "static")
+    x2 = x2d.reshape(-1, x2d.shape[-1])
+    ref2 = out_actual.reshape(-1, out_actual.shape[-1])
+    if not (PIPELINE_AWQ_SEARCH and USE_TENSOR_CORE_EVAL and fast and module.bias is None and w.is_cuda
+            and ops.awq_gemm_supported(x2, w)):
+        return False
+    alphas = list(st.loss.keys())
+    dev, dt = w.device, w.dtype
+    main = torch.cuda.current_stream(dev)
+    if st.side_stream is None:
+        st.side_stream = torch.cuda.Stream(dev)
+        st.wfq_bufs = [torch.empty_like(w), torch.empty_like(w)]
+    side, bufs = st.side_stream, st.wfq_bufs
+    scales = [get_scale(st.act_scale, st.weight_scale, a) for a in alphas]
+    w_s = [s.to(dt) for s in scales]
+    x_s = [(1 / s).to(dt) for s in scales]
+    accs = torch.zeros(len(alphas), dtype=torch.float64, device=dev)
+    side.wait_stream(main)                      # weight, scales and buffers are ready
+    done_q = [torch.cuda.Event() for _ in alphas]
+    done_g = [torch.cuda.Event() for _ in alphas]
+    for i in range(len(alphas)):
+        with torch.cuda.stream(side):
+            if i >= 2:
+                side.wait_event(done_g[i - 2])  # the GEMM that read this buffer has finished
+            ops.awq_scale_fake_int(w, w_s[i], st.block_size, wq._num_bits, wq._unsigned, wq._narrow_range,
+                                   out=bufs[i % 2])
+            done_q[i].record(side)
+        xin = x2d * x_s[i]
+        if module.input_quantizer.is_enabled:
+            xin = module.input_quantizer(xin)
+        main.wait_event(done_q[i])
+        ops.awq_gemm_sqerr(xin.reshape(-1, xin.shape[-1]), bufs[i % 2], ref2, accs[i:i + 1], st.gemm_status)
+        done_g[i].record(main)
+    side.wait_stream(main)
+    losses = (accs / ref2.numel()).to(torch.float32)
+    for i, a in enumerate(alphas):
+        st.loss[a] += losses[i]
+    return True
+
+
 def _awq_forward(self, input, *args, **kwargs):
     st = self.awq_lite
     for q in (self.input_quantizer, self.weight_quantizer):
@@ -244,8 +299,9 @@ def _awq_forward(self, input, *args, **kwargs):
         if st.is_input_quantized:
             self.input_quantizer._calibrator.collect(input)
         return out_actual
-    for alpha in st.loss:
-        st.loss[alpha] += _evaluate_alpha(self, st, input, out_actual, alpha)
+    if not _search_pipelined(self, st, input, out_actual):
+        for alpha in st.loss:
+            st.loss[alpha] += _evaluate_alpha(self, st, input, out_actual, alpha)
     st.num_search_steps += 1
     return out_actual
 
@@ -313,6 +369,7 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
             warnings.warn(f"awq_lite: the second forward_loop(model) did not reach {name}.")
         if st.gemm_status is not None and int(st.gemm_status) != 0:
             raise RuntimeError(f"awq_lite: the evaluation kernel timed out in {name} (status {int(st.gemm_status)})")
+        st.wfq_bufs = None
         if st.is_enabled:
             st.loss = {k: float(v) for k, v in st.loss.items()}
             st.best_alpha = min(st.loss, key=st.loss.get)

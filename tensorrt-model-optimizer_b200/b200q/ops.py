@@ -420,12 +420,17 @@ def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None
 # --------------------------------------------------------------------------- awq_lite ----------
 
 def awq_scale_fake_int(w: torch.Tensor, s: torch.Tensor, block: int, num_bits: int = 4,
-                       unsigned: bool = False, narrow_range: bool = False) -> torch.Tensor:
+                       unsigned: bool = False, narrow_range: bool = False,
+                       out: torch.Tensor | None = None) -> torch.Tensor:
     """fake_int over blocks of ``block`` along the last dim of T(w * s), s broadcast over rows."""
     w = _prep(w)
     s = _prep(s.to(w.dtype))
     assert w.dim() == 2 and s.numel() == w.shape[1]
-    y = torch.empty_like(w)
+    if out is None:
+        y = torch.empty_like(w)
+    else:
+        assert out.shape == w.shape and out.dtype == w.dtype and out.is_contiguous() and out.device == w.device
+        y = out
     with torch.cuda.device(w.device):
         call("b200q_awq_scale_fake_int", w.data_ptr(), s.data_ptr(), y.data_ptr(), w.shape[0], w.shape[1],
              block, dtype_code(w), num_bits, int(unsigned), int(narrow_range), _stream(w))

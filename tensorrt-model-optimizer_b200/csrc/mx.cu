@@ -130,14 +130,23 @@ mxfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, int lanes, uint8
     for (int p = 0; p < PPL; ++p) {
       float f[P];
       E::unpack(v[p], f);
+      // magnitudes through the hardware conversion (round to nearest even), then the three ties
+      // whose even neighbour is the larger one (0.75, 1.75, 3.5) are moved down: the reference
+      // counts the bounds strictly below |q|, which sends every tie toward zero.  The sign bit is
+      // set for everything that is not > 0, zero included; NaN encodes as magnitude 0.
       uint32_t out = 0;
 #pragma unroll
-      for (int k = 0; k < P; ++k) {
-        const float q = f[k] * mul;
-        const float a = fabsf(q);
-        uint32_t code = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.f);
-        code |= (q > 0.f) ? 0u : 8u;
-        out |= code << (4 * k);
+      for (int k = 0; k < P; k += 2) {
+        const float q0 = f[k] * mul, q1 = f[k + 1] * mul;
+        const float a0 = fabsf(q0), a1 = fabsf(q1);
+        const uint32_t byte = f32x2_to_e2m1x2(a0, a1);
+        uint32_t m0 = byte & 7u, m1 = (byte >> 4) & 7u;
+        m0 -= static_cast<uint32_t>((a0 == 0.75f) | (a0 == 1.75f) | (a0 == 3.5f));
+        m1 -= static_cast<uint32_t>((a1 == 0.75f) | (a1 == 1.75f) | (a1 == 3.5f));
+        m0 = (a0 == a0) ? m0 : 0u;
+        m1 = (a1 == a1) ? m1 : 0u;
+        const uint32_t c0 = m0 | ((q0 > 0.f) ? 0u : 8u), c1 = m1 | ((q1 > 0.f) ? 0u : 8u);
+        out |= (c0 | (c1 << 4)) << (4 * k);
       }
       uint8_t* dst = packed + (t * PPL + p) * (P / 2);
       if (P == 8) *reinterpret_cast<uint32_t*>(dst) = out;
