@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself on CPU.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where a checkout of the reference is available:
 
-    python tests/golden/make_golden.py [--ref /path/to/TensorRT-Model-Optimizer]
+    python tests/golden/make_golden.py --ref /path/to/TensorRT-Model-Optimizer
 
 The reference is imported unmodified with three shims (it cannot be pip-installed offline):
 its distribution version is supplied, the optional ``pulp`` / ``torchprofile`` imports are
@@ -440,7 +440,7 @@ def golden_reference_test_tables(out, ref_root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of a TensorRT-Model-Optimizer checkout")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     import_reference(args.ref)

@@ -1,7 +1,7 @@
 """Model-level golden vectors: run the REFERENCE's mtq.quantize / mtq.compress on CPU for a small
 MLP and store what it produced (amax buffers, AWQ losses and scales, packed weights).
 
-    python tests/golden/make_golden_model.py [--ref /path/to/TensorRT-Model-Optimizer]
+    python tests/golden/make_golden_model.py --ref /path/to/TensorRT-Model-Optimizer
 
 Uses the same import shims as make_golden.py.
 """
@@ -218,7 +218,7 @@ def golden_clip_smooth(mtq, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of a TensorRT-Model-Optimizer checkout")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     mtq = import_reference(args.ref)
