@@ -485,3 +485,55 @@ def test_hist_mse_kernel_vs_host_search(ops):
         want = _mse_amax(counts, edges, bits, unsigned, stride, start)
         assert abs(amax.item() - want) <= 1e-6 * want, (nbins, amax.item(), want)
         assert torch.isfinite(errs).all()
+
+
+def test_back_to_back_dependent_launches_keep_stream_order(ops):
+    """The kernels overlap their launch with the previous kernel's tail; a kernel must still see
+    everything its predecessor wrote.  Chains of dependent launches (abs-max -> fake quant that
+    reads it -> abs-max of the result -> histogram of the result) with nothing in between, many
+    times over, against results computed step by step with synchronisation in between."""
+    torch.manual_seed(11)
+    xs = [(torch.randn(1 << 20, device="cuda") * (1 + i)).bfloat16() for i in range(6)]
+    want = []
+    for x in xs:                                   # reference: every step synchronised
+        a = ops.amax_tensor(x); torch.cuda.synchronize()
+        y = ops.fake_e4m3(x, a); torch.cuda.synchronize()
+        b = ops.amax_tensor(y); torch.cuda.synchronize()
+        z = ops.nvfp4_fake(y, b); torch.cuda.synchronize()
+        c = torch.zeros(2048, dtype=torch.int64, device="cuda")
+        ops.hist_collect(z, c, 2048, float(b)); torch.cuda.synchronize()
+        want.append((a.clone(), y.clone(), b.clone(), z.clone(), c.clone()))
+    for rep in range(20):                          # the same chains, enqueued without any host wait
+        got = []
+        rmax = [float(w[2]) for w in want]
+        for x, r in zip(xs, rmax):
+            a = ops.amax_tensor(x)
+            y = ops.fake_e4m3(x, a)
+            b = ops.amax_tensor(y)
+            z = ops.nvfp4_fake(y, b)
+            c = torch.zeros(2048, dtype=torch.int64, device="cuda")
+            ops.hist_collect(z, c, 2048, r)
+            got.append((a, y, b, z, c))
+        torch.cuda.synchronize()
+        for g, w in zip(got, want):
+            for u, v in zip(g, w):
+                assert torch.equal(u, v), rep
+
+
+def test_plain_c_host_program_through_the_c_abi(tmp_path):
+    """tests/c/cabi_host.c: a C program (gcc, CUDA runtime, no Python objects) quantises through the
+    shared library and checks the result and the status codes itself."""
+    import os
+    import subprocess
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    lib_dir = root / "tensorrt-model-optimizer_b200" / "b200q" / "_lib"
+    cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    exe = tmp_path / "cabi_host"
+    subprocess.run(["gcc", "-std=c99", "-O1", str(root / "tests" / "c" / "cabi_host.c"), "-I", str(root / "include"),
+                    "-I", str(cuda / "include"), "-L", str(lib_dir), "-lb200q", "-L", str(cuda / "lib64"), "-lcudart",
+                    "-lm", f"-Wl,-rpath,{lib_dir}", f"-Wl,-rpath,{cuda / 'lib64'}", "-o", str(exe)], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    assert "cabi_host ok" in r.stdout
