@@ -1,0 +1,137 @@
+"""End-to-end flow on a small Llama-shaped model (HF module names): quantize -> calibrate ->
+compress -> forward -> checkpoint export, for the NVFP4, FP8 and INT4-AWQ configurations."""
+import copy
+
+import pytest
+import torch
+from torch import nn
+
+pytestmark = pytest.mark.gpu
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, d):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(d))
+
+    def forward(self, x):
+        return self.weight * x * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5).to(x.dtype)
+
+
+class Attention(nn.Module):
+    def __init__(self, d, heads, kv_heads):
+        super().__init__()
+        self.h, self.kv, self.hd = heads, kv_heads, d // heads
+        self.q_proj = nn.Linear(d, d, bias=False)
+        self.k_proj = nn.Linear(d, self.kv * self.hd, bias=False)
+        self.v_proj = nn.Linear(d, self.kv * self.hd, bias=False)
+        self.o_proj = nn.Linear(d, d, bias=False)
+
+    def forward(self, x):
+        b, t, d = x.shape
+        q = self.q_proj(x).view(b, t, self.h, self.hd).transpose(1, 2)
+        k = self.k_proj(x).view(b, t, self.kv, self.hd).transpose(1, 2).repeat_interleave(self.h // self.kv, 1)
+        v = self.v_proj(x).view(b, t, self.kv, self.hd).transpose(1, 2).repeat_interleave(self.h // self.kv, 1)
+        y = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return self.o_proj(y.transpose(1, 2).reshape(b, t, d))
+
+
+class MLP(nn.Module):
+    def __init__(self, d, inter):
+        super().__init__()
+        self.gate_proj = nn.Linear(d, inter, bias=False)
+        self.up_proj = nn.Linear(d, inter, bias=False)
+        self.down_proj = nn.Linear(inter, d, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class Layer(nn.Module):
+    def __init__(self, d, heads, kv_heads, inter):
+        super().__init__()
+        self.input_layernorm, self.post_attention_layernorm = RMSNorm(d), RMSNorm(d)
+        self.self_attn, self.mlp = Attention(d, heads, kv_heads), MLP(d, inter)
+
+    def forward(self, x):
+        x = x + self.self_attn(self.input_layernorm(x))
+        return x + self.mlp(self.post_attention_layernorm(x))
+
+
+class TinyLlama(nn.Module):
+    def __init__(self, vocab=512, d=256, heads=4, kv_heads=2, inter=512, layers=2):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(vocab, d)
+        self.layers = nn.ModuleList(Layer(d, heads, kv_heads, inter) for _ in range(layers))
+        self.norm = RMSNorm(d)
+        self.lm_head = nn.Linear(d, vocab, bias=False)
+
+    def forward(self, ids):
+        x = self.embed_tokens(ids)
+        for layer in self.layers:
+            x = layer(x)
+        return self.lm_head(self.norm(x))
+
+
+@pytest.mark.parametrize("name", ["NVFP4_DEFAULT_CFG", "FP8_DEFAULT_CFG", "INT4_AWQ_CFG"])
+def test_llama_shaped_model_end_to_end(name):
+    import b200q as mtq
+    from b200q import export
+    from b200q.nn import QuantLinear
+
+    torch.manual_seed(0)
+    model = TinyLlama().to(torch.bfloat16).cuda().eval()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    batches = [torch.randint(0, 512, (4, 128), device="cuda", generator=g) for _ in range(2)]
+    with torch.no_grad():
+        ref = model(batches[0]).float()
+
+    def loop(m):
+        with torch.no_grad():
+            for b in batches:
+                m(b)
+
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), loop)
+    linears = {n: m for n, m in model.named_modules() if isinstance(m, QuantLinear)}
+    assert len(linears) == 2 * 7 + 1
+    assert not linears["lm_head"].weight_quantizer.is_enabled            # "*lm_head*" is excluded by the configs
+    enabled = [n for n, m in linears.items() if m.weight_quantizer.is_enabled]
+    assert len(enabled) == 14
+    with torch.no_grad():
+        fake = model(batches[0]).float()
+    rel = (fake - ref).abs().mean() / ref.abs().mean()
+    assert torch.isfinite(fake).all() and rel < (0.5 if name == "INT4_AWQ_CFG" else 0.35), float(rel)
+    mtq.compress(model)
+    with torch.no_grad():
+        real = model(batches[0]).float()
+    assert torch.isfinite(real).all()
+    assert (real - fake).abs().mean() < 0.1 * fake.abs().mean() + 1e-3
+    w = model.layers[0].mlp.up_proj.weight
+    if name != "FP8_DEFAULT_CFG":
+        assert w.dtype == torch.uint8 and w.shape == (512, 128)            # two 4-bit values per byte
+    else:
+        assert w.dtype == torch.float8_e4m3fn
+
+
+@pytest.mark.parametrize("name", ["NVFP4_DEFAULT_CFG", "FP8_DEFAULT_CFG"])
+def test_llama_shaped_checkpoint_export(name):
+    import b200q as mtq
+    from b200q import export
+
+    torch.manual_seed(0)
+    model = TinyLlama().to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 512, (2, 64), device="cuda")
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(ids))
+    sd = export.export_hf_state_dict(model, torch.bfloat16)
+    assert "lm_head.weight" in sd and sd["lm_head.weight"].dtype == torch.bfloat16
+    assert not any("quantizer" in k for k in sd)
+    for layer in range(2):
+        for lin in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                    "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"):
+            p = f"layers.{layer}.{lin}."
+            assert sd[p + "weight_scale"].numel() > 0 and sd[p + "input_scale"].numel() == 1
+            if name == "NVFP4_DEFAULT_CFG":
+                assert sd[p + "weight"].dtype == torch.uint8 and sd[p + "weight_scale"].dtype == torch.float8_e4m3fn
+                assert sd[p + "weight_scale_2"].dtype == torch.float32
+            else:
+                assert sd[p + "weight"].dtype == torch.float8_e4m3fn
