@@ -298,7 +298,8 @@ def run_b200(args):
                                    "real quantize + pack: fp32 global scale, E4M3 scale per 16, E2M1 nibbles",
                        "layers": args.layers, "sharding": f"layers split over {world} rank(s)",
                        "l2": "inputs (>=1.7 GB per rank) are larger than L2; no flush needed",
-                       "bytes_per_element": BYTES_TOTAL, "ptq_seconds": ms_per_step * 1e-3},
+                       "bytes_per_element": BYTES_TOTAL, "ptq_seconds": ms_per_step * 1e-3,
+                       "tensors_per_second": args.layers * len(LAYER_SHAPES) / (ms_per_step * 1e-3)},
             "roofline": {"bound": "hbm", "kernel": "nvfp4_group_quantize_kernel", "achieved": achieved,
                          "peak": peak, "peak_source": f"of {which}", "unit": "GB/s",
                          "frac": achieved / peak if achieved else None,

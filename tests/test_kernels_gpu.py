@@ -537,3 +537,40 @@ def test_plain_c_host_program_through_the_c_abi(tmp_path):
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
     assert "cabi_host ok" in r.stdout
+
+
+def test_tensors_beyond_2_31_elements(ops):
+    """64-bit indexing: one bf16 tensor of 2^31 + 2^20 elements (4.3 GB) through the abs-max, NVFP4
+    quantise / dequantise and histogram kernels, checked by size-independent properties."""
+    n = (1 << 31) + (1 << 20)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    step = 1 << 28
+    for i in range(0, n, step):
+        m = min(step, n - i)
+        x[i:i + m] = (torch.randn(m, generator=g, device="cuda") * 0.02).bfloat16()
+    x[-1] = 3.0                                  # the maximum sits in the very last element
+    x[(1 << 31) + 5] = -2.5
+    amax = ops.amax_tensor(x)
+    assert float(amax) == 3.0
+    xv = x.view(-1, 4096)
+    packed, scales, s2 = ops.nvfp4_quantize(xv, amax=amax)
+    assert float(s2) == float(torch.tensor(3.0) / torch.tensor(2688.0))
+    deq = ops.nvfp4_dequantize(packed, scales, s2, torch.bfloat16)
+    assert deq.shape == xv.shape
+    assert float(deq.view(-1)[-1]) == 3.0 and abs(float(deq.view(-1)[(1 << 31) + 5]) + 2.5) < 0.1
+    # slices at the start, across the 2^31 boundary and at the very end against the oracle
+    for lo in (0, (1 << 31) - (1 << 15), n - (1 << 16)):
+        sl = slice(lo, lo + (1 << 16))
+        xs = f32_from_tensor(x[sl]).reshape(-1, 4096)
+        wp, ws, _ = qo.nvfp4_quantize(xs, 16, amax=np.float32(3.0))
+        assert np.array_equal(packed.view(-1)[lo // 2: lo // 2 + (1 << 15)].cpu().numpy(), wp.reshape(-1)), lo
+        assert np.array_equal(scales.view(torch.uint8).view(-1)[lo // 16: lo // 16 + (1 << 12)].cpu().numpy(),
+                              ws.reshape(-1)), lo
+        want = qo.nvfp4_dequantize(wp, ws, np.float32(3.0) / np.float32(2688.0), 16, "bf16")
+        assert same_bits(f32_from_tensor(deq.view(-1)[sl]), want.reshape(-1)), lo
+    del packed, scales
+    # every element lands in exactly one bin
+    counts = torch.zeros(2048, dtype=torch.int64, device="cuda")
+    ops.hist_collect(deq.view(-1), counts, 2048, 3.0)
+    assert int(counts.sum()) == n and int(counts[-1]) >= 1
