@@ -4,7 +4,7 @@ algorithm options :958-1150) for the formats this package accelerates."""
 from __future__ import annotations
 
 import copy
-from dataclasses import dataclass, field, fields
+from dataclasses import dataclass, fields
 from typing import Any
 
 __all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG", "FP8_DEFAULT_CFG",

@@ -18,7 +18,7 @@ from torch import nn
 from . import dist as qdist
 from . import ops
 from .calib import MseCalibrator
-from .nn import QuantModule, SequentialQuantizer, TensorQuantizer, is_quantized_linear
+from .nn import SequentialQuantizer, TensorQuantizer, is_quantized_linear
 
 __all__ = ["max_calibrate", "mse_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection",
            "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]

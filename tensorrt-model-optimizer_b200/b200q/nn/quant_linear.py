@@ -13,7 +13,7 @@ from torch import nn
 
 from ..config import QuantizerAttributeConfig
 from ..qtensor import QTensorWrapper
-from .tensor_quantizer import SequentialQuantizer, TensorQuantizer
+from .tensor_quantizer import TensorQuantizer
 
 __all__ = ["QuantModule", "QuantLinear", "RealQuantLinear", "is_quantized_linear"]
 

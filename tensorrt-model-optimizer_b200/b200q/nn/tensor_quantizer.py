@@ -8,7 +8,6 @@ calibrator during calibration and dispatches fake or real quantisation to the CU
 from __future__ import annotations
 
 import contextlib
-import math
 import warnings
 
 import torch
