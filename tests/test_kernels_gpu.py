@@ -574,3 +574,29 @@ def test_tensors_beyond_2_31_elements(ops):
     counts = torch.zeros(2048, dtype=torch.int64, device="cuda")
     ops.hist_collect(deq.view(-1), counts, 2048, 3.0)
     assert int(counts.sum()) == n and int(counts[-1]) >= 1
+
+
+def test_kernels_capture_into_a_cuda_graph(ops):
+    """A chain of dependent launches captured once and replayed on new data in the same buffers."""
+    x = torch.zeros(1 << 20, dtype=torch.bfloat16, device="cuda")
+    amax = torch.zeros((), device="cuda")
+    ops.amax_tensor(x, out=amax); ops.nvfp4_fake(x, amax)          # load everything before capture
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            amax.zero_()
+            ops.amax_tensor(x, out=amax)
+            y = ops.fake_e4m3(x, amax)
+            z = ops.nvfp4_fake(y, amax)
+    torch.cuda.current_stream().wait_stream(s)
+    for i in range(3):
+        new = (torch.randn(1 << 20, device="cuda") * (i + 1)).bfloat16()
+        x.copy_(new)
+        graph.replay()
+        torch.cuda.synchronize()
+        a = ops.amax_tensor(new)
+        want = ops.nvfp4_fake(ops.fake_e4m3(new, a), a)
+        assert torch.equal(amax, a) and torch.equal(z, want), i
