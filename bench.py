@@ -9,8 +9,9 @@ q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336, bf16, Student
 scaled to std 0.02.  With N GPUs the 32 layers are split across the ranks (strong scaling, no
 data-path collective).  Prints one JSON line (rank 0).
 
-``--impl reference`` times the CPU restatement of the reference's torch path (oracle/) on the
-host cores for a bounded sample of the same workload.
+``--impl reference`` times the reference's CPU torch path (restated operation by operation in
+oracle/torch_path.py) on the host cores for a bounded sample of the same workload, and reports a
+fused multi-threaded C restatement (oracle/nvfp4_ref.c) beside it.
 """
 from __future__ import annotations
 
@@ -155,6 +156,37 @@ def cpu_nvfp4_sample(seconds_target: float = 15.0, threads: int | None = None):
                            f"(oracle/nvfp4_ref.c), {threads} threads"}
 
 
+def cpu_torch_path_sample(seconds_target: float = 15.0):
+    """Time the reference's CPU torch path (oracle/torch_path.py: the same sequence of torch tensor
+    operations as NVFP4QTensor.quantize on a CPU tensor, all intra-op threads) on one gate_proj-shaped
+    bf16 weight; returns (GB/s of algorithmic bytes, info)."""
+    import torch
+
+    from oracle import torch_path
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    rows, cols = 14336, 4096
+    g = torch.Generator().manual_seed(0)
+    z = torch.randn(rows, cols, generator=g)
+    chi = sum(torch.randn(rows, cols, generator=g) ** 2 for _ in range(4)) / 4
+    w = (z / chi.sqrt() * (0.02 / 2 ** 0.5)).to(torch.bfloat16)
+    del z, chi
+    t0 = time.perf_counter()
+    torch_path.nvfp4_quantize(w, 16)
+    dt1 = time.perf_counter() - t0
+    reps = max(1, min(20, int(seconds_target / max(dt1, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        torch_path.nvfp4_quantize(w, 16)
+    dt = (time.perf_counter() - t0) / reps
+    gbs = rows * cols * BYTES_TOTAL / dt / 1e9
+    return gbs, {"cores": torch.get_num_threads(), "kind": "port",
+                 "sample": f"{reps} passes over one gate_proj-shaped weight [{rows},{cols}] bf16 "
+                           f"({dt * 1e3:.0f} ms per pass): the reference's CPU torch path, restated operation by "
+                           f"operation (oracle/torch_path.py), torch intra-op threads = {torch.get_num_threads()}"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -164,18 +196,24 @@ def run_reference(args):
     vals = []
     info = None
     for i in range(steps + warm):
-        gbs, info = cpu_nvfp4_sample(per_step)
+        gbs, info = cpu_torch_path_sample(per_step)
         if i >= warm:
             vals.append(gbs)
     v = statistics.mean(vals)
+    c_gbs, c_info = cpu_nvfp4_sample(5.0)
+    info["fused_c_port"] = {"value": c_gbs, "unit": "GB/s", **c_info}
     ms_full = N_LAYERS * ELEMS_PER_LAYER * BYTES_TOTAL / (v * 1e9) * 1e3
     line = {
         "impl": "reference", "metric": "nvfp4_weight_quantize_hbm_gbps", "value": v, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": ms_full,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "llama3-8b-shape linear weights, NVFP4 quantize+pack (block 16)",
-                   "note": "ms_per_step extrapolated from the sample to the full 32-layer model"},
+        "config": {"workload": "llama3-8b-shape linear weights (224 tensors, 6.98e9 elements), NVFP4 "
+                               "real quantize + pack: fp32 global scale, E4M3 scale per 16, E2M1 nibbles",
+                   "layers": N_LAYERS, "bytes_per_element": BYTES_TOTAL,
+                   "note": "each step is a bounded sample (one gate_proj-shaped tensor, repeated); value is its "
+                           "throughput in the same algorithmic bytes, ms_per_step the extrapolation to the "
+                           "full 32-layer model"},
         "cpu_baseline": {"value": v, "unit": "GB/s", **info},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -275,8 +313,10 @@ def run_b200(args):
     # ---- CPU baseline (rank 0, N=1 only) ---------------------------------------------------
     cpu = None
     if world == 1 and not args.no_cpu:
-        gbs, info = cpu_nvfp4_sample(12.0)
+        gbs, info = cpu_torch_path_sample(12.0)
         cpu = {"value": gbs, "unit": "GB/s", **info}
+        c_gbs, c_info = cpu_nvfp4_sample(6.0)
+        cpu["fused_c_port"] = {"value": c_gbs, "unit": "GB/s", **c_info}
 
     formats = None
     if world == 1 and not args.no_formats:

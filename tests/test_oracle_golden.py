@@ -264,3 +264,25 @@ def test_mxfp4_qtensor_matches_reference_cpu_path():
             assert np.array_equal(scales, g[k + "_scales"]), k
             deq = qo.mxfp4_dequantize(packed, scales, block, T)
             assert same_bits(deq, to_f32(g[k + "_deq"], T)), k
+
+
+def test_torch_path_restatement_matches_reference_bytes():
+    """oracle/torch_path.py (what `bench.py --impl reference` times) against the reference's bytes."""
+    import torch
+
+    from oracle import torch_path
+
+    g = load("nvfp4")
+    n = 0
+    for T, dt in (("f32", torch.float32), ("f16", torch.float16), ("bf16", torch.bfloat16)):
+        for k in [k[: -len("_x")] for k in g.files if k.startswith(T + "_") and k.endswith("_x")]:
+            if k + "_packed" not in g.files or k + "_amax" in g.files:
+                continue
+            x = torch.from_numpy(to_f32(g[k + "_x"], T)).to(dt)
+            if x.shape[-1] % 16:
+                continue
+            packed, scales, s2 = torch_path.nvfp4_quantize(x, 16)
+            assert np.array_equal(packed.numpy(), g[k + "_packed"]), k
+            assert np.array_equal(scales.view(torch.uint8).numpy(), g[k + "_scales"]), k
+            n += 1
+    assert n >= 3
