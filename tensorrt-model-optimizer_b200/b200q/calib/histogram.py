@@ -38,8 +38,7 @@ class HistogramCalibrator(_Calibrator):
         super().__init__(num_bits, axis, unsigned)
         if axis is not None:
             raise NotImplementedError("Calibrator histogram collection only supports per tensor scaling")
-        if skip_zeros:
-            raise NotImplementedError("skip_zeros is not supported by the CUDA histogram")
+        self._skip_zeros = skip_zeros
         self._init_bins = num_bins     # bins of the first batch's range
         self._num_bins = num_bins      # live bins (grows; refreshed by _resolve)
         self._calib_hist = None        # int64 [capacity] on the device; first _num_bins are live
@@ -103,6 +102,10 @@ class HistogramCalibrator(_Calibrator):
         x = x.detach()
         if not x.is_floating_point() or x.dtype == torch.float64:
             x = x.float()
+        if self._skip_zeros:   # the reference's option: exact zeros are not samples (a masked copy)
+            x = x[x != 0]
+            if x.numel() == 0:
+                return
         if self._calib_hist is None:
             self.set_range(float(ops.amax_tensor(x)), x.device)
         ops.hist_collect_open(x, self._calib_hist, self._init_bins, self._range0, self._overflow)

@@ -414,9 +414,10 @@ class _AWQClipState:
         if self.per_tensor:
             self.loss_t = torch.zeros(len(self.ratios), dtype=torch.float32, device=dev)
         else:
-            if ci % self.block_size:
-                raise NotImplementedError("awq_clip: in_features must be a multiple of the block size")
-            self.loss_t = torch.zeros((len(self.ratios), co, ci // self.block_size), dtype=torch.float32, device=dev)
+            # a ragged last block is zero-padded (weights and tokens), as the reference pads them
+            self.pad = (-ci) % self.block_size
+            self.loss_t = torch.zeros((len(self.ratios), co, (ci + self.pad) // self.block_size),
+                                      dtype=torch.float32, device=dev)
             self.ratios_t = torch.tensor(self.ratios, dtype=torch.float32, device=dev)
         self.best_clip_val = None
         self.best_loss = None
@@ -453,8 +454,11 @@ def _clip_search(module, st, inputs, max_tokens):
     x2 = inputs.reshape(-1, inputs.shape[-1])
     x2 = x2[0:: max(1, x2.shape[0] // max_tokens)].contiguous()
     st.num_tokens += x2.shape[0]
-    ops.awq_clip_loss(module.weight, x2.to(module.weight.dtype), st.w_amax, st.ratios_t, st.loss_t,
-                      st.block_size, wq._num_bits, wq._unsigned, wq._narrow_range)
+    w, x2 = module.weight, x2.to(module.weight.dtype)
+    if st.pad:
+        w, x2 = F.pad(w, (0, st.pad)), F.pad(x2, (0, st.pad))
+    ops.awq_clip_loss(w, x2, st.w_amax, st.ratios_t, st.loss_t, st.block_size, wq._num_bits, wq._unsigned,
+                      wq._narrow_range)
 
 
 def _awq_clip_forward(self, input, *args, **kwargs):

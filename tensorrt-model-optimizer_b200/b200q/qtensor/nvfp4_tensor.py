@@ -62,10 +62,15 @@ class NVFP4QTensor(BaseQuantizedTensor):
                  keep_high_precision=False, try_tensorrt=False):
         """-> (NVFP4QTensor, per-block scale float8_e4m3fn, per-tensor scale fp32).  One fused
         kernel (plus the abs-max pass when no per-tensor scale is given)."""
-        if keep_high_precision:
-            raise NotImplementedError("keep_high_precision is not part of the accelerated path")
         shape, dtype = input.shape, input.dtype
         x = reduce_block_padding(input, {-1: block_size})
+        if keep_high_precision:   # the scaled values before the 4-bit cast (a debugging aid of the reference)
+            s2 = weights_scaling_factor_2 if weights_scaling_factor_2 is not None else cls.get_weights_scaling_factor_2(x)
+            sc = weights_scaling_factor
+            if sc is None:
+                sc = cls.get_weights_scaling_factor(x, block_size, s2)[0]
+            xb = x.reshape(*x.shape[:-1], -1, block_size)
+            return (xb.float() / (sc.to(torch.float32) * s2.to(x.device)).unsqueeze(-1)).reshape(x.shape)
         packed, scales, s2 = ops.nvfp4_quantize(x, scale2=weights_scaling_factor_2,
                                                 scales_in=weights_scaling_factor, block=block_size)
         if weights_scaling_factor is not None:

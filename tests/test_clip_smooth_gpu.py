@@ -177,3 +177,35 @@ def test_nvfp4_awq_clip_per_tensor_path(mtq):
         fq = dynamic_block_quant(w0[name], 16, (st.w_amax * st.ratios[best]).float(), None, (2, 1), (4, 3))
         assert torch.isfinite(fq).all()
     assert torch.isfinite(model(batches[0])).all()
+
+
+def test_awq_clip_ragged_in_features_and_small_options(mtq):
+    """in_features not a multiple of the block: the last block is zero-padded as in the reference;
+    plus the calibrator's skip_zeros option and NVFP4QTensor's keep_high_precision."""
+    from b200q.qtensor import NVFP4QTensor
+
+    torch.manual_seed(2)
+    model = torch.nn.Sequential(torch.nn.Linear(80, 32, bias=False)).to(torch.bfloat16).cuda()
+    x = torch.randn(40, 80, device="cuda", dtype=torch.bfloat16)
+    cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+    cfg["quant_cfg"]["*weight_quantizer"]["block_sizes"] = {-1: 32, "type": "static"}
+    cfg["algorithm"] = {"method": "awq_clip", "debug": True}
+    mtq.quantize(model, cfg, lambda m: m(x))
+    st = model[0].awq_clip
+    assert st.pad == 16 and st.loss_t.shape == (11, 32, 3) and model[0].weight_quantizer._amax.numel() == 32 * 3
+    assert torch.isfinite(st.loss_t).all() and torch.isfinite(model(x)).all()
+
+    cal = mtq.calib.HistogramCalibrator(8, None, False, num_bins=64, skip_zeros=True)
+    v = torch.tensor([0.0, 0.0, 0.5, 1.0, 0.0, 2.0], device="cuda")
+    cal.collect(v)
+    assert int(cal.hist.sum()) == 3 and int(cal.hist[0]) == 0
+
+    w = torch.randn(8, 64, device="cuda", dtype=torch.bfloat16)
+    hp = NVFP4QTensor.quantize(w, 16, keep_high_precision=True)
+    q, s, s2 = NVFP4QTensor.quantize(w, 16)
+    assert hp.shape == w.shape and hp.dtype == torch.float32 and float(hp.abs().max()) <= 6.0 * 1.07
+    # the 4-bit codes are the E2M1 rounding of exactly these scaled values
+    from oracle import quant_oracle as qo
+    codes = qo.e2m1_encode(hp.cpu().numpy())
+    want = (codes[..., 1::2] << 4) | codes[..., 0::2]
+    assert np.array_equal(q._quantized_data.cpu().numpy(), want)
