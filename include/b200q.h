@@ -290,6 +290,14 @@ int b200q_awq_clip_loss(const void* w, const void* x, const void* w_amax, const 
                         float* loss, int64_t rows, int64_t cols, int block, int ntok, int dtype,
                         int num_bits, int is_unsigned, int narrow_range, void* stream);
 
+/* ---------------------------------------------------------------- rotation ------------------ */
+
+/* Walsh-Hadamard transform (Sylvester order) of every row of x [rows, n], n a power of two <= 32768:
+ *   y = T(float(T(H x)) * scale)   (sums in fp32; scale = 1/sqrt(n) gives the normalised transform).
+ * Stands in for fast_hadamard_transform.hadamard_transform, a third-party CUDA package the
+ * reference calls from normalized_hadamard_transform (modelopt/torch/quantization/nn/functional.py:75-109). */
+int b200q_hadamard(const void* x, void* y, int64_t rows, int n, int dtype, float scale, void* stream);
+
 /* ---------------------------------------------------------------- MX (E8M0-scaled) formats -- */
 
 /* element formats of b200q_mx_fake (numbering of the reference's Types enum) */

@@ -60,6 +60,7 @@ SIGNATURES = {
     "b200q_nvfp4_fake_blocks": [_p, _p, _i64, _i, _i, _p, _p],
     "b200q_nvfp4_dequantize_blocks": [_p, _p, _p, _p, _i64, _i, _i, _p],
     "b200q_awq_clip_loss": [_p, _p, _p, _p, _i, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _p],
+    "b200q_hadamard": [_p, _p, _i64, _i, _i, _f, _p],
     "b200q_mx_fake": [_p, _p, _i64, _i, _i, _i, _p],
     "b200q_mxfp4_quantize": [_p, _i64, _i, _i, _p, _p, _p],
 }

@@ -12,7 +12,7 @@ __all__ = ["QuantizerAttributeConfig", "INT8_DEFAULT_CFG", "INT8_WEIGHT_ONLY_CFG
            "INT8_SMOOTHQUANT_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG",
            "FP8_PER_CHANNEL_PER_TOKEN_CFG", "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG", "W4A8_AWQ_BETA_CFG", "W4A8_NVFP4_FP8_CFG",
            "W4A8_MXFP4_FP8_CFG", "NVFP4_MLP_WEIGHT_ONLY_CFG", "NVFP4_MLP_ONLY_CFG", "MXFP4_MLP_WEIGHT_ONLY_CFG",
-           "FP8_KV_CFG", "FP8_AFFINE_KV_CFG", "NVFP4_KV_CFG", "NVFP4_AFFINE_KV_CFG",
+           "FP8_KV_CFG", "FP8_AFFINE_KV_CFG", "NVFP4_KV_CFG", "NVFP4_AFFINE_KV_CFG", "NVFP4_KV_ROTATE_CFG",
            "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG", "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG",
            "choices", "need_calibration"]
 
@@ -182,6 +182,16 @@ NVFP4_AFFINE_KV_CFG = {"quant_cfg": {"*[kv]_bmm_quantizer": {"num_bits": (2, 1),
                                                              "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
                                                              "bias": {-2: None, -4: None, "type": "static"}},
                                      "default": {"enable": False}}, "algorithm": "max"}
+
+
+NVFP4_KV_ROTATE_CFG = {
+    "quant_cfg": {"*q_bmm_quantizer": {"enable": False, "rotate": True},
+                  "*k_bmm_quantizer": {"num_bits": (2, 1), "axis": None, "enable": True, "rotate": True,
+                                       "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}},
+                  "*v_bmm_quantizer": {"num_bits": (2, 1), "axis": None, "enable": True,
+                                       "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}}},
+    "algorithm": "max",
+}
 
 
 def _mx(num_bits):

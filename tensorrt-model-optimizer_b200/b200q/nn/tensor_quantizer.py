@@ -19,7 +19,7 @@ from .. import calib, ops
 from ..config import QuantizerAttributeConfig
 from ..qtensor import (BaseQuantizedTensor, FP8QTensor, INT4QTensor, INT8QTensor, MXFP4QTensor,
                        NVFP4QTensor, QTensorWrapper)
-from ..tensor_quant import dynamic_block_quant, fake_tensor_quant, scaled_e4m3
+from ..tensor_quant import dynamic_block_quant, fake_tensor_quant, normalized_hadamard_transform, scaled_e4m3
 from ..utils import convert_quantization_axis_to_reduce_axis, reduce_amax
 
 __all__ = ["TensorQuantizer", "SequentialQuantizer"]
@@ -64,8 +64,6 @@ class TensorQuantizer(nn.Module):
         self._trt_high_precision_dtype = c.trt_high_precision_dtype
         self._rotate = c.rotate
         self._pass_through_bwd = c.pass_through_bwd
-        if self._rotate:
-            raise NotImplementedError("rotation is not part of the accelerated path")
         self._bias_calibrator = None
         self._calibrator = self._make_calibrator(c.calibrator)
         for attr in ("_block_reshape_size", "_padding", "_slices", "_original_shape", "_amax_shape_for_export"):
@@ -490,6 +488,8 @@ class TensorQuantizer(nn.Module):
             return inputs
         if self.pre_quant_scale is not None:
             inputs = inputs * self.pre_quant_scale
+        if self._rotate:
+            inputs = normalized_hadamard_transform(inputs)
         if self._disabled:
             self._input_dtype = inputs.dtype
             return inputs
@@ -539,6 +539,7 @@ class TensorQuantizer(nn.Module):
         s += f" block_sizes={self._block_sizes}," if self._block_sizes else f" axis={self._axis}" if self._axis is not None else " per-tensor"
         s += f" amax={self._short_amax()}"
         s += " pre_quant_scale" if self.pre_quant_scale is not None else ""
+        s += " rotated" if self._rotate else ""
         s += f" calibrator={self._calibrator.__class__.__name__}" if self._calibrator is not None else ""
         s += " quant" if self._if_quant else ""
         s += " calib" if self._if_calib else ""

@@ -537,3 +537,16 @@ def awq_clip_loss(w: torch.Tensor, x: torch.Tensor, w_amax: torch.Tensor, ratios
              ratios.numel(), loss.data_ptr(), rows, cols, block, x.shape[0], dtype_code(w), num_bits,
              int(unsigned), int(narrow_range), _stream(w))
     return loss
+
+
+# --------------------------------------------------------------------------- rotation ----------
+
+def hadamard(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Walsh-Hadamard transform along the last dimension (a power of two), times ``scale``."""
+    x = _prep(x, 2)
+    n = x.shape[-1]
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        call("b200q_hadamard", x.data_ptr(), y.data_ptr(), x.numel() // n, n, dtype_code(x), ctypes.c_float(scale),
+             _stream(x))
+    return y

@@ -10,7 +10,7 @@ from torch.autograd import Function
 
 from . import ops
 
-__all__ = ["fake_tensor_quant", "scaled_e4m3", "dynamic_block_quant", "quantize_op",
+__all__ = ["normalized_hadamard_transform", "fake_tensor_quant", "scaled_e4m3", "dynamic_block_quant", "quantize_op",
            "dynamic_block_quantize_op"]
 
 
@@ -154,6 +154,28 @@ class DynamicBlockQuantizationFunction(Function):
     @staticmethod
     def backward(ctx, grad_outputs):
         return _backward(ctx, grad_outputs, 9)
+
+
+class _HadamardFunction(Function):
+    """H x along the last dimension; H is symmetric, so the backward is the same transform."""
+
+    @staticmethod
+    def forward(ctx, inputs, scale):
+        ctx.scale = scale
+        return ops.hadamard(inputs, scale)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return ops.hadamard(grad.contiguous(), ctx.scale), None
+
+
+def normalized_hadamard_transform(inputs: torch.Tensor) -> torch.Tensor:
+    """Hadamard rotation of the last dimension, scaled by 1/sqrt(n) (reference:
+    modelopt/torch/quantization/nn/functional.py:75-109, which calls the third-party
+    ``fast_hadamard_transform`` CUDA package and divides its output by sqrt(n))."""
+    n = inputs.shape[-1]
+    assert n & (n - 1) == 0, "Fast hadamard only works for inputs.shape[-1] == power of 2."
+    return _HadamardFunction.apply(inputs, 1.0 / (n ** 0.5))
 
 
 fake_tensor_quant = FakeTensorQuantFunction.apply

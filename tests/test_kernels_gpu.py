@@ -600,3 +600,45 @@ def test_kernels_capture_into_a_cuda_graph(ops):
         a = ops.amax_tensor(new)
         want = ops.nvfp4_fake(ops.fake_e4m3(new, a), a)
         assert torch.equal(amax, a) and torch.equal(z, want), i
+
+
+@pytest.mark.parametrize("T", TS)
+@pytest.mark.parametrize("n", [2, 16, 32, 64, 128, 512, 1024, 4096])
+def test_hadamard_transform(ops, T, n):
+    """Against the Sylvester matrix: exact for small-integer inputs (every sum and the 1/sqrt(n)
+    scaling for n a power of 4 are exact in T), within rounding for random inputs; H(H(x)) = n x."""
+    import scipy.linalg
+
+    H = scipy.linalg.hadamard(n).astype(np.float64)
+    rng = np.random.default_rng(n)
+    xi = rng.integers(-1, 2, (37, n)).astype(np.float32)           # entries in {-1, 0, 1}
+    yi = f32_from_tensor(ops.hadamard(tensor_from_f32(xi, T), 1.0))
+    want = xi.astype(np.float64) @ H
+    exact = np.abs(want).max() <= (256 if T == "bf16" else 2048)   # sums representable in T
+    if exact:
+        assert np.array_equal(yi, want.astype(np.float32))
+        back = f32_from_tensor(ops.hadamard(tensor_from_f32(yi, T), 1.0 / n))
+        assert np.array_equal(back, xi)
+    x = rnd((64, n), T, n + 1)
+    y = f32_from_tensor(ops.hadamard(tensor_from_f32(x, T), 1.0 / np.sqrt(n)))
+    want = qo.round_to((qo.round_to((x.astype(np.float64) @ H).astype(np.float32), T) * np.float32(1.0 / np.sqrt(n))
+                        ).astype(np.float32), T)
+    tol = {"f32": 1e-5, "f16": 2e-3, "bf16": 1.6e-2}[T]
+    assert np.allclose(y, want, rtol=tol, atol=tol * np.abs(want).max())
+    if T != "f32":   # 16-bit outputs: the rounding to T hides the order of the fp32 sums almost everywhere
+        assert np.mean(y != want) < 0.05
+
+
+def test_rotating_quantizer(ops):
+    import b200q as mtq
+
+    x = tensor_from_f32(rnd((4, 8, 128), "bf16", 3), "bf16")
+    q = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(enable=False, rotate=True)).cuda()
+    assert torch.equal(q(x), ops.hadamard(x, 1.0 / 128 ** 0.5))     # a disabled quantiser still rotates
+    k = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(
+        num_bits=(2, 1), block_sizes={-1: 16, "type": "dynamic", "scale_bits": (4, 3)}, axis=None, rotate=True)).cuda()
+    r = ops.hadamard(x, 1.0 / 128 ** 0.5)
+    assert torch.equal(k(x), ops.nvfp4_fake(r, r.abs().amax().float()))
+    xg = x.float().requires_grad_(True)
+    q(xg).sum().backward()
+    assert torch.allclose(xg.grad, ops.hadamard(torch.ones_like(xg), 1.0 / 128 ** 0.5))
