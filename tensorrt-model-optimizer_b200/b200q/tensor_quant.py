@@ -184,8 +184,9 @@ dynamic_block_quant = DynamicBlockQuantizationFunction.apply
 
 
 def _register_reference_op_names():
-    """Also expose the two ops under the reference's names (``tensorrt::quantize_op``,
-    ``tensorrt::dynamic_block_quantize_op``, tensor_quant.py:226-273) so that code and exported
+    """Also expose the ops under the reference's names (``tensorrt::quantize_op``,
+    ``tensorrt::dynamic_block_quantize_op`` and its ``.overload`` without a global amax,
+    tensor_quant.py:226-273) so that code and exported
     graphs that refer to ``torch.ops.tensorrt.*`` resolve to these kernels.  Skipped when that
     namespace already defines them (the reference itself is imported in the same process)."""
     try:
@@ -197,6 +198,17 @@ def _register_reference_op_names():
         lib.impl("quantize_op", lambda i, a, nb, eb, u, nr: quantize_op(i, a, nb, eb, u, nr), "CUDA")
         lib.impl("dynamic_block_quantize_op",
                  lambda i, bs, a, nb, eb, snb, seb: dynamic_block_quantize_op(i, bs, a, nb, eb, snb, seb), "CUDA")
+        lib.define("dynamic_block_quantize_op.overload(Tensor input, int block_size, None amax, int num_bits, "
+                   "int exponent_bits, int scale_num_bits, int scale_exponent_bits) -> Tensor")
+
+        def _none_amax(i, bs, a, nb, eb, snb, seb):
+            # no global amax: the MX formats need none, NVFP4 takes the tensor's own abs-max
+            am = (torch.zeros((), dtype=torch.float32, device=i.device) if (seb, snb - seb - 1) == (8, 0)
+                  else ops.amax_tensor(i))
+            return dynamic_block_quantize_op(i, bs, am, nb, eb, snb, seb)
+
+        lib.impl("dynamic_block_quantize_op.overload", _none_amax, "CUDA")
+        lib.impl("dynamic_block_quantize_op.overload", lambda i, bs, a, nb, eb, snb, seb: torch.empty_like(i), "Meta")
         lib.impl("quantize_op", lambda i, a, nb, eb, u, nr: torch.empty_like(i), "Meta")
         lib.impl("dynamic_block_quantize_op", lambda i, bs, a, nb, eb, snb, seb: torch.empty_like(i), "Meta")
         return lib

@@ -267,6 +267,11 @@ def test_reference_op_names_resolve_to_these_kernels(mtq):
     c = torch.ops.tensorrt.dynamic_block_quantize_op(x, 16, amax, 4, 2, 8, 4)
     assert torch.equal(c, mtq.ops.nvfp4_fake(x, amax))
     assert torch.ops.tensorrt.quantize_op(x.to("meta"), amax.to("meta"), 8, 0, False, True).shape == x.shape
+    # the overload without a global amax: NVFP4 takes the tensor's own abs-max, the MX formats need none
+    d = torch.ops.tensorrt.dynamic_block_quantize_op.overload(x, 16, None, 4, 2, 8, 4)
+    assert torch.equal(d, c)
+    e = torch.ops.tensorrt.dynamic_block_quantize_op.overload(x, 32, None, 8, 4, 9, 8)
+    assert torch.equal(e, mtq.ops.mx_fake(x, 32, (4, 3)))
 
 
 def test_batched_exchanges_over_nccl_single_rank(mtq):
