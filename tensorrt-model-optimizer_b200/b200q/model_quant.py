@@ -12,7 +12,7 @@ from .model_calib import awq, max_calibrate, mse_calibrate, smoothquant
 from .nn import QuantLinear, RealQuantLinear, SequentialQuantizer, TensorQuantizer
 from .qtensor import pack_real_quantize_weight
 
-__all__ = ["quantize", "calibrate", "compress", "disable_quantizer", "enable_quantizer",
+__all__ = ["quantize", "calibrate", "compress", "restore_from_modelopt_state", "disable_quantizer", "enable_quantizer",
            "print_quant_summary", "fold_weight", "modelopt_state"]
 
 def _awq_variant(variant):
@@ -117,9 +117,58 @@ def _record_mode(model, mode, config=None):
 
 
 def modelopt_state(model: nn.Module) -> dict:
-    """Modes applied so far plus the per-quantiser Python state (buffers are in ``state_dict()``)."""
+    """Everything besides ``state_dict()`` that is needed to rebuild a quantised model: the modes
+    applied so far with their configurations, the per-quantiser Python state (properties and buffer
+    shapes, reference nn/modules/tensor_quantizer.py:1000-1072) and, for compressed models, the
+    metadata of the packed weights (reference compress.py:179-193, qtensor/base_qtensor.py:130-136)."""
+    from .qtensor import QTensorWrapper
+
+    def qstate(m):
+        if isinstance(m, SequentialQuantizer):
+            return {"is_sequential_quantizer": True, "members": [q.get_modelopt_state() for q in m]}
+        return m.get_modelopt_state()
+
     return {
         "modelopt_state_dict": list(model.__dict__.get("_b200q_state", [])),
-        "quantizer_state": {n: m.get_modelopt_state() for n, m in model.named_modules()
-                            if isinstance(m, TensorQuantizer)},
+        "quantizer_state": {n: qstate(m) for n, m in model.named_modules()
+                            if isinstance(m, (TensorQuantizer, SequentialQuantizer))
+                            and not any(isinstance(p, SequentialQuantizer) and n.startswith(pn + ".")
+                                        for pn, p in model.named_modules())},
+        "q_tensor_state": {n: dict(m.weight.get_state(), device=str(m.weight.device))
+                           for n, m in model.named_modules()
+                           if isinstance(m, QuantLinear) and isinstance(m.weight, QTensorWrapper)},
     }
+
+
+@torch.no_grad()
+def restore_from_modelopt_state(model: nn.Module, state: dict) -> nn.Module:
+    """Rebuild the quantised structure of a freshly constructed ``model`` from ``modelopt_state``:
+    modules are converted, every quantiser gets its properties and empty buffers of the recorded
+    shapes, compressed layers get packed-weight placeholders.  ``model.load_state_dict(...)`` then
+    restores the values (reference opt/conversion.py:444-611 for this path's modes)."""
+    from .conversion import replace_quant_module, set_quantizer_by_cfg
+    from .qtensor import QTensorWrapper
+
+    modes = state.get("modelopt_state_dict", [])
+    replace_quant_module(model)
+    for mode, cfg in modes:
+        if mode == "quantize" and cfg is not None:
+            set_quantizer_by_cfg(model, cfg["quant_cfg"])       # also builds SequentialQuantizers
+    named = dict(model.named_modules())
+    for name, st in state.get("quantizer_state", {}).items():
+        q = named.get(name)
+        if q is None:
+            raise KeyError(f"quantizer {name} of the saved state does not exist in the model")
+        if st.get("is_sequential_quantizer"):
+            for member, ms in zip(q, st["members"]):
+                member.set_from_modelopt_state(ms)
+        else:
+            q.set_from_modelopt_state(st)
+        q.to(next((p.device for p in model.parameters()), torch.device("cpu")))
+    for name, meta in state.get("q_tensor_state", {}).items():
+        m = named[name]
+        m.__class__ = RealQuantLinear
+        packed = torch.empty(meta["quantized_data.shape"], dtype=meta["quantized_data.dtype"], device=m.weight.device)
+        m.weight = QTensorWrapper(packed, metadata=dict(meta["metadata"]))
+    model.__dict__["_b200q_state"] = list(modes)
+    return model

@@ -547,7 +547,7 @@ class TensorQuantizer(nn.Module):
 
     def get_modelopt_state(self, properties_only=False):
         """Python-side state needed to rebuild the quantiser (buffers travel in the state dict)."""
-        skip = {"_calibrator", "_original_shape", "_block_reshape_size", "_padding", "_slices",
+        skip = {"_calibrator", "_bias_calibrator", "_original_shape", "_block_reshape_size", "_padding", "_slices",
                 "_amax_shape_for_export", "_input_dtype"}
         state = {k: v for k, v in self.__dict__.items()
                  if k.startswith("_") and k not in skip and k not in nn.Module().__dict__

@@ -303,3 +303,41 @@ def test_bias_calibrator_matches_reference_values():
     assert mean.compute_bias() is None
     with pytest.raises(ValueError):
         BiasCalibrator("median")
+
+
+@pytest.mark.parametrize("name", ["NVFP4_DEFAULT_CFG", "W4A8_AWQ_BETA_CFG", "INT8_DEFAULT_CFG"])
+def test_modelopt_state_restores_structure_on_cpu(name):
+    """Checkpoint / resume without compute: the recorded modes, the quantiser properties and the
+    buffer shapes are enough for ``load_state_dict(strict=True)`` on a fresh model."""
+    import copy
+    import io
+
+    torch.manual_seed(0)
+    m = MLP()
+    from b200q.conversion import convert_to_quantized_model
+    from b200q.model_quant import _record_mode
+    cfg = copy.deepcopy(getattr(mtq, name))
+    convert_to_quantized_model(m, cfg)
+    _record_mode(m, "quantize", cfg)
+    # stand-in for calibration: amax buffers of the shapes calibration would leave
+    for n, q in m.named_modules():
+        if isinstance(q, TensorQuantizer) and q.is_enabled \
+                and not (q.block_sizes and q.block_sizes.get("type") == "dynamic"):
+            q.amax = torch.rand(()) + 0.5
+    m.up_proj.input_quantizer.pre_quant_scale = torch.rand(32) + 0.5
+    buf = io.BytesIO()
+    torch.save({"model": m.state_dict(), "modelopt": mtq.modelopt_state(m)}, buf)
+    buf.seek(0)
+    ckpt = torch.load(buf, weights_only=False)
+
+    fresh = MLP()
+    mtq.restore_from_modelopt_state(fresh, ckpt["modelopt"])
+    fresh.load_state_dict(ckpt["model"], strict=True)
+    for (na, a), (nb, b) in zip(m.named_modules(), fresh.named_modules()):
+        assert na == nb and type(a) is type(b)
+        if isinstance(a, TensorQuantizer):
+            assert a.get_modelopt_state() == b.get_modelopt_state(), na
+    assert torch.equal(fresh.up_proj.input_quantizer.pre_quant_scale, m.up_proj.input_quantizer.pre_quant_scale)
+    with pytest.raises(KeyError):
+        bad = dict(ckpt["modelopt"], quantizer_state={"no.such.quantizer": {}})
+        mtq.restore_from_modelopt_state(MLP(), bad)

@@ -135,3 +135,37 @@ def test_llama_shaped_checkpoint_export(name):
                 assert sd[p + "weight_scale_2"].dtype == torch.float32
             else:
                 assert sd[p + "weight"].dtype == torch.float8_e4m3fn
+
+
+@pytest.mark.parametrize("name,do_compress", [("NVFP4_DEFAULT_CFG", True), ("INT4_AWQ_CFG", True),
+                                              ("W4A8_AWQ_BETA_CFG", False), ("FP8_DEFAULT_CFG", False),
+                                              ("INT8_SMOOTHQUANT_CFG", False)])
+def test_save_and_restore_quantized_model(name, do_compress, tmp_path):
+    """Checkpoint / resume: state_dict + modelopt_state of a quantised (and compressed) model,
+    written to disk, restore a freshly constructed model to the same outputs."""
+    import b200q as mtq
+    from b200q.qtensor import QTensorWrapper
+
+    torch.manual_seed(0)
+    model = TinyLlama().to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 512, (2, 64), device="cuda")
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(ids))
+    if do_compress:
+        mtq.compress(model)
+    with torch.no_grad():
+        want = model(ids)
+    torch.save({"model": model.state_dict(), "modelopt": mtq.modelopt_state(model)}, tmp_path / "ckpt.pt")
+
+    ckpt = torch.load(tmp_path / "ckpt.pt", weights_only=False)
+    torch.manual_seed(123)                                   # different initial weights
+    fresh = TinyLlama().to(torch.bfloat16).cuda().eval()
+    mtq.restore_from_modelopt_state(fresh, ckpt["modelopt"])
+    missing, unexpected = fresh.load_state_dict(ckpt["model"], strict=True)
+    assert not missing and not unexpected
+    if do_compress:
+        assert isinstance(fresh.layers[0].mlp.up_proj.weight, QTensorWrapper)
+    with torch.no_grad():
+        got = fresh(ids)
+    assert torch.equal(got, want)
+    assert [m for m, _ in mtq.modelopt_state(fresh)["modelopt_state_dict"]] == \
+           [m for m, _ in ckpt["modelopt"]["modelopt_state_dict"]]
