@@ -318,6 +318,45 @@ int b200q_mx_fake(const void* x, void* y, int64_t nblocks, int block, int dtype,
 int b200q_mxfp4_quantize(const void* x, int64_t nblocks, int block, int dtype, uint8_t* packed,
                          uint8_t* scales, void* stream);
 
+/* ---------------------------------------------------------------- real-quant GEMMs ---------- */
+
+/* FP8 per-tensor linear layer on the tensor cores (tcgen05 kind::f8f6f4, fp32 accumulation in TMEM):
+ *   out[m, n] = T(sum_k a[m, k] * b[n, k] * (*scale_a) * (*scale_b) + bias[n])
+ * a [m, k], b [n, k] E4M3 bytes, k contiguous; scale_a, scale_b device fp32 scalars (scale_b may be
+ * NULL = 1); bias [n] of type T or NULL; out [m, n] of type T.  k a multiple of 16, n of 8; rows
+ * beyond m or n are never read or written.  *status_io (device word, caller zeroes it) receives
+ * error bits if a bounded wait inside the kernel ran out.  Replaces torch._scaled_mm in
+ * _fp8_gemm_impl (modelopt/torch/quantization/backends/fp8_per_tensor_gemm.py:41-55). */
+int b200q_fp8_gemm(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
+                   const void* bias, void* out, int64_t m, int64_t n, int64_t k, int dtype,
+                   uint32_t* status_io, void* stream);
+
+/* The activation (or weight) operand of b200q_fp8_gemm: q = e4m3(clamp(T(x / *scale), -448, 448)),
+ * *scale a device scalar of type T, n elements.  Replaces _to_fp8
+ * (modelopt/torch/quantization/backends/fp8_per_tensor_gemm.py:35-37). */
+int b200q_fp8_gemm_operand(const void* x, const void* scale, uint8_t* q, int64_t n, int dtype,
+                           void* stream);
+
+/* NVFP4 linear layer on the tensor cores (tcgen05 kind::mxf4nvf4 with block scaling):
+ *   out[m, n] = T(T(*alpha * sum_blk sfa[m, blk] * sfb[n, blk] * sum_{j<16} a[m, 16 blk + j] * b[n, 16 blk + j]) + bias[n])
+ * a [m, k/2], b [n, k/2] packed E2M1 (even element in the low nibble); sfa, sfb E4M3 block scales
+ * in the tiled order b200q_nvfp4_swizzle_scales writes; alpha device fp32 scalar (the product of
+ * the two per-tensor scales); k a multiple of 32, n of 8.  Replaces torch.ops.trtllm.nvfp4_gemm
+ * (modelopt/torch/quantization/backends/nvfp4_gemm.py:57-64). */
+int b200q_nvfp4_gemm(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                     const float* alpha, const void* bias, void* out, int64_t m, int64_t n, int64_t k,
+                     int dtype, uint32_t* status_io, void* stream);
+
+/* Block scales [rows, cols] (one byte per 16 elements, row-major, as b200q_nvfp4_quantize writes
+ * them) into 128-row x 4-scale tiles of 512 bytes: scale (r, c) goes to byte
+ *   ((r / 128) * tiles_k + c / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4,
+ * tiles_k = 4 * ceil(cols / 16); rows are padded to 128 and cols to 16 with zeros, so `swizzled`
+ * holds ceil(rows / 128) * tiles_k * 512 bytes.  For cols a multiple of 16 this is the scale order
+ * of the block-scaled tensor-core instructions (the layout fp4_quantize of the reference's GEMM
+ * backend returns, nvfp4_gemm.py:55). */
+int b200q_nvfp4_swizzle_scales(const uint8_t* scales, uint8_t* swizzled, int64_t rows, int64_t cols,
+                               void* stream);
+
 /* ---------------------------------------------------------------- export packers ------------ */
 
 /* INT4 weights in the checkpoint layout: q = clamp(round_half_even(w / scale[r, c/block]), -8, 7)

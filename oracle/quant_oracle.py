@@ -540,3 +540,50 @@ def mxfp4_dequantize(packed: np.ndarray, scales: np.ndarray, block=32, T="f32") 
     v = np.where(codes & 8, -mags, mags).astype(np.float32)
     v = v.reshape(-1, block) * np.exp2(scales.reshape(-1, 1).astype(np.float32) - 127).astype(np.float32)
     return round_to(v.reshape(codes.shape).astype(np.float32), T)
+
+
+# --------------------------------------------------------------------------- real-quant GEMMs ---
+# The reference hands these products to library kernels (torch._scaled_mm, and TensorRT-LLM's
+# nvfp4_gemm, which is not in the reference tree): the oracle is the defining sum in float64, so a
+# comparison with it carries the fp32-accumulation tolerance stated in the tests.
+
+def fp8_to_gemm_operand(x: np.ndarray, scale, T="f32") -> np.ndarray:
+    """_to_fp8 (backends/fp8_per_tensor_gemm.py:35-37): (x / scale).clamp(-448, 448).to(e4m3), the
+    quotient in x's dtype."""
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        q = round_to((np.asarray(x, F32) / F32(scale)).astype(F32), T)
+    return e4m3_encode(np.clip(q, F32(-448.0), F32(448.0)), "torch")
+
+
+def fp8_gemm(a8: np.ndarray, b8: np.ndarray, scale_a, scale_b, bias=None, T="f32") -> np.ndarray:
+    """_fp8_gemm_impl (backends/fp8_per_tensor_gemm.py:41-55): a8 [m, k], b8 [n, k] E4M3 codes;
+    T(sum_k a b * scale_a * scale_b + bias)."""
+    acc = e4m3_decode(a8).astype(np.float64) @ e4m3_decode(b8).astype(np.float64).T
+    y = acc * np.float64(F32(scale_a)) * np.float64(F32(scale_b))
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    return round_to(y.astype(F32), T)
+
+
+def nvfp4_gemm(a4: np.ndarray, sfa: np.ndarray, b4: np.ndarray, sfb: np.ndarray, alpha, bias=None,
+               T="f32") -> np.ndarray:
+    """_fp4_linear (backends/nvfp4_gemm.py:33-69): a4 [m, k/2], b4 [n, k/2] packed E2M1, sfa
+    [m, k/16], sfb [n, k/16] E4M3 codes (row-major); T(T(alpha * sum) + bias)."""
+    a = nvfp4_dequantize(a4, sfa, 1.0).astype(np.float64)
+    b = nvfp4_dequantize(b4, sfb, 1.0).astype(np.float64)
+    y = round_to(((a @ b.T) * np.float64(F32(alpha))).astype(F32), T)
+    if bias is not None:
+        y = round_to((y + np.asarray(bias, F32)).astype(F32), T)
+    return y
+
+
+def nvfp4_swizzle_scales(scales: np.ndarray) -> np.ndarray:
+    """Block scales [rows, cols] (bytes) in the 128-row x 4-scale tile order of the block-scaled
+    tensor-core instructions: byte (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4 of tile
+    [r / 128][c / 4]; rows padded to 128, cols to 16."""
+    rows, cols = scales.shape
+    rt, ct = -(-rows // 128), -(-cols // 16) * 4
+    padded = np.zeros((rt * 128, ct * 4), dtype=np.uint8)
+    padded[:rows, :cols] = scales
+    t = padded.reshape(rt, 4, 32, ct, 4)            # [row tile, r / 32, r % 32, col tile, c % 4]
+    return np.ascontiguousarray(t.transpose(0, 3, 2, 1, 4)).reshape(-1)

@@ -7,6 +7,8 @@ children.  The forward is ``F.linear(input_quantizer(x), weight_quantizer(W), b)
 """
 from __future__ import annotations
 
+import warnings
+
 import torch
 import torch.nn.functional as F
 from torch import nn
@@ -66,8 +68,33 @@ class QuantLinear(nn.Linear, QuantModule):
 
 
 class RealQuantLinear(QuantLinear):
-    """QuantLinear whose weight is stored packed (after ``compress``); the forward dequantises it
-    through the weight quantiser."""
+    """QuantLinear whose weight is stored packed (after ``compress``).  The forward runs a
+    registered real-quant GEMM on the packed weight when one is enabled and applies
+    (``backends.enable_real_quant_gemm``; reference quant_linear.py:191-239), else dequantises the
+    weight through the weight quantiser."""
+
+    allow_real_quant_gemm = True
+
+    @property
+    def _should_run_real_quant_gemm(self):
+        iq = self.input_quantizer
+        return (getattr(self, "_use_real_quant_gemm", False) and self.allow_real_quant_gemm
+                and not (iq.is_enabled and iq._if_calib))
+
+    def has_real_quant_gemm_impl(self, input, *args, **kwargs) -> bool:
+        if not hasattr(self, "_real_quant_gemm_impl"):      # matched once, then kept
+            from .. import backends
+            self._real_quant_gemm_impl = backends.gemm_registry.find_match(self, input, *args, **kwargs)
+            if self._real_quant_gemm_impl is None:
+                warnings.warn(f"RealQuantLinear: no real-quant GEMM found: {self}.")
+        return self._real_quant_gemm_impl is not None
+
+    def forward(self, input, *args, **kwargs):
+        if (self._should_run_real_quant_gemm and input.numel() > 1
+                and self.has_real_quant_gemm_impl(input, *args, **kwargs)):
+            out = self._real_quant_gemm_impl(self, input, self.weight, self.bias, *args, **kwargs)
+            return self.output_quantizer(out)
+        return super().forward(input, *args, **kwargs)
 
     def _quantized_weight(self):
         w = self.weight

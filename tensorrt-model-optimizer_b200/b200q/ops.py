@@ -550,3 +550,100 @@ def hadamard(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
         call("b200q_hadamard", x.data_ptr(), y.data_ptr(), x.numel() // n, n, dtype_code(x), ctypes.c_float(scale),
              _stream(x))
     return y
+
+
+# --------------------------------------------------------------------------- real-quant GEMMs --
+
+_QGEMM_STATUS: dict = {}
+
+
+def qgemm_status(device) -> torch.Tensor:
+    """The int32 device word that collects error bits of the GEMM kernels' bounded waits on
+    ``device`` (0 = every wait completed).  Reading it synchronises; the layers never do."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    st = _QGEMM_STATUS.get(device)
+    if st is None:
+        st = _QGEMM_STATUS[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return st
+
+
+def check_qgemm_status(device):
+    code = int(qgemm_status(device).item())
+    if code:
+        qgemm_status(device).zero_()
+        raise RuntimeError(f"a bounded wait inside a tensor-core GEMM kernel ran out (status bits {code:#x})")
+
+
+def _gemm_out(a, n, bias, out_dtype):
+    if out_dtype not in _DT:
+        raise TypeError(f"unsupported output dtype {out_dtype}")
+    if bias is not None:
+        bias = _cuda(bias, "bias").to(out_dtype).contiguous()
+        assert bias.numel() == n
+    return torch.empty((a.shape[0], n), dtype=out_dtype, device=a.device), bias
+
+
+def fp8_gemm(a8: torch.Tensor, b8: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor | None = None,
+             bias: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """a8 [m, k], b8 [n, k] float8_e4m3fn (or their bytes), fp32 device scalars scale_a / scale_b ->
+    out_dtype [m, n] = a8 @ b8.T * scale_a * scale_b + bias, on the tensor cores."""
+    a8 = _cuda(a8, "a").contiguous().view(torch.uint8)
+    b8 = _cuda(b8, "b").contiguous().view(torch.uint8)
+    assert a8.dim() == 2 and b8.dim() == 2 and a8.shape[1] == b8.shape[1]
+    (m, k), n = a8.shape, b8.shape[0]
+    sa = _amax_f32(scale_a, a8.device).reshape(())
+    sb = _amax_f32(scale_b, a8.device).reshape(()) if scale_b is not None else None
+    out, bias = _gemm_out(a8, n, bias, out_dtype)
+    with torch.cuda.device(a8.device):
+        call("b200q_fp8_gemm", a8.data_ptr(), b8.data_ptr(), sa.data_ptr(), sb.data_ptr() if sb is not None else None,
+             bias.data_ptr() if bias is not None else None, out.data_ptr(), m, n, k, _DT[out_dtype],
+             qgemm_status(a8.device).data_ptr(), _stream(a8))
+    return out
+
+
+def fp8_gemm_operand(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3(clamp(x / scale, -448, 448)) with the quotient in x's dtype; ``scale`` has one element."""
+    x = _prep(x)
+    s = _cuda(scale, "scale").detach().to(x.dtype).reshape(1).contiguous()
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        call("b200q_fp8_gemm_operand", x.data_ptr(), s.data_ptr(), q.data_ptr(), x.numel(), dtype_code(x), _stream(x))
+    return q.view(torch.float8_e4m3fn)
+
+
+def nvfp4_swizzled_scale_bytes(rows: int, cols: int) -> int:
+    return -(-rows // 128) * (-(-cols // 16) * 4) * 512
+
+
+def nvfp4_swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
+    """Block scales [rows, K/16] (float8_e4m3fn or bytes, row-major) -> flat uint8 in the 128 x 4 tile
+    order the block-scaled GEMM reads (rows padded to 128, K to 256, with zeros)."""
+    s = _cuda(scales, "scales").contiguous().view(torch.uint8)
+    s = s.reshape(-1, s.shape[-1])
+    rows, cols = s.shape
+    out = torch.empty(nvfp4_swizzled_scale_bytes(rows, cols), dtype=torch.uint8, device=s.device)
+    with torch.cuda.device(s.device):
+        call("b200q_nvfp4_swizzle_scales", s.data_ptr(), out.data_ptr(), rows, cols, _stream(s))
+    return out
+
+
+def nvfp4_gemm(a4: torch.Tensor, sfa: torch.Tensor, b4: torch.Tensor, sfb: torch.Tensor, alpha: torch.Tensor,
+               bias: torch.Tensor | None = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """a4 [m, k/2], b4 [n, k/2] packed E2M1; sfa, sfb the block scales as ``nvfp4_swizzle_scales``
+    returns them; alpha fp32 device scalar -> out_dtype [m, n], on the tensor cores."""
+    a4 = _cuda(a4, "a").contiguous().view(torch.uint8)
+    b4 = _cuda(b4, "b").contiguous().view(torch.uint8)
+    assert a4.dim() == 2 and b4.dim() == 2 and a4.shape[1] == b4.shape[1]
+    m, n, k = a4.shape[0], b4.shape[0], a4.shape[1] * 2
+    sfa, sfb = _cuda(sfa, "sfa").view(torch.uint8), _cuda(sfb, "sfb").view(torch.uint8)
+    assert sfa.numel() == nvfp4_swizzled_scale_bytes(m, k // 16), "sfa is not in the tiled order for this shape"
+    assert sfb.numel() == nvfp4_swizzled_scale_bytes(n, k // 16), "sfb is not in the tiled order for this shape"
+    al = _amax_f32(alpha, a4.device).reshape(())
+    out, bias = _gemm_out(a4, n, bias, out_dtype)
+    with torch.cuda.device(a4.device):
+        call("b200q_nvfp4_gemm", a4.data_ptr(), b4.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), al.data_ptr(),
+             bias.data_ptr() if bias is not None else None, out.data_ptr(), m, n, k, _DT[out_dtype],
+             qgemm_status(a4.device).data_ptr(), _stream(a4))
+    return out

@@ -15,6 +15,13 @@ struct ToE4m3 {
     return f32_to_e4m3_torch(round_to_t<T>(__fdiv_rn(x, scale)));
   }
 };
+// saturating variant: the quotient is clamped to the E4M3 range before the cast (NaN stays NaN)
+struct ToE4m3Sat {
+  template <typename T> static __device__ __forceinline__ uint32_t cvt(float x, float scale) {
+    const float v = round_to_t<T>(__fdiv_rn(x, scale));
+    return f32_to_e4m3_torch(v != v ? v : fminf(448.f, fmaxf(-448.f, v)));
+  }
+};
 struct ToInt8 {
   template <typename T> static __device__ __forceinline__ uint32_t cvt(float x, float scale) {
     float r = rintf(round_to_t<T>(__fdiv_rn(x, scale)));
@@ -106,6 +113,14 @@ extern "C" int b200q_fp8_quantize(const void* x, const void* scales, uint8_t* q,
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x);
   if (outer <= 0 || axis <= 0 || inner <= 0) return B200Q_ERR_SHAPE;
   return launch_qcast<ToE4m3>(x, scales, q, outer, axis, inner, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200q_fp8_gemm_operand(const void* x, const void* scale, uint8_t* q, int64_t n, int dtype,
+                                      void* stream) {
+  B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(scale); B200Q_REQUIRE_PTR(q);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x);
+  if (n <= 0) return B200Q_ERR_SHAPE;
+  return launch_qcast<ToE4m3Sat>(x, scale, q, n, 1, 1, dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200q_int8_quantize(const void* x, const void* scales, int8_t* q, int64_t outer,

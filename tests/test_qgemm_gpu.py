@@ -1,0 +1,256 @@
+"""Real-quant GEMM consumers (tcgen05 kind::f8f6f4 and kind::mxf4nvf4) against the float64 oracle.
+
+Tolerance: the kernels accumulate in fp32 inside the tensor cores in an order the hardware chooses,
+so results are compared with the float64 sum at |err| <= 2^-7 * |y| + 2e-3 * sum_k |a_k b_k| * scale
+(one bf16 ulp of the result plus an fp32-accumulation allowance); layouts and scale plumbing are
+bit-exact (swizzle kernel)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), ".."))
+from oracle import quant_oracle as qo  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from b200q import ops
+    return ops
+
+
+def _check(got: torch.Tensor, want: np.ndarray, absdot: np.ndarray, what):
+    g = got.float().cpu().numpy().astype(np.float64)
+    tol = np.abs(want) * 2.0 ** -7 + 2e-3 * absdot + 1e-30
+    bad = np.abs(g - want) > tol
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance, worst " \
+                          f"{np.max(np.abs(g - want) / tol):.2f}x"
+
+
+@pytest.mark.parametrize("rows,cols", [(128, 16), (256, 32), (137, 21), (1, 4), (300, 16), (512, 512)])
+def test_swizzle_scales_matches_oracle(rows, cols):
+    ops = _ops()
+    rng = np.random.default_rng(rows * 1000 + cols)
+    s = rng.integers(0, 127, size=(rows, cols), dtype=np.uint8)
+    got = ops.nvfp4_swizzle_scales(torch.from_numpy(s).cuda()).cpu().numpy()
+    assert np.array_equal(got, qo.nvfp4_swizzle_scales(s))
+
+
+def _fp8_case(m, n, k, seed, dtype, with_bias):
+    rng = np.random.default_rng(seed)
+    a8 = qo.e4m3_encode(rng.standard_normal((m, k)).astype(np.float32) * 2, "torch")
+    b8 = qo.e4m3_encode(rng.standard_normal((n, k)).astype(np.float32) * 2, "torch")
+    sa, sb = np.float32(0.013), np.float32(0.37)
+    bias = rng.standard_normal(n).astype(np.float32) if with_bias else None
+    if bias is not None:
+        bias = torch.from_numpy(bias).to(dtype).float().numpy()
+    return a8, b8, sa, sb, bias
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 256, 512), (256, 512, 1024), (100, 136, 80),
+                                   (1, 128, 256), (333, 1000, 4096), (512, 4096, 512), (2048, 2048, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_fp8_gemm_matches_float64_sum(m, n, k, dtype):
+    if dtype is not torch.bfloat16 and m * n * k > 256 * 512 * 1024:
+        pytest.skip("large shapes run in bf16 only")
+    ops = _ops()
+    T = {torch.bfloat16: "bf16", torch.float16: "f16", torch.float32: "f32"}[dtype]
+    a8, b8, sa, sb, bias = _fp8_case(m, n, k, m + n + k, dtype, with_bias=(m % 2 == 0))
+    got = ops.fp8_gemm(torch.from_numpy(a8).cuda(), torch.from_numpy(b8).cuda(), torch.tensor(sa), torch.tensor(sb),
+                       None if bias is None else torch.from_numpy(bias).cuda(), dtype)
+    ops.check_qgemm_status("cuda")
+    af, bf = qo.e4m3_decode(a8).astype(np.float64), qo.e4m3_decode(b8).astype(np.float64)
+    want = af @ bf.T * float(sa) * float(sb) + (0 if bias is None else bias.astype(np.float64))
+    absdot = np.abs(af) @ np.abs(bf).T * float(sa) * float(sb)
+    _check(got, want, absdot, f"fp8 {m}x{n}x{k}")
+    # and the rounded oracle itself within one ulp of T
+    ref = qo.fp8_gemm(a8, b8, sa, sb, bias, T).astype(np.float64)
+    _check(got, ref, absdot, f"fp8 oracle {m}x{n}x{k}")
+
+
+def test_fp8_gemm_tile_choices_agree(monkeypatch):
+    ops = _ops()
+    a8, b8, sa, sb, _ = _fp8_case(256, 512, 768, 5, torch.bfloat16, False)
+    outs = []
+    for tile in ("128", "256"):
+        monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
+        outs.append(ops.fp8_gemm(torch.from_numpy(a8).cuda(), torch.from_numpy(b8).cuda(), torch.tensor(sa),
+                                 torch.tensor(sb)))
+    ops.check_qgemm_status("cuda")
+    assert torch.equal(outs[0], outs[1])     # same K order within a tile: identical sums
+
+
+def test_fp8_gemm_integer_inputs_are_exact():
+    """Small integers: every product and partial sum is exact in fp32, so the result is too."""
+    ops = _ops()
+    rng = np.random.default_rng(0)
+    a = rng.integers(-4, 5, size=(256, 512)).astype(np.float32)
+    b = rng.integers(-4, 5, size=(384, 512)).astype(np.float32)
+    got = ops.fp8_gemm(torch.from_numpy(a).cuda().to(torch.float8_e4m3fn), torch.from_numpy(b).cuda().to(torch.float8_e4m3fn),
+                       torch.tensor(1.0), torch.tensor(1.0), None, torch.float32)
+    ops.check_qgemm_status("cuda")
+    assert np.array_equal(got.cpu().numpy(), a @ b.T)
+
+
+def _nvfp4_operand(rng, rows, k):
+    x = (rng.standard_normal((rows, k)) * np.exp(rng.standard_normal((rows, 1)))).astype(np.float32)
+    packed, scales, s2 = qo.nvfp4_quantize(x, 16)
+    return x, packed, scales, s2
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (128, 256, 512), (256, 512, 1024), (100, 136, 320),
+                                   (1, 128, 64), (333, 1000, 4096), (512, 4096, 512), (2048, 2048, 2048)])
+def test_nvfp4_gemm_matches_float64_sum(m, n, k):
+    ops = _ops()
+    rng = np.random.default_rng(m + 3 * n + 7 * k)
+    _, a4, sfa, s2a = _nvfp4_operand(rng, m, k)
+    _, b4, sfb, s2b = _nvfp4_operand(rng, n, k)
+    alpha = np.float32(s2a) * np.float32(s2b)
+    bias = rng.standard_normal(n).astype(np.float32) if m % 2 == 0 else None
+    if bias is not None:
+        bias = torch.from_numpy(bias).to(torch.bfloat16).float().numpy()
+    dev = lambda t: torch.from_numpy(t).cuda()  # noqa: E731
+    got = ops.nvfp4_gemm(dev(a4), ops.nvfp4_swizzle_scales(dev(sfa)), dev(b4), ops.nvfp4_swizzle_scales(dev(sfb)),
+                         torch.tensor(alpha), None if bias is None else dev(bias), torch.bfloat16)
+    ops.check_qgemm_status("cuda")
+    af = qo.nvfp4_dequantize(a4, sfa, 1.0).astype(np.float64)
+    bf = qo.nvfp4_dequantize(b4, sfb, 1.0).astype(np.float64)
+    want = af @ bf.T * float(alpha) + (0 if bias is None else bias.astype(np.float64))
+    absdot = np.abs(af) @ np.abs(bf).T * float(alpha)
+    _check(got, want, absdot, f"nvfp4 {m}x{n}x{k}")
+    ref = qo.nvfp4_gemm(a4, sfa, b4, sfb, alpha, bias, "bf16").astype(np.float64)
+    _check(got, ref, absdot, f"nvfp4 oracle {m}x{n}x{k}")
+
+
+def test_nvfp4_gemm_exact_on_exactly_representable_products():
+    """Codes in {0, +-1, +-2} with power-of-two block scales: every partial sum is an integer multiple
+    of a power of two well inside fp32, so the kernel must reproduce the sum exactly; this pins the
+    nibble order, the block-to-scale mapping and the row/column order of the scale tiles."""
+    ops = _ops()
+    rng = np.random.default_rng(1)
+    m, n, k = 256, 384, 512
+    codes = np.array([0, 2, 4, 10, 12], dtype=np.uint8)          # 0, 1, 2, -1, -2
+    qa, qb = rng.choice(codes, size=(m, k)), rng.choice(codes, size=(n, k))
+    a4 = ((qa[:, 1::2] << 4) | qa[:, 0::2]).astype(np.uint8)
+    b4 = ((qb[:, 1::2] << 4) | qb[:, 0::2]).astype(np.uint8)
+    pow2 = np.array([0x28, 0x30, 0x38, 0x40, 0x48], dtype=np.uint8)   # E4M3 0.25, 0.5, 1, 2, 4
+    sfa, sfb = rng.choice(pow2, size=(m, k // 16)), rng.choice(pow2, size=(n, k // 16))
+    dev = lambda t: torch.from_numpy(t).cuda()  # noqa: E731
+    got = ops.nvfp4_gemm(dev(a4), ops.nvfp4_swizzle_scales(dev(sfa)), dev(b4), ops.nvfp4_swizzle_scales(dev(sfb)),
+                         torch.tensor(1.0), None, torch.float32)
+    ops.check_qgemm_status("cuda")
+    want = qo.nvfp4_dequantize(a4, sfa, 1.0).astype(np.float64) @ qo.nvfp4_dequantize(b4, sfb, 1.0).astype(np.float64).T
+    assert np.array_equal(got.cpu().numpy().astype(np.float64), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_fp8_gemm_operand_matches_oracle_bytes(dtype):
+    ops = _ops()
+    T = {torch.bfloat16: "bf16", torch.float16: "f16", torch.float32: "f32"}[dtype]
+    rng = np.random.default_rng(3)
+    x = torch.from_numpy((rng.standard_normal((64, 1000)) * 3).astype(np.float32)).to(dtype)
+    x[0, :4] = torch.tensor([1e4, -1e4, float("nan"), 0.0], dtype=dtype)      # beyond the range: saturate
+    scale = torch.tensor(0.0123).to(dtype)
+    got = ops.fp8_gemm_operand(x.cuda(), scale.cuda()).view(torch.uint8).cpu().numpy()
+    want = qo.fp8_to_gemm_operand(x.float().numpy(), scale.float().item(), T)
+    assert np.array_equal(got, want)
+    assert got[0, 0] == 0x7E and got[0, 1] == 0xFE and (got[0, 2] & 0x7F) == 0x7F
+
+
+# ------------------------------------------------------------------ layer level ---------------------
+
+def _one_layer(cfg_name, k=512, n=384, bias=True, tokens=(4, 48)):
+    import copy
+
+    import b200q as mtq
+    from torch import nn
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(k, n, bias=bias)).to(torch.bfloat16).cuda()
+    x = torch.randn(*tokens, k, device="cuda", dtype=torch.bfloat16)
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, cfg_name)), lambda m: m(x))
+    with torch.no_grad():
+        fake = model(x)
+    mtq.compress(model)
+    with torch.no_grad():
+        dequant = model(x)
+    return mtq, model, x, fake, dequant
+
+
+@pytest.mark.parametrize("cfg_name,impl", [("FP8_DEFAULT_CFG", "Fp8PerTensorLinear"), ("NVFP4_DEFAULT_CFG", "Nvfp4Linear")])
+@pytest.mark.parametrize("bias", [True, False])
+def test_real_quant_linear_runs_registered_gemm(cfg_name, impl, bias):
+    """enable_real_quant_gemm switches the compressed layer to the tensor-core GEMM; the result
+    agrees with the dequantise-then-bf16-GEMM path to bf16 rounding of the two different sums."""
+    mtq, model, x, fake, dequant = _one_layer(cfg_name, bias=bias)
+    from b200q import backends, ops
+    from b200q.nn import RealQuantLinear
+    assert isinstance(model[0], RealQuantLinear)
+    backends.enable_real_quant_gemm(model)
+    assert backends.is_real_quant_gemm_enabled(model)
+    with torch.no_grad():
+        out = model(x)
+    ops.check_qgemm_status("cuda")
+    assert model[0]._real_quant_gemm_impl == getattr(backends, impl).apply
+    assert out.shape == dequant.shape and out.dtype == dequant.dtype
+    err = (out.float() - dequant.float()).abs().max() / dequant.float().abs().max()
+    assert err < 2e-2, err
+    cos = torch.nn.functional.cosine_similarity(out.float().flatten(), dequant.float().flatten(), dim=0)
+    assert cos > 0.9995, cos
+    backends.disable_real_quant_gemm(model)
+    with torch.no_grad():
+        assert torch.equal(model(x), dequant)
+
+
+def test_real_quant_gemm_not_used_when_shapes_do_not_qualify():
+    mtq, model, x, fake, dequant = _one_layer("NVFP4_DEFAULT_CFG", k=544, n=384)     # k % 64 != 0
+    from b200q import backends
+    backends.enable_real_quant_gemm(model)
+    with pytest.warns(UserWarning, match="no real-quant GEMM"):
+        with torch.no_grad():
+            out = model(x)
+    assert torch.equal(out, dequant)
+
+
+@pytest.mark.parametrize("cfg_name", ["FP8_DEFAULT_CFG", "NVFP4_DEFAULT_CFG"])
+def test_real_quant_gemm_backward_uses_high_precision(cfg_name):
+    mtq, model, x, fake, dequant = _one_layer(cfg_name, bias=True)
+    from b200q import backends
+    backends.enable_real_quant_gemm(model)
+    xg = x.clone().requires_grad_(True)
+    out = model(xg)
+    out.float().sum().backward()
+    w = model[0].weight_quantizer(model[0].weight)            # dequantised weight
+    want = torch.ones_like(out) @ w
+    assert torch.allclose(xg.grad.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert model[0].bias.grad is not None and torch.allclose(
+        model[0].bias.grad.float(), torch.full_like(model[0].bias, x.shape[0] * x.shape[1]).float())
+
+
+def test_fp8_layer_matches_oracle_end_to_end():
+    """Uncompressed weight: both operands are cast by ops.fp8_gemm_operand; compare with the oracle
+    restatement of _to_fp8 + _scaled_mm on the same tensors."""
+    import b200q as mtq
+    from b200q import backends, ops
+    from b200q.nn import RealQuantLinear
+    from torch import nn
+    torch.manual_seed(1)
+    model = nn.Sequential(nn.Linear(256, 128, bias=True)).to(torch.bfloat16).cuda()
+    x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16)
+    mtq.quantize(model, mtq.FP8_DEFAULT_CFG, lambda m: m(x))
+    model[0].__class__ = RealQuantLinear
+    backends.enable_real_quant_gemm(model)
+    with torch.no_grad():
+        out = model(x)
+    ops.check_qgemm_status("cuda")
+    lin = model[0]
+    sa = float(lin.input_quantizer.amax.float() / 448.0)
+    sb = float(lin.weight_quantizer.amax.float() / 448.0)
+    bf = lambda v: torch.tensor(v).to(torch.bfloat16).float().item()  # noqa: E731
+    a8 = qo.fp8_to_gemm_operand(x.float().cpu().numpy(), bf(sa), "bf16")
+    b8 = qo.fp8_to_gemm_operand(lin.weight.detach().float().cpu().numpy(), bf(sb), "bf16")
+    want = qo.fp8_gemm(a8, b8, np.float32(sa), np.float32(sb), lin.bias.detach().float().cpu().numpy(), "bf16")
+    af, bfm = qo.e4m3_decode(a8).astype(np.float64), qo.e4m3_decode(b8).astype(np.float64)
+    _check(out, want.astype(np.float64), np.abs(af) @ np.abs(bfm).T * sa * sb, "fp8 layer")
