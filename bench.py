@@ -466,6 +466,46 @@ def run_formats(dev, peak):
     r = timed(lambda: [torch.nn.functional.linear(x, wfq) for _ in range(21)], 1, reps=3, groups=3)
     out["cublas_linear_512x14336x4096_for_comparison"] = {"ms_per_gemm": r["ms"] / 21,
                                                           "tflops": flops / (r["ms"] * 1e-3) / 1e12}
+    del ws, wfq, bufs
+    # the real-quant GEMM consumers (a 70B-shape projection: 4096 tokens x 8192 -> 8192), beside
+    # the library kernels torch._scaled_mm reaches for the same operands
+    m_, n_, k_ = 4096, 8192, 8192
+    flops = 2.0 * m_ * n_ * k_
+    a16 = torch.randn(m_, k_, generator=g, device=dev).bfloat16()
+    b16 = (torch.randn(n_, k_, generator=g, device=dev) * 0.02).bfloat16()
+    one = torch.ones((), device=dev)
+
+    def tflops(fn):
+        r = timed(fn, 1, reps=5, groups=3)
+        return {"ms": r["ms"], "tflops": flops / (r["ms"] * 1e-3) / 1e12}
+
+    sa, sb = ops.amax_tensor(a16) / 448.0, ops.amax_tensor(b16) / 448.0
+    a8, b8 = ops.fp8_gemm_operand(a16, sa), ops.fp8_gemm_operand(b16, sb)
+    out["fp8_gemm_tcgen05_4096x8192x8192"] = tflops(lambda: ops.fp8_gemm(a8, b8, sa, sb))
+    out["fp8_gemm_tcgen05_4096x8192x8192"]["with_activation_cast"] = tflops(
+        lambda: ops.fp8_gemm(ops.fp8_gemm_operand(a16, sa), b8, sa, sb))
+    out["library_scaled_mm_fp8_for_comparison"] = tflops(
+        lambda: torch._scaled_mm(a8, b8.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16, use_fast_accum=True))
+    a4, sfa, s2a = ops.nvfp4_quantize(a16)
+    b4, sfb, s2b = ops.nvfp4_quantize(b16)
+    sfa_t, sfb_t, alpha = ops.nvfp4_swizzle_scales(sfa), ops.nvfp4_swizzle_scales(sfb), s2a * s2b
+    out["nvfp4_gemm_tcgen05_4096x8192x8192"] = tflops(lambda: ops.nvfp4_gemm(a4, sfa_t, b4, sfb_t, alpha))
+
+    def nvfp4_linear():
+        q, sf, s2 = ops.nvfp4_quantize(a16)
+        return ops.nvfp4_gemm(q, ops.nvfp4_swizzle_scales(sf), b4, sfb_t, s2 * s2b)
+
+    out["nvfp4_gemm_tcgen05_4096x8192x8192"]["with_activation_quantise"] = tflops(nvfp4_linear)
+    try:
+        f4 = torch.float4_e2m1fn_x2
+        lib = lambda: torch._scaled_mm(a4.view(f4), b4.view(f4).t(), scale_a=sfa_t.view(torch.float8_e4m3fn),  # noqa: E731
+                                       scale_b=sfb_t.view(torch.float8_e4m3fn), out_dtype=torch.bfloat16)
+        same = bool(torch.equal(lib(), ops.nvfp4_gemm(a4, sfa_t, b4, sfb_t, one)))
+        out["library_scaled_mm_nvfp4_for_comparison"] = dict(tflops(lib), identical_to_ours=same)
+    except Exception as e:  # the library path is a comparison only
+        out["library_scaled_mm_nvfp4_for_comparison"] = {"unavailable": str(e)[:120]}
+    out["bf16_cublas_4096x8192x8192_for_comparison"] = tflops(lambda: torch.nn.functional.linear(a16, b16))
+    out["gemm_kernel_status"] = int(ops.qgemm_status(dev).item())
     return out
 
 
@@ -509,6 +549,17 @@ def run_profile_kernels():
         ops.mx_fake(x[i % 2], 32, (4, 3))
         ops.mxfp4_quantize(x[i % 2], 32)
         ops.awq_clip_loss(w, xs, w_amax, ratios, clip_loss, 128, 4, False, False)
+    # real-quant GEMM consumers on a 2048 x 4096 x 4096 problem
+    a16, b16 = a.new_empty(2048, k).normal_(generator=g), w[:4096]
+    one = torch.ones((), device=dev)
+    a8, b8 = ops.fp8_gemm_operand(a16, one), ops.fp8_gemm_operand(b16, one * 0.001)
+    a4, sfa, _ = ops.nvfp4_quantize(a16)
+    b4, sfb, _ = ops.nvfp4_quantize(b16)
+    sfa_t, sfb_t = ops.nvfp4_swizzle_scales(sfa), ops.nvfp4_swizzle_scales(sfb)
+    for i in range(3):
+        ops.fp8_gemm(a8, b8, one, one)
+        ops.nvfp4_gemm(a4, sfa_t, b4, sfb_t, one)
+    ops.check_qgemm_status(dev)
     torch.cuda.synchronize()
     print(json.dumps({"profile_kernels": "done", "gemm_status": int(status)}))
 

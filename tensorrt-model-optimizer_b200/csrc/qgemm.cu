@@ -10,7 +10,8 @@
 // tcgen05.cp lays a 32 x 16-byte shared-memory matrix into tensor memory, so a tile goes from
 // global memory to tensor memory with one bulk copy and one tcgen05.cp and no shuffling.
 //
-// One CTA computes one 128 x BN output tile (BN = 128 on two CTAs per SM, or 256).  Warp 0 streams
+// One CTA computes MT stacked 128 x BN output tiles on one weight tile (128 x 128 on two CTAs per SM,
+// 128 x 256, or 256 x 256 for FP8 / 256 x 192 for NVFP4).  Warp 0 streams
 // 128-byte-wide operand tiles (128 FP8 or 256 FP4 values of K) and the scale tiles into a
 // shared-memory ring with TMA, one thread of warp 1 copies the scales into tensor memory and issues
 // tcgen05.mma (kind::f8f6f4, or kind::mxf4nvf4 with block scaling) into a TMEM accumulator, warps
@@ -34,20 +35,30 @@ constexpr uint32_t kQSfTile = 512;  // one 128-row x 4-scale tile
 enum : int { kQFp8 = 0, kQNvfp4 = 1 };
 enum : uint32_t { kQErrProducerWait = 16, kQErrMmaWait = 32, kQErrEpilogueWait = 64 };
 
-template <int KIND, int BN> struct QCfg {
+template <int KIND, int BN, int MT> struct QCfg {
+  static constexpr int kBTiles = (BN + 127) / 128;           // 128-row scale tiles a weight tile touches
   static constexpr uint32_t kTileA = kQM * kQKBytes;
   static constexpr uint32_t kTileB = BN * kQKBytes;
-  // four MMAs per stage, each with its own scale tile per 128 rows
-  static constexpr uint32_t kSfA = KIND == kQNvfp4 ? 4 * kQSfTile : 0;
-  static constexpr uint32_t kSfB = KIND == kQNvfp4 ? 4 * kQSfTile * (BN / 128) : 0;
-  static constexpr uint32_t kStageBytes = kTileA + kTileB + kSfA + kSfB;   // a multiple of 1024
-  static constexpr int kStages = BN == 128 ? 3 : 4;
-  static constexpr int kCtasPerSm = BN == 128 ? 2 : 1;
-  // TMEM columns: the fp32 accumulator, then per MMA of a stage 4 columns of A scales and BN / 32 of B scales
-  static constexpr uint32_t kSfAColsPerMma = 4, kSfBColsPerMma = BN / 32;
-  static constexpr uint32_t kSfACol = BN, kSfBCol = BN + 4 * kSfAColsPerMma;
-  static constexpr uint32_t kUsedCols = KIND == kQNvfp4 ? kSfBCol + 4 * kSfBColsPerMma : BN;
+  // four MMAs per stage and row tile, each with its own scale tile per 128 rows
+  static constexpr uint32_t kSfA = KIND == kQNvfp4 ? 4 * kQSfTile * MT : 0;
+  static constexpr uint32_t kSfB = KIND == kQNvfp4 ? 4 * kQSfTile * kBTiles : 0;
+  static constexpr uint32_t kStageBytes = MT * kTileA + kTileB + kSfA + kSfB;   // a multiple of 1024
+  static constexpr int kStages = (BN == 128 && MT == 1) ? 3 : (kStageBytes > 56 * 1024 ? 3 : 4);
+  static constexpr int kCtasPerSm = (BN == 128 && MT == 1) ? 2 : 1;
+  // TMEM columns: MT fp32 accumulators of BN columns, then sets of scale columns: per MMA of a stage
+  // 4 columns of A scales per row tile and 4 of B scales per 128 weight rows.  Stages take the sets
+  // in turn, so the scale copy of a stage does not wait for the MMAs of the one before.
+  static constexpr uint32_t kSfAColsPerMma = 4 * MT, kSfBColsPerMma = 4 * kBTiles;
+  static constexpr uint32_t kSfColsPerStage = 4 * (kSfAColsPerMma + kSfBColsPerMma);
+  static constexpr uint32_t kAccCols = BN * MT;
+  static constexpr uint32_t kTmemBudget = kCtasPerSm == 2 ? 256 : 512;
+  static constexpr int kSfSets = KIND == kQNvfp4
+      ? ((kTmemBudget - kAccCols) / kSfColsPerStage < kStages ? (kTmemBudget - kAccCols) / kSfColsPerStage : kStages) : 0;
+  static_assert(KIND != kQNvfp4 || kSfSets >= 1, "no TMEM left for the block scales");
+  static constexpr uint32_t kSfACol = kAccCols, kSfBCol = kAccCols + 4 * kSfAColsPerMma;
+  static constexpr uint32_t kUsedCols = kAccCols + kSfSets * kSfColsPerStage;
   static constexpr uint32_t kTmemCols = kUsedCols <= 128 ? 128 : (kUsedCols <= 256 ? 256 : 512);
+  static_assert(kUsedCols <= kTmemBudget, "TMEM overcommitted");
   // instruction descriptor, K-major A and B, N = BN, M = 128:
   //   f8f6f4:   D fp32 (bit 4), A and B E4M3 (format 0)
   //   mxf4nvf4: A and B E2M1 (format 1 at bits 7 and 10), scales UE4M3 (bit 23 clear), scale ids 0
@@ -109,41 +120,53 @@ struct QEpilogue {
   int bias_after_round;  // 1: T(T(acc * alpha) + bias), 0: T(acc * alpha + bias)
 };
 
+constexpr uint32_t kQEpiPitch = 32 * 4 + 16;   // staging row: 32 fp32 + 16 bytes against bank conflicts
+
+// One 32-row x 32-column piece of the output: lane = row in, scaled and biased, converted to T and
+// staged in shared memory so that the global stores go out as whole 64- or 128-byte row segments
+// (the accumulator arrives one row per lane; storing it that way writes 32 scattered half sectors).
 template <typename T>
-__device__ __forceinline__ void q_store_chunk(const QEpilogue& ep, const uint32_t* acc, float alpha, int64_t row,
-                                              int64_t N, int col0, int ncols) {
-  T* dst = static_cast<T*>(ep.out) + row * N + col0;
+__device__ __forceinline__ void q_store_chunk(const QEpilogue& ep, const uint32_t* acc, float alpha, uint8_t* stage,
+                                              int lane, int64_t row0, int64_t M, int64_t N, int col0) {
   const T* bias = static_cast<const T*>(ep.bias);
-  float y[32];
+  constexpr int kPer = 16 / sizeof(T);          // elements per 16-byte part
+  constexpr int kParts = 32 / kPer;             // parts per row segment
+  uint8_t* mine = stage + lane * kQEpiPitch;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float v = __uint_as_float(acc[j]) * alpha;
-    if (bias && j < ncols) {
-      const float b = Elem<T>::to_float(bias[col0 + j]);
-      v = ep.bias_after_round ? Elem<T>::to_float(Elem<T>::from_float(v)) + b : v + b;
+  for (int v = 0; v < kParts; ++v) {
+    T tmp[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int c = v * kPer + j;
+      float y = __uint_as_float(acc[c]) * alpha;
+      if (bias && col0 + c < N) {
+        const float b = Elem<T>::to_float(__ldg(bias + col0 + c));
+        y = ep.bias_after_round ? Elem<T>::to_float(Elem<T>::from_float(y)) + b : y + b;
+      }
+      tmp[j] = Elem<T>::from_float(y);
     }
-    y[j] = v;
+    *reinterpret_cast<uint4*>(mine + v * 16) = *reinterpret_cast<const uint4*>(tmp);
   }
-  if (ncols == 32) {
-    constexpr int kPer = 16 / sizeof(T);
+  __syncwarp();
+  const int part = lane % kParts, rsub = lane / kParts;
+  T* out = static_cast<T*>(ep.out);
 #pragma unroll
-    for (int v = 0; v < 32 / kPer; ++v) {
-      T tmp[kPer];
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) tmp[j] = Elem<T>::from_float(y[v * kPer + j]);
-      reinterpret_cast<uint4*>(dst)[v] = *reinterpret_cast<const uint4*>(tmp);
-    }
-  } else {
-    for (int j = 0; j < ncols; ++j) dst[j] = Elem<T>::from_float(y[j]);
+  for (int i = 0; i < kParts; ++i) {
+    const int r = rsub + i * (32 / kParts);
+    const int64_t row = row0 + r;
+    const int col = col0 + part * kPer;
+    if (row < M && col < N)                    // N is a multiple of 8: a part is inside or outside as a whole
+      *reinterpret_cast<uint4*>(out + row * N + col) = *reinterpret_cast<const uint4*>(stage + r * kQEpiPitch + part * 16);
   }
+  __syncwarp();
 }
 
-template <int KIND, int BN>
-__global__ void __launch_bounds__(kQThreads, QCfg<KIND, BN>::kCtasPerSm)
+template <int KIND, int BN, int MT>
+__global__ void __launch_bounds__(kQThreads, QCfg<KIND, BN, MT>::kCtasPerSm)
 qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, int64_t M, int64_t N,
              int num_k_blocks, QEpilogue ep, uint32_t* __restrict__ status) {
-  using Cfg = QCfg<KIND, BN>;
+  using Cfg = QCfg<KIND, BN, MT>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes, kTmemCols = Cfg::kTmemCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -151,7 +174,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   QGemmSmem* sm = reinterpret_cast<QGemmSmem*>(ring + kStages * kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // row tiles are the fast grid dimension: CTAs that share a weight tile run together
-  const int m0 = blockIdx.x * kQM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * kQM * MT, n0 = blockIdx.y * BN;
+  // scale tiles of the weight rows n0 .. n0 + BN - 1: they start inside 128-row tile n0 / 128, at
+  // 32-row group (n0 % 128) / 32, which is the TMEM column the MMA starts reading B scales from
+  const int64_t sfb_tile0 = n0 / 128;
+  const uint32_t sfb_col_shift = (n0 % 128) / 32;
+  const int64_t sfb_tiles_total = (N + 127) / 128;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
@@ -171,21 +199,34 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   if (warp == 0) {
     if (lane == 0) {
       const int64_t sf_tiles_k = static_cast<int64_t>(num_k_blocks) * 4;   // scale tiles per 128 rows
+      // scale tiles past the last one are not read (their rows lie beyond M or N and are never stored)
+      int b_tiles = Cfg::kBTiles;
+      if (sfb_tile0 + b_tiles > sfb_tiles_total) b_tiles = static_cast<int>(sfb_tiles_total - sfb_tile0);
+      int a_tiles = MT;
+      if (m0 / 128 + a_tiles > (M + 127) / 128) a_tiles = static_cast<int>((M + 127) / 128 - m0 / 128);
+      const uint32_t stage_tx = kStageBytes - (Cfg::kBTiles - b_tiles + MT - a_tiles) * 4 * kQSfTile;
       for (int kb = 0; kb < num_k_blocks; ++kb) {
         const int s = kb % kStages;
         const uint32_t ph = (kb / kStages) & 1;
         if (!mbar_wait_bounded(&sm->empty[s], ph ^ 1, &sm->abort, status, kQErrProducerWait)) break;
         uint8_t* a = ring + s * kStageBytes;
-        mbar_expect_tx(&sm->full[s], kStageBytes);
-        tma_load_2d(a, &map_a, &sm->full[s], kb * kQKBytes, m0);
-        tma_load_2d(a + Cfg::kTileA, &map_b, &sm->full[s], kb * kQKBytes, n0);
-        if constexpr (KIND == kQNvfp4) {
-          uint8_t* sa = a + Cfg::kTileA + Cfg::kTileB;
-          bulk_load(sa, sfa + ((m0 / 128) * sf_tiles_k + kb * 4) * kQSfTile, 4 * kQSfTile, &sm->full[s]);
+        mbar_expect_tx(&sm->full[s], KIND == kQNvfp4 ? stage_tx : kStageBytes);
 #pragma unroll
-          for (int t = 0; t < BN / 128; ++t)
-            bulk_load(sa + Cfg::kSfA + t * 4 * kQSfTile, sfb + ((n0 / 128 + t) * sf_tiles_k + kb * 4) * kQSfTile,
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(a + mt * Cfg::kTileA, &map_a, &sm->full[s], kb * kQKBytes, m0 + mt * kQM);
+        tma_load_2d(a + MT * Cfg::kTileA, &map_b, &sm->full[s], kb * kQKBytes, n0);
+        if constexpr (KIND == kQNvfp4) {
+          uint8_t* sa = a + MT * Cfg::kTileA + Cfg::kTileB;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            if (mt < a_tiles)
+              bulk_load(sa + mt * 4 * kQSfTile, sfa + ((m0 / 128 + mt) * sf_tiles_k + kb * 4) * kQSfTile,
                       4 * kQSfTile, &sm->full[s]);
+#pragma unroll
+          for (int t = 0; t < Cfg::kBTiles; ++t)
+            if (t < b_tiles)
+              bulk_load(sa + Cfg::kSfA + t * 4 * kQSfTile, sfb + ((sfb_tile0 + t) * sf_tiles_k + kb * 4) * kQSfTile,
+                        4 * kQSfTile, &sm->full[s]);
         }
       }
     }
@@ -199,26 +240,34 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a = smem_u32(ring + s * kStageBytes);
-        const uint64_t da = umma_desc(a), db = umma_desc(a + Cfg::kTileA);
-        if constexpr (KIND == kQNvfp4) {
-          const uint32_t sa = a + Cfg::kTileA + Cfg::kTileB, sb = sa + Cfg::kSfA;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            tmem_cp_sf(tmem + Cfg::kSfACol + k * Cfg::kSfAColsPerMma, sf_desc(sa + k * kQSfTile));
-#pragma unroll
-            for (int t = 0; t < BN / 128; ++t)
-              tmem_cp_sf(tmem + Cfg::kSfBCol + k * Cfg::kSfBColsPerMma + 4 * t, sf_desc(sb + (t * 4 + k) * kQSfTile));
-          }
-        }
+        const uint64_t db = umma_desc(a + MT * Cfg::kTileA);
+        uint32_t tsf = tmem;                                      // this stage's set of scale columns
+        if constexpr (KIND == kQNvfp4) tsf = tmem + (kb % Cfg::kSfSets) * Cfg::kSfColsPerStage;
+        const uint32_t sa = a + MT * Cfg::kTileA + Cfg::kTileB, sb = sa + Cfg::kSfA;
+        // per 32 bytes of K (32 FP8 or 64 FP4 values): the scale tiles of that slice into TMEM, then
+        // its MMAs, so an MMA waits for its own scales only and the later copies run under it
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          // 32 bytes of K per MMA (32 FP8 or 64 FP4 values): +2 in the descriptor's 16-byte units
-          const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
           if constexpr (KIND == kQNvfp4) {
-            umma_nvf4(tmem, da + 2 * k, db + 2 * k, Cfg::kIdesc, accumulate,
-                      tmem + Cfg::kSfACol + k * Cfg::kSfAColsPerMma, tmem + Cfg::kSfBCol + k * Cfg::kSfBColsPerMma);
-          } else {
-            umma_f8(tmem, da + 2 * k, db + 2 * k, Cfg::kIdesc, accumulate);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+              tmem_cp_sf(tsf + Cfg::kSfACol + k * Cfg::kSfAColsPerMma + 4 * mt, sf_desc(sa + (mt * 4 + k) * kQSfTile));
+#pragma unroll
+            for (int t = 0; t < Cfg::kBTiles; ++t)
+              tmem_cp_sf(tsf + Cfg::kSfBCol + k * Cfg::kSfBColsPerMma + 4 * t, sf_desc(sb + (t * 4 + k) * kQSfTile));
+          }
+          const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            // +2 per slice in the descriptor's 16-byte units
+            const uint64_t da = umma_desc(a + mt * Cfg::kTileA);
+            if constexpr (KIND == kQNvfp4) {
+              umma_nvf4(tmem + mt * BN, da + 2 * k, db + 2 * k, Cfg::kIdesc, accumulate,
+                        tsf + Cfg::kSfACol + k * Cfg::kSfAColsPerMma + 4 * mt,
+                        tsf + Cfg::kSfBCol + k * Cfg::kSfBColsPerMma + sfb_col_shift);
+            } else {
+              umma_f8(tmem + mt * BN, da + 2 * k, db + 2 * k, Cfg::kIdesc, accumulate);
+            }
           }
         }
         umma_commit(&sm->empty[s]);   // the slot is free once these copies and MMAs have read it
@@ -231,18 +280,22 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const bool ok = mbar_wait_bounded(&sm->accum, 0, &sm->abort, status, kQErrEpilogueWait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
+      // every load of the ring has been consumed by now: its first bytes serve as staging space
+      uint8_t* stage = ring + quarter * 32 * kQEpiPitch;
       const float alpha = __ldg(ep.alpha0) * (ep.alpha1 ? __ldg(ep.alpha1) : 1.f);
-      const int64_t row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, acc);   // all lanes: .sync.aligned
-        const int col0 = n0 + c * 32;
-        const int ncols = static_cast<int>(N - col0 < 32 ? N - col0 : 32);
-        if (row < M && ncols > 0) {
-          if (ep.dtype == B200Q_BF16) q_store_chunk<__nv_bfloat16>(ep, acc, alpha, row, N, col0, ncols);
-          else if (ep.dtype == B200Q_F16) q_store_chunk<__half>(ep, acc, alpha, row, N, col0, ncols);
-          else q_store_chunk<float>(ep, acc, alpha, row, N, col0, ncols);
+      for (int mt = 0; mt < MT; ++mt) {
+        const int64_t row0 = m0 + mt * kQM + quarter * 32;
+        if (row0 >= M) break;                                              // warp-uniform
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;                                            // warp-uniform
+          uint32_t acc[32];
+          tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);   // whole warp
+          if (ep.dtype == B200Q_BF16) q_store_chunk<__nv_bfloat16>(ep, acc, alpha, stage, lane, row0, M, N, col0);
+          else if (ep.dtype == B200Q_F16) q_store_chunk<__half>(ep, acc, alpha, stage, lane, row0, M, N, col0);
+          else q_store_chunk<float>(ep, acc, alpha, stage, lane, row0, M, N, col0);
         }
       }
     }
@@ -291,38 +344,50 @@ static bool make_byte_map(CUtensorMap* map, const void* base, int64_t rows, int6
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+template <int KIND, int BN, int MT>
+static int qgemm_launch_tile(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
+                             int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
+  using Cfg = QCfg<KIND, BN, MT>;
+  const int64_t mtiles = (m + kQM * MT - 1) / (kQM * MT), ntiles = (n + BN - 1) / BN;
+  if (ntiles > 65535) return B200Q_ERR_UNSUPPORTED;
+  CUtensorMap map_a, map_b;
+  if (!make_byte_map(&map_a, a, m, kbytes, kQM) || !make_byte_map(&map_b, b, n, kbytes, BN)) return B200Q_ERR_CUDA;
+  const int num_k_blocks = static_cast<int>((kbytes + kQKBytes - 1) / kQKBytes);
+  const size_t smem = Cfg::kStages * Cfg::kStageBytes + sizeof(QGemmSmem) + 1024;
+  if (cudaFuncSetAttribute(qgemm_kernel<KIND, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return B200Q_ERR_CUDA;
+  dim3 grid(static_cast<unsigned>(mtiles), static_cast<unsigned>(ntiles));
+  qgemm_kernel<KIND, BN, MT><<<grid, kQThreads, smem, st>>>(map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep, status);
+  return launch_status();
+}
+
+// Tile choice, from measurements on 70B-shape problems.  FP8: 256 x 256 per CTA when that still
+// gives every SM two tiles or more, else 128 x 256, else 128 x 128 on two CTAs per SM.  NVFP4: two
+// co-resident 128 x 128 CTAs hide each other's scale-copy latency and win up to very large
+// problems, where 256 x 192 (384 accumulator columns + the block scales) takes over.
+// B200Q_QGEMM_TILE = "128", "256" (128 x 256) or "big" forces one.
 template <int KIND>
 static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
                         int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
+  constexpr int kBigN = KIND == kQNvfp4 ? 192 : 256;
   const int64_t sms = sm_count_cached();
-  const int64_t mtiles = (m + kQM - 1) / kQM;
-  int bn = 128;
-  // 128 x 256 tiles (a third less operand traffic per FLOP) when the weight splits evenly and
-  // every SM still gets 0.4 tiles or more; else 128 x 128 on two CTAs per SM
-  if (n % 256 == 0 && mtiles * (n / 256) * 10 >= sms * 4) bn = 256;
-  if (const char* e = getenv("B200Q_QGEMM_TILE")) {
-    const int v = atoi(e);
-    if (v == 128) bn = 128;
-    if (v == 256 && n % 256 == 0) bn = 256;
+  const int64_t mt128 = (m + 127) / 128, big_tiles = ((m + 255) / 256) * ((n + kBigN - 1) / kBigN);
+  int choice = 128;
+  if (KIND == kQFp8) {
+    if (mt128 * ((n + 255) / 256) * 10 >= sms * 4) choice = 256;
+    if (m > 128 && big_tiles >= 2 * sms) choice = 512;
+  } else if (big_tiles >= 20 * sms) {
+    choice = 512;
   }
-  const int64_t ntiles = (n + bn - 1) / bn;
-  if (ntiles > 65535) return B200Q_ERR_UNSUPPORTED;
-  CUtensorMap map_a, map_b;
-  if (!make_byte_map(&map_a, a, m, kbytes, kQM) || !make_byte_map(&map_b, b, n, kbytes, bn)) return B200Q_ERR_CUDA;
-  const int num_k_blocks = static_cast<int>((kbytes + kQKBytes - 1) / kQKBytes);
-  auto launch = [&](auto bn_tag) -> int {
-    constexpr int BN = decltype(bn_tag)::value;
-    using Cfg = QCfg<KIND, BN>;
-    const size_t smem = Cfg::kStages * Cfg::kStageBytes + sizeof(QGemmSmem) + 1024;
-    if (cudaFuncSetAttribute(qgemm_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return B200Q_ERR_CUDA;
-    dim3 grid(static_cast<unsigned>(mtiles), static_cast<unsigned>(ntiles));
-    qgemm_kernel<KIND, BN><<<grid, kQThreads, smem, st>>>(map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep, status);
-    return launch_status();
-  };
-  if (bn == 256) return launch(std::integral_constant<int, 256>{});
-  return launch(std::integral_constant<int, 128>{});
+  if (const char* e = getenv("B200Q_QGEMM_TILE")) {
+    if (e[0] == 'b') choice = 512;
+    else if (atoi(e) == 128) choice = 128;
+    else if (atoi(e) == 256) choice = 256;
+  }
+  if (choice == 512) return qgemm_launch_tile<KIND, kBigN, 2>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
+  if (choice == 256) return qgemm_launch_tile<KIND, 256, 1>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
+  return qgemm_launch_tile<KIND, 128, 1>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
 }
 
 }  // namespace b200q

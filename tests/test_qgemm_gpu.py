@@ -73,14 +73,14 @@ def test_fp8_gemm_matches_float64_sum(m, n, k, dtype):
 
 def test_fp8_gemm_tile_choices_agree(monkeypatch):
     ops = _ops()
-    a8, b8, sa, sb, _ = _fp8_case(256, 512, 768, 5, torch.bfloat16, False)
+    a8, b8, sa, sb, _ = _fp8_case(300, 520, 768, 5, torch.bfloat16, False)
     outs = []
-    for tile in ("128", "256"):
+    for tile in ("128", "256", "big"):
         monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
         outs.append(ops.fp8_gemm(torch.from_numpy(a8).cuda(), torch.from_numpy(b8).cuda(), torch.tensor(sa),
                                  torch.tensor(sb)))
     ops.check_qgemm_status("cuda")
-    assert torch.equal(outs[0], outs[1])     # same K order within a tile: identical sums
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])     # same K order: identical sums
 
 
 def test_fp8_gemm_integer_inputs_are_exact():
@@ -125,13 +125,15 @@ def test_nvfp4_gemm_matches_float64_sum(m, n, k):
     _check(got, ref, absdot, f"nvfp4 oracle {m}x{n}x{k}")
 
 
-def test_nvfp4_gemm_exact_on_exactly_representable_products():
+@pytest.mark.parametrize("tile", ["128", "256", "big"])
+def test_nvfp4_gemm_exact_on_exactly_representable_products(tile, monkeypatch):
     """Codes in {0, +-1, +-2} with power-of-two block scales: every partial sum is an integer multiple
     of a power of two well inside fp32, so the kernel must reproduce the sum exactly; this pins the
     nibble order, the block-to-scale mapping and the row/column order of the scale tiles."""
     ops = _ops()
+    monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
     rng = np.random.default_rng(1)
-    m, n, k = 256, 384, 512
+    m, n, k = 300, 1000, 512                       # ragged row and column tiles for every tile shape
     codes = np.array([0, 2, 4, 10, 12], dtype=np.uint8)          # 0, 1, 2, -1, -2
     qa, qb = rng.choice(codes, size=(m, k)), rng.choice(codes, size=(n, k))
     a4 = ((qa[:, 1::2] << 4) | qa[:, 0::2]).astype(np.uint8)
