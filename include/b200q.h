@@ -331,11 +331,13 @@ int b200q_fp8_gemm(const uint8_t* a, const uint8_t* b, const float* scale_a, con
                    const void* bias, void* out, int64_t m, int64_t n, int64_t k, int dtype,
                    uint32_t* status_io, void* stream);
 
-/* The activation (or weight) operand of b200q_fp8_gemm: q = e4m3(clamp(T(x / *scale), -448, 448)),
- * *scale a device scalar of type T, n elements.  Replaces _to_fp8
+/* The activation (or weight) operand of b200q_fp8_gemm: q = e4m3(clamp(x / *scale, -448, 448)),
+ * *scale a device fp32 scalar, n elements.  round_quotient != 0 rounds the quotient to T before the
+ * clamp, as the eager tensor expression does; 0 keeps it in fp32, as a fused graph of the same
+ * expression does.  Replaces _to_fp8
  * (modelopt/torch/quantization/backends/fp8_per_tensor_gemm.py:35-37). */
-int b200q_fp8_gemm_operand(const void* x, const void* scale, uint8_t* q, int64_t n, int dtype,
-                           void* stream);
+int b200q_fp8_gemm_operand(const void* x, const float* scale, uint8_t* q, int64_t n, int dtype,
+                           int round_quotient, void* stream);
 
 /* NVFP4 linear layer on the tensor cores (tcgen05 kind::mxf4nvf4 with block scaling):
  *   out[m, n] = T(T(*alpha * sum_blk sfa[m, blk] * sfb[n, blk] * sum_{j<16} a[m, 16 blk + j] * b[n, 16 blk + j]) + bias[n])

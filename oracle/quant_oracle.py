@@ -547,11 +547,14 @@ def mxfp4_dequantize(packed: np.ndarray, scales: np.ndarray, block=32, T="f32") 
 # nvfp4_gemm, which is not in the reference tree): the oracle is the defining sum in float64, so a
 # comparison with it carries the fp32-accumulation tolerance stated in the tests.
 
-def fp8_to_gemm_operand(x: np.ndarray, scale, T="f32") -> np.ndarray:
-    """_to_fp8 (backends/fp8_per_tensor_gemm.py:35-37): (x / scale).clamp(-448, 448).to(e4m3), the
-    quotient in x's dtype."""
+def fp8_to_gemm_operand(x: np.ndarray, scale, T="f32", fused=False) -> np.ndarray:
+    """_to_fp8 (backends/fp8_per_tensor_gemm.py:35-37): (x / scale).clamp(-448, 448).to(e4m3) with an
+    fp32 0-dim scale: the quotient float(x) / scale is rounded to x's dtype (eager evaluation;
+    ``fused`` keeps it in fp32, as a compiled graph of the expression does)."""
     with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
-        q = round_to((np.asarray(x, F32) / F32(scale)).astype(F32), T)
+        q = (np.asarray(x, F32) / F32(scale)).astype(F32)
+        if not fused:
+            q = round_to(q, T)
     return e4m3_encode(np.clip(q, F32(-448.0), F32(448.0)), "torch")
 
 

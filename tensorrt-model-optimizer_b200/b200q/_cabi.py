@@ -56,7 +56,7 @@ SIGNATURES = {
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],
     "b200q_fp8_gemm": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
-    "b200q_fp8_gemm_operand": [_p, _p, _p, _i64, _i, _p],
+    "b200q_fp8_gemm_operand": [_p, _p, _p, _i64, _i, _i, _p],
     "b200q_nvfp4_gemm": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
     "b200q_nvfp4_swizzle_scales": [_p, _p, _i64, _i64, _p],
     "b200q_int4_export_pack": [_p, _p, _i, _p, _i64, _i64, _i, _i, _p],

@@ -4,8 +4,9 @@ modelopt/torch/quantization/backends/fp8_per_tensor_gemm.py:35-207).
 The activation is cast to E4M3 with scale ``amax / 448`` (``ops.fp8_gemm_operand``), the weight is
 the compressed ``FP8QTensor`` (or is cast the same way), and one tcgen05 kernel computes
 ``out = a8 @ w8.T * scale_a * scale_b + bias`` (``ops.fp8_gemm``) in place of ``torch._scaled_mm``.
-The scale enters the cast in the activation's dtype (the eager-mode arithmetic of the reference's
-expression) and the GEMM epilogue in fp32."""
+The cast follows the eager arithmetic of the reference's expression (fp32 scale, quotient rounded to
+the activation's dtype, clamp, E4M3 cast; pinned by a fixture of the reference run on the CPU);
+``ops.fp8_gemm_operand(..., fused=True)`` keeps the quotient in fp32 as a compiled graph does."""
 from __future__ import annotations
 
 import torch

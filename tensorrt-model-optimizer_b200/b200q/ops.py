@@ -603,13 +603,16 @@ def fp8_gemm(a8: torch.Tensor, b8: torch.Tensor, scale_a: torch.Tensor, scale_b:
     return out
 
 
-def fp8_gemm_operand(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
-    """e4m3(clamp(x / scale, -448, 448)) with the quotient in x's dtype; ``scale`` has one element."""
+def fp8_gemm_operand(x: torch.Tensor, scale: torch.Tensor, fused: bool = False) -> torch.Tensor:
+    """e4m3(clamp(x / scale, -448, 448)), ``scale`` one fp32 element.  The quotient is rounded to x's
+    dtype before the clamp (the eager arithmetic of the expression) unless ``fused`` (the quotient
+    stays in fp32, as in a compiled graph)."""
     x = _prep(x)
-    s = _cuda(scale, "scale").detach().to(x.dtype).reshape(1).contiguous()
+    s = _amax_f32(scale, x.device).reshape(1)
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        call("b200q_fp8_gemm_operand", x.data_ptr(), s.data_ptr(), q.data_ptr(), x.numel(), dtype_code(x), _stream(x))
+        call("b200q_fp8_gemm_operand", x.data_ptr(), s.data_ptr(), q.data_ptr(), x.numel(), dtype_code(x),
+             0 if fused else 1, _stream(x))
     return q.view(torch.float8_e4m3fn)
 
 

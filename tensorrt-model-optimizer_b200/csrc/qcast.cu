@@ -15,13 +15,45 @@ struct ToE4m3 {
     return f32_to_e4m3_torch(round_to_t<T>(__fdiv_rn(x, scale)));
   }
 };
-// saturating variant: the quotient is clamped to the E4M3 range before the cast (NaN stays NaN)
-struct ToE4m3Sat {
-  template <typename T> static __device__ __forceinline__ uint32_t cvt(float x, float scale) {
-    const float v = round_to_t<T>(__fdiv_rn(x, scale));
-    return f32_to_e4m3_torch(v != v ? v : fminf(448.f, fmaxf(-448.f, v)));
+// GEMM operand cast: fp32 scale, the quotient clamped to the E4M3 range before the cast (NaN stays
+// NaN).  ROUND: the quotient is rounded to T first, as an eager tensor expression does; without it
+// the quotient stays in fp32, as in a fused (compiled) graph.
+template <typename T, bool ROUND> __device__ __forceinline__ uint32_t e4m3_operand(float x, float scale) {
+  float v = __fdiv_rn(x, scale);
+  if (ROUND) v = round_to_t<T>(v);
+  return f32_to_e4m3_torch(v != v ? v : fminf(448.f, fmaxf(-448.f, v)));
+}
+
+template <typename T, bool ROUND>
+__global__ void __launch_bounds__(256)
+fp8_operand_kernel(const T* __restrict__ x, const float* __restrict__ scale, uint8_t* __restrict__ q, int64_t n) {
+  pdl_prologue();
+  using E = Elem<T>;
+  constexpr int P = E::kPerPack;
+  const float s = __ldg(scale);
+  const int64_t npack = n / P, stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const bool vec_out = (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < npack; i += stride) {
+    float f[P];
+    E::unpack(ld_stream(xv + i), f);
+    uint32_t w[P / 4];
+#pragma unroll
+    for (int k = 0; k < P / 4; ++k)
+      w[k] = e4m3_operand<T, ROUND>(f[4 * k], s) | (e4m3_operand<T, ROUND>(f[4 * k + 1], s) << 8) |
+             (e4m3_operand<T, ROUND>(f[4 * k + 2], s) << 16) | (e4m3_operand<T, ROUND>(f[4 * k + 3], s) << 24);
+    if (vec_out) {
+      if (P == 8) *reinterpret_cast<uint2*>(q + i * P) = make_uint2(w[0], w[P / 4 - 1]);
+      else *reinterpret_cast<uint32_t*>(q + i * P) = w[0];
+    } else {
+#pragma unroll
+      for (int k = 0; k < P; ++k) q[i * P + k] = static_cast<uint8_t>(w[k / 4] >> (8 * (k % 4)));
+    }
   }
-};
+  // ragged tail
+  for (int64_t i = npack * P + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+    q[i] = static_cast<uint8_t>(e4m3_operand<T, ROUND>(E::to_float(x[i]), s));
+}
 struct ToInt8 {
   template <typename T> static __device__ __forceinline__ uint32_t cvt(float x, float scale) {
     float r = rintf(round_to_t<T>(__fdiv_rn(x, scale)));
@@ -115,12 +147,19 @@ extern "C" int b200q_fp8_quantize(const void* x, const void* scales, uint8_t* q,
   return launch_qcast<ToE4m3>(x, scales, q, outer, axis, inner, dtype, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int b200q_fp8_gemm_operand(const void* x, const void* scale, uint8_t* q, int64_t n, int dtype,
-                                      void* stream) {
+extern "C" int b200q_fp8_gemm_operand(const void* x, const float* scale, uint8_t* q, int64_t n, int dtype,
+                                      int round_quotient, void* stream) {
   B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(scale); B200Q_REQUIRE_PTR(q);
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x);
   if (n <= 0) return B200Q_ERR_SHAPE;
-  return launch_qcast<ToE4m3Sat>(x, scale, q, n, 1, 1, dtype, static_cast<cudaStream_t>(stream));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&] {
+    const int grid = grid_for(n / Elem<T>::kPerPack + 1, 256, 8);
+    const T* xp = static_cast<const T*>(x);
+    if (round_quotient) launch_pdl(fp8_operand_kernel<T, true>, grid, 256, 0, s, xp, scale, q, n);
+    else launch_pdl(fp8_operand_kernel<T, false>, grid, 256, 0, s, xp, scale, q, n);
+    return launch_status();
+  });
 }
 
 extern "C" int b200q_int8_quantize(const void* x, const void* scales, int8_t* q, int64_t outer,

@@ -438,6 +438,41 @@ def golden_reference_test_tables(out, ref_root):
     np.savez_compressed(out / "reference_test_tables.npz", **cases)
 
 
+def golden_fp8_gemm(out):
+    """The reference's FP8 per-tensor linear (backends/fp8_per_tensor_gemm.py) on the CPU: its own
+    ``_to_fp8`` and ``_fp8_gemm_impl`` run eagerly (torch.compile switched off), torch._scaled_mm
+    being the CPU kernel of this torch build."""
+    import torch._dynamo
+    torch._dynamo.config.disable = True
+    from modelopt.torch.quantization.backends import fp8_per_tensor_gemm as ref
+
+    class Q:  # stands in for a TensorQuantizer: the function only reads .amax
+        def __init__(self, amax):
+            self.amax = amax
+
+    class M:  # stands in for a RealQuantLinear with an uncompressed weight
+        pass
+
+    data = {}
+    for i, (m, n, k, T, with_bias) in enumerate([(64, 128, 256, "bf16", True), (100, 136, 80, "bf16", False),
+                                                 (32, 64, 512, "f16", True), (48, 96, 128, "f32", True)]):
+        x = gen((m, k), T, 100 + i, 2.0)
+        w = gen((n, k), T, 200 + i, 0.05, heavy=True)
+        bias = gen((n,), T, 300 + i) if with_bias else None
+        mod = M()
+        mod.input_quantizer, mod.weight_quantizer = Q(x.abs().amax()), Q(w.abs().amax())
+        mod.weight = w
+        y = ref.fp8_per_tensor_gemm(mod, x, bias)
+        data[f"case{i}_x"], data[f"case{i}_w"], data[f"case{i}_y"] = bits(x), bits(w), bits(y)
+        data[f"case{i}_a8"] = bits(ref._to_fp8(x, mod._scale_a))
+        data[f"case{i}_b8"] = bits(ref._to_fp8(w, mod._scale_b))
+        data[f"case{i}_scale_a"], data[f"case{i}_scale_b"] = mod._scale_a.numpy(), mod._scale_b.numpy()
+        if bias is not None:
+            data[f"case{i}_bias"] = bits(bias)
+        data[f"case{i}_meta"] = np.array([m, n, k, {"f32": 0, "f16": 1, "bf16": 2}[T], int(with_bias)])
+    np.savez_compressed(out / "fp8_gemm.npz", **data)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True, help="path of a TensorRT-Model-Optimizer checkout")
@@ -446,7 +481,8 @@ def main():
     import_reference(args.ref)
     torch.manual_seed(0)
     fns = {"fake_int": golden_fake_int, "fake_e4m3": golden_fake_e4m3, "nvfp4": golden_nvfp4,
-           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export, "mxfp4": golden_mxfp4, "bias": golden_bias}
+           "int4": golden_int4, "q8": golden_q8, "amax": golden_amax, "hist": golden_hist, "export": golden_export, "mxfp4": golden_mxfp4, "bias": golden_bias,
+           "fp8_gemm": golden_fp8_gemm}
     for name, fn in fns.items():
         if args.only and name not in args.only.split(","):
             continue

@@ -286,3 +286,34 @@ def test_torch_path_restatement_matches_reference_bytes():
             assert np.array_equal(scales.view(torch.uint8).numpy(), g[k + "_scales"]), k
             n += 1
     assert n >= 3
+
+
+def test_fp8_gemm_operand_and_product_match_reference_cpu_run():
+    """Fixture: the reference's fp8_per_tensor_gemm on the CPU.  The operand cast is bit-exact; the
+    product (torch._scaled_mm there, a float64 sum here) agrees to one ulp of T plus an
+    accumulation allowance."""
+    d = load("fp8_gemm")
+    for i in range(4):
+        m, n, k, t, wb = (int(v) for v in d[f"case{i}_meta"])
+        T = ["f32", "f16", "bf16"][t]
+        x, w = to_f32(d[f"case{i}_x"], T), to_f32(d[f"case{i}_w"], T)
+        sa, sb = np.float32(d[f"case{i}_scale_a"]), np.float32(d[f"case{i}_scale_b"])
+        a8, b8 = qo.fp8_to_gemm_operand(x, sa, T), qo.fp8_to_gemm_operand(w, sb, T)
+        assert np.array_equal(a8, d[f"case{i}_a8"]) and np.array_equal(b8, d[f"case{i}_b8"])
+        bias = to_f32(d[f"case{i}_bias"], T) if wb else None
+        y = qo.fp8_gemm(a8, b8, sa, sb, bias, T).astype(np.float64)
+        want = to_f32(d[f"case{i}_y"], T).astype(np.float64)
+        absdot = np.abs(qo.e4m3_decode(a8)).astype(np.float64) @ np.abs(qo.e4m3_decode(b8)).astype(np.float64).T
+        tol = np.abs(want) * 2.0 ** -7 + 2e-3 * absdot * float(sa) * float(sb)
+        assert np.all(np.abs(y - want) <= tol)
+        assert np.mean(y == want) > (0.99 if T != "f32" else 0.1)
+
+
+def test_nvfp4_scale_tiling_roundtrip():
+    rng = np.random.default_rng(0)
+    s = rng.integers(0, 127, size=(300, 40), dtype=np.uint8)
+    t = qo.nvfp4_swizzle_scales(s)
+    assert t.size == 3 * 12 * 512
+    for r, c in [(0, 0), (31, 3), (32, 0), (137, 21), (299, 39)]:
+        assert t[((r // 128) * 12 + c // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + c % 4] == s[r, c]
+    assert t.sum() == s.sum()          # padding is zero

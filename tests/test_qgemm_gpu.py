@@ -155,11 +155,15 @@ def test_fp8_gemm_operand_matches_oracle_bytes(dtype):
     rng = np.random.default_rng(3)
     x = torch.from_numpy((rng.standard_normal((64, 1000)) * 3).astype(np.float32)).to(dtype)
     x[0, :4] = torch.tensor([1e4, -1e4, float("nan"), 0.0], dtype=dtype)      # beyond the range: saturate
-    scale = torch.tensor(0.0123).to(dtype)
-    got = ops.fp8_gemm_operand(x.cuda(), scale.cuda()).view(torch.uint8).cpu().numpy()
-    want = qo.fp8_to_gemm_operand(x.float().numpy(), scale.float().item(), T)
-    assert np.array_equal(got, want)
-    assert got[0, 0] == 0x7E and got[0, 1] == 0xFE and (got[0, 2] & 0x7F) == 0x7F
+    scale = torch.tensor(0.0123)
+    for fused in (False, True):
+        got = ops.fp8_gemm_operand(x.cuda(), scale.cuda(), fused=fused).view(torch.uint8).cpu().numpy()
+        want = qo.fp8_to_gemm_operand(x.float().numpy(), np.float32(scale.item()), T, fused=fused)
+        assert np.array_equal(got, want)
+        assert got[0, 0] == 0x7E and got[0, 1] == 0xFE and (got[0, 2] & 0x7F) == 0x7F
+    odd = x.flatten()[3:3 + 4099].cuda()                                   # unaligned start, ragged tail
+    assert np.array_equal(ops.fp8_gemm_operand(odd, scale.cuda()).view(torch.uint8).cpu().numpy(),
+                          qo.fp8_to_gemm_operand(odd.float().cpu().numpy(), np.float32(scale.item()), T))
 
 
 # ------------------------------------------------------------------ layer level ---------------------
@@ -250,9 +254,38 @@ def test_fp8_layer_matches_oracle_end_to_end():
     lin = model[0]
     sa = float(lin.input_quantizer.amax.float() / 448.0)
     sb = float(lin.weight_quantizer.amax.float() / 448.0)
-    bf = lambda v: torch.tensor(v).to(torch.bfloat16).float().item()  # noqa: E731
-    a8 = qo.fp8_to_gemm_operand(x.float().cpu().numpy(), bf(sa), "bf16")
-    b8 = qo.fp8_to_gemm_operand(lin.weight.detach().float().cpu().numpy(), bf(sb), "bf16")
+    a8 = qo.fp8_to_gemm_operand(x.float().cpu().numpy(), np.float32(sa), "bf16")
+    b8 = qo.fp8_to_gemm_operand(lin.weight.detach().float().cpu().numpy(), np.float32(sb), "bf16")
     want = qo.fp8_gemm(a8, b8, np.float32(sa), np.float32(sb), lin.bias.detach().float().cpu().numpy(), "bf16")
     af, bfm = qo.e4m3_decode(a8).astype(np.float64), qo.e4m3_decode(b8).astype(np.float64)
     _check(out, want.astype(np.float64), np.abs(af) @ np.abs(bfm).T * sa * sb, "fp8 layer")
+
+
+def _golden_fp8_cases():
+    from _util import load, to_f32 as unbits
+    d = load("fp8_gemm")
+    for i in range(4):
+        m, n, k, t, wb = (int(v) for v in d[f"case{i}_meta"])
+        T = ["f32", "f16", "bf16"][t]
+        yield i, T, {key: d[f"case{i}_{key}"] for key in ("x", "w", "y", "a8", "b8", "scale_a", "scale_b")}, \
+            (d[f"case{i}_bias"] if wb else None), unbits
+
+
+def test_fp8_linear_matches_reference_fixture():
+    """The reference's fp8_per_tensor_gemm run on the CPU (tests/golden/make_golden.py): operand bytes
+    bit-exact, output within the accumulation tolerance."""
+    ops = _ops()
+    TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+    for i, T, c, bias, unbits in _golden_fp8_cases():
+        x = torch.from_numpy(unbits(c["x"], T)).to(TD[T]).cuda()
+        w = torch.from_numpy(unbits(c["w"], T)).to(TD[T]).cuda()
+        sa, sb = torch.from_numpy(c["scale_a"]).cuda(), torch.from_numpy(c["scale_b"]).cuda()
+        a8, b8 = ops.fp8_gemm_operand(x, sa), ops.fp8_gemm_operand(w, sb)
+        assert np.array_equal(a8.view(torch.uint8).cpu().numpy(), c["a8"]), f"case {i} activation bytes"
+        assert np.array_equal(b8.view(torch.uint8).cpu().numpy(), c["b8"]), f"case {i} weight bytes"
+        b = None if bias is None else torch.from_numpy(unbits(bias, T)).to(TD[T]).cuda()
+        got = ops.fp8_gemm(a8, b8, sa, sb, b, TD[T])
+        ops.check_qgemm_status("cuda")
+        af, bf = qo.e4m3_decode(c["a8"]).astype(np.float64), qo.e4m3_decode(c["b8"]).astype(np.float64)
+        absdot = np.abs(af) @ np.abs(bf).T * float(c["scale_a"]) * float(c["scale_b"])
+        _check(got, unbits(c["y"], T).astype(np.float64), absdot, f"fixture case {i}")
