@@ -13,9 +13,10 @@
 // One CTA computes MT stacked 128 x BN output tiles on one weight tile (128 x 128 on two CTAs per SM,
 // 128 x 256, or 256 x 256 for FP8 / 256 x 192 for NVFP4).  Warp 0 streams
 // 128-byte-wide operand tiles (128 FP8 or 256 FP4 values of K) and the scale tiles into a
-// shared-memory ring with TMA, one thread of warp 1 copies the scales into tensor memory and issues
-// tcgen05.mma (kind::f8f6f4, or kind::mxf4nvf4 with block scaling) into a TMEM accumulator, warps
-// 2-5 read the accumulator with tcgen05.ld, apply scale and bias and store the output rows.
+// shared-memory ring with TMA, one thread of warp 1 issues tcgen05.mma (kind::f8f6f4, or
+// kind::mxf4nvf4 with block scaling) into a TMEM accumulator, warps 2-5 move the block scales of
+// each stage from shared memory into tensor memory during the main loop (tcgen05.st) and afterwards
+// read the accumulator with tcgen05.ld, apply scale and bias and store the output rows.
 //
 // Every mbarrier wait is bounded: when a wait runs out, an error bit is set in the caller's status
 // word, the CTA stops waiting anywhere else, lets its outstanding work drain, frees its TMEM and
@@ -55,6 +56,10 @@ template <int KIND, int BN, int MT> struct QCfg {
   static constexpr int kSfSets = KIND == kQNvfp4
       ? ((kTmemBudget - kAccCols) / kSfColsPerStage < kStages ? (kTmemBudget - kAccCols) / kSfColsPerStage : kStages) : 0;
   static_assert(KIND != kQNvfp4 || kSfSets >= 1, "no TMEM left for the block scales");
+  // With a set per ring stage, the four otherwise idle epilogue warps move the scales (shared memory
+  // -> registers -> tcgen05.st, each warp into its own lane quarter); tcgen05.cp, which takes the
+  // tensor pipe for about 130 cycles per 512-byte tile, is left to the tile shape that has no room.
+  static constexpr bool kSfByWarps = KIND == kQNvfp4 && kSfSets >= kStages;
   static constexpr uint32_t kSfACol = kAccCols, kSfBCol = kAccCols + 4 * kSfAColsPerMma;
   static constexpr uint32_t kUsedCols = kAccCols + kSfSets * kSfColsPerStage;
   static constexpr uint32_t kTmemCols = kUsedCols <= 128 ? 128 : (kUsedCols <= 256 ? 256 : 512);
@@ -69,6 +74,8 @@ template <int KIND, int BN, int MT> struct QCfg {
 struct QGemmSmem {
   uint64_t full[kQMaxStages];
   uint64_t empty[kQMaxStages];
+  uint64_t sf_full[kQMaxStages];
+  uint64_t sf_ready[kQMaxStages];
   uint64_t accum;
   uint32_t tmem_base;
   uint32_t abort;
@@ -105,6 +112,14 @@ __device__ __forceinline__ uint64_t sf_desc(uint32_t saddr) {
   d |= static_cast<uint64_t>(128 >> 4) << 32;
   d |= static_cast<uint64_t>(1) << 46;
   return d;
+}
+// one warp: lane i writes four 32-bit columns of TMEM lane (lane field of taddr) + i
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint4 v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // 32 lanes x 128 bits from shared memory into 4 TMEM columns, repeated in all four lane quarters
 __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
@@ -182,7 +197,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   const int64_t sfb_tiles_total = (N + 127) / 128;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], 1);
+      mbar_init(&sm->sf_full[s], 1); mbar_init(&sm->sf_ready[s], 4);
+    }
     mbar_init(&sm->accum, 1);
     sm->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -204,30 +222,40 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       if (sfb_tile0 + b_tiles > sfb_tiles_total) b_tiles = static_cast<int>(sfb_tiles_total - sfb_tile0);
       int a_tiles = MT;
       if (m0 / 128 + a_tiles > (M + 127) / 128) a_tiles = static_cast<int>((M + 127) / 128 - m0 / 128);
-      const uint32_t stage_tx = kStageBytes - (Cfg::kBTiles - b_tiles + MT - a_tiles) * 4 * kQSfTile;
       for (int kb = 0; kb < num_k_blocks; ++kb) {
         const int s = kb % kStages;
         const uint32_t ph = (kb / kStages) & 1;
         if (!mbar_wait_bounded(&sm->empty[s], ph ^ 1, &sm->abort, status, kQErrProducerWait)) break;
         uint8_t* a = ring + s * kStageBytes;
-        mbar_expect_tx(&sm->full[s], KIND == kQNvfp4 ? stage_tx : kStageBytes);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(a + mt * Cfg::kTileA, &map_a, &sm->full[s], kb * kQKBytes, m0 + mt * kQM);
-        tma_load_2d(a + MT * Cfg::kTileA, &map_b, &sm->full[s], kb * kQKBytes, n0);
         if constexpr (KIND == kQNvfp4) {
+          // the (small) scale tiles first: with kSfByWarps on a barrier of their own, so the warps
+          // that move them to TMEM are done by the time the operand tiles have landed
+          uint64_t* sf_bar = Cfg::kSfByWarps ? &sm->sf_full[s] : &sm->full[s];
+          const uint32_t sf_tx = (a_tiles + b_tiles) * 4 * kQSfTile;
+          if (Cfg::kSfByWarps) {
+            mbar_expect_tx(&sm->sf_full[s], sf_tx);
+            mbar_expect_tx(&sm->full[s], MT * Cfg::kTileA + Cfg::kTileB);
+          } else {
+            mbar_expect_tx(&sm->full[s], MT * Cfg::kTileA + Cfg::kTileB + sf_tx);
+          }
           uint8_t* sa = a + MT * Cfg::kTileA + Cfg::kTileB;
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
             if (mt < a_tiles)
               bulk_load(sa + mt * 4 * kQSfTile, sfa + ((m0 / 128 + mt) * sf_tiles_k + kb * 4) * kQSfTile,
-                      4 * kQSfTile, &sm->full[s]);
+                        4 * kQSfTile, sf_bar);
 #pragma unroll
           for (int t = 0; t < Cfg::kBTiles; ++t)
             if (t < b_tiles)
               bulk_load(sa + Cfg::kSfA + t * 4 * kQSfTile, sfb + ((sfb_tile0 + t) * sf_tiles_k + kb * 4) * kQSfTile,
-                        4 * kQSfTile, &sm->full[s]);
+                        4 * kQSfTile, sf_bar);
+        } else {
+          mbar_expect_tx(&sm->full[s], kStageBytes);
         }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          tma_load_2d(a + mt * Cfg::kTileA, &map_a, &sm->full[s], kb * kQKBytes, m0 + mt * kQM);
+        tma_load_2d(a + MT * Cfg::kTileA, &map_b, &sm->full[s], kb * kQKBytes, n0);
       }
     }
   } else if (warp == 1) {
@@ -242,13 +270,18 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         const uint32_t a = smem_u32(ring + s * kStageBytes);
         const uint64_t db = umma_desc(a + MT * Cfg::kTileA);
         uint32_t tsf = tmem;                                      // this stage's set of scale columns
-        if constexpr (KIND == kQNvfp4) tsf = tmem + (kb % Cfg::kSfSets) * Cfg::kSfColsPerStage;
+        if constexpr (KIND == kQNvfp4) tsf = tmem + ((Cfg::kSfByWarps ? s : kb) % Cfg::kSfSets) * Cfg::kSfColsPerStage;
+        if constexpr (Cfg::kSfByWarps) {
+          ok = mbar_wait_bounded(&sm->sf_ready[s], ph, &sm->abort, status, kQErrMmaWait);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
         const uint32_t sa = a + MT * Cfg::kTileA + Cfg::kTileB, sb = sa + Cfg::kSfA;
         // per 32 bytes of K (32 FP8 or 64 FP4 values): the scale tiles of that slice into TMEM, then
         // its MMAs, so an MMA waits for its own scales only and the later copies run under it
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          if constexpr (KIND == kQNvfp4) {
+          if constexpr (KIND == kQNvfp4 && !Cfg::kSfByWarps) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
               tmem_cp_sf(tsf + Cfg::kSfACol + k * Cfg::kSfAColsPerMma + 4 * mt, sf_desc(sa + (mt * 4 + k) * kQSfTile));
@@ -277,6 +310,33 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   } else {
     // epilogue warps 2..5: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read
     const int quarter = warp & 3;
+    if constexpr (Cfg::kSfByWarps) {
+      // during the main loop: the scales of each stage from shared memory into this warp's lane
+      // quarter of the stage's TMEM columns (lane i: bytes 16 i .. 16 i + 15 of a tile = its four
+      // columns), then one arrival per warp on the stage's sf_ready barrier
+      const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+      for (int kb = 0; kb < num_k_blocks; ++kb) {
+        const int s = kb % kStages;
+        if (!mbar_wait_bounded(&sm->sf_full[s], (kb / kStages) & 1, &sm->abort, status, kQErrEpilogueWait)) break;
+        const uint8_t* sf = ring + s * kStageBytes + MT * Cfg::kTileA + Cfg::kTileB + lane * 16;
+        const uint32_t tsf = tmem + lane_base + s * Cfg::kSfColsPerStage;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            tmem_st4(tsf + Cfg::kSfACol + k * Cfg::kSfAColsPerMma + 4 * mt,
+                     *reinterpret_cast<const uint4*>(sf + (mt * 4 + k) * kQSfTile));
+#pragma unroll
+          for (int t = 0; t < Cfg::kBTiles; ++t)
+            tmem_st4(tsf + Cfg::kSfBCol + k * Cfg::kSfBColsPerMma + 4 * t,
+                     *reinterpret_cast<const uint4*>(sf + Cfg::kSfA + (t * 4 + k) * kQSfTile));
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm->sf_ready[s]);
+      }
+    }
     const bool ok = mbar_wait_bounded(&sm->accum, 0, &sm->abort, status, kQErrEpilogueWait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -364,9 +424,9 @@ static int qgemm_launch_tile(const uint8_t* a, const uint8_t* b, const uint8_t* 
 
 // Tile choice, from measurements on 70B-shape problems.  FP8: 256 x 256 per CTA when that still
 // gives every SM two tiles or more, else 128 x 256, else 128 x 128 on two CTAs per SM.  NVFP4: two
-// co-resident 128 x 128 CTAs hide each other's scale-copy latency and win up to very large
-// problems, where 256 x 192 (384 accumulator columns + the block scales) takes over.
-// B200Q_QGEMM_TILE = "128", "256" (128 x 256) or "big" forces one.
+// co-resident 128 x 128 CTAs win up to very large problems, where 128 x 256 takes over; 256 x 192
+// (384 accumulator columns + the block scales, scale copies by tcgen05.cp) is kept for the
+// override.  B200Q_QGEMM_TILE = "128", "256" (128 x 256) or "big" forces one.
 template <int KIND>
 static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
                         int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
@@ -377,8 +437,8 @@ static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
   if (KIND == kQFp8) {
     if (mt128 * ((n + 255) / 256) * 10 >= sms * 4) choice = 256;
     if (m > 128 && big_tiles >= 2 * sms) choice = 512;
-  } else if (big_tiles >= 20 * sms) {
-    choice = 512;
+  } else if (mt128 * ((n + 255) / 256) >= 16 * sms) {
+    choice = 256;
   }
   if (const char* e = getenv("B200Q_QGEMM_TILE")) {
     if (e[0] == 'b') choice = 512;
