@@ -6,9 +6,10 @@
 // A = quantised activations [M, K], B = quantised weights [N, K], K contiguous (E4M3 bytes, or two
 // E2M1 codes per byte with the even element in the low nibble).  NVFP4 block scales are E4M3 bytes
 // in 128-row x 4-scale tiles of 512 bytes (byte (r % 32) * 16 + (r / 32) * 4 + s of tile
-// [r / 128][k / 64]), with the K extent padded to a multiple of 256 elements: the order in which
-// tcgen05.cp lays a 32 x 16-byte shared-memory matrix into tensor memory, so a tile goes from
-// global memory to tensor memory with one bulk copy and one tcgen05.cp and no shuffling.
+// [r / 128][k / 64]), with the K extent padded to a multiple of 256 elements: the order the
+// block-scaled MMA reads them in from tensor memory (row r in lane r % 32, column r / 32 of the tile's
+// four), so a tile goes from global memory to tensor memory with one bulk copy and four-column
+// stores (or one tcgen05.cp) and no shuffling.
 //
 // One CTA computes MT stacked 128 x BN output tiles on one weight tile (128 x 128 on two CTAs per SM,
 // 128 x 256, or 256 x 256 for FP8 / 256 x 192 for NVFP4).  Warp 0 streams
