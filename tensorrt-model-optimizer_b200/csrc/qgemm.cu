@@ -30,7 +30,8 @@ namespace b200q {
 
 constexpr int kQM = 128;            // output rows per CTA
 constexpr int kQKBytes = 128;       // bytes of K per ring stage = one 128-byte swizzle row
-constexpr int kQThreads = 192;
+constexpr int kQThreads = 192;       // producer warp, MMA warp, four epilogue warps
+constexpr int kQThreadsWide = 320;   // ... and four more epilogue warps where one CTA has the SM to itself
 constexpr int kQMaxStages = 4;
 constexpr uint32_t kQSfTile = 512;  // one 128-row x 4-scale tile
 
@@ -47,6 +48,9 @@ template <int KIND, int BN, int MT> struct QCfg {
   static constexpr uint32_t kStageBytes = MT * kTileA + kTileB + kSfA + kSfB;   // a multiple of 1024
   static constexpr int kStages = (BN == 128 && MT == 1) ? 3 : (kStageBytes > 56 * 1024 ? 3 : 4);
   static constexpr int kCtasPerSm = (BN == 128 && MT == 1) ? 2 : 1;
+  // the un-overlapped epilogue of a lone CTA is drained by eight warps, two per TMEM lane quarter
+  static constexpr int kThreads = kCtasPerSm == 1 ? kQThreadsWide : kQThreads;
+  static constexpr int kEpiWarps = kThreads / 32 - 2;
   // TMEM columns: MT fp32 accumulators of BN columns, then sets of scale columns: per MMA of a stage
   // 4 columns of A scales per row tile and 4 of B scales per 128 weight rows.  Stages take the sets
   // in turn, so the scale copy of a stage does not wait for the MMAs of the one before.
@@ -178,7 +182,7 @@ __device__ __forceinline__ void q_store_chunk(const QEpilogue& ep, const uint32_
 }
 
 template <int KIND, int BN, int MT>
-__global__ void __launch_bounds__(kQThreads, QCfg<KIND, BN, MT>::kCtasPerSm)
+__global__ void __launch_bounds__(QCfg<KIND, BN, MT>::kThreads, QCfg<KIND, BN, MT>::kCtasPerSm)
 qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, int64_t M, int64_t N,
              int num_k_blocks, QEpilogue ep, uint32_t* __restrict__ status) {
@@ -309,9 +313,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       umma_commit(&sm->accum);        // fires when every MMA issued above has completed
     }
   } else {
-    // epilogue warps 2..5: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read
+    // epilogue warps 2..: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read; with
+    // eight of them, warps 6..9 take the upper half of the columns
     const int quarter = warp & 3;
-    if constexpr (Cfg::kSfByWarps) {
+    const int col_part = (warp - 2) >> 2;
+    constexpr int kColParts = Cfg::kEpiWarps / 4, kChunksPerPart = BN / 32 / kColParts;
+    if (Cfg::kSfByWarps && col_part == 0) {
       // during the main loop: the scales of each stage from shared memory into this warp's lane
       // quarter of the stage's TMEM columns (lane i: bytes 16 i .. 16 i + 15 of a tile = its four
       // columns), then one arrival per warp on the stage's sf_ready barrier
@@ -342,14 +349,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
       // every load of the ring has been consumed by now: its first bytes serve as staging space
-      uint8_t* stage = ring + quarter * 32 * kQEpiPitch;
+      uint8_t* stage = ring + (warp - 2) * 32 * kQEpiPitch;
       const float alpha = __ldg(ep.alpha0) * (ep.alpha1 ? __ldg(ep.alpha1) : 1.f);
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         const int64_t row0 = m0 + mt * kQM + quarter * 32;
         if (row0 >= M) break;                                              // warp-uniform
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = col_part * kChunksPerPart; c < (col_part + 1) * kChunksPerPart; ++c) {
           const int col0 = n0 + c * 32;
           if (col0 >= N) break;                                            // warp-uniform
           uint32_t acc[32];
@@ -419,15 +426,15 @@ static int qgemm_launch_tile(const uint8_t* a, const uint8_t* b, const uint8_t* 
                            static_cast<int>(smem)) != cudaSuccess)
     return B200Q_ERR_CUDA;
   dim3 grid(static_cast<unsigned>(mtiles), static_cast<unsigned>(ntiles));
-  qgemm_kernel<KIND, BN, MT><<<grid, kQThreads, smem, st>>>(map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep, status);
+  qgemm_kernel<KIND, BN, MT><<<grid, Cfg::kThreads, smem, st>>>(map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep, status);
   return launch_status();
 }
 
 // Tile choice, from measurements on 70B-shape problems.  FP8: 256 x 256 per CTA when that still
-// gives every SM two tiles or more, else 128 x 256, else 128 x 128 on two CTAs per SM.  NVFP4: two
-// co-resident 128 x 128 CTAs win up to very large problems, where 128 x 256 takes over; 256 x 192
-// (384 accumulator columns + the block scales, scale copies by tcgen05.cp) is kept for the
-// override.  B200Q_QGEMM_TILE = "128", "256" (128 x 256) or "big" forces one.
+// gives every SM two tiles or more, else 128 x 256 while 0.4 tiles per SM or more remain, else
+// 128 x 128 on two CTAs per SM.  NVFP4: 128 x 256 under the same condition, else 128 x 128;
+// 256 x 192 (384 accumulator columns + the block scales, scale copies by tcgen05.cp) is kept for
+// the override.  B200Q_QGEMM_TILE = "128", "256" (128 x 256) or "big" forces one.
 template <int KIND>
 static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
                         int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
@@ -438,7 +445,7 @@ static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
   if (KIND == kQFp8) {
     if (mt128 * ((n + 255) / 256) * 10 >= sms * 4) choice = 256;
     if (m > 128 && big_tiles >= 2 * sms) choice = 512;
-  } else if (mt128 * ((n + 255) / 256) >= 16 * sms) {
+  } else if (mt128 * ((n + 255) / 256) * 10 >= sms * 4) {
     choice = 256;
   }
   if (const char* e = getenv("B200Q_QGEMM_TILE")) {
