@@ -9,7 +9,8 @@
 // One CTA computes one 128 x BN output tile (BN = 128 or 256).  Warp 0 streams 128 x 64 and
 // BN x 64 operand tiles into a shared-memory ring with TMA (128-byte swizzle), one thread of warp 1
 // issues tcgen05.mma (UMMA 128 x BN x 16, bf16 -> fp32 in TMEM) and frees ring slots with
-// tcgen05.commit, warps 2-5 read the accumulator with tcgen05.ld and do the epilogue.
+// tcgen05.commit, warps 2-5 (2-9 where a CTA has the SM to itself) read the accumulator with
+// tcgen05.ld and do the epilogue.
 //
 // Every mbarrier wait is bounded: when a wait runs out, an error bit is set in the caller's status
 // word, the CTA stops waiting anywhere else, lets its outstanding work drain, frees its TMEM and
@@ -24,7 +25,8 @@ constexpr int kGM = 128, kGK = 64;                   // CTA tile rows; kGK bf16 
 constexpr int kMaxStages = 4;
 constexpr int kUmmaK = 16;
 constexpr uint32_t kTileBytesA = kGM * kGK * 2;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;       // producer warp, MMA warp, four epilogue warps
+constexpr int kGemmThreadsWide = 320;   // ... and four more epilogue warps where one CTA has the SM to itself
 // Two tile widths: 128 x 128 with a 3-deep ring (96 KB, two CTAs per SM, so one CTA's epilogue
 // overlaps the other's main loop) and 128 x 256 with a 4-deep ring (192 KB, one CTA per SM, a
 // third less operand traffic per FLOP).
@@ -36,6 +38,9 @@ template <int BN, int MT> struct GemmCfg {
   static constexpr uint32_t kStageBytes = MT * kTileBytesA + kTileBytesB;
   static constexpr uint32_t kTmemCols = BN * MT;       // fp32 accumulator columns
   static constexpr int kCtasPerSm = (BN == 128 && MT == 1) ? 2 : 1;
+  // the un-overlapped epilogue of a lone CTA is drained by eight warps, two per TMEM lane quarter
+  static constexpr int kThreads = kCtasPerSm == 1 ? kGemmThreadsWide : kGemmThreads;
+  static constexpr int kColParts = (kThreads / 32 - 2) / 4;
   // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((kGM >> 4) << 24);
 };
@@ -56,7 +61,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, GemmSm
 }
 
 template <int BN, int MT>
-__global__ void __launch_bounds__(kGemmThreads, GemmCfg<BN, MT>::kCtasPerSm)
+__global__ void __launch_bounds__(GemmCfg<BN, MT>::kThreads, GemmCfg<BN, MT>::kCtasPerSm)
 awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const __nv_bfloat16* __restrict__ ref, int64_t N, int num_k_blocks,
                       double* __restrict__ sum_io, float* __restrict__ c_out, uint32_t* __restrict__ status) {
@@ -125,8 +130,10 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       umma_commit(&sm->accum);        // fires when every MMA issued above has completed
     }
   } else {
-    // epilogue warps 2..5: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read
+    // epilogue warps 2..: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read
     const int quarter = warp & 3;
+    const int col_part = (warp - 2) >> 2;       // warps 6..9 take the upper half of the columns
+    constexpr int kChunksPerPart = BN / 32 / Cfg::kColParts;
     const bool ok = mbar_wait(&sm->accum, 0, sm, status, kErrEpilogueWait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float sq = 0.f;
@@ -136,7 +143,7 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int64_t row = m0 + mt * kGM + quarter * 32 + lane;
         const __nv_bfloat16* rrow = ref + row * N + n0;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = col_part * kChunksPerPart; c < (col_part + 1) * kChunksPerPart; ++c) {
           uint32_t acc[32];
           tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);
           const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
@@ -223,7 +230,7 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
                              static_cast<int>(smem)) != cudaSuccess)
       return B200Q_ERR_CUDA;
     dim3 grid(static_cast<unsigned>(m / (kGM * MT)), static_cast<unsigned>(n / BN));
-    awq_gemm_sqerr_kernel<BN, MT><<<grid, kGemmThreads, smem, st>>>(
+    awq_gemm_sqerr_kernel<BN, MT><<<grid, Cfg::kThreads, smem, st>>>(
         map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
         status_io);
     return launch_status();
