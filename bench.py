@@ -466,6 +466,18 @@ def run_formats(dev, peak):
     r = timed(lambda: [torch.nn.functional.linear(x, wfq) for _ in range(21)], 1, reps=3, groups=3)
     out["cublas_linear_512x14336x4096_for_comparison"] = {"ms_per_gemm": r["ms"] / 21,
                                                           "tflops": flops / (r["ms"] * 1e-3) / 1e12}
+    # the down projection of the same MLP (few tiles, long K): K split over two CTAs per tile
+    xd = torch.randn(512, 14336, generator=g, device=dev).bfloat16()
+    wd = (torch.randn(4096, 14336, generator=g, device=dev) * 0.02).bfloat16()
+    refd = torch.nn.functional.linear(xd, wd)
+    r = timed(lambda: [ops.awq_gemm_sqerr(xd, wd, refd, acc, status) for _ in range(21)], 1, reps=3, groups=3)
+    out["awq_gemm_sqerr_tcgen05_512x4096x14336"] = {
+        "ms_per_gemm": r["ms"] / 21, "tflops": flops / (r["ms"] * 1e-3) / 1e12,
+        "k_splits": ops.awq_gemm_splits(512, 4096, 14336, dev), "kernel_status": int(status)}
+    r = timed(lambda: [torch.nn.functional.linear(xd, wd) for _ in range(21)], 1, reps=3, groups=3)
+    out["cublas_linear_512x4096x14336_for_comparison"] = {"ms_per_gemm": r["ms"] / 21,
+                                                          "tflops": flops / (r["ms"] * 1e-3) / 1e12}
+    del xd, wd, refd
     del ws, wfq, bufs
     # the real-quant GEMM consumers (a 70B-shape projection: 4096 tokens x 8192 -> 8192), beside
     # the library kernels torch._scaled_mm reaches for the same operands

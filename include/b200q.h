@@ -267,6 +267,15 @@ int b200q_sq_diff_sum(const void* a, const void* b, int64_t n, int dtype, double
 int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
                          int64_t k, double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* The same with the K extent split over `splits` (1..16) CTAs per output tile, for shapes with few
+ * tiles and a long K (a down projection: 512 x 4096 x 14336).  Each CTA leaves an fp32 partial tile
+ * in `workspace` (splits * m * n floats); the CTA of a tile that finishes last adds them in split
+ * order, so the result does not depend on timing, and runs the same epilogue.  `counters` holds one
+ * zeroed uint32 per 128 x 128 tile; the kernel leaves them zero again.  splits == 1 ignores both. */
+int b200q_awq_gemm_sqerr_splitk(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
+                                int64_t k, int splits, float* workspace, uint32_t* counters,
+                                double* sum_io, float* c_out, uint32_t* status_io, void* stream);
+
 /* NVFP4 with a block size other than 16 (any even size; NVFP4QTensor.quantize and
  * dynamic_block_quant take the block size as an argument, modelopt/torch/quantization/qtensor/
  * nvfp4_tensor.py:142-232, tensor_quant.py:158-198).  Same arithmetic and argument meaning as

@@ -59,6 +59,7 @@ SIGNATURES = {
     "b200q_fp8_gemm_operand": [_p, _p, _p, _i64, _i, _i, _p],
     "b200q_nvfp4_gemm": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
     "b200q_nvfp4_swizzle_scales": [_p, _p, _i64, _i64, _p],
+    "b200q_awq_gemm_sqerr_splitk": [_p, _p, _p, _i64, _i64, _i64, _i, _p, _p, _p, _p, _p, _p],
     "b200q_int4_export_pack": [_p, _p, _i, _p, _i64, _i64, _i, _i, _p],
     "b200q_nvfp4_quantize_blocks": [_p, _i64, _i, _i, _p, _p, _p, _p, _p, _i, _p],
     "b200q_nvfp4_fake_blocks": [_p, _p, _i64, _i, _i, _p, _p],

@@ -454,17 +454,43 @@ def awq_gemm_supported(a: torch.Tensor, b: torch.Tensor) -> bool:
             and a.shape[1] == b.shape[1])
 
 
+_SPLITK_SCRATCH: dict = {}
+
+
+def awq_gemm_splits(m: int, n: int, k: int, device) -> int:
+    """How many CTAs share the K extent of one output tile: 1 unless the 128 x 128 tiles leave half of
+    the SMs' two CTA slots empty and K is long enough to give every split 16 K blocks or more."""
+    tiles = (m // 128) * (n // 128)
+    slots = 2 * torch.cuda.get_device_properties(device).multi_processor_count
+    return max(1, min(slots // max(tiles, 1), k // 64 // 16, 4))
+
+
 def awq_gemm_sqerr(a: torch.Tensor, b: torch.Tensor, ref: torch.Tensor, acc: torch.Tensor,
-                   status: torch.Tensor, c_out: torch.Tensor | None = None):
+                   status: torch.Tensor, c_out: torch.Tensor | None = None, splits: int | None = None):
     """acc (float64, 1 element) += sum of squared bf16 differences between bf16(a @ b.T) and ref.
-    ``status`` is an int32 device word that collects error bits of the kernel's bounded waits."""
+    ``status`` is an int32 device word that collects error bits of the kernel's bounded waits.
+    ``splits`` (default: ``awq_gemm_splits``) CTAs share the K extent of a tile; their scratch
+    (fp32 partial tiles, tile counters) is kept per device, stream and shape and reused in stream
+    order."""
     a, b, ref = _prep(a), _prep(b), _prep(ref)
     m, k = a.shape
     n = b.shape[0]
     assert ref.shape == (m, n) and ref.dtype == torch.bfloat16 and acc.dtype == torch.float64
+    if splits is None:
+        splits = awq_gemm_splits(m, n, k, a.device)
     with torch.cuda.device(a.device):
-        call("b200q_awq_gemm_sqerr", a.data_ptr(), b.data_ptr(), ref.data_ptr(), m, n, k, acc.data_ptr(),
-             c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(a))
+        if splits <= 1:
+            call("b200q_awq_gemm_sqerr", a.data_ptr(), b.data_ptr(), ref.data_ptr(), m, n, k, acc.data_ptr(),
+                 c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(a))
+        else:
+            key = (a.device, _stream(a), splits, m, n)
+            scratch = _SPLITK_SCRATCH.get(key)
+            if scratch is None:
+                scratch = _SPLITK_SCRATCH[key] = (torch.empty(splits * m * n, dtype=torch.float32, device=a.device),
+                                                  torch.zeros((m // 128) * (n // 128), dtype=torch.int32, device=a.device))
+            call("b200q_awq_gemm_sqerr_splitk", a.data_ptr(), b.data_ptr(), ref.data_ptr(), m, n, k, splits,
+                 scratch[0].data_ptr(), scratch[1].data_ptr(), acc.data_ptr(),
+                 c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(a))
     return acc
 
 

@@ -9,8 +9,7 @@
 // One CTA computes one 128 x BN output tile (BN = 128 or 256).  Warp 0 streams 128 x 64 and
 // BN x 64 operand tiles into a shared-memory ring with TMA (128-byte swizzle), one thread of warp 1
 // issues tcgen05.mma (UMMA 128 x BN x 16, bf16 -> fp32 in TMEM) and frees ring slots with
-// tcgen05.commit, warps 2-5 (2-9 where a CTA has the SM to itself) read the accumulator with
-// tcgen05.ld and do the epilogue.
+// tcgen05.commit, warps 2-5 read the accumulator with tcgen05.ld and do the epilogue.
 //
 // Every mbarrier wait is bounded: when a wait runs out, an error bit is set in the caller's status
 // word, the CTA stops waiting anywhere else, lets its outstanding work drain, frees its TMEM and
@@ -26,7 +25,6 @@ constexpr int kMaxStages = 4;
 constexpr int kUmmaK = 16;
 constexpr uint32_t kTileBytesA = kGM * kGK * 2;
 constexpr int kGemmThreads = 192;       // producer warp, MMA warp, four epilogue warps
-constexpr int kGemmThreadsWide = 320;   // ... and four more epilogue warps where one CTA has the SM to itself
 // Two tile widths: 128 x 128 with a 3-deep ring (96 KB, two CTAs per SM, so one CTA's epilogue
 // overlaps the other's main loop) and 128 x 256 with a 4-deep ring (192 KB, one CTA per SM, a
 // third less operand traffic per FLOP).
@@ -38,8 +36,11 @@ template <int BN, int MT> struct GemmCfg {
   static constexpr uint32_t kStageBytes = MT * kTileBytesA + kTileBytesB;
   static constexpr uint32_t kTmemCols = BN * MT;       // fp32 accumulator columns
   static constexpr int kCtasPerSm = (BN == 128 && MT == 1) ? 2 : 1;
-  // the un-overlapped epilogue of a lone CTA is drained by eight warps, two per TMEM lane quarter
-  static constexpr int kThreads = kCtasPerSm == 1 ? kGemmThreadsWide : kGemmThreads;
+  // Four epilogue warps.  Eight (two per TMEM lane quarter, as the real-quant GEMMs use) make the
+  // kernel alone 6-8 % faster, but the search runs it under the next candidate's quantise kernel on
+  // a second stream, and with the wider CTA that overlap was lost (2.16-2.23 ms per 21 candidates
+  // against 2.04-2.10 ms).
+  static constexpr int kThreads = kGemmThreads;
   static constexpr int kColParts = (kThreads / 32 - 2) / 4;
   // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((kGM >> 4) << 24);
@@ -53,7 +54,50 @@ struct GemmSmem {
   uint64_t accum;
   uint32_t tmem_base;
   uint32_t abort;
+  uint32_t last_split;   // split-K: 1 in the CTA that found the other splits' partial tiles complete
 };
+
+// Split-K staging: a warp's 32 x 32 fp32 piece passes through shared memory so that global memory
+// sees whole 128-byte row segments (8 lanes per row, 4 rows per instruction) instead of one row per lane.
+constexpr uint32_t kSplitPitch = 32 * 4 + 16;
+__device__ __forceinline__ void split_store_piece(const uint32_t* acc, uint8_t* stage, int lane, float* dst, int64_t ld) {
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * kSplitPitch);
+#pragma unroll
+  for (int v = 0; v < 8; ++v) mine[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+  __syncwarp();
+  const int part = lane & 7, rsub = lane >> 3;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = rsub + 4 * i;
+    *reinterpret_cast<uint4*>(dst + r * ld + part * 4) = *reinterpret_cast<const uint4*>(stage + r * kSplitPitch + part * 16);
+  }
+  __syncwarp();
+}
+// sum of the `splits` partial pieces (in split order) back into one row per lane
+__device__ __forceinline__ void split_load_piece(uint32_t* acc, uint8_t* stage, int lane, const float* src, int64_t ld,
+                                                 int64_t split_stride, int splits) {
+  const int part = lane & 7, rsub = lane >> 3;
+  float4 sum[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < splits; ++z) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 p = __ldcg(reinterpret_cast<const float4*>(src + z * split_stride + (rsub + 4 * i) * ld + part * 4));
+      sum[i].x += p.x; sum[i].y += p.y; sum[i].z += p.z; sum[i].w += p.w;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(stage + (rsub + 4 * i) * kSplitPitch + part * 16) = sum[i];
+  __syncwarp();
+  const uint4* mine = reinterpret_cast<const uint4*>(stage + lane * kSplitPitch);
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    const uint4 q = mine[v];
+    acc[4 * v] = q.x; acc[4 * v + 1] = q.y; acc[4 * v + 2] = q.z; acc[4 * v + 3] = q.w;
+  }
+  __syncwarp();
+}
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, GemmSmem* sm, uint32_t* status,
                                           uint32_t code) {
@@ -63,9 +107,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, GemmSm
 template <int BN, int MT>
 __global__ void __launch_bounds__(GemmCfg<BN, MT>::kThreads, GemmCfg<BN, MT>::kCtasPerSm)
 awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const __nv_bfloat16* __restrict__ ref, int64_t N, int num_k_blocks,
-                      double* __restrict__ sum_io, float* __restrict__ c_out, uint32_t* __restrict__ status) {
+                      const __nv_bfloat16* __restrict__ ref, int64_t N, int total_k_blocks, int kb_per_split,
+                      float* __restrict__ partial, uint32_t* __restrict__ counters, double* __restrict__ sum_io,
+                      float* __restrict__ c_out, uint32_t* __restrict__ status) {
   using Cfg = GemmCfg<BN, MT>;
+  // split-K (gridDim.z > 1): this CTA sums K blocks kb0 .. kb0 + num_k_blocks - 1 and leaves an fp32
+  // partial tile in `partial`; the CTA of a tile that finishes last adds the partial tiles in split
+  // order (so the sum does not depend on timing) and runs the loss epilogue
+  const int splits = gridDim.z;
+  const int kb0 = blockIdx.z * kb_per_split;
+  const int num_k_blocks = min(kb_per_split, total_k_blocks - kb0);
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes, kTmemCols = Cfg::kTmemCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -101,8 +152,8 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         uint8_t* a = ring + s * kStageBytes;
         mbar_expect_tx(&sm->full[s], kStageBytes);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * kTileBytesA, &map_a, &sm->full[s], kb * kGK, m0 + mt * kGM);
-        tma_load_2d(a + MT * kTileBytesA, &map_b, &sm->full[s], kb * kGK, n0);
+        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * kTileBytesA, &map_a, &sm->full[s], (kb0 + kb) * kGK, m0 + mt * kGM);
+        tma_load_2d(a + MT * kTileBytesA, &map_b, &sm->full[s], (kb0 + kb) * kGK, n0);
       }
     }
   } else if (warp == 1) {
@@ -132,20 +183,53 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else {
     // epilogue warps 2..: TMEM lanes (warp % 4) * 32 .. + 31 are the rows this warp may read
     const int quarter = warp & 3;
-    const int col_part = (warp - 2) >> 2;       // warps 6..9 take the upper half of the columns
+    const int col_part = (warp - 2) >> 2;       // 0 with four epilogue warps; a wider CTA would split the columns
     constexpr int kChunksPerPart = BN / 32 / Cfg::kColParts;
     const bool ok = mbar_wait(&sm->accum, 0, sm, status, kErrEpilogueWait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     float sq = 0.f;
-    if (ok) {
+    bool finish = ok;                       // this CTA runs the loss epilogue
+    const int64_t m_total = static_cast<int64_t>(gridDim.x) * kGM * MT;
+    uint8_t* stage = ring + (warp - 2) * 32 * kSplitPitch;   // the ring is idle once the accumulator is complete
+    if (splits > 1) {
+      constexpr int kEpiThreads = Cfg::kThreads - 64;
+      if (ok) {
+#pragma unroll 1
+        for (int mt = 0; mt < MT; ++mt) {
+          const int64_t row0 = m0 + mt * kGM + quarter * 32;
+#pragma unroll 1
+          for (int c = col_part * kChunksPerPart; c < (col_part + 1) * kChunksPerPart; ++c) {
+            uint32_t acc[32];
+            tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);
+            split_store_piece(acc, stage, lane, partial + (blockIdx.z * m_total + row0) * N + n0 + c * 32, N);
+          }
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");      // the epilogue warps only
+      if (threadIdx.x == 64) {
+        uint32_t* counter = counters + blockIdx.y * gridDim.x + blockIdx.x;
+        const uint32_t seen = atomicAdd(counter, 1u);
+        sm->last_split = seen == static_cast<uint32_t>(splits - 1);
+        if (sm->last_split) *counter = 0;                                    // ready for the next launch
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      finish = ok && *reinterpret_cast<volatile uint32_t*>(&sm->last_split) != 0;
+      __threadfence();
+    }
+    if (finish) {
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
-        const int64_t row = m0 + mt * kGM + quarter * 32 + lane;
+        const int64_t row0 = m0 + mt * kGM + quarter * 32;
+        const int64_t row = row0 + lane;
         const __nv_bfloat16* rrow = ref + row * N + n0;
 #pragma unroll 1
         for (int c = col_part * kChunksPerPart; c < (col_part + 1) * kChunksPerPart; ++c) {
           uint32_t acc[32];
-          tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);
+          if (splits == 1)
+            tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);
+          else
+            split_load_piece(acc, stage, lane, partial + row0 * N + n0 + c * 32, N, m_total * N, splits);
           const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -169,7 +253,7 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
     for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    if (lane == 0 && ok) atomicAdd(sum_io, static_cast<double>(sq));
+    if (lane == 0 && finish) atomicAdd(sum_io, static_cast<double>(sq));
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -198,9 +282,9 @@ static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k
 
 using namespace b200q;
 
-extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
-                                    int64_t k, double* sum_io, float* c_out, uint32_t* status_io,
-                                    void* stream) {
+static int awq_gemm_launch(const void* a, const void* b, const void* ref, int64_t m, int64_t n, int64_t k, int splits,
+                           float* partial, uint32_t* counters, double* sum_io, float* c_out, uint32_t* status_io,
+                           void* stream) {
   B200Q_REQUIRE_PTR(a); B200Q_REQUIRE_PTR(b); B200Q_REQUIRE_PTR(ref); B200Q_REQUIRE_PTR(sum_io);
   B200Q_REQUIRE_PTR(status_io);
   B200Q_REQUIRE_ALIGNED(a); B200Q_REQUIRE_ALIGNED(b); B200Q_REQUIRE_ALIGNED(ref);
@@ -219,6 +303,11 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
     if (v == 256 && n % 256 == 0) { bn = 256; mt = 1; }
     if (v == 512 && n % 256 == 0 && m % 256 == 0) { bn = 256; mt = 2; }
   }
+  const int total_kb = static_cast<int>(k / kGK);
+  if (splits < 1 || splits > 16 || splits > total_kb) return B200Q_ERR_ARG;
+  if (splits > 1) { bn = 128; mt = 1; }                   // more, smaller CTAs is the point of splitting
+  const int kb_per_split = (total_kb + splits - 1) / splits;
+  const int zdim = (total_kb + kb_per_split - 1) / kb_per_split;   // every split has at least one block
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, bn)) return B200Q_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -229,10 +318,10 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
     if (cudaFuncSetAttribute(awq_gemm_sqerr_kernel<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return B200Q_ERR_CUDA;
-    dim3 grid(static_cast<unsigned>(m / (kGM * MT)), static_cast<unsigned>(n / BN));
+    dim3 grid(static_cast<unsigned>(m / (kGM * MT)), static_cast<unsigned>(n / BN), static_cast<unsigned>(zdim));
     awq_gemm_sqerr_kernel<BN, MT><<<grid, Cfg::kThreads, smem, st>>>(
-        map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, static_cast<int>(k / kGK), sum_io, c_out,
-        status_io);
+        map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, total_kb, kb_per_split, partial, counters, sum_io,
+        c_out, status_io);
     return launch_status();
   };
   using I1 = std::integral_constant<int, 1>;
@@ -242,4 +331,17 @@ extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* re
   if (bn == 256 && mt == 2) return launch(I256{}, I2{});
   if (bn == 256) return launch(I256{}, I1{});
   return launch(I128{}, I1{});
+}
+
+extern "C" int b200q_awq_gemm_sqerr(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
+                                    int64_t k, double* sum_io, float* c_out, uint32_t* status_io,
+                                    void* stream) {
+  return awq_gemm_launch(a, b, ref, m, n, k, 1, nullptr, nullptr, sum_io, c_out, status_io, stream);
+}
+
+extern "C" int b200q_awq_gemm_sqerr_splitk(const void* a, const void* b, const void* ref, int64_t m, int64_t n,
+                                           int64_t k, int splits, float* workspace, uint32_t* counters,
+                                           double* sum_io, float* c_out, uint32_t* status_io, void* stream) {
+  if (splits > 1) { B200Q_REQUIRE_PTR(workspace); B200Q_REQUIRE_PTR(counters); B200Q_REQUIRE_ALIGNED(workspace); }
+  return awq_gemm_launch(a, b, ref, m, n, k, splits, workspace, counters, sum_io, c_out, status_io, stream);
 }

@@ -85,3 +85,35 @@ def test_awq_lite_search_same_result_with_and_without_tensor_core_kernel():
         for k in la:
             assert abs(la[k] - lb[k]) <= 1e-3 * lb[k], (n, k, la[k], lb[k])
         assert aa == ab and torch.equal(sa, sb)
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(128, 128, 256, 2), (256, 384, 1024, 4), (512, 512, 4096 + 64, 3),
+                                          (512, 4096, 14336, None)])
+def test_awq_gemm_split_k_matches_unsplit(m, n, k, splits):
+    """Split-K: partial tiles summed in split order by the last CTA of a tile.  Same product to fp32
+    summation order, loss within the 1e-3 of the AWQ losses (bf16 roundings of the product flip with
+    the summation order), bit-identical from run to run, counters left at zero."""
+    from b200q import ops
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g, device="cuda").bfloat16()
+    b = (torch.randn(n, k, generator=g, device="cuda") * 0.05).bfloat16()
+    ref = (a.float() @ b.float().T + 0.01 * torch.randn(m, n, generator=g, device="cuda")).bfloat16()
+    status = torch.zeros((), dtype=torch.int32, device="cuda")
+    if splits is None:
+        splits = ops.awq_gemm_splits(m, n, k, a.device)
+        assert splits >= 2                               # the down-projection shape is split by default
+    outs = []
+    for s in (1, splits, splits):
+        acc = torch.zeros((), dtype=torch.float64, device="cuda")
+        c = torch.full((m, n), float("nan"), device="cuda")
+        ops.awq_gemm_sqerr(a, b, ref, acc, status, c_out=c, splits=s)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        outs.append((c, acc.item()))
+    (c1, l1), (c2, l2), (c3, l3) = outs
+    assert torch.allclose(c2, c1, rtol=1e-5, atol=1e-5 * float(c1.abs().max()))
+    assert abs(l2 - l1) <= 1e-3 * l1
+    assert torch.equal(c2, c3) and l2 == l3 or abs(l2 - l3) <= 1e-12 * l2   # the sum order inside a tile is fixed
+    for key, (_, counters) in ops._SPLITK_SCRATCH.items():
+        assert int(counters.abs().sum()) == 0
