@@ -18,10 +18,36 @@ struct ToE4m3 {
 // GEMM operand cast: fp32 scale, the quotient clamped to the E4M3 range before the cast (NaN stays
 // NaN).  ROUND: the quotient is rounded to T first, as an eager tensor expression does; without it
 // the quotient stays in fp32, as in a fused (compiled) graph.
-template <typename T, bool ROUND> __device__ __forceinline__ uint32_t e4m3_operand(float x, float scale) {
-  float v = __fdiv_rn(x, scale);
+// The division goes through the reciprocal of the scale (y, formed once per thread) with two
+// residual corrections, which returns the correctly rounded quotient wherever scale and numerator
+// are in the safe range (`fast`: the scale; checked per element: the numerator); zeros keep their
+// sign, everything else takes the IEEE division.  The saturating hardware conversion then does the
+// clamp to +-448 and the NaN code in one step.
+template <typename T, bool ROUND> __device__ __forceinline__ float operand_quotient(float x, float scale, float y, bool fast) {
+  float v = !fast ? __fdiv_rn(x, scale)
+                  : (x == 0.f ? x : (div_safe(fabsf(x)) ? div_rn_rcp(x, scale, y) : __fdiv_rn(x, scale)));
   if (ROUND) v = round_to_t<T>(v);
-  return f32_to_e4m3_torch(v != v ? v : fminf(448.f, fmaxf(-448.f, v)));
+  return v;
+}
+template <typename T, bool ROUND>
+__device__ __forceinline__ uint32_t e4m3_operand(float x, float scale, float y, bool fast) {
+  return f32_to_e4m3_sat(operand_quotient<T, ROUND>(x, scale, y, fast));
+}
+// two elements: packed corrections when both numerators are safe (or zero)
+template <typename T, bool ROUND>
+__device__ __forceinline__ uint32_t e4m3_operand2(float a, float b, float scale, float y, bool fast) {
+  const bool za = a == 0.f, zb = b == 0.f;
+  float va, vb;
+  if (fast && (za || div_safe(fabsf(a))) && (zb || div_safe(fabsf(b)))) {
+    const float2 q = div2_rn_rcp(make_float2(a, b), make_float2(-scale, -scale), make_float2(y, y));
+    va = za ? a : q.x;
+    vb = zb ? b : q.y;
+    if (ROUND) { va = round_to_t<T>(va); vb = round_to_t<T>(vb); }
+  } else {
+    va = operand_quotient<T, ROUND>(a, scale, y, fast);
+    vb = operand_quotient<T, ROUND>(b, scale, y, fast);
+  }
+  return f32x2_to_e4m3x2_sat(va, vb);
 }
 
 template <typename T, bool ROUND>
@@ -31,6 +57,8 @@ fp8_operand_kernel(const T* __restrict__ x, const float* __restrict__ scale, uin
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   const float s = __ldg(scale);
+  const float y = __frcp_rn(s);
+  const bool fast = div_safe(s);
   const int64_t npack = n / P, stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   const bool vec_out = (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
@@ -40,8 +68,8 @@ fp8_operand_kernel(const T* __restrict__ x, const float* __restrict__ scale, uin
     uint32_t w[P / 4];
 #pragma unroll
     for (int k = 0; k < P / 4; ++k)
-      w[k] = e4m3_operand<T, ROUND>(f[4 * k], s) | (e4m3_operand<T, ROUND>(f[4 * k + 1], s) << 8) |
-             (e4m3_operand<T, ROUND>(f[4 * k + 2], s) << 16) | (e4m3_operand<T, ROUND>(f[4 * k + 3], s) << 24);
+      w[k] = e4m3_operand2<T, ROUND>(f[4 * k], f[4 * k + 1], s, y, fast) |
+             (e4m3_operand2<T, ROUND>(f[4 * k + 2], f[4 * k + 3], s, y, fast) << 16);
     if (vec_out) {
       if (P == 8) *reinterpret_cast<uint2*>(q + i * P) = make_uint2(w[0], w[P / 4 - 1]);
       else *reinterpret_cast<uint32_t*>(q + i * P) = w[0];
@@ -52,7 +80,7 @@ fp8_operand_kernel(const T* __restrict__ x, const float* __restrict__ scale, uin
   }
   // ragged tail
   for (int64_t i = npack * P + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-    q[i] = static_cast<uint8_t>(e4m3_operand<T, ROUND>(E::to_float(x[i]), s));
+    q[i] = static_cast<uint8_t>(e4m3_operand<T, ROUND>(E::to_float(x[i]), s, y, fast));
 }
 struct ToInt8 {
   template <typename T> static __device__ __forceinline__ uint32_t cvt(float x, float scale) {

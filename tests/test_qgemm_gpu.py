@@ -155,6 +155,7 @@ def test_fp8_gemm_operand_matches_oracle_bytes(dtype):
     rng = np.random.default_rng(3)
     x = torch.from_numpy((rng.standard_normal((64, 1000)) * 3).astype(np.float32)).to(dtype)
     x[0, :4] = torch.tensor([1e4, -1e4, float("nan"), 0.0], dtype=dtype)      # beyond the range: saturate
+    x[1, :6] = torch.tensor([-0.0, float("inf"), -float("inf"), 1e-30, -1e-30, 6e-8], dtype=dtype)   # signed zero, infinities, tiny
     scale = torch.tensor(0.0123)
     for fused in (False, True):
         got = ops.fp8_gemm_operand(x.cuda(), scale.cuda(), fused=fused).view(torch.uint8).cpu().numpy()
