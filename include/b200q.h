@@ -99,7 +99,10 @@ int b200q_fake_e4m3_axis(const void* x, void* y, int64_t outer, int64_t axis, in
 
 /* flags for b200q_nvfp4_quantize */
 enum {
-  B200Q_NVFP4_GLOBAL_IS_SCALE2 = 1 /* `global` holds weights_scaling_factor_2, not amax */
+  B200Q_NVFP4_GLOBAL_IS_SCALE2 = 1, /* `global` holds weights_scaling_factor_2, not amax */
+  B200Q_NVFP4_SATURATE_SCALES = 2   /* block scales above the E4M3 range saturate to 448 (as the fake-quant
+                                       path and the GEMM's activation quantiser do) instead of becoming the
+                                       NaN code of the tensor cast: for data that can exceed a calibrated amax */
 };
 
 /* Two-level-scale NVFP4 real quantisation of nblocks runs of 16 contiguous elements:

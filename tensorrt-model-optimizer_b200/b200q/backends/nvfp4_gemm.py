@@ -45,7 +45,8 @@ def nvfp4_gemm(quant_module, input_tensor, bias=None):
     if input_tensor.dtype == torch.float32:
         input_tensor = input_tensor.to(torch.float16)
     x2 = input_tensor.reshape(-1, input_tensor.shape[-1])
-    a4, sfa, s2a = ops.nvfp4_quantize(x2, amax=quant_module.input_quantizer.amax)
+    # activations may exceed the calibrated amax: their block scales saturate, as in the fake-quant path
+    a4, sfa, s2a = ops.nvfp4_quantize(x2, amax=quant_module.input_quantizer.amax, saturate_scales=True)
     b4, sfb_tiled, s2b = _weight_operand(quant_module)
     quant_module.alpha = s2a * s2b
     out = ops.nvfp4_gemm(a4, ops.nvfp4_swizzle_scales(sfa), b4, sfb_tiled, quant_module.alpha, bias, x2.dtype)

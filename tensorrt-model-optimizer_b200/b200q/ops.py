@@ -162,10 +162,12 @@ def fake_e4m3(x: torch.Tensor, amax: torch.Tensor | None) -> torch.Tensor:
 # --------------------------------------------------------------------------- NVFP4 -------------
 
 def nvfp4_quantize(x: torch.Tensor, amax: torch.Tensor | None = None, scale2: torch.Tensor | None = None,
-                   scales_in: torch.Tensor | None = None, block: int = 16):
+                   scales_in: torch.Tensor | None = None, block: int = 16, saturate_scales: bool = False):
     """x [..., K] with K % block == 0 -> (packed uint8 [..., K/2], scales float8_e4m3fn [..., K/block],
     scale2 fp32 0-dim).  ``amax`` (any float dtype, 1 element) or ``scale2`` may be given; with
-    neither the tensor's own abs-max is used.  block 16 (the format's own) runs the fast kernels."""
+    neither the tensor's own abs-max is used.  block 16 (the format's own) runs the fast kernels.
+    ``saturate_scales`` (block 16): a block whose scale exceeds the E4M3 range (data beyond a calibrated
+    amax) gets 448, as in the fake-quant path, instead of the NaN code of the tensor cast."""
     x = _prep(x, 32 if block == 16 else 16)
     K = x.shape[-1]
     if K % block or block % 2:
@@ -175,10 +177,12 @@ def nvfp4_quantize(x: torch.Tensor, amax: torch.Tensor | None = None, scale2: to
     packed = torch.empty((*x.shape[:-1], K // 2), dtype=torch.uint8, device=dev)
     scales = torch.empty((*x.shape[:-1], K // block), dtype=torch.uint8, device=dev)
     s2 = torch.empty((), dtype=torch.float32, device=dev)
-    flags = 0
+    flags = 2 if saturate_scales else 0
+    if saturate_scales and block != 16:
+        raise ValueError("saturate_scales is built for block size 16")
     if scale2 is not None:
         glob = _amax_f32(scale2, dev).reshape(())
-        flags = 1
+        flags |= 1
     elif amax is not None:
         glob = _amax_f32(amax, dev).reshape(())
     else:

@@ -259,14 +259,15 @@ template <typename T>
 __device__ __forceinline__ void nvfp4_quant_block(const Block16<T>& blk, int64_t b, const Nvfp4Tensor& tn,
                                                   const uint8_t* __restrict__ scales_in,
                                                   uint8_t* __restrict__ packed,
-                                                  uint8_t* __restrict__ scales, bool pair = false) {
+                                                  uint8_t* __restrict__ scales, bool pair = false,
+                                                  bool sat_scales = false) {
   uint32_t abits = blk.amax_f32bits();
   if (pair) abits = max(abits, __shfl_xor_sync(__activemask(), abits, 1));
   const float bamax = __uint_as_float(abits);
   const int64_t sb = pair ? (b >> 1) : b;
   uint32_t code;
   if (scales_in) code = scales_in[sb];
-  else code = nvfp4_scale_code<true>(bamax, tn);
+  else code = sat_scales ? nvfp4_scale_code<false>(bamax, tn) : nvfp4_scale_code<true>(bamax, tn);
   const float d = e4m3_to_f32(code) * tn.s2;
   float f[16];
   blk.decode(f);
@@ -280,7 +281,7 @@ __global__ void __launch_bounds__(kNvThreads)
 nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __restrict__ global,
                       bool global_is_s2, const uint8_t* __restrict__ scales_in,
                       uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                      float* __restrict__ s2_out, bool pair) {
+                      float* __restrict__ s2_out, bool pair, bool sat_scales) {
   pdl_prologue();
   const float g = __ldg(global);
   const Nvfp4Tensor tn(global_is_s2 ? g : __fdiv_rn(g, 2688.f));
@@ -297,7 +298,7 @@ nvfp4_quantize_kernel(const T* __restrict__ x, int64_t nblocks, const float* __r
 #pragma unroll
     for (int u = 0; u < kNvUnroll; ++u) {
       const int64_t b = b0 + u * stride;
-      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, tn, scales_in, packed, scales, pair);
+      if (b < nblocks) nvfp4_quant_block<T>(blk[u], b, tn, scales_in, packed, scales, pair, sat_scales);
     }
   }
 }
@@ -454,7 +455,8 @@ int nvfp4_launch_quantize(const void* x, int64_t nunits, int dtype, const float*
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(nunits, kNvTileBlocks, 8);
     launch_pdl(nvfp4_quantize_kernel<T>, grid, kNvThreads, 0, s, static_cast<const T*>(x), nunits, global,
-               (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0, scales_in, packed, scales, s2_out, pair);
+               (flags & B200Q_NVFP4_GLOBAL_IS_SCALE2) != 0, scales_in, packed, scales, s2_out, pair,
+               (flags & B200Q_NVFP4_SATURATE_SCALES) != 0);
     return launch_status();
   });
 }
@@ -487,7 +489,7 @@ extern "C" int b200q_nvfp4_quantize(const void* x, int64_t nblocks, int dtype, c
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED32(x);
   if ((reinterpret_cast<uintptr_t>(packed) & 7u) != 0) return B200Q_ERR_ALIGN;
   if (nblocks <= 0) return B200Q_ERR_SHAPE;
-  if (flags & ~B200Q_NVFP4_GLOBAL_IS_SCALE2) return B200Q_ERR_ARG;
+  if (flags & ~(B200Q_NVFP4_GLOBAL_IS_SCALE2 | B200Q_NVFP4_SATURATE_SCALES)) return B200Q_ERR_ARG;
   return nvfp4_launch_quantize(x, nblocks, dtype, global, scales_in, packed, scales, s2_out, flags, false,
                                static_cast<cudaStream_t>(stream));
 }

@@ -169,3 +169,30 @@ def test_save_and_restore_quantized_model(name, do_compress, tmp_path):
     assert torch.equal(got, want)
     assert [m for m, _ in mtq.modelopt_state(fresh)["modelopt_state_dict"]] == \
            [m for m, _ in ckpt["modelopt"]["modelopt_state_dict"]]
+
+
+@pytest.mark.parametrize("name", ["NVFP4_DEFAULT_CFG", "FP8_DEFAULT_CFG"])
+def test_llama_shaped_model_runs_on_real_quant_gemms(name):
+    """quantize -> compress -> enable_real_quant_gemm: every projection runs the tensor-core GEMM on
+    the packed weight, and the logits stay close to the dequantise-then-bf16 path."""
+    import b200q as mtq
+    from b200q import backends, ops
+    from b200q.nn import RealQuantLinear
+
+    torch.manual_seed(0)
+    model = TinyLlama().to(torch.bfloat16).cuda().eval()
+    ids = torch.randint(0, 512, (4, 128), device="cuda")
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(ids))
+    mtq.compress(model)
+    with torch.no_grad():
+        want = model(ids).float()
+    backends.enable_real_quant_gemm(model)
+    with torch.no_grad():
+        got = model(ids).float()
+    ops.check_qgemm_status("cuda")
+    layers = [m for m in model.modules() if isinstance(m, RealQuantLinear)]
+    used = [m for m in layers if getattr(m, "_real_quant_gemm_impl", None) is not None]
+    assert len(layers) == 14 and len(used) == 14          # 2 x (q, k, v, o, gate, up, down); lm_head is not quantised
+    cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
+    assert cos > 0.999, cos
+    assert (got - want).abs().max() <= 0.05 * want.abs().max()

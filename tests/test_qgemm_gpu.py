@@ -290,3 +290,23 @@ def test_fp8_linear_matches_reference_fixture():
         af, bf = qo.e4m3_decode(c["a8"]).astype(np.float64), qo.e4m3_decode(c["b8"]).astype(np.float64)
         absdot = np.abs(af) @ np.abs(bf).T * float(c["scale_a"]) * float(c["scale_b"])
         _check(got, unbits(c["y"], T).astype(np.float64), absdot, f"fixture case {i}")
+
+
+def test_nvfp4_quantize_saturating_scales_for_data_beyond_the_amax():
+    """Activations above a calibrated amax: with saturate_scales the block scale stops at 448 (oracle
+    cast "sat"), without it the tensor cast's NaN code appears (oracle cast "torch"); both bit-exact."""
+    ops = _ops()
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((64, 256)).astype(np.float32)
+    x[3, 32:48] *= 40.0                                  # one block far beyond the amax below
+    xt = torch.from_numpy(x).to(torch.bfloat16)
+    xf = xt.float().numpy()
+    amax = np.float32(3.0)
+    for sat, cast in ((True, "sat"), (False, "torch")):
+        packed, scales, s2 = ops.nvfp4_quantize(xt.cuda(), amax=torch.tensor(amax), saturate_scales=sat)
+        want_p, want_s, want_s2 = qo.nvfp4_quantize(xf, 16, amax=amax, cast=cast)
+        assert np.array_equal(scales.view(torch.uint8).cpu().numpy(), want_s)
+        assert np.float32(s2.item()) == want_s2
+        ok = (want_s & 0x7F) != 0x7F                     # codes of a NaN-scaled block are unspecified
+        assert np.array_equal(packed.cpu().numpy().reshape(64, 16, 8)[ok], want_p.reshape(64, 16, 8)[ok])
+    assert ((want_s & 0x7F) == 0x7F).sum() >= 1          # the torch cast did produce the NaN code
