@@ -131,6 +131,16 @@ __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+
 struct QEpilogue {
   const float* alpha0;   // output scale = *alpha0 * (alpha1 ? *alpha1 : 1)
   const float* alpha1;
@@ -181,12 +191,20 @@ __device__ __forceinline__ void q_store_chunk(const QEpilogue& ep, const uint32_
   __syncwarp();
 }
 
-template <int KIND, int BN, int MT>
+// KSPLIT: the two CTAs of a cluster (1, 1, 2) each sum half of the K blocks of one tile; CTA 1 hands
+// its fp32 accumulator to CTA 0 through distributed shared memory and CTA 0 adds (own + partner, a
+// fixed order) and runs the epilogue.  For shapes with fewer tiles than SMs and a long K.
+template <int KIND, int BN, int MT, bool KSPLIT>
 __global__ void __launch_bounds__(QCfg<KIND, BN, MT>::kThreads, QCfg<KIND, BN, MT>::kCtasPerSm)
 qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
              const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, int64_t M, int64_t N,
-             int num_k_blocks, QEpilogue ep, uint32_t* __restrict__ status) {
+             int total_k_blocks, QEpilogue ep, uint32_t* __restrict__ status) {
   using Cfg = QCfg<KIND, BN, MT>;
+  static_assert(!KSPLIT || (BN == 128 && MT == 1), "the partner's 128 x 128 fp32 tile must fit in the idle ring");
+  const int krank = KSPLIT ? static_cast<int>(blockIdx.z) : 0;
+  const int kb_first_half = KSPLIT ? (total_k_blocks + 1) / 2 : total_k_blocks;
+  const int kb0 = krank * kb_first_half;
+  const int num_k_blocks = krank ? total_k_blocks - kb_first_half : kb_first_half;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kStageBytes = Cfg::kStageBytes, kTmemCols = Cfg::kTmemCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -221,7 +239,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      const int64_t sf_tiles_k = static_cast<int64_t>(num_k_blocks) * 4;   // scale tiles per 128 rows
+      const int64_t sf_tiles_k = static_cast<int64_t>(total_k_blocks) * 4;   // scale tiles per 128 rows
       // scale tiles past the last one are not read (their rows lie beyond M or N and are never stored)
       int b_tiles = Cfg::kBTiles;
       if (sfb_tile0 + b_tiles > sfb_tiles_total) b_tiles = static_cast<int>(sfb_tiles_total - sfb_tile0);
@@ -247,20 +265,20 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
             if (mt < a_tiles)
-              bulk_load(sa + mt * 4 * kQSfTile, sfa + ((m0 / 128 + mt) * sf_tiles_k + kb * 4) * kQSfTile,
+              bulk_load(sa + mt * 4 * kQSfTile, sfa + ((m0 / 128 + mt) * sf_tiles_k + (kb0 + kb) * 4) * kQSfTile,
                         4 * kQSfTile, sf_bar);
 #pragma unroll
           for (int t = 0; t < Cfg::kBTiles; ++t)
             if (t < b_tiles)
-              bulk_load(sa + Cfg::kSfA + t * 4 * kQSfTile, sfb + ((sfb_tile0 + t) * sf_tiles_k + kb * 4) * kQSfTile,
+              bulk_load(sa + Cfg::kSfA + t * 4 * kQSfTile, sfb + ((sfb_tile0 + t) * sf_tiles_k + (kb0 + kb) * 4) * kQSfTile,
                         4 * kQSfTile, sf_bar);
         } else {
           mbar_expect_tx(&sm->full[s], kStageBytes);
         }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          tma_load_2d(a + mt * Cfg::kTileA, &map_a, &sm->full[s], kb * kQKBytes, m0 + mt * kQM);
-        tma_load_2d(a + MT * Cfg::kTileA, &map_b, &sm->full[s], kb * kQKBytes, n0);
+          tma_load_2d(a + mt * Cfg::kTileA, &map_a, &sm->full[s], (kb0 + kb) * kQKBytes, m0 + mt * kQM);
+        tma_load_2d(a + MT * Cfg::kTileA, &map_b, &sm->full[s], (kb0 + kb) * kQKBytes, n0);
       }
     }
   } else if (warp == 1) {
@@ -347,9 +365,28 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     }
     const bool ok = mbar_wait_bounded(&sm->accum, 0, &sm->abort, status, kQErrEpilogueWait);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
+    constexpr uint32_t kXPitch = BN * 4 + 16;                      // KSPLIT: a row of the partner's fp32 tile
+    constexpr uint32_t kXBytes = KSPLIT ? kQM * kXPitch : 0;
+    if constexpr (KSPLIT) {
+      cluster_sync_all();     // both accumulators are complete and both rings idle
+      if (krank == 1 && ok) {
+        // this CTA's accumulator rows into CTA 0's ring: lane = row, 128 contiguous bytes per piece
+        const uint32_t remote = map_to_cta(ring + (quarter * 32 + lane) * kXPitch, 0);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t acc[32];
+          tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, acc);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote + c * 128 + v * 16),
+                         "r"(acc[4 * v]), "r"(acc[4 * v + 1]), "r"(acc[4 * v + 2]), "r"(acc[4 * v + 3]) : "memory");
+        }
+      }
+      cluster_sync_all();     // the partner's tile has arrived (release / acquire at cluster scope)
+    }
+    if (ok && krank == 0) {
       // every load of the ring has been consumed by now: its first bytes serve as staging space
-      uint8_t* stage = ring + (warp - 2) * 32 * kQEpiPitch;
+      uint8_t* stage = ring + kXBytes + (warp - 2) * 32 * kQEpiPitch;
       const float alpha = __ldg(ep.alpha0) * (ep.alpha1 ? __ldg(ep.alpha1) : 1.f);
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
@@ -361,12 +398,26 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           if (col0 >= N) break;                                            // warp-uniform
           uint32_t acc[32];
           tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);   // whole warp
+          if constexpr (KSPLIT) {
+            const uint4* part = reinterpret_cast<const uint4*>(ring + (quarter * 32 + lane) * kXPitch + c * 128);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              const uint4 p = part[v];
+              acc[4 * v] = __float_as_uint(__uint_as_float(acc[4 * v]) + __uint_as_float(p.x));
+              acc[4 * v + 1] = __float_as_uint(__uint_as_float(acc[4 * v + 1]) + __uint_as_float(p.y));
+              acc[4 * v + 2] = __float_as_uint(__uint_as_float(acc[4 * v + 2]) + __uint_as_float(p.z));
+              acc[4 * v + 3] = __float_as_uint(__uint_as_float(acc[4 * v + 3]) + __uint_as_float(p.w));
+            }
+          }
           if (ep.dtype == B200Q_BF16) q_store_chunk<__nv_bfloat16>(ep, acc, alpha, stage, lane, row0, M, N, col0);
           else if (ep.dtype == B200Q_F16) q_store_chunk<__half>(ep, acc, alpha, stage, lane, row0, M, N, col0);
           else q_store_chunk<float>(ep, acc, alpha, stage, lane, row0, M, N, col0);
         }
       }
     }
+  }
+  if constexpr (KSPLIT) {
+    if (warp < 2) { cluster_sync_all(); cluster_sync_all(); }   // the producer and MMA warps keep the two cluster barriers whole
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -422,11 +473,43 @@ static int qgemm_launch_tile(const uint8_t* a, const uint8_t* b, const uint8_t* 
   if (!make_byte_map(&map_a, a, m, kbytes, kQM) || !make_byte_map(&map_b, b, n, kbytes, BN)) return B200Q_ERR_CUDA;
   const int num_k_blocks = static_cast<int>((kbytes + kQKBytes - 1) / kQKBytes);
   const size_t smem = Cfg::kStages * Cfg::kStageBytes + sizeof(QGemmSmem) + 1024;
-  if (cudaFuncSetAttribute(qgemm_kernel<KIND, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (cudaFuncSetAttribute(qgemm_kernel<KIND, BN, MT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return B200Q_ERR_CUDA;
   dim3 grid(static_cast<unsigned>(mtiles), static_cast<unsigned>(ntiles));
-  qgemm_kernel<KIND, BN, MT><<<grid, Cfg::kThreads, smem, st>>>(map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep, status);
+  qgemm_kernel<KIND, BN, MT, false><<<grid, Cfg::kThreads, smem, st>>>(map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep,
+                                                                       status);
+  return launch_status();
+}
+
+// 128 x 128 tiles with the K extent shared by the two CTAs of a cluster
+template <int KIND>
+static int qgemm_launch_ksplit(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
+                               int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
+  using Cfg = QCfg<KIND, 128, 1>;
+  const int64_t mtiles = (m + kQM - 1) / kQM, ntiles = (n + 127) / 128;
+  if (ntiles > 65535) return B200Q_ERR_UNSUPPORTED;
+  CUtensorMap map_a, map_b;
+  if (!make_byte_map(&map_a, a, m, kbytes, kQM) || !make_byte_map(&map_b, b, n, kbytes, 128)) return B200Q_ERR_CUDA;
+  const int num_k_blocks = static_cast<int>((kbytes + kQKBytes - 1) / kQKBytes);
+  const size_t smem = Cfg::kStages * Cfg::kStageBytes + sizeof(QGemmSmem) + 1024;
+  auto kern = qgemm_kernel<KIND, 128, 1, true>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return B200Q_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(mtiles), static_cast<unsigned>(ntiles), 2);
+  cfg.blockDim = dim3(Cfg::kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 2;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, map_a, map_b, sfa, sfb, m, n, num_k_blocks, ep, status) != cudaSuccess) {
+    cudaGetLastError();
+    return B200Q_ERR_CUDA;
+  }
   return launch_status();
 }
 
@@ -434,7 +517,8 @@ static int qgemm_launch_tile(const uint8_t* a, const uint8_t* b, const uint8_t* 
 // gives every SM two tiles or more, else 128 x 256 while 0.4 tiles per SM or more remain, else
 // 128 x 128 on two CTAs per SM.  NVFP4: 128 x 256 under the same condition, else 128 x 128;
 // 256 x 192 (384 accumulator columns + the block scales, scale copies by tcgen05.cp) is kept for
-// the override.  B200Q_QGEMM_TILE = "128", "256" (128 x 256) or "big" forces one.
+// the override.  B200Q_QGEMM_TILE = "128", "256" (128 x 256), "big" or "k2" (128 x 128 with the K
+// extent shared by a cluster of two CTAs) forces one.
 template <int KIND>
 static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
                         int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
@@ -448,11 +532,17 @@ static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
   } else if (mt128 * ((n + 255) / 256) * 10 >= sms * 4) {
     choice = 256;
   }
-  if (const char* e = getenv("B200Q_QGEMM_TILE")) {
+  // no more 128 x 128 tiles than SMs and a long K (80 blocks of 128 bytes or more, from measurements on
+  // 128..512 x 4096..8192 x 8192..28672): two CTAs per tile, each summing half of K
+  const int64_t kblocks = (kbytes + kQKBytes - 1) / kQKBytes;
+  bool ksplit = mt128 * ((n + 127) / 128) <= sms && kblocks >= 80;
+  if (const char* e = getenv("B200Q_QGEMM_TILE"); e && e[0]) {
+    ksplit = e[0] == 'k' && kblocks >= 2;
     if (e[0] == 'b') choice = 512;
     else if (atoi(e) == 128) choice = 128;
     else if (atoi(e) == 256) choice = 256;
   }
+  if (ksplit) return qgemm_launch_ksplit<KIND>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
   if (choice == 512) return qgemm_launch_tile<KIND, kBigN, 2>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
   if (choice == 256) return qgemm_launch_tile<KIND, 256, 1>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
   return qgemm_launch_tile<KIND, 128, 1>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);

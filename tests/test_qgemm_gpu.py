@@ -75,12 +75,14 @@ def test_fp8_gemm_tile_choices_agree(monkeypatch):
     ops = _ops()
     a8, b8, sa, sb, _ = _fp8_case(300, 520, 768, 5, torch.bfloat16, False)
     outs = []
-    for tile in ("128", "256", "big"):
+    for tile in ("128", "256", "big", "k2"):
         monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
         outs.append(ops.fp8_gemm(torch.from_numpy(a8).cuda(), torch.from_numpy(b8).cuda(), torch.tensor(sa),
-                                 torch.tensor(sb)))
+                                 torch.tensor(sb), None, torch.float32))
     ops.check_qgemm_status("cuda")
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])     # same K order: identical sums
+    # two half sums added once: equal to fp32 rounding of the different summation order
+    assert torch.allclose(outs[3], outs[0], rtol=1e-5, atol=1e-5 * float(outs[0].abs().max()))
 
 
 def test_fp8_gemm_integer_inputs_are_exact():
@@ -125,7 +127,7 @@ def test_nvfp4_gemm_matches_float64_sum(m, n, k):
     _check(got, ref, absdot, f"nvfp4 oracle {m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("tile", ["128", "256", "big"])
+@pytest.mark.parametrize("tile", ["128", "256", "big", "k2"])
 def test_nvfp4_gemm_exact_on_exactly_representable_products(tile, monkeypatch):
     """Codes in {0, +-1, +-2} with power-of-two block scales: every partial sum is an integer multiple
     of a power of two well inside fp32, so the kernel must reproduce the sum exactly; this pins the
@@ -310,3 +312,34 @@ def test_nvfp4_quantize_saturating_scales_for_data_beyond_the_amax():
         ok = (want_s & 0x7F) != 0x7F                     # codes of a NaN-scaled block are unspecified
         assert np.array_equal(packed.cpu().numpy().reshape(64, 16, 8)[ok], want_p.reshape(64, 16, 8)[ok])
     assert ((want_s & 0x7F) == 0x7F).sum() >= 1          # the torch cast did produce the NaN code
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 1024, 4096 + 256), (100, 520, 2048), (128, 128, 256)])
+def test_gemm_k_split_over_a_cluster_matches(m, n, k, monkeypatch):
+    """The cluster K-split (two CTAs per tile, partner's tile through distributed shared memory)
+    against the single-CTA result, FP8 and NVFP4, ragged tiles and an odd number of K blocks; exact
+    integer data must come out exactly."""
+    ops = _ops()
+    rng = np.random.default_rng(k)
+    a8 = qo.e4m3_encode(rng.standard_normal((m, k)).astype(np.float32), "torch")
+    b8 = qo.e4m3_encode(rng.standard_normal((n, k)).astype(np.float32), "torch")
+    _, a4, sfa, _ = _nvfp4_operand(rng, m, k)
+    _, b4, sfb, _ = _nvfp4_operand(rng, n, k)
+    dev = lambda t: torch.from_numpy(t).cuda()  # noqa: E731
+    one = torch.tensor(1.0)
+    res = {}
+    for tile in ("128", "k2"):
+        monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
+        res[tile] = (ops.fp8_gemm(dev(a8), dev(b8), one, one, None, torch.float32),
+                     ops.nvfp4_gemm(dev(a4), ops.nvfp4_swizzle_scales(dev(sfa)), dev(b4),
+                                    ops.nvfp4_swizzle_scales(dev(sfb)), one, None, torch.float32))
+    ops.check_qgemm_status("cuda")
+    for i in range(2):
+        ref, got = res["128"][i], res["k2"][i]
+        assert torch.allclose(got, ref, rtol=2e-5, atol=2e-5 * float(ref.abs().max()))
+    ai = rng.integers(-3, 4, size=(m, k)).astype(np.float32)
+    bi = rng.integers(-3, 4, size=(n, k)).astype(np.float32)
+    got = ops.fp8_gemm(torch.from_numpy(ai).cuda().to(torch.float8_e4m3fn), torch.from_numpy(bi).cuda().to(torch.float8_e4m3fn),
+                       one, one, None, torch.float32)
+    ops.check_qgemm_status("cuda")
+    assert np.array_equal(got.cpu().numpy(), ai @ bi.T)
