@@ -4,3 +4,4 @@ from .gemm_registry import (disable_real_quant_gemm, enable_real_quant_gemm, gem
                             is_real_quant_gemm_enabled)
 from .fp8_per_tensor_gemm import Fp8PerTensorLinear, fp8_per_tensor_gemm  # noqa: F401
 from .nvfp4_gemm import Nvfp4Linear, nvfp4_gemm  # noqa: F401
+from ..ops import check_qgemm_status as check_gemm_status, qgemm_status as gemm_status  # noqa: F401,E402

@@ -3,7 +3,10 @@ modelopt/torch/quantization/backends/gemm_registry.py:31-156).
 
 An entry is a GEMM callable ``f(module, input, weight, bias, *args, **kwargs)`` plus a predicate
 ``check(module, input, args, kwargs)``; a ``RealQuantLinear`` asks the registry once for the first
-entry whose predicate accepts it and keeps the answer."""
+entry whose predicate accepts it and keeps the answer.
+
+The tensor-core kernels never synchronise: error bits of their bounded device-side waits collect in
+a per-device status word, which ``backends.check_gemm_status(device)`` reads (and raises on)."""
 from __future__ import annotations
 
 from typing import Callable
