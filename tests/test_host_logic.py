@@ -341,3 +341,40 @@ def test_modelopt_state_restores_structure_on_cpu(name):
     with pytest.raises(KeyError):
         bad = dict(ckpt["modelopt"], quantizer_state={"no.such.quantizer": {}})
         mtq.restore_from_modelopt_state(MLP(), bad)
+
+
+def test_gemm_registry_and_real_quant_switches_on_cpu():
+    """Host logic of the GEMM back ends: registration order, enable / disable marks, and the
+    availability checks refusing what they cannot run (CPU tensors, other formats)."""
+    from b200q import backends
+    from b200q.backends.gemm_registry import GEMMRegistry
+    from b200q.backends.fp8_per_tensor_gemm import _fp8_availability_check
+    from b200q.backends.nvfp4_gemm import _nvfp4_availability_check
+
+    assert backends.Fp8PerTensorLinear.apply in backends.gemm_registry
+    assert backends.Nvfp4Linear.apply in backends.gemm_registry
+    reg = GEMMRegistry()
+    f = lambda *a, **k: "f"  # noqa: E731
+    g = lambda *a, **k: "g"  # noqa: E731
+    reg.register(f, lambda module, input, args, kwargs: input.shape[-1] == 8)
+    reg.register(g)                                        # no predicate: always available
+    assert reg.find_match(None, torch.zeros(2, 8)) is f and reg.find_match(None, torch.zeros(2, 4)) is g
+    reg.unregister(f)
+    assert f not in reg and reg.find_match(None, torch.zeros(2, 8)) is g
+
+    m = MLP()
+    mtq.replace_quant_module(m)
+    mtq.set_quantizer_by_cfg(m, mtq.FP8_DEFAULT_CFG["quant_cfg"])
+    assert not backends.is_real_quant_gemm_enabled(m)
+    backends.enable_real_quant_gemm(m)
+    assert m.up_proj._use_real_quant_gemm and not hasattr(m.lm_head, "_use_real_quant_gemm")   # lm_head quantisers are off
+    assert backends.is_real_quant_gemm_enabled(m)
+    backends.disable_real_quant_gemm(m)
+    assert not backends.is_real_quant_gemm_enabled(m)
+    x = torch.zeros(4, 32)
+    assert not _fp8_availability_check(m.up_proj, x, (), {})       # CPU input, not a RealQuantLinear
+    assert not _nvfp4_availability_check(m.up_proj, x, (), {})
+    # a QuantLinear ignores the mark: its forward is the fake-quant path (disabled here -> plain linear)
+    mtq.disable_quantizer(m, "*")
+    backends.enable_real_quant_gemm(m)
+    assert torch.equal(m.up_proj(x), torch.nn.functional.linear(x, m.up_proj.weight))
