@@ -3,7 +3,8 @@
  *
  * Every entry point takes plain device pointers and sizes, launches on the CUDA stream it is
  * given (a cudaStream_t passed as void*; NULL = legacy default stream), allocates nothing and
- * never synchronises.  The return value is B200Q_OK (0) or a negative b200q_status; on an
+ * never synchronises (one exception, stated there: b200q_nvfp4_group_quantize_noalloc copies a
+ * small table from pageable host memory).  The return value is B200Q_OK (0) or a negative b200q_status; on an
  * error nothing has been launched.  Pointers must be 16-byte aligned unless stated otherwise.
  *
  * The comment above each declaration names the interface of the reference (ModelOpt 0.40,
@@ -165,10 +166,17 @@ int b200q_nvfp4_group_quantize(const b200q_nvfp4_desc* descs, int n, int64_t tot
  *               pointers the caller owns), amax and tile_begin are ignored.
  *   n:          at most b200q_nvfp4_group_max_tensors_noalloc() (1024); more is refused with
  *               B200Q_ERR_CAPACITY and nothing is launched.
- * The first call made on a device looks up the array's device address; make that call before any
- * stream capture begins.  All calls on a device share the one array: the table is rewritten and
- * the abs-max slots cleared by every call, and two calls whose GPU work overlaps (different
- * streams, different threads) race on it — serialise them. */
+ * The first call made on a device looks up the array's device address (and keeps it for the life
+ * of the process; after a cudaDeviceReset by the host application the next call asks again when its
+ * first copy fails).  Make that first call before any stream capture begins anywhere in the
+ * process.  The entry point itself must not be called on a capturing stream: the table is copied
+ * from a buffer in the callee's stack frame, which a captured copy would outlive, so a capturing
+ * stream is refused with B200Q_ERR_UNSUPPORTED before anything is enqueued.  Unlike the other entry
+ * points this one may wait on the stream: the table goes to the device in chunks of 64
+ * descriptors from pageable memory, and the runtime stages such a copy before it returns.
+ * All calls on a device share the one array: the table is rewritten and the abs-max slots cleared
+ * by every call, and two calls whose GPU work overlaps (different streams, different threads)
+ * race on it — serialise them. */
 int b200q_nvfp4_group_quantize_noalloc(const b200q_nvfp4_desc* host_descs, int n, int dtype,
                                        void* stream);
 int b200q_nvfp4_group_max_tensors_noalloc(void);
@@ -342,6 +350,13 @@ int b200q_mxfp4_quantize(const void* x, int64_t nblocks, int block, int dtype, u
 int b200q_fp8_gemm(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
                    const void* bias, void* out, int64_t m, int64_t n, int64_t k, int dtype,
                    uint32_t* status_io, void* stream);
+
+/* Test and tuning switch of b200q_fp8_gemm / b200q_nvfp4_gemm (no counterpart in the reference):
+ * forces the CTA tile of every later launch in the process — 128 (128 x 128), 256 (128 x 256),
+ * 512 (the largest tile) or 2 (128 x 128 with K shared by a cluster of two CTAs); 0 restores the
+ * automatic choice.  Other values are ignored.  Returns the previous setting.  Not synchronised
+ * with concurrent launches from other threads. */
+int b200q_qgemm_tile_override(int tile);
 
 /* The activation (or weight) operand of b200q_fp8_gemm: q = e4m3(clamp(x / *scale, -448, 448)),
  * *scale a device fp32 scalar, n elements.  round_quotient != 0 rounds the quotient to T before the

@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],
     "b200q_fp8_gemm": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
+    "b200q_qgemm_tile_override": [_i],
     "b200q_fp8_gemm_operand": [_p, _p, _p, _i64, _i, _i, _p],
     "b200q_nvfp4_gemm": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
     "b200q_nvfp4_swizzle_scales": [_p, _p, _i64, _i64, _p],
@@ -71,7 +72,7 @@ SIGNATURES = {
 }
 _RESTYPES = {"b200q_strerror": C.c_char_p}
 _NO_STATUS = {"b200q_strerror", "b200q_version", "b200q_sm_count", "b200q_nvfp4_group_tile_elems",
-              "b200q_nvfp4_group_max_tensors_noalloc"}
+              "b200q_nvfp4_group_max_tensors_noalloc", "b200q_qgemm_tile_override"}
 
 
 def _load() -> C.CDLL:

@@ -561,14 +561,18 @@ constexpr size_t kNoAllocBytes = kNoAllocAmaxOffset + sizeof(float) * kNoAllocMa
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 constexpr int kMaxDevices = 64;
+constexpr int kNoAllocChunk = 64;                          // descriptors staged per host-to-device copy
 static unsigned char* g_noalloc_ptr[kMaxDevices] = {};   // device address of the array, per device
 
 // Device address of the scratch array on the current device (looked up on the first call made
-// with that device current; a benign race between threads stores the same value twice).
-static int noalloc_scratch(unsigned char** out) {
+// with that device current; a benign race between threads stores the same value twice).  The
+// address is cached for the life of the process; `refresh` asks the runtime again (used once when a
+// copy into the cached address fails, which is what a host application's cudaDeviceReset between
+// two calls leads to).
+static int noalloc_scratch(unsigned char** out, bool refresh) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200Q_ERR_CUDA;
-  if (g_noalloc_ptr[dev] == nullptr) {
+  if (refresh || g_noalloc_ptr[dev] == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return B200Q_ERR_CUDA;
     g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
@@ -587,29 +591,55 @@ extern "C" int b200q_nvfp4_group_quantize_noalloc(const b200q_nvfp4_desc* host_d
   B200Q_REQUIRE_DTYPE(dtype);
   if (n <= 0) return B200Q_ERR_SHAPE;
   if (n > kNoAllocMaxTensors) return B200Q_ERR_CAPACITY;
-  unsigned char* scratch = nullptr;
-  if (int e = noalloc_scratch(&scratch)) return e;
-  b200q_nvfp4_desc* d_descs = reinterpret_cast<b200q_nvfp4_desc*>(scratch);
-  float* d_amax = reinterpret_cast<float*>(scratch + kNoAllocAmaxOffset);
-
-  // host copy of the table on the stack: abs-max slots redirected into the scratch, tiles numbered
-  b200q_nvfp4_desc table[kNoAllocMaxTensors];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The table travels from a buffer in this function's frame: a captured copy would keep a pointer
+  // into a frame that is gone when the graph replays, so a capturing stream is refused outright.
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess) { cudaGetLastError(); return B200Q_ERR_CUDA; }
+  if (capturing != cudaStreamCaptureStatusNone) return B200Q_ERR_UNSUPPORTED;
+  // everything is validated before anything is enqueued
   int64_t tiles = 0;
   for (int i = 0; i < n; ++i) {
-    table[i] = host_descs[i];
-    if (table[i].x == nullptr || table[i].packed == nullptr) return B200Q_ERR_NULL;
-    if (table[i].nblocks <= 0) return B200Q_ERR_SHAPE;
-    if ((reinterpret_cast<uintptr_t>(table[i].x) & 31u) || (reinterpret_cast<uintptr_t>(table[i].packed) & 7u))
-      return B200Q_ERR_ALIGN;
-    table[i].amax = d_amax + i;
-    table[i].tile_begin = tiles;
-    tiles += (table[i].nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
+    const b200q_nvfp4_desc& d = host_descs[i];
+    if (d.x == nullptr || d.packed == nullptr) return B200Q_ERR_NULL;
+    if (d.nblocks <= 0) return B200Q_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(d.x) & 31u) || (reinterpret_cast<uintptr_t>(d.packed) & 7u)) return B200Q_ERR_ALIGN;
+    tiles += (d.nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
   }
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // The array keeps whatever the previous call left: the table is overwritten and the abs-max
-  // slots, which the first kernel only ever raises, are cleared.
-  if (cudaMemcpyAsync(d_descs, table, sizeof(b200q_nvfp4_desc) * n, cudaMemcpyHostToDevice, s) != cudaSuccess)
-    return B200Q_ERR_CUDA;
+  unsigned char* scratch = nullptr;
+  if (int e = noalloc_scratch(&scratch, false)) return e;
+
+  // The table is staged through a small buffer in this frame (3.5 KB, so a worker thread with a
+  // small stack can call this), kNoAllocChunk descriptors per copy: abs-max slots redirected into
+  // the scratch, tiles numbered.  The buffer is pageable host memory, so cudaMemcpyAsync returns
+  // only after the runtime has taken its own copy of it (which is what makes reusing the buffer for
+  // the next chunk safe) and may wait for earlier work of the stream to do so.
+  b200q_nvfp4_desc chunk[kNoAllocChunk];
+  int64_t tile_begin = 0;
+  for (int c0 = 0; c0 < n; c0 += kNoAllocChunk) {
+    const int cn = n - c0 < kNoAllocChunk ? n - c0 : kNoAllocChunk;
+    const int64_t chunk_tile_begin = tile_begin;
+    for (int attempt = 0;; ++attempt) {
+      float* d_amax = reinterpret_cast<float*>(scratch + kNoAllocAmaxOffset);
+      tile_begin = chunk_tile_begin;
+      for (int i = 0; i < cn; ++i) {
+        chunk[i] = host_descs[c0 + i];
+        chunk[i].amax = d_amax + c0 + i;
+        chunk[i].tile_begin = tile_begin;
+        tile_begin += (chunk[i].nblocks + kNvTileBlocks - 1) / kNvTileBlocks;
+      }
+      b200q_nvfp4_desc* dst = reinterpret_cast<b200q_nvfp4_desc*>(scratch) + c0;
+      if (cudaMemcpyAsync(dst, chunk, sizeof(b200q_nvfp4_desc) * cn, cudaMemcpyHostToDevice, s) == cudaSuccess) break;
+      cudaGetLastError();
+      // first chunk only: the cached address may belong to a context that was reset since
+      if (attempt > 0 || c0 > 0) return B200Q_ERR_CUDA;
+      if (int e = noalloc_scratch(&scratch, true)) return e;
+    }
+  }
+  b200q_nvfp4_desc* d_descs = reinterpret_cast<b200q_nvfp4_desc*>(scratch);
+  float* d_amax = reinterpret_cast<float*>(scratch + kNoAllocAmaxOffset);
+  // The array keeps whatever the previous call left: the table is overwritten above and the
+  // abs-max slots, which the first kernel only ever raises, are cleared here.
   if (cudaMemsetAsync(d_amax, 0, sizeof(float) * n, s) != cudaSuccess) return B200Q_ERR_CUDA;
   return B200Q_DISPATCH(dtype, [&] {
     int grid = grid_for(tiles, 1, 8);

@@ -22,7 +22,6 @@
 // Every mbarrier wait is bounded: when a wait runs out, an error bit is set in the caller's status
 // word, the CTA stops waiting anywhere else, lets its outstanding work drain, frees its TMEM and
 // returns.
-#include <cstdlib>
 
 #include "umma.cuh"
 
@@ -417,13 +416,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     }
   }
   if constexpr (KSPLIT) {
-    if (warp < 2) { cluster_sync_all(); cluster_sync_all(); }   // the producer and MMA warps keep the two cluster barriers whole
+    // the producer and MMA warps keep the two cluster barriers whole; their lanes left a one-lane
+    // loop above, and an .aligned barrier needs the warp converged
+    if (warp < 2) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (warp == 1) {
+    __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
   }
 }
@@ -517,8 +519,10 @@ static int qgemm_launch_ksplit(const uint8_t* a, const uint8_t* b, const uint8_t
 // gives every SM two tiles or more, else 128 x 256 while 0.4 tiles per SM or more remain, else
 // 128 x 128 on two CTAs per SM.  NVFP4: 128 x 256 under the same condition, else 128 x 128;
 // 256 x 192 (384 accumulator columns + the block scales, scale copies by tcgen05.cp) is kept for
-// the override.  B200Q_QGEMM_TILE = "128", "256" (128 x 256), "big" or "k2" (128 x 128 with the K
-// extent shared by a cluster of two CTAs) forces one.
+// the override: b200q_qgemm_tile_override(128 | 256 (128 x 256) | 512 ("big") | 2 (128 x 128 with
+// the K extent shared by a cluster of two CTAs)) forces one for every later launch of the process,
+// 0 returns to the automatic choice.
+static int g_qgemm_tile_override = 0;
 template <int KIND>
 static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, int64_t m,
                         int64_t n, int64_t kbytes, const QEpilogue& ep, uint32_t* status, cudaStream_t st) {
@@ -536,11 +540,9 @@ static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
   // 128..512 x 4096..8192 x 8192..28672): two CTAs per tile, each summing half of K
   const int64_t kblocks = (kbytes + kQKBytes - 1) / kQKBytes;
   bool ksplit = mt128 * ((n + 127) / 128) <= sms && kblocks >= 80;
-  if (const char* e = getenv("B200Q_QGEMM_TILE"); e && e[0]) {
-    ksplit = e[0] == 'k' && kblocks >= 2;
-    if (e[0] == 'b') choice = 512;
-    else if (atoi(e) == 128) choice = 128;
-    else if (atoi(e) == 256) choice = 256;
+  if (const int forced = g_qgemm_tile_override) {
+    ksplit = forced == 2 && kblocks >= 2;
+    if (forced == 128 || forced == 256 || forced == 512) choice = forced;
   }
   if (ksplit) return qgemm_launch_ksplit<KIND>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
   if (choice == 512) return qgemm_launch_tile<KIND, kBigN, 2>(a, b, sfa, sfb, m, n, kbytes, ep, status, st);
@@ -551,6 +553,12 @@ static int qgemm_launch(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
 }  // namespace b200q
 
 using namespace b200q;
+
+extern "C" int b200q_qgemm_tile_override(int tile) {
+  const int before = g_qgemm_tile_override;
+  if (tile == 0 || tile == 2 || tile == 128 || tile == 256 || tile == 512) g_qgemm_tile_override = tile;
+  return before;
+}
 
 extern "C" int b200q_fp8_gemm(const uint8_t* a, const uint8_t* b, const float* scale_a, const float* scale_b,
                               const void* bias, void* out, int64_t m, int64_t n, int64_t k, int dtype,

@@ -450,3 +450,48 @@ def test_affine_bias_quantization_matches_reference(mtq):
         # the bias is a mean formed in another summation order: a last-bit difference of the bias can move
         # single elements across a rounding boundary of the quantiser
         assert np.mean(np.abs(y - ref) > 1e-5) < 2e-3 and np.abs(y - ref).max() < 0.1, tag
+
+
+def test_scaled_e4m3_on_a_non_contiguous_input(mtq):
+    """Mirror of TestScaledE4M3.test_e4m3_incontiguous
+    (tests/gpu/torch/quantization/test_tensor_quant_cuda.py:129-134 of the reference): a transposed
+    view goes in, the result has its logical layout and equals the eager cast element by element."""
+    from b200q import tensor_quant
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(4, 4, device="cuda", generator=g).transpose(1, 0)
+    assert not x.is_contiguous()
+    want = x.to(torch.float8_e4m3fn).to(x.dtype)          # fp8_eager with amax 448: scale 1
+    got = tensor_quant.scaled_e4m3(x, None, None, 4, 3)
+    assert got.shape == x.shape
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+    big = torch.randn(96, 200, device="cuda", generator=g)[:, ::2].t()   # strided and transposed
+    amax = big.abs().amax()
+    ref = qo.fake_e4m3(big.contiguous().cpu().numpy(), np.float32(amax.item()), "f32")
+    assert np.array_equal(tensor_quant.scaled_e4m3(big, amax, None, 4, 3).cpu().numpy(), ref)
+
+
+def test_fake_quant_backward_is_the_straight_through_estimator(mtq):
+    """Mirror of TestScaledE4M3.test_backward (same file, :136-146): without an amax the gradient
+    passes through unchanged; with one (and pass_through_bwd=False) it is zeroed where |x| > amax
+    (FakeTensorQuantFunction / ScaledE4M3Function backward, tensor_quant.py:293-301)."""
+    from b200q import tensor_quant
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(3, 7, device="cuda", generator=g).requires_grad_()
+    labels = torch.randint(6, (3,), device="cuda", generator=g)
+    qx = tensor_quant.scaled_e4m3(x, None, None, 4, 3)
+    qx.retain_grad()
+    torch.nn.CrossEntropyLoss()(qx, labels).backward()
+    assert torch.allclose(qx.grad, x.grad)
+
+    amax = torch.tensor(0.7, device="cuda")
+    for fn, args in ((tensor_quant.scaled_e4m3, (amax, None, 4, 3)),
+                     (tensor_quant.fake_tensor_quant, (amax, None, 8, False, True))):
+        y = x.detach().clone().requires_grad_()
+        out = fn(y, *args)
+        w = torch.arange(1, 22, device="cuda", dtype=torch.float32).reshape(3, 7)
+        (out * w).sum().backward()
+        inside = (y.detach().abs() <= amax)
+        assert bool(inside.any()) and bool((~inside).any())
+        assert torch.equal(y.grad, torch.where(inside, w, torch.zeros_like(w)))

@@ -17,6 +17,24 @@ from oracle import quant_oracle as qo  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
+_TILE_CODES = {"128": 128, "256": 256, "big": 512, "k2": 2}
+
+
+def _force_tile(monkeypatch, tile):
+    """Force one CTA tile shape of the real-quant GEMMs (process-wide switch of the library)."""
+    from b200q import _cabi
+
+    _cabi.lib.b200q_qgemm_tile_override(_TILE_CODES[tile])
+
+
+@pytest.fixture(autouse=True)
+def _automatic_tile_choice_after_each_test():
+    yield
+    from b200q import _cabi
+
+    _cabi.lib.b200q_qgemm_tile_override(0)
+
+
 def _ops():
     from b200q import ops
     return ops
@@ -76,7 +94,7 @@ def test_fp8_gemm_tile_choices_agree(monkeypatch):
     a8, b8, sa, sb, _ = _fp8_case(300, 520, 768, 5, torch.bfloat16, False)
     outs = []
     for tile in ("128", "256", "big", "k2"):
-        monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
+        _force_tile(monkeypatch, tile)
         outs.append(ops.fp8_gemm(torch.from_numpy(a8).cuda(), torch.from_numpy(b8).cuda(), torch.tensor(sa),
                                  torch.tensor(sb), None, torch.float32))
     ops.check_qgemm_status("cuda")
@@ -133,7 +151,7 @@ def test_nvfp4_gemm_exact_on_exactly_representable_products(tile, monkeypatch):
     of a power of two well inside fp32, so the kernel must reproduce the sum exactly; this pins the
     nibble order, the block-to-scale mapping and the row/column order of the scale tiles."""
     ops = _ops()
-    monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
+    _force_tile(monkeypatch, tile)
     rng = np.random.default_rng(1)
     m, n, k = 300, 1000, 512                       # ragged row and column tiles for every tile shape
     codes = np.array([0, 2, 4, 10, 12], dtype=np.uint8)          # 0, 1, 2, -1, -2
@@ -329,7 +347,7 @@ def test_gemm_k_split_over_a_cluster_matches(m, n, k, monkeypatch):
     one = torch.tensor(1.0)
     res = {}
     for tile in ("128", "k2"):
-        monkeypatch.setenv("B200Q_QGEMM_TILE", tile)
+        _force_tile(monkeypatch, tile)
         res[tile] = (ops.fp8_gemm(dev(a8), dev(b8), one, one, None, torch.float32),
                      ops.nvfp4_gemm(dev(a4), ops.nvfp4_swizzle_scales(dev(sfa)), dev(b4),
                                     ops.nvfp4_swizzle_scales(dev(sfb)), one, None, torch.float32))
