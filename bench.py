@@ -578,6 +578,29 @@ def run_profile_kernels():
     print(json.dumps({"profile_kernels": "done", "gemm_status": int(status)}))
 
 
+def run_profile_awq_fused(n_alpha: int = 2):
+    """Three launches of the fused awq_lite search kernel on the BASELINE config-4 up_proj shape with
+    ``n_alpha`` candidates (about 0.3 GB on the device) — the program its ncu summary was captured from."""
+    import torch
+
+    from b200q import ops
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    m, n, k = 512, 14336, 4096
+    x = (torch.randn(m, k, generator=g, device=dev) * torch.exp(torch.randn(k, generator=g, device=dev))).bfloat16()
+    w = (torch.randn(n, k, generator=g, device=dev) * 0.02).bfloat16()
+    s = torch.exp(0.5 * torch.randn(n_alpha, k, generator=g, device=dev))
+    a_all = x.unsqueeze(0) * (1 / s).bfloat16().unsqueeze(1)
+    ref = torch.nn.functional.linear(x, w)
+    loss = torch.zeros(n_alpha, dtype=torch.float64, device=dev)
+    status = torch.zeros((), dtype=torch.int32, device=dev)
+    for _ in range(3):
+        ops.awq_search_fused(a_all, w, s.bfloat16(), ref, loss, status)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_awq_fused": "done", "status": int(status), "loss0": float(loss[0])}))
+
+
 def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
     import torch
     import torch.distributed as dist
@@ -795,9 +818,13 @@ def main():
     ap.add_argument("--batches", type=int, default=2, help="calib70b: batches per rank per layer")
     ap.add_argument("--profile-kernels", action="store_true",
                     help="run a few launches of the secondary kernels and exit (for ncu captures)")
+    ap.add_argument("--profile-awq-fused", type=int, default=0, metavar="N_ALPHA",
+                    help="run three launches of the fused awq_lite search kernel with N_ALPHA candidates and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
-    if args.profile_kernels:
+    if args.profile_awq_fused:
+        run_profile_awq_fused(args.profile_awq_fused)
+    elif args.profile_kernels:
         run_profile_kernels()
     elif args.impl == "reference":
         run_reference(args)

@@ -287,6 +287,23 @@ int b200q_awq_gemm_sqerr_splitk(const void* a, const void* b, const void* ref, i
                                 int64_t k, int splits, float* workspace, uint32_t* counters,
                                 double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* All candidates of one awq_lite search step (one layer, one calibration batch) in one persistent
+ * launch on the tensor cores, with the weight-side producer fused into the GEMM's operand path:
+ *   loss_io[a] += sum_{m,n} float(bf16(bf16(sum_k a_all[a][m,k] * fq_a(w)[n,k]) - ref[m,n]))^2
+ *   fq_a(w) = per-`block` dynamic integer fake quant (as b200q_awq_scale_fake_int) of bf16(w * s_all[a])
+ * a_all [n_alpha, m, k] = the activations times each candidate's inverse scale, w [n, k] the raw
+ * weight, s_all [n_alpha, k], ref [m, n]: all bf16 row-major; loss_io float64 [n_alpha].  The scaled
+ * and fake-quantised weight is formed in shared memory only.  block must be 128, k a multiple of
+ * 128, n a multiple of 32 (other requests return B200Q_ERR_UNSUPPORTED); m is free.  c_out (fp32
+ * [n_alpha, m, n], may be NULL) receives the products.  *status_io (device word, caller zeroes it)
+ * receives error bits if a bounded wait inside the kernel ran out.  Replaces, for every alpha of
+ * the grid at once, the body of the patched forward of awq_lite
+ * (modelopt/torch/quantization/model_calib.py:671-685 with update_loss :623-627). */
+int b200q_awq_search_fused(const void* a_all, const void* w, const void* s_all, const void* ref,
+                           int n_alpha, int64_t m, int64_t n, int64_t k, int block, int num_bits,
+                           int is_unsigned, int narrow_range, double* loss_io, float* c_out,
+                           uint32_t* status_io, void* stream);
+
 /* NVFP4 with a block size other than 16 (any even size; NVFP4QTensor.quantize and
  * dynamic_block_quant take the block size as an argument, modelopt/torch/quantization/qtensor/
  * nvfp4_tensor.py:142-232, tensor_quant.py:158-198).  Same arithmetic and argument meaning as

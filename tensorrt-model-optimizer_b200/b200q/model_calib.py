@@ -200,6 +200,7 @@ class _AWQLiteState:
                             if module.weight.is_cuda else None)
         self.side_stream = None   # second stream and two weight-sized buffers of the pipelined search
         self.wfq_bufs = None
+        self.cand_scales = None   # (weight-side, input-side) scales of every candidate, [n_alpha, cin] each
 
 
 def _evaluate_alpha(module, st, x2d, out_actual, alpha):
@@ -230,6 +231,46 @@ def _evaluate_alpha(module, st, x2d, out_actual, alpha):
         return (acc / ref2.numel()).to(torch.float32)
     out = F.linear(xin, wfq, module.bias)
     return ops.mse_loss(out, out_actual)
+
+
+# evaluate every candidate of a batch in one persistent launch that forms the scaled, fake-quantised
+# weight in shared memory on the way into the tensor cores (``b200q_awq_search_fused``)
+FUSED_AWQ_SEARCH = True
+# bytes of scaled activations (candidates x tokens x channels) formed per launch of the fused search
+FUSED_AWQ_SEARCH_BYTES = 1 << 30
+
+
+def _search_fused(module, st, x2d, out_actual) -> bool:
+    """All candidates of one batch by the fused kernel: per launch, one elementwise multiply forms
+    the scaled activations of a group of candidates, then one kernel evaluates the whole group.
+    Same arithmetic as ``_evaluate_alpha`` (the weight side bit for bit, the product to the fp32
+    summation order); returns False when the layer is outside what the kernel covers."""
+    wq = module.weight_quantizer
+    w = module.weight
+    fast = (wq._fake_quant and isinstance(wq._num_bits, int) and st.block_size
+            and wq._block_sizes.get("type", "static") == "static")
+    x2 = x2d.reshape(-1, x2d.shape[-1])
+    ref2 = out_actual.reshape(-1, out_actual.shape[-1])
+    if not (FUSED_AWQ_SEARCH and USE_TENSOR_CORE_EVAL and fast and module.bias is None
+            and not module.input_quantizer.is_enabled and ops.awq_search_fused_supported(x2, w, st.block_size)):
+        return False
+    alphas = list(st.loss.keys())
+    if st.cand_scales is None:   # constants of the layer once the statistics are final
+        scales = torch.stack([get_scale(st.act_scale, st.weight_scale, a) for a in alphas])
+        st.cand_scales = (scales.to(w.dtype), (1 / scales).to(w.dtype))
+    w_s, x_s = st.cand_scales
+    m, k = x2.shape
+    group = max(1, min(len(alphas), FUSED_AWQ_SEARCH_BYTES // max(1, m * k * 2)))
+    accs = torch.zeros(len(alphas), dtype=torch.float64, device=w.device)
+    for g0 in range(0, len(alphas), group):
+        g1 = min(len(alphas), g0 + group)
+        a_all = x2.unsqueeze(0) * x_s[g0:g1].unsqueeze(1)
+        ops.awq_search_fused(a_all, w, w_s[g0:g1], ref2, accs[g0:g1], st.gemm_status, st.block_size,
+                             wq._num_bits, wq._unsigned, wq._narrow_range)
+    losses = (accs / ref2.numel()).to(torch.float32)
+    for i, a in enumerate(alphas):
+        st.loss[a] += losses[i]
+    return True
 
 
 # run the weight-side kernel of candidate i+1 on a second stream while the GEMM of candidate i runs
@@ -299,7 +340,7 @@ def _awq_forward(self, input, *args, **kwargs):
         if st.is_input_quantized:
             self.input_quantizer._calibrator.collect(input)
         return out_actual
-    if not _search_pipelined(self, st, input, out_actual):
+    if not _search_fused(self, st, input, out_actual) and not _search_pipelined(self, st, input, out_actual):
         for alpha in st.loss:
             st.loss[alpha] += _evaluate_alpha(self, st, input, out_actual, alpha)
     st.num_search_steps += 1

@@ -498,6 +498,34 @@ def awq_gemm_sqerr(a: torch.Tensor, b: torch.Tensor, ref: torch.Tensor, acc: tor
     return acc
 
 
+def awq_search_fused_supported(x2: torch.Tensor, w: torch.Tensor, block) -> bool:
+    """Shapes / dtype the fused all-candidates search kernel covers."""
+    return (x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x2.is_cuda and w.is_cuda and x2.dim() == 2
+            and w.dim() == 2 and block == 128 and w.shape[1] % 128 == 0 and w.shape[0] % 32 == 0
+            and x2.shape[1] == w.shape[1] and x2.shape[0] > 0)
+
+
+def awq_search_fused(a_all: torch.Tensor, w: torch.Tensor, s_all: torch.Tensor, ref: torch.Tensor,
+                     loss: torch.Tensor, status: torch.Tensor, block: int = 128, num_bits: int = 4,
+                     unsigned: bool = False, narrow_range: bool = False, c_out: torch.Tensor | None = None):
+    """loss[a] (float64) += squared bf16 error of ``a_all[a] @ fq(w * s_all[a]).T`` against ``ref`` for every
+    candidate a, in one launch (``b200q_awq_search_fused``).  a_all [n_alpha, m, k], w [n, k], s_all [n_alpha, k],
+    ref [m, n], all bf16; ``status`` an int32 device word for the kernel's bounded waits."""
+    a_all, w, s_all, ref = _prep(a_all), _prep(w), _prep(s_all), _prep(ref)
+    n_alpha, m, k = a_all.shape
+    n = w.shape[0]
+    assert w.shape == (n, k) and s_all.shape == (n_alpha, k) and ref.shape == (m, n)
+    assert a_all.dtype == w.dtype == s_all.dtype == ref.dtype == torch.bfloat16
+    assert loss.dtype == torch.float64 and loss.numel() == n_alpha and loss.is_contiguous()
+    if c_out is not None:
+        assert c_out.dtype == torch.float32 and c_out.shape == (n_alpha, m, n) and c_out.is_contiguous()
+    with torch.cuda.device(w.device):
+        call("b200q_awq_search_fused", a_all.data_ptr(), w.data_ptr(), s_all.data_ptr(), ref.data_ptr(), n_alpha,
+             m, n, k, block, num_bits, int(unsigned), int(narrow_range), loss.data_ptr(),
+             c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(w))
+    return loss
+
+
 def int4_export_pack(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """w [rows, cols], scales [rows, cols/block] (fp32 or w.dtype) -> uint8 [rows/2, cols]."""
     w = _prep(w)
