@@ -287,12 +287,21 @@ int b200q_awq_gemm_sqerr_splitk(const void* a, const void* b, const void* ref, i
                                 int64_t k, int splits, float* workspace, uint32_t* counters,
                                 double* sum_io, float* c_out, uint32_t* status_io, void* stream);
 
+/* out[a, r, :] = T(x[r, :] * s[a, :]) for a = 0 .. n_alpha - 1: the activations of an awq_lite search
+ * step under every candidate's input-side scale in one pass (x [rows, cols], s [n_alpha, cols], out
+ * [n_alpha, rows, cols], all T; cols a multiple of 8, or 4 for fp32).  Replaces the pre_quant_scale
+ * multiply of the input quantiser that the patched forward runs once per alpha
+ * (modelopt/torch/quantization/model_calib.py:671-685; nn/modules/tensor_quantizer.py:882-883). */
+int b200q_awq_scale_acts(const void* x, const void* s, void* out, int64_t rows, int64_t cols, int n_alpha,
+                         int dtype, void* stream);
+
 /* All candidates of one awq_lite search step (one layer, one calibration batch) in one persistent
  * launch on the tensor cores, with the weight-side producer fused into the GEMM's operand path:
  *   loss_io[a] += sum_{m,n} float(bf16(bf16(sum_k a_all[a][m,k] * fq_a(w)[n,k]) - ref[m,n]))^2
  *   fq_a(w) = per-`block` dynamic integer fake quant (as b200q_awq_scale_fake_int) of bf16(w * s_all[a])
  * a_all [n_alpha, m, k] = the activations times each candidate's inverse scale, w [n, k] the raw
- * weight, s_all [n_alpha, k], ref [m, n]: all bf16 row-major; loss_io float64 [n_alpha].  The scaled
+ * weight (32-byte aligned), s_all [n_alpha, k], ref [m, n]: all bf16 row-major; loss_io float64
+ * [n_alpha].  The scaled
  * and fake-quantised weight is formed in shared memory only.  block must be 128, k a multiple of
  * 128, n a multiple of 32 (other requests return B200Q_ERR_UNSUPPORTED); m is free.  c_out (fp32
  * [n_alpha, m, n], may be NULL) receives the products.  *status_io (device word, caller zeroes it)

@@ -55,6 +55,7 @@ SIGNATURES = {
     "b200q_awq_scale_fake_int": [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _i, _p],
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],
+    "b200q_awq_scale_acts": [_p, _p, _p, _i64, _i64, _i, _i, _p],
     "b200q_awq_search_fused": [_p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p],
     "b200q_fp8_gemm": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
     "b200q_qgemm_tile_override": [_i],

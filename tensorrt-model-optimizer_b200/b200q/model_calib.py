@@ -264,7 +264,7 @@ def _search_fused(module, st, x2d, out_actual) -> bool:
     accs = torch.zeros(len(alphas), dtype=torch.float64, device=w.device)
     for g0 in range(0, len(alphas), group):
         g1 = min(len(alphas), g0 + group)
-        a_all = x2.unsqueeze(0) * x_s[g0:g1].unsqueeze(1)
+        a_all = ops.awq_scale_acts(x2, x_s[g0:g1])
         ops.awq_search_fused(a_all, w, w_s[g0:g1], ref2, accs[g0:g1], st.gemm_status, st.block_size,
                              wq._num_bits, wq._unsigned, wq._narrow_range)
     losses = (accs / ref2.numel()).to(torch.float32)

@@ -498,6 +498,19 @@ def awq_gemm_sqerr(a: torch.Tensor, b: torch.Tensor, ref: torch.Tensor, acc: tor
     return acc
 
 
+def awq_scale_acts(x2: torch.Tensor, s_all: torch.Tensor) -> torch.Tensor:
+    """[n_alpha, rows, cols] = x2[None] * s_all[:, None] in x2's dtype, one pass (``b200q_awq_scale_acts``)."""
+    x2, s_all = _prep(x2), _prep(s_all.to(x2.dtype))
+    rows, cols = x2.shape
+    n_alpha = s_all.shape[0]
+    assert s_all.shape == (n_alpha, cols)
+    out = torch.empty((n_alpha, rows, cols), dtype=x2.dtype, device=x2.device)
+    with torch.cuda.device(x2.device):
+        call("b200q_awq_scale_acts", x2.data_ptr(), s_all.data_ptr(), out.data_ptr(), rows, cols, n_alpha,
+             dtype_code(x2), _stream(x2))
+    return out
+
+
 def awq_search_fused_supported(x2: torch.Tensor, w: torch.Tensor, block) -> bool:
     """Shapes / dtype the fused all-candidates search kernel covers."""
     return (x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x2.is_cuda and w.is_cuda and x2.dim() == 2
@@ -511,7 +524,7 @@ def awq_search_fused(a_all: torch.Tensor, w: torch.Tensor, s_all: torch.Tensor, 
     """loss[a] (float64) += squared bf16 error of ``a_all[a] @ fq(w * s_all[a]).T`` against ``ref`` for every
     candidate a, in one launch (``b200q_awq_search_fused``).  a_all [n_alpha, m, k], w [n, k], s_all [n_alpha, k],
     ref [m, n], all bf16; ``status`` an int32 device word for the kernel's bounded waits."""
-    a_all, w, s_all, ref = _prep(a_all), _prep(w), _prep(s_all), _prep(ref)
+    a_all, w, s_all, ref = _prep(a_all), _prep(w, 32), _prep(s_all), _prep(ref)
     n_alpha, m, k = a_all.shape
     n = w.shape[0]
     assert w.shape == (n, k) and s_all.shape == (n_alpha, k) and ref.shape == (m, n)

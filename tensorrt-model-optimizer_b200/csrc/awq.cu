@@ -116,9 +116,70 @@ sq_diff_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, int64_t n, 
   }
 }
 
+// out[a, m, :] = T(x[m, :] * s[a, :]) for every candidate a: the activations of an awq_lite search step
+// under each candidate's inverse scale, written once (the read of x stays in L2 across candidates).
+// One thread per 16-byte pack of x; it keeps the pack in registers and loops over the candidates.
+template <typename T>
+__global__ void __launch_bounds__(256)
+awq_scale_acts_kernel(const T* __restrict__ x, const T* __restrict__ s, T* __restrict__ out, int64_t rows,
+                      int64_t packs_per_row, int n_alpha) {
+  pdl_prologue();
+  using E = Elem<T>;
+  constexpr int P = E::kPerPack;
+  const int64_t npack = rows * packs_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const uint4* sv = reinterpret_cast<const uint4*>(s);
+  uint4* ov = reinterpret_cast<uint4*>(out);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < npack; i += stride) {
+    const uint4 a = ld_stream(xv + i);
+    const int64_t col = i % packs_per_row;
+    for (int c = 0; c < n_alpha; ++c) {
+      const uint4 b = __ldg(sv + c * packs_per_row + col);
+      uint4 r;
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t rw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const __nv_bfloat162 pr = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&aw[k]),
+                                            *reinterpret_cast<const __nv_bfloat162*>(&bw[k]));
+          rw[k] = *reinterpret_cast<const uint32_t*>(&pr);
+        }
+        r = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+      } else {
+        float fa[P], fb[P];
+        E::unpack(a, fa);
+        E::unpack(b, fb);
+#pragma unroll
+        for (int k = 0; k < P; ++k) fa[k] = round_t<T>(fa[k] * fb[k]);
+        r = E::pack(fa);
+      }
+      st_stream(ov + c * npack + i, r);
+    }
+  }
+}
+
 }  // namespace b200q
 
 using namespace b200q;
+
+extern "C" int b200q_awq_scale_acts(const void* x, const void* s, void* out, int64_t rows, int64_t cols, int n_alpha,
+                                    int dtype, void* stream) {
+  B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(s); B200Q_REQUIRE_PTR(out);
+  B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x); B200Q_REQUIRE_ALIGNED(s); B200Q_REQUIRE_ALIGNED(out);
+  if (rows <= 0 || cols <= 0 || n_alpha <= 0) return B200Q_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return B200Q_DISPATCH(dtype, [&]() -> int {
+    constexpr int P = Elem<T>::kPerPack;
+    if (cols % P) return B200Q_ERR_SHAPE;
+    const int64_t ppr = cols / P;
+    int grid = grid_for(rows * ppr, 256, 8);
+    launch_pdl(awq_scale_acts_kernel<T>, grid, 256, 0, st, static_cast<const T*>(x), static_cast<const T*>(s),
+               static_cast<T*>(out), rows, ppr, n_alpha);
+    return launch_status();
+  });
+}
 
 extern "C" int b200q_awq_scale_fake_int(const void* w, const void* s, void* y, int64_t rows, int64_t cols,
                                         int block, int dtype, int num_bits, int is_unsigned,

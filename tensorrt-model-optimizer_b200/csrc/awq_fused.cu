@@ -14,37 +14,76 @@
 // half (128 rows) of the W slab, so per FLOP a CTA asks L2 for a quarter less than a 256 x 256
 // single-CTA tile and the W slab is fetched exactly once per candidate.
 //
-// Warps of a CTA (16):
-//   0      A producer: TMA 128 x 64 tiles into a 4-deep ring, completion counted on the EVEN CTA's barrier
-//   1      MMA issuer (even CTA only) and TMEM allocation
-//   2      W producer: TMA raw 128 x 128 weight units (two swizzled 128 x 64 boxes) and the unit's 128
-//          scale factors into a 3-deep ring
-//   4-7    epilogue: tcgen05.ld the accumulator, squared error against R, one atomic per warp and item
-//   8-15   transform, two groups of four warps taking alternate units: in shared memory, in place:
-//          bf16(W * s), block abs-max (2 lanes = one 128-block), integer fake quant, then a proxy fence
-//          and an arrival on the even CTA's "unit ready" barrier
+// Warps of a CTA (24; a warp's scheduler is its index modulo 4):
+//   0      MMA issuer (even CTA only) and TMEM allocation           } scheduler 0 carries no transform warp, so
+//   8      A producer: TMA 128 x 64 tiles into a 4-deep ring,       } these latency-critical threads do not
+//          completion counted on the EVEN CTA's barrier             } queue for issue slots behind arithmetic
+//   12     W producer: TMA raw 128 x 128 weight units (two swizzled }
+//          128 x 64 boxes) and the unit's 128 scale factors into a 3-deep ring
+//   4-7, 16-19   epilogue (two warps per TMEM lane quarter): tcgen05.ld the accumulator, squared error
+//          against R, one atomic per warp and item
+//   1-3, 9-11, 13-15, 21-23   transform (twelve warps), in shared memory, in place.  A W unit is sixteen
+//          warp-sized tasks of eight rows, taken round-robin across unit boundaries; a lane owns 32
+//          consecutive elements of one weight row (four lanes = one 128-block): bf16(W * s), the block
+//          abs-max (two shuffles), the integer fake quant, stored back where they came from in the
+//          swizzled layout the tensor core reads; then a proxy fence (generic -> async) and an arrival
+//          on the even CTA's "unit ready" barrier.
 // The MMA thread waits for "A tile landed in both CTAs" and "W unit transformed in both CTAs", issues
-// 2 x 4 MMAs per 64-wide K slice, and releases ring slots to both CTAs with tcgen05.commit.  Producers
-// and transformers run ahead into the next item while the epilogue drains the accumulator.
+// 2 x 4 MMAs per 64-wide K slice, and releases ring slots to both CTAs with tcgen05.commit.  The A
+// producer and the transformers run ahead into the next item while the epilogue drains the
+// accumulator.  Every pair starts its K loop at a different offset, so that the pairs, which all
+// read the same activations, do not ask L2 for the same lines at the same moment.
 //
 // Every wait is bounded: when one runs out, an error bit is set in the caller's status word, the CTA
 // stops waiting anywhere else, and the kernel ends through its normal exit (TMEM released).
 #include "umma.cuh"
 
+// Measurement switches (0 in the library; set when building a throw-away copy to find which stage
+// bounds the pipeline): 1 = the transform only waits, fences and arrives; 2 = the epilogue only reads
+// the accumulator; 4 = A tiles are loaded for the first ring fill only; 8 = the same for W units.
+#ifndef B200Q_FUSED_ABLATE
+#define B200Q_FUSED_ABLATE 0
+#endif
+#ifndef B200Q_FUSED_ROTATE
+#define B200Q_FUSED_ROTATE 1
+#endif
+#ifndef B200Q_FUSED_ROUND
+#define B200Q_FUSED_ROUND 1
+#endif
+
 namespace b200q {
+
+#if B200Q_FUSED_ABLATE & 16
+// timing trace of CTA 0 (throw-away builds only): c_out is reused as a buffer of clock values,
+// [role][unit][4]; roles: 0 W producer, 1 transform warp 8, 2 transform warp 12, 3 MMA (W side), 4 MMA (A side)
+#define B200Q_TRACE(role, idx, slot) \
+  do { if (blockIdx.x == 0 && (idx) < 256u) reinterpret_cast<long long*>(c_out)[((role) * 256 + (idx)) * 4 + (slot)] = clock64(); } while (0)
+#else
+#define B200Q_TRACE(role, idx, slot) do {} while (0)
+#endif
 
 constexpr int kFK = 64;                                  // K elements of one A stage: one 128-byte swizzle row
 constexpr uint32_t kFTileBytes = 128 * kFK * 2;          // 128 rows x 64 bf16 = 16 KB: one TMA box
 constexpr uint32_t kFUnitBytes = 2 * kFTileBytes;        // a W unit: 128 rows x 128 K = two boxes
 constexpr int kFPairN = 256;                             // columns of a pair's tile (128 weight rows per CTA)
-constexpr int kFWUnits = 3;
-constexpr uint32_t kFScaleBytes = 128 * 2;               // one unit's share of a candidate's scale vector
-constexpr int kFThreads = 512;
-constexpr int kFTransformWarps = 8, kFEpilogueWarps = 4;
-constexpr int kFMaxStages = 6;
+#ifndef B200Q_FUSED_WUNITS
+#define B200Q_FUSED_WUNITS 3
+#endif
+constexpr int kFWUnits = B200Q_FUSED_WUNITS;   // W unit slots: landing, being transformed, being read by the MMAs
+constexpr uint32_t kFScaleBytes = 128 * 2;     // one unit's share of a candidate's scale vector
+constexpr int kFThreads = 768;
+// Warp roles.  A warp's scheduler is its index modulo 4.  Scheduler 0 hosts the latency-critical MMA
+// issuer and the A producer and no transform warp, so that neither has to compete for issue slots
+// with the arithmetic; the twelve transform warps are 1-3, 9-11, 13-15 and 21-23, the eight epilogue
+// warps 4-7 and 16-19.
+constexpr int kFWarpMma = 0, kFWarpAProducer = 8, kFWarpWProducer = 12;
+constexpr int kFTransformCount = 12, kFOctets = 16;      // row octets (warp-sized tasks) per W unit
+constexpr int kFEpilogueWarps = 8;       // two per TMEM lane quarter (warps 4-7 and 16-19), alternate column chunks
+constexpr int kFMaxStages = 10;
 
 template <int MT> struct FusedCfg {
-  static constexpr int kAStages = MT == 2 ? 4 : 6;
+  // what the transformed-weight ring leaves of the 227 KB goes to the activation ring
+  static constexpr int kAStages = (7 - kFWUnits) * 2 / MT;
   static constexpr uint32_t kAStageBytes = MT * kFTileBytes;
   static constexpr uint32_t kRingBytes = kAStages * kAStageBytes + kFWUnits * (kFUnitBytes + kFScaleBytes);
   static constexpr uint32_t kTmemCols = MT * kFPairN;    // 512 or 256: a power of two
@@ -59,7 +98,7 @@ enum : uint32_t {
 struct FusedSmem {
   uint64_t a_full[kFMaxStages];    // even CTA's copy is the one in use: both CTAs' tiles count on it
   uint64_t a_empty[kFMaxStages];
-  uint64_t w_full[kFWUnits];       // raw unit landed (each CTA its own)
+  uint64_t w_full[kFWUnits];       // raw unit and its scale factors landed (each CTA its own)
   uint64_t b_ready[kFWUnits];      // unit transformed in both CTAs (even CTA's copy)
   uint64_t b_empty[kFWUnits];
   uint64_t acc_full;               // all MMAs of an item complete
@@ -79,10 +118,25 @@ __device__ __forceinline__ uint64_t f32x2_mul(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 __device__ __forceinline__ uint64_t f32x2_add(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 struct FusedItem {
@@ -105,7 +159,7 @@ __global__ void __launch_bounds__(kFThreads, 1)
 awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         const __nv_bfloat16* __restrict__ s_all, const __nv_bfloat16* __restrict__ ref,
                         double* __restrict__ loss, float* __restrict__ c_out, int n_alpha, int M, int N, int K,
-                        IntQ q, uint32_t* __restrict__ status) {
+                        IntQ q, float one, uint32_t* __restrict__ status) {
   using Cfg = FusedCfg<MT>;
   constexpr int SA = Cfg::kAStages, SW = kFWUnits;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -121,12 +175,15 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   const int slabs_m = (M + slab_rows - 1) / slab_rows, slabs_n = (N + kFPairN - 1) / kFPairN;
   const int num_items = n_alpha * slabs_m * slabs_n;
   const int k_slices = K / kFK;                      // K is a multiple of 128: an even count
+  const int k_units = k_slices / 2;
+  // this pair's K loop starts at unit `rot` and wraps around
+  const int rot = B200Q_FUSED_ROTATE ? static_cast<int>((static_cast<int64_t>(pair) * k_units) / num_pairs) % k_units : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SA; ++s) { mbar_init(&sm->a_full[s], 1); mbar_init(&sm->a_empty[s], 1); }
     for (int u = 0; u < SW; ++u) {
       mbar_init(&sm->w_full[u], 1);
-      mbar_init(&sm->b_ready[u], 2 * (kFTransformWarps / 2));   // one group of transform warps per unit, both CTAs
+      mbar_init(&sm->b_ready[u], 2 * kFOctets);   // one arrival per warp-sized task of the unit, both CTAs
       mbar_init(&sm->b_empty[u], 1);
     }
     mbar_init(&sm->acc_full, 1);
@@ -134,7 +191,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     sm->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // the same warp of both CTAs: one allocation for the pair
+  if (warp == kFWarpMma) {   // the same warp of both CTAs: one allocation for the pair
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(Cfg::kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
@@ -144,7 +201,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sm->tmem_base);
 
-  if (warp == 0) {
+  if (warp == kFWarpAProducer) {
     // ---------------------------------------------------------------- A producer --------------
     if (lane == 0) {
       uint32_t it = 0;
@@ -155,17 +212,22 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int row0 = w.alpha * M + w.slab_m * slab_rows + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < k_slices; ++kb, ++it) {
           const int s = it % SA;
+          B200Q_TRACE(0, it >> 1, (it & 1) * 2);
           ok = mbar_wait_bounded(&sm->a_empty[s], ((it / SA) & 1) ^ 1, &sm->abort, status, kFErrAProducer);
           if (!ok) break;
+          B200Q_TRACE(0, it >> 1, (it & 1) * 2 + 1);
+          if ((B200Q_FUSED_ABLATE & 4) && it >= static_cast<uint32_t>(SA)) continue;
           const uint32_t full_leader = map_to_cta(&sm->a_full[s], 0);
           if (leader) mbar_expect_tx(&sm->a_full[s], 2 * Cfg::kAStageBytes);      // both CTAs' tiles
           uint8_t* dst = ring_a + s * Cfg::kAStageBytes;
+          int kr = kb + 2 * rot;
+          kr -= kr >= k_slices ? k_slices : 0;
 #pragma unroll
-          for (int t = 0; t < MT; ++t) tma_load_2d_pair(dst + t * kFTileBytes, &map_a, full_leader, kb * kFK, row0 + t * 256);
+          for (int t = 0; t < MT; ++t) tma_load_2d_pair(dst + t * kFTileBytes, &map_a, full_leader, kr * kFK, row0 + t * 256);
         }
       }
     }
-  } else if (warp == 2) {
+  } else if (warp == kFWarpWProducer) {
     // ---------------------------------------------------------------- W producer --------------
     if (lane == 0) {
       uint32_t wu = 0;
@@ -174,162 +236,201 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const FusedItem w = fused_item(item, slabs_m, slabs_n);
         const int n_row = w.slab_n * kFPairN + static_cast<int>(rank) * 128;
         const __nv_bfloat16* s_row = s_all + static_cast<int64_t>(w.alpha) * K;
-        for (int ub = 0; ub < k_slices / 2; ++ub, ++wu) {
+        for (int ub = 0; ub < k_units; ++ub, ++wu) {
           const int u = wu % SW;
           ok = mbar_wait_bounded(&sm->b_empty[u], ((wu / SW) & 1) ^ 1, &sm->abort, status, kFErrWProducer);
           if (!ok) break;
+          int ur = ub + rot;
+          ur -= ur >= k_units ? k_units : 0;
           uint8_t* dst = ring_w + u * kFUnitBytes;
           mbar_expect_tx(&sm->w_full[u], kFUnitBytes + kFScaleBytes);
-          bulk_load(ring_s + u * kFScaleBytes, s_row + ub * 128, kFScaleBytes, &sm->w_full[u]);
-          tma_load_2d(dst, &map_w, &sm->w_full[u], ub * 128, n_row);
-          tma_load_2d(dst + kFTileBytes, &map_w, &sm->w_full[u], ub * 128 + kFK, n_row);
+          bulk_load(ring_s + u * kFScaleBytes, s_row + ur * 128, kFScaleBytes, &sm->w_full[u]);
+          tma_load_2d(dst, &map_w, &sm->w_full[u], ur * 128, n_row);
+          tma_load_2d(dst + kFTileBytes, &map_w, &sm->w_full[u], ur * 128 + kFK, n_row);
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == kFWarpMma) {
     // ---------------------------------------------------------------- MMA issuer --------------
     if (lane == 0 && leader) {
       uint32_t it = 0, wu = 0, done = 0;
       bool ok = true;
+      // a barrier of the odd CTA sits at the same offset of its shared memory: one address difference
+      const uint32_t peer_delta = map_to_cta(sm, 1) - smem_u32(sm);
+      auto commit_both = [&](uint64_t* bar) {   // arrives in both CTAs once the MMAs issued so far have completed
+        const uint32_t a = smem_u32(bar);
+        umma_commit_pair(a);
+        umma_commit_pair(a + peer_delta);
+      };
       for (int item = pair; item < num_items && ok; item += num_pairs, ++done) {
         if (done > 0) {   // the previous item's accumulator has been read out in both CTAs
           ok = mbar_wait_bounded_cluster(&sm->acc_empty, (done - 1) & 1, &sm->abort, status, kFErrMma);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        int u = 0;
-        for (int kb = 0; kb < k_slices; ++kb, ++it) {
-          if ((kb & 1) == 0) {
-            u = wu % SW;
-            ok = mbar_wait_bounded_cluster(&sm->b_ready[u], (wu / SW) & 1, &sm->abort, status, kFErrMma);
-            if (!ok) break;
-          }
-          const int s = it % SA;
-          ok = mbar_wait_bounded(&sm->a_full[s], (it / SA) & 1, &sm->abort, status, kFErrMma);
+        for (int ub = 0; ub < k_units && ok; ++ub, ++wu) {
+          const int u = wu % SW;
+          B200Q_TRACE(3, wu, 0);
+          ok = mbar_wait_bounded_cluster(&sm->b_ready[u], (wu / SW) & 1, &sm->abort, status, kFErrMma);
           if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(ring_a + s * Cfg::kAStageBytes);
-          const uint64_t db = umma_desc(smem_u32(ring_w + u * kFUnitBytes + (kb & 1) * kFTileBytes));
+          B200Q_TRACE(3, wu, 1);
+          const uint64_t db0 = umma_desc(smem_u32(ring_w + u * kFUnitBytes));
 #pragma unroll
-          for (int t = 0; t < MT; ++t) {
-            const uint64_t da = umma_desc(a_addr + t * kFTileBytes);
+          for (int half = 0; half < 2; ++half, ++it) {   // the unit's two 64-wide K slices
+            const int s = it % SA;
+            B200Q_TRACE(4, it >> 1, (it & 1) * 2);
+            ok = mbar_wait_bounded(&sm->a_full[s], (it / SA) & 1, &sm->abort, status, kFErrMma);
+            if (!ok) break;
+            B200Q_TRACE(4, it >> 1, (it & 1) * 2 + 1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da0 = umma_desc(smem_u32(ring_a + s * Cfg::kAStageBytes));
+            const uint64_t db = db0 + half * (kFTileBytes >> 4);
 #pragma unroll
-            for (int k = 0; k < kFK / 16; ++k)   // 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-              umma_bf16_pair(tmem + t * kFPairN, da + 2 * k, db + 2 * k, Cfg::kIdesc, (kb | k) != 0 ? 1u : 0u);
+            for (int t = 0; t < MT; ++t) {
+#pragma unroll
+              for (int k = 0; k < kFK / 16; ++k)   // 16 bf16 = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+                umma_bf16_pair(tmem + t * kFPairN, da0 + t * (kFTileBytes >> 4) + 2 * k, db + 2 * k, Cfg::kIdesc,
+                               (ub | half | k) != 0 ? 1u : 0u);
+            }
+            commit_both(&sm->a_empty[s]);   // the stage is free in both CTAs once these MMAs have read it
           }
-          // the slot is free in both CTAs once these MMAs have read it
-          umma_commit_pair(map_to_cta(&sm->a_empty[s], 0));
-          umma_commit_pair(map_to_cta(&sm->a_empty[s], 1));
-          if (kb & 1) {
-            umma_commit_pair(map_to_cta(&sm->b_empty[u], 0));
-            umma_commit_pair(map_to_cta(&sm->b_empty[u], 1));
-            ++wu;
-          }
+          if (!ok) break;
+          B200Q_TRACE(3, wu, 2);
+          commit_both(&sm->b_empty[u]);
         }
         if (!ok) break;
-        umma_commit_pair(map_to_cta(&sm->acc_full, 0));   // fires when every MMA issued above has completed
-        umma_commit_pair(map_to_cta(&sm->acc_full, 1));
+        commit_both(&sm->acc_full);   // fires when every MMA issued above has completed
       }
     }
-  } else if (warp >= 8) {
+  } else if ((warp & 3) != 0 && (warp >> 2) != 1 && (warp >> 2) != 4) {
     // ---------------------------------------------------------------- transform ---------------
-    // The eight warps form two groups of four; a group takes every other W unit, so two units are in
-    // the transform stage at a time and one group's latencies (barrier, shared-memory round trips, the
-    // proxy fence) hide under the other's arithmetic.  Within a unit a lane owns one row of one 64-wide
-    // box at a time (64 elements, 8 swizzled 16-byte chunks: chunk j of row r sits at j ^ (r & 7));
-    // lanes l and l + 16 hold the two halves of a 128-block; a warp covers 32 rows in two passes.
+    // A W unit (128 rows x 128 K) is sixteen warp-sized tasks of eight rows; the twelve transform warps
+    // take tasks round-robin across unit boundaries, so at any moment they are spread over two or three
+    // units and over all phases of a task (waiting for the unit to land, arithmetic, the fence).
+    // Lane -> quarter qd = lane >> 3 of the 128-block of one row; the eight lanes of a quarter-warp store
+    // to eight consecutive rows, i.e. eight different 16-byte positions of the 128-byte swizzle pattern
+    // (chunk j of row r sits at j ^ (r & 7)): conflict-free.
     //
     // Arithmetic, per block: v = bf16(w * s); amax = max |v|; scale = 7 / amax; out = bf16(k / scale) with
     // k = rint(v * scale).  Because the abs-max is the block's own, |v * scale| <= 7 (1 + 2^-24) and the
     // clamp to [-8, 7] never acts.  k / scale takes only 15 values per block, so instead of one exact
-    // division per element the two lanes of a block check once, for k = 1..7, that bf16(k * y) with
+    // division per element the four lanes of a block check once, for k = 1..7, that bf16(k * y) with
     // y = RN(1 / scale) equals bf16(RN(k / scale)) (it does except when k * y falls within a rounding
     // error of a bf16 tie) and then multiply; a block that fails the check, a dead or out-of-range
     // scale, or a bit width other than 4 takes the element-wise exact path.  Zeros come out as +0
     // where the stand-alone kernel keeps the sign: the product does not see the difference.
-    const int group = (warp - 8) >> 2, gw = (warp - 8) & 3, box = lane >> 4;
+    const int wq = warp >> 2;                                           // 0, 2, 3 or 5
+    const int t_id = (wq - (wq >= 2 ? 1 : 0) - (wq >= 5 ? 1 : 0)) * 3 + (warp & 3) - 1;   // 0 .. 11
+    const int qd = lane >> 3, r_in = lane & 7;
+    const int j0 = (qd & 1) * 4;                                        // first 16-byte chunk in the 64-wide box
     const bool four_bit = q.bound == 7.f && q.lo == -8.f;
+    const uint32_t my_items = static_cast<uint32_t>((num_items - pair + num_pairs - 1) / num_pairs);
+    const uint32_t units_total = my_items * static_cast<uint32_t>(k_units);
+    const uint32_t tasks_total = units_total * kFOctets;
     bool ok = true;
-    const uint32_t units_total = static_cast<uint32_t>((num_items - pair + num_pairs - 1) / num_pairs) * (k_slices / 2);
-    for (uint32_t wu = group; wu < units_total && ok; wu += 2) {
+    for (uint32_t task = t_id; task < tasks_total && ok; task += kFTransformCount) {
+      const uint32_t wu = task / kFOctets;
       const int u = wu % SW;
-      // every lane observes the barrier itself; the decision to go on is the warp's (shuffles follow)
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&sm->w_full[u], (wu / SW) & 1, &sm->abort, status, kFErrTransform));
+      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 0);
+      // the raw unit has landed: every lane observes the completed phase itself, and only when it is
+      // not there yet does lane 0 poll
+      const uint32_t parity = (wu / SW) & 1;
+      bool landed = __all_sync(0xffffffffu, mbar_try(&sm->w_full[u], parity));
+      if (!landed) {
+        landed = lane != 0 || mbar_wait_bounded(&sm->w_full[u], parity, &sm->abort, status, kFErrTransform);
+        landed = __all_sync(0xffffffffu, landed) && __all_sync(0xffffffffu, mbar_try(&sm->w_full[u], parity));
+      }
+      ok = landed;
       if (!ok) break;
-      // this lane's 64 scale factors of the unit (the lanes of a box read the same addresses: broadcast)
-      const uint4* sp = reinterpret_cast<const uint4*>(ring_s + u * kFScaleBytes + box * 128);
-#pragma unroll 1
-      for (int pass = 0; pass < 2; ++pass) {
-        const int row = gw * 32 + pass * 16 + (lane & 15), sw = row & 7;
-        uint8_t* rowp = ring_w + u * kFUnitBytes + box * kFTileBytes + row * 128;
-        uint32_t pr[32];
-        uint32_t mx = 0;
+      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 1);
+      const int row = static_cast<int>(task % kFOctets) * 8 + r_in, sw = row & 7;
+      uint8_t* dst = ring_w + u * kFUnitBytes + (qd >> 1) * kFTileBytes + row * 128;
+      uint32_t pr[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 wv = *reinterpret_cast<const uint4*>(rowp + ((j ^ sw) << 4));
+      for (int jj = 0; jj < 4; ++jj) {
+        const uint4 v = *reinterpret_cast<const uint4*>(dst + (((j0 + jj) ^ sw) << 4));
+        pr[4 * jj] = v.x; pr[4 * jj + 1] = v.y; pr[4 * jj + 2] = v.z; pr[4 * jj + 3] = v.w;
+      }
+      if (!(B200Q_FUSED_ABLATE & 1)) {
+        // this lane's 32 scale factors (the eight lanes of a quarter read the same 64 bytes: broadcast)
+        const uint4* sp = reinterpret_cast<const uint4*>(ring_s + u * kFScaleBytes + qd * 64);
+        uint32_t mx[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
           const uint4 sv = sp[j];
-          const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+          const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             // packed bf16 multiply = the product rounded to bf16, two elements per instruction
-            const __nv_bfloat162 p2 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&ww[i]),
+            const __nv_bfloat162 p2 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pr[4 * j + i]),
                                               *reinterpret_cast<const __nv_bfloat162*>(&ss[i]));
             pr[4 * j + i] = *reinterpret_cast<const uint32_t*>(&p2);
-            mx = __vmaxu2(mx, pr[4 * j + i] & 0x7fff7fffu);     // |x| patterns: integer order = magnitude order
+            mx[i] = __vmaxu2(mx[i], pr[4 * j + i] & 0x7fff7fffu);   // |x| patterns: integer order = magnitude order
           }
         }
-        uint32_t bits = max(mx & 0xffffu, mx >> 16) << 16;
+        const uint32_t m2 = __vmaxu2(__vmaxu2(mx[0], mx[1]), __vmaxu2(mx[2], mx[3]));
+        uint32_t bits = max(m2 & 0xffffu, m2 >> 16) << 16;
+        bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 8));
         bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, 16));
         const IntScale sc = make_int_scale(q, __uint_as_float(bits));
-        bool fast = four_bit && sc.live && sc.fast;
+        // this lane's share of the check: k = 2 qd + 1 and 2 qd + 2 (7 twice in the last quarter); done by
+        // every lane (a few instructions) so that the shuffles are warp-wide instructions
         const float2 y2 = make_float2(sc.y, sc.y);
-        {
-          // this lane's share of the check: k = 1..4 (first box) or 4..7 (second box); done by every
-          // lane (a few instructions) so that the shuffle below is one warp-wide instruction
-          const float k0 = box ? 4.f : 1.f;
-          const float2 nd = make_float2(-sc.scale, -sc.scale);
-          const float2 ka = make_float2(k0, k0 + 1.f), kb = make_float2(k0 + 2.f, k0 + 3.f);
-          const float2 ea = div2_rn_rcp(ka, nd, y2), eb = div2_rn_rcp(kb, nd, y2);
-          const float2 fa = __fmul2_rn(ka, y2), fb = __fmul2_rn(kb, y2);
-          const bool same = Elem<__nv_bfloat16>::pack2(ea.x, ea.y) == Elem<__nv_bfloat16>::pack2(fa.x, fa.y) &&
-                            Elem<__nv_bfloat16>::pack2(eb.x, eb.y) == Elem<__nv_bfloat16>::pack2(fb.x, fb.y);
-          const bool peer_same = __shfl_xor_sync(0xffffffffu, same ? 1 : 0, 16) != 0;
-          fast = fast && same && peer_same;      // the two lanes of a block agree: same scale, both checks
-        }
-        if (fast) {
+        const float ka = static_cast<float>(2 * qd + 1);
+        const float2 k2 = make_float2(ka, qd == 3 ? 7.f : ka + 1.f);
+        const float2 e2 = div2_rn_rcp(k2, make_float2(-sc.scale, -sc.scale), y2), f2 = __fmul2_rn(k2, y2);
+        uint32_t same = Elem<__nv_bfloat16>::pack2(e2.x, e2.y) == Elem<__nv_bfloat16>::pack2(f2.x, f2.y) ? 1u : 0u;
+        same &= __shfl_xor_sync(0xffffffffu, same, 8);
+        same &= __shfl_xor_sync(0xffffffffu, same, 16);
+        // the four lanes of a block agree: same scale, all four checks
+        if (four_bit && sc.live && sc.fast && same) {
           // The product is rounded to fp32 BEFORE it is rounded to an integer, as the reference does (a
-          // block's own ties, e.g. v / amax = 13 / 14, sit exactly on .5 only after that first rounding):
-          // the rounding instruction between the two multiplies also keeps either from being fused
-          // with anything.
+          // block's own ties, e.g. v / amax = 13 / 14, sit exactly on .5 only after that first rounding).
           const uint64_t scale_p = f32x2_pack(sc.scale, sc.scale), y_p = f32x2_pack(sc.y, sc.y);
+#if B200Q_FUSED_ROUND == 1
+          // rint(t) = (t + 1.5 * 2^23) - 1.5 * 2^23, the first sum written as fma(t, one, magic) with `one`
+          // = 1.0f arriving as a kernel parameter: the assembler fuses a multiply with a following add
+          // even when both carry an explicit rounding mode (observed: ties moved), which would round
+          // the exact product instead of t; it cannot fuse a multiply into an existing multiply-add
+          const uint64_t one_p = f32x2_pack(one, one), magic = f32x2_pack(12582912.f, 12582912.f),
+                         nmagic = f32x2_pack(-12582912.f, -12582912.f);
+#endif
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const uint64_t t2 = f32x2_mul(f32x2_pack(__uint_as_float(pr[i] << 16), __uint_as_float(pr[i] & 0xffff0000u)), scale_p);
-            const float r_lo = rintf(__uint_as_float(static_cast<uint32_t>(t2)));
-            const float r_hi = rintf(__uint_as_float(static_cast<uint32_t>(t2 >> 32)));
-            const uint64_t o2 = f32x2_mul(f32x2_pack(r_lo, r_hi), y_p);
+#if B200Q_FUSED_ROUND == 1
+            const uint64_t r2 = f32x2_add(f32x2_fma(t2, one_p, magic), nmagic);
+#else
+            const uint64_t r2 = f32x2_pack(rintf(__uint_as_float(static_cast<uint32_t>(t2))),
+                                           rintf(__uint_as_float(static_cast<uint32_t>(t2 >> 32))));
+#endif
+            const uint64_t o2 = f32x2_mul(r2, y_p);
             pr[i] = Elem<__nv_bfloat16>::pack2(__uint_as_float(static_cast<uint32_t>(o2)),
                                                __uint_as_float(static_cast<uint32_t>(o2 >> 32)));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 16; ++i) {
             const float lo = intq_apply(__uint_as_float(pr[i] << 16), sc, q);
             const float hi = intq_apply(__uint_as_float(pr[i] & 0xffff0000u), sc, q);
             pr[i] = Elem<__nv_bfloat16>::pack2(lo, hi);
           }
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(rowp + ((j ^ sw) << 4)) = make_uint4(pr[4 * j], pr[4 * j + 1], pr[4 * j + 2], pr[4 * j + 3]);
       }
+      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 2);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+        *reinterpret_cast<uint4*>(dst + (((j0 + jj) ^ sw) << 4)) =
+            make_uint4(pr[4 * jj], pr[4 * jj + 1], pr[4 * jj + 2], pr[4 * jj + 3]);
       fence_async_shared();     // these stores are read next by the tensor cores of both CTAs
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(&sm->b_ready[u], 0));
+      if (lane == 0) mbar_arrive_remote(map_to_cta(&sm->b_ready[u], 0));
+      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 3);
     }
-  } else if (warp >= 4) {
+  } else if ((warp >> 2) == 1 || (warp >> 2) == 4) {
     // ---------------------------------------------------------------- epilogue ----------------
     const int quarter = warp & 3;        // TMEM lanes quarter * 32 .. + 31 are the rows this warp may read
+    const int second = warp >= 16 ? 1 : 0;   // which of the quarter's two warps: it takes the odd chunks
     const uint32_t acc_empty_leader = map_to_cta(&sm->acc_empty, 0);
     uint32_t done = 0;
     bool ok = true;
@@ -339,43 +440,55 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       if (!ok) break;                     // warp-uniform: the TMEM loads below are warp-wide
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sq = 0.f;
+      // 16-column chunks of this lane's rows; the reference values of a chunk are requested one chunk
+      // ahead of the accumulator read they are compared with
+      const int chunks_n = min(kFPairN, N - w.slab_n * kFPairN) / 16;          // warp-uniform (N % 32 == 0)
+      const int total_chunks = MT * chunks_n;
+      auto row_of = [&](int t) { return w.slab_m * slab_rows + t * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane; };
+      auto load_ref = [&](int idx, uint4* r4) {
+        const int t = idx / chunks_n, cc = idx - t * chunks_n;
+        const int row = row_of(t);
+        if (row < M && !(B200Q_FUSED_ABLATE & 2)) {
+          const uint4* rp = reinterpret_cast<const uint4*>(ref + static_cast<int64_t>(row) * N + w.slab_n * kFPairN + cc * 16);
+          r4[0] = __ldg(rp);
+          r4[1] = __ldg(rp + 1);
+        }
+      };
+      uint4 cur[2], nxt[2];
+      if (second < total_chunks) load_ref(second, cur);
 #pragma unroll 1
-      for (int t = 0; t < MT; ++t) {
-        const int row = w.slab_m * slab_rows + t * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
-        const bool row_ok = row < M;
-        const __nv_bfloat16* rrow = ref + static_cast<int64_t>(row) * N;
-        float* crow = c_out ? c_out + (static_cast<int64_t>(w.alpha) * M + row) * N : nullptr;
-#pragma unroll 1
-        for (int cc = 0; cc < kFPairN / 32; ++cc) {
-          const int col0 = w.slab_n * kFPairN + cc * 32;
-          if (col0 >= N) break;                                           // warp-uniform (N % 32 == 0)
-          uint32_t acc[32];
-          tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + t * kFPairN + cc * 32, acc);
-          if (row_ok) {
-            const uint4* rp = reinterpret_cast<const uint4*>(rrow + col0);
+      for (int idx = second; idx < total_chunks; idx += 2) {
+        const int t = idx / chunks_n, cc = idx - t * chunks_n;
+        if (idx + 2 < total_chunks) load_ref(idx + 2, nxt);
+        uint32_t acc[16];
+        tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + t * kFPairN + cc * 16, acc);
+        const int row = row_of(t);
+        if (row < M && !(B200Q_FUSED_ABLATE & 2)) {
+          // bf16(bf16(acc) - ref) two elements at a time: the packed bf16 subtraction rounds the exact
+          // difference once, which is what rounding the fp32 difference of two bf16 values gives
+          const uint32_t rr[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
 #pragma unroll
-            for (int vv = 0; vv < 4; ++vv) {
-              const uint4 r4 = __ldg(rp + vv);
-              float rf[8];
-              Elem<__nv_bfloat16>::unpack(r4, rf);
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t o2 = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
+            const __nv_bfloat162 d2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&o2),
+                                              *reinterpret_cast<const __nv_bfloat162*>(&rr[j]));
+            const uint32_t db = *reinterpret_cast<const uint32_t*>(&d2);
+            const float d_lo = __uint_as_float(db << 16), d_hi = __uint_as_float(db & 0xffff0000u);
+            sq = fmaf(d_lo, d_lo, sq);
+            sq = fmaf(d_hi, d_hi, sq);
+          }
+          if (c_out && !(B200Q_FUSED_ABLATE & 16)) {
+            float* cp = c_out + (static_cast<int64_t>(w.alpha) * M + row) * N + w.slab_n * kFPairN + cc * 16;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float a = __uint_as_float(acc[8 * vv + j]);
-                const float o = __bfloat162float(__float2bfloat16_rn(a));
-                const float d = __bfloat162float(__float2bfloat16_rn(o - rf[j]));
-                sq = fmaf(d, d, sq);
-              }
-            }
-            if (crow) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) crow[col0 + j] = __uint_as_float(acc[j]);
-            }
+            for (int j = 0; j < 16; ++j) cp[j] = __uint_as_float(acc[j]);
           }
         }
+        cur[0] = nxt[0];
+        cur[1] = nxt[1];
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);   // the accumulator may be overwritten
+      if (lane == 0) mbar_arrive_remote(acc_empty_leader);   // the accumulator may be overwritten
       for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
       if (lane == 0) atomicAdd(loss + w.alpha, static_cast<double>(sq));
     }
@@ -386,7 +499,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   __syncthreads();
   cluster_barrier();   // neither CTA leaves (or frees the pair's TMEM) while the other still works
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (warp == 1) {
+  if (warp == kFWarpMma) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::kTmemCols));
   }
 }
@@ -439,7 +552,7 @@ static int fused_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, cons
   }
   const int64_t pairs = items < pairs_cached[dev] ? items : pairs_cached[dev];
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-  if (cudaLaunchKernelEx(&cfg, kern, map_a, map_w, s_all, ref, loss, c_out, n_alpha, m, n, k, q, status) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, map_a, map_w, s_all, ref, loss, c_out, n_alpha, m, n, k, q, 1.0f, status) != cudaSuccess) {
     cudaGetLastError();
     return B200Q_ERR_CUDA;
   }

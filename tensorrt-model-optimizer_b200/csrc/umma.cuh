@@ -133,6 +133,12 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
+// the same with the default (CTA-scope) release: for arrivals that only publish this CTA's own shared
+// memory to the tensor cores (through a proxy fence) or hand back tensor memory, where nothing the
+// other CTA's threads read is involved
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
 // bounded wait that acquires at cluster scope (the arrivals come from both CTAs)
 __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t* bar, uint32_t parity, uint32_t* abort_flag,
                                                           uint32_t* status, uint32_t code) {

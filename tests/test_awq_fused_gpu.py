@@ -163,3 +163,14 @@ def test_awq_lite_same_selection_with_the_fused_search():
         for key in la:
             assert abs(la[key] - lb[key]) <= 1e-3 * lb[key], (n, key, la[key], lb[key])
         assert aa == ab and torch.equal(sa, sb) and torch.equal(wa, wb)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_awq_scale_acts_equals_the_broadcast_multiply(dtype):
+    from b200q import ops
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = (torch.randn(300, 1024, generator=g, device="cuda") * 3).to(dtype)
+    s = torch.exp(torch.randn(5, 1024, generator=g, device="cuda")).to(dtype)
+    got = ops.awq_scale_acts(x, s)
+    assert torch.equal(got, x.unsqueeze(0) * s.unsqueeze(1))
