@@ -590,3 +590,85 @@ def nvfp4_swizzle_scales(scales: np.ndarray) -> np.ndarray:
     padded[:rows, :cols] = scales
     t = padded.reshape(rt, 4, 32, ct, 4)            # [row tile, r / 32, r % 32, col tile, c % 4]
     return np.ascontiguousarray(t.transpose(0, 3, 2, 1, 4)).reshape(-1)
+
+
+# --------------------------------------------------------------------------- awq_lite ----------
+# modelopt/torch/quantization/model_calib.py:588-627 (helpers) and :645-690 (the patched forward).
+# Statistics are reduced in the tensor dtype T (torch accumulates a bf16 / fp16 mean in fp32 and
+# rounds once), then widened to fp32; the search itself is fp32 except where it multiplies tensors.
+
+FP32_TINY = F32(np.finfo(np.float32).tiny)
+_TINY = {"f32": FP32_TINY, "f16": F32(np.finfo(np.float16).tiny), "bf16": F32(2.0 ** -126)}
+
+
+def awq_weight_scale(w: np.ndarray, block: int, T="f32") -> np.ndarray:
+    """get_weight_scale (:588-603): mean over rows of |W| / (block amax + tiny), everything in T."""
+    w = np.asarray(w, dtype=F32)
+    rows, cols = w.shape
+    wp = pad_last(w, block)
+    blocks = np.abs(wp).reshape(-1, block)
+    amax = blocks.max(axis=1, keepdims=True)
+    denom = round_to(amax + _TINY[T], T)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        scale = round_to(blocks / denom, T).reshape(rows, -1)[:, :cols]
+    return round_to(scale.mean(axis=0, dtype=F32), T)
+
+
+def awq_act_scale(x: np.ndarray, T="f32") -> np.ndarray:
+    """get_act_scale (:605-606): per input channel, the mean of |x| over tokens, in T."""
+    x = np.abs(np.asarray(x, dtype=F32)).reshape(-1, x.shape[-1])
+    return round_to(x.mean(axis=0, dtype=F32), T)
+
+
+def awq_get_scale(act_scale: np.ndarray, weight_scale: np.ndarray, alpha) -> np.ndarray:
+    """get_scale (:608-621), fp32: a^alpha / (w^(1-alpha) + tiny), clamped to [1e-4, 1e4], divided by
+    sqrt(max * min)."""
+    a, w = np.asarray(act_scale, dtype=F32), np.asarray(weight_scale, dtype=F32)
+    alpha = F32(alpha)
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        s = (np.power(a, alpha) / (np.power(w, F32(1) - alpha) + FP32_TINY)).astype(F32)
+        s = np.clip(s, F32(1e-4), F32(1e4)).astype(F32)
+        return (s / np.sqrt((s.max() * s.min()).astype(F32))).astype(F32)
+
+
+def awq_fake_weight(w: np.ndarray, s: np.ndarray, block: int, T="f32", num_bits=4) -> np.ndarray:
+    """The weight the search evaluates: pre_quant_scale multiply in T, dynamic per-block amax in T,
+    integer fake quant with narrow_range False (nn/modules/tensor_quantizer.py:882-883, 633-686)."""
+    v = round_to(np.asarray(w, dtype=F32) * round_to(s, T)[None, :], T)
+    rows, cols = v.shape
+    vp = pad_last(v, block).reshape(-1, block)
+    amax = np.abs(vp).max(axis=1, keepdims=True)
+    return fake_int(vp, amax, num_bits, False, False, T).reshape(rows, -1)[:, :cols]
+
+
+def awq_linear(x: np.ndarray, w: np.ndarray, T="f32") -> np.ndarray:
+    """F.linear without bias: products summed in fp32, the result rounded to T."""
+    return round_to(np.asarray(x, dtype=F32) @ np.asarray(w, dtype=F32).T, T)
+
+
+def awq_lite_search(w: np.ndarray, batches: list, block: int, alphas, T="f32", num_bits=4):
+    """One linear layer through the cache pass and the search pass: returns (weight_scale,
+    act_scale, {alpha: loss}, best_alpha, best_scale).  ``alphas`` are the keys of the reference's loss
+    dictionary: the elements of torch.arange(0, 1 + step, step) in fp32 as Python floats (:569-571).  loss = sum over batches of
+    mean(float(T(out - out_actual))^2) (:623-627); the first minimum wins (:632-633)."""
+    wsc = awq_weight_scale(w, block, T)
+    asc = np.zeros(w.shape[1], dtype=F32)
+    for x in batches:
+        asc = (asc + awq_act_scale(x, T)).astype(F32)
+    asc = (asc / F32(len(batches))).astype(F32)
+    losses = {}
+    for alpha in alphas:
+        s = awq_get_scale(asc, wsc, alpha)
+        wq = awq_fake_weight(w, s, block, T, num_bits)
+        with np.errstate(divide="ignore"):
+            xs = round_to((F32(1) / s).astype(F32), T)
+        total = F32(0)
+        for x in batches:
+            x2 = np.asarray(x, dtype=F32).reshape(-1, x.shape[-1])
+            out = awq_linear(round_to(x2 * xs[None, :], T), wq, T)
+            ref = awq_linear(x2, w, T)
+            d = round_to(out - ref, T)
+            total = F32(total + F32(np.mean(d.astype(np.float64) ** 2)))
+        losses[alpha] = float(total)
+    best = min(losses, key=losses.get)
+    return wsc, asc, losses, best, awq_get_scale(asc, wsc, best)

@@ -33,9 +33,9 @@ class MLP(nn.Module):
         return self.down_proj(torch.nn.functional.silu(self.up_proj(x)))
 
 
-def make_model(seed, dtype):
+def make_model(seed, dtype, hidden=128, inter=256):
     torch.manual_seed(seed)
-    m = MLP()
+    m = MLP(hidden, inter)
     with torch.no_grad():
         for p in m.parameters():
             p.copy_(torch.randn_like(p) * 0.05)
@@ -48,11 +48,14 @@ def make_batches(seed, n, dtype, hidden=128, tokens=48):
     return [(torch.randn(tokens, hidden, generator=g) * mag).to(dtype) for _ in range(n)]
 
 
-def golden_awq(mtq, out):
+def golden_awq(mtq, out, fixture="awq", hidden=128, inter=256, tokens=48):
+    """awq_lite through the reference.  ``awq`` is the 128 -> 256 -> 128 MLP with 48 tokens per batch;
+    ``awq128`` (hidden 256, intermediate 512, 128 tokens per batch) has token counts and channel counts
+    that are multiples of 128."""
     cases = {}
     for tag, dtype in (("bf16", torch.bfloat16), ("f32", torch.float32)):
-        model = make_model(11, dtype)
-        batches = make_batches(12, 2, dtype)
+        model = make_model(11, dtype, hidden, inter)
+        batches = make_batches(12, 2, dtype, hidden, tokens)
         cases[f"{tag}_w_up"] = bits(model.up_proj.weight)
         cases[f"{tag}_w_down"] = bits(model.down_proj.weight)
         for i, b in enumerate(batches):
@@ -79,7 +82,7 @@ def golden_awq(mtq, out):
             cases[f"{tag}_{name}_w_amax"] = bits(lin.weight_quantizer._amax)
         y = model(batches[0])
         cases[f"{tag}_y_fake"] = bits(y)
-    np.savez_compressed(out / "awq.npz", **cases)
+    np.savez_compressed(out / f"{fixture}.npz", **cases)
 
 
 def golden_flows(mtq, out):
@@ -226,12 +229,17 @@ def main():
         golden_export_layers(mtq, HERE)
         print("wrote export_layers")
         return
+    if args.only == "awq128":
+        golden_awq(mtq, HERE, "awq128", hidden=256, inter=512, tokens=128)
+        print("wrote awq128")
+        return
     if args.only == "clip_smooth":
         golden_clip_smooth(mtq, HERE)
         print("wrote clip_smooth")
         return
     golden_awq(mtq, HERE)
-    print("wrote awq")
+    golden_awq(mtq, HERE, "awq128", hidden=256, inter=512, tokens=128)
+    print("wrote awq, awq128")
     golden_flows(mtq, HERE)
     print("wrote flows")
     golden_clip_smooth(mtq, HERE)

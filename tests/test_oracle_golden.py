@@ -317,3 +317,31 @@ def test_nvfp4_scale_tiling_roundtrip():
     for r, c in [(0, 0), (31, 3), (32, 0), (137, 21), (299, 39)]:
         assert t[((r // 128) * 12 + c // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + c % 4] == s[r, c]
     assert t.sum() == s.sum()          # padding is zero
+
+
+@pytest.mark.parametrize("fixture", ["awq", "awq128"])
+@pytest.mark.parametrize("T", ["bf16", "f32"])
+def test_awq_lite_restatement_matches_the_reference(fixture, T):
+    """The oracle's awq_lite search (statistics, scale function, loss per alpha, selection) against what
+    the reference computed on the CPU: bf16 statistics bit for bit, fp32 ones to the summation order of a
+    mean, losses to 1e-4, the selected alpha exactly and its scale to 1e-5."""
+    g = load(fixture)
+    p = T + "_"
+    w_up, w_down = to_f32(g[p + "w_up"], T), to_f32(g[p + "w_down"], T)
+    xs = [to_f32(g[f"{p}x{i}"], T) for i in range(2)]
+
+    def silu(v):
+        return (v.astype(np.float64) / (1.0 + np.exp(-v.astype(np.float64)))).astype(np.float32)
+
+    hs = [qo.round_to(silu(qo.awq_linear(x, w_up, T)), T) for x in xs]
+    for name, w, inputs in (("up_proj", w_up, xs), ("down_proj", w_down, hs)):
+        k = f"{p}{name}_"
+        alphas = [float(a) for a in g[k + "alphas"]]
+        wsc, asc, losses, best, scale = qo.awq_lite_search(w, inputs, 128, alphas, T)
+        if T == "bf16":
+            assert np.array_equal(wsc, g[k + "weight_scale"]) and np.array_equal(asc, g[k + "act_scale"])
+        else:
+            assert np.allclose(wsc, g[k + "weight_scale"], rtol=5e-6) and np.allclose(asc, g[k + "act_scale"], rtol=5e-6)
+        assert np.allclose(np.array(list(losses.values())), g[k + "losses"], rtol=1e-4)
+        assert best == float(g[k + "best_alpha"])
+        assert np.allclose(scale, g[k + "best_scale"], rtol=1e-5)
