@@ -324,7 +324,7 @@ def test_nvfp4_scale_tiling_roundtrip():
 def test_awq_lite_restatement_matches_the_reference(fixture, T):
     """The oracle's awq_lite search (statistics, scale function, loss per alpha, selection) against what
     the reference computed on the CPU: bf16 statistics bit for bit, fp32 ones to the summation order of a
-    mean, losses to 1e-4, the selected alpha exactly and its scale to 1e-5."""
+    mean, losses to 1e-4 (5e-4 behind this test's silu), the selected alpha exactly and its scale to 1e-5."""
     g = load(fixture)
     p = T + "_"
     w_up, w_down = to_f32(g[p + "w_up"], T), to_f32(g[p + "w_down"], T)
@@ -342,6 +342,8 @@ def test_awq_lite_restatement_matches_the_reference(fixture, T):
             assert np.array_equal(wsc, g[k + "weight_scale"]) and np.array_equal(asc, g[k + "act_scale"])
         else:
             assert np.allclose(wsc, g[k + "weight_scale"], rtol=5e-6) and np.allclose(asc, g[k + "act_scale"], rtol=5e-6)
-        assert np.allclose(np.array(list(losses.values())), g[k + "losses"], rtol=1e-4)
+        # (the down projection's inputs pass through this test's own silu, whose last bit can differ from
+        # torch's: in fp32 that moves single quantisation ties, a few 1e-4 of a loss)
+        assert np.allclose(np.array(list(losses.values())), g[k + "losses"], rtol=1e-4 if name == "up_proj" else 5e-4)
         assert best == float(g[k + "best_alpha"])
         assert np.allclose(scale, g[k + "best_scale"], rtol=1e-5)
