@@ -244,6 +244,18 @@ int b200q_hist_mse(const unsigned long long* counts, int nbins, const float* edg
 int b200q_hist_collect_open(const void* x, int64_t n, int dtype, int nbins, float range_max, int capacity,
                             unsigned long long* counts, unsigned long long* overflow, void* stream);
 
+/* The same binning with the range read from DEVICE memory when the kernel runs (*range_dev = right
+ * edge of bin nbins - 1, e.g. the slot an abs-max kernel has just written or a value received from
+ * another rank: no host round trip before the first batch), and with the counts added to n_dest
+ * (1..4) histograms at once: calibrators that are handed the very same tensor (the q/k/v or the
+ * gate/up input quantisers of a layer) share one pass over it.  counts[i] / overflow[i] are HOST arrays of
+ * device pointers; every destination uses the same range.  A range that is not positive and finite puts
+ * every non-zero element into the out-of-range counters.  The reference bins once per calibrator
+ * (modelopt/torch/quantization/calib/histogram.py:77-130). */
+int b200q_hist_collect_shared(const void* x, int64_t n, int dtype, int nbins, const float* range_dev,
+                              int capacity, unsigned long long* const* counts,
+                              unsigned long long* const* overflow, int n_dest, void* stream);
+
 /* *amax_out = edge of the first bin whose cumulative share (float64 running sum of count/total)
  * reaches percentile/100: edges[i] when edges (fp32 [nbins+1]) is given, else bin_width*i.
  * Replaces _compute_amax_percentile (calib/histogram.py:328-343). */

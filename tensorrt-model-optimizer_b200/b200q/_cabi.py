@@ -49,6 +49,7 @@ SIGNATURES = {
     "b200q_int8_quantize": [_p, _p, _p, _i64, _i64, _i64, _i, _p],
     "b200q_hist_collect": [_p, _i64, _i, _i, _f, _p, _p],
     "b200q_hist_collect_open": [_p, _i64, _i, _i, _f, _i, _p, _p, _p],
+    "b200q_hist_collect_shared": [_p, _i64, _i, _i, _p, _i, _p, _p, _i, _p],
     "b200q_hist_entropy": [_p, _i, _i, _i, _i, _p, _f, _p, _p, _p],
     "b200q_hist_mse": [_p, _i, _p, _d, _i, _i, _p, _p, _p],
     "b200q_hist_percentile": [_p, _i, _p, _f, _d, _p, _p],

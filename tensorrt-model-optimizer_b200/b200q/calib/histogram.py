@@ -27,7 +27,136 @@ import torch
 from .. import ops
 from .calibrator import _Calibrator
 
-__all__ = ["HistogramCalibrator", "calibrate_weights"]
+__all__ = ["HistogramCalibrator", "HistogramArena", "attach_histogram_arena", "calibrate_weights"]
+
+
+class HistogramArena:
+    """One allocation for the counters of many histogram calibrators.
+
+    ``counts`` is int64 ``[Q, capacity]``, ``overflow`` int64 ``[Q]`` and ``ranges`` fp32 ``[Q]`` (the first
+    batch's abs-max of each calibrator = right edge of its bin ``num_bins - 1``); calibrator ``i`` works on
+    row ``i`` of each.  What this buys:
+
+    * the first batch fixes a calibrator's range on the DEVICE (the abs-max kernel writes its slot, the
+      binning kernel reads it): no host round trip per calibrator;
+    * the data-parallel exchange is in place: one broadcast of ``ranges``, one SUM all-reduce of ``counts``
+      (``b200q.dist``), no packing or unpacking;
+    * the live length of every histogram is read back with one copy (``resolve``);
+    * calibrators that are handed the very same tensor one after the other (the q/k/v or gate/up input
+      quantisers of a layer) share one binning pass: a collect is held back until the next collect shows
+      whether it is for the same tensor, and up to four calibrators are served by one launch.  Two
+      calibrators can share only if they have shared every batch since their first (they then alias one
+      range slot); the held-back tensor is kept alive, and a tensor that was modified in place before its
+      pass ran raises.
+    """
+
+    MAX_SHARE = 4
+
+    def __init__(self, calibrators):
+        self.cals = list(calibrators)
+        if not self.cals:
+            raise ValueError("no calibrators")
+        self.num_bins = self.cals[0]._init_bins
+        self.capacity = self.num_bins * HistogramCalibrator.CAPACITY_FACTOR
+        for i, c in enumerate(self.cals):
+            if c._init_bins != self.num_bins or c._calib_hist is not None or c._arena is not None:
+                raise ValueError("an arena takes fresh calibrators of one bin count")
+            c._arena, c._arena_index = self, i
+        self.counts = self.overflow = self.ranges = None
+        self._last_range = None   # (key, calibrator, tensor) of the latest first-batch observation
+        self._pending = None      # (key, tensor, [calibrators]) of the collect that is held back
+        self._stale = False
+
+    def _allocate(self, device):
+        q = len(self.cals)
+        self.counts = torch.zeros((q, self.capacity), dtype=torch.int64, device=device)
+        self.overflow = torch.zeros(q, dtype=torch.int64, device=device)
+        self.ranges = torch.zeros(q, dtype=torch.float32, device=device)
+        for i, c in enumerate(self.cals):
+            c._calib_hist = self.counts[i]
+            c._overflow = self.overflow[i:i + 1]
+            c._range_dev = self.ranges[i:i + 1]
+
+    @staticmethod
+    def _key(x):
+        return (x.data_ptr(), x._version, tuple(x.shape), tuple(x.stride()), x.dtype, x.device)
+
+    def observe_range(self, cal, x):
+        """First batch of ``cal``: its abs-max becomes the range.  A calibrator whose first batch is the
+        tensor another calibrator has just observed aliases that calibrator's slot instead of reading
+        the tensor again."""
+        if self.counts is None:
+            self._allocate(x.device)
+        key = self._key(x)
+        last = getattr(self, "_last_range", None)
+        if last is not None and last[0] == key and last[1]._range_dev is not None:
+            cal._range_dev = last[1]._range_dev
+        else:
+            ops.amax_tensor(x, out=cal._range_dev)
+            self._last_range = (key, cal, x)
+        cal._ranged = True
+
+    def submit(self, cal, x):
+        key = self._key(x)
+        p = self._pending
+        if (p is not None and p[0] == key and len(p[2]) < self.MAX_SHARE
+                and p[2][0]._range_dev.data_ptr() == cal._range_dev.data_ptr() and cal not in p[2]):
+            p[2].append(cal)
+            return
+        self.flush()
+        last = getattr(self, "_last_range", None)
+        if last is not None and last[0] != key:
+            self._last_range = None
+        self._pending = (key, x, [cal])
+
+    def flush(self):
+        p, self._pending = self._pending, None
+        if p is None:
+            return
+        key, x, cals = p
+        if x._version != key[1]:
+            raise RuntimeError("HistogramArena: a tensor was modified in place between collect() and the binning "
+                               "pass that was held back for it (set HistogramArena.MAX_SHARE = 1 to bin at once)")
+        ops.hist_collect_shared(x, [c._calib_hist for c in cals], [c._overflow for c in cals], self.num_bins,
+                                cals[0]._range_dev)
+        self._stale = True
+
+    def resolve(self):
+        """Bring every calibrator's live length, range and bin edges up to date with ONE device->host copy."""
+        self.flush()
+        self._last_range = None
+        if self.counts is None or not self._stale:
+            return
+        self._stale = False
+        idx = torch.arange(1, self.capacity + 1, device=self.counts.device)
+        live = ((self.counts != 0) * idx).amax(dim=1)
+        ranges = torch.stack([c._range_dev[0] for c in self.cals])
+        host = torch.stack([live.double(), self.overflow.double(), ranges.double()]).tolist()
+        for c, n_live, over, rng in zip(self.cals, *host):
+            if not c._ranged:
+                continue
+            if over > 0:
+                raise RuntimeError(
+                    f"HistogramCalibrator: {int(over)} samples were NaN, inf or beyond "
+                    f"{HistogramCalibrator.CAPACITY_FACTOR}x the range of the first batch ({rng}); they were not binned.")
+            c._set_live(int(n_live), rng)
+
+
+def attach_histogram_arena(model, share_inputs: bool = True):
+    """Give all fresh HistogramCalibrators of ``model`` (grouped by bin count) a common arena.  Returns the
+    arenas (possibly none)."""
+    from ..nn import TensorQuantizer
+
+    groups = {}
+    for _, m in model.named_modules():
+        if isinstance(m, TensorQuantizer):
+            c = getattr(m, "_calibrator", None)
+            if isinstance(c, HistogramCalibrator) and c._calib_hist is None and c._arena is None and not c._skip_zeros:
+                groups.setdefault(c._init_bins, []).append(c)
+    arenas = [HistogramArena(cs) for cs in groups.values()]
+    for a in arenas:
+        a.MAX_SHARE = HistogramArena.MAX_SHARE if share_inputs else 1
+    return arenas
 
 
 class HistogramCalibrator(_Calibrator):
@@ -46,6 +175,10 @@ class HistogramCalibrator(_Calibrator):
         self._range0 = None            # python float: right edge of bin _init_bins - 1
         self._overflow = None          # int64 [1] on the device
         self._stale = False            # counters changed since _num_bins was last read from them
+        self._arena = None             # HistogramArena this calibrator's counters live in, if any
+        self._arena_index = -1
+        self._range_dev = None         # fp32 [1] on the device: the range, when it is kept there (arena)
+        self._ranged = False
 
     # ---- range management ------------------------------------------------------------------
     def set_range(self, x_max: float, device):
@@ -62,8 +195,31 @@ class HistogramCalibrator(_Calibrator):
     def _width(self):
         return None if self._calib_bin_edges is None else float(self._calib_bin_edges[1] - self._calib_bin_edges[0])
 
+    def _set_live(self, n_live: int, range0: float):
+        """Arena read-back: live bins and the range the device holds."""
+        if self._calib_bin_edges is None or self._range0 != range0:
+            self._calib_bin_edges = torch.linspace(0, range0, self._init_bins + 1, device=self._calib_hist.device)
+            self._range0 = range0
+            self._num_bins = self._init_bins
+        n = max(n_live, self._init_bins)
+        if n > self._num_bins:
+            width = self._calib_bin_edges[1] - self._calib_bin_edges[0]
+            self._calib_bin_edges = torch.arange(n + 1, device=self._calib_hist.device, dtype=torch.float32) * width
+            self._num_bins = n
+
+    def observe_range(self, x):
+        """Fix the range from ``x`` (the first batch) without binning it."""
+        x = x.detach()
+        if self._arena is not None:
+            self._arena.observe_range(self, x)
+        elif self._calib_hist is None:
+            self.set_range(float(ops.amax_tensor(x)), x.device)
+
     def _resolve(self):
         """Bring ``_num_bins`` / ``_calib_bin_edges`` up to date with the device counters."""
+        if self._arena is not None:
+            self._arena.resolve()
+            return
         if not self._stale:
             return
         self._stale = False
@@ -106,12 +262,30 @@ class HistogramCalibrator(_Calibrator):
             x = x[x != 0]
             if x.numel() == 0:
                 return
+        if self._arena is not None:
+            if not self._ranged:
+                self._arena.observe_range(self, x)
+            self._arena.submit(self, x)
+            return
         if self._calib_hist is None:
             self.set_range(float(ops.amax_tensor(x)), x.device)
         ops.hist_collect_open(x, self._calib_hist, self._init_bins, self._range0, self._overflow)
         self._stale = True
 
     def reset(self):
+        if self._arena is not None:
+            self._arena.flush()
+            if self._calib_hist is not None:
+                self._calib_hist.zero_()
+                self._overflow.zero_()
+            if self._arena.ranges is not None:
+                self._range_dev = self._arena.ranges[self._arena_index:self._arena_index + 1]
+            self._ranged = False
+            self._calib_bin_edges = None
+            self._range0 = None
+            self._num_bins = self._init_bins
+            self._arena._stale = True
+            return
         self._calib_bin_edges = None
         self._calib_hist = None
         self._overflow = None
@@ -128,7 +302,7 @@ class HistogramCalibrator(_Calibrator):
         return self._calib_hist[: self._num_bins]
 
     def compute_amax(self, method: str, *, stride: int = 1, start_bin: int = 128, percentile: float = 99.99):
-        if self._calib_hist is None:
+        if self._calib_hist is None or (self._arena is not None and not self._ranged):
             return None
         self._resolve()
         if method == "percentile":

@@ -380,20 +380,16 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
             m.input_quantizer.load_calib_amax()
     if dist.is_available() and dist.is_initialized():
         qdist.sync_amax(model)
-    for name, m in layers:
-        st = m.awq_lite
-        if st.num_cache_steps > 0:
-            st.act_scale = st.act_scale / st.num_cache_steps
-            has_nan = bool(torch.any(torch.isnan(st.act_scale)) or torch.any(torch.isnan(st.weight_scale)))
-            if dist.is_available() and dist.is_initialized():
-                flags = [None] * dist.get_world_size()
-                dist.all_gather_object(flags, has_nan)
-                has_nan = any(flags)
-            if has_nan:
+    cached = [m.awq_lite for _, m in layers if m.awq_lite.num_cache_steps > 0]
+    for st in cached:
+        st.act_scale = st.act_scale / st.num_cache_steps
+    if cached:
+        # one device->host copy for all layers' NaN flags, one collective for all layers' statistics
+        nan = torch.stack([torch.isnan(st.act_scale).any() | torch.isnan(st.weight_scale).any().to(st.act_scale.device)
+                           for st in cached]).tolist()
+        for st, bad in zip(cached, qdist.sync_awq_statistics([st.act_scale for st in cached], nan)):
+            if bad:
                 st.is_enabled = False
-            elif dist.is_available() and dist.is_initialized():
-                dist.all_reduce(st.act_scale, op=dist.ReduceOp.SUM)
-                st.act_scale /= dist.get_world_size()
 
     # pass 2: search
     cache_mode[0] = False

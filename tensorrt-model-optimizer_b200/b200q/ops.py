@@ -380,6 +380,24 @@ def hist_collect_open(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_m
     return counts
 
 
+def hist_collect_shared(x: torch.Tensor, counts: list, overflow: list, nbins: int, range_dev: torch.Tensor):
+    """Bin |x| once and add the counts to every histogram of ``counts`` (1..4 int64 CUDA tensors of one
+    capacity, open-ended as in ``hist_collect_open``), the range being the fp32 device scalar ``range_dev``."""
+    x = _prep(x)
+    n = len(counts)
+    assert 1 <= n <= 4 and len(overflow) == n
+    cap = counts[0].numel()
+    for c, o in zip(counts, overflow):
+        assert c.dtype == torch.int64 and c.is_cuda and c.is_contiguous() and c.numel() == cap
+        assert o.dtype == torch.int64 and o.is_cuda and o.numel() >= 1
+    assert range_dev.dtype == torch.float32 and range_dev.is_cuda and range_dev.numel() >= 1
+    cp = (ctypes.c_void_p * n)(*[c.data_ptr() for c in counts])
+    op = (ctypes.c_void_p * n)(*[o.data_ptr() for o in overflow])
+    with torch.cuda.device(x.device):
+        call("b200q_hist_collect_shared", x.data_ptr(), x.numel(), dtype_code(x), nbins, range_dev.data_ptr(), cap,
+             ctypes.cast(cp, ctypes.c_void_p), ctypes.cast(op, ctypes.c_void_p), n, _stream(x))
+
+
 def hist_entropy(counts: torch.Tensor, nbins: int, edges: torch.Tensor, num_levels: int, start_bin: int = 128,
                  stride: int = 1):
     """Entropy-calibrated amax (0-dim fp32 tensor) and the per-candidate divergences (fp64)."""

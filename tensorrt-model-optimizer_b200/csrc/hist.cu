@@ -38,11 +38,36 @@ struct HistOpen {
   unsigned long long* overflow;
 };
 
+// Where a launch adds its counts: up to kHistMaxDests histograms (calibrators that were handed the
+// very same tensor share one binning pass), each with its own out-of-range counter.
+constexpr int kHistMaxDests = 4;
+struct HistDests {
+  unsigned long long* counts[kHistMaxDests];
+  unsigned long long* overflow[kHistMaxDests];
+  int n;
+};
+__device__ __forceinline__ void hist_add(const HistDests& d, uint32_t bin, unsigned long long c) {
+#pragma unroll
+  for (int i = 0; i < kHistMaxDests; ++i)
+    if (i < d.n) atomicAdd(d.counts[i] + bin, c);
+}
+__device__ __forceinline__ void hist_overflow(const HistDests& d, unsigned long long c) {
+#pragma unroll
+  for (int i = 0; i < kHistMaxDests; ++i)
+    if (i < d.n && d.overflow[i] != nullptr) atomicAdd(d.overflow[i], c);
+}
+
 template <typename T, bool kAllShared>
 __global__ void __launch_bounds__(kHistThreads)
 hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
-                    int smem_bins, int replicas, unsigned long long* __restrict__ counts) {
+                    int smem_bins, int replicas, HistDests dests, const float* __restrict__ range_dev) {
   pdl_prologue();
+  if (range_dev != nullptr) {   // the range lives on the device (no host round trip before the first batch)
+    range_max = *range_dev;
+    open.cap_range = open.capacity == nbins ? range_max
+                                            : static_cast<float>(static_cast<double>(range_max) * open.capacity / nbins);
+    if (!(range_max > 0.f) || !(open.cap_range < 3.0e38f)) open.cap_range = -1.f;   // nothing can be binned
+  }
   using E = Elem<T>;
   constexpr int P = E::kPerPack;
   extern __shared__ uint32_t sh[];
@@ -67,7 +92,7 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
     if (a <= open.cap_range) {  // false for values beyond the last bin and for NaN
       b = min(b, a <= range_max ? last : cap_last);
       if (kAllShared || b < static_cast<uint32_t>(smem_bins)) atomicAdd(mine + b, 1u);
-      else atomicAdd(counts + b, 1ull);
+      else hist_add(dests, b, 1ull);
     } else {
       ++beyond;
     }
@@ -110,11 +135,10 @@ hist_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_m
   for (int b = threadIdx.x; b < smem_bins; b += blockDim.x) {
     unsigned long long c = 0;
     for (int r = 0; r < replicas; ++r) c += sh[r * stride_r + b];
-    if (c) atomicAdd(counts + b, c);
+    if (c) hist_add(dests, b, c);
   }
   beyond = __reduce_add_sync(0xffffffffu, beyond);
-  if (open.overflow != nullptr && beyond != 0 && (threadIdx.x & 31) == 0)
-    atomicAdd(open.overflow, static_cast<unsigned long long>(beyond));
+  if (beyond != 0 && (threadIdx.x & 31) == 0) hist_overflow(dests, static_cast<unsigned long long>(beyond));
 }
 
 // ---- 16-bit inputs: value counting -------------------------------------------------------------
@@ -136,6 +160,46 @@ struct Hist16Layout {
   int smem_bins;      // bins with a shared counter
 };
 
+// largest 16-bit pattern of type T whose value is <= v (v >= 0), capped at the largest finite
+template <typename T> __host__ __device__ inline uint32_t floor_bits16(float v);
+template <> __host__ __device__ inline uint32_t floor_bits16<__nv_bfloat16>(float v) {
+  uint32_t u;
+#ifdef __CUDA_ARCH__
+  u = __float_as_uint(v);
+#else
+  memcpy(&u, &v, 4);
+#endif
+  u >>= 16;   // truncation rounds a non-negative value down
+  return u > 0x7f7fu ? 0x7f7fu : u;
+}
+template <> __host__ __device__ inline uint32_t floor_bits16<__half>(float v) {
+  if (!(v < 65504.f)) return 0x7bffu;
+  const __half h = __float2half_rd(v);
+  unsigned short r;
+#ifdef __CUDA_ARCH__
+  r = __half_as_ushort(h);
+#else
+  memcpy(&r, &h, 2);
+#endif
+  return r;
+}
+// counter layout of the value-counting kernel for one range (host: at launch; device: when the range is
+// only known there)
+template <typename T>
+__host__ __device__ inline Hist16Layout hist16_layout(float range_max, float cap_range, int nbins, int smem_bins) {
+  Hist16Layout lay;
+  lay.hi1 = floor_bits16<T>(cap_range) + 1;
+  lay.lo = floor_bits16<T>(range_max / (2.f * static_cast<float>(nbins)));
+  if (lay.lo >= lay.hi1) lay.lo = lay.hi1 - 1;
+  lay.values = static_cast<int>(lay.hi1 - lay.lo + 1);
+  lay.values = (lay.values + 3) & ~3;   // padding counters are never addressed
+  lay.smem_bins = smem_bins;
+  lay.rshift = 4;   // 16 replicas: 32 are conflict-free but measured no faster, and double the clearing
+  while (lay.rshift > 0 && (static_cast<int64_t>(lay.values) << lay.rshift) + lay.smem_bins + 3 > kHist16SmemWords)
+    --lay.rshift;
+  return lay;
+}
+
 __device__ __forceinline__ void red_shared_inc(uint32_t addr) {
   asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(addr), "r"(1u) : "memory");
 }
@@ -151,11 +215,23 @@ template <> __device__ __forceinline__ float value_of_bits16<__half>(uint32_t id
 template <typename T>
 __global__ void __launch_bounds__(kHistThreads)
 hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range_max, HistOpen open,
-                      Hist16Layout lay, unsigned long long* __restrict__ counts) {
+                      Hist16Layout lay, HistDests dests, const float* __restrict__ range_dev) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
   pdl_launch_dependents();
   extern __shared__ uint32_t sh[];
   uint4* sh4 = reinterpret_cast<uint4*>(sh);
+  if (range_dev != nullptr) {
+    // The range lives on the device (written by the abs-max kernel of the first batch, or received from
+    // another rank): the counter layout the host would have derived from it is derived here.  The
+    // predecessor wrote it, so its read waits like every other global access.
+    pdl_wait();
+    range_max = *range_dev;
+    open.cap_range = open.capacity == nbins ? range_max
+                                            : static_cast<float>(static_cast<double>(range_max) * open.capacity / nbins);
+    const bool valid = range_max > 0.f && open.cap_range < 3.0e38f;
+    if (!valid) { range_max = 1.f; open.cap_range = 0.f; }   // every element lands in the out-of-range counter
+    lay = hist16_layout<T>(range_max, open.cap_range, nbins, lay.smem_bins);
+  }
   const int vwords = lay.values << lay.rshift;             // a multiple of 4 (host pads `values`)
   // clearing the (CTA-private) counters overlaps the previous kernel's tail; global memory is
   // touched only after pdl_wait()
@@ -221,32 +297,17 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
     uint32_t b = quot < 8388608.f ? (__float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu) : cap_last;
     b = min(b, a <= range_max ? last : cap_last);
     if (b < static_cast<uint32_t>(lay.smem_bins)) atomicAdd(bins + b, c);
-    else atomicAdd(counts + b, static_cast<unsigned long long>(c));
+    else hist_add(dests, b, static_cast<unsigned long long>(c));
   }
-  if (open.overflow != nullptr && threadIdx.x <= rmask) {   // the index that holds what is out of range
+  if (threadIdx.x <= rmask) {   // the index that holds what is out of range
     const uint32_t c = sh[(in_range << lay.rshift) + threadIdx.x];
-    if (c) atomicAdd(open.overflow, static_cast<unsigned long long>(c));
+    if (c) hist_overflow(dests, static_cast<unsigned long long>(c));
   }
   __syncthreads();
   for (int b = threadIdx.x; b < lay.smem_bins; b += blockDim.x) {
     const uint32_t c = bins[b];
-    if (c) atomicAdd(counts + b, static_cast<unsigned long long>(c));
+    if (c) hist_add(dests, b, static_cast<unsigned long long>(c));
   }
-}
-
-// largest 16-bit pattern of type `dtype` whose value is <= v (v >= 0), capped at the largest finite
-static uint32_t floor_bits16(float v, int dtype) {
-  if (dtype == B200Q_BF16) {
-    uint32_t u;
-    memcpy(&u, &v, 4);
-    u >>= 16;   // truncation rounds a non-negative value down
-    return u > 0x7f7fu ? 0x7f7fu : u;
-  }
-  if (!(v < 65504.f)) return 0x7bffu;
-  const __half h = __float2half_rd(v);
-  unsigned short r;
-  memcpy(&r, &h, 2);
-  return r;
 }
 
 // Percentile read-out.  The quotients count / total are formed by all threads; one thread then adds
@@ -424,36 +485,42 @@ __global__ void hist_mse_pick_kernel(const double* __restrict__ errs, int ncand,
 
 using namespace b200q;
 
-static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, float range_max, int capacity,
-                             unsigned long long* counts, unsigned long long* overflow, void* stream) {
-  B200Q_REQUIRE_PTR(x); B200Q_REQUIRE_PTR(counts);
+// range_dev == nullptr: the range is `range_max`; otherwise it is read from the device when the kernel runs
+// (and the 16-bit kernel sizes its shared memory for the largest counter layout any range can need).
+static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, float range_max, const float* range_dev,
+                             int capacity, const HistDests& dests, void* stream) {
+  B200Q_REQUIRE_PTR(x);
   B200Q_REQUIRE_DTYPE(dtype); B200Q_REQUIRE_ALIGNED(x);
+  if (dests.n < 1 || dests.n > kHistMaxDests) return B200Q_ERR_ARG;
+  for (int i = 0; i < dests.n; ++i) B200Q_REQUIRE_PTR(dests.counts[i]);
   if (n <= 0 || nbins <= 0 || capacity < nbins || capacity > (1 << 22)) return B200Q_ERR_SHAPE;
-  if (!(range_max > 0.f)) return B200Q_ERR_ARG;
   HistOpen open;
   open.capacity = capacity;
-  // right end of the last bin; for the closed histogram exactly range_max
-  open.cap_range = capacity == nbins ? range_max
-                                     : static_cast<float>(static_cast<double>(range_max) * capacity / nbins);
-  if (!(open.cap_range < 3.0e38f)) return B200Q_ERR_ARG;
-  open.overflow = overflow;
+  open.overflow = nullptr;
+  open.cap_range = 0.f;
+  if (range_dev == nullptr) {
+    if (!(range_max > 0.f)) return B200Q_ERR_ARG;
+    // right end of the last bin; for the closed histogram exactly range_max
+    open.cap_range = capacity == nbins ? range_max
+                                       : static_cast<float>(static_cast<double>(range_max) * capacity / nbins);
+    if (!(open.cap_range < 3.0e38f)) return B200Q_ERR_ARG;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // 32-bit shared counters: one launch bins at most 2^36 elements (< 2^32 per CTA)
   const int64_t chunk = int64_t{1} << 36;
   if (dtype != B200Q_F32) {
-    Hist16Layout lay;
-    lay.hi1 = floor_bits16(open.cap_range, dtype) + 1;
-    lay.lo = floor_bits16(range_max / (2.f * static_cast<float>(nbins)), dtype);
-    if (lay.lo >= lay.hi1) lay.lo = lay.hi1 - 1;
-    lay.values = static_cast<int>(lay.hi1 - lay.lo + 1);
-    lay.values = (lay.values + 3) & ~3;   // padding counters are never addressed
-    lay.smem_bins = capacity < kHist16MaxSmemBins ? capacity : kHist16MaxSmemBins;
-    lay.rshift = 4;   // 16 replicas: 32 are conflict-free but measured no faster, and double the clearing
-    while (lay.rshift > 0 && (static_cast<int64_t>(lay.values) << lay.rshift) + lay.smem_bins + 3 > kHist16SmemWords)
-      --lay.rshift;
-    const size_t smem = ((static_cast<size_t>(lay.values) << lay.rshift) + ((lay.smem_bins + 3) & ~3)) * sizeof(uint32_t);
+    const int smem_bins = capacity < kHist16MaxSmemBins ? capacity : kHist16MaxSmemBins;
     return B200Q_DISPATCH(dtype, [&]() -> int {
       if constexpr (sizeof(T) == 2) {
+        Hist16Layout lay;
+        size_t smem;
+        if (range_dev == nullptr) {
+          lay = hist16_layout<T>(range_max, open.cap_range, nbins, smem_bins);
+          smem = ((static_cast<size_t>(lay.values) << lay.rshift) + ((lay.smem_bins + 3) & ~3)) * sizeof(uint32_t);
+        } else {
+          lay.lo = lay.hi1 = 0; lay.values = 0; lay.rshift = 0; lay.smem_bins = smem_bins;
+          smem = static_cast<size_t>(kHist16SmemWords) * sizeof(uint32_t);
+        }
         auto kern = hist16_collect_kernel<T>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kHist16SmemWords * 4) != cudaSuccess)
           return B200Q_ERR_CUDA;
@@ -461,7 +528,7 @@ static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, flo
           const int64_t len = n - off < chunk ? n - off : chunk;
           const int grid = grid_for(len / 8, kHistThreads * 4, 1);
           launch_pdl(kern, grid, kHistThreads, smem, s, static_cast<const T*>(x) + off, len, nbins, range_max, open,
-                     lay, counts);
+                     lay, dests, range_dev);
         }
         return launch_status();
       } else {
@@ -482,21 +549,45 @@ static int hist_collect_impl(const void* x, int64_t n, int dtype, int nbins, flo
     const int64_t len = n - off < chunk ? n - off : chunk;
     const int grid = grid_for(len / 4, kHistThreads * 4, 1);
     launch_pdl(kern, grid, kHistThreads, smem, s, static_cast<const float*>(x) + off, len, nbins, range_max, open, smem_bins,
-                                          replicas, counts);
+               replicas, dests, range_dev);
   }
   return launch_status();
 }
 
+static HistDests one_dest(unsigned long long* counts, unsigned long long* overflow) {
+  HistDests d = {};
+  d.counts[0] = counts;
+  d.overflow[0] = overflow;
+  d.n = 1;
+  return d;
+}
+
 extern "C" int b200q_hist_collect(const void* x, int64_t n, int dtype, int nbins, float range_max,
                                   unsigned long long* counts, void* stream) {
-  return hist_collect_impl(x, n, dtype, nbins, range_max, nbins, counts, nullptr, stream);
+  B200Q_REQUIRE_PTR(counts);
+  return hist_collect_impl(x, n, dtype, nbins, range_max, nullptr, nbins, one_dest(counts, nullptr), stream);
 }
 
 extern "C" int b200q_hist_collect_open(const void* x, int64_t n, int dtype, int nbins, float range_max,
                                        int capacity, unsigned long long* counts, unsigned long long* overflow,
                                        void* stream) {
-  B200Q_REQUIRE_PTR(overflow);
-  return hist_collect_impl(x, n, dtype, nbins, range_max, capacity, counts, overflow, stream);
+  B200Q_REQUIRE_PTR(counts); B200Q_REQUIRE_PTR(overflow);
+  return hist_collect_impl(x, n, dtype, nbins, range_max, nullptr, capacity, one_dest(counts, overflow), stream);
+}
+
+extern "C" int b200q_hist_collect_shared(const void* x, int64_t n, int dtype, int nbins, const float* range_dev,
+                                         int capacity, unsigned long long* const* counts,
+                                         unsigned long long* const* overflow, int n_dest, void* stream) {
+  B200Q_REQUIRE_PTR(range_dev); B200Q_REQUIRE_PTR(counts); B200Q_REQUIRE_PTR(overflow);
+  if (n_dest < 1 || n_dest > kHistMaxDests) return B200Q_ERR_ARG;
+  HistDests d = {};
+  d.n = n_dest;
+  for (int i = 0; i < n_dest; ++i) {
+    B200Q_REQUIRE_PTR(counts[i]); B200Q_REQUIRE_PTR(overflow[i]);
+    d.counts[i] = counts[i];
+    d.overflow[i] = overflow[i];
+  }
+  return hist_collect_impl(x, n, dtype, nbins, 0.f, range_dev, capacity, d, stream);
 }
 
 extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,

@@ -204,6 +204,64 @@ def test_sync_histograms_two_gloo_ranks():
     _spawn(_hist_job)
 
 
+def _arena_job(rank, world):
+    """Arena calibrators: ranges broadcast in place, counters summed in place (no packing), one
+    collective each; the result is the element-wise sum of what the ranks held."""
+    from b200q.calib import attach_histogram_arena
+
+    m = MLP()
+    mtq.replace_quant_module(m)
+    cfg = {"*input_quantizer": {"num_bits": 8, "axis": None, "calibrator": "histogram"},
+           "*weight_quantizer": {"enable": False}, "default": {"enable": False}}
+    mtq.set_quantizer_by_cfg(m, cfg)
+    (arena,) = attach_histogram_arena(m)
+    assert len(arena.cals) == 3
+    arena._allocate(torch.device("cpu"))
+    rng = np.random.default_rng(9 + rank)
+    arena.ranges.copy_(torch.tensor([1.0, 2.0, 3.0]) + 10.0 * rank)
+    for c in arena.cals:
+        c._ranged = True
+    mtq.dist.agree_histogram_ranges(m)
+    assert torch.equal(arena.ranges, torch.tensor([1.0, 2.0, 3.0]))        # rank 0's everywhere
+    live = 2048 + 500 * rank                                                 # rank 1 reached further bins
+    mine = torch.zeros_like(arena.counts)
+    mine[:, :live] = torch.from_numpy(rng.integers(0, 1000, (3, live)))
+    arena.counts.copy_(mine)
+    ptr = arena.counts.data_ptr()
+    assert mtq.dist.sync_histograms(m) == 2
+    assert arena.counts.data_ptr() == ptr                                    # reduced where it was
+    gathered = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    assert torch.equal(arena.counts, sum(gathered))
+    arena.resolve()
+    for i, c in enumerate(arena.cals):
+        assert c._num_bins == 2048 + 500 and c.hist.numel() == 2548
+        assert abs(float(c._calib_bin_edges[2048]) - (1.0 + i)) < 1e-6
+
+
+def test_sync_histogram_arena_two_gloo_ranks():
+    _spawn(_arena_job)
+
+
+def _awq_stats_job(rank, world):
+    """awq_lite's exchange between its passes: act_scale becomes the mean over the ranks, and a layer
+    with a NaN on ANY rank is flagged on ALL ranks and left alone; one collective for all layers."""
+    a = [torch.full((8,), 1.0 + rank), torch.full((4,), 10.0 * (rank + 1)), torch.arange(6, dtype=torch.float32) + rank]
+    if rank == 1:
+        a[1][2] = float("nan")
+    before = [t.clone() for t in a]
+    nan = [bool(torch.isnan(t).any()) for t in a]
+    flags = mtq.dist.sync_awq_statistics(a, nan)
+    assert flags == [False, True, False]
+    assert torch.equal(a[0], torch.full((8,), 1.5))
+    assert torch.equal(a[2], torch.arange(6, dtype=torch.float32) + 0.5)
+    assert torch.equal(torch.nan_to_num(a[1]), torch.nan_to_num(before[1]))   # the flagged layer keeps its own
+
+
+def test_awq_statistics_exchange_two_gloo_ranks():
+    _spawn(_awq_stats_job)
+
+
 def _failing_rank_job(rank, world):
     """A rank that never joins the exchange: the others get an error from the collective's
     timeout instead of hanging (host-side failure, no GPU involved)."""
