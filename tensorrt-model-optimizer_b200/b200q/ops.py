@@ -247,7 +247,9 @@ class NvFp4Group:
     amax slots and launches, so it can be repeated (and timed) without host work per tensor.
     """
 
-    def __init__(self, tensors: list[torch.Tensor]):
+    def __init__(self, tensors: list[torch.Tensor], separate_outputs: bool = False):
+        """``separate_outputs``: every tensor's packed bytes and block scales get an allocation of their
+        own (for results that outlive the group, e.g. module weights) instead of slices of two arenas."""
         if not tensors:
             raise ValueError("empty tensor list")
         self.tensors = [_prep(t, 32) for t in tensors]
@@ -258,8 +260,9 @@ class NvFp4Group:
         total_packed = sum(t.numel() // 2 for t in self.tensors)
         total_scales = sum(t.numel() // 16 for t in self.tensors)
         # one allocation per output kind; 32-byte aligned slices
-        self._packed = torch.empty(total_packed + 32 * n, dtype=torch.uint8, device=dev)
-        self._scales = torch.empty(total_scales + 32 * n, dtype=torch.uint8, device=dev)
+        if not separate_outputs:
+            self._packed = torch.empty(total_packed + 32 * n, dtype=torch.uint8, device=dev)
+            self._scales = torch.empty(total_scales + 32 * n, dtype=torch.uint8, device=dev)
         self.amax = torch.zeros(n, dtype=torch.float32, device=dev)
         self.scale2 = torch.empty(n, dtype=torch.float32, device=dev)
         descs = (_cabi.NvFp4Desc * n)()
@@ -272,8 +275,12 @@ class NvFp4Group:
             if t.shape[-1] % 16:
                 raise ValueError("last dimension must be a multiple of 16")
             K = t.shape[-1]
-            p = self._packed[po:po + t.numel() // 2].view(*t.shape[:-1], K // 2)
-            s = self._scales[so:so + t.numel() // 16].view(*t.shape[:-1], K // 16)
+            if separate_outputs:
+                p = torch.empty((*t.shape[:-1], K // 2), dtype=torch.uint8, device=dev)
+                s = torch.empty((*t.shape[:-1], K // 16), dtype=torch.uint8, device=dev)
+            else:
+                p = self._packed[po:po + t.numel() // 2].view(*t.shape[:-1], K // 2)
+                s = self._scales[so:so + t.numel() // 16].view(*t.shape[:-1], K // 16)
             self.packed.append(p)
             self.scales.append(s.view(torch.float8_e4m3fn))
             d = descs[i]
@@ -291,13 +298,20 @@ class NvFp4Group:
         self._descs = host.to(dev)
         self.elements = sum(t.numel() for t in self.tensors)
 
-    def run(self, amax_pass: bool = True):
+    def run(self, amax_pass: bool = True, amax_values: dict | None = None):
+        """``amax_values`` {index: tensor}: global abs-max to use for those tensors instead of their own (a
+        calibrated or clipped weight amax)."""
         dc = _DT[self.dtype]
         with torch.cuda.device(self.device):
             st = torch.cuda.current_stream(self.device).cuda_stream
             if amax_pass:
                 self.amax.zero_()
                 call("b200q_nvfp4_group_amax", self._descs.data_ptr(), self.n, self.total_tiles, dc, st)
+            if amax_values:
+                idx = torch.tensor(sorted(amax_values), dtype=torch.int64, device=self.device)
+                vals = torch.stack([amax_values[i].detach().to(device=self.device, dtype=torch.float32).reshape(())
+                                    for i in sorted(amax_values)])
+                self.amax.index_copy_(0, idx, vals)
             call("b200q_nvfp4_group_quantize", self._descs.data_ptr(), self.n, self.total_tiles, dc, st)
         return self.packed, self.scales, self.scale2
 

@@ -57,9 +57,10 @@ class HostNvFp4Packer:
             })
         return out
 
-    def pack(self, host_groups, host_out):
+    def pack(self, host_groups, host_out, amax_values=None):
         """Quantise every group of ``host_groups`` (lists of pinned host tensors) into
-        ``host_out`` (from :meth:`alloc_host_outputs`).  Returns after everything has landed."""
+        ``host_out`` (from :meth:`alloc_host_outputs`).  ``amax_values[i]`` ({index in group: tensor}) gives
+        calibrated global abs-max values for group i.  Returns after everything has landed."""
         with torch.cuda.device(self.device):
             for i, tensors in enumerate(host_groups):
                 slot = self.slots[i % self.depth]
@@ -75,7 +76,7 @@ class HostNvFp4Packer:
                 if i >= self.depth:
                     self.s_run.wait_event(slot["drained"])  # outputs of the previous user were read out
                 with torch.cuda.stream(self.s_run):
-                    grp.run()
+                    grp.run(amax_values=amax_values[i] if amax_values else None)
                     slot["done"].record(self.s_run)
                 self.s_out.wait_event(slot["done"])
                 with torch.cuda.stream(self.s_out):
@@ -87,3 +88,39 @@ class HostNvFp4Packer:
                     slot["drained"].record(self.s_out)
             self.s_out.synchronize()
         return host_out
+
+
+def pack_host_tensors(tensors, device="cuda", amax=None, group_bytes: int = 256 << 20):
+    """NVFP4-pack a list of host (CPU) weight tensors of any shapes through the GPU: tensors are
+    bucketed by (shape, dtype), every bucket is streamed through a :class:`HostNvFp4Packer` in groups of
+    about ``group_bytes``.  ``amax[i]`` (or None) is a calibrated global abs-max for tensor i.  Returns, in
+    the order of ``tensors``, tuples (packed uint8, block scales float8_e4m3fn, scale2 fp32 0-dim), all on
+    the host."""
+    results = [None] * len(tensors)
+    buckets = {}
+    for i, t in enumerate(tensors):
+        buckets.setdefault((tuple(t.shape), t.dtype), []).append(i)
+    for (shape, dtype), idxs in buckets.items():
+        nbytes = 1
+        for d in shape:
+            nbytes *= d
+        nbytes *= torch.empty((), dtype=dtype).element_size()
+        per = max(1, min(len(idxs), group_bytes // max(nbytes, 1)))
+        full = len(idxs) // per * per
+        # groups of `per` tensors, then one smaller group for what is left
+        for ids, g in ((idxs[:full], per), (idxs[full:], len(idxs) - full)):
+            if not ids:
+                continue
+            packer = HostNvFp4Packer([shape] * g, dtype, device)
+            groups = [[tensors[j] for j in ids[k:k + g]] for k in range(0, len(ids), g)]
+            out = packer.alloc_host_outputs(len(groups))
+            av = None
+            if amax is not None:
+                av = [{k: amax[j] for k, j in enumerate(ids[b:b + g]) if amax[j] is not None}
+                      for b in range(0, len(ids), g)]
+            packer.pack(groups, out, av)
+            for b in range(len(groups)):
+                for k in range(g):
+                    results[ids[b * g + k]] = (out[b]["packed"][k], out[b]["scales"][k].view(torch.float8_e4m3fn),
+                                               out[b]["scale2"][k].clone())
+    return results

@@ -57,12 +57,60 @@ class QTensorWrapper(torch.nn.Parameter):
                 "quantized_data.dtype": self.data.dtype}
 
 
+def _nvfp4_groupable(m, wq) -> bool:
+    """A weight whose real quantisation is plain NVFP4 (block 16, E4M3 block scales, nothing applied to
+    the weight first): these are quantised together, two launches per device and dtype."""
+    bs = wq._block_sizes or {}
+    w = m.weight
+    return (wq._num_bits == (2, 1) and bs.get("scale_bits") == (4, 3) and bs.get(-1) == 16
+            and bs.get("type") == "dynamic" and not getattr(wq, "_rotate", False)
+            and getattr(wq, "pre_quant_scale", None) is None and getattr(wq, "_bias", None) is None
+            and w.dim() == 2 and w.shape[-1] % 16 == 0 and w.is_floating_point()
+            and w.dtype in (torch.float32, torch.float16, torch.bfloat16)
+            and (w.is_cuda or torch.cuda.is_available()))
+
+
+def _pack_nvfp4_grouped(items):
+    """items: [(module, weight quantiser)].  CUDA weights: one ``NvFp4Group`` (abs-max launch + quantise
+    launch) per device and dtype.  Host weights: streamed through the GPU by ``pipeline.pack_host_tensors``
+    and left on the host.  A quantiser that carries a calibrated ``_amax`` has it used as the global
+    abs-max, as ``NVFP4QTensor.quantize`` is given it by ``_real_quantize``."""
+    from .. import ops
+    from ..pipeline import pack_host_tensors
+    from .nvfp4_tensor import NVFP4QTensor
+
+    def finish(m, wq, packed, scales, s2):
+        wq._set_buffer("_scale", scales)
+        wq._set_buffer("_double_scale", s2)
+        wq._dequantize = True
+        m.weight = QTensorWrapper(NVFP4QTensor(m.weight.shape, m.weight.dtype, packed))
+
+    by = {}
+    for m, wq in items:
+        by.setdefault((m.weight.device, m.weight.dtype), []).append((m, wq))
+    for (dev, _), lst in by.items():
+        amax = [wq._amax if hasattr(wq, "_amax") and wq._amax.numel() == 1 else None for _, wq in lst]
+        if dev.type == "cuda":
+            grp = ops.NvFp4Group([m.weight.data for m, _ in lst], separate_outputs=True)
+            packed, scales, s2 = grp.run(amax_values={i: a for i, a in enumerate(amax) if a is not None})
+            for i, (m, wq) in enumerate(lst):
+                finish(m, wq, packed[i], scales[i], s2[i].clone())
+        else:
+            res = pack_host_tensors([m.weight.data for m, _ in lst], "cuda", amax)
+            for (m, wq), (p, sc, s2) in zip(lst, res):
+                finish(m, wq, p, sc, s2)
+
+
 def pack_real_quantize_weight(module, force_quantize: bool = False):
     """Replace the weight of every sub-module whose weight quantiser is in real-quant mode by its
-    packed form (the quantiser keeps the scales as buffers)."""
+    packed form (the quantiser keeps the scales as buffers).  Plain NVFP4 weights are packed together by
+    the grouped kernels (``_pack_nvfp4_grouped``); every other format goes through its quantiser one
+    weight at a time, as the reference does for all of them
+    (modelopt/torch/quantization/qtensor/base_qtensor.py:196-229)."""
     from ..nn import SequentialQuantizer
 
     with torch.no_grad():
+        grouped, single = [], []
         for name, m in module.named_modules():
             wq = getattr(m, "weight_quantizer", None)
             if wq is None or getattr(m, "weight", None) is None or m.weight.is_meta:
@@ -72,4 +120,8 @@ def pack_real_quantize_weight(module, force_quantize: bool = False):
             if wq.is_enabled and not wq._fake_quant and m.weight.element_size() > 1:
                 if force_quantize:
                     wq._dequantize = False
-                m.weight = QTensorWrapper(wq(m.weight))
+                (grouped if _nvfp4_groupable(m, wq) else single).append((m, wq))
+        if grouped:
+            _pack_nvfp4_grouped(grouped)
+        for m, wq in single:
+            m.weight = QTensorWrapper(wq(m.weight))

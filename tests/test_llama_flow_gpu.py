@@ -196,3 +196,68 @@ def test_llama_shaped_model_runs_on_real_quant_gemms(name):
     cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0)
     assert cos > 0.999, cos
     assert (got - want).abs().max() <= 0.05 * want.abs().max()
+
+
+def _nvfp4_weight_only_tree(n_layers, device, dtype=torch.bfloat16):
+    """A Llama-shaped tree of linears (scaled-down dims, real names) with NVFP4 weight quantisers."""
+    import b200q as mtq
+
+    dims = {"q_proj": (256, 256), "k_proj": (64, 256), "v_proj": (64, 256), "o_proj": (256, 256),
+            "gate_proj": (896, 256), "up_proj": (896, 256), "down_proj": (256, 896)}
+    g = torch.Generator().manual_seed(0)
+    layers = torch.nn.ModuleList()
+    for _ in range(n_layers):
+        layer = torch.nn.ModuleDict()
+        for name, (n, k) in dims.items():
+            lin = torch.nn.Linear(k, n, bias=False)
+            with torch.no_grad():
+                lin.weight.copy_(torch.randn(n, k, generator=g) * 0.02)
+            layer[name] = lin
+        layers.append(layer)
+    model = torch.nn.ModuleDict({"layers": layers}).to(device=device, dtype=dtype)
+    mtq.replace_quant_module(model)
+    mtq.set_quantizer_by_cfg(model, {"*weight_quantizer": {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}, "axis": None, "enable": True},
+                                     "*input_quantizer": {"enable": False}, "default": {"enable": False}})
+    return model
+
+
+@pytest.mark.parametrize("where", ["cuda", "cpu"])
+def test_compress_packs_nvfp4_weights_with_the_grouped_kernels(where, monkeypatch):
+    """mtq.compress on a Llama-shaped tree: all NVFP4 weights of a device go through ONE grouped abs-max
+    launch and ONE grouped quantise launch (a host-resident model is streamed through the GPU instead),
+    and every packed weight, block scale and global scale equals what the per-weight path
+    (``NVFP4QTensor.quantize``, oracle-checked elsewhere) produces; a calibrated, clipped weight amax is
+    honoured."""
+    import b200q as mtq
+    from b200q import ops
+    from b200q.qtensor import NVFP4QTensor
+
+    model = _nvfp4_weight_only_tree(2, where)
+    originals = {n: m.weight.detach().clone().cuda() for n, m in model.named_modules() if hasattr(m, "weight_quantizer")}
+    assert len(originals) == 14
+    clipped = "layers.1.down_proj"
+    wq = dict(model.named_modules())[clipped].weight_quantizer
+    wq.amax = (originals[clipped].float().abs().max() * 0.7).to(where)
+    launches = []
+    real = ops.NvFp4Group.run
+    monkeypatch.setattr(ops.NvFp4Group, "run", lambda self, *a, **k: (launches.append(self.n), real(self, *a, **k))[1])
+    mtq.compress(model)
+    torch.cuda.synchronize()
+    if where == "cuda":
+        assert launches == [14], "one grouped pass for all fourteen weights"
+    else:
+        assert sum(launches) == 14 and len(launches) <= 8
+    for name, w in originals.items():
+        m = dict(model.named_modules())[name]
+        assert m.weight.dtype == torch.uint8 and m.weight.device.type == where
+        s2 = None
+        if name == clipped:
+            s2 = NVFP4QTensor.get_weights_scaling_factor_2_from_quantizer(type("Q", (), {"_amax": wq._amax.cuda()}))
+        q, sc, d = NVFP4QTensor.quantize(w, 16, weights_scaling_factor_2=s2)
+        assert torch.equal(m.weight.data.cuda(), q._quantized_data), name
+        assert torch.equal(m.weight_quantizer._scale.view(torch.uint8).cuda(), sc.view(torch.uint8)), name
+        assert m.weight_quantizer._double_scale.item() == d.item(), name
+    if where == "cuda":
+        x = torch.randn(8, 256, device="cuda", dtype=torch.bfloat16)
+        y = model["layers"][0]["q_proj"](x)
+        assert torch.isfinite(y).all()
