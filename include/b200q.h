@@ -264,6 +264,19 @@ int b200q_hist_percentile(const unsigned long long* counts, int nbins, const flo
 
 /* ---------------------------------------------------------------- awq_lite search ---------- */
 
+/* MSE calibration, all candidates in one pass: x (T, viewed as [outer, channels, inner], contiguous) is
+ * read once and, taken as fp32, fake-quantised under each of the n_cand (<= 16) candidate amax values
+ * cand_amax[s * channels + c] (fp32);
+ *   loss_io[s * channels + c] += sum over the elements of channel c of (x - fq(x, cand))^2    (float64)
+ * format 0: integer fake quant (num_bits / is_unsigned / narrow_range as b200q_fake_int_tensor);
+ * format 1: FP8 E4M3 (b200q_fake_e4m3_tensor).  channels == 1 is the per-tensor case; otherwise inner
+ * must be a multiple of the 16-byte pack and at least 32 packs (else B200Q_ERR_UNSUPPORTED).
+ * Replaces the loop over candidates of MseCalibrator.collect — per candidate a fake-quant pass, a
+ * squared error and a reduction (modelopt/torch/quantization/calib/mse.py:76-100). */
+int b200q_mse_candidates(const void* x, int64_t outer, int64_t channels, int64_t inner, int dtype,
+                         const float* cand_amax, int n_cand, int format, int num_bits, int is_unsigned,
+                         int narrow_range, double* loss_io, void* stream);
+
 /* One candidate of the awq_lite search, weight side: for w[rows, cols] and s[cols] (both T),
  *   v = T(w * s[col]);  amax = max|v| over each run of `block` elements of a row;
  *   y = T(fake_int(v, amax, num_bits, ...))      (integer fake quant as b200q_fake_int_tensor)

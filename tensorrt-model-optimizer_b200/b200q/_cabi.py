@@ -53,6 +53,7 @@ SIGNATURES = {
     "b200q_hist_entropy": [_p, _i, _i, _i, _i, _p, _f, _p, _p, _p],
     "b200q_hist_mse": [_p, _i, _p, _d, _i, _i, _p, _p, _p],
     "b200q_hist_percentile": [_p, _i, _p, _f, _d, _p, _p],
+    "b200q_mse_candidates": [_p, _i64, _i64, _i64, _i, _p, _i, _i, _i, _i, _i, _p, _p],
     "b200q_awq_scale_fake_int": [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _i, _p],
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],

@@ -105,9 +105,15 @@ def mse_calibrate(model: nn.Module, forward_loop=None, distributed_sync=True, nu
                     q._amax = saved
                     q._if_quant, q._if_calib, q._fake_quant = if_quant, if_calib, fake
 
+            # a plain integer / E4M3 fake quantiser: every candidate in one kernel pass over each batch
+            fused = None
+            plain = (m._fake_quant and m._block_sizes is None and m.pre_quant_scale is None
+                     and getattr(m, "_bias", None) is None and not getattr(m, "_rotate", False))
+            if plain and (isinstance(m._num_bits, int) or tuple(m._num_bits) == (4, 3)):
+                fused = {"num_bits": m._num_bits, "unsigned": m._unsigned, "narrow_range": m._narrow_range}
             m._calibrator = MseCalibrator(amax=m._amax.clone().detach(), axis=m._calibrator._axis,
                                           num_steps=num_steps, start_multiplier=start_multiplier,
-                                          stop_multiplier=stop_multiplier, quant_func=quant_func)
+                                          stop_multiplier=stop_multiplier, quant_func=quant_func, fused=fused)
     enable_stats_collection(model)
     if forward_loop is None:
         weight_only_quantize(model)

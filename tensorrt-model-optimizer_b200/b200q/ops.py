@@ -453,6 +453,52 @@ def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None
     return out
 
 
+# --------------------------------------------------------------------------- MSE search --------
+
+def mse_candidates_supported(x: torch.Tensor, axis) -> bool:
+    """Layouts the one-pass candidate kernel covers: per tensor, or one channel axis with at least 32
+    sixteen-byte packs of contiguous elements behind it."""
+    if not x.is_cuda or x.dtype not in _DT:
+        return False
+    if axis is None:
+        return True
+    if not isinstance(axis, int):
+        return False
+    inner = 1
+    for d in x.shape[axis % x.dim() + 1:]:
+        inner *= d
+    per_pack = 16 // x.element_size()
+    return inner % per_pack == 0 and inner >= 32 * per_pack
+
+
+def mse_candidates(x: torch.Tensor, cand: torch.Tensor, loss: torch.Tensor, axis=None, num_bits=8,
+                   unsigned: bool = False, narrow_range: bool = True) -> torch.Tensor:
+    """loss[s, c] (float64) += squared fake-quantisation error of x (taken as fp32) under candidate amax
+    cand[s, c] (fp32), every candidate in one pass over x.  ``num_bits`` an int, or (4, 3) for FP8 E4M3."""
+    x = _prep(x)
+    if axis is None:
+        outer, channels, inner = 1, 1, x.numel()
+    else:
+        ax = axis % x.dim()
+        outer = inner = 1
+        for d in x.shape[:ax]:
+            outer *= d
+        for d in x.shape[ax + 1:]:
+            inner *= d
+        channels = x.shape[ax]
+    cand = cand.detach().to(device=x.device, dtype=torch.float32).contiguous()
+    s = cand.numel() // channels
+    assert cand.numel() == s * channels and loss.dtype == torch.float64 and loss.numel() == s * channels
+    assert loss.is_cuda and loss.is_contiguous()
+    fp8 = not isinstance(num_bits, int)
+    if fp8 and tuple(num_bits) != (4, 3):
+        raise ValueError("mse_candidates covers integer formats and E4M3")
+    with torch.cuda.device(x.device):
+        call("b200q_mse_candidates", x.data_ptr(), outer, channels, inner, dtype_code(x), cand.data_ptr(), s,
+             1 if fp8 else 0, 8 if fp8 else num_bits, int(unsigned), int(narrow_range), loss.data_ptr(), _stream(x))
+    return loss
+
+
 # --------------------------------------------------------------------------- awq_lite ----------
 
 def awq_scale_fake_int(w: torch.Tensor, s: torch.Tensor, block: int, num_bits: int = 4,
