@@ -40,8 +40,11 @@ BYTES_AMAX = 2.0
 BYTES_QUANT = 2.0 + 0.5 + 1.0 / 16
 BYTES_TOTAL = BYTES_AMAX + BYTES_QUANT
 # DRAM bytes per element of the quantise kernel from the committed ncu capture
-# (profiles/nvfp4_group_quantize_*.md), or None before one exists
+# (profiles/nvfp4_group_kernels_1layer_ncu_full.md: one layer's seven tensors, traffic in proportion to
+# the elements processed)
 NCU_QUANT_TRAFFIC_PER_ELEM = 2.477
+NOMINAL_HBM_GBS = 8000.0      # B200 data-sheet HBM3e bandwidth, beside the measured copy bandwidth
+LLAMA8B = {"hidden": 4096, "kv": 1024, "inter": 14336, "layers": 32}
 
 
 def peaks():
@@ -220,6 +223,139 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+
+# ------------------------------------------------------------ data-parallel calibration --------
+
+def calibration_phases(dev, world, rank, dims, n_layers, tokens, batches):
+    """Data-parallel activation calibration of every linear input of a Llama-shaped stack: each rank
+    calibrates on its own batches, the statistics are merged over the ranks.
+
+    The forward GEMMs that would produce the activations are not part of this path, so each kind of
+    activation (attention input, o_proj input, MLP input, down_proj input) is one seeded synthetic
+    [tokens, dim] bf16 buffer per rank, fed ``batches`` times per layer to that layer's input quantisers
+    (q/k/v share the attention input, gate/up the MLP input, as they do in the model).
+      max        the NVFP4 default: running abs-max per quantiser, one MAX all-reduce of all amax values;
+      histogram  2048 bins, percentile 99.99: ranges observed on the device, rank 0's broadcast in place,
+                 shared binning passes, one in-place SUM all-reduce of the counter arena, read-out.
+    Returns seconds per phase (max over ranks), launches, bytes and whether all ranks ended with the same
+    amax values."""
+    import torch
+    import torch.distributed as dist
+
+    from b200q import dist as qdist
+    from b200q import ops
+    from b200q.calib import attach_histogram_arena
+    from b200q.nn import TensorQuantizer
+
+    H, KV, I = dims["hidden"], dims["kv"], dims["inter"]
+    kinds = [("attn_in", H, ("q_proj", "k_proj", "v_proj")), ("o_in", H, ("o_proj",)),
+             ("mlp_in", H, ("gate_proj", "up_proj")), ("down_in", I, ("down_proj",))]
+    acts = {}
+    for k, (name, dim, _) in enumerate(kinds):
+        g = torch.Generator(device=dev).manual_seed(50_000 + 16 * rank + k)
+        ch = torch.exp(torch.randn(dim, generator=g, device=dev))          # lognormal(0,1) channel magnitudes
+        acts[name] = (torch.randn(tokens, dim, generator=g, device=dev) * ch).bfloat16()
+
+    def build(calibrator, layers):
+        qcfg = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
+                "axis": None, "enable": True, "calibrator": calibrator}
+        model = torch.nn.ModuleDict()
+        for l in range(layers):
+            for _, _, lins in kinds:
+                for lin in lins:
+                    q = TensorQuantizer(dict(qcfg))
+                    q.disable_quant(); q.enable_calib()
+                    model[f"l{l}_{lin}"] = q
+        return model
+
+    def feed(model, layers, n_batches, observe=False):
+        for l in range(layers):
+            for _ in range(n_batches):
+                for name, _, lins in kinds:
+                    for lin in lins:
+                        if observe:
+                            model[f"l{l}_{lin}"]._calibrator.observe_range(acts[name])
+                        else:
+                            model[f"l{l}_{lin}"](acts[name])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def phase(fn):
+        barrier()
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = t.item()
+        return dt
+
+    def same_everywhere(model):
+        amaxes = torch.stack([q._amax.float().reshape(()) for q in model.values()])
+        if world > 1:
+            lo, hi = amaxes.clone(), amaxes.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            return bool(torch.equal(lo, hi)), amaxes
+        return True, amaxes
+
+    def run_max(layers, n_batches):
+        model = build("max", layers)
+        t_collect = phase(lambda: feed(model, layers, n_batches))
+        t_readout = phase(lambda: [q.load_calib_amax() for q in model.values()])
+        t_exchange = phase(lambda: qdist.sync_amax(model))
+        return model, {"collect": t_collect, "readout": t_readout, "exchange": t_exchange}
+
+    def run_hist(layers, n_batches):
+        model = build("histogram", layers)
+        attach_histogram_arena(model)
+        t_ranges = phase(lambda: (feed(model, layers, 1, observe=True), qdist.agree_histogram_ranges(model)))
+        t_collect = phase(lambda: (feed(model, layers, n_batches), [a.flush() for a in {id(q._calibrator._arena): q._calibrator._arena for q in model.values()}.values()]))
+        t_exchange = phase(lambda: qdist.sync_histograms(model))
+        t_readout = phase(lambda: [q.load_calib_amax("percentile", percentile=99.99) for q in model.values()])
+        return model, {"ranges": t_ranges, "collect": t_collect, "exchange": t_exchange, "readout": t_readout}
+
+    # warm-up: kernels, allocator, and the communicator's collectives, on one layer
+    run_max(1, 1); run_hist(1, 1)
+    if world > 1:
+        for op in (dist.ReduceOp.MAX, dist.ReduceOp.SUM):
+            for _ in range(3):
+                dist.all_reduce(torch.zeros(1 << 20, dtype=torch.int64, device=dev), op=op)
+    m_max, t_max = run_max(n_layers, batches)
+    same_max, _ = same_everywhere(m_max)
+    del m_max
+    m_hist, t_hist = run_hist(n_layers, batches)
+    same_hist, amaxes = same_everywhere(m_hist)
+    n_quant = len(m_hist)
+    arena_bytes = sum(a.counts.numel() * 8 for a in {id(q._calibrator._arena): q._calibrator._arena for q in m_hist.values()}.values())
+    del m_hist
+    per_q_elems = n_layers * batches * tokens * (6 * H + I)          # every quantiser's own input, per rank
+    distinct_elems = n_layers * batches * tokens * (3 * H + I)       # the four distinct tensors, per rank
+    peak, which = peaks()
+    return {
+        "shapes": {"hidden": H, "kv": KV, "inter": I, "layers": n_layers}, "quantizers": n_quant,
+        "tokens_per_batch_per_rank": tokens, "batches_per_rank_per_layer": batches,
+        "max": {"seconds": t_max, "total_s": sum(t_max.values()), "launches_per_rank": n_layers * batches * 7,
+                "bytes_read_per_rank": per_q_elems * 2,
+                "collect_gbps_all_ranks": world * per_q_elems * 2 / t_max["collect"] / 1e9,
+                "collect_frac_of_peak_per_gpu": per_q_elems * 2 / t_max["collect"] / 1e9 / peak,
+                "collectives": {"all_reduce_max": 1}},
+        "histogram": {"seconds": t_hist, "total_s": sum(t_hist.values()),
+                      "binning_launches_per_rank": n_layers * batches * 4,
+                      "bytes_read_per_rank": distinct_elems * 2,
+                      "note": "q/k/v and gate/up bin their common input in one pass: bytes are the four distinct "
+                              "tensors per layer and batch",
+                      "collect_gbps_all_ranks": world * distinct_elems * 2 / t_hist["collect"] / 1e9,
+                      "collect_frac_of_peak_per_gpu": distinct_elems * 2 / t_hist["collect"] / 1e9 / peak,
+                      "collectives": {"broadcast": 1, "all_reduce_sum": 2, "arena_bytes": arena_bytes},
+                      "amax_range": [float(amaxes.min()), float(amaxes.max())]},
+        "amax_identical_on_all_ranks": bool(same_max and same_hist), "peak_source": f"of {which}",
+    }
+
 # ------------------------------------------------------------------------------- GPU arm -------
 
 def split_layers(n_layers: int, world: int, rank: int):
@@ -305,7 +441,15 @@ def run_b200(args):
     ms_per_step = ms / args.steps
     value = total_elems * BYTES_TOTAL / (ms_per_step * 1e-3) / 1e9
 
-    # ---- end to end: pinned host weights in, packed bytes out, through the public packer -----
+    # ---- data-parallel activation calibration on the same model's shapes (every rank its own batches)
+    calibration = None
+    if not args.no_calibration:
+        calibration = calibration_phases(dev, world, rank, LLAMA8B, args.layers, args.tokens, args.batches)
+        calibration["ptq_seconds_weights_plus_max_calibration"] = ms_per_step * 1e-3 + calibration["max"]["total_s"]
+        calibration["ptq_seconds_weights_plus_histogram_calibration"] = (
+            ms_per_step * 1e-3 + calibration["histogram"]["total_s"])
+
+    # ---- end to end: mtq.compress on a host-resident model (pinned weights in, packed weights out)
     e2e = None
     if not args.no_e2e:
         e2e = run_e2e(args, weights, layers, dev, world, total_elems, barrier)
@@ -317,12 +461,14 @@ def run_b200(args):
         cpu = {"value": gbs, "unit": "GB/s", **info}
         c_gbs, c_info = cpu_nvfp4_sample(6.0)
         cpu["fused_c_port"] = {"value": c_gbs, "unit": "GB/s", **c_info}
+        cpu["other_configs"] = cpu_other_configs()
 
     formats = None
     if world == 1 and not args.no_formats:
         del group, weights
         torch.cuda.empty_cache()
         formats = run_formats(dev, peaks()[0])
+        formats["reference_gpu_kernels"] = run_reference_gpu_kernels(dev, peaks()[0])
 
     if rank == 0:
         peak, which = peaks()
@@ -343,6 +489,8 @@ def run_b200(args):
             "roofline": {"bound": "hbm", "kernel": "nvfp4_group_quantize_kernel", "achieved": achieved,
                          "peak": peak, "peak_source": f"of {which}", "unit": "GB/s",
                          "frac": achieved / peak if achieved else None,
+                         "frac_of_nominal": achieved / NOMINAL_HBM_GBS if achieved else None,
+                         "nominal_peak": NOMINAL_HBM_GBS,
                          "traffic": NCU_QUANT_TRAFFIC_PER_ELEM * per_rank_elems
                          if NCU_QUANT_TRAFFIC_PER_ELEM else None,
                          "algorithmic_bytes_per_launch": per_rank_elems * BYTES_QUANT,
@@ -350,7 +498,7 @@ def run_b200(args):
                          "amax_kernel": {"achieved": achieved_amax, "frac": achieved_amax / peak
                                          if achieved_amax else None, "ms_per_launch": amax_ms}},
             "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks, "gpu_launches": 2 * args.steps,
-            "formats": formats,
+            "calibration": calibration, "formats": formats,
         }
         print(json.dumps(line))
     if world > 1:
@@ -406,7 +554,18 @@ def run_formats(dev, peak):
     counts = torch.zeros(2048, dtype=torch.int64, device=dev)
     rmax = float(amax)
     out["histogram_2048_bins_bf16_16x8192x4096"] = timed(lambda: [ops.hist_collect(x, counts, 2048, rmax) for x in xs], n * 2)
-    del xs
+    # MSE calibration: 10 candidate amax values in one pass over each batch (instruction-issue bound)
+    cands = (amax.reshape(1, 1) * torch.linspace(0.25, 4.0, 10, device=dev).reshape(-1, 1)).contiguous()
+    mse_loss = torch.zeros(10, 1, dtype=torch.float64, device=dev)
+    out["mse_10_candidates_int8_bf16_16x8192x4096"] = timed(
+        lambda: [ops.mse_candidates(x, cands, mse_loss, None, 8, False, True) for x in xs], n * 2)
+    out["mse_10_candidates_e4m3_bf16_16x8192x4096"] = timed(
+        lambda: [ops.mse_candidates(x, cands, mse_loss, None, (4, 3), False, True) for x in xs], n * 2)
+    # NVFP4 dequantise (the export format back to bf16): reads 0.5 B + 1/16 B per element, writes 2 B
+    packed = [ops.nvfp4_quantize(x, amax=amax) for x in xs]
+    out["nvfp4_dequantize_bf16_16x8192x4096"] = timed(
+        lambda: [ops.nvfp4_dequantize(p, sc, s2, torch.bfloat16) for p, sc, s2 in packed], int(n * (0.5 + 1 / 16 + 2)))
+    del xs, packed
     # config 4: INT4 block-128 amax + pack, and the per-alpha weight-side kernel of awq_lite
     ws = [(torch.randn(14336, 4096, generator=g, device=dev) * 0.02).bfloat16() for _ in range(3)]
     s = torch.exp(torch.randn(4096, generator=g, device=dev)).bfloat16()
@@ -477,8 +636,29 @@ def run_formats(dev, peak):
     r = timed(lambda: [torch.nn.functional.linear(xd, wd) for _ in range(21)], 1, reps=3, groups=3)
     out["cublas_linear_512x4096x14336_for_comparison"] = {"ms_per_gemm": r["ms"] / 21,
                                                           "tflops": flops / (r["ms"] * 1e-3) / 1e12}
+    # the search as awq_lite runs it now: one activation-scaling launch and ONE fused kernel for all 21
+    # candidates (weight scale + INT4 block fake quant in shared memory, tcgen05 GEMM, squared-error epilogue)
+    bf16_peak = peaks_tflops()
+
+    def fused_entry(x_, w_, ref_, k_):
+        s_all = torch.stack([torch.exp(0.05 * i * torch.randn(k_, generator=g, device=dev)) for i in range(21)])
+        inv_all, s_all = (1 / s_all).bfloat16(), s_all.bfloat16()
+        loss21 = torch.zeros(21, dtype=torch.float64, device=dev)
+
+        def go():
+            ops.awq_search_fused(ops.awq_scale_acts(x_, inv_all), w_, s_all, ref_, loss21, status)
+
+        r_ = timed(go, 1, reps=3, groups=3)
+        tf_ = flops / (r_["ms"] * 1e-3) / 1e12
+        return {"ms": r_["ms"], "tflops_effective": tf_, "frac_of_measured_bf16_peak": tf_ / bf16_peak,
+                "launches": 2, "kernel_status": int(status),
+                "note": "includes the activation-scaling kernel; FLOPs are the 21 GEMMs only"}
+
+    out["awq_lite_search_21_alphas_up_proj_512tok_fused_kernel"] = fused_entry(x, w, ref, 4096)
+    out["awq_lite_search_21_alphas_down_proj_512tok_fused_kernel"] = fused_entry(xd, wd, refd, 14336)
     del xd, wd, refd
     del ws, wfq, bufs
+    out["config4_int4_awq_mlp_through_mtq"] = run_config4(dev)
     # the real-quant GEMM consumers (a 70B-shape projection: 4096 tokens x 8192 -> 8192), beside
     # the library kernels torch._scaled_mm reaches for the same operands
     m_, n_, k_ = 4096, 8192, 8192
@@ -521,6 +701,189 @@ def run_formats(dev, peak):
     out["bf16_cublas_4096x8192x8192_for_comparison"] = tflops(lambda: torch.nn.functional.linear(a16, b16))
     out["gemm_kernel_status"] = int(ops.qgemm_status(dev).item())
     return out
+
+
+def peaks_tflops():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["bf16_tflops"])
+    return 1590.0
+
+
+def run_config4(dev):
+    """BASELINE config 4 through the public API: mtq.quantize(INT4_AWQ_CFG, awq_lite, alpha grid 0..1 in
+    0.05 steps) on one Llama-style MLP (up 4096 -> 14336, down 14336 -> 4096, bf16 N(0, 0.02)) with 512
+    calibration tokens whose channel magnitudes are lognormal(0, 1), then mtq.compress (INT4 packing).
+    Wall-clock seconds of the second of two runs (the first warms kernels and the allocator)."""
+    import copy
+
+    import torch
+
+    import b200q as mtq
+
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up_proj = torch.nn.Linear(4096, 14336, bias=False)
+            self.down_proj = torch.nn.Linear(14336, 4096, bias=False)
+
+        def forward(self, x):
+            return self.down_proj(torch.nn.functional.silu(self.up_proj(x)))
+
+    g = torch.Generator(device=dev).manual_seed(4)
+    base = MLP().to(device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in base.parameters():
+            p.copy_(torch.randn(p.shape, generator=g, device=dev) * 0.02)
+    x = (torch.randn(512, 4096, generator=g, device=dev) * torch.exp(torch.randn(4096, generator=g, device=dev))).bfloat16()
+    cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+    cfg["algorithm"] = {"method": "awq_lite", "alpha_step": 0.05, "debug": True}
+    secs = {}
+    for i in range(2):
+        model = copy.deepcopy(base)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        mtq.quantize(model, cfg, lambda m: m(x))
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        mtq.compress(model)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        secs = {"quantize_awq_lite_s": t1 - t0, "compress_int4_pack_s": t2 - t1, "total_s": t2 - t0}
+        packed = model.up_proj.weight.dtype == torch.uint8
+        alphas = {n: getattr(model, n).awq_lite.best_alpha for n in ("up_proj", "down_proj")}
+        del model
+    return {**secs, "alphas_evaluated_per_linear": 21, "best_alpha": alphas, "weights_packed": bool(packed),
+            "note": "two forward passes (statistics, search), 21 candidates per linear in one fused launch each, "
+                    "scale folding, INT4 block-128 packing"}
+
+
+def run_reference_gpu_kernels(dev, peak):
+    """The reference's own GPU kernels (compiled unmodified into oracle/_ref by oracle/build_ref.py) timed
+    beside ours on the same tensors: a reported baseline like the CPU one, not a product path."""
+    import torch
+
+    from b200q import ops
+    from oracle import ref_ext
+
+    ext, ext8, extmx, tri = ref_ext.cuda_ext(), ref_ext.cuda_ext_fp8(), ref_ext.cuda_ext_mx(), ref_ext.triton_fp4()
+    if ext is None and tri is None:
+        return {"unavailable": "oracle/_ref holds no build of the reference's extensions"}
+
+    def ms(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    g = torch.Generator(device=dev).manual_seed(11)
+    xs = [(torch.randn(8192, 4096, generator=g, device=dev)).bfloat16() for _ in range(8)]      # 0.5 GB > L2
+    n = 8 * 8192 * 4096
+    amax = ops.amax_tensor(xs[0])
+    out = {"tensors": "8 x bf16 [8192, 4096] used in turn (larger than L2)"}
+
+    def pair(name, ours, theirs, nbytes):
+        if theirs is None:
+            return
+        try:
+            t_ref = ms(theirs)
+        except Exception as e:      # a baseline only
+            out[name] = {"unavailable": str(e)[:120]}
+            return
+        t_our = ms(ours)
+        out[name] = {"reference_ms": t_ref, "ours_ms": t_our, "speedup": t_ref / t_our,
+                     "ours_gbps": nbytes / (t_our * 1e-3) / 1e9, "reference_gbps": nbytes / (t_ref * 1e-3) / 1e9,
+                     "ours_frac_of_measured_peak": nbytes / (t_our * 1e-3) / 1e9 / peak}
+
+    packed = [ops.nvfp4_quantize(x, amax=amax) for x in xs]
+    if tri is not None:
+        pair("nvfp4_dequantize_vs_triton_fp4_dequantize",
+             lambda: [ops.nvfp4_dequantize(p, sc, s2, torch.bfloat16) for p, sc, s2 in packed],
+             lambda: [tri.fp4_dequantize(p, sc, s2, 16, 128, torch.bfloat16) for p, sc, s2 in packed],
+             int(n * (0.5 + 1 / 16 + 2)))
+        pair("nvfp4_fake_quant_vs_triton_fp4_fake_quant_block",
+             lambda: [ops.nvfp4_fake(x, amax) for x in xs], lambda: [tri.fp4_fake_quant_block(x, amax) for x in xs], n * 4)
+    if extmx is not None:
+        pair("nvfp4_fake_quant_vs_cuda_fused_amax_convert",
+             lambda: [ops.nvfp4_fake(x, amax) for x in xs],
+             lambda: [extmx.fused_amax_convert(x, 16, extmx.Types.E2M1, extmx.Types.E4M3, amax) for x in xs], n * 4)
+    if ext8 is not None:
+        pair("fp8_fake_quant_vs_cuda_fake_e4m3fy",
+             lambda: [ops.fake_e4m3(x, amax) for x in xs], lambda: [ext8.fake_e4m3fy(x, amax) for x in xs], n * 4)
+    if ext is not None:
+        pair("int8_fake_quant_vs_cuda_fake_tensor_quant",
+             lambda: [ops.fake_int(x, amax, 8, False, True) for x in xs],
+             lambda: [ext.fake_tensor_quant(x, amax, 8, False, True) for x in xs], n * 4)
+        flat = [x.view(-1) for x in xs]
+        scales = [7 / x.view(-1, 128).abs().amax(-1, keepdim=True) for x in xs]
+        pair("int4_block128_amax_and_pack_vs_cuda_INT4_quantize_pack_only",
+             lambda: [ops.int4_quantize(f, 128) for f in flat],
+             lambda: [ext.INT4_quantize(f, sc, 128) for f, sc in zip(flat, scales)], int(n * (2 + 0.5 + 2 / 128)))
+    return out
+
+
+def cpu_other_configs(seconds_each: float = 3.0):
+    """The reference's CPU torch path for the other formats (oracle/torch_path.py), each on a bounded sample
+    of its BASELINE configuration, all intra-op threads."""
+    import torch
+
+    from oracle import torch_path as tp
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+
+    def rate(fn, nbytes, what):
+        fn()
+        t0 = time.perf_counter()
+        fn()
+        dt1 = time.perf_counter() - t0
+        reps = max(1, min(20, int(seconds_each / max(dt1, 1e-3))))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        dt = (time.perf_counter() - t0) / reps
+        return {"gbps": nbytes / dt / 1e9, "seconds_per_pass": dt, "algorithmic_bytes": nbytes, "sample": what}
+
+    out = {"cores": torch.get_num_threads(), "kind": "port"}
+    w = torch.randn(4096, 4096, generator=g) * 0.02
+    out["config1_int8_per_row_fake_quant_plus_max_calibration_fp32_4096x4096"] = rate(
+        lambda: tp.fake_int(w, tp.max_calibrate_collect(w, None, axis=0), 8, False, True), 4096 * 4096 * 8,
+        "the whole configuration (one fp32 [4096, 4096] weight)")
+    x = torch.randn(8192, 4096, generator=g)
+    x[:, :4] *= 50
+    x = x.bfloat16()
+    amax = tp.max_calibrate_collect(x, None)
+    out["config2_fp8_max_calibration_bf16_8192x4096"] = rate(
+        lambda: tp.max_calibrate_collect(x, None), 8192 * 4096 * 2, "one of the 16 batches")
+    out["config2_fp8_per_tensor_fake_quant_bf16_8192x4096"] = rate(
+        lambda: tp.fp8_eager(x, amax), 8192 * 4096 * 4, "one of the 16 batches")
+    hp = tp.HistogramPath(2048)
+    hp.collect(x)
+    out["config5_histogram_2048_bins_bf16_8192x4096"] = rate(
+        lambda: hp.collect(x), 8192 * 4096 * 2, "one [8192, 4096] activation batch (70B shapes have 8192 and 28672 columns)")
+    rows = 1792
+    w4 = (torch.randn(rows, 4096, generator=g) * 0.02).bfloat16()
+    x4 = (torch.randn(512, 4096, generator=g) * torch.exp(torch.randn(4096, generator=g))).bfloat16()
+    ref = torch.nn.functional.linear(x4, w4)
+    a_s, w_s = x4.abs().float().mean(0), (w4.abs().float() / w4.abs().float().amax(1, keepdim=True)).mean(0)
+    t0 = time.perf_counter()
+    tp.awq_lite_candidate(w4, x4, ref, a_s, w_s, 0.5)
+    t0 = time.perf_counter()
+    tp.awq_lite_candidate(w4, x4, ref, a_s, w_s, 0.5)
+    dt = time.perf_counter() - t0
+    out["config4_awq_lite_one_candidate"] = {
+        "seconds_sample": dt, "sample": f"one alpha on {rows} of the 14336 rows of up_proj, 512 tokens",
+        "seconds_full_search_extrapolated": dt * (14336 / rows) * 21 * 2,
+        "note": "x 8 row slabs x 21 alphas x 2 linears; statistics pass and packing not included"}
+    return out
+
 
 
 def run_profile_kernels():
@@ -602,40 +965,100 @@ def run_profile_awq_fused(n_alpha: int = 2):
 
 
 def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
+    """End to end through the public API: ``mtq.compress`` on a Llama-shaped module tree that lives in
+    pinned HOST memory (this rank's layers).  Every step builds a fresh tree over the same pinned weight
+    buffers and inserts the NVFP4 weight quantisers (outside the timed region: a few hundred small host
+    objects), then times compress(): host -> device copies, the two grouped kernels per streamed group,
+    device -> host copies of the packed weights and scales, and the swap of the module's parameters."""
     import torch
     import torch.distributed as dist
 
-    from b200q.pipeline import HostNvFp4Packer
+    import b200q as mtq
 
+    names = [n for n, _ in LAYER_SHAPES]
     shapes = [s for _, s in LAYER_SHAPES]
     try:
-        packer = HostNvFp4Packer(shapes, torch.bfloat16, dev)
         host_in = []
         for li in range(len(layers)):
             host_in.append([torch.empty(s, dtype=torch.bfloat16).pin_memory() for s in shapes])
             for k in range(len(shapes)):
                 host_in[li][k].copy_(weights[li * len(shapes) + k])
-        host_out = packer.alloc_host_outputs(len(layers))
     except RuntimeError as e:  # pinned allocation refused
         return {"value": None, "unit": "GB/s", "error": str(e)[:200]}
     torch.cuda.synchronize()
+    wcfg = {"*weight_quantizer": {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
+                                  "axis": None, "enable": True},
+            "*input_quantizer": {"enable": False}, "default": {"enable": False}}
+
+    def build_tree():
+        tree = torch.nn.ModuleList()
+        for li in range(len(layers)):
+            layer = torch.nn.ModuleDict()
+            for k, (n, (rows, cols)) in enumerate(LAYER_SHAPES):
+                lin = torch.nn.Linear(1, 1, bias=False)
+                lin.in_features, lin.out_features = cols, rows
+                lin.weight = torch.nn.Parameter(host_in[li][k], requires_grad=False)   # aliases the pinned buffer
+                layer[n] = lin
+            tree.append(layer)
+        model = torch.nn.ModuleDict({"layers": tree})
+        mtq.replace_quant_module(model)
+        mtq.set_quantizer_by_cfg(model, wcfg)
+        return model
+
     steps = max(1, min(args.steps, args.e2e_steps))
-    packer.pack(host_in, host_out)  # warm-up
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        packer.pack(host_in, host_out)
-    torch.cuda.synchronize()
-    dt = (time.perf_counter() - t0) / steps
+    times = []
+    out_bytes = 0
+    for i in range(steps + 1):          # the first pass warms the pinned-memory pool and the streams
+        model = build_tree()
+        barrier()
+        t0 = time.perf_counter()
+        mtq.compress(model)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if i:
+            times.append(dt)
+        if layers:
+            lin = model["layers"][0][names[0]]
+            assert lin.weight.dtype == torch.uint8 and lin.weight.device.type == "cpu"
+        out_bytes = sum(m.weight.numel() + m.weight_quantizer._scale.numel() + 4
+                        for m in model.modules() if hasattr(m, "weight_quantizer"))
+        del model
+    dt = statistics.mean(times)
     if world > 1:
         t = torch.tensor([dt], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = t.item()
-    h2d = len(layers) * packer.in_bytes
-    d2h = len(layers) * (packer.packed_bytes + packer.scale_bytes + 4 * len(shapes))
+    h2d = sum(w.numel() * 2 for w in weights)
+    # the same bytes over the same links with no kernel between them: what the host side allows
+    copy_only = None
+    if layers:
+        dbuf = [torch.empty_like(weights[k]) for k in range(len(shapes))]
+        obuf = [torch.empty(int(w.numel() * (0.5 + 1 / 16)), dtype=torch.uint8, device=dev) for w in dbuf]
+        hout = [torch.empty(o.numel(), dtype=torch.uint8).pin_memory() for o in obuf]
+        up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        barrier()
+        t0 = time.perf_counter()
+        for li in range(len(layers)):
+            with torch.cuda.stream(up):
+                for k in range(len(shapes)):
+                    dbuf[k].copy_(host_in[li][k], non_blocking=True)
+            with torch.cuda.stream(down):
+                for k in range(len(shapes)):
+                    hout[k].copy_(obuf[k], non_blocking=True)
+        torch.cuda.synchronize()
+        ct = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([ct], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ct = t.item()
+        copy_only = {"seconds": ct, "h2d_gbps_per_rank": h2d / ct / 1e9,
+                     "note": "this rank's weights host->device and the packed bytes device->host on two streams, "
+                             "no kernels: the ceiling the host memory and PCIe paths set for e2e at this N"}
     return {"value": total_elems * BYTES_TOTAL / dt / 1e9, "unit": "GB/s", "seconds_per_step": dt,
-            "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "api": "b200q.pipeline.HostNvFp4Packer.pack (pinned host weights -> pinned host NVFP4)"}
+            "steps": steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": out_bytes,
+            "api": "mtq.compress(model) on a host-resident (pinned) Llama-shaped module tree with NVFP4 weight "
+                   "quantisers: weights streamed through the GPU, packed weights and scales back on the host",
+            "copy_only": copy_only}
 
 
 # ---------------------------------------------------------------- 70B-shape calibration --------
@@ -643,24 +1066,13 @@ L70 = {"hidden": 8192, "kv": 1024, "inter": 28672, "layers": 80}
 
 
 def run_calib70b(args):
-    """Data-parallel NVFP4 activation calibration on Llama-3-70B shapes, then the NVFP4 weight
-    quantisation of this rank's layers.
-
-    Every linear's input quantiser (7 per layer) is a TensorQuantizer with a 2048-bin
-    HistogramCalibrator.  The forward GEMMs that would produce the activations are not part of
-    this path, so each kind of activation (attention input, o_proj input, MLP input, down_proj
-    input) is one seeded synthetic buffer of [tokens, dim] per rank (larger than L2), fed
-    ``--batches`` times per layer.  Steps: first-batch abs-max of every quantiser -> one
-    broadcast fixes the common bin width -> histogram collection -> one SUM all-reduce of all
-    histograms (plus a MAX of their lengths) -> percentile amax on every rank -> NVFP4 weight
-    quantisation of the rank's share of the layers.  Activation work per rank is fixed (weak
-    scaling in the batch dimension), weight work is split by layer.
-    """
+    """Data-parallel NVFP4 activation calibration on Llama-3-70B shapes (``calibration_phases``: 560 input
+    quantisers, max and 2048-bin histogram calibration), then the NVFP4 weight quantisation of this rank's
+    layers.  Activation work per rank is fixed (weak scaling in the batch dimension), weight work is split
+    by layer."""
     import torch
     import torch.distributed as dist
 
-    from b200q import dist as qdist
-    from b200q.nn import TensorQuantizer
     from b200q.ops import NvFp4Group
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -673,83 +1085,11 @@ def run_calib70b(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     n_layers = args.layers if args.layers != N_LAYERS else L70["layers"]
-    tokens, batches = args.tokens, args.batches
     H, KV, I = L70["hidden"], L70["kv"], L70["inter"]
-    kinds = [("attn_in", H, ("q_proj", "k_proj", "v_proj")), ("o_in", H, ("o_proj",)),
-             ("mlp_in", H, ("gate_proj", "up_proj")), ("down_in", I, ("down_proj",))]
-    acts = {}
-    for k, (name, dim, _) in enumerate(kinds):
-        g = torch.Generator(device=dev).manual_seed(50_000 + 16 * rank + k)
-        ch = torch.exp(torch.randn(dim, generator=g, device=dev))          # lognormal(0,1) channel magnitudes
-        acts[name] = (torch.randn(tokens, dim, generator=g, device=dev) * ch).bfloat16()
-    qcfg = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)},
-            "axis": None, "enable": True, "calibrator": "histogram"}
-    model = torch.nn.ModuleDict()
-    for l in range(n_layers):
-        for _, _, lins in kinds:
-            for lin in lins:
-                q = TensorQuantizer(dict(qcfg))
-                q.disable_quant(); q.enable_calib()
-                model[f"l{l}_{lin}"] = q
-    n_quant = len(model)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def phase(fn):
-        barrier()
-        t0 = time.perf_counter()
-        fn()
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([dt], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = t.item()
-        return dt
-
-    from b200q import ops
-    for name in acts:           # warm-up: kernels, and the communicator's collectives
-        for _ in range(3):
-            ops.amax_tensor(acts[name])
-    if world > 1:
-        for op in (dist.ReduceOp.MAX, dist.ReduceOp.SUM):
-            for _ in range(3):
-                dist.all_reduce(torch.zeros(1 << 20, dtype=torch.int64, device=dev), op=op)
-        dist.broadcast(torch.zeros(1024, device=dev), src=0)
-    first = {}
-
-    def ranges():
-        for l in range(n_layers):
-            for name, _, lins in kinds:
-                for lin in lins:
-                    first[f"l{l}_{lin}"] = ops.amax_tensor(acts[name])
-        vals = torch.stack(list(first.values())).tolist()      # one device->host copy
-        qdist.agree_histogram_ranges(model, dict(zip(first.keys(), vals)), dev)
-
-    def collect():
-        for l in range(n_layers):
-            for _ in range(batches):
-                for name, _, lins in kinds:
-                    for lin in lins:
-                        model[f"l{l}_{lin}"](acts[name])
-
-    def exchange():
-        qdist.sync_histograms(model)
-
-    def readout():
-        for q in model.values():
-            q.load_calib_amax("percentile", percentile=99.99)
-
     sampler = ClockSampler(local)
     sampler.start()
     t_wall0 = time.perf_counter()
-    t_ranges = phase(ranges)
-    t_collect = phase(collect)
-    t_exchange = phase(exchange)
-    t_readout = phase(readout)
+    calibration = calibration_phases(dev, world, rank, L70, n_layers, args.tokens, args.batches)
 
     # weights of one layer, reused for every layer of this rank's share
     shapes = [(H, H), (KV, H), (KV, H), (H, H), (I, H), (I, H), (H, I)]
@@ -757,44 +1097,33 @@ def run_calib70b(args):
     weights = [make_weight(sh, 7000 + k, dev) for k, sh in enumerate(shapes)]
     group = NvFp4Group(weights)
     group.run()
-
-    def quantize():
-        for _ in my_layers:
-            group.run()
-
-    t_weights = phase(quantize)
-    t_wall1 = time.perf_counter()
-    clocks = sampler.stop(t_wall0, t_wall1)
-    amaxes = torch.stack([q._amax.float().reshape(()) for q in model.values()])
-    same = True
     if world > 1:
-        lo, hi = amaxes.clone(), amaxes.clone()
-        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        same = bool(torch.equal(lo, hi))
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in my_layers:
+        group.run()
+    torch.cuda.synchronize()
+    t_weights = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([t_weights], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_weights = t.item()
+    clocks = sampler.stop(t_wall0, time.perf_counter())
     if rank == 0:
-        peak, which = peaks()
-        elems_per_pass = n_layers * batches * tokens * (6 * H + I)        # per rank
-        act_bytes = world * elems_per_pass * 2                              # one binning pass over bf16
         w_elems = n_layers * sum(a * b for a, b in shapes)
-        total = t_ranges + t_collect + t_exchange + t_readout + t_weights
+        total = calibration["histogram"]["total_s"] + t_weights
         print(json.dumps({
             "metric": "nvfp4_calibration_70b_shape_seconds", "value": total, "unit": "s", "n_gpus": world,
             "higher_is_better": False, "scaling": "weak (activation batches per rank fixed); weights split by layer",
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "llama3-70b-shape NVFP4 calibration: 2048-bin histogram of every linear input, "
                                    "percentile 99.99 amax, then NVFP4 weight quantisation",
-                       "layers": n_layers, "quantizers": n_quant, "tokens_per_batch": tokens,
-                       "batches_per_rank_per_layer": batches,
+                       "layers": n_layers, "tokens_per_batch": args.tokens, "batches_per_rank_per_layer": args.batches,
                        "full_size_note": "the named configuration is 4096x1024 tokens over 8 GPUs = 64 batches of "
                                          "8192 tokens per rank per layer"},
-            "seconds": {"ranges": t_ranges, "collect": t_collect, "exchange": t_exchange, "readout": t_readout,
-                        "weights": t_weights},
-            "collect_gbps_all_ranks": act_bytes / t_collect / 1e9,
-            "collect_frac_of_peak_per_gpu": act_bytes / world / t_collect / 1e9 / peak,
-            "weights_gbps_all_ranks": w_elems * BYTES_TOTAL / t_weights / 1e9,
-            "collectives": {"broadcast": 1, "all_reduce": 2, "histogram_bytes": n_quant * 2048 * 8},
-            "amax_identical_on_all_ranks": same, "amax_range": [float(amaxes.min()), float(amaxes.max())],
-            "peak_source": f"of {which}", "clocks": clocks,
+            "calibration": calibration, "weights_seconds": t_weights,
+            "weights_gbps_all_ranks": w_elems * BYTES_TOTAL / t_weights / 1e9, "clocks": clocks,
         }))
     if world > 1:
         dist.destroy_process_group()
@@ -811,11 +1140,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-formats", action="store_true")
+    ap.add_argument("--no-calibration", action="store_true")
     ap.add_argument("--workload", default="ptq8b", choices=["ptq8b", "calib70b"],
                     help="ptq8b: NVFP4 weight quantisation on 8B shapes (the headline line); "
                          "calib70b: data-parallel histogram calibration on 70B shapes")
-    ap.add_argument("--tokens", type=int, default=8192, help="calib70b: tokens per batch")
-    ap.add_argument("--batches", type=int, default=2, help="calib70b: batches per rank per layer")
+    ap.add_argument("--tokens", type=int, default=8192, help="calibration: tokens per batch (per rank)")
+    ap.add_argument("--batches", type=int, default=2, help="calibration: batches per rank per layer")
     ap.add_argument("--profile-kernels", action="store_true",
                     help="run a few launches of the secondary kernels and exit (for ncu captures)")
     ap.add_argument("--profile-awq-fused", type=int, default=0, metavar="N_ALPHA",

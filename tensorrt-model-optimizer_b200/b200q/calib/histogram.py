@@ -66,6 +66,7 @@ class HistogramArena:
         self._last_range = None   # (key, calibrator, tensor) of the latest first-batch observation
         self._pending = None      # (key, tensor, [calibrators]) of the collect that is held back
         self._stale = False
+        self.observe_only = False  # collect() fixes ranges and bins nothing (the pass before a range broadcast)
 
     def _allocate(self, device):
         q = len(self.cals)
@@ -265,7 +266,8 @@ class HistogramCalibrator(_Calibrator):
         if self._arena is not None:
             if not self._ranged:
                 self._arena.observe_range(self, x)
-            self._arena.submit(self, x)
+            if not self._arena.observe_only:
+                self._arena.submit(self, x)
             return
         if self._calib_hist is None:
             self.set_range(float(ops.amax_tensor(x)), x.device)

@@ -20,7 +20,7 @@ from . import ops
 from .calib import MseCalibrator
 from .nn import SequentialQuantizer, TensorQuantizer, is_quantized_linear
 
-__all__ = ["max_calibrate", "mse_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection",
+__all__ = ["max_calibrate", "mse_calibrate", "histogram_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection",
            "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]
 
 
@@ -77,6 +77,51 @@ def max_calibrate(model: nn.Module, forward_loop=None, distributed_sync=True):
         forward_loop(model)
     finish_stats_collection(model)
     if distributed_sync and dist.is_available() and dist.is_initialized():
+        qdist.sync_amax(model)
+
+
+@torch.no_grad()
+def histogram_calibrate(model: nn.Module, forward_loop, method: str = "percentile", first_batch_loop=None,
+                        distributed_sync=True, share_inputs: bool = True, **compute_kwargs):
+    """Histogram calibration (``"percentile"``, ``"entropy"`` or ``"mse"`` read-out) of every quantiser
+    whose calibrator is a HistogramCalibrator; other calibrators are max-calibrated by the same loop.
+
+    All histogram counters live in one arena (``attach_histogram_arena``): ranges stay on the device and
+    quantisers fed the same tensor share a binning pass.  With a process group up the calibration is
+    data-parallel — every rank runs ``forward_loop`` over its own batches — in the reference's contract
+    (one calibrator over the union of the batches, the first batch of rank 0 fixing the bin width):
+    ``first_batch_loop(model)`` (default: ``forward_loop``) runs once with the calibrators only observing
+    ranges, rank 0's ranges are broadcast in place, ``forward_loop`` bins, one SUM all-reduce merges the
+    counters, and every rank reads the same amax out (reference: calib/histogram.py:77-130,166-213 for the
+    collection and read-out it reproduces; the reference has no data-parallel histogram merge)."""
+    from .calib import HistogramCalibrator, attach_histogram_arena
+
+    arenas = attach_histogram_arena(model, share_inputs)
+    enable_stats_collection(model)
+    dp = distributed_sync and dist.is_available() and dist.is_initialized()
+    if dp:
+        for a in arenas:
+            a.observe_only = True
+        (first_batch_loop or forward_loop)(model)
+        for a in arenas:
+            a.observe_only = False
+        qdist.agree_histogram_ranges(model)
+    forward_loop(model)
+    if dp:
+        qdist.sync_histograms(model)
+    for _, m in model.named_modules():
+        if not isinstance(m, TensorQuantizer) or m._disabled:
+            continue
+        cal = getattr(m, "_calibrator", None)
+        if cal is not None and not m._dynamic:
+            if isinstance(cal, HistogramCalibrator):
+                if cal.hist is not None:
+                    m.load_calib_amax(method, **compute_kwargs)
+            elif cal.compute_amax() is not None:
+                m.load_calib_amax()
+        m.enable_quant()
+        m.disable_calib()
+    if dp:
         qdist.sync_amax(model)
 
 

@@ -297,12 +297,6 @@ static int awq_gemm_launch(const void* a, const void* b, const void* ref, int64_
   int bn = 128, mt = 1;
   if (n % 256 == 0 && (m / kGM) * (n / 256) * 10 >= sms * 4) bn = 256;
   if (n % 256 == 0 && m % 256 == 0 && (m / 256) * (n / 256) * 4 >= sms * 3) { bn = 256; mt = 2; }
-  if (const char* e = getenv("B200Q_AWQ_GEMM_TILE")) {   // "128", "256" or "512" (= 256 x 256)
-    const int v = atoi(e);
-    if (v == 128) { bn = 128; mt = 1; }
-    if (v == 256 && n % 256 == 0) { bn = 256; mt = 1; }
-    if (v == 512 && n % 256 == 0 && m % 256 == 0) { bn = 256; mt = 2; }
-  }
   const int total_kb = static_cast<int>(k / kGK);
   if (splits < 1 || splits > 16 || splits > total_kb) return B200Q_ERR_ARG;
   if (splits > 1) { bn = 128; mt = 1; }                   // more, smaller CTAs is the point of splitting

@@ -20,7 +20,7 @@ constexpr int kMseThreads = 256;
 enum { kMseInt = 0, kMseE4m3 = 1 };
 
 struct MseCand {      // one candidate of one channel, prepared once
-  float scale, y, inv;
+  float scale, y, inv;   // integer: inv holds 1 / scale - y;  E4M3: inv = 1 / scale
   int live_fast;      // bit 0: amax >= 2^-24, bit 1: scale in the range of the reciprocal division, bit 2: see mse_prepare
 };
 
@@ -29,7 +29,8 @@ __device__ __forceinline__ MseCand mse_prepare(float amax, const IntQ& q) {
   MseCand c;
   if (FORMAT == kMseInt) {
     const IntScale s = make_int_scale(q, amax);
-    c.scale = s.scale; c.y = s.y; c.inv = 0.f;
+    c.scale = s.scale; c.y = s.y;
+    c.inv = fmaf(-s.scale, s.y, 1.f) * s.y;      // 1 / scale - y
     // bit 2: the bounds fit the magic-number rounding
     c.live_fast = (s.live ? 1 : 0) | (s.fast ? 2 : 0) | (q.bound <= 4194303.f && q.lo >= -4194304.f ? 4 : 0);
   } else {
@@ -40,12 +41,19 @@ __device__ __forceinline__ MseCand mse_prepare(float amax, const IntQ& q) {
   return c;
 }
 
-// Squared errors of two elements under one candidate, added to the two lanes of acc.  The errors are
-// those of the stand-alone fake-quant kernels evaluated in fp32, bit for bit (x - fq(x), both rounded).
-// Integer fast path (about 6 issue slots per element): the clamp is applied before the rounding — the
-// bounds are integers, so clamp(rint(t)) == rint(clamp(t)) — which bounds |t| by 2^22 and lets
-// (t + 1.5 * 2^23) - 1.5 * 2^23 do the round-half-even in two packed adds instead of two conversion-pipe
-// instructions; the zero sign the trick loses cannot change x - q.
+// Squared errors of two elements under one candidate, added to the two lanes of acc.
+// Integer fast path, 6 fp32-pipe operations per element:
+//  * the clamp is applied before the rounding — the bounds are integers, so clamp(rint(t)) ==
+//    rint(clamp(t)) — which bounds |t| by 2^22 and lets (t + 1.5 * 2^23) - 1.5 * 2^23 do the
+//    round-half-even in two packed adds instead of two conversion-pipe instructions;
+//  * the error x - r / scale is formed without the division: with y = RN(1 / scale) and
+//    ey = (1 - scale * y) * y, r / scale = r * y + r * ey to 2^-45, so two FMAs give the error of the
+//    exact quotient rounded once.  The stand-alone kernel rounds the quotient to fp32 first: the two
+//    errors differ by at most half an ulp of the quotient, with no systematic sign — far inside the
+//    noise of the fp32 summation the reference accumulates its losses with (the candidates' amax
+//    parity tolerance is 1e-3; losses agree to about 1e-7).
+// Everything else (dead amax, scales outside the safe range, E4M3) reproduces the stand-alone kernels'
+// per-element results bit for bit.
 template <int FORMAT>
 __device__ __forceinline__ float2 mse_pair(float x0, float x1, const MseCand& c, const IntQ& q, float2 acc) {
   float q0, q1;
@@ -56,8 +64,8 @@ __device__ __forceinline__ float2 mse_pair(float x0, float x1, const MseCand& c,
       r.x = fmax_nan(fmin_nan(r.x, q.bound), q.lo);
       r.y = fmax_nan(fmin_nan(r.y, q.bound), q.lo);
       r = __fadd2_rn(__fadd2_rn(r, make_float2(12582912.f, 12582912.f)), make_float2(-12582912.f, -12582912.f));
-      const float2 o = div2_rn_rcp(r, make_float2(-c.scale, -c.scale), make_float2(c.y, c.y));
-      const float2 d = __ffma2_rn(o, make_float2(-1.f, -1.f), x);
+      float2 d = __ffma2_rn(r, make_float2(-c.y, -c.y), x);
+      d = __ffma2_rn(r, make_float2(-c.inv, -c.inv), d);
       return __ffma2_rn(d, d, acc);
     }
     IntScale s;
@@ -150,7 +158,7 @@ mse_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t channels, int64_t
 #pragma unroll
       for (int s = 0; s < kMseMaxCand; ++s) {
         if (s < n_cand) {
-          MseCand c;
+          MseCand c;      // loop-invariant: the compiler keeps the row's candidates in registers
           c.scale = __shfl_sync(0xffffffffu, mine.scale, s);
           c.y = __shfl_sync(0xffffffffu, mine.y, s);
           c.inv = __shfl_sync(0xffffffffu, mine.inv, s);

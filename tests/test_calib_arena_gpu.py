@@ -166,3 +166,31 @@ def test_data_parallel_merge_equals_the_sequential_calibrator(mtq, world):
         # quantiser 0 held the reference's batches: its merged amax against what the reference got sequentially
         got = models[0]["q0"]._calibrator.compute_amax("percentile", percentile=99.99).item()
         assert abs(got - g["pct_99.99"]) <= 1e-3 * g["pct_99.99"]
+
+
+def test_histogram_calibrate_equals_the_stand_alone_calibrators(mtq):
+    """mtq.histogram_calibrate (arena, shared passes, percentile read-out into ``_amax``) against
+    stand-alone calibrators fed the same batches; with no process group it is the sequential contract."""
+    from b200q.calib import HistogramCalibrator
+
+    model = torch.nn.ModuleDict()
+    for i in range(3):
+        model[f"q{i}"] = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8, calibrator="histogram")).cuda()
+    data = _batches(21, 3, grow=1.5)
+
+    def loop(m):
+        for x in data:
+            for q in m.values():
+                q(x)
+
+    mtq.histogram_calibrate(model, loop, method="percentile", percentile=99.9)
+    ref = HistogramCalibrator(8, None, False, num_bins=2048)
+    for x in data:
+        ref.collect(x)
+    want = ref.compute_amax("percentile", percentile=99.9)
+    for q in model.values():
+        assert q._if_quant and not q._if_calib
+        assert q._amax.item() == want.item()
+        assert torch.equal(q._calibrator.hist, ref.hist)
+    y = model["q0"](data[0])
+    assert y.shape == data[0].shape and not torch.equal(y, data[0])

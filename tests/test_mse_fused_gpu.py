@@ -2,9 +2,13 @@
 replaces (reference: modelopt/torch/quantization/calib/mse.py:76-100 — per candidate a fake-quant pass,
 ``F.mse_loss(reduction="none")`` and a sum).
 
-The kernel's per-element errors are those of the stand-alone fake-quant kernels in fp32 (bit-identical
-arithmetic); only the order of the float64 summation differs from torch's fp32 reduction, so losses are
-compared at 2e-6 relative against a float64 sum of the loop's per-element errors."""
+Tolerance on the losses, against a float64 sum of the loop's per-element errors:
+|loss - want| <= 1e-5 * want + 2e-7 * sum(x^2).  The integer path forms x - r / scale from the exact
+quotient (two FMAs) where the loop rounds the quotient to fp32 first: per element the error d moves by
+at most half an ulp of the quotient q, so d^2 moves by at most |d| * ulp(q) <= 6e-8 * (d^2 + q^2) — the
+second term of the bound (it only matters where x sits almost on the grid, as 16-bit inputs do).
+Partial sums are fp32 per thread (the first term).  The selected amax — what calibration returns,
+parity tolerance 1e-3 — is asserted equal."""
 import copy
 
 import pytest
@@ -55,9 +59,11 @@ def test_candidates_kernel_equals_the_loop(dtype, shape, axis, fmt):
     loss = torch.zeros(cands.shape, dtype=torch.float64, device="cuda")
     ops.mse_candidates(x, cands, loss, axis, num_bits, unsigned, narrow)
     want = _loop_losses(x, cands, axis, num_bits, unsigned, narrow)
-    assert torch.allclose(loss, want, rtol=2e-6, atol=1e-30), (loss - want).abs().max()
+    energy = (x.double() ** 2).sum() if axis is None else \
+        (x.double() ** 2).sum(dim=[i for i in range(x.dim()) if i != axis]).reshape(1, -1)
+    assert ((loss - want).abs() <= 1e-5 * want + 2e-7 * energy).all(), (loss - want).abs().max()
     ops.mse_candidates(x, cands, loss, axis, num_bits, unsigned, narrow)      # accumulates
-    assert torch.allclose(loss, 2 * want, rtol=2e-6, atol=1e-30)
+    assert ((loss - 2 * want).abs() <= 2e-5 * want + 4e-7 * energy).all()
 
 
 def test_candidates_kernel_dead_and_tiny_amax():
@@ -72,7 +78,7 @@ def test_candidates_kernel_dead_and_tiny_amax():
         ops.mse_candidates(x, cands, loss, None, bits, False, True)
         want = _loop_losses(x, cands, None, bits, False, True)
         assert torch.isfinite(loss).all()
-        assert torch.allclose(loss, want, rtol=2e-6), (bits, loss, want)
+        assert torch.allclose(loss, want, rtol=1e-5), (bits, loss, want)
 
 
 def test_unsupported_layouts_are_refused_and_take_the_loop():

@@ -120,45 +120,71 @@ def _on_a_rounding_boundary(x, where):
     return rel <= 4e-7
 
 
+# one ulp of a 16-bit type; fp32: a block scale one ulp apart moves the rounded product by up to two
+_ULP = {torch.float32: 2.0 ** -22, torch.float16: 2.0 ** -10, torch.bfloat16: 2.0 ** -7}
+
+
+def _split_differences(mine, ref, T):
+    """(different E2M1 code, beyond the last-bit allowance of T without being a code difference).  Neighbouring E2M1
+    values are at least 20 % apart, so 1 % separates a different code from a last-bit difference."""
+    a, b = mine.float(), ref.float()
+    gap = (a - b).abs()
+    big = torch.maximum(a.abs(), b.abs())
+    code = gap > 0.01 * big
+    return code, (gap > 1.01 * _ULP[T] * big) & ~code
+
+
 @pytest.mark.parametrize("T", TS)
-def test_nvfp4_fake_quant_against_the_triton_kernel_of_the_reference(T):
-    """R1 count: elements where the Triton kernel and the torch path (= ours) disagree.  fp32 inputs:
-    below 1e-6 of the elements.  16-bit inputs: exact ties are common (8- and 11-bit significands over a
-    4-bit scale), the approximate division lands just below them, up to 2e-3 of the elements; every one
-    of them sits on a rounding boundary."""
+@pytest.mark.parametrize("seed", [4, 7])
+def test_nvfp4_fake_quant_against_the_triton_kernel_of_the_reference(T, seed):
+    """Where the Triton kernel and the torch path (= ours) disagree.
+    (1) Different codes: the kernel's approximate division lands just beside exact ties of
+    |x| / scale.  fp32 inputs: below 1e-6 of the elements; 16-bit inputs, where exact ties are common
+    (8- and 11-bit significands over a 4-bit scale): up to 2e-3.  Every one sits on a rounding boundary.
+    (2) Last-bit differences of whole tensors: the kernel's wrapper forms scale2 = amax / 2688 on the
+    GPU, where torch multiplies by the rounded reciprocal of a host scalar; the torch path on the CPU —
+    the golden vectors, and our kernel — divides.  The two differ by one ulp for about a quarter of all
+    amax values (seed 4 is one), which shows in fp32 outputs only.  Nothing else differs by more than
+    the last bit of the tensor's type."""
     from b200q import ops
 
     tri = _need(ref_ext.triton_fp4())
-    x, amax = _nvfp4_case(T)
+    x, amax = _nvfp4_case(T, seed)
     mine = ops.nvfp4_fake(x, amax)
     ref = tri.fp4_fake_quant_block(x, amax)
-    diff = mine != ref
-    frac = diff.float().mean().item()
-    assert frac <= (1e-6 if T == torch.float32 else 2e-3), frac
-    if diff.any():
-        assert _on_a_rounding_boundary(x, diff).all()
+    code, beyond = _split_differences(mine, ref, T)
+    assert not beyond.any()
+    frac = code.float().mean().item()
+    same_scale2 = (amax / 2688.0).item() == (amax.cpu() / 2688.0).item()      # GPU: amax * (1 / 2688)
+    if same_scale2:
+        assert frac <= (1e-6 if T == torch.float32 else 2e-3), frac
+        if code.any():
+            assert _on_a_rounding_boundary(x, code).all()
+    else:
+        # a scale2 one ulp apart also moves a few block scales across an E4M3 rounding boundary
+        assert T == torch.float32 and seed == 4
+        assert frac <= 1e-4, frac
+        assert (mine != ref).float().mean().item() > 0.5
 
 
 @pytest.mark.parametrize("T", TS)
 def test_nvfp4_fake_quant_against_the_cuda_kernel_of_the_reference(T):
     """The fast-math CUDA kernel forms the block scale as e4m3(.) / (448 * 6 / amax) in double and
     multiplies by its reciprocal: its block scale can differ from e4m3(.) * (amax / 2688) in the last
-    fp32 bit (visible in fp32 outputs only, as a 1-ulp difference of whole blocks), and its codes differ
-    at rounding boundaries.  Asserted: any difference beyond 2e-7 relative is at a boundary, and those
-    are at most 3e-3 of the elements."""
+    fp32 bit (whole blocks of an fp32 output one ulp apart), and its codes differ at rounding
+    boundaries: at most 3e-3 of the elements, each of them on a boundary."""
     from b200q import ops
 
     ext = _need(ref_ext.cuda_ext_mx())
     x, amax = _nvfp4_case(T)
     mine = ops.nvfp4_fake(x, amax)
     ref = ext.fused_amax_convert(x, 16, ext.Types.E2M1, ext.Types.E4M3, amax)
-    diff = (mine.float() - ref.float()).abs() > 2e-7 * mine.float().abs()
-    if T != torch.float32:
-        assert torch.equal(diff, mine != ref)
-    frac = diff.float().mean().item()
+    code, beyond = _split_differences(mine, ref, T)
+    assert not beyond.any()
+    frac = code.float().mean().item()
     assert frac <= 3e-3, frac
-    if diff.any():
-        assert _on_a_rounding_boundary(x, diff).all()
+    if code.any():
+        assert _on_a_rounding_boundary(x, code).all()
 
 
 @pytest.mark.parametrize("T", TS)
