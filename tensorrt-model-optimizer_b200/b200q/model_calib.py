@@ -20,7 +20,7 @@ from . import ops
 from .calib import MseCalibrator
 from .nn import SequentialQuantizer, TensorQuantizer, is_quantized_linear
 
-__all__ = ["max_calibrate", "mse_calibrate", "histogram_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection",
+__all__ = ["max_calibrate", "mse_calibrate", "histogram_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection", "load_calib_amax_all",
            "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]
 
 
@@ -34,20 +34,45 @@ def enable_stats_collection(model: nn.Module):
                 m.disable()
 
 
+def load_calib_amax_all(items):
+    """Load the calibrated amax of many quantisers with ONE validity read.  ``items``: (name, quantiser,
+    args, kwargs) with the arguments of ``calibrator.compute_amax``.  Quantisers whose calibrator has
+    seen nothing are skipped.  The reference loads and validates quantiser by quantiser
+    (model_calib.py:145-185), one device->host read each; here the values are tested together, per
+    device, and the error names every offending quantiser."""
+    from .calib import MaxCalibrator
+
+    loaded = {}
+    for name, q, args, kwargs in items:
+        cal = q._calibrator
+        extra = {"check": False} if isinstance(cal, MaxCalibrator) else {}
+        value = cal.compute_amax(*args, **kwargs, **extra)
+        if value is None:
+            continue
+        q._store_calib_amax(value)
+        loaded.setdefault(q._amax.device, []).append((name, q))
+    for dev, group in loaded.items():
+        flat = torch.cat([q._amax.detach().reshape(-1).float() for _, q in group])
+        if bool((~torch.isfinite(flat) | (flat < 0)).any()):
+            bad = [n for n, q in group if not q.validate_attr(attr_name="_amax")]
+            raise ValueError(f"calibrated amax of {bad} contains nan, inf or negative values")
+    return sum(len(g) for g in loaded.values())
+
+
 def finish_stats_collection(model: nn.Module, method: str | None = None):
-    for _, m in model.named_modules():
+    items, done = [], []
+    for name, m in model.named_modules():
         if not isinstance(m, TensorQuantizer) or m._disabled:
             continue
         cal = getattr(m, "_calibrator", None)
         if cal and not m._dynamic:
-            if isinstance(cal, MseCalibrator):
-                if cal.compute_amax() is not None:
-                    m.load_calib_amax()
-            elif method in {"mse", "entropy"}:
-                if cal.compute_amax(method) is not None:
-                    m.load_calib_amax(method)
-            elif cal.compute_amax() is not None:
-                m.load_calib_amax()
+            if isinstance(cal, MseCalibrator) or method not in {"mse", "entropy"}:
+                items.append((name, m, (), {}))
+            else:
+                items.append((name, m, (method,), {}))
+        done.append(m)
+    load_calib_amax_all(items)
+    for m in done:
         if m.bias_calibrator is not None and m.bias_type == "static":
             m.load_calib_bias()
         m.enable_quant()
@@ -109,16 +134,19 @@ def histogram_calibrate(model: nn.Module, forward_loop, method: str = "percentil
     forward_loop(model)
     if dp:
         qdist.sync_histograms(model)
-    for _, m in model.named_modules():
+    items, done = [], []
+    for name, m in model.named_modules():
         if not isinstance(m, TensorQuantizer) or m._disabled:
             continue
         cal = getattr(m, "_calibrator", None)
         if cal is not None and not m._dynamic:
             if isinstance(cal, HistogramCalibrator):
-                if cal.hist is not None:
-                    m.load_calib_amax(method, **compute_kwargs)
-            elif cal.compute_amax() is not None:
-                m.load_calib_amax()
+                items.append((name, m, (method,), compute_kwargs))
+            else:
+                items.append((name, m, (), {}))
+        done.append(m)
+    load_calib_amax_all(items)
+    for m in done:
         m.enable_quant()
         m.disable_calib()
     if dp:

@@ -283,6 +283,9 @@ class TensorQuantizer(nn.Module):
         if calib_amax is None:
             raise RuntimeError("Calibrator returned None. This usually happens when calibrator hasn't seen any tensor.")
         self.validate_attr(attr_value=calib_amax, attr_name="_amax", raise_error=True)
+        self._store_calib_amax(calib_amax)
+
+    def _store_calib_amax(self, calib_amax):
         if not hasattr(self, "_amax"):
             self.register_buffer("_amax", calib_amax.clone().detach())
         else:
