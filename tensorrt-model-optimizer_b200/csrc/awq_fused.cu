@@ -41,26 +41,15 @@
 // Measurement switches (0 in the library; set when building a throw-away copy to find which stage
 // bounds the pipeline): 1 = the transform only waits, fences and arrives; 2 = the epilogue only reads
 // the accumulator; 4 = A tiles are loaded for the first ring fill only; 8 = the same for W units.
+// B200Q_FUSED_ROTATE 0 starts every pair's K loop at slice 0.
 #ifndef B200Q_FUSED_ABLATE
 #define B200Q_FUSED_ABLATE 0
 #endif
 #ifndef B200Q_FUSED_ROTATE
 #define B200Q_FUSED_ROTATE 1
 #endif
-#ifndef B200Q_FUSED_ROUND
-#define B200Q_FUSED_ROUND 1
-#endif
 
 namespace b200q {
-
-#if B200Q_FUSED_ABLATE & 16
-// timing trace of CTA 0 (throw-away builds only): c_out is reused as a buffer of clock values,
-// [role][unit][4]; roles: 0 W producer, 1 transform warp 8, 2 transform warp 12, 3 MMA (W side), 4 MMA (A side)
-#define B200Q_TRACE(role, idx, slot) \
-  do { if (blockIdx.x == 0 && (idx) < 256u) reinterpret_cast<long long*>(c_out)[((role) * 256 + (idx)) * 4 + (slot)] = clock64(); } while (0)
-#else
-#define B200Q_TRACE(role, idx, slot) do {} while (0)
-#endif
 
 constexpr int kFK = 64;                                  // K elements of one A stage: one 128-byte swizzle row
 constexpr uint32_t kFTileBytes = 128 * kFK * 2;          // 128 rows x 64 bf16 = 16 KB: one TMA box
@@ -212,10 +201,8 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int row0 = w.alpha * M + w.slab_m * slab_rows + static_cast<int>(rank) * 128;
         for (int kb = 0; kb < k_slices; ++kb, ++it) {
           const int s = it % SA;
-          B200Q_TRACE(0, it >> 1, (it & 1) * 2);
           ok = mbar_wait_bounded(&sm->a_empty[s], ((it / SA) & 1) ^ 1, &sm->abort, status, kFErrAProducer);
           if (!ok) break;
-          B200Q_TRACE(0, it >> 1, (it & 1) * 2 + 1);
           if ((B200Q_FUSED_ABLATE & 4) && it >= static_cast<uint32_t>(SA)) continue;
           const uint32_t full_leader = map_to_cta(&sm->a_full[s], 0);
           if (leader) mbar_expect_tx(&sm->a_full[s], 2 * Cfg::kAStageBytes);      // both CTAs' tiles
@@ -270,18 +257,14 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
         for (int ub = 0; ub < k_units && ok; ++ub, ++wu) {
           const int u = wu % SW;
-          B200Q_TRACE(3, wu, 0);
           ok = mbar_wait_bounded_cluster(&sm->b_ready[u], (wu / SW) & 1, &sm->abort, status, kFErrMma);
           if (!ok) break;
-          B200Q_TRACE(3, wu, 1);
           const uint64_t db0 = umma_desc(smem_u32(ring_w + u * kFUnitBytes));
 #pragma unroll
           for (int half = 0; half < 2; ++half, ++it) {   // the unit's two 64-wide K slices
             const int s = it % SA;
-            B200Q_TRACE(4, it >> 1, (it & 1) * 2);
             ok = mbar_wait_bounded(&sm->a_full[s], (it / SA) & 1, &sm->abort, status, kFErrMma);
             if (!ok) break;
-            B200Q_TRACE(4, it >> 1, (it & 1) * 2 + 1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint64_t da0 = umma_desc(smem_u32(ring_a + s * Cfg::kAStageBytes));
             const uint64_t db = db0 + half * (kFTileBytes >> 4);
@@ -295,7 +278,6 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             commit_both(&sm->a_empty[s]);   // the stage is free in both CTAs once these MMAs have read it
           }
           if (!ok) break;
-          B200Q_TRACE(3, wu, 2);
           commit_both(&sm->b_empty[u]);
         }
         if (!ok) break;
@@ -331,7 +313,6 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     for (uint32_t task = t_id; task < tasks_total && ok; task += kFTransformCount) {
       const uint32_t wu = task / kFOctets;
       const int u = wu % SW;
-      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 0);
       // the raw unit has landed: every lane observes the completed phase itself, and only when it is
       // not there yet does lane 0 poll
       const uint32_t parity = (wu / SW) & 1;
@@ -342,7 +323,6 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       }
       ok = landed;
       if (!ok) break;
-      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 1);
       const int row = static_cast<int>(task % kFOctets) * 8 + r_in, sw = row & 7;
       uint8_t* dst = ring_w + u * kFUnitBytes + (qd >> 1) * kFTileBytes + row * 128;
       uint32_t pr[16];
@@ -387,23 +367,16 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           // The product is rounded to fp32 BEFORE it is rounded to an integer, as the reference does (a
           // block's own ties, e.g. v / amax = 13 / 14, sit exactly on .5 only after that first rounding).
           const uint64_t scale_p = f32x2_pack(sc.scale, sc.scale), y_p = f32x2_pack(sc.y, sc.y);
-#if B200Q_FUSED_ROUND == 1
           // rint(t) = (t + 1.5 * 2^23) - 1.5 * 2^23, the first sum written as fma(t, one, magic) with `one`
           // = 1.0f arriving as a kernel parameter: the assembler fuses a multiply with a following add
           // even when both carry an explicit rounding mode (observed: ties moved), which would round
           // the exact product instead of t; it cannot fuse a multiply into an existing multiply-add
           const uint64_t one_p = f32x2_pack(one, one), magic = f32x2_pack(12582912.f, 12582912.f),
                          nmagic = f32x2_pack(-12582912.f, -12582912.f);
-#endif
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const uint64_t t2 = f32x2_mul(f32x2_pack(__uint_as_float(pr[i] << 16), __uint_as_float(pr[i] & 0xffff0000u)), scale_p);
-#if B200Q_FUSED_ROUND == 1
             const uint64_t r2 = f32x2_add(f32x2_fma(t2, one_p, magic), nmagic);
-#else
-            const uint64_t r2 = f32x2_pack(rintf(__uint_as_float(static_cast<uint32_t>(t2))),
-                                           rintf(__uint_as_float(static_cast<uint32_t>(t2 >> 32))));
-#endif
             const uint64_t o2 = f32x2_mul(r2, y_p);
             pr[i] = Elem<__nv_bfloat16>::pack2(__uint_as_float(static_cast<uint32_t>(o2)),
                                                __uint_as_float(static_cast<uint32_t>(o2 >> 32)));
@@ -417,7 +390,6 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           }
         }
       }
-      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 2);
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj)
         *reinterpret_cast<uint4*>(dst + (((j0 + jj) ^ sw) << 4)) =
@@ -425,7 +397,6 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       fence_async_shared();     // these stores are read next by the tensor cores of both CTAs
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(&sm->b_ready[u], 0));
-      if (lane == 0 && t_id == 0) B200Q_TRACE(1, task / kFTransformCount, 3);
     }
   } else if ((warp >> 2) == 1 || (warp >> 2) == 4) {
     // ---------------------------------------------------------------- epilogue ----------------
@@ -477,7 +448,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             sq = fmaf(d_lo, d_lo, sq);
             sq = fmaf(d_hi, d_hi, sq);
           }
-          if (c_out && !(B200Q_FUSED_ABLATE & 16)) {
+          if (c_out) {
             float* cp = c_out + (static_cast<int64_t>(w.alpha) * M + row) * N + w.slab_n * kFPairN + cc * 16;
 #pragma unroll
             for (int j = 0; j < 16; ++j) cp[j] = __uint_as_float(acc[j]);

@@ -194,3 +194,27 @@ def test_histogram_calibrate_equals_the_stand_alone_calibrators(mtq):
         assert torch.equal(q._calibrator.hist, ref.hist)
     y = model["q0"](data[0])
     assert y.shape == data[0].shape and not torch.equal(y, data[0])
+
+
+def test_batched_amax_load_reports_every_invalid_quantiser(mtq):
+    """finish_stats_collection loads all calibrated amax values with one validity read; a NaN or inf
+    input is reported with the names of the quantisers it reached (the reference raises at the first)."""
+    from b200q.model_calib import enable_stats_collection, finish_stats_collection
+
+    model = torch.nn.ModuleDict({f"q{i}": mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8)).cuda()
+                                 for i in range(4)})
+    good = torch.randn(64, 64, device="cuda")
+    enable_stats_collection(model)
+    for q in model.values():
+        q(good)
+    finish_stats_collection(model)
+    for q in model.values():
+        assert q._amax.item() == good.abs().max().item() and q._if_quant and not q._if_calib
+    bad = good.clone()
+    bad[3, 3] = float("inf")
+    enable_stats_collection(model)
+    for name, q in model.items():
+        q._calibrator.reset()
+        q(bad if name in ("q1", "q3") else good)
+    with pytest.raises(ValueError, match=r"q1.*q3"):
+        finish_stats_collection(model)

@@ -361,3 +361,18 @@ def test_gemm_k_split_over_a_cluster_matches(m, n, k, monkeypatch):
                        one, one, None, torch.float32)
     ops.check_qgemm_status("cuda")
     assert np.array_equal(got.cpu().numpy(), ai @ bi.T)
+
+
+def test_a_reported_wait_run_out_reaches_the_caller():
+    """Host side of the bounded waits: a kernel that gives up a wait ORs an error bit into the device
+    status word; ``check_qgemm_status`` turns a non-zero word into an exception and clears it.  The word
+    is written from the host here — no kernel is made to time out."""
+    from b200q import ops
+
+    word = ops.qgemm_status("cuda")
+    ops.check_qgemm_status("cuda")            # clean
+    word.fill_(0x400)
+    with pytest.raises(RuntimeError, match="0x400"):
+        ops.check_qgemm_status("cuda")
+    assert int(word.item()) == 0
+    ops.check_qgemm_status("cuda")
