@@ -51,9 +51,9 @@ class HostNvFp4Packer:
         out = []
         for _ in range(ngroups):
             out.append({
-                "packed": [torch.empty((*s[:-1], s[-1] // 2), dtype=torch.uint8).pin_memory() for s in self.shapes],
-                "scales": [torch.empty((*s[:-1], s[-1] // 16), dtype=torch.uint8).pin_memory() for s in self.shapes],
-                "scale2": torch.empty(len(self.shapes), dtype=torch.float32).pin_memory(),
+                "packed": [torch.empty((*s[:-1], s[-1] // 2), dtype=torch.uint8, pin_memory=True) for s in self.shapes],
+                "scales": [torch.empty((*s[:-1], s[-1] // 16), dtype=torch.uint8, pin_memory=True) for s in self.shapes],
+                "scale2": torch.empty(len(self.shapes), dtype=torch.float32, pin_memory=True),
             })
         return out
 
@@ -90,37 +90,72 @@ class HostNvFp4Packer:
         return host_out
 
 
-def pack_host_tensors(tensors, device="cuda", amax=None, group_bytes: int = 256 << 20):
-    """NVFP4-pack a list of host (CPU) weight tensors of any shapes through the GPU: tensors are
-    bucketed by (shape, dtype), every bucket is streamed through a :class:`HostNvFp4Packer` in groups of
-    about ``group_bytes``.  ``amax[i]`` (or None) is a calibrated global abs-max for tensor i.  Returns, in
+def _repeating_unit(keys):
+    """Smallest p such that ``keys`` is a whole number (>= 2) of repetitions of its first p entries (the
+    linears of one transformer layer, in model order), or None."""
+    n = len(keys)
+    for p in range(1, n // 2 + 1):
+        if n % p == 0 and all(keys[i] == keys[i - p] for i in range(p, n)):
+            return p
+    return None
+
+
+def _plan_groups(keys, sizes, group_bytes):
+    """Split tensor indices into groups for the packer; groups with the same signature (shapes and dtype
+    in order) are streamed through one packer without draining its pipeline.  A model made of repeated
+    layers becomes groups of whole layers (several small layers per group, or a large layer cut at the
+    same places every time); anything else is bucketed by shape."""
+    n = len(keys)
+    p = _repeating_unit(keys)
+    groups = []
+    if p is not None:
+        unit_bytes = sum(sizes[:p])
+        if unit_bytes <= group_bytes:
+            per = max(1, group_bytes // max(unit_bytes, 1)) * p
+            groups = [list(range(i, min(i + per, n))) for i in range(0, n, per)]
+        else:
+            cuts, acc = [0], 0
+            for j in range(p):
+                if acc and acc + sizes[j] > group_bytes:
+                    cuts.append(j)
+                    acc = 0
+                acc += sizes[j]
+            cuts.append(p)
+            for base in range(0, n, p):
+                groups += [list(range(base + lo, base + hi)) for lo, hi in zip(cuts[:-1], cuts[1:])]
+        return groups
+    buckets = {}
+    for i, k in enumerate(keys):
+        buckets.setdefault(k, []).append(i)
+    for k, idxs in buckets.items():
+        per = max(1, min(len(idxs), group_bytes // max(sizes[idxs[0]], 1)))
+        groups += [idxs[i:i + per] for i in range(0, len(idxs), per)]
+    return groups
+
+
+def pack_host_tensors(tensors, device="cuda", amax=None, group_bytes: int = 512 << 20):
+    """NVFP4-pack a list of host (CPU) weight tensors of any shapes through the GPU.  The tensors are
+    split into groups of about ``group_bytes`` (``_plan_groups``) and all groups of one signature are
+    streamed through one :class:`HostNvFp4Packer`, whose three streams overlap the copies and kernels of
+    consecutive groups.  ``amax[i]`` (or None) is a calibrated global abs-max for tensor i.  Returns, in
     the order of ``tensors``, tuples (packed uint8, block scales float8_e4m3fn, scale2 fp32 0-dim), all on
     the host."""
     results = [None] * len(tensors)
-    buckets = {}
-    for i, t in enumerate(tensors):
-        buckets.setdefault((tuple(t.shape), t.dtype), []).append(i)
-    for (shape, dtype), idxs in buckets.items():
-        nbytes = 1
-        for d in shape:
-            nbytes *= d
-        nbytes *= torch.empty((), dtype=dtype).element_size()
-        per = max(1, min(len(idxs), group_bytes // max(nbytes, 1)))
-        full = len(idxs) // per * per
-        # groups of `per` tensors, then one smaller group for what is left
-        for ids, g in ((idxs[:full], per), (idxs[full:], len(idxs) - full)):
-            if not ids:
-                continue
-            packer = HostNvFp4Packer([shape] * g, dtype, device)
-            groups = [[tensors[j] for j in ids[k:k + g]] for k in range(0, len(ids), g)]
-            out = packer.alloc_host_outputs(len(groups))
-            av = None
-            if amax is not None:
-                av = [{k: amax[j] for k, j in enumerate(ids[b:b + g]) if amax[j] is not None}
-                      for b in range(0, len(ids), g)]
-            packer.pack(groups, out, av)
-            for b in range(len(groups)):
-                for k in range(g):
-                    results[ids[b * g + k]] = (out[b]["packed"][k], out[b]["scales"][k].view(torch.float8_e4m3fn),
-                                               out[b]["scale2"][k].clone())
+    keys = [(tuple(t.shape), t.dtype) for t in tensors]
+    sizes = [t.numel() * t.element_size() for t in tensors]
+    by_signature = {}
+    for ids in _plan_groups(keys, sizes, group_bytes):
+        by_signature.setdefault(tuple(keys[i] for i in ids), []).append(ids)
+    for signature, id_groups in by_signature.items():
+        packer = HostNvFp4Packer([shape for shape, _ in signature], signature[0][1], device)
+        groups = [[tensors[j] for j in ids] for ids in id_groups]
+        out = packer.alloc_host_outputs(len(groups))
+        av = None
+        if amax is not None:
+            av = [{k: amax[j] for k, j in enumerate(ids) if amax[j] is not None} for ids in id_groups]
+        packer.pack(groups, out, av)
+        for b, ids in enumerate(id_groups):
+            for k, j in enumerate(ids):
+                results[j] = (out[b]["packed"][k], out[b]["scales"][k].view(torch.float8_e4m3fn),
+                              out[b]["scale2"][k].clone())
     return results

@@ -436,3 +436,30 @@ def test_gemm_registry_and_real_quant_switches_on_cpu():
     mtq.disable_quantizer(m, "*")
     backends.enable_real_quant_gemm(m)
     assert torch.equal(m.up_proj(x), torch.nn.functional.linear(x, m.up_proj.weight))
+
+
+def test_host_packer_group_plan():
+    """Groups for the host-to-host NVFP4 packer: whole layers of a repeated stack (one signature, so one
+    pipeline that never drains), a large layer cut at the same places every time, shape buckets for
+    anything irregular; every tensor in exactly one group."""
+    import torch
+
+    from b200q.pipeline import _plan_groups, _repeating_unit
+
+    bf = torch.bfloat16
+    layer = [((4096, 4096), bf), ((1024, 4096), bf), ((1024, 4096), bf), ((4096, 4096), bf),
+             ((14336, 4096), bf), ((14336, 4096), bf), ((4096, 14336), bf)]
+    keys = layer * 32
+    sizes = [a * b * 2 for (a, b), _ in keys]
+    assert _repeating_unit(keys) == 7
+    groups = _plan_groups(keys, sizes, 512 << 20)
+    assert groups == [list(range(i, i + 7)) for i in range(0, 224, 7)]
+    assert len({tuple(keys[i] for i in g) for g in groups}) == 1
+    cut = _plan_groups(keys, sizes, 200 << 20)               # a layer is 436 MB: cut into three pieces
+    assert len(cut) == 96 and len({tuple(keys[i] for i in g) for g in cut}) == 3
+    assert all(sum(sizes[i] for i in g) <= 200 << 20 for g in cut)
+    irregular = keys + [((128256, 4096), bf)]
+    flat = sorted(i for g in _plan_groups(irregular, sizes + [128256 * 4096 * 2], 512 << 20) for i in g)
+    assert flat == list(range(225))
+    small = _plan_groups(layer[:2] * 3, [1, 1] * 3, 512 << 20)
+    assert small == [[0, 1, 2, 3, 4, 5]]
