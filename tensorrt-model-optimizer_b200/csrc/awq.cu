@@ -134,28 +134,38 @@ awq_scale_acts_kernel(const T* __restrict__ x, const T* __restrict__ s, T* __res
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < npack; i += stride) {
     const uint4 a = ld_stream(xv + i);
     const int64_t col = i % packs_per_row;
-    for (int c = 0; c < n_alpha; ++c) {
-      const uint4 b = __ldg(sv + c * packs_per_row + col);
-      uint4 r;
-      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-        uint32_t rw[4];
+    // candidates in rounds of eight: the eight scale loads of a round are in flight together (one
+    // dependent L2 round trip per round instead of one per candidate).  Plain stores: the search kernel
+    // reads these tiles next, and most of them are still in L2 then.
+    for (int c0 = 0; c0 < n_alpha; c0 += 8) {
+      uint4 b[8];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const __nv_bfloat162 pr = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&aw[k]),
-                                            *reinterpret_cast<const __nv_bfloat162*>(&bw[k]));
-          rw[k] = *reinterpret_cast<const uint32_t*>(&pr);
+      for (int u = 0; u < 8; ++u)
+        if (c0 + u < n_alpha) b[u] = __ldg(sv + (c0 + u) * packs_per_row + col);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (c0 + u >= n_alpha) break;
+        uint4 r;
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+          uint32_t rw[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162 pr = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&aw[k]),
+                                              *reinterpret_cast<const __nv_bfloat162*>(&bw[k]));
+            rw[k] = *reinterpret_cast<const uint32_t*>(&pr);
+          }
+          r = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+        } else {
+          float fa[P], fb[P];
+          E::unpack(a, fa);
+          E::unpack(b[u], fb);
+#pragma unroll
+          for (int k = 0; k < P; ++k) fa[k] = round_t<T>(fa[k] * fb[k]);
+          r = E::pack(fa);
         }
-        r = make_uint4(rw[0], rw[1], rw[2], rw[3]);
-      } else {
-        float fa[P], fb[P];
-        E::unpack(a, fa);
-        E::unpack(b, fb);
-#pragma unroll
-        for (int k = 0; k < P; ++k) fa[k] = round_t<T>(fa[k] * fb[k]);
-        r = E::pack(fa);
+        ov[(c0 + u) * npack + i] = r;
       }
-      st_stream(ov + c * npack + i, r);
     }
   }
 }

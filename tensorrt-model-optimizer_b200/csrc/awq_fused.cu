@@ -60,13 +60,18 @@ constexpr int kFPairN = 256;                             // columns of a pair's 
 #endif
 constexpr int kFWUnits = B200Q_FUSED_WUNITS;   // W unit slots: landing, being transformed, being read by the MMAs
 constexpr uint32_t kFScaleBytes = 128 * 2;     // one unit's share of a candidate's scale vector
-constexpr int kFThreads = 768;
+#ifndef B200Q_FUSED_THREADS
+#define B200Q_FUSED_THREADS 768
+#endif
+constexpr int kFThreads = B200Q_FUSED_THREADS;           // 768, 896 or 1024: whole groups of four warps
 // Warp roles.  A warp's scheduler is its index modulo 4.  Scheduler 0 hosts the latency-critical MMA
 // issuer and the A producer and no transform warp, so that neither has to compete for issue slots
 // with the arithmetic; the twelve transform warps are 1-3, 9-11, 13-15 and 21-23, the eight epilogue
 // warps 4-7 and 16-19.
 constexpr int kFWarpMma = 0, kFWarpAProducer = 8, kFWarpWProducer = 12;
-constexpr int kFTransformCount = 12, kFOctets = 16;      // row octets (warp-sized tasks) per W unit
+// three transform warps in every group of four warps except the two epilogue groups
+constexpr int kFTransformCount = (kFThreads / 128 - 2) * 3;
+constexpr int kFOctets = 16;                             // row octets (warp-sized tasks) per W unit
 constexpr int kFEpilogueWarps = 8;       // two per TMEM lane quarter (warps 4-7 and 16-19), alternate column chunks
 constexpr int kFMaxStages = 10;
 
