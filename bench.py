@@ -920,6 +920,11 @@ def run_profile_kernels():
     w_amax = w.reshape(n, k // 128, 128).abs().amax(-1).reshape(-1, 1)
     ratios = torch.tensor([0.5 + 0.05 * i for i in range(10)] + [1.0], device=dev)
     clip_loss = torch.zeros(11, n, k // 128, device=dev)
+    amax_slot = torch.zeros((), device=dev)
+    mse_cands = (amax.reshape(1, 1) * torch.linspace(0.25, 4.0, 10, device=dev).reshape(-1, 1)).contiguous()
+    mse_loss = torch.zeros(10, 1, dtype=torch.float64, device=dev)
+    mse_cands_rows = (w.abs().amax(dim=1).float().reshape(1, -1) * torch.linspace(0.25, 4.0, 10, device=dev).reshape(-1, 1)).contiguous()
+    mse_loss_rows = torch.zeros(10, n, dtype=torch.float64, device=dev)
     for i in range(4):
         wfq = ops.awq_scale_fake_int(w, s, 128, 4, False, False)
         ops.awq_gemm_sqerr(a, wfq, ref, acc, status)
@@ -932,6 +937,9 @@ def run_profile_kernels():
         ops.mx_fake(x[i % 2], 32, (4, 3))
         ops.mxfp4_quantize(x[i % 2], 32)
         ops.awq_clip_loss(w, xs, w_amax, ratios, clip_loss, 128, 4, False, False)
+        ops.amax_tensor(x[i % 2], out=amax_slot)
+        ops.mse_candidates(x[i % 2], mse_cands, mse_loss, None, 8, False, True)
+        ops.mse_candidates(w, mse_cands_rows, mse_loss_rows, 0, 8, False, True)
     # real-quant GEMM consumers on a 2048 x 4096 x 4096 problem
     a16, b16 = a.new_empty(2048, k).normal_(generator=g), w[:4096]
     one = torch.ones((), device=dev)

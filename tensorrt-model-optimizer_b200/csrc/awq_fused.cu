@@ -14,7 +14,7 @@
 // half (128 rows) of the W slab, so per FLOP a CTA asks L2 for a quarter less than a 256 x 256
 // single-CTA tile and the W slab is fetched exactly once per candidate.
 //
-// Warps of a CTA (24; a warp's scheduler is its index modulo 4):
+// Warps of a CTA (32; a warp's scheduler is its index modulo 4):
 //   0      MMA issuer (even CTA only) and TMEM allocation           } scheduler 0 carries no transform warp, so
 //   8      A producer: TMA 128 x 64 tiles into a 4-deep ring,       } these latency-critical threads do not
 //          completion counted on the EVEN CTA's barrier             } queue for issue slots behind arithmetic
@@ -22,7 +22,7 @@
 //          128 x 64 boxes) and the unit's 128 scale factors into a 3-deep ring
 //   4-7, 16-19   epilogue (two warps per TMEM lane quarter): tcgen05.ld the accumulator, squared error
 //          against R, one atomic per warp and item
-//   1-3, 9-11, 13-15, 21-23   transform (twelve warps), in shared memory, in place.  A W unit is sixteen
+//   1-3, 9-11, 13-15, 21-23, 25-27, 29-31   transform (eighteen warps), in shared memory, in place.  A W unit is sixteen
 //          warp-sized tasks of eight rows, taken round-robin across unit boundaries; a lane owns 32
 //          consecutive elements of one weight row (four lanes = one 128-block): bf16(W * s), the block
 //          abs-max (two shuffles), the integer fake quant, stored back where they came from in the
@@ -61,13 +61,13 @@ constexpr int kFPairN = 256;                             // columns of a pair's 
 constexpr int kFWUnits = B200Q_FUSED_WUNITS;   // W unit slots: landing, being transformed, being read by the MMAs
 constexpr uint32_t kFScaleBytes = 128 * 2;     // one unit's share of a candidate's scale vector
 #ifndef B200Q_FUSED_THREADS
-#define B200Q_FUSED_THREADS 768
+#define B200Q_FUSED_THREADS 1024
 #endif
-constexpr int kFThreads = B200Q_FUSED_THREADS;           // 768, 896 or 1024: whole groups of four warps
+constexpr int kFThreads = B200Q_FUSED_THREADS;           // whole groups of four warps; 1024 (64 registers) measured 2-3 % faster than 768
 // Warp roles.  A warp's scheduler is its index modulo 4.  Scheduler 0 hosts the latency-critical MMA
 // issuer and the A producer and no transform warp, so that neither has to compete for issue slots
-// with the arithmetic; the twelve transform warps are 1-3, 9-11, 13-15 and 21-23, the eight epilogue
-// warps 4-7 and 16-19.
+// with the arithmetic; the transform warps are the other three of every group of four except the two
+// epilogue groups (warps 4-7 and 16-19).
 constexpr int kFWarpMma = 0, kFWarpAProducer = 8, kFWarpWProducer = 12;
 // three transform warps in every group of four warps except the two epilogue groups
 constexpr int kFTransformCount = (kFThreads / 128 - 2) * 3;
@@ -291,7 +291,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
   } else if ((warp & 3) != 0 && (warp >> 2) != 1 && (warp >> 2) != 4) {
     // ---------------------------------------------------------------- transform ---------------
-    // A W unit (128 rows x 128 K) is sixteen warp-sized tasks of eight rows; the twelve transform warps
+    // A W unit (128 rows x 128 K) is sixteen warp-sized tasks of eight rows; the transform warps
     // take tasks round-robin across unit boundaries, so at any moment they are spread over two or three
     // units and over all phases of a task (waiting for the unit to land, arithmetic, the fence).
     // Lane -> quarter qd = lane >> 3 of the 128-block of one row; the eight lanes of a quarter-warp store
