@@ -39,3 +39,20 @@ def test_argument_validation_without_gpu():
     assert lib.b200q_amax_tensor(p16, 0, 2, p16, None) == -4            # shape
     assert lib.b200q_fake_int_tensor(p16, p16, 16, 0, p16, 40, 0, 1, None) == -5  # bits
     assert b"aligned" in lib.b200q_strerror(-3)
+
+
+def test_reference_extensions_load_without_a_gpu():
+    """oracle/_ref (the reference's own CUDA extensions, built by oracle/build_ref.py where a checkout of the
+    reference exists) loads without a GPU and exports what the GPU tests call.  Skipped when not built."""
+    import pytest
+
+    from oracle import ref_ext
+
+    ext, ext8, extmx = ref_ext.cuda_ext(), ref_ext.cuda_ext_fp8(), ref_ext.cuda_ext_mx()
+    if ext is None or ext8 is None or extmx is None:
+        pytest.skip("oracle/_ref was not built")
+    for name in ("fake_tensor_quant", "fake_tensor_quant_with_axis", "INT4_quantize", "INT4_dequantize"):
+        assert callable(getattr(ext, name))
+    for name in ("fake_e4m3fy", "fake_e4m3fy_with_axis"):
+        assert callable(getattr(ext8, name))
+    assert callable(extmx.fused_amax_convert) and hasattr(extmx.Types, "E2M1") and hasattr(extmx.Types, "E8M0")
