@@ -83,7 +83,7 @@ __device__ __forceinline__ float2 mse_pair(float x0, float x1, const MseCand& c,
 
 // Per tensor: all CTAs stride over the packs; S accumulators per thread; one fp64 atomic per CTA and candidate.
 template <typename T, int FORMAT>
-__global__ void __launch_bounds__(kMseThreads)
+__global__ void __launch_bounds__(kMseThreads, 4)
 mse_tensor_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ cand, int n_cand, IntQ q,
                   double* __restrict__ loss) {
   pdl_prologue();
@@ -134,7 +134,7 @@ mse_tensor_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ 
 // Per channel, x viewed as [outer, channels, inner] with `inner` contiguous elements per (outer, channel)
 // row: one warp per row; the row's S candidates are prepared by lanes 0..S-1 and passed by shuffle.
 template <typename T, int FORMAT>
-__global__ void __launch_bounds__(kMseThreads)
+__global__ void __launch_bounds__(kMseThreads, 4)
 mse_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t channels, int64_t inner,
                 const float* __restrict__ cand, int n_cand, IntQ q, double* __restrict__ loss) {
   pdl_prologue();
@@ -199,7 +199,7 @@ extern "C" int b200q_mse_candidates(const void* x, int64_t outer, int64_t channe
     const T* xp = static_cast<const T*>(x);
     if (channels == 1) {
       const int64_t n = outer * inner;
-      const int grid = grid_for(n / P, kMseThreads, 8);
+      const int grid = grid_for(n / P, kMseThreads, 4);      // 64 registers: four CTAs per SM are resident
       if (format == kMseInt) launch_pdl(mse_tensor_kernel<T, kMseInt>, grid, kMseThreads, 0, st, xp, n, cand_amax, n_cand, q, loss_io);
       else launch_pdl(mse_tensor_kernel<T, kMseE4m3>, grid, kMseThreads, 0, st, xp, n, cand_amax, n_cand, q, loss_io);
       return launch_status();
@@ -207,7 +207,7 @@ extern "C" int b200q_mse_candidates(const void* x, int64_t outer, int64_t channe
     // rows of `inner` contiguous elements: whole 16-byte packs, each row aligned
     if (inner % P || inner < 32 * P) return B200Q_ERR_UNSUPPORTED;
     const int64_t rows = outer * channels;
-    const int grid = grid_for(rows * 32, kMseThreads, 8);
+    const int grid = grid_for(rows * 32, kMseThreads, 4);
     if (format == kMseInt) launch_pdl(mse_rows_kernel<T, kMseInt>, grid, kMseThreads, 0, st, xp, rows, channels, inner, cand_amax, n_cand, q, loss_io);
     else launch_pdl(mse_rows_kernel<T, kMseE4m3>, grid, kMseThreads, 0, st, xp, rows, channels, inner, cand_amax, n_cand, q, loss_io);
     return launch_status();
