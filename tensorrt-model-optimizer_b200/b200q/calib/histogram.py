@@ -254,8 +254,7 @@ class HistogramCalibrator(_Calibrator):
         self._calib_hist[:n] = counts
         self._stale = False
 
-    @torch.no_grad()
-    def collect(self, x):
+    def collect(self, x):   # works on x.detach(): no autograd context needed (it costs microseconds per call)
         x = x.detach()
         if not x.is_floating_point() or x.dtype == torch.float64:
             x = x.float()

@@ -6,6 +6,7 @@ no fallback implementation.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 
 import torch
@@ -38,6 +39,18 @@ def _prep(x: torch.Tensor, align: int = 16) -> torch.Tensor:
     return x
 
 
+_SAME_DEVICE = contextlib.nullcontext()
+
+
+def _on(device):
+    """Context that makes ``device`` current for a launch; free when it already is (the usual case: the
+    full device guard costs several microseconds per call, as much as a small kernel's launch)."""
+    index = device.index
+    if index is None or index == torch.cuda.current_device():
+        return _SAME_DEVICE
+    return torch.cuda.device(device)
+
+
 def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -53,7 +66,7 @@ def amax_tensor(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     x = _prep(x)
     if out is None:
         out = torch.zeros((), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_amax_tensor", x.data_ptr(), x.numel(), dtype_code(x), out.data_ptr(), _stream(x))
     return out
 
@@ -65,7 +78,7 @@ def amax_axis3(x: torch.Tensor, outer: int, axis: int, inner: int,
     assert x.numel() == outer * axis * inner
     if out is None:
         out = torch.zeros(axis, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_amax_axis", x.data_ptr(), outer, axis, inner, dtype_code(x), out.data_ptr(), _stream(x))
     return out
 
@@ -77,7 +90,7 @@ def amax_blocks(x: torch.Tensor, block: int) -> torch.Tensor:
     if n % block:
         raise ValueError(f"numel {n} is not divisible by block {block}")
     out = torch.empty(n // block, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_amax_blocks", x.data_ptr(), n // block, block, dtype_code(x), out.data_ptr(), _stream(x))
     return out
 
@@ -112,7 +125,7 @@ def fake_int(x: torch.Tensor, amax: torch.Tensor, num_bits: int = 8, unsigned: b
     if x.numel() == 0:
         return y
     am = _amax_f32(amax, x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         if am.numel() == 1:
             call("b200q_fake_int_tensor", x.data_ptr(), y.data_ptr(), x.numel(), dtype_code(x),
                  am.data_ptr(), num_bits, int(unsigned), int(narrow_range), _stream(x))
@@ -132,7 +145,7 @@ def fake_int_rows_dynamic(x: torch.Tensor, num_bits: int = 8, unsigned: bool = F
     rows, cols = x.shape
     y = torch.empty_like(x)
     am = torch.empty(rows, dtype=torch.float32, device=x.device) if return_amax else None
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_fake_int_rows_dynamic", x.data_ptr(), y.data_ptr(), rows, cols, dtype_code(x),
              am.data_ptr() if am is not None else None, num_bits, int(unsigned), int(narrow_range),
              _stream(x))
@@ -144,7 +157,7 @@ def fake_e4m3(x: torch.Tensor, amax: torch.Tensor | None) -> torch.Tensor:
     y = torch.empty_like(x)
     if x.numel() == 0:
         return y
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         if amax is None:
             call("b200q_fake_e4m3_tensor", x.data_ptr(), y.data_ptr(), x.numel(), dtype_code(x), None, _stream(x))
             return y
@@ -191,7 +204,7 @@ def nvfp4_quantize(x: torch.Tensor, amax: torch.Tensor | None = None, scale2: to
     if scales_in is not None:
         sin = _cuda(scales_in, "scales_in").contiguous().view(torch.uint8)
         assert sin.numel() == nblocks
-    with torch.cuda.device(dev):
+    with _on(dev):
         if block == 16:
             call("b200q_nvfp4_quantize", x.data_ptr(), nblocks, dtype_code(x), glob.data_ptr(),
                  sin.data_ptr() if sin is not None else None, packed.data_ptr(), scales.data_ptr(),
@@ -211,7 +224,7 @@ def nvfp4_dequantize(packed: torch.Tensor, scales: torch.Tensor, scale2: torch.T
     y = torch.empty((*packed.shape[:-1], packed.shape[-1] * 2), dtype=dtype, device=packed.device)
     nblocks = y.numel() // block
     assert scales.numel() == nblocks
-    with torch.cuda.device(packed.device):
+    with _on(packed.device):
         if block == 16:
             call("b200q_nvfp4_dequantize", packed.data_ptr(), scales.data_ptr(), s2.data_ptr(), y.data_ptr(),
                  nblocks, _DT[dtype], _stream(packed))
@@ -230,7 +243,7 @@ def nvfp4_fake(x: torch.Tensor, amax: torch.Tensor | None = None, block: int = 1
     am = amax_tensor(x) if amax is None else _amax_f32(amax, x.device)
     if am.numel() != 1:
         am = am.amax()
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         if block == 16:
             call("b200q_nvfp4_fake", x.data_ptr(), y.data_ptr(), x.numel() // 16, dtype_code(x), am.data_ptr(),
                  _stream(x))
@@ -302,7 +315,7 @@ class NvFp4Group:
         """``amax_values`` {index: tensor}: global abs-max to use for those tensors instead of their own (a
         calibrated or clipped weight amax)."""
         dc = _DT[self.dtype]
-        with torch.cuda.device(self.device):
+        with _on(self.device):
             st = torch.cuda.current_stream(self.device).cuda_stream
             if amax_pass:
                 self.amax.zero_()
@@ -332,7 +345,7 @@ def int4_quantize(x: torch.Tensor, block: int, scales_in: torch.Tensor | None = 
     else:
         scales = torch.empty((nb, 1), dtype=x.dtype, device=x.device)
         sin, sout = None, scales.data_ptr()
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_int4_quantize", x.data_ptr(), nb, block, dtype_code(x), sin, sout, packed.data_ptr(),
              _stream(x))
     return packed, scales
@@ -343,7 +356,7 @@ def int4_dequantize(packed: torch.Tensor, scales: torch.Tensor, block: int) -> t
     scales = _cuda(scales, "scales").contiguous()
     n = packed.numel() * 2
     y = torch.empty(n, dtype=scales.dtype, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _on(packed.device):
         call("b200q_int4_dequantize", packed.data_ptr(), scales.data_ptr(), y.data_ptr(), n // block, block,
              dtype_code(scales), _stream(packed))
     return y
@@ -356,7 +369,7 @@ def _q8(name: str, x: torch.Tensor, scales: torch.Tensor, outer: int, axis: int,
     s = _cuda(scales, "scales").to(x.dtype).contiguous()
     assert s.numel() == axis and x.numel() == outer * axis * inner
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call(name, x.data_ptr(), s.data_ptr(), q.data_ptr(), outer, axis, inner, dtype_code(x), _stream(x))
     return q.view(out_dtype)
 
@@ -375,7 +388,7 @@ def hist_collect(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_max: f
     """counts (int64 [>= nbins], CUDA) += histogram of |x| over [0, range_max] with nbins bins."""
     x = _prep(x)
     assert counts.dtype == torch.int64 and counts.is_cuda and counts.numel() >= nbins
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_hist_collect", x.data_ptr(), x.numel(), dtype_code(x), nbins,
              ctypes.c_float(range_max), counts.data_ptr(), _stream(x))
     return counts
@@ -388,7 +401,7 @@ def hist_collect_open(x: torch.Tensor, counts: torch.Tensor, nbins: int, range_m
     x = _prep(x)
     assert counts.dtype == torch.int64 and counts.is_cuda and counts.numel() >= nbins
     assert overflow.dtype == torch.int64 and overflow.is_cuda and overflow.numel() >= 1
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_hist_collect_open", x.data_ptr(), x.numel(), dtype_code(x), nbins, ctypes.c_float(range_max),
              counts.numel(), counts.data_ptr(), overflow.data_ptr(), _stream(x))
     return counts
@@ -407,7 +420,7 @@ def hist_collect_shared(x: torch.Tensor, counts: list, overflow: list, nbins: in
     assert range_dev.dtype == torch.float32 and range_dev.is_cuda and range_dev.numel() >= 1
     cp = (ctypes.c_void_p * n)(*[c.data_ptr() for c in counts])
     op = (ctypes.c_void_p * n)(*[o.data_ptr() for o in overflow])
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_hist_collect_shared", x.data_ptr(), x.numel(), dtype_code(x), nbins, range_dev.data_ptr(), cap,
              ctypes.cast(cp, ctypes.c_void_p), ctypes.cast(op, ctypes.c_void_p), n, _stream(x))
 
@@ -420,7 +433,7 @@ def hist_entropy(counts: torch.Tensor, nbins: int, edges: torch.Tensor, num_leve
     out = torch.empty((), dtype=torch.float32, device=counts.device)
     e = edges.to(device=counts.device, dtype=torch.float32).contiguous()
     assert e.numel() >= nbins + 1 and counts.dtype == torch.int64
-    with torch.cuda.device(counts.device):
+    with _on(counts.device):
         call("b200q_hist_entropy", counts.data_ptr(), nbins, num_levels, start_bin, stride, e.data_ptr(),
              ctypes.c_float(0.0), divs.data_ptr(), out.data_ptr(), _stream(counts))
     return out, divs
@@ -434,7 +447,7 @@ def hist_mse(counts: torch.Tensor, nbins: int, edges: torch.Tensor, bound: float
     out = torch.empty((), dtype=torch.float32, device=counts.device)
     e = edges.to(device=counts.device, dtype=torch.float32).contiguous()
     assert e.numel() >= nbins + 1 and counts.dtype == torch.int64
-    with torch.cuda.device(counts.device):
+    with _on(counts.device):
         call("b200q_hist_mse", counts.data_ptr(), nbins, e.data_ptr(), ctypes.c_double(bound), start_bin, stride,
              errs.data_ptr(), out.data_ptr(), _stream(counts))
     return out, errs
@@ -447,7 +460,7 @@ def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None
     if edges is not None:
         e = edges.to(device=counts.device, dtype=torch.float32).contiguous()
         assert e.numel() >= nbins + 1
-    with torch.cuda.device(counts.device):
+    with _on(counts.device):
         call("b200q_hist_percentile", counts.data_ptr(), nbins, e.data_ptr() if e is not None else None,
              ctypes.c_float(width), ctypes.c_double(percentile), out.data_ptr(), _stream(counts))
     return out
@@ -493,7 +506,7 @@ def mse_candidates(x: torch.Tensor, cand: torch.Tensor, loss: torch.Tensor, axis
     fp8 = not isinstance(num_bits, int)
     if fp8 and tuple(num_bits) != (4, 3):
         raise ValueError("mse_candidates covers integer formats and E4M3")
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_mse_candidates", x.data_ptr(), outer, channels, inner, dtype_code(x), cand.data_ptr(), s,
              1 if fp8 else 0, 8 if fp8 else num_bits, int(unsigned), int(narrow_range), loss.data_ptr(), _stream(x))
     return loss
@@ -513,7 +526,7 @@ def awq_scale_fake_int(w: torch.Tensor, s: torch.Tensor, block: int, num_bits: i
     else:
         assert out.shape == w.shape and out.dtype == w.dtype and out.is_contiguous() and out.device == w.device
         y = out
-    with torch.cuda.device(w.device):
+    with _on(w.device):
         call("b200q_awq_scale_fake_int", w.data_ptr(), s.data_ptr(), y.data_ptr(), w.shape[0], w.shape[1],
              block, dtype_code(w), num_bits, int(unsigned), int(narrow_range), _stream(w))
     return y
@@ -524,7 +537,7 @@ def mse_loss(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     a, b = _prep(a), _prep(b)
     assert a.shape == b.shape and a.dtype == b.dtype
     acc = torch.zeros((), dtype=torch.float64, device=a.device)
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         call("b200q_sq_diff_sum", a.data_ptr(), b.data_ptr(), a.numel(), dtype_code(a), acc.data_ptr(), _stream(a))
     return (acc / a.numel()).to(torch.float32)
 
@@ -560,7 +573,7 @@ def awq_gemm_sqerr(a: torch.Tensor, b: torch.Tensor, ref: torch.Tensor, acc: tor
     assert ref.shape == (m, n) and ref.dtype == torch.bfloat16 and acc.dtype == torch.float64
     if splits is None:
         splits = awq_gemm_splits(m, n, k, a.device)
-    with torch.cuda.device(a.device):
+    with _on(a.device):
         if splits <= 1:
             call("b200q_awq_gemm_sqerr", a.data_ptr(), b.data_ptr(), ref.data_ptr(), m, n, k, acc.data_ptr(),
                  c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(a))
@@ -583,7 +596,7 @@ def awq_scale_acts(x2: torch.Tensor, s_all: torch.Tensor) -> torch.Tensor:
     n_alpha = s_all.shape[0]
     assert s_all.shape == (n_alpha, cols)
     out = torch.empty((n_alpha, rows, cols), dtype=x2.dtype, device=x2.device)
-    with torch.cuda.device(x2.device):
+    with _on(x2.device):
         call("b200q_awq_scale_acts", x2.data_ptr(), s_all.data_ptr(), out.data_ptr(), rows, cols, n_alpha,
              dtype_code(x2), _stream(x2))
     return out
@@ -610,7 +623,7 @@ def awq_search_fused(a_all: torch.Tensor, w: torch.Tensor, s_all: torch.Tensor, 
     assert loss.dtype == torch.float64 and loss.numel() == n_alpha and loss.is_contiguous()
     if c_out is not None:
         assert c_out.dtype == torch.float32 and c_out.shape == (n_alpha, m, n) and c_out.is_contiguous()
-    with torch.cuda.device(w.device):
+    with _on(w.device):
         call("b200q_awq_search_fused", a_all.data_ptr(), w.data_ptr(), s_all.data_ptr(), ref.data_ptr(), n_alpha,
              m, n, k, block, num_bits, int(unsigned), int(narrow_range), loss.data_ptr(),
              c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(w))
@@ -627,7 +640,7 @@ def int4_export_pack(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     if sc.dtype not in (torch.float32, w.dtype):
         sc = sc.float()
     out = torch.empty((rows // 2, cols), dtype=torch.uint8, device=w.device)
-    with torch.cuda.device(w.device):
+    with _on(w.device):
         call("b200q_int4_export_pack", w.data_ptr(), sc.data_ptr(), int(sc.dtype == torch.float32),
              out.data_ptr(), rows, cols, block, dtype_code(w), _stream(w))
     return out
@@ -646,7 +659,7 @@ def mx_fake(x: torch.Tensor, block: int, num_bits) -> torch.Tensor:
     xx = torch.nn.functional.pad(x, (0, pad)) if pad else x
     xx = _prep(xx)
     y = torch.empty_like(xx)
-    with torch.cuda.device(xx.device):
+    with _on(xx.device):
         call("b200q_mx_fake", xx.data_ptr(), y.data_ptr(), xx.numel() // block, block, dtype_code(xx), fmt,
              _stream(xx))
     return y[..., : shape[-1]].contiguous() if pad else y
@@ -659,7 +672,7 @@ def mxfp4_quantize(x: torch.Tensor, block: int = 32):
     assert n % block == 0
     packed = torch.empty((*x.shape[:-1], x.shape[-1] // 2), dtype=torch.uint8, device=x.device)
     scales = torch.empty((n // block, 1), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_mxfp4_quantize", x.data_ptr(), n // block, block, dtype_code(x), packed.data_ptr(),
              scales.data_ptr(), _stream(x))
     return packed, scales
@@ -681,7 +694,7 @@ def awq_clip_loss(w: torch.Tensor, x: torch.Tensor, w_amax: torch.Tensor, ratios
     assert ratios.dtype == torch.float32 and ratios.is_cuda and ratios.is_contiguous()
     assert loss.dtype == torch.float32 and loss.is_cuda and loss.is_contiguous()
     assert loss.numel() == ratios.numel() * rows * (cols // block)
-    with torch.cuda.device(w.device):
+    with _on(w.device):
         call("b200q_awq_clip_loss", w.data_ptr(), x.data_ptr(), w_amax.data_ptr(), ratios.data_ptr(),
              ratios.numel(), loss.data_ptr(), rows, cols, block, x.shape[0], dtype_code(w), num_bits,
              int(unsigned), int(narrow_range), _stream(w))
@@ -695,7 +708,7 @@ def hadamard(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     x = _prep(x, 2)
     n = x.shape[-1]
     y = torch.empty_like(x)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_hadamard", x.data_ptr(), y.data_ptr(), x.numel() // n, n, dtype_code(x), ctypes.c_float(scale),
              _stream(x))
     return y
@@ -745,7 +758,7 @@ def fp8_gemm(a8: torch.Tensor, b8: torch.Tensor, scale_a: torch.Tensor, scale_b:
     sa = _amax_f32(scale_a, a8.device).reshape(())
     sb = _amax_f32(scale_b, a8.device).reshape(()) if scale_b is not None else None
     out, bias = _gemm_out(a8, n, bias, out_dtype)
-    with torch.cuda.device(a8.device):
+    with _on(a8.device):
         call("b200q_fp8_gemm", a8.data_ptr(), b8.data_ptr(), sa.data_ptr(), sb.data_ptr() if sb is not None else None,
              bias.data_ptr() if bias is not None else None, out.data_ptr(), m, n, k, _DT[out_dtype],
              qgemm_status(a8.device).data_ptr(), _stream(a8))
@@ -759,7 +772,7 @@ def fp8_gemm_operand(x: torch.Tensor, scale: torch.Tensor, fused: bool = False) 
     x = _prep(x)
     s = _amax_f32(scale, x.device).reshape(1)
     q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         call("b200q_fp8_gemm_operand", x.data_ptr(), s.data_ptr(), q.data_ptr(), x.numel(), dtype_code(x),
              0 if fused else 1, _stream(x))
     return q.view(torch.float8_e4m3fn)
@@ -776,7 +789,7 @@ def nvfp4_swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
     s = s.reshape(-1, s.shape[-1])
     rows, cols = s.shape
     out = torch.empty(nvfp4_swizzled_scale_bytes(rows, cols), dtype=torch.uint8, device=s.device)
-    with torch.cuda.device(s.device):
+    with _on(s.device):
         call("b200q_nvfp4_swizzle_scales", s.data_ptr(), out.data_ptr(), rows, cols, _stream(s))
     return out
 
@@ -794,7 +807,7 @@ def nvfp4_gemm(a4: torch.Tensor, sfa: torch.Tensor, b4: torch.Tensor, sfb: torch
     assert sfb.numel() == nvfp4_swizzled_scale_bytes(n, k // 16), "sfb is not in the tiled order for this shape"
     al = _amax_f32(alpha, a4.device).reshape(())
     out, bias = _gemm_out(a4, n, bias, out_dtype)
-    with torch.cuda.device(a4.device):
+    with _on(a4.device):
         call("b200q_nvfp4_gemm", a4.data_ptr(), b4.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), al.data_ptr(),
              bias.data_ptr() if bias is not None else None, out.data_ptr(), m, n, k, _DT[out_dtype],
              qgemm_status(a4.device).data_ptr(), _stream(a4))
