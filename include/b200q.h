@@ -338,6 +338,17 @@ int b200q_awq_search_fused(const void* a_all, const void* w, const void* s_all, 
                            int is_unsigned, int narrow_range, double* loss_io, float* c_out,
                            uint32_t* status_io, void* stream);
 
+/* The same persistent CTA-pair kernel fed with weights that are ALREADY scaled and fake-quantised:
+ *   loss_io[a] += sum_{m,n} float(bf16(bf16(sum_k a_all[a][m,k] * wq_all[a][n,k]) - ref[m,n]))^2
+ * wq_all [n_alpha, n, k] bf16 (e.g. from b200q_awq_scale_fake_int, one candidate after the other), the
+ * other arguments as above; k a multiple of 128, n a multiple of 32.  With n_alpha = 1 this is one
+ * bf16 GEMM with the squared-error epilogue.  It is what the search uses for batches of several thousand
+ * rows: the fused form above re-creates a candidate's weight once per 512-row slab, this form once per
+ * candidate.  Same reference lines as b200q_awq_gemm_sqerr (model_calib.py:671-685,623-627). */
+int b200q_awq_search_prequant(const void* a_all, const void* wq_all, const void* ref, int n_alpha,
+                              int64_t m, int64_t n, int64_t k, double* loss_io, float* c_out,
+                              uint32_t* status_io, void* stream);
+
 /* NVFP4 with a block size other than 16 (any even size; NVFP4QTensor.quantize and
  * dynamic_block_quant take the block size as an argument, modelopt/torch/quantization/qtensor/
  * nvfp4_tensor.py:142-232, tensor_quant.py:158-198).  Same arithmetic and argument meaning as

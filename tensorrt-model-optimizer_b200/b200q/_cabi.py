@@ -59,6 +59,7 @@ SIGNATURES = {
     "b200q_awq_gemm_sqerr": [_p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p],
     "b200q_awq_scale_acts": [_p, _p, _p, _i64, _i64, _i, _i, _p],
     "b200q_awq_search_fused": [_p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _i, _i, _p, _p, _p, _p],
+    "b200q_awq_search_prequant": [_p, _p, _p, _i, _i64, _i64, _i64, _p, _p, _p, _p],
     "b200q_fp8_gemm": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _p, _p],
     "b200q_qgemm_tile_override": [_i],
     "b200q_fp8_gemm_operand": [_p, _p, _p, _i64, _i, _i, _p],

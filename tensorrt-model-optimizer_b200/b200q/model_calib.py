@@ -317,6 +317,20 @@ def _evaluate_alpha(module, st, x2d, out_actual, alpha):
 FUSED_AWQ_SEARCH = True
 # bytes of scaled activations (candidates x tokens x channels) formed per launch of the fused search
 FUSED_AWQ_SEARCH_BYTES = 1 << 30
+# batches with more rows than this hand the kernel finished weights instead of the raw weight
+FUSED_AWQ_SEARCH_MAX_ROWS = 2048
+
+
+# one grow-only buffer per device and dtype for the finished weights of a group of candidates, shared by
+# all layers of a model (their searches run one after the other on the stream); dropped when awq_lite ends
+_SEARCH_SCRATCH: dict = {}
+
+
+def _search_scratch(device, dtype, numel):
+    buf = _SEARCH_SCRATCH.get((device, dtype))
+    if buf is None or buf.numel() < numel:
+        buf = _SEARCH_SCRATCH[(device, dtype)] = torch.empty(numel, dtype=dtype, device=device)
+    return buf[:numel]
 
 
 def _search_fused(module, st, x2d, out_actual) -> bool:
@@ -339,13 +353,27 @@ def _search_fused(module, st, x2d, out_actual) -> bool:
         st.cand_scales = (scales.to(w.dtype), (1 / scales).to(w.dtype))
     w_s, x_s = st.cand_scales
     m, k = x2.shape
-    group = max(1, min(len(alphas), FUSED_AWQ_SEARCH_BYTES // max(1, m * k * 2)))
+    # The kernel forms a candidate's weight in shared memory on its way into the tensor cores, once per
+    # 512-row slab of the batch.  That is free while the tensor cores wait for operands anyway (measured:
+    # 512 to 2048 rows, the fused form is as fast or faster); beyond that the repeated transform starts to
+    # cost, so each candidate's weight is written once by the stand-alone weight-side kernel and the same
+    # kernel runs on the finished weights (8192 rows: 17 ms against 19 ms for the up_proj shape).
+    prequant = m > FUSED_AWQ_SEARCH_MAX_ROWS
+    per_alpha = m * k * 2 + (w.numel() * 2 if prequant else 0)
+    group = max(1, min(len(alphas), FUSED_AWQ_SEARCH_BYTES // max(1, per_alpha)))
     accs = torch.zeros(len(alphas), dtype=torch.float64, device=w.device)
+    wq_all = _search_scratch(w.device, w.dtype, group * w.numel()).view(group, *w.shape) if prequant else None
     for g0 in range(0, len(alphas), group):
         g1 = min(len(alphas), g0 + group)
         a_all = ops.awq_scale_acts(x2, x_s[g0:g1])
-        ops.awq_search_fused(a_all, w, w_s[g0:g1], ref2, accs[g0:g1], st.gemm_status, st.block_size,
-                             wq._num_bits, wq._unsigned, wq._narrow_range)
+        if prequant:
+            for i in range(g0, g1):
+                ops.awq_scale_fake_int(w, w_s[i], st.block_size, wq._num_bits, wq._unsigned, wq._narrow_range,
+                                       out=wq_all[i - g0])
+            ops.awq_search_prequant(a_all, wq_all[: g1 - g0], ref2, accs[g0:g1], st.gemm_status)
+        else:
+            ops.awq_search_fused(a_all, w, w_s[g0:g1], ref2, accs[g0:g1], st.gemm_status, st.block_size,
+                                 wq._num_bits, wq._unsigned, wq._narrow_range)
     losses = (accs / ref2.numel()).to(torch.float32)
     for i, a in enumerate(alphas):
         st.loss[a] += losses[i]
@@ -472,7 +500,10 @@ def awq_lite(model: nn.Module, forward_loop, alpha_step: float = 0.1, debug: boo
 
     # pass 2: search
     cache_mode[0] = False
-    forward_loop(model)
+    try:
+        forward_loop(model)
+    finally:
+        _SEARCH_SCRATCH.clear()
 
     for name, m in layers:
         st = m.awq_lite

@@ -630,6 +630,32 @@ def awq_search_fused(a_all: torch.Tensor, w: torch.Tensor, s_all: torch.Tensor, 
     return loss
 
 
+def awq_search_prequant_supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes / dtype the CTA-pair kernel covers when it is handed finished (fake-quantised) weights."""
+    return (x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x2.is_cuda and w.is_cuda and x2.dim() == 2
+            and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] % 32 == 0 and x2.shape[1] == w.shape[1]
+            and x2.shape[0] > 0)
+
+
+def awq_search_prequant(a_all: torch.Tensor, wq_all: torch.Tensor, ref: torch.Tensor, loss: torch.Tensor,
+                        status: torch.Tensor, c_out: torch.Tensor | None = None):
+    """loss[a] (float64) += squared bf16 error of ``a_all[a] @ wq_all[a].T`` against ``ref`` for every candidate
+    a, in one launch of the persistent CTA-pair kernel (``b200q_awq_search_prequant``).  a_all [n_alpha, m, k],
+    wq_all [n_alpha, n, k] (already scaled and fake-quantised), ref [m, n], all bf16."""
+    a_all, wq_all, ref = _prep(a_all), _prep(wq_all, 32), _prep(ref)
+    n_alpha, m, k = a_all.shape
+    n = wq_all.shape[1]
+    assert wq_all.shape == (n_alpha, n, k) and ref.shape == (m, n)
+    assert a_all.dtype == wq_all.dtype == ref.dtype == torch.bfloat16
+    assert loss.dtype == torch.float64 and loss.numel() == n_alpha and loss.is_contiguous()
+    if c_out is not None:
+        assert c_out.dtype == torch.float32 and c_out.shape == (n_alpha, m, n) and c_out.is_contiguous()
+    with _on(wq_all.device):
+        call("b200q_awq_search_prequant", a_all.data_ptr(), wq_all.data_ptr(), ref.data_ptr(), n_alpha, m, n, k,
+             loss.data_ptr(), c_out.data_ptr() if c_out is not None else None, status.data_ptr(), _stream(wq_all))
+    return loss
+
+
 def int4_export_pack(w: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """w [rows, cols], scales [rows, cols/block] (fp32 or w.dtype) -> uint8 [rows/2, cols]."""
     w = _prep(w)

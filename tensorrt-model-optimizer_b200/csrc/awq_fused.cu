@@ -162,6 +162,9 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   uint8_t* ring_s = ring_w + SW * kFUnitBytes;       // the 128 scale factors of each W unit (256 bytes per slot)
   FusedSmem* sm = reinterpret_cast<FusedSmem*>(ring_s + SW * kFScaleBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // no scale vectors: the weight operand holds every candidate's weight already scaled and fake-quantised
+  // (n_alpha * N rows); the transform warps then only hand the landed units on to the MMA issuer
+  const bool prequant = s_all == nullptr;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -226,8 +229,9 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       bool ok = true;
       for (int item = pair; item < num_items && ok; item += num_pairs) {
         const FusedItem w = fused_item(item, slabs_m, slabs_n);
-        const int n_row = w.slab_n * kFPairN + static_cast<int>(rank) * 128;
-        const __nv_bfloat16* s_row = s_all + static_cast<int64_t>(w.alpha) * K;
+        // pre-quantised weights: candidate a's weight is rows [a * N, (a + 1) * N) of the operand
+        const int n_row = (prequant ? w.alpha * N : 0) + w.slab_n * kFPairN + static_cast<int>(rank) * 128;
+        const __nv_bfloat16* s_row = prequant ? nullptr : s_all + static_cast<int64_t>(w.alpha) * K;
         for (int ub = 0; ub < k_units; ++ub, ++wu) {
           const int u = wu % SW;
           ok = mbar_wait_bounded(&sm->b_empty[u], ((wu / SW) & 1) ^ 1, &sm->abort, status, kFErrWProducer);
@@ -235,8 +239,8 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           int ur = ub + rot;
           ur -= ur >= k_units ? k_units : 0;
           uint8_t* dst = ring_w + u * kFUnitBytes;
-          mbar_expect_tx(&sm->w_full[u], kFUnitBytes + kFScaleBytes);
-          bulk_load(ring_s + u * kFScaleBytes, s_row + ur * 128, kFScaleBytes, &sm->w_full[u]);
+          mbar_expect_tx(&sm->w_full[u], kFUnitBytes + (prequant ? 0u : kFScaleBytes));
+          if (!prequant) bulk_load(ring_s + u * kFScaleBytes, s_row + ur * 128, kFScaleBytes, &sm->w_full[u]);
           tma_load_2d(dst, &map_w, &sm->w_full[u], ur * 128, n_row);
           tma_load_2d(dst + kFTileBytes, &map_w, &sm->w_full[u], ur * 128 + kFK, n_row);
         }
@@ -330,6 +334,11 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       if (!ok) break;
       const int row = static_cast<int>(task % kFOctets) * 8 + r_in, sw = row & 7;
       uint8_t* dst = ring_w + u * kFUnitBytes + (qd >> 1) * kFTileBytes + row * 128;
+      if (prequant) {      // the unit was written by the async proxy and is read by it: nothing to fence
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(map_to_cta(&sm->b_ready[u], 0));
+        continue;
+      }
       uint32_t pr[16];
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
@@ -539,6 +548,27 @@ static int fused_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, cons
 
 using namespace b200q;
 
+static int fused_entry(const void* a_all, const void* w, int64_t w_rows, const void* s_all, const void* ref,
+                       int n_alpha, int64_t m, int64_t n, int64_t k, IntQ q, double* loss_io, float* c_out,
+                       uint32_t* status_io, void* stream) {
+  if (n_alpha * m > (1ll << 30) || w_rows > (1ll << 30) || k > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
+  const int mt = m > 256 ? 2 : 1;
+  const int64_t slabs_m = (m + 256 * mt - 1) / (256 * mt), slabs_n = (n + kFPairN - 1) / kFPairN;
+  const int64_t items = n_alpha * slabs_m * slabs_n;
+  if (items > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
+  CUtensorMap map_a, map_w;
+  if (!fused_make_map(&map_a, a_all, static_cast<int64_t>(n_alpha) * m, k) || !fused_make_map(&map_w, w, w_rows, k))
+    return B200Q_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(s_all);
+  const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(ref);
+  if (mt == 2)
+    return fused_launch<2>(map_a, map_w, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
+                           static_cast<int>(k), q, status_io, items, st);
+  return fused_launch<1>(map_a, map_w, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
+                         static_cast<int>(k), q, status_io, items, st);
+}
+
 extern "C" int b200q_awq_search_fused(const void* a_all, const void* w, const void* s_all, const void* ref,
                                       int n_alpha, int64_t m, int64_t n, int64_t k, int block, int num_bits,
                                       int is_unsigned, int narrow_range, double* loss_io, float* c_out,
@@ -550,21 +580,18 @@ extern "C" int b200q_awq_search_fused(const void* a_all, const void* w, const vo
   if (num_bits < 1 || num_bits + (is_unsigned ? 1 : 0) > 24) return B200Q_ERR_ARG;
   // one W unit = one quantisation block = two swizzle rows; the epilogue masks whole 32-column chunks
   if (block != 128 || k % 128 || n % 32) return B200Q_ERR_UNSUPPORTED;
-  if (n_alpha * m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
-  const int mt = m > 256 ? 2 : 1;
-  const int64_t slabs_m = (m + 256 * mt - 1) / (256 * mt), slabs_n = (n + kFPairN - 1) / kFPairN;
-  const int64_t items = n_alpha * slabs_m * slabs_n;
-  if (items > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
-  CUtensorMap map_a, map_w;
-  if (!fused_make_map(&map_a, a_all, static_cast<int64_t>(n_alpha) * m, k) || !fused_make_map(&map_w, w, n, k))
-    return B200Q_ERR_CUDA;
-  const IntQ q = make_intq(num_bits, is_unsigned, narrow_range);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(s_all);
-  const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(ref);
-  if (mt == 2)
-    return fused_launch<2>(map_a, map_w, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
-                           static_cast<int>(k), q, status_io, items, st);
-  return fused_launch<1>(map_a, map_w, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
-                         static_cast<int>(k), q, status_io, items, st);
+  return fused_entry(a_all, w, n, s_all, ref, n_alpha, m, n, k, make_intq(num_bits, is_unsigned, narrow_range),
+                     loss_io, c_out, status_io, stream);
+}
+
+extern "C" int b200q_awq_search_prequant(const void* a_all, const void* wq_all, const void* ref, int n_alpha,
+                                         int64_t m, int64_t n, int64_t k, double* loss_io, float* c_out,
+                                         uint32_t* status_io, void* stream) {
+  B200Q_REQUIRE_PTR(a_all); B200Q_REQUIRE_PTR(wq_all); B200Q_REQUIRE_PTR(ref);
+  B200Q_REQUIRE_PTR(loss_io); B200Q_REQUIRE_PTR(status_io);
+  B200Q_REQUIRE_ALIGNED(a_all); B200Q_REQUIRE_ALIGNED(wq_all); B200Q_REQUIRE_ALIGNED(ref);
+  if (n_alpha <= 0 || m <= 0 || n <= 0 || k <= 0) return B200Q_ERR_SHAPE;
+  if (k % 128 || n % 32) return B200Q_ERR_UNSUPPORTED;
+  return fused_entry(a_all, wq_all, static_cast<int64_t>(n_alpha) * n, nullptr, ref, n_alpha, m, n, k, IntQ{7.f, -8.f},
+                     loss_io, c_out, status_io, stream);
 }

@@ -174,3 +174,75 @@ def test_awq_scale_acts_equals_the_broadcast_multiply(dtype):
     s = torch.exp(torch.randn(5, 1024, generator=g, device="cuda")).to(dtype)
     got = ops.awq_scale_acts(x, s)
     assert torch.equal(got, x.unsqueeze(0) * s.unsqueeze(1))
+
+
+@pytest.mark.parametrize("n_alpha,m,n,k", [
+    (1, 512, 1024, 512),       # one GEMM with the loss epilogue
+    (3, 1024, 512, 256),       # two row slabs per candidate
+    (2, 1300, 288, 384),       # ragged rows (three slabs, the last mostly empty) and a ragged column slab
+    (4, 100, 96, 128),         # small everything
+])
+def test_pair_kernel_on_finished_weights(n_alpha, m, n, k):
+    """b200q_awq_search_prequant: the CTA-pair kernel handed every candidate's weight already scaled and
+    fake-quantised.  Products against a float32 torch matmul of the same bf16 operands (1e-5 of the
+    largest product: summation order only), losses against the formula on the kernel's own products (1e-6)
+    and against the stand-alone tensor-core kernel (1e-3)."""
+    from b200q import ops
+
+    w, a_all, w_s, ref = _case(n_alpha, m, n, k, seed=7 * m + n)
+    wq_all = torch.stack([ops.awq_scale_fake_int(w, w_s[a], 128, 4, False, False) for a in range(n_alpha)])
+    assert ops.awq_search_prequant_supported(a_all[0], w)
+    loss = torch.zeros(n_alpha, dtype=torch.float64, device="cuda")
+    status = torch.zeros((), dtype=torch.int32, device="cuda")
+    c = torch.full((n_alpha, m, n), float("nan"), device="cuda")
+    ops.awq_search_prequant(a_all, wq_all, ref, loss, status, c_out=c)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    for a in range(n_alpha):
+        want = a_all[a].float() @ wq_all[a].float().T
+        assert torch.allclose(c[a], want, rtol=1e-5, atol=1e-5 * float(want.abs().max())), a
+        d = (c[a].bfloat16() - ref).float()
+        want_loss = (d * d).sum().item()
+        assert abs(loss[a].item() - want_loss) <= 1e-6 * want_loss
+        if m % 128 == 0 and n % 128 == 0 and k % 64 == 0:
+            acc = torch.zeros((), dtype=torch.float64, device="cuda")
+            ops.awq_gemm_sqerr(a_all[a], wq_all[a], ref, acc, status, splits=1)
+            assert abs(loss[a].item() - acc.item()) <= 1e-3 * acc.item()
+    # the fused form on the raw weight gives the same losses
+    loss2 = torch.zeros(n_alpha, dtype=torch.float64, device="cuda")
+    ops.awq_search_fused(a_all, w, w_s, ref, loss2, status)
+    assert status.item() == 0
+    assert torch.allclose(loss, loss2, rtol=1e-6)
+
+
+def test_awq_lite_with_a_large_batch_takes_the_finished_weight_path(monkeypatch):
+    """A calibration batch of 2304 tokens (more than FUSED_AWQ_SEARCH_MAX_ROWS): the search writes each
+    candidate's weight once and runs the pair kernel on the finished weights; same alpha, scales and
+    folded weights as the two-kernel pipeline."""
+    import b200q as mtq
+    from b200q import model_calib, ops
+
+    torch.manual_seed(0)
+    base = torch.nn.Sequential(torch.nn.Linear(256, 512, bias=False)).cuda().bfloat16()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = (torch.randn(2304, 256, generator=g, device="cuda") * torch.exp(torch.randn(256, generator=g, device="cuda"))).bfloat16()
+    calls = []
+    real = ops.awq_search_prequant
+    monkeypatch.setattr(ops, "awq_search_prequant", lambda *a, **k: (calls.append(a[0].shape), real(*a, **k))[1])
+    results = []
+    for use in (True, False):
+        model_calib.FUSED_AWQ_SEARCH = use
+        try:
+            m = copy.deepcopy(base)
+            cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+            cfg["algorithm"] = {"method": "awq_lite", "alpha_step": 0.1, "debug": True}
+            mtq.quantize(m, cfg, lambda mod: mod(x))
+            results.append((m[0].awq_lite.loss, m[0].awq_lite.best_alpha, m[0].awq_lite.best_scale, m[0].weight.detach().clone()))
+        finally:
+            model_calib.FUSED_AWQ_SEARCH = True
+    assert calls and calls[0][1:] == (2304, 256)
+    assert not model_calib._SEARCH_SCRATCH
+    (la, aa, sa, wa), (lb, ab, sb, wb) = results
+    for key in la:
+        assert abs(la[key] - lb[key]) <= 1e-3 * lb[key], (key, la[key], lb[key])
+    assert aa == ab and torch.equal(sa, sb) and torch.equal(wa, wb)
