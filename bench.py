@@ -322,8 +322,8 @@ def calibration_phases(dev, world, rank, dims, n_layers, tokens, batches):
             [(n, q, ("percentile",), {"percentile": 99.99}) for n, q in model.items()]))
         return model, {"observe": t_observe, "ranges": t_ranges, "collect": t_collect, "exchange": t_exchange, "readout": t_readout}
 
-    # warm-up: kernels, allocator, and the communicator's collectives, on one layer
-    run_max(1, 1); run_hist(1, 1)
+    # warm-up: kernels, allocator blocks of the sizes the timed pass uses, and the communicator's collectives
+    run_max(n_layers, 1); run_hist(n_layers, 1)
     if world > 1:
         for op in (dist.ReduceOp.MAX, dist.ReduceOp.SUM):
             for _ in range(3):

@@ -262,6 +262,21 @@ int b200q_hist_collect_shared(const void* x, int64_t n, int dtype, int nbins, co
 int b200q_hist_percentile(const unsigned long long* counts, int nbins, const float* edges,
                           float bin_width, double percentile, float* amax_out, void* stream);
 
+/* One histogram of a batched read-out (device-resident table, 8-byte aligned). */
+typedef struct {
+  const unsigned long long* counts;   /* [nbins] live counters */
+  const float* edges;                 /* [nbins + 1] bin edges, or NULL: edge i = bin_width * i */
+  float bin_width;
+  int nbins;
+} b200q_hist_desc;
+
+/* The percentile read-out of n histograms in one launch (one CTA each): amax_out[i] as
+ * b200q_hist_percentile gives for descs[i].  Replaces the per-quantiser loop over
+ * _compute_amax_percentile in finish_stats_collection (calib/histogram.py:328-343,
+ * model_calib.py:145-185). */
+int b200q_hist_percentile_batch(const b200q_hist_desc* descs, int n, double percentile, float* amax_out,
+                                void* stream);
+
 /* ---------------------------------------------------------------- awq_lite search ---------- */
 
 /* MSE calibration, all candidates in one pass: x (T, viewed as [outer, channels, inner], contiguous) is

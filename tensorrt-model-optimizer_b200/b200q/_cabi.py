@@ -22,6 +22,12 @@ class NvFp4Desc(C.Structure):
                 ("nblocks", _i64), ("tile_begin", _i64)]
 
 
+class HistDesc(C.Structure):
+    """Mirror of ``b200q_hist_desc``."""
+
+    _fields_ = [("counts", _p), ("edges", _p), ("bin_width", C.c_float), ("nbins", _i)]
+
+
 # name -> argtypes (restype is int unless listed in _RESTYPES)
 SIGNATURES = {
     "b200q_strerror": [_i],
@@ -53,6 +59,7 @@ SIGNATURES = {
     "b200q_hist_entropy": [_p, _i, _i, _i, _i, _p, _f, _p, _p, _p],
     "b200q_hist_mse": [_p, _i, _p, _d, _i, _i, _p, _p, _p],
     "b200q_hist_percentile": [_p, _i, _p, _f, _d, _p, _p],
+    "b200q_hist_percentile_batch": [_p, _i, C.c_double, _p, _p],
     "b200q_mse_candidates": [_p, _i64, _i64, _i64, _i, _p, _i, _i, _i, _i, _i, _p, _p],
     "b200q_awq_scale_fake_int": [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _i, _p],
     "b200q_sq_diff_sum": [_p, _p, _i64, _i, _p, _p],

@@ -40,17 +40,33 @@ def load_calib_amax_all(items):
     seen nothing are skipped.  The reference loads and validates quantiser by quantiser
     (model_calib.py:145-185), one device->host read each; here the values are tested together, per
     device, and the error names every offending quantiser."""
-    from .calib import MaxCalibrator
+    from .calib import HistogramCalibrator, MaxCalibrator
 
     loaded = {}
+    batched = {}      # (device, percentile) -> histogram calibrators read out by one launch
     for name, q, args, kwargs in items:
         cal = q._calibrator
+        if (isinstance(cal, HistogramCalibrator) and tuple(args) == ("percentile",) and set(kwargs) <= {"percentile"}
+                and cal._calib_hist is not None and cal._calib_hist.is_cuda
+                and (cal._arena is None or cal._ranged)):
+            pct = kwargs.get("percentile", 99.99)
+            if pct < 0 or pct > 100:
+                raise ValueError("Invalid percentile. Must be in range 0 <= percentile <= 100.")
+            cal._resolve()
+            batched.setdefault((cal._calib_hist.device, pct), []).append((name, q))
+            continue
         extra = {"check": False} if isinstance(cal, MaxCalibrator) else {}
         value = cal.compute_amax(*args, **kwargs, **extra)
         if value is None:
             continue
         q._store_calib_amax(value)
         loaded.setdefault(q._amax.device, []).append((name, q))
+    for (dev, pct), group in batched.items():
+        values = ops.hist_percentile_batch(
+            [(q._calibrator._calib_hist, q._calibrator._num_bins, q._calibrator._calib_bin_edges) for _, q in group], pct)
+        for i, (name, q) in enumerate(group):
+            q._store_calib_amax(values[i])
+            loaded.setdefault(q._amax.device, []).append((name, q))
     for dev, group in loaded.items():
         flat = torch.cat([q._amax.detach().reshape(-1).float() for _, q in group])
         if bool((~torch.isfinite(flat) | (flat < 0)).any()):

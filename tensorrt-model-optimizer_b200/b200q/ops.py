@@ -466,6 +466,27 @@ def hist_percentile(counts: torch.Tensor, nbins: int, edges: torch.Tensor | None
     return out
 
 
+def hist_percentile_batch(items, percentile: float) -> torch.Tensor:
+    """Percentile read-out of many histograms in one launch.  ``items``: (counts int64 device tensor, nbins,
+    edges fp32 device tensor [>= nbins + 1]) per histogram, all on one device.  Returns fp32 [len(items)]."""
+    n = len(items)
+    dev = items[0][0].device
+    descs = (_cabi.HistDesc * n)()
+    keep = []
+    for d, (counts, nbins, edges) in zip(descs, items):
+        e = edges.to(device=dev, dtype=torch.float32).contiguous()
+        assert counts.dtype == torch.int64 and counts.is_contiguous() and counts.numel() >= nbins
+        assert e.numel() >= nbins + 1
+        keep.append(e)
+        d.counts, d.edges, d.bin_width, d.nbins = counts.data_ptr(), e.data_ptr(), 0.0, int(nbins)
+    table = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8).to(dev)
+    out = torch.empty(n, dtype=torch.float32, device=dev)
+    with _on(dev):
+        call("b200q_hist_percentile_batch", table.data_ptr(), n, ctypes.c_double(percentile), out.data_ptr(),
+             torch.cuda.current_stream(dev).cuda_stream)
+    return out
+
+
 # --------------------------------------------------------------------------- MSE search --------
 
 def mse_candidates_supported(x: torch.Tensor, axis) -> bool:

@@ -315,11 +315,9 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
 constexpr int kPctThreads = 1024;
 constexpr int kPctChunk = 4096;   // quotients staged per round (32 KB of shared memory)
 
-__global__ void __launch_bounds__(kPctThreads)
-hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
-                       const float* __restrict__ edges, float bin_width, double frac,
-                       float* __restrict__ amax_out) {
-  pdl_prologue();
+__device__ __forceinline__ void hist_percentile_body(const unsigned long long* __restrict__ counts, int nbins,
+                                                     const float* __restrict__ edges, float bin_width, double frac,
+                                                     float* __restrict__ amax_out) {
   __shared__ double q[kPctChunk];
   __shared__ unsigned long long warp_sums[kPctThreads / 32];
   __shared__ unsigned long long total_s;
@@ -356,6 +354,22 @@ hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
     const int idx = idx_s < 0 ? nbins : idx_s;
     *amax_out = edges ? edges[idx] : bin_width * static_cast<float>(idx);
   }
+}
+
+__global__ void __launch_bounds__(kPctThreads)
+hist_percentile_kernel(const unsigned long long* __restrict__ counts, int nbins,
+                       const float* __restrict__ edges, float bin_width, double frac,
+                       float* __restrict__ amax_out) {
+  pdl_prologue();
+  hist_percentile_body(counts, nbins, edges, bin_width, frac, amax_out);
+}
+
+// One CTA per histogram: the percentile read-out of all calibrators of a model in one launch.
+__global__ void __launch_bounds__(kPctThreads)
+hist_percentile_batch_kernel(const b200q_hist_desc* __restrict__ descs, double frac, float* __restrict__ amax_out) {
+  pdl_prologue();
+  const b200q_hist_desc d = descs[blockIdx.x];
+  hist_percentile_body(d.counts, d.nbins, d.edges, d.bin_width, frac, amax_out + blockIdx.x);
 }
 
 // ---- entropy (KL-divergence) read-out -------------------------------------------------------------
@@ -598,6 +612,17 @@ extern "C" int b200q_hist_percentile(const unsigned long long* counts, int nbins
   if (!(percentile >= 0.0 && percentile <= 100.0)) return B200Q_ERR_ARG;
   hist_percentile_kernel<<<1, kPctThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       counts, nbins, edges, bin_width, percentile / 100.0, amax_out);
+  return launch_status();
+}
+
+extern "C" int b200q_hist_percentile_batch(const b200q_hist_desc* descs, int n, double percentile, float* amax_out,
+                                           void* stream) {
+  B200Q_REQUIRE_PTR(descs); B200Q_REQUIRE_PTR(amax_out);
+  if ((reinterpret_cast<uintptr_t>(descs) & 7u) != 0) return B200Q_ERR_ALIGN;
+  if (n <= 0) return B200Q_ERR_SHAPE;
+  if (!(percentile >= 0.0 && percentile <= 100.0)) return B200Q_ERR_ARG;
+  hist_percentile_batch_kernel<<<n, kPctThreads, 0, static_cast<cudaStream_t>(stream)>>>(descs, percentile / 100.0,
+                                                                                        amax_out);
   return launch_status();
 }
 

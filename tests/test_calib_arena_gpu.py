@@ -218,3 +218,26 @@ def test_batched_amax_load_reports_every_invalid_quantiser(mtq):
         q(bad if name in ("q1", "q3") else good)
     with pytest.raises(ValueError, match=r"q1.*q3"):
         finish_stats_collection(model)
+
+
+def test_batched_percentile_read_out_equals_the_single_one(mtq):
+    """load_calib_amax_all reads the percentile amax of all histogram calibrators with one launch; every
+    value equals the single-histogram kernel's (bit for bit: the same code per CTA), for arena and
+    stand-alone calibrators, grown and not grown histograms."""
+    from b200q.calib import attach_histogram_arena
+    from b200q.model_calib import load_calib_amax_all
+
+    model = _quantizers(mtq, 5)
+    loose = mtq.nn.TensorQuantizer(mtq.QuantizerAttributeConfig(num_bits=8, calibrator="histogram")).cuda()
+    loose.enable_calib(); loose.disable_quant()
+    attach_histogram_arena(model)
+    model["loose"] = loose
+    for i, q in enumerate(model.values()):
+        for x in _batches(40 + i, 3, grow=1.0 * i):
+            q(x)
+    want = {n: q._calibrator.compute_amax("percentile", percentile=99.9).item() for n, q in model.items()}
+    assert model["q4"]._calibrator._num_bins > 2048          # grown histograms are part of the batch
+    n = load_calib_amax_all([(name, q, ("percentile",), {"percentile": 99.9}) for name, q in model.items()])
+    assert n == 6
+    for name, q in model.items():
+        assert q._amax.item() == want[name], name
