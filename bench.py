@@ -7,11 +7,20 @@ One step = NVFP4 real quantisation + packing (global abs-max pass, then block-sc
 pack pass) of every linear weight of a random-init Llama-3-8B-shaped model: 32 layers of
 q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336, bf16, Student-t(4) values
 scaled to std 0.02.  With N GPUs the 32 layers are split across the ranks (strong scaling, no
-data-path collective).  Prints one JSON line (rank 0).
+data-path collective).  Prints one JSON line (rank 0) with, beside the contract's keys:
+
+  roofline      the quantise kernel against the measured copy bandwidth (and the nominal 8 TB/s)
+  e2e           mtq.compress on a host-resident (pinned) module tree, with the copy-only ceiling beside it
+  calibration   data-parallel max and histogram calibration of the model's 224 input quantisers, every
+                rank on its own batches, exchanges included (at every N)
+  cpu_baseline  the reference's CPU torch path on the host cores (N = 1), also for the other formats
+  formats       the other kernels of the path (N = 1): fake quant, calibration, INT4, MSE, dequantise, the
+                awq_lite search, the real-quant GEMMs, and the reference's own GPU kernels timed beside ours
 
 ``--impl reference`` times the reference's CPU torch path (restated operation by operation in
 oracle/torch_path.py) on the host cores for a bounded sample of the same workload, and reports a
-fused multi-threaded C restatement (oracle/nvfp4_ref.c) beside it.
+fused multi-threaded C restatement (oracle/nvfp4_ref.c) beside it.  ``--workload calib70b`` runs the
+calibration phases on Llama-3-70B shapes followed by that model's weight quantisation.
 """
 from __future__ import annotations
 
