@@ -479,6 +479,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
   }
 
+  grace_after_abort(&sm->abort);
   __syncwarp();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();

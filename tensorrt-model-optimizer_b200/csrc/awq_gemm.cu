@@ -256,6 +256,7 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (lane == 0 && finish) atomicAdd(sum_io, static_cast<double>(sq));
   }
 
+  grace_after_abort(&sm->abort);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

@@ -408,6 +408,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     if (warp < 2) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
   }
 
+  grace_after_abort(&sm->abort);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

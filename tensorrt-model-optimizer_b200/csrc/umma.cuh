@@ -41,6 +41,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Last step of a CTA that gave up a wait: a bounded pause (about 64 microseconds) before it frees its
+// tensor memory and leaves, so that bulk copies and MMAs it still has in flight — their latencies are
+// microseconds — have landed in shared and tensor memory that is still its own.  Free when nothing went wrong.
+__device__ __forceinline__ void grace_after_abort(const uint32_t* abort_flag) {
+  if (*reinterpret_cast<const volatile uint32_t*>(abort_flag)) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
