@@ -194,7 +194,7 @@ __host__ __device__ inline Hist16Layout hist16_layout(float range_max, float cap
   lay.values = static_cast<int>(lay.hi1 - lay.lo + 1);
   lay.values = (lay.values + 3) & ~3;   // padding counters are never addressed
   lay.smem_bins = smem_bins;
-  lay.rshift = 4;   // 16 replicas: 32 are conflict-free but measured no faster, and double the clearing
+  lay.rshift = 4;   // 16 replicas; measured on 33.5 M-element batches: 8 replicas 17.5 us per launch, 16: 14.0, 32: 17.4
   while (lay.rshift > 0 && (static_cast<int64_t>(lay.values) << lay.rshift) + lay.smem_bins + 3 > kHist16SmemWords)
     --lay.rshift;
   return lay;
@@ -280,8 +280,7 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   __syncthreads();
 
   // values -> bins with the reference arithmetic: bin = int(RN(RN(a * nbins) / range)), the right
-  // edge in the last bin.  Thread v sums the replicas of value v starting at its own lane's
-  // replica, so that the lanes of a warp read different banks.
+  // edge in the last bin.  Thread v sums the replicas of value v.
   uint32_t* bins = sh + vwords;
   const float fbins = static_cast<float>(nbins);
   const uint32_t last = static_cast<uint32_t>(nbins - 1), cap_last = static_cast<uint32_t>(open.capacity - 1);
@@ -289,7 +288,19 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   for (int v = threadIdx.x; v < in_range; v += blockDim.x) {
     const uint32_t* row = sh + (v << lay.rshift);
     uint32_t c = 0;
-    for (uint32_t k = 0; k <= rmask; ++k) c += row[(k + threadIdx.x) & rmask];
+    // This phase reads every replica of every value once (about 100 KB): it runs at the speed of shared
+    // memory, so the reads are laid out free of bank conflicts.  A row of 2^rshift words starts at bank
+    // (lane << rshift) % 32; lanes whose rows start in the same bank begin at different replicas.
+    if (lay.rshift == 4) {        // sixteen replicas: four 16-byte reads, rotated by lane / 2
+      const uint4* row4 = reinterpret_cast<const uint4*>(row);
+      const uint32_t rot = (threadIdx.x >> 1) & 3u;
+      const uint4 p0 = row4[rot], p1 = row4[(rot + 1) & 3u], p2 = row4[(rot + 2) & 3u], p3 = row4[(rot + 3) & 3u];
+      c = (p0.x + p0.y + p0.z + p0.w) + (p1.x + p1.y + p1.z + p1.w) + (p2.x + p2.y + p2.z + p2.w) +
+          (p3.x + p3.y + p3.z + p3.w);
+    } else {
+      const uint32_t rot = (threadIdx.x & 31u) >> (5 - lay.rshift);
+      for (uint32_t k = 0; k <= rmask; ++k) c += row[(k + rot) & rmask];
+    }
     if (c == 0) continue;
     const float a = value_of_bits16<T>(lay.lo + v);
     if (!(a <= open.cap_range)) continue;   // cannot happen by construction of hi1; kept as a guard
