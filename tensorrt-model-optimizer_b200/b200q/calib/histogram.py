@@ -391,5 +391,46 @@ def _mse_amax(hist, edges, num_bits, unsigned, stride=1, start_bin=128):
 
 
 def calibrate_weights(model, method="percentile", perchannel=True, percentile=99.99, num_bins=2048):
-    """Not part of the accelerated path: weights are calibrated by ``max_calibrate``."""
-    warnings.warn("calibrate_weights is not provided; use b200q.calibrate(model, 'max')")
+    """Calibrate the weight quantiser of every quantised sub-module from its weight alone, with ``method``
+    ("max", "mse" or "percentile") regardless of the calibrator the quantiser carries; per output channel
+    (axis 0) when ``perchannel``.  The reference builds one numpy histogram per channel on the host
+    (modelopt/torch/quantization/calib/histogram.py:346-433); here every channel gets a device histogram
+    (one binning launch each) and, for "percentile", all channels of a weight are read out by one launch.
+    Each value equals what a HistogramCalibrator fed that tensor or channel returns."""
+    from ..utils import convert_quantization_axis_to_reduce_axis, reduce_amax
+
+    for _, module in model.named_modules():
+        wq, w = getattr(module, "weight_quantizer", None), getattr(module, "weight", None)
+        if wq is None or w is None:
+            continue
+        w = w.detach()
+        axis = 0 if perchannel else None
+        if method == "max":
+            amax = reduce_amax(w, axis=convert_quantization_axis_to_reduce_axis(w, axis))
+        elif method in ("mse", "percentile"):
+            if method == "percentile" and (percentile < 0 or percentile > 100):
+                raise ValueError("Invalid percentile. Must be in range 0 <= percentile <= 100.")
+            parts = [w] if axis is None else [w.select(axis, i) for i in range(w.shape[axis])]
+            cals = []
+            for part in parts:
+                cal = HistogramCalibrator(wq.num_bits, None, wq.unsigned, num_bins=num_bins)
+                cal.collect(part.contiguous())
+                cals.append(cal)
+            if method == "percentile" and w.is_cuda:
+                for cal in cals:
+                    cal._resolve()
+                values = ops.hist_percentile_batch([(c._calib_hist, c._num_bins, c._calib_bin_edges) for c in cals],
+                                                   percentile)
+            else:
+                values = torch.stack([c.compute_amax(method).reshape(()).to(w.device) for c in cals])
+            if axis is None:
+                amax = values.reshape(())
+            else:
+                shape = [1] * w.dim()
+                shape[axis] = w.shape[axis]
+                amax = values.reshape(shape)
+        else:
+            raise TypeError(f"Unsupported calibration method {method}")
+        if amax.numel() == 1:
+            amax = amax.reshape(())
+        wq.amax = amax.to(w.dtype) if method == "max" else amax
