@@ -29,6 +29,15 @@ class QuantLinear(nn.Linear, QuantModule):
     default_quant_desc_weight = QuantizerAttributeConfig(num_bits=8, axis=0)
     default_quant_desc_output = QuantizerAttributeConfig(num_bits=8)
 
+    def __init__(self, in_features, out_features, bias=True, device=None, dtype=None, quant_desc_input=None,
+                 quant_desc_weight=None, quant_desc_output=None):
+        """Build a quantised linear layer directly (the reference's legacy constructor with
+        ``quant_desc_*`` descriptors, nn/modules/quant_linear.py and quant_module.py); ``convert`` is the
+        way an existing ``nn.Linear`` becomes one."""
+        nn.Linear.__init__(self, in_features, out_features, bias=bias, device=device, dtype=dtype)
+        self._original_cls = nn.Linear
+        self._setup(quant_desc_input, quant_desc_weight, quant_desc_output)
+
     @classmethod
     def convert(cls, module: nn.Linear) -> "QuantLinear":
         """Turn ``module`` into a QuantLinear in place and return it."""
@@ -38,10 +47,10 @@ class QuantLinear(nn.Linear, QuantModule):
         module._setup()
         return module
 
-    def _setup(self):
-        self.input_quantizer = TensorQuantizer(self.default_quant_desc_input)
-        self.weight_quantizer = TensorQuantizer(self.default_quant_desc_weight)
-        self.output_quantizer = TensorQuantizer(self.default_quant_desc_output)
+    def _setup(self, quant_desc_input=None, quant_desc_weight=None, quant_desc_output=None):
+        self.input_quantizer = TensorQuantizer(quant_desc_input or self.default_quant_desc_input)
+        self.weight_quantizer = TensorQuantizer(quant_desc_weight or self.default_quant_desc_weight)
+        self.output_quantizer = TensorQuantizer(quant_desc_output or self.default_quant_desc_output)
         self.output_quantizer.disable()
         dev = self.weight.device
         if dev.type != "meta":
