@@ -149,6 +149,7 @@ def restore_from_modelopt_state(model: nn.Module, state: dict) -> nn.Module:
     from .conversion import replace_quant_module, set_quantizer_by_cfg
     from .qtensor import QTensorWrapper
 
+    assert not model.__dict__.get("_b200q_state"), "Model already has modelopt state!"
     modes = state.get("modelopt_state_dict", [])
     replace_quant_module(model)
     for mode, cfg in modes:

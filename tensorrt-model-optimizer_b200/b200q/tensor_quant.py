@@ -17,6 +17,10 @@ __all__ = ["normalized_hadamard_transform", "fake_tensor_quant", "scaled_e4m3", 
 @torch.library.custom_op("b200q::quantize_op", mutates_args=())
 def quantize_op(input: torch.Tensor, amax: torch.Tensor, num_bits: int = 8, exponent_bits: int = 0,
                 unsigned: bool = False, narrow_range: bool = True) -> torch.Tensor:
+    if input.dtype == torch.float64:
+        # the reference kernels take a double tensor and compute on its float cast
+        # (modelopt/torch/quantization/src/tensor_quant_gpu.cu:29-44,64-78): same here, around the fp32 kernel
+        return quantize_op(input.float(), amax, num_bits, exponent_bits, unsigned, narrow_range).double()
     if num_bits == 8 and exponent_bits == 4:
         return ops.fake_e4m3(input, amax)
     if exponent_bits == 0:
