@@ -239,6 +239,13 @@ class QuantizerAttributeConfig:
                 raise ValueError("num_bits must be a positive integer or a tuple of positive integers.")
         elif not (isinstance(self.num_bits, tuple) and len(self.num_bits) == 2):
             raise ValueError("num_bits must be a positive integer or a tuple of positive integers.")
+        if isinstance(self.num_bits, tuple):
+            # reference config.py:710-746: the floating formats that exist, and only E4M3 without dynamic blocks
+            if self.num_bits not in ((4, 3), (5, 2), (2, 1), (1, 2), (0, 3), (3, 0), (3, 2), (2, 3)):
+                raise ValueError("Supported FPx quantization formats: FP8 (E4M3, E5M2), FP6(E3M2, E2M3), FP4(E2M1).")
+            if self.num_bits != (4, 3) and (self.block_sizes is None or self.block_sizes.get("type") != "dynamic"):
+                raise ValueError("Only blockwise dynamic quantization is supported with quantization formats "
+                                 f"E{self.num_bits[0]}M{self.num_bits[1]}.")
         if self.learn_amax:
             raise ValueError("learn_amax is deprecated and reserved for backward compatibility.")
         if self.type not in ("static", "dynamic"):

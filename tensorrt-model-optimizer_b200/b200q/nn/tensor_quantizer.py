@@ -99,6 +99,16 @@ class TensorQuantizer(nn.Module):
         if self._calibrator is not None:
             self._calibrator._num_bits = v
 
+    @unsigned.setter
+    def unsigned(self, v):
+        self._unsigned = v
+        if self._calibrator is not None:
+            self._calibrator._unsigned = v
+
+    @narrow_range.setter
+    def narrow_range(self, v):
+        self._narrow_range = v
+
     @block_sizes.setter
     def block_sizes(self, v):
         self._axis = None

@@ -118,8 +118,31 @@ def _axis_view(x: torch.Tensor, amax: torch.Tensor):
     return outer, n, inner
 
 
+def _kept_dims_first(x: torch.Tensor, amax):
+    """``amax`` that broadcasts over ``x`` with two or more kept dimensions (e.g. the [n0, 1, n2, 1] of blocks
+    over several dimensions) -> the permutation of ``x`` that brings the kept dimensions to the front, where
+    they flatten into the rows of a per-row problem; None for every other amax."""
+    if not isinstance(amax, torch.Tensor) or amax.dim() != x.dim():
+        return None
+    kept = [d for d in range(x.dim()) if amax.shape[d] != 1]
+    if len(kept) < 2 or any(amax.shape[d] != x.shape[d] for d in kept):
+        return None
+    return kept + [d for d in range(x.dim()) if d not in kept]
+
+
+def _per_row_of_permuted(fn, x, amax, perm, *args):
+    xp = x.permute(perm).contiguous()
+    rows = amax.numel()
+    yp = fn(xp.reshape(rows, -1), amax.permute(perm).reshape(rows, 1), *args)
+    inverse = [perm.index(d) for d in range(len(perm))]
+    return yp.reshape(xp.shape).permute(inverse).contiguous()
+
+
 def fake_int(x: torch.Tensor, amax: torch.Tensor, num_bits: int = 8, unsigned: bool = False,
              narrow_range: bool = True) -> torch.Tensor:
+    perm = _kept_dims_first(x, amax)
+    if perm is not None:
+        return _per_row_of_permuted(fake_int, x, amax, perm, num_bits, unsigned, narrow_range)
     x = _prep(x)
     y = torch.empty_like(x)
     if x.numel() == 0:
@@ -153,6 +176,9 @@ def fake_int_rows_dynamic(x: torch.Tensor, num_bits: int = 8, unsigned: bool = F
 
 
 def fake_e4m3(x: torch.Tensor, amax: torch.Tensor | None) -> torch.Tensor:
+    perm = _kept_dims_first(x, amax)
+    if perm is not None:
+        return _per_row_of_permuted(fake_e4m3, x, amax, perm)
     x = _prep(x)
     y = torch.empty_like(x)
     if x.numel() == 0:

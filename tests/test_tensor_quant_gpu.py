@@ -211,3 +211,17 @@ def test_fp4_grid_points_and_rounding_boundaries(tq, dtype, block_size):
     below = mid.clone()
     below[:, :-1] -= 0.1
     check(below * sign, grid * sign)
+
+
+# ---- an amax kept along several dimensions (the reference's eager broadcast, tensor_quant.py:574-612) -----
+
+@pytest.mark.parametrize("amax_shape", [(2, 2, 1, 2, 1), (2, 2, 1, 1, 1), (1, 2, 3, 1, 2)])
+def test_amax_kept_along_several_dimensions(tq, amax_shape):
+    x = _rand(2, 2, 3, 2, 2, seed=30)
+    reduce = [d for d, n in enumerate(amax_shape) if n == 1]
+    amax = x.abs().amax(dim=reduce, keepdim=True) * 0.8
+    assert tuple(amax.shape) == amax_shape
+    scale = torch.full((), 127.0, device="cuda") / amax
+    want = torch.clamp(torch.round(x * scale), -128, 127) / scale
+    assert torch.equal(tq.fake_tensor_quant(x, amax, None, 8, False, False), want)
+    assert torch.allclose(tq.scaled_e4m3(x, amax, None, 4, 3), fp8_eager(x.clamp(-amax, amax), amax))
