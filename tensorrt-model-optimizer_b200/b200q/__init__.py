@@ -8,6 +8,7 @@ from .conversion import (replace_quant_module, set_quantizer_attribute, set_quan
                          set_quantizer_by_cfg_context)
 from .model_calib import awq_clip, awq_lite, histogram_calibrate, max_calibrate, mse_calibrate, smoothquant  # noqa: F401
 from .model_quant import (calibrate, compress, disable_quantizer, enable_quantizer, fold_weight,  # noqa: F401
-                          modelopt_state, print_quant_summary, quantize, restore_from_modelopt_state)
+                          modelopt_state, postprocess_amax, print_quant_summary, quantize,
+                          restore_from_modelopt_state)
 
 __version__ = "0.1.0"

@@ -21,7 +21,7 @@ from .calib import MseCalibrator
 from .nn import SequentialQuantizer, TensorQuantizer, is_quantized_linear
 
 __all__ = ["max_calibrate", "mse_calibrate", "histogram_calibrate", "awq_lite", "awq_clip", "smoothquant", "awq", "enable_stats_collection", "finish_stats_collection", "load_calib_amax_all",
-           "weight_only_quantize", "apply_pre_quant_scale_and_smooth"]
+           "weight_only_quantize", "apply_pre_quant_scale_and_smooth", "disable_pre_quant_scale_and_resmooth"]
 
 
 def enable_stats_collection(model: nn.Module):
@@ -250,20 +250,47 @@ def get_scale(x_max, w_max, alpha):
     return (s / (s.max() * s.min()).sqrt()).view(-1)
 
 
+def _fold_into_weight(linear, per_input_channel):
+    """W <- (W * v[None, :]) in the weight's dtype, then the weight amax is calibrated afresh."""
+    w = linear.weight
+    w.data.copy_((w * per_input_channel.to(w.device).squeeze()[None, :]).to(w.dtype))
+    linear.weight_quantizer.reset_amax()
+    max_calibrate(linear, lambda lin: lin.weight_quantizer(lin.weight), distributed_sync=False)
+
+
 @torch.no_grad()
-def apply_pre_quant_scale_and_smooth(linear, pre_quant_scale):
+def disable_pre_quant_scale_and_resmooth(linear, delete_pre_quant_scale: bool = False):
+    """Undo the smoothing of one quantised linear layer: the input-side scale is folded back into the weight
+    and switched off (kept as a buffer unless ``delete_pre_quant_scale``), the input amax returns to the
+    largest per-channel value seen before smoothing (reference model_calib.py:308-339)."""
+    assert is_quantized_linear(linear), "Only quantized linear modules are supported"
+    iq = linear.input_quantizer
+    assert iq._enable_pre_quant_scale, "pre_quant_scale should be enabled first!"
+    assert hasattr(iq, "_pre_quant_scale"), "pre_quant_scale should be available"
+    _fold_into_weight(linear, iq._pre_quant_scale.to(torch.float32))
+    iq._enable_pre_quant_scale = False
+    if iq.amax is not None:
+        assert hasattr(iq, "_amax_for_smoothing")
+        iq.amax = iq._amax_for_smoothing.amax().to(device=linear.weight.device, dtype=linear.weight.dtype)
+    if delete_pre_quant_scale:
+        delattr(iq, "_pre_quant_scale")
+
+
+@torch.no_grad()
+def apply_pre_quant_scale_and_smooth(linear, pre_quant_scale=None):
     """Set ``input_quantizer.pre_quant_scale`` and fold its inverse into the weight, then
-    re-calibrate the weight amax (reference model_calib.py:344-408)."""
+    re-calibrate the weight amax (reference model_calib.py:344-408).  Without a scale the quantiser's
+    stored (switched-off) one is applied again."""
     assert is_quantized_linear(linear), "Only quantized linear modules are supported"
     assert linear.input_quantizer.pre_quant_scale is None, "pre_quant_scale should be None first!"
+    if pre_quant_scale is None:
+        pre_quant_scale = getattr(linear.input_quantizer, "_pre_quant_scale", None)
+    assert pre_quant_scale is not None, "pre_quant_scale should be provided or already set"
     assert torch.all(pre_quant_scale > 0), "pre_quant_scale should be positive"
     pqs = pre_quant_scale.to(torch.float32)
     linear.input_quantizer._enable_pre_quant_scale = True
     linear.input_quantizer.pre_quant_scale = pqs.to(linear.weight.dtype)
-    inv = 1.0 / pqs
-    linear.weight.data.copy_((linear.weight * inv.to(linear.weight.device).squeeze()[None, :]).to(linear.weight.dtype))
-    linear.weight_quantizer.reset_amax()
-    max_calibrate(linear, lambda lin: lin.weight_quantizer(lin.weight), distributed_sync=False)
+    _fold_into_weight(linear, 1.0 / pqs)
     if linear.input_quantizer.amax is not None:
         assert hasattr(linear.input_quantizer, "_amax_for_smoothing")
         dev, dt = linear.weight.device, linear.weight.dtype

@@ -12,7 +12,7 @@ from .model_calib import awq, max_calibrate, mse_calibrate, smoothquant
 from .nn import QuantLinear, RealQuantLinear, SequentialQuantizer, TensorQuantizer
 from .qtensor import pack_real_quantize_weight
 
-__all__ = ["quantize", "calibrate", "compress", "restore_from_modelopt_state", "disable_quantizer", "enable_quantizer",
+__all__ = ["quantize", "calibrate", "compress", "restore_from_modelopt_state", "postprocess_amax", "disable_quantizer", "enable_quantizer",
            "print_quant_summary", "fold_weight", "modelopt_state"]
 
 def _awq_variant(variant):
@@ -82,6 +82,16 @@ def compress(model: nn.Module, config=None) -> nn.Module:
             wq._dequantize = False
         pack_real_quantize_weight(model)
     _record_mode(model, "real_quantize")
+    return model
+
+
+def postprocess_amax(model: nn.Module, key: str, post_process_fn) -> nn.Module:
+    """Replace the amax of every calibrated quantiser whose name matches the wildcard ``key`` by
+    ``post_process_fn(amax)`` (reference model_quant.py:121-133)."""
+    assert isinstance(key, str), "key should be a string"
+    for name, m in model.named_modules():
+        if isinstance(m, TensorQuantizer) and hasattr(m, "_amax") and fnmatch.fnmatch(name, key):
+            m.amax = post_process_fn(m.amax)
     return model
 
 
