@@ -113,3 +113,61 @@ def test_compress_config_selects_layers_by_pattern(name):
     assert seen == {True: 2, False: 1}
     x = SimpleLinear.get_input().cuda()
     assert model(x).shape[0] == x.shape[0]
+
+
+# ---- every configuration of the reference's sweep on the small model --------------------------------------
+# (tests/gpu/torch/quantization/test_quantize_cuda.py:30-84; the SVDQuant entry is outside this library)
+
+SWEEP = ["INT8_DEFAULT_CFG", "FP8_DEFAULT_CFG", "W4A8_AWQ_BETA_CFG", "INT8_SMOOTHQUANT_CFG",
+         "INT4_BLOCKWISE_WEIGHT_ONLY_CFG", "INT4_AWQ_CFG", "INT4_AWQ_CLIP", "INT4_AWQ_FULL", "NVFP4_DEFAULT_CFG",
+         "NVFP4_AWQ_LITE_CFG", "NVFP4_AWQ_CLIP_CFG", "NVFP4_AWQ_FULL_CFG", "MXFP8_DEFAULT_CFG", "MXFP6_DEFAULT_CFG",
+         "MXFP4_DEFAULT_CFG", "MXINT8_DEFAULT_CFG", "NVFP4_KV_ROTATE_CFG", "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG"]
+
+
+@pytest.mark.parametrize("name", SWEEP)
+def test_quantize_runs_for_every_configuration(name):
+    import b200q as mtq
+
+    if name in ("INT4_AWQ_CLIP", "INT4_AWQ_FULL"):          # the reference's test-local variants of INT4_AWQ_CFG
+        cfg = copy.deepcopy(mtq.INT4_AWQ_CFG)
+        cfg["algorithm"] = {"INT4_AWQ_CLIP": "awq_clip", "INT4_AWQ_FULL": "awq_full"}[name]
+    else:
+        cfg = copy.deepcopy(getattr(mtq, name))
+    if name == "FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG":
+        cfg["quant_cfg"]["*weight_quantizer"]["block_sizes"] = {-1: 8, -2: 8}
+    torch.manual_seed(3)
+    model = SimpleLinear().cuda()
+    data = [model.get_input().cuda() for _ in range(8)]
+    with torch.no_grad():
+        plain = model(data[0])
+    mtq.quantize(model, cfg, lambda m: [m(b) for b in data])
+    assert all(hasattr(m, "weight_quantizer") for m in model.net if isinstance(m, nn.Linear))
+    with torch.no_grad():
+        out = model(data[0])
+    assert out.shape == plain.shape and torch.isfinite(out).all()
+    assert (out - plain).abs().mean() <= 0.5 * plain.abs().mean() + 0.05
+
+
+@pytest.mark.parametrize("name", ["INT8_SMOOTHQUANT_CFG", "W4A8_AWQ_BETA_CFG"])
+def test_save_restore_of_a_fake_quantised_model(name):
+    """Reference test_quantize_cuda.py:86-95 (the linear-model rows): also restores into a model built on
+    the CPU and moved afterwards."""
+    import b200q as mtq
+
+    model, data = _quantized(name, batches=2)
+    state = mtq.modelopt_state(model)
+    torch.manual_seed(1)
+    fresh = SimpleLinear().cuda()
+    mtq.restore_from_modelopt_state(fresh, state)
+    fresh.load_state_dict(model.state_dict())
+    with torch.no_grad():
+        want = model(data[0])
+        assert torch.allclose(want, fresh(data[0]))
+    late = SimpleLinear()
+    mtq.restore_from_modelopt_state(late, state)
+    late.load_state_dict(model.state_dict())
+    late.cuda()
+    with torch.no_grad():
+        assert torch.allclose(want, late(data[0]))
+    if name == "INT8_SMOOTHQUANT_CFG":
+        assert all(m.input_quantizer.axis is None for m in fresh.net if isinstance(m, nn.Linear))
