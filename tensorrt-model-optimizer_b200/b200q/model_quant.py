@@ -64,7 +64,11 @@ def compress(model: nn.Module, config=None) -> nn.Module:
     real-quant mode and the weight is replaced by its packed form (``QTensorWrapper``); scales are
     kept as ``_scale`` / ``_double_scale`` buffers of the quantiser.
 
-    ``config`` may carry ``{"compress": {pattern: bool}}`` to choose layers by name."""
+    ``config`` may carry ``{"compress": {pattern: bool}}`` to choose layers by name and
+    ``{"quant_gemm": bool}`` (default on, as in the reference's compress.py:124-128): layers whose input and
+    weight quantisers are both enabled are marked to run a registered real-quantisation GEMM."""
+    from .backends.gemm_registry import disable_real_quant_gemm, enable_real_quant_gemm
+
     patterns = (config or {}).get("compress", {"default": True}) if isinstance(config, dict) else {"default": True}
     with SequentialQuantizer.convert_to_single_quantizer(model):
         for name, m in model.named_modules():
@@ -81,7 +85,9 @@ def compress(model: nn.Module, config=None) -> nn.Module:
             wq._fake_quant = False
             wq._dequantize = False
         pack_real_quantize_weight(model)
-    _record_mode(model, "real_quantize")
+    quant_gemm = bool(config.get("quant_gemm", True)) if isinstance(config, dict) else True
+    (enable_real_quant_gemm if quant_gemm else disable_real_quant_gemm)(model)
+    _record_mode(model, "real_quantize", {"quant_gemm": quant_gemm})
     return model
 
 
@@ -181,5 +187,9 @@ def restore_from_modelopt_state(model: nn.Module, state: dict) -> nn.Module:
         m.__class__ = RealQuantLinear
         packed = torch.empty(meta["quantized_data.shape"], dtype=meta["quantized_data.dtype"], device=m.weight.device)
         m.weight = QTensorWrapper(packed, metadata=dict(meta["metadata"]))
+    for mode, cfg in modes:
+        if mode == "real_quantize":
+            from .backends.gemm_registry import disable_real_quant_gemm, enable_real_quant_gemm
+            (enable_real_quant_gemm if (cfg or {}).get("quant_gemm", True) else disable_real_quant_gemm)(model)
     model.__dict__["_b200q_state"] = list(modes)
     return model

@@ -71,7 +71,7 @@ def test_quantize_max_calibration_matches_reference(mtq, fmt):
         # GEMMs accumulate in a different order on the two devices: outputs agree to bf16 noise
         assert np.allclose(f32_from_tensor(y), ref, rtol=5e-2, atol=5e-3 * np.abs(ref).max())
     else:
-        mtq.compress(model)
+        mtq.compress(model, config={"quant_gemm": False})
         assert np.array_equal(np.array(sorted(model.state_dict().keys())), g["nvfp4_state_keys"])
         for name in ("up_proj", "down_proj"):
             lin = getattr(model, name)

@@ -81,8 +81,11 @@ def _grads(model, x):
 @pytest.mark.parametrize(("which", "atol_bias", "atol_input"), [("nvfp4", 0.5, 0.2), ("fp8", 0.02, 0.02)])
 def test_gradients_through_a_compressed_model(which, atol_bias, atol_input):
     mtq, cfg, _ = _case(which)
-    torch.manual_seed(1)
-    model = SimpleLinear().half().cuda()
+    # the reference's weights and inputs (CPU generator, seed 42): its two models are built one after the
+    # other when the test module loads, the input and the calibration batches after a re-seed
+    torch.manual_seed(42)
+    model = [SimpleLinear(), SimpleLinear()][("nvfp4", "fp8").index(which)].half().cuda()
+    torch.manual_seed(42)
     x = model.get_input().half().cuda().requires_grad_(True)
     data = [model.get_input().half().cuda() for _ in range(8)]
     mtq.quantize(model, cfg, lambda m: [m(b) for b in data])
@@ -119,3 +122,28 @@ def test_dynamic_and_calibrated_scales_fake_and_compressed(which, atol, rtol):
                 assert torch.allclose(want, through_gemm, atol=atol, rtol=rtol)
                 assert torch.allclose(through_gemm, fake(x), atol=atol / 2)
                 assert torch.allclose(through_gemm, packed(x), atol=atol / 2)
+
+
+def test_compress_switches_the_gemm_on(tmp_path):
+    """Reference backends/test_gemm_registry.py:107-131 and compress.py:124-128."""
+    import b200q as mtq
+
+    def quantized():
+        torch.manual_seed(3)
+        model = SimpleLinear().cuda()
+        data = [model.get_input().cuda() for _ in range(8)]
+        mtq.quantize(model, copy.deepcopy(mtq.FP8_DEFAULT_CFG), lambda m: [m(b) for b in data])
+        return model
+
+    packed, fake, off = quantized(), quantized(), quantized()
+    assert not hasattr(packed.net[0], "_use_real_quant_gemm")
+    mtq.compress(packed)
+    assert packed.net[0]._use_real_quant_gemm is True
+    assert not hasattr(fake.net[0], "_use_real_quant_gemm")
+    mtq.compress(off, config={"quant_gemm": False})
+    assert not getattr(off.net[0], "_use_real_quant_gemm", False)
+    from b200q import backends
+    backends.enable_real_quant_gemm(fake)
+    assert fake.net[0]._use_real_quant_gemm is True
+    backends.disable_real_quant_gemm(fake)
+    assert fake.net[0]._use_real_quant_gemm is False

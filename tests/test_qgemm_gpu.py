@@ -200,7 +200,7 @@ def _one_layer(cfg_name, k=512, n=384, bias=True, tokens=(4, 48)):
     mtq.quantize(model, copy.deepcopy(getattr(mtq, cfg_name)), lambda m: m(x))
     with torch.no_grad():
         fake = model(x)
-    mtq.compress(model)
+    mtq.compress(model, config={"quant_gemm": False})       # first the dequantise-then-GEMM path
     with torch.no_grad():
         dequant = model(x)
     return mtq, model, x, fake, dequant
