@@ -3,6 +3,8 @@ modelopt/torch/quantization/model_quant.py:53-231,499-523; compress.py:53-222)."
 from __future__ import annotations
 
 import fnmatch
+import inspect
+import warnings
 
 import torch
 from torch import nn
@@ -35,6 +37,12 @@ def calibrate(model: nn.Module, algorithm="max", forward_loop=None) -> nn.Module
     through the model; it may be called more than once."""
     if algorithm is None:
         return model
+    if forward_loop is not None and not inspect.signature(forward_loop).parameters:
+        # the older calling form (reference model_quant.py:79-100): a loop over a captured model
+        warnings.warn("forward_loop should take the model as its argument; a loop without arguments is "
+                      "accepted for backward compatibility.", DeprecationWarning)
+        bare_loop = forward_loop
+        forward_loop = lambda model: bare_loop()  # noqa: E731
     opts = {}
     if isinstance(algorithm, dict):
         opts = {k: v for k, v in algorithm.items() if k != "method"}

@@ -1,0 +1,159 @@
+"""``mtq.quantize`` on the reference's small linear model with the configurations of the reference's own
+test file (tests/unit/torch/quantization/test_quantize_cpu.py): double quantisation through sequential
+quantisers with awq_lite, INT8 with the mse search, an invalid configuration, a forward loop without
+arguments, a custom calibrator class surviving save / restore, per-class configuration, static weights
+with dynamic per-token activations, and block_sizes given as axes.  The model and data live on the GPU;
+convolution rows are absent (only linear layers are on this library's path)."""
+import copy
+
+import pytest
+import torch
+from torch import nn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mtq():
+    import b200q
+
+    return b200q
+
+
+class SimpleLinear(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.net = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 16))
+
+    def forward(self, x):
+        return self.net(x)
+
+    @staticmethod
+    def get_input():
+        return torch.randn(2, 16, device="cuda")
+
+
+WINT4INT8_CFG = {
+    "quant_cfg": {"*weight_quantizer": [{"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+                                        {"num_bits": 8, "axis": 0, "enable": True}],
+                  "*input_quantizer": {"num_bits": 8, "axis": None, "enable": True}},
+    "algorithm": "awq_lite",
+}
+INT8_MSE_CFG = {"quant_cfg": {"*weight_quantizer": {"num_bits": 8, "axis": 0},
+                              "*input_quantizer": {"num_bits": 8, "axis": None}}, "algorithm": "mse"}
+STATIC_WEIGHT_DYNAMIC_ACTIVATION_CFG = {
+    "quant_cfg": {"*weight_quantizer": {"num_bits": 8, "axis": 0},
+                  "*input_quantizer": {"num_bits": 8, "axis": (0, 1), "type": "dynamic"},
+                  "default": {"enable": False}},
+    "algorithm": "max",
+}
+
+
+def _model(seed=0):
+    torch.manual_seed(seed)
+    return SimpleLinear().cuda()
+
+
+@pytest.mark.parametrize("cfg", [WINT4INT8_CFG, INT8_MSE_CFG], ids=["wint4int8_awq_lite", "int8_mse"])
+def test_quantize_runs(mtq, cfg):
+    model = _model()
+    data = [model.get_input() for _ in range(2)]
+    with torch.no_grad():
+        plain = model(data[0])
+    mtq.quantize(model, copy.deepcopy(cfg), lambda m: [m(b) for b in data])
+    layers = [m for m in model.net if isinstance(m, nn.Linear)]
+    assert all(mtq.nn.quant_linear.is_quantized_linear(m) for m in layers)
+    if cfg is WINT4INT8_CFG:
+        assert all(isinstance(m.weight_quantizer, mtq.nn.SequentialQuantizer) for m in layers)
+        assert all(q.amax is not None for m in layers for q in m.weight_quantizer)
+    with torch.no_grad():
+        out = model(data[0])
+    assert torch.isfinite(out).all() and (out - plain).abs().mean() <= 0.5 * plain.abs().mean() + 0.05
+
+
+def test_an_invalid_configuration_is_refused(mtq):
+    cfg = {"quant_cfg": {"*": {"num_bits": 4, "axis": 0, "block_sizes": {-1: 128}}}, "algorithm": "max"}
+    with pytest.raises(ValueError, match="axis must be None when block_sizes is not None."):
+        mtq.quantize(_model(), cfg)
+
+
+def test_a_forward_loop_without_arguments(mtq):
+    model = _model()
+    data = [model.get_input() for _ in range(2)]
+
+    def forward_loop():
+        for batch in data:
+            model(batch)
+
+    mtq.quantize(model, copy.deepcopy(mtq.INT8_DEFAULT_CFG), forward_loop=forward_loop)
+    assert all(m.input_quantizer.amax is not None for m in model.net if isinstance(m, nn.Linear))
+
+
+def test_a_custom_calibrator_survives_save_and_restore(mtq):
+    class DoublingMaxCalibrator(mtq.calib.MaxCalibrator):
+        def compute_amax(self, *args, **kwargs):
+            return 2 * super().compute_amax(*args, **kwargs)
+
+    cfg = {"quant_cfg": {"*": {"num_bits": 4, "axis": None, "enable": True,
+                               "calibrator": (DoublingMaxCalibrator, (4, None, False))}}, "algorithm": "max"}
+    ref = _model()
+    x = ref.get_input()
+    mtq.quantize(ref, cfg, lambda m: m(x))
+    assert torch.equal(ref.net[0].input_quantizer.amax, 2 * x.abs().amax())
+    fresh = _model(seed=1)
+    mtq.restore_from_modelopt_state(fresh, mtq.modelopt_state(ref))
+    fresh.load_state_dict(ref.state_dict())
+    with torch.no_grad():
+        assert torch.allclose(ref(x), fresh(x))
+    for name, m in fresh.named_modules():
+        if name.endswith("quantizer"):
+            assert type(m._calibrator) is DoublingMaxCalibrator
+
+
+def test_per_class_configuration(mtq):
+    cfg = {"quant_cfg": {"nn.Linear": {"*": {"num_bits": 4, "axis": -1, "enable": True}},
+                         "nn.BatchNorm2d": {"*": {"enable": False}},
+                         "*output_quantizer": {"num_bits": 8, "enable": True}}, "algorithm": "max"}
+    model = _model()
+    x = model.get_input()
+    mtq.quantize(model, cfg, lambda m: m(x))
+    for name, m in model.named_modules():
+        if isinstance(m, nn.Linear):
+            for q in (m.weight_quantizer, m.input_quantizer):
+                assert q.num_bits == 4 and q.axis == -1 and q.is_enabled
+        if name.endswith("output_quantizer"):
+            assert m.is_enabled and m.num_bits == 8
+
+
+def test_static_weights_with_dynamic_activations(mtq):
+    model = _model()
+    x = model.get_input()
+    mtq.quantize(model, copy.deepcopy(STATIC_WEIGHT_DYNAMIC_ACTIVATION_CFG), lambda m: m(m.get_input()))
+    for name, m in model.named_modules():
+        if name.endswith("weight_quantizer"):
+            assert m.amax is not None
+        if name.endswith("input_quantizer"):
+            assert m.amax is None
+    assert torch.isfinite(model(x)).all()
+    model = _model()
+    mtq.quantize(model, copy.deepcopy(STATIC_WEIGHT_DYNAMIC_ACTIVATION_CFG))           # no forward loop at all
+    assert all(m.amax is not None for n, m in model.named_modules() if n.endswith("weight_quantizer"))
+
+
+def test_block_sizes_given_as_axes_equal_the_axis_form(mtq):
+    ref_cfg = {"quant_cfg": {"*weight_quantizer": {"num_bits": 8, "axis": 0},
+                             "*input_quantizer": {"num_bits": 8, "axis": None, "type": "dynamic"},
+                             "default": {"enable": False}}, "algorithm": "max"}
+    cfg = {"quant_cfg": {"*weight_quantizer": {"num_bits": 8, "block_sizes": {1: None}},
+                         "*input_quantizer": {"num_bits": 8, "block_sizes": {0: None, 1: None}, "type": "dynamic"},
+                         "default": {"enable": False}}, "algorithm": "max"}
+    model_ref = _model()
+    model = copy.deepcopy(model_ref)
+    x = model_ref.get_input()
+    mtq.quantize(model_ref, ref_cfg, lambda m: m(x))
+    mtq.quantize(model, cfg, lambda m: m(x))
+    with torch.no_grad():
+        assert torch.allclose(model_ref(x), model(x))
+    for a, b in zip(model_ref.net, model.net):
+        if hasattr(a, "weight_quantizer"):
+            assert torch.equal(a.weight_quantizer.amax.reshape(-1), b.weight_quantizer.amax.reshape(-1))
