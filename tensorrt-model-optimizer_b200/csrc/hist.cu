@@ -250,6 +250,23 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   };
   uint4 cur[4], nxt[4];
   load4(i, cur);
+  // value -> bin with the reference arithmetic: bin = int(RN(RN(a * nbins) / range)), the right edge in
+  // the last bin; kSkip for a value beyond the capacity (cannot happen by construction of hi1: a guard).
+  // The bins of the first two values that this thread folds after the stream are computed here, while the
+  // first loads are in flight, so that the divisions are off the tail that nothing overlaps.
+  constexpr uint32_t kSkip = 0xffffffffu;
+  const float fbins = static_cast<float>(nbins);
+  const uint32_t last = static_cast<uint32_t>(nbins - 1), cap_last = static_cast<uint32_t>(open.capacity - 1);
+  const int in_range = static_cast<int>(lay.hi1 - lay.lo);   // index hi1 - lo holds what is out of range
+  auto bin_of = [&](int v) -> uint32_t {
+    const float a = value_of_bits16<T>(lay.lo + v);
+    if (!(a <= open.cap_range)) return kSkip;
+    const float quot = __fdiv_rn(a * fbins, range_max);
+    const uint32_t b = quot < 8388608.f ? (__float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu) : cap_last;
+    return min(b, a <= range_max ? last : cap_last);
+  };
+  const uint32_t bin0 = bin_of(min(static_cast<int>(threadIdx.x), in_range - 1));
+  const uint32_t bin1 = bin_of(min(static_cast<int>(threadIdx.x + blockDim.x), in_range - 1));
   __syncthreads();
   const uint32_t rmask = (1u << lay.rshift) - 1u;
   const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(sh));
@@ -279,15 +296,10 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
   }
   __syncthreads();
 
-  // values -> bins with the reference arithmetic: bin = int(RN(RN(a * nbins) / range)), the right
-  // edge in the last bin.  Thread v sums the replicas of value v.
+  // values -> bins.  Thread v sums the replicas of value v.
   uint32_t* bins = sh + vwords;
-  const float fbins = static_cast<float>(nbins);
-  const uint32_t last = static_cast<uint32_t>(nbins - 1), cap_last = static_cast<uint32_t>(open.capacity - 1);
-  const int in_range = static_cast<int>(lay.hi1 - lay.lo);   // index hi1 - lo holds what is out of range
-  for (int v = threadIdx.x; v < in_range; v += blockDim.x) {
+  auto replica_sum = [&](int v) -> uint32_t {
     const uint32_t* row = sh + (v << lay.rshift);
-    uint32_t c = 0;
     // This phase reads every replica of every value once (about 100 KB): it runs at the speed of shared
     // memory, so the reads are laid out free of bank conflicts.  A row of 2^rshift words starts at bank
     // (lane << rshift) % 32; lanes whose rows start in the same bank begin at different replicas.
@@ -295,20 +307,27 @@ hist16_collect_kernel(const T* __restrict__ x, int64_t n, int nbins, float range
       const uint4* row4 = reinterpret_cast<const uint4*>(row);
       const uint32_t rot = (threadIdx.x >> 1) & 3u;
       const uint4 p0 = row4[rot], p1 = row4[(rot + 1) & 3u], p2 = row4[(rot + 2) & 3u], p3 = row4[(rot + 3) & 3u];
-      c = (p0.x + p0.y + p0.z + p0.w) + (p1.x + p1.y + p1.z + p1.w) + (p2.x + p2.y + p2.z + p2.w) +
-          (p3.x + p3.y + p3.z + p3.w);
-    } else {
-      const uint32_t rot = (threadIdx.x & 31u) >> (5 - lay.rshift);
-      for (uint32_t k = 0; k <= rmask; ++k) c += row[(k + rot) & rmask];
+      return (p0.x + p0.y + p0.z + p0.w) + (p1.x + p1.y + p1.z + p1.w) + (p2.x + p2.y + p2.z + p2.w) +
+             (p3.x + p3.y + p3.z + p3.w);
     }
-    if (c == 0) continue;
-    const float a = value_of_bits16<T>(lay.lo + v);
-    if (!(a <= open.cap_range)) continue;   // cannot happen by construction of hi1; kept as a guard
-    const float quot = __fdiv_rn(a * fbins, range_max);
-    uint32_t b = quot < 8388608.f ? (__float_as_uint(__fadd_rz(quot, 8388608.f)) & 0x7fffffu) : cap_last;
-    b = min(b, a <= range_max ? last : cap_last);
+    uint32_t c = 0;
+    const uint32_t rot = (threadIdx.x & 31u) >> (5 - lay.rshift);
+    for (uint32_t k = 0; k <= rmask; ++k) c += row[(k + rot) & rmask];
+    return c;
+  };
+  auto add_to_bin = [&](uint32_t b, uint32_t c) {
+    if (c == 0 || b == kSkip) return;
     if (b < static_cast<uint32_t>(lay.smem_bins)) atomicAdd(bins + b, c);
     else hist_add(dests, b, static_cast<unsigned long long>(c));
+  };
+  int v = threadIdx.x;
+  if (v < in_range) add_to_bin(bin0, replica_sum(v));
+  v += blockDim.x;
+  if (v < in_range) add_to_bin(bin1, replica_sum(v));
+  v += blockDim.x;
+  for (; v < in_range; v += blockDim.x) {
+    const uint32_t c = replica_sum(v);
+    if (c) add_to_bin(bin_of(v), c);
   }
   if (threadIdx.x <= rmask) {   // the index that holds what is out of range
     const uint32_t c = sh[(in_range << lay.rshift) + threadIdx.x];
