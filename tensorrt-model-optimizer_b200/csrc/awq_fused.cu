@@ -74,6 +74,7 @@ constexpr int kFTransformCount = (kFThreads / 128 - 2) * 3;
 constexpr int kFOctets = 16;                             // row octets (warp-sized tasks) per W unit
 constexpr int kFEpilogueWarps = 8;       // two per TMEM lane quarter (warps 4-7 and 16-19), alternate column chunks
 constexpr int kFMaxStages = 10;
+constexpr int kFRefPieces = kFPairN / kFK;   // the reference tile of an item travels as four 64-column pieces
 
 template <int MT> struct FusedCfg {
   // what the transformed-weight ring leaves of the 227 KB goes to the activation ring
@@ -97,6 +98,8 @@ struct FusedSmem {
   uint64_t b_empty[kFWUnits];
   uint64_t acc_full;               // all MMAs of an item complete
   uint64_t acc_empty;              // accumulator read out in both CTAs (even CTA's copy)
+  uint64_t r_full[kFRefPieces];    // a piece of the item's reference tile landed (each CTA its own)
+  uint32_t r_readers[kFRefPieces]; // epilogue warps that are done with the piece
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -151,6 +154,7 @@ __device__ __forceinline__ FusedItem fused_item(int item, int slabs_m, int slabs
 template <int MT>
 __global__ void __launch_bounds__(kFThreads, 1)
 awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                        const __grid_constant__ CUtensorMap map_r,
                         const __nv_bfloat16* __restrict__ s_all, const __nv_bfloat16* __restrict__ ref,
                         double* __restrict__ loss, float* __restrict__ c_out, int n_alpha, int M, int N, int K,
                         IntQ q, float one, uint32_t* __restrict__ status) {
@@ -185,6 +189,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
     mbar_init(&sm->acc_full, 1);
     mbar_init(&sm->acc_empty, 2 * kFEpilogueWarps);
+    for (int j = 0; j < kFRefPieces; ++j) { mbar_init(&sm->r_full[j], 1); sm->r_readers[j] = 0; }
     sm->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -219,6 +224,23 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           kr -= kr >= k_slices ? k_slices : 0;
 #pragma unroll
           for (int t = 0; t < MT; ++t) tma_load_2d_pair(dst + t * kFTileBytes, &map_a, full_leader, kr * kFK, row0 + t * 256);
+        }
+        // The item's reference tile (this CTA's rows, 256 columns) follows its last A tile through the same
+        // ring, one 64-column piece per stage: the epilogue then reads it from shared memory instead of
+        // waiting for L2 sixteen times while the tensor cores stand still.  These stages are not the MMA
+        // issuer's: it skips them, and the epilogue hands them back.  The even CTA's "A landed" barrier
+        // still gets its arrival (no bytes), so that its phases keep counting the uses of the stage.
+        const int ref_row0 = w.slab_m * slab_rows + static_cast<int>(rank) * 128;
+        for (int j = 0; j < kFRefPieces && ok; ++j, ++it) {
+          const int s = it % SA;
+          ok = mbar_wait_bounded(&sm->a_empty[s], ((it / SA) & 1) ^ 1, &sm->abort, status, kFErrAProducer);
+          if (!ok) break;
+          if (leader) mbar_expect_tx(&sm->a_full[s], 0);
+          mbar_expect_tx(&sm->r_full[j], Cfg::kAStageBytes);
+          uint8_t* dst = ring_a + s * Cfg::kAStageBytes;
+#pragma unroll
+          for (int t = 0; t < MT; ++t)
+            tma_load_2d(dst + t * kFTileBytes, &map_r, &sm->r_full[j], w.slab_n * kFPairN + j * kFK, ref_row0 + t * 256);
         }
       }
     }
@@ -291,6 +313,7 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
         if (!ok) break;
         commit_both(&sm->acc_full);   // fires when every MMA issued above has completed
+        it += kFRefPieces;            // the stages that carry the item's reference tile to the epilogue
       }
     }
   } else if ((warp & 3) != 0 && (warp >> 2) != 1 && (warp >> 2) != 4) {
@@ -425,52 +448,60 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       if (!ok) break;                     // warp-uniform: the TMEM loads below are warp-wide
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sq = 0.f;
-      // 16-column chunks of this lane's rows; the reference values of a chunk are requested one chunk
-      // ahead of the accumulator read they are compared with
+      // 16-column chunks of this lane's rows, piece by piece of the reference tile as the pieces land in
+      // the A ring (rows of 128 bytes, 16-byte unit u of row r at position u ^ (r & 7)); the quarter's two
+      // warps take alternate chunks
       const int chunks_n = min(kFPairN, N - w.slab_n * kFPairN) / 16;          // warp-uniform (N % 32 == 0)
-      const int total_chunks = MT * chunks_n;
-      auto row_of = [&](int t) { return w.slab_m * slab_rows + t * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane; };
-      auto load_ref = [&](int idx, uint4* r4) {
-        const int t = idx / chunks_n, cc = idx - t * chunks_n;
-        const int row = row_of(t);
-        if (row < M && !(B200Q_FUSED_ABLATE & 2)) {
-          const uint4* rp = reinterpret_cast<const uint4*>(ref + static_cast<int64_t>(row) * N + w.slab_n * kFPairN + cc * 16);
-          r4[0] = __ldg(rp);
-          r4[1] = __ldg(rp + 1);
-        }
-      };
-      uint4 cur[2], nxt[2];
-      if (second < total_chunks) load_ref(second, cur);
-#pragma unroll 1
-      for (int idx = second; idx < total_chunks; idx += 2) {
-        const int t = idx / chunks_n, cc = idx - t * chunks_n;
-        if (idx + 2 < total_chunks) load_ref(idx + 2, nxt);
-        uint32_t acc[16];
-        tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + t * kFPairN + cc * 16, acc);
-        const int row = row_of(t);
-        if (row < M && !(B200Q_FUSED_ABLATE & 2)) {
-          // bf16(bf16(acc) - ref) two elements at a time: the packed bf16 subtraction rounds the exact
-          // difference once, which is what rounding the fp32 difference of two bf16 values gives
-          const uint32_t rr[8] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w};
+      const int r_in = quarter * 32 + lane;                                     // this lane's row within a 128-row box
+      const uint32_t first_use = done * static_cast<uint32_t>(k_slices + kFRefPieces) + static_cast<uint32_t>(k_slices);
+      for (int j = 0; j < kFRefPieces && ok; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&sm->r_full[j], done & 1, &sm->abort, status, kFErrEpilogue));
+        if (!ok) break;
+        const int s = static_cast<int>((first_use + j) % SA);
+        const uint8_t* piece = ring_a + s * Cfg::kAStageBytes + r_in * 128;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t o2 = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
-            const __nv_bfloat162 d2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&o2),
-                                              *reinterpret_cast<const __nv_bfloat162*>(&rr[j]));
-            const uint32_t db = *reinterpret_cast<const uint32_t*>(&d2);
-            const float d_lo = __uint_as_float(db << 16), d_hi = __uint_as_float(db & 0xffff0000u);
-            sq = fmaf(d_lo, d_lo, sq);
-            sq = fmaf(d_hi, d_hi, sq);
-          }
-          if (c_out) {
-            float* cp = c_out + (static_cast<int64_t>(w.alpha) * M + row) * N + w.slab_n * kFPairN + cc * 16;
+        for (int t = 0; t < MT; ++t) {
+          const int row = w.slab_m * slab_rows + t * 256 + static_cast<int>(rank) * 128 + r_in;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) cp[j] = __uint_as_float(acc[j]);
+          for (int c = 0; c < 2; ++c) {
+            const int cp = 2 * c + second;                  // chunk within the piece: 16-byte units 2 cp, 2 cp + 1
+            const int cc = j * (kFK / 16) + cp;
+            if (cc >= chunks_n) continue;                   // warp-uniform
+            uint32_t acc[16];
+            tmem_ld16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + t * kFPairN + cc * 16, acc);
+            if (row < M && !(B200Q_FUSED_ABLATE & 2)) {
+              const uint8_t* src = piece + t * kFTileBytes;
+              const uint4 r0 = *reinterpret_cast<const uint4*>(src + (((2 * cp) ^ (r_in & 7)) << 4));
+              const uint4 r1 = *reinterpret_cast<const uint4*>(src + (((2 * cp + 1) ^ (r_in & 7)) << 4));
+              // bf16(bf16(acc) - ref) two elements at a time: the packed bf16 subtraction rounds the exact
+              // difference once, which is what rounding the fp32 difference of two bf16 values gives
+              const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const uint32_t o2 = Elem<__nv_bfloat16>::pack2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+                const __nv_bfloat162 d2 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&o2),
+                                                  *reinterpret_cast<const __nv_bfloat162*>(&rr[i]));
+                const uint32_t db = *reinterpret_cast<const uint32_t*>(&d2);
+                const float d_lo = __uint_as_float(db << 16), d_hi = __uint_as_float(db & 0xffff0000u);
+                sq = fmaf(d_lo, d_lo, sq);
+                sq = fmaf(d_hi, d_hi, sq);
+              }
+              if (c_out) {
+                float* cp_out = c_out + (static_cast<int64_t>(w.alpha) * M + row) * N + w.slab_n * kFPairN + cc * 16;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) cp_out[i] = __uint_as_float(acc[i]);
+              }
+            }
           }
         }
-        cur[0] = nxt[0];
-        cur[1] = nxt[1];
+        // the last of this CTA's eight epilogue warps to finish the piece gives the stage back to the A producer
+        __syncwarp();
+        if (lane == 0 && atomicAdd(&sm->r_readers[j], 1u) == kFEpilogueWarps - 1) {
+          sm->r_readers[j] = 0;
+          mbar_arrive_remote(map_to_cta(&sm->a_empty[s], rank));
+        }
       }
+      if (!ok) break;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(acc_empty_leader);   // the accumulator may be overwritten
@@ -504,7 +535,7 @@ static bool fused_make_map(CUtensorMap* map, const void* base, int64_t rows, int
 }
 
 template <int MT>
-static int fused_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const __nv_bfloat16* s_all,
+static int fused_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_r, const __nv_bfloat16* s_all,
                         const __nv_bfloat16* ref, double* loss, float* c_out, int n_alpha, int m, int n, int k,
                         IntQ q, uint32_t* status, int64_t items, cudaStream_t st) {
   using Cfg = FusedCfg<MT>;
@@ -538,7 +569,7 @@ static int fused_launch(const CUtensorMap& map_a, const CUtensorMap& map_w, cons
   }
   const int64_t pairs = items < pairs_cached[dev] ? items : pairs_cached[dev];
   cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-  if (cudaLaunchKernelEx(&cfg, kern, map_a, map_w, s_all, ref, loss, c_out, n_alpha, m, n, k, q, 1.0f, status) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, map_a, map_w, map_r, s_all, ref, loss, c_out, n_alpha, m, n, k, q, 1.0f, status) != cudaSuccess) {
     cudaGetLastError();
     return B200Q_ERR_CUDA;
   }
@@ -557,16 +588,17 @@ static int fused_entry(const void* a_all, const void* w, int64_t w_rows, const v
   const int64_t slabs_m = (m + 256 * mt - 1) / (256 * mt), slabs_n = (n + kFPairN - 1) / kFPairN;
   const int64_t items = n_alpha * slabs_m * slabs_n;
   if (items > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
-  CUtensorMap map_a, map_w;
-  if (!fused_make_map(&map_a, a_all, static_cast<int64_t>(n_alpha) * m, k) || !fused_make_map(&map_w, w, w_rows, k))
+  CUtensorMap map_a, map_w, map_r;
+  if (!fused_make_map(&map_a, a_all, static_cast<int64_t>(n_alpha) * m, k) || !fused_make_map(&map_w, w, w_rows, k) ||
+      !fused_make_map(&map_r, ref, m, n))
     return B200Q_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(s_all);
   const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(ref);
   if (mt == 2)
-    return fused_launch<2>(map_a, map_w, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
+    return fused_launch<2>(map_a, map_w, map_r, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
                            static_cast<int>(k), q, status_io, items, st);
-  return fused_launch<1>(map_a, map_w, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
+  return fused_launch<1>(map_a, map_w, map_r, sp, rp, loss_io, c_out, n_alpha, static_cast<int>(m), static_cast<int>(n),
                          static_cast<int>(k), q, status_io, items, st);
 }
 
