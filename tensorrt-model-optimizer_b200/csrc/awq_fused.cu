@@ -16,10 +16,10 @@
 //
 // Warps of a CTA (32; a warp's scheduler is its index modulo 4):
 //   0      MMA issuer (even CTA only) and TMEM allocation           } scheduler 0 carries no transform warp, so
-//   8      A producer: TMA 128 x 64 tiles into a 4-deep ring,       } these latency-critical threads do not
+//   8      A producer: TMA 128 x 64 tiles into a 3-deep ring,       } these latency-critical threads do not
 //          completion counted on the EVEN CTA's barrier             } queue for issue slots behind arithmetic
 //   12     W producer: TMA raw 128 x 128 weight units (two swizzled }
-//          128 x 64 boxes) and the unit's 128 scale factors into a 3-deep ring
+//          128 x 64 boxes) and the unit's 128 scale factors into a 4-deep ring
 //   4-7, 16-19   epilogue (two warps per TMEM lane quarter): tcgen05.ld the accumulator, squared error
 //          against R, one atomic per warp and item
 //   1-3, 9-11, 13-15, 21-23, 25-27, 29-31   transform (eighteen warps), in shared memory, in place.  A W unit is sixteen
@@ -31,8 +31,9 @@
 // The MMA thread waits for "A tile landed in both CTAs" and "W unit transformed in both CTAs", issues
 // 2 x 4 MMAs per 64-wide K slice, and releases ring slots to both CTAs with tcgen05.commit.  The A
 // producer and the transformers run ahead into the next item while the epilogue drains the
-// accumulator.  Every pair starts its K loop at a different offset, so that the pairs, which all
-// read the same activations, do not ask L2 for the same lines at the same moment.
+// accumulator.  Where few activations are being read at a time, every pair starts its K loop at a different
+// offset, so that the pairs, which all read the same activations, do not ask L2 for the same lines at the
+// same moment.
 //
 // Every wait is bounded: when one runs out, an error bit is set in the caller's status word, the CTA
 // stops waiting anywhere else, and the kernel ends through its normal exit (TMEM released).
@@ -56,9 +57,12 @@ constexpr uint32_t kFTileBytes = 128 * kFK * 2;          // 128 rows x 64 bf16 =
 constexpr uint32_t kFUnitBytes = 2 * kFTileBytes;        // a W unit: 128 rows x 128 K = two boxes
 constexpr int kFPairN = 256;                             // columns of a pair's tile (128 weight rows per CTA)
 #ifndef B200Q_FUSED_WUNITS
-#define B200Q_FUSED_WUNITS 3
+#define B200Q_FUSED_WUNITS 4
 #endif
-constexpr int kFWUnits = B200Q_FUSED_WUNITS;   // W unit slots: landing, being transformed, being read by the MMAs
+// W unit slots (landing, being transformed, waiting, being read by the MMAs).  Measured on the 21-candidate
+// search of 512 x 14336 x 4096, with the rest of the 227 KB as activation stages: 2 units + 5 stages 1.64 ms,
+// 3 + 4 1.09, 4 + 3 1.06, 5 + 2 1.15.
+constexpr int kFWUnits = B200Q_FUSED_WUNITS;
 constexpr uint32_t kFScaleBytes = 128 * 2;     // one unit's share of a candidate's scale vector
 #ifndef B200Q_FUSED_THREADS
 #define B200Q_FUSED_THREADS 1024
@@ -177,8 +181,13 @@ awq_fused_search_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   const int num_items = n_alpha * slabs_m * slabs_n;
   const int k_slices = K / kFK;                      // K is a multiple of 128: an even count
   const int k_units = k_slices / 2;
-  // this pair's K loop starts at unit `rot` and wraps around
-  const int rot = B200Q_FUSED_ROTATE ? static_cast<int>((static_cast<int64_t>(pair) * k_units) / num_pairs) % k_units : 0;
+  // this pair's K loop starts at unit `rot` and wraps around when the activations that the pairs working at the same time read are few (the pairs of one candidate all
+  // read the same rows: starting apart keeps them off the same L2 lines at the same moment).  When they are
+  // many (long K, few column slabs per candidate) starting together is what keeps a tile in L2 until every
+  // pair of its candidate has read it: 512 x 4096 x 14336, 21 candidates, 1.11 ms rotated, 1.03 ms not.
+  const bool rotate = B200Q_FUSED_ROTATE && static_cast<int64_t>(num_pairs) * M * K * 2 <=
+                                                static_cast<int64_t>(slabs_m) * slabs_n * (16ll << 20);
+  const int rot = rotate ? static_cast<int>((static_cast<int64_t>(pair) * k_units) / num_pairs) % k_units : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < SA; ++s) { mbar_init(&sm->a_full[s], 1); mbar_init(&sm->a_empty[s], 1); }
