@@ -42,8 +42,16 @@ def load_calib_amax_all(items):
     device, and the error names every offending quantiser."""
     from .calib import HistogramCalibrator, MaxCalibrator
 
-    loaded = {}
+    loaded = {}       # device -> [(name, quantiser)]
+    checks = {}       # device -> fp32 tensors holding every value loaded on it
     batched = {}      # (device, percentile) -> histogram calibrators read out by one launch
+    running_max = {}  # (device, dtype) -> max calibrators whose running maxima are converted together
+
+    def took(name, q, values_fp32=None):
+        dev = q._amax.device
+        loaded.setdefault(dev, []).append((name, q))
+        checks.setdefault(dev, []).append(q._amax.detach().reshape(-1).float() if values_fp32 is None else values_fp32)
+
     for name, q, args, kwargs in items:
         cal = q._calibrator
         if (isinstance(cal, HistogramCalibrator) and tuple(args) == ("percentile",) and set(kwargs) <= {"percentile"}
@@ -55,22 +63,39 @@ def load_calib_amax_all(items):
             cal._resolve()
             batched.setdefault((cal._calib_hist.device, pct), []).append((name, q))
             continue
+        if type(cal) is MaxCalibrator and not args and not kwargs and cal._acc is not None and cal._acc.is_cuda:
+            running_max.setdefault((cal._acc.device, cal._dtype), []).append((name, q))
+            continue
         extra = {"check": False} if isinstance(cal, MaxCalibrator) else {}
         value = cal.compute_amax(*args, **kwargs, **extra)
         if value is None:
             continue
         q._store_calib_amax(value)
-        loaded.setdefault(q._amax.device, []).append((name, q))
+        took(name, q)
+    # max calibrators: one concatenation and one conversion to the collected dtype per device and dtype; the
+    # quantisers' buffers are slices of the result (two launches instead of two per quantiser)
+    for (dev, dtype), group in running_max.items():
+        accs = [q._calibrator._acc for _, q in group]
+        flat = torch.cat(accs) if len(accs) > 1 else accs[0].clone()
+        conv = flat.to(dtype)
+        off = 0
+        for (name, q), acc in zip(group, accs):
+            n = acc.numel()
+            q._store_calib_amax(conv[off:off + n].reshape(q._calibrator._shape), owned=True)
+            off += n
+            loaded.setdefault(dev, []).append((name, q))
+        checks.setdefault(dev, []).append(flat)
     for (dev, pct), group in batched.items():
         values = ops.hist_percentile_batch(
             [(q._calibrator._calib_hist, q._calibrator._num_bins, q._calibrator._calib_bin_edges) for _, q in group], pct)
         for i, (name, q) in enumerate(group):
-            q._store_calib_amax(values[i])
-            loaded.setdefault(q._amax.device, []).append((name, q))
-    for dev, group in loaded.items():
-        flat = torch.cat([q._amax.detach().reshape(-1).float() for _, q in group])
+            q._store_calib_amax(values[i], owned=True)
+            loaded.setdefault(dev, []).append((name, q))
+        checks.setdefault(dev, []).append(values.reshape(-1).float())
+    for dev, parts in checks.items():
+        flat = torch.cat(parts) if len(parts) > 1 else parts[0]
         if bool((~torch.isfinite(flat) | (flat < 0)).any()):
-            bad = [n for n, q in group if not q.validate_attr(attr_name="_amax")]
+            bad = [n for n, q in loaded[dev] if not q.validate_attr(attr_name="_amax")]
             raise ValueError(f"calibrated amax of {bad} contains nan, inf or negative values")
     return sum(len(g) for g in loaded.values())
 

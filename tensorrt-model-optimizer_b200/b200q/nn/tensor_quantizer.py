@@ -295,11 +295,13 @@ class TensorQuantizer(nn.Module):
         self.validate_attr(attr_value=calib_amax, attr_name="_amax", raise_error=True)
         self._store_calib_amax(calib_amax)
 
-    def _store_calib_amax(self, calib_amax):
+    def _store_calib_amax(self, calib_amax, owned=False):
+        """``owned``: the tensor is a fresh result that nothing else writes (a slice of a batched read-out):
+        it becomes the buffer itself instead of being copied."""
         if not hasattr(self, "_amax"):
-            self.register_buffer("_amax", calib_amax.clone().detach())
+            self.register_buffer("_amax", calib_amax.detach() if owned else calib_amax.clone().detach())
         else:
-            self._amax.data.copy_(calib_amax.clone().detach().to(self._amax.device))
+            self._amax.data.copy_(calib_amax.detach().to(self._amax.device))
 
     def validate_attr(self, attr_value=None, attr_name="_amax", raise_error=False, warn_error=False, name=""):
         attr_value = attr_value if attr_value is not None else getattr(self, attr_name, None)
