@@ -21,7 +21,9 @@
 //   12     W producer: TMA raw 128 x 128 weight units (two swizzled }
 //          128 x 64 boxes) and the unit's 128 scale factors into a 4-deep ring
 //   4-7, 16-19   epilogue (two warps per TMEM lane quarter): tcgen05.ld the accumulator, squared error
-//          against R, one atomic per warp and item
+//          against R, one atomic per warp and item.  R's tile for the item (this CTA's rows, 256 columns)
+//          is sent by the A producer through the A ring after the item's last A tile, as four 64-column
+//          pieces; the MMA issuer skips those stages and the epilogue hands them back
 //   1-3, 9-11, 13-15, 21-23, 25-27, 29-31   transform (eighteen warps), in shared memory, in place.  A W unit is sixteen
 //          warp-sized tasks of eight rows, taken round-robin across unit boundaries; a lane owns 32
 //          consecutive elements of one weight row (four lanes = one 128-block): bf16(W * s), the block
