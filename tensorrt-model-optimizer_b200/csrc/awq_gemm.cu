@@ -44,6 +44,13 @@ template <int BN, int MT> struct GemmCfg {
   static constexpr int kColParts = (kThreads / 32 - 2) / 4;
   // instruction descriptor: D fp32, A/B bf16, both K-major, N = BN, M = 128
   static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((BN >> 3) << 17) | ((kGM >> 4) << 24);
+  // The tile of the reference output follows the operands through the ring: 64-column
+  // pieces of MT boxes of 128 rows, as many per stage as fit, in the uses right after the last K block.
+  static constexpr uint32_t kRefPieceBytes = MT * kTileBytesA;
+  static constexpr int kRefPieces = BN / kGK;
+  static constexpr int kRefPiecesPerStage = kStageBytes / kRefPieceBytes;
+  static constexpr int kRefStages = (kRefPieces + kRefPiecesPerStage - 1) / kRefPiecesPerStage;
+  static_assert(kRefStages <= kStages, "the reference tile must fit in the ring");
 };
 
 enum : uint32_t { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 4 };
@@ -107,7 +114,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, GemmSm
 template <int BN, int MT>
 __global__ void __launch_bounds__(GemmCfg<BN, MT>::kThreads, GemmCfg<BN, MT>::kCtasPerSm)
 awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const __nv_bfloat16* __restrict__ ref, int64_t N, int total_k_blocks, int kb_per_split,
+                      const __grid_constant__ CUtensorMap map_r,
+                      int64_t N, int total_k_blocks, int kb_per_split,
                       float* __restrict__ partial, uint32_t* __restrict__ counters, double* __restrict__ sum_io,
                       float* __restrict__ c_out, uint32_t* __restrict__ status) {
   using Cfg = GemmCfg<BN, MT>;
@@ -155,6 +163,22 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * kTileBytesA, &map_a, &sm->full[s], (kb0 + kb) * kGK, m0 + mt * kGM);
         tma_load_2d(a + MT * kTileBytesA, &map_b, &sm->full[s], (kb0 + kb) * kGK, n0);
       }
+      if (!*reinterpret_cast<volatile uint32_t*>(&sm->abort)) {
+        // the reference tile, into the stages the last MMAs free: the epilogue then reads it from shared
+        // memory instead of waiting for one L2 round trip per 32-column chunk with the tensor cores idle
+        for (int j = 0; j < Cfg::kRefStages; ++j) {
+          const int use = num_k_blocks + j, s = use % kStages;
+          if (!mbar_wait(&sm->empty[s], ((use / kStages) & 1) ^ 1, sm, status, kErrProducerWait)) break;
+          const int first = j * Cfg::kRefPiecesPerStage;
+          const int count = min(Cfg::kRefPiecesPerStage, Cfg::kRefPieces - first);
+          mbar_expect_tx(&sm->full[s], count * Cfg::kRefPieceBytes);
+          uint8_t* dst = ring + s * kStageBytes;
+          for (int p = 0; p < count; ++p)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+              tma_load_2d(dst + (p * MT + mt) * kTileBytesA, &map_r, &sm->full[s], n0 + (first + p) * kGK, m0 + mt * kGM);
+        }
+      }
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -190,7 +214,10 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     float sq = 0.f;
     bool finish = ok;                       // this CTA runs the loss epilogue
     const int64_t m_total = static_cast<int64_t>(gridDim.x) * kGM * MT;
-    uint8_t* stage = ring + (warp - 2) * 32 * kSplitPitch;   // the ring is idle once the accumulator is complete
+    // split-K scratch: the ring is idle once the accumulator is complete, except for the stage(s) that hold
+    // the reference tile; the scratch sits in the stage after them
+    // (split launches run 128 x 128 tiles: one of three stages holds the reference tile)
+    uint8_t* stage = ring + ((num_k_blocks + Cfg::kRefStages) % kStages) * kStageBytes + (warp - 2) * 32 * kSplitPitch;
     if (splits > 1) {
       constexpr int kEpiThreads = Cfg::kThreads - 64;
       if (ok) {
@@ -222,7 +249,6 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       for (int mt = 0; mt < MT; ++mt) {
         const int64_t row0 = m0 + mt * kGM + quarter * 32;
         const int64_t row = row0 + lane;
-        const __nv_bfloat16* rrow = ref + row * N + n0;
 #pragma unroll 1
         for (int c = col_part * kChunksPerPart; c < (col_part + 1) * kChunksPerPart; ++c) {
           uint32_t acc[32];
@@ -230,10 +256,18 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             tmem_ld32(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + mt * BN + c * 32, acc);
           else
             split_load_piece(acc, stage, lane, partial + row0 * N + n0 + c * 32, N, m_total * N, splits);
-          const uint4* rp = reinterpret_cast<const uint4*>(rrow + c * 32);
+          // the chunk's 64 bytes of this lane's row sit in the ring (rows of 128 bytes, 16-byte unit u
+          // of row r at position u ^ (r & 7)); chunk c is the half (c & 1) of 64-column piece c / 2
+          const uint8_t* srow;
+          {
+            const int piece = c >> 1, j = piece / Cfg::kRefPiecesPerStage, p = piece - j * Cfg::kRefPiecesPerStage;
+            const int use = num_k_blocks + j, s = use % kStages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&sm->full[s], (use / kStages) & 1, sm, status, kErrEpilogueWait))) break;
+            srow = ring + s * kStageBytes + (p * MT + mt) * kTileBytesA + (quarter * 32 + lane) * 128;
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            const uint4 r4 = __ldg(rp + v);
+            const uint4 r4 = *reinterpret_cast<const uint4*>(srow + ((((c & 1) * 4 + v) ^ (lane & 7)) << 4));
             float rf[8];
             Elem<__nv_bfloat16>::unpack(r4, rf);
 #pragma unroll
@@ -250,6 +284,14 @@ awq_gemm_sqerr_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             for (int j = 0; j < 32; ++j) cp[j] = __uint_as_float(acc[j]);
           }
         }
+      }
+    }
+    if (!finish && warp == 2 && lane == 0) {
+      // a CTA that does not run the loss epilogue (another split finishes the tile) still asked for the
+      // reference tile: the copy must have landed before this CTA's shared memory is given up
+      for (int j = 0; j < Cfg::kRefStages; ++j) {
+        const int use = num_k_blocks + j;
+        if (!mbar_wait(&sm->full[use % kStages], (use / kStages) & 1, sm, status, kErrEpilogueWait)) break;
       }
     }
     for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
@@ -303,8 +345,9 @@ static int awq_gemm_launch(const void* a, const void* b, const void* ref, int64_
   if (splits > 1) { bn = 128; mt = 1; }                   // more, smaller CTAs is the point of splitting
   const int kb_per_split = (total_kb + splits - 1) / splits;
   const int zdim = (total_kb + kb_per_split - 1) / kb_per_split;   // every split has at least one block
-  CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, bn)) return B200Q_ERR_CUDA;
+  CUtensorMap map_a, map_b, map_r;
+  if (!make_map(&map_a, a, m, k, kGM) || !make_map(&map_b, b, n, k, bn) || !make_map(&map_r, ref, m, n, kGM))
+    return B200Q_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto launch = [&](auto bn_tag, auto mt_tag) -> int {
     constexpr int BN = decltype(bn_tag)::value, MT = decltype(mt_tag)::value;
@@ -315,7 +358,7 @@ static int awq_gemm_launch(const void* a, const void* b, const void* ref, int64_
       return B200Q_ERR_CUDA;
     dim3 grid(static_cast<unsigned>(m / (kGM * MT)), static_cast<unsigned>(n / BN), static_cast<unsigned>(zdim));
     awq_gemm_sqerr_kernel<BN, MT><<<grid, Cfg::kThreads, smem, st>>>(
-        map_a, map_b, static_cast<const __nv_bfloat16*>(ref), n, total_kb, kb_per_split, partial, counters, sum_io,
+        map_a, map_b, map_r, n, total_kb, kb_per_split, partial, counters, sum_io,
         c_out, status_io);
     return launch_status();
   };
