@@ -11,14 +11,60 @@ from .config import QuantizerAttributeConfig
 from .nn import QuantLinear, QuantModule, SequentialQuantizer, TensorQuantizer
 
 __all__ = ["replace_quant_module", "set_quantizer_by_cfg", "set_quantizer_attribute",
-           "set_quantizer_by_cfg_context", "convert_to_quantized_model"]
+           "set_quantizer_by_cfg_context", "convert_to_quantized_model", "register", "unregister",
+           "QuantModuleRegistry"]
+
+
+class _QuantModuleRegistry:
+    """User-registered quantised classes by the exact type they replace (reference
+    modelopt/torch/quantization/nn/modules/quant_module.py ``QuantModuleRegistry`` with
+    conversion.py:330-400).  ``nn.Linear`` is built in and not listed here."""
+
+    def __init__(self):
+        self._by_original: dict[type, type] = {}
+
+    def get(self, original_cls):
+        return self._by_original.get(original_cls)
+
+    def __contains__(self, original_cls):
+        return original_cls in self._by_original
+
+    def register(self, original_cls, quantized_cls):
+        assert hasattr(quantized_cls, "_setup"), (
+            "Quantized class must have a _setup method which initializes various quantizers.")
+        assert issubclass(quantized_cls, original_cls), "the quantized class must derive from the class it replaces"
+        self._by_original[original_cls] = quantized_cls
+
+    def unregister(self, original_cls):
+        if original_cls not in self._by_original:
+            raise KeyError(f"{original_cls} is not registered")
+        del self._by_original[original_cls]
+
+
+QuantModuleRegistry = _QuantModuleRegistry()
+
+
+def register(original_cls, quantized_cls):
+    """Register ``quantized_cls`` (a subclass of ``original_cls`` with a ``_setup()`` that creates its
+    quantisers and a ``forward`` that calls them) to replace modules of exactly ``original_cls``."""
+    QuantModuleRegistry.register(original_cls, quantized_cls)
+
+
+def unregister(original_cls):
+    QuantModuleRegistry.unregister(original_cls)
 
 
 def replace_quant_module(model: nn.Module):
-    """Convert every ``nn.Linear`` (exact type or subclass not yet converted) in place."""
+    """Convert, in place, every ``nn.Linear`` (exact type or subclass not yet converted) and every module
+    whose exact type has a registered quantised class (class patch, then ``_setup()``)."""
     for m in list(model.modules()):
         if isinstance(m, nn.Linear) and not isinstance(m, QuantModule):
             QuantLinear.convert(m)
+            continue
+        quantized_cls = QuantModuleRegistry.get(type(m))
+        if quantized_cls is not None:
+            m.__class__ = quantized_cls
+            m._setup()
     return model
 
 

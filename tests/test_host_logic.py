@@ -463,3 +463,38 @@ def test_host_packer_group_plan():
     assert flat == list(range(225))
     small = _plan_groups(layer[:2] * 3, [1, 1] * 3, 512 << 20)
     assert small == [[0, 1, 2, 3, 4, 5]]
+
+
+def test_register_a_custom_quantized_module():
+    """Reference tests/unit/torch/quantization/test_module_registry.py: a user class replaces every module
+    of exactly the registered type, its quantisers answer to the wildcard configuration, and it can be
+    unregistered again."""
+    from b200q.nn import TensorQuantizer
+
+    class QuantReLU(nn.ReLU):
+        def _setup(self):
+            self.input_quantizer = TensorQuantizer(mtq.QuantizerAttributeConfig())
+            self.output_quantizer = TensorQuantizer(mtq.QuantizerAttributeConfig(enable=False))
+
+        def forward(self, x):
+            return self.output_quantizer(super().forward(self.input_quantizer(x)))
+
+    model = nn.Sequential(nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 8), nn.ReLU(), nn.LeakyReLU())
+    mtq.register(original_cls=nn.ReLU, quantized_cls=QuantReLU)
+    try:
+        assert mtq.QuantModuleRegistry.get(nn.ReLU) is QuantReLU and nn.ReLU in mtq.QuantModuleRegistry
+        mtq.replace_quant_module(model)
+        assert sum(isinstance(m, QuantReLU) for m in model.modules()) == 2
+        assert type(model[4]) is nn.LeakyReLU
+        mtq.set_quantizer_by_cfg(model, {"*input_quantizer": {"num_bits": 4, "enable": False}})
+        assert model[1].input_quantizer.num_bits == 4 and not model[1].input_quantizer.is_enabled
+        x = torch.randn(2, 8)
+        mtq.disable_quantizer(model, "*")
+        assert torch.equal(model[1](x), torch.relu(x))
+    finally:
+        mtq.unregister(nn.ReLU)
+    assert mtq.QuantModuleRegistry.get(nn.ReLU) is None
+    with pytest.raises(KeyError):
+        mtq.unregister(nn.ReLU)
+    with pytest.raises(AssertionError, match="_setup"):
+        mtq.register(nn.ReLU, nn.ReLU)
