@@ -351,3 +351,43 @@ def test_sequential_quantizer_attributes(mtq):
     assert sq.fake_quant is True
     sq[0]._fake_quant = False
     assert sq.fake_quant is False and sq[1]._fake_quant is True
+
+
+# ---- affine (bias) quantisation and printing (tests/unit/torch/quantization/test_affine_quant.py:52-98,
+# ---- test_print.py) ---------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("num_bits", [(2, 1), (4, 3)])
+@pytest.mark.parametrize("bias_type", ["static", "dynamic"])
+@pytest.mark.parametrize("method", ["mean", "max_min"])
+@pytest.mark.parametrize("axis", [(-1,), (-1, -3), (-1, -2, -3)])
+def test_bias_calibration_shapes(mtq, num_bits, bias_type, method, axis):
+    from b200q.model_calib import enable_stats_collection, finish_stats_collection
+
+    x = _rand(2, 3, 4, 16, seed=40)
+    cfg = {"num_bits": num_bits, "bias": {**dict.fromkeys(axis), "type": bias_type, "method": method}}
+    if num_bits == (2, 1):
+        cfg["block_sizes"] = {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}
+    q = _tq(mtq, **cfg)
+    enable_stats_collection(q)
+    y = q(x)
+    finish_stats_collection(q)
+    assert y.shape == x.shape
+    positive = {a % x.dim() for a in axis}
+    want = tuple(1 if d in positive else n for d, n in enumerate(x.shape))
+    if bias_type == "static":
+        assert tuple(q._bias_calibrator._calib_bias.shape) == want
+        assert torch.allclose(q._bias_calibrator._calib_bias, q.bias_value)
+    out = q(x)
+    assert out.shape == x.shape and torch.isfinite(out).all()
+
+
+def test_printing(mtq, capsys):
+    print(mtq.nn.TensorQuantizer())
+    model = torch.nn.Sequential(torch.nn.Linear(33, 65), mtq.nn.QuantLinear(33, 65))
+    print(model)
+    print(mtq.calib.MaxCalibrator(7, 1, False))
+    hist = mtq.calib.HistogramCalibrator(8, None, True)
+    hist.collect(_rand(10, seed=41, uniform=True))
+    print(hist)
+    text = capsys.readouterr().out
+    assert "TensorQuantizer" in text and "QuantLinear" in text and "MaxCalibrator" in text and "HistogramCalibrator" in text
