@@ -157,3 +157,45 @@ def test_block_sizes_given_as_axes_equal_the_axis_form(mtq):
     for a, b in zip(model_ref.net, model.net):
         if hasattr(a, "weight_quantizer"):
             assert torch.equal(a.weight_quantizer.amax.reshape(-1), b.weight_quantizer.amax.reshape(-1))
+
+
+def test_rotated_query_and_key_quantisers_of_a_registered_attention_module(mtq):
+    """Reference tests/gpu/torch/quantization/test_hadamard.py:46-82, with the attention class registered by
+    hand (``mtq.register``) instead of generated by the reference's Hugging Face plugin: rotating both the
+    query and the key by the same orthonormal Hadamard matrix leaves q·kᵀ, hence the output, unchanged;
+    rotating the key alone does not."""
+    import torch.nn.functional as F
+
+    class Attention(nn.Module):
+        def forward(self, q, k, v):
+            return F.scaled_dot_product_attention(q, k, v)
+
+    class QuantAttention(Attention):
+        def _setup(self):
+            self.q_bmm_quantizer = mtq.nn.TensorQuantizer()
+            self.k_bmm_quantizer = mtq.nn.TensorQuantizer()
+            self.v_bmm_quantizer = mtq.nn.TensorQuantizer()
+
+        def forward(self, q, k, v):
+            return super().forward(self.q_bmm_quantizer(q), self.k_bmm_quantizer(k), self.v_bmm_quantizer(v))
+
+    mtq.register(original_cls=Attention, quantized_cls=QuantAttention)
+    try:
+        model = nn.Sequential(Attention()).cuda()
+        mtq.replace_quant_module(model)
+        assert isinstance(model[0], QuantAttention)
+        mtq.set_quantizer_by_cfg(model, {"*": {"enable": False}})
+        g = torch.Generator(device="cuda").manual_seed(0)
+        q, k, v = (torch.randn(2, 4, 16, 64, generator=g, device="cuda") for _ in range(3))
+        want = model[0](q, k, v)
+        assert torch.equal(want, F.scaled_dot_product_attention(q, k, v))
+        with mtq.set_quantizer_by_cfg_context(model, {"*[qk]_bmm_quantizer": {"rotate": True, "enable": False}}):
+            assert model[0].q_bmm_quantizer._rotate and model[0].k_bmm_quantizer._rotate
+            both = model[0](q, k, v)
+        assert not model[0].q_bmm_quantizer._rotate
+        assert torch.allclose(both, want, atol=0.05)
+        with mtq.set_quantizer_by_cfg_context(model, {"*k_bmm_quantizer": {"rotate": True, "enable": False}}):
+            key_only = model[0](q, k, v)
+        assert not torch.allclose(key_only, want, atol=0.05)
+    finally:
+        mtq.unregister(Attention)
