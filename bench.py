@@ -1096,6 +1096,152 @@ def run_e2e(args, weights, layers, dev, world, total_elems, barrier):
 L70 = {"hidden": 8192, "kv": 1024, "inter": 28672, "layers": 80}
 
 
+def model_flow_70b(dev, world, rank, n_layers, sequences_per_rank, seq_len=1024, micro_batch=8):
+    """The calibration of BASELINE config 5 as a user runs it, on a reduced depth: a random-init decoder of
+    Llama-3-70B layer shapes (hidden 8192, 64 query / 8 key-value heads of 128, intermediate 28672, bf16;
+    embedding over the 128256-token vocabulary, ``n_layers`` layers, final norm; plain torch modules whose
+    names end in q_proj .. down_proj), seeded random token IDs batch-sharded over the ranks, NVFP4 quantisers
+    on every linear with 2048-bin histogram calibrators on the inputs, ``mtq.histogram_calibrate`` with the
+    percentile-99.99 read-out.  The forward GEMMs and attention are torch's (not part of the hand-written
+    path); reported are the calibration's wall time, the same forward passes without any quantiser, and
+    whether every rank ended with identical amax values."""
+    import copy
+
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from torch import nn
+
+    import b200q as mtq
+
+    H, HEADS, KVH, HD, I, VOCAB = 8192, 64, 8, 128, 28672, 128256
+
+    class RMSNorm(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = nn.Parameter(torch.ones(H))
+
+        def forward(self, x):
+            v = x.float()
+            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5)).to(x.dtype) * self.weight
+
+    class Attention(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = nn.Linear(H, HEADS * HD, bias=False)
+            self.k_proj = nn.Linear(H, KVH * HD, bias=False)
+            self.v_proj = nn.Linear(H, KVH * HD, bias=False)
+            self.o_proj = nn.Linear(HEADS * HD, H, bias=False)
+
+        def forward(self, x):
+            b, s, _ = x.shape
+            q = self.q_proj(x).view(b, s, HEADS, HD).transpose(1, 2)
+            k = self.k_proj(x).view(b, s, KVH, HD).transpose(1, 2)
+            v = self.v_proj(x).view(b, s, KVH, HD).transpose(1, 2)
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            return self.o_proj(o.transpose(1, 2).reshape(b, s, HEADS * HD))
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj = nn.Linear(H, I, bias=False)
+            self.up_proj = nn.Linear(H, I, bias=False)
+            self.down_proj = nn.Linear(I, H, bias=False)
+
+        def forward(self, x):
+            return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.input_layernorm, self.self_attn = RMSNorm(), Attention()
+            self.post_attention_layernorm, self.mlp = RMSNorm(), MLP()
+
+        def forward(self, x):
+            x = x + self.self_attn(self.input_layernorm(x))
+            return x + self.mlp(self.post_attention_layernorm(x))
+
+    class Decoder(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed_tokens = nn.Embedding(VOCAB, H)
+            self.layers = nn.ModuleList(Layer() for _ in range(n_layers))
+            self.norm = RMSNorm()
+
+        def forward(self, ids):
+            x = self.embed_tokens(ids)
+            for layer in self.layers:
+                x = layer(x)
+            return self.norm(x)
+
+    torch.manual_seed(1234)                                # the same replica on every rank
+    with torch.device(dev):
+        model = Decoder().to(torch.bfloat16)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() == 2:
+                p.normal_(0.0, 0.02)
+    model.eval()
+    g = torch.Generator(device=dev).manual_seed(0)
+    ids_all = torch.randint(0, VOCAB, (world * sequences_per_rank, seq_len), generator=g, device=dev)
+    mine = ids_all[rank * sequences_per_rank:(rank + 1) * sequences_per_rank]
+    batches = list(mine.split(micro_batch))
+
+    def forward_loop(m):
+        with torch.no_grad():
+            for ids in batches:
+                m(ids)
+
+    def timed(fn):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = t.item()
+        return dt
+
+    forward_loop(model)                                    # warm-up: GEMM plans, allocator
+    t_forward = timed(lambda: forward_loop(model))
+    cfg = copy.deepcopy(mtq.NVFP4_DEFAULT_CFG)
+    cfg["quant_cfg"]["*input_quantizer"]["calibrator"] = "histogram"
+    mtq.replace_quant_module(model)
+    mtq.set_quantizer_by_cfg(model, cfg["quant_cfg"])
+    first = batches[:1]
+    t_calib = timed(lambda: mtq.histogram_calibrate(
+        model, forward_loop, method="percentile", percentile=99.99,
+        first_batch_loop=lambda m: [m(ids) for ids in first]))
+    qs = [(n, m) for n, m in model.named_modules() if isinstance(m, mtq.nn.TensorQuantizer) and m.amax is not None]
+    amaxes = torch.cat([m.amax.float().reshape(-1) for _, m in qs])
+    same = True
+    if world > 1:
+        lo, hi = amaxes.clone(), amaxes.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool(torch.equal(lo, hi))
+    with torch.no_grad():
+        out = model(batches[0])                            # the calibrated, fake-quantised model runs
+    inputs_q = [m for n, m in qs if n.endswith("input_quantizer")]
+    return {
+        "model": "llama3-70b layer shapes, %d layers, random init, bf16; token IDs randint(0, 128256), seed 0" % n_layers,
+        "sequences_per_rank": sequences_per_rank, "seq_len": seq_len, "micro_batch_sequences": micro_batch,
+        "tokens_per_rank": sequences_per_rank * seq_len, "quantizers_with_amax": len(qs),
+        "histogram_input_quantizers": len(inputs_q),
+        "seconds": {"forward_only": t_forward, "histogram_calibrate": t_calib,
+                    "note": "histogram_calibrate = range pass over the first micro-batch + the forward passes with "
+                            "collection + exchanges + read-out; forward_only = the same forward passes before "
+                            "conversion"},
+        "input_amax_range": [float(min(m.amax.float().min() for m in inputs_q)),
+                             float(max(m.amax.float().max() for m in inputs_q))],
+        "amax_identical_on_all_ranks": same, "output_finite": bool(torch.isfinite(out.float()).all()),
+    }
+
+
 def run_calib70b(args):
     """Data-parallel NVFP4 activation calibration on Llama-3-70B shapes (``calibration_phases``: 560 input
     quantisers, max and 2048-bin histogram calibration), then the NVFP4 weight quantisation of this rank's
@@ -1141,6 +1287,11 @@ def run_calib70b(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_weights = t.item()
     clocks = sampler.stop(t_wall0, time.perf_counter())
+    model_flow = None
+    if args.model_layers > 0:
+        del group, weights
+        torch.cuda.empty_cache()
+        model_flow = model_flow_70b(dev, world, rank, args.model_layers, args.model_sequences)
     if rank == 0:
         w_elems = n_layers * sum(a * b for a, b in shapes)
         total = calibration["histogram"]["total_s"] + t_weights
@@ -1155,6 +1306,7 @@ def run_calib70b(args):
                                          "8192 tokens per rank per layer"},
             "calibration": calibration, "weights_seconds": t_weights,
             "weights_gbps_all_ranks": w_elems * BYTES_TOTAL / t_weights / 1e9, "clocks": clocks,
+            "model_flow": model_flow,
         }))
     if world > 1:
         dist.destroy_process_group()
@@ -1177,6 +1329,11 @@ def main():
                          "calib70b: data-parallel histogram calibration on 70B shapes")
     ap.add_argument("--tokens", type=int, default=8192, help="calibration: tokens per batch (per rank)")
     ap.add_argument("--batches", type=int, default=2, help="calibration: batches per rank per layer")
+    ap.add_argument("--model-layers", type=int, default=2,
+                    help="calib70b: depth of the 70B-shape decoder that is calibrated through mtq.histogram_calibrate "
+                         "on token IDs (0 = skip)")
+    ap.add_argument("--model-sequences", type=int, default=32,
+                    help="calib70b: sequences of 1024 tokens per rank for that model (the named configuration has 512)")
     ap.add_argument("--profile-kernels", action="store_true",
                     help="run a few launches of the secondary kernels and exit (for ncu captures)")
     ap.add_argument("--profile-awq-fused", type=int, default=0, metavar="N_ALPHA",
