@@ -131,8 +131,12 @@ class HistogramArena:
         self._stale = False
         idx = torch.arange(1, self.capacity + 1, device=self.counts.device)
         live = ((self.counts != 0) * idx).amax(dim=1)
-        ranges = torch.stack([c._range_dev[0] for c in self.cals])
+        # every calibrator's range slot (its own, or the slot of the calibrator whose first batch it shared)
+        base = self.ranges.data_ptr()
+        slots = torch.tensor([(c._range_dev.data_ptr() - base) // 4 for c in self.cals], device=self.counts.device)
+        ranges = self.ranges[slots]
         host = torch.stack([live.double(), self.overflow.double(), ranges.double()]).tolist()
+        fresh, grown = [], []
         for c, n_live, over, rng in zip(self.cals, *host):
             if not c._ranged:
                 continue
@@ -140,7 +144,36 @@ class HistogramArena:
                 raise RuntimeError(
                     f"HistogramCalibrator: {int(over)} samples were NaN, inf or beyond "
                     f"{HistogramCalibrator.CAPACITY_FACTOR}x the range of the first batch ({rng}); they were not binned.")
-            c._set_live(int(n_live), rng)
+            if c._calib_bin_edges is None or c._range0 != rng:
+                fresh.append((c, rng))
+            n = max(int(n_live), c._init_bins)
+            if n > (c._init_bins if fresh and fresh[-1][0] is c else c._num_bins):
+                grown.append((c, n, rng))
+        # the bin edges of all calibrators by two batched computations instead of one or two launches each
+        dev = self.counts.device
+        if fresh:
+            rows = _batched_linspace(torch.tensor([r for _, r in fresh], dtype=torch.float32, device=dev), self.num_bins + 1)
+            for (c, rng), row in zip(fresh, rows):
+                c._calib_bin_edges, c._range0, c._num_bins = row, rng, c._init_bins
+        if grown:
+            width = (torch.tensor([r for _, _, r in grown], dtype=torch.float32, device=dev)
+                     / torch.full((), self.num_bins, dtype=torch.float32, device=dev))
+            idx = torch.arange(max(n for _, n, _ in grown) + 1, dtype=torch.float32, device=dev)
+            rows = idx[None, :] * width[:, None]
+            for (c, n, _), row in zip(grown, rows):
+                c._calib_bin_edges, c._num_bins = row[:n + 1], n
+
+
+def _batched_linspace(ends: torch.Tensor, steps: int) -> torch.Tensor:
+    """Row i = ``torch.linspace(0, ends[i], steps)`` to the bit, for fp32 ``ends`` on a CUDA device: torch's
+    kernel forms the first half as ``step * i`` and the second half as ``end - step * (steps - 1 - i)`` in ONE
+    fused multiply-add (a single rounding); the float64 detour below rounds once as well (the product is
+    exact in float64).  Checked against torch.linspace in tests/test_calib_arena_gpu.py."""
+    step = ends / torch.full((), steps - 1, dtype=torch.float32, device=ends.device)
+    idx = torch.arange(steps, dtype=torch.float32, device=ends.device)
+    lo = step[:, None] * idx[None, :]
+    hi = (ends.double()[:, None] - step.double()[:, None] * ((steps - 1) - idx).double()[None, :]).float()
+    return torch.where(idx[None, :] < (steps // 2), lo, hi)
 
 
 def attach_histogram_arena(model, share_inputs: bool = True):

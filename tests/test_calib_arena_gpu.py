@@ -241,3 +241,41 @@ def test_batched_percentile_read_out_equals_the_single_one(mtq):
     assert n == 6
     for name, q in model.items():
         assert q._amax.item() == want[name], name
+
+
+def test_batched_bin_edges_equal_torch_linspace_and_the_grown_form():
+    """The arena builds all calibrators' bin edges in two batched computations; each row must be what the
+    single calibrator builds: ``torch.linspace(0, range, bins + 1)`` to the bit (torch's kernel rounds the
+    second half once, through a fused multiply-add), and ``arange(n + 1) * width`` once the histogram grew."""
+    from b200q.calib.histogram import _batched_linspace
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ends = torch.cat([torch.rand(500, generator=g, device="cuda") * 100 + 0.01,
+                      torch.tensor([33.72509765625, 85.3857421875, 1.0, 3.0, 7.123456], device="cuda")])
+    for steps in (2049, 33, 1001):
+        want = torch.stack([torch.linspace(0, float(e), steps, device="cuda") for e in ends])
+        assert torch.equal(_batched_linspace(ends, steps), want), steps
+
+
+def test_arena_read_back_gives_the_single_calibrators_edges_after_growth():
+    from b200q.calib import HistogramCalibrator, attach_histogram_arena
+    from b200q.nn import TensorQuantizer
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    batches = [torch.randn(256, 512, generator=g, device="cuda").bfloat16() * s for s in (1.0, 1.0, 3.0)]   # the third grows the range
+    model = torch.nn.ModuleDict({f"q{i}": TensorQuantizer({"num_bits": 8, "calibrator": "histogram"}) for i in range(3)}).cuda()
+    for q in model.values():
+        q.disable_quant(); q.enable_calib()
+    attach_histogram_arena(model)
+    alone = [HistogramCalibrator(8, None, False) for _ in range(3)]
+    for i, (q, cal) in enumerate(zip(model.values(), alone)):
+        for b in batches[: 2 + (i > 0)]:        # the first calibrator never grows
+            q(b * (i + 1))
+            cal.collect(b * (i + 1))
+    for q, cal in zip(model.values(), alone):
+        a = q._calibrator
+        a._resolve(); cal._resolve()
+        assert a._num_bins == cal._num_bins
+        assert torch.equal(a._calib_bin_edges, cal._calib_bin_edges)
+        assert torch.equal(a._calib_hist[: a._num_bins], cal._calib_hist[: cal._num_bins])
+        assert torch.equal(a.compute_amax("percentile", percentile=99.9), cal.compute_amax("percentile", percentile=99.9))
