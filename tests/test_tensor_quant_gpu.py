@@ -225,3 +225,25 @@ def test_amax_kept_along_several_dimensions(tq, amax_shape):
     want = torch.clamp(torch.round(x * scale), -128, 127) / scale
     assert torch.equal(tq.fake_tensor_quant(x, amax, None, 8, False, False), want)
     assert torch.allclose(tq.scaled_e4m3(x, amax, None, 4, 3), fp8_eager(x.clamp(-amax, amax), amax))
+
+
+# ---- a tensor on a GPU that is not the current one (test_tensor_quant_cuda.py:33-41,148-155) --------------
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensors_on_a_gpu_that_is_not_current(tq):
+    from b200q import ops
+
+    torch.cuda.set_device(0)
+    other = torch.device("cuda", torch.cuda.device_count() - 1)
+    x0 = _rand(3, 4, seed=50)
+    x = x0.to(other)
+    assert torch.cuda.current_device() == 0
+    got = tq.fake_tensor_quant(x, x.abs().max(), None)
+    assert got.device == other and torch.equal(got.cpu(), tq.fake_tensor_quant(x0, x0.abs().max(), None).cpu())
+    e = tq.scaled_e4m3(x, None, None, 4, 3)
+    assert e.device == other and torch.equal(e.cpu(), tq.scaled_e4m3(x0, None, None, 4, 3).cpu())
+    w = _rand(64, 256, seed=51, dtype=torch.bfloat16)
+    p0, s0, g0 = ops.nvfp4_quantize(w)
+    p1, s1, g1 = ops.nvfp4_quantize(w.to(other))
+    assert p1.device == other and torch.equal(p0.cpu(), p1.cpu()) and torch.equal(s0.cpu(), s1.cpu()) and g0.item() == g1.item()
+    assert torch.cuda.current_device() == 0
