@@ -99,6 +99,10 @@ class RealQuantLinear(QuantLinear):
         return self._real_quant_gemm_impl is not None
 
     def forward(self, input, *args, **kwargs):
+        from ..utils import is_torch_export_mode
+
+        if is_torch_export_mode():      # torch.export traces the fake-quantisation forward
+            return super().forward(input, *args, **kwargs)
         if (self._should_run_real_quant_gemm and input.numel() > 1
                 and self.has_real_quant_gemm_impl(input, *args, **kwargs)):
             out = self._real_quant_gemm_impl(self, input, self.weight, self.bias, *args, **kwargs)

@@ -20,7 +20,7 @@ from ..config import QuantizerAttributeConfig
 from ..qtensor import (BaseQuantizedTensor, FP8QTensor, INT4QTensor, INT8QTensor, MXFP4QTensor,
                        NVFP4QTensor, QTensorWrapper)
 from ..tensor_quant import dynamic_block_quant, fake_tensor_quant, normalized_hadamard_transform, scaled_e4m3
-from ..utils import convert_quantization_axis_to_reduce_axis, reduce_amax
+from ..utils import convert_quantization_axis_to_reduce_axis, is_torch_export_mode, reduce_amax
 
 __all__ = ["TensorQuantizer", "SequentialQuantizer"]
 
@@ -332,7 +332,7 @@ class TensorQuantizer(nn.Module):
     # ---- amax / block helpers ---------------------------------------------------------------
     def _get_amax(self, inputs):
         if hasattr(self, "_amax"):
-            return self._amax.data
+            return self._amax.detach() if is_torch_export_mode() else self._amax.data
         red = convert_quantization_axis_to_reduce_axis(inputs, self._axis)
         return reduce_amax(inputs, axis=red, keepdims=True).detach()
 

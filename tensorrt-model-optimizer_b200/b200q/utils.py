@@ -2,12 +2,14 @@
 computed by the single-pass CUDA reductions."""
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.nn.functional as F
 
 from . import ops
 
-__all__ = ["reduce_amax", "reduce_block_amax", "reduce_block_padding",
+__all__ = ["export_torch_mode", "is_torch_export_mode", "reduce_amax", "reduce_block_amax", "reduce_block_padding",
            "convert_quantization_axis_to_reduce_axis"]
 
 
@@ -92,3 +94,24 @@ def reduce_block_padding(input: torch.Tensor, block_sizes: dict, pad_value: floa
                 pad[(nd - 1 - d) * 2 + 1] = block - rem
                 x = F.pad(x, pad, value=pad_value)
         return x
+
+
+# ---- torch.export ---------------------------------------------------------------------------------------
+_EXPORT_MODE = False
+
+
+@contextlib.contextmanager
+def export_torch_mode():
+    """While active, quantised modules run the forms ``torch.export`` can trace: packed layers take the
+    fake-quantisation forward instead of a registered GEMM, amax buffers are read detached (reference
+    modelopt/torch/quantization/utils.py:360-374)."""
+    global _EXPORT_MODE
+    saved, _EXPORT_MODE = _EXPORT_MODE, True
+    try:
+        yield
+    finally:
+        _EXPORT_MODE = saved
+
+
+def is_torch_export_mode() -> bool:
+    return _EXPORT_MODE

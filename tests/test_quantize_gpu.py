@@ -199,3 +199,33 @@ def test_rotated_query_and_key_quantisers_of_a_registered_attention_module(mtq):
         assert not torch.allclose(key_only, want, atol=0.05)
     finally:
         mtq.unregister(Attention)
+
+
+@pytest.mark.parametrize(("name", "rtol", "atol"), [("FP8_DEFAULT_CFG", 1e-3, 1e-2), ("NVFP4_DEFAULT_CFG", 1e-3, 5e-1)])
+def test_torch_export_of_a_quantized_model(mtq, name, rtol, atol):
+    """Reference tests/gpu/torch/quantization/test_torch_export.py: ``torch.export`` traces the quantised
+    model through the registered ops (their meta implementations) and the exported program reproduces the
+    eager output."""
+    from b200q.utils import export_torch_mode
+
+    class SimpleNetwork(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.linear1 = nn.Linear(16, 32)
+            self.linear2 = nn.Linear(32, 16)
+
+        def forward(self, x):
+            return self.linear2(torch.relu(self.linear1(x)))
+
+    torch.manual_seed(42)
+    x = torch.randn(2, 16, device="cuda")
+    model = SimpleNetwork().eval().cuda()
+    with torch.inference_mode():
+        mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(x))
+        want = model(x)
+        with export_torch_mode():
+            program = torch.export.export(model, (x,), strict=False)
+            got = program.module()(x)
+    assert torch.allclose(want, got, rtol=rtol, atol=atol)
+    ops_seen = {str(n.target) for n in program.graph.nodes if n.op == "call_function"}
+    assert any("quantize_op" in t for t in ops_seen), ops_seen
