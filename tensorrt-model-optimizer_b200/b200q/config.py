@@ -234,6 +234,8 @@ class QuantizerAttributeConfig:
     def __post_init__(self):
         if isinstance(self.num_bits, list):
             self.num_bits = tuple(self.num_bits)
+        if isinstance(self.num_bits, tuple) and not all(isinstance(x, int) and x > 0 for x in self.num_bits):
+            raise ValueError("num_bits must be a positive integer or a tuple of positive integers.")
         if isinstance(self.num_bits, int):
             if self.num_bits < 1:
                 raise ValueError("num_bits must be a positive integer or a tuple of positive integers.")
@@ -273,6 +275,20 @@ class QuantizerAttributeConfig:
 
     def dict(self):
         return {f.name: getattr(self, f.name) for f in fields(self)}
+
+
+def _checked_init(init):
+    """A configuration that says nothing but ``enable=True`` is refused, as the reference's validator refuses
+    it (config.py:683-707): enabling needs to know what to enable."""
+    def __init__(self, *args, **kwargs):
+        if not args and set(kwargs) == {"enable"} and kwargs["enable"] is True:
+            raise ValueError("Invalid quantizer config: Cannot specify only {'enable': True}. "
+                             "Additional parameters are required when enabling quantization.")
+        init(self, *args, **kwargs)
+    return __init__
+
+
+QuantizerAttributeConfig.__init__ = _checked_init(QuantizerAttributeConfig.__init__)
 
 
 def need_calibration(config) -> bool:

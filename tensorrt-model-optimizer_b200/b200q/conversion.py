@@ -93,32 +93,29 @@ def set_quantizer_attribute(model: nn.Module, wildcard_or_filter, attribute, par
                 module = seq
             module.set_from_attribute_config([_as_cfg(a, None) for a in attribute])
         else:
+            if isinstance(module, SequentialQuantizer) and isinstance(attribute, dict):
+                # a dictionary changes what it names in every member (reference tensor_quantizer.py:1182-1196)
+                module.set_from_attribute_config([dict(attribute)] * len(module))
+                continue
             if isinstance(module, SequentialQuantizer):
-                parent = model.get_submodule(name.rpartition(".")[0]) if "." in name else model
+                parent =model.get_submodule(name.rpartition(".")[0]) if "." in name else model
                 module = TensorQuantizer()
                 setattr(parent, name.rpartition(".")[2], module)
             module.set_from_attribute_config(_as_cfg(attribute, module))
 
 
 def _as_cfg(attribute, module):
-    if isinstance(attribute, QuantizerAttributeConfig):
-        return attribute
-    attribute = dict(attribute)
-    if set(attribute) == {"enable"} and module is not None:
-        # a bare enable/disable keeps the quantiser's other attributes
-        cfg = QuantizerAttributeConfig(
-            enable=attribute["enable"], num_bits=module._num_bits, axis=module._axis,
-            fake_quant=module._fake_quant, unsigned=module._unsigned, narrow_range=module._narrow_range,
-            type="dynamic" if module._dynamic else "static", block_sizes=module._block_sizes,
-            calibrator=module._calibrator if module._calibrator is not None else "max")
-        return cfg
-    return QuantizerAttributeConfig(**attribute)
+    """Dictionaries pass through: a configured quantiser changes only what they name
+    (``TensorQuantizer.set_from_attribute_config``)."""
+    return attribute if isinstance(attribute, QuantizerAttributeConfig) else dict(attribute)
 
 
 def set_quantizer_by_cfg(model: nn.Module, quant_cfg: dict):
     """``quant_cfg`` maps wildcards (or ``nn.<Class>`` names) to attribute dictionaries; the
-    ``"default"`` entry is applied first, then the others in order."""
-    quant_cfg = dict(quant_cfg)
+    ``"default"`` entry is applied first, then the others in order.  Entries are applied as complete
+    records, ``{"enable": ...}`` alone as a switch (``_full_entries``); ``set_quantizer_attribute`` with a
+    dictionary changes only what the dictionary names."""
+    quant_cfg = _full_entries(dict(quant_cfg))
     if "default" in quant_cfg:
         set_quantizer_attribute(model, "*", quant_cfg["default"])
         quant_cfg.pop("default")
@@ -152,7 +149,31 @@ def set_quantizer_by_cfg_context(model: nn.Module, quant_cfg: dict):
                 m.__dict__.update(saved[name])
 
 
+def _full_entries(quant_cfg: dict, strict: bool = False) -> dict:
+    """The entries of a configuration dictionary as complete attribute records: what an entry does not name
+    takes its default (``enable`` included), as in the reference, whose configuration model turns every entry
+    into a QuantizerAttributeConfig before it is applied (config.py QuantizeConfig).  An entry that names
+    nothing but ``enable`` is a switch and stays a dictionary, so that it leaves the format of a configured
+    quantiser alone; with ``strict`` (the quantize() entry) ``{"enable": True}`` alone is refused there too."""
+    def full(entry):
+        if isinstance(entry, (list, tuple)):
+            return [full(e) for e in entry]
+        if isinstance(entry, dict):
+            if set(entry) == {"enable"} and not (strict and entry["enable"] is True):
+                return dict(entry)
+            return QuantizerAttributeConfig(**entry)
+        return entry
+
+    out = {}
+    for pattern, entry in quant_cfg.items():
+        if isinstance(pattern, str) and pattern.startswith("nn.") and isinstance(entry, dict):
+            out[pattern] = {sub: full(e) for sub, e in entry.items()}
+        else:
+            out[pattern] = full(entry)
+    return out
+
+
 def convert_to_quantized_model(model: nn.Module, config: dict):
     replace_quant_module(model)
-    set_quantizer_by_cfg(model, config.get("quant_cfg", {}))
+    set_quantizer_by_cfg(model, _full_entries(config.get("quant_cfg", {}), strict=True))
     return model

@@ -48,9 +48,34 @@ class TensorQuantizer(nn.Module):
         self._input_dtype = None
 
     # ---- configuration --------------------------------------------------------------------
+    def _current_attributes(self) -> dict:
+        """The quantiser's attributes in the vocabulary of QuantizerAttributeConfig (the axis that static block
+        quantisation derives for its reshaped input is not an attribute and reads as None)."""
+        return {"enable": not self._disabled, "num_bits": self._num_bits,
+                "axis": None if self._block_sizes is not None else self._axis, "fake_quant": self._fake_quant,
+                "unsigned": self._unsigned, "narrow_range": self._narrow_range,
+                "type": "dynamic" if self._dynamic else "static", "block_sizes": self._block_sizes, "bias": self._bias,
+                "trt_high_precision_dtype": self._trt_high_precision_dtype, "rotate": self._rotate,
+                "pass_through_bwd": self._pass_through_bwd}
+
     def set_from_attribute_config(self, attribute_cfg):
+        """A ``QuantizerAttributeConfig`` sets every attribute; a dictionary changes only the attributes it
+        names on a quantiser that is already configured (reference tensor_quantizer.py:135-168), e.g.
+        ``{"enable": False}`` switches the quantiser off and leaves its format and calibrator alone."""
+        keep_calibrator = None
         if isinstance(attribute_cfg, dict):
-            attribute_cfg = QuantizerAttributeConfig(**attribute_cfg)
+            given = dict(attribute_cfg)
+            if hasattr(self, "_num_bits"):
+                merged = {**self._current_attributes(), **given}
+                if given.get("axis") is not None and "block_sizes" not in given:
+                    merged["block_sizes"] = None
+                if given.get("block_sizes") is not None and "axis" not in given:
+                    merged["axis"] = None
+                if "calibrator" not in given and self._calibrator is not None:
+                    keep_calibrator = self._calibrator
+                    merged["calibrator"] = keep_calibrator
+                given = merged
+            attribute_cfg = QuantizerAttributeConfig(**given)
         c = attribute_cfg
         self._disabled = not c.enable
         self._num_bits = c.num_bits
@@ -66,6 +91,8 @@ class TensorQuantizer(nn.Module):
         self._pass_through_bwd = c.pass_through_bwd
         self._bias_calibrator = None
         self._calibrator = self._make_calibrator(c.calibrator)
+        if keep_calibrator is not None:     # the calibrator follows the attributes it was built from
+            keep_calibrator._num_bits, keep_calibrator._axis, keep_calibrator._unsigned = c.num_bits, c.axis, c.unsigned
         for attr in ("_block_reshape_size", "_padding", "_slices", "_original_shape", "_amax_shape_for_export"):
             if hasattr(self, attr):
                 delattr(self, attr)

@@ -498,3 +498,25 @@ def test_register_a_custom_quantized_module():
         mtq.unregister(nn.ReLU)
     with pytest.raises(AssertionError, match="_setup"):
         mtq.register(nn.ReLU, nn.ReLU)
+
+
+def test_quantizer_attribute_config_like_the_reference_tests():
+    """Reference tests/unit/torch/quantization/test_tensor_quant_cpu.py:33-87."""
+    C = mtq.QuantizerAttributeConfig
+    assert C(num_bits=5).num_bits == 5 and C(num_bits=5).axis is None
+    assert C(axis=(0, 1, 3)).num_bits == 8 and C(axis=(0, 1, 3)).axis == (0, 1, 3)
+    for cfg in (C(num_bits=2, fake_quant=True, axis=(1, 2)), C(num_bits=2, unsigned=True)):
+        assert C(**cfg.dict()) == cfg
+    with pytest.raises(ValueError, match="Cannot specify only {'enable': True}"):
+        C(enable=True)
+    C(enable=False)
+    C()
+    for bits in (0, -1, (0, 3), (-1, 2)):
+        with pytest.raises(ValueError, match="num_bits must be a positive integer or a tuple of positive integers."):
+            C(enable=True, num_bits=bits)
+    m = MLP()
+    mtq.replace_quant_module(m)
+    mtq.set_quantizer_by_cfg(m, mtq.INT8_DEFAULT_CFG["quant_cfg"])
+    mtq.disable_quantizer(m, "*up_proj*")
+    mtq.enable_quantizer(m, "*up_proj*")          # a bare enable through the wildcard API keeps the attributes
+    assert m.up_proj.weight_quantizer.is_enabled and m.up_proj.weight_quantizer.num_bits == 8

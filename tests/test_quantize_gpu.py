@@ -229,3 +229,32 @@ def test_torch_export_of_a_quantized_model(mtq, name, rtol, atol):
     assert torch.allclose(want, got, rtol=rtol, atol=atol)
     ops_seen = {str(n.target) for n in program.graph.nodes if n.op == "call_function"}
     assert any("quantize_op" in t for t in ops_seen), ops_seen
+
+
+def test_quantizer_context_restores_everything_but_what_calibration_added(mtq):
+    """Reference tests/unit/torch/quantization/test_tensor_quant_cpu.py:104-134: inside
+    ``set_quantizer_by_cfg_context`` only the output quantisers are on and get calibrated; afterwards the
+    model computes what it computed before and every other buffer is untouched."""
+    cfg = {"quant_cfg": {"*weight_quantizer": [{"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+                                               {"num_bits": 8, "axis": 0, "enable": True}],
+                         "*input_quantizer": {"num_bits": 8, "enable": True},
+                         "default": {"enable": False}},
+           "algorithm": "awq_full"}
+    model = _model().eval()
+    x = model.get_input()
+    mtq.quantize(model, cfg, lambda m: m(x))
+    state = {k: v.clone() for k, v in model.state_dict().items()}
+    with torch.no_grad():
+        want = model(x)
+    mtq.set_quantizer_by_cfg(model, {"*output_quantizer": {"enable": True}})
+    with mtq.set_quantizer_by_cfg_context(model, {"*": {"enable": False}, "*output_quantizer": {"enable": True}}):
+        for name, m in model.named_modules():
+            if isinstance(m, mtq.nn.TensorQuantizer):
+                assert m.is_enabled == name.endswith("output_quantizer"), name
+        mtq.calibrate(model, "max", lambda m: m(x * 10))
+    mtq.set_quantizer_by_cfg(model, {"*output_quantizer": {"enable": False}})
+    with torch.no_grad():
+        assert torch.allclose(model(x), want)
+    for k, v in model.state_dict().items():
+        if "output_quantizer" not in k:
+            assert torch.equal(v, state[k]), k
