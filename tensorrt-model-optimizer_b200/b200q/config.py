@@ -292,16 +292,21 @@ QuantizerAttributeConfig.__init__ = _checked_init(QuantizerAttributeConfig.__ini
 
 
 def need_calibration(config) -> bool:
-    """True when some enabled static quantiser of ``config`` needs calibration data."""
+    """True when ``config`` needs calibration data (reference config.py:1205-1231): any algorithm other than
+    "max", or some enabled quantiser other than a weight quantiser whose ``type`` is not "dynamic".  A dynamic
+    ``block_sizes`` type alone does not count as dynamic: NVFP4 activations take their second-level scale
+    from a calibrated per-tensor amax."""
     if config.get("algorithm") not in ("max", None):
         return True
+
+    def not_dynamic(c):
+        return bool(c.get("enable", True) and c.get("type", "") != "dynamic"
+                    and c.get("*", {}).get("enable", True))
+
     for name, cfg in config.get("quant_cfg", {}).items():
+        if "weight_quantizer" in str(name):
+            continue
         cfgs = cfg if isinstance(cfg, (list, tuple)) else [cfg]
-        for c in cfgs:
-            if not isinstance(c, dict) or "*" in c:
-                continue
-            if c.get("enable", True) and "weight_quantizer" not in name:
-                bs = c.get("block_sizes") or {}
-                if c.get("type", "static") != "dynamic" and bs.get("type", "static") != "dynamic":
-                    return True
+        if any(not_dynamic(c if isinstance(c, dict) else c.to_dict()) for c in cfgs):
+            return True
     return False

@@ -520,3 +520,42 @@ def test_quantizer_attribute_config_like_the_reference_tests():
     mtq.disable_quantizer(m, "*up_proj*")
     mtq.enable_quantizer(m, "*up_proj*")          # a bare enable through the wildcard API keeps the attributes
     assert m.up_proj.weight_quantizer.is_enabled and m.up_proj.weight_quantizer.num_bits == 8
+
+
+def test_need_calibration_like_the_reference_test():
+    """Reference tests/unit/torch/quantization/test_config_validation.py:28-35.  NVFP4 needs data although its
+    block scales are dynamic: the second-level scale comes from a calibrated per-tensor amax."""
+    from b200q.config import need_calibration
+
+    assert need_calibration(mtq.FP8_DEFAULT_CFG)
+    assert not need_calibration(mtq.FP8_PER_CHANNEL_PER_TOKEN_CFG)
+    assert not need_calibration(mtq.FP8_2D_BLOCKWISE_WEIGHT_ONLY_CFG)
+    assert need_calibration(mtq.INT4_AWQ_CFG)
+    assert need_calibration(mtq.W4A8_AWQ_BETA_CFG)
+    assert need_calibration(mtq.NVFP4_DEFAULT_CFG)
+
+
+@pytest.mark.parametrize(("shape", "quant_axis", "expected"), [
+    ((2, 3, 4), None, None), ((2, 3, 4), 0, [1, 2]), ((2, 3, 4), -2, [0, 2]),
+    ((2, 3, 4, 5), [0, -1], [1, 2]), ((2, 3, 4), (0, 2), [1])])
+def test_quantization_axis_to_reduce_axis_like_the_reference_test(shape, quant_axis, expected):
+    """Reference tests/unit/torch/quantization/test_utils.py:62-103."""
+    from b200q.utils import convert_quantization_axis_to_reduce_axis
+
+    assert convert_quantization_axis_to_reduce_axis(torch.empty(shape), quant_axis) == expected
+
+
+def test_replaced_modules_with_quantisers_off_compute_what_the_originals_do():
+    """Reference tests/unit/torch/quantization/test_quantize_replace.py:35-58, the linear model: conversion
+    keeps the parameters, and with every quantiser switched off nothing of the forward changes (no kernel
+    runs, so this holds on the CPU too)."""
+    torch.manual_seed(0)
+    ref = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 16))
+    quantised = nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 16))
+    quantised.load_state_dict(ref.state_dict())
+    mtq.replace_quant_module(quantised)
+    for m in quantised.modules():
+        assert not isinstance(m, nn.Linear) or (hasattr(m, "weight_quantizer") and hasattr(m, "input_quantizer"))
+    mtq.set_quantizer_attribute(quantised, "*", {"enable": False})
+    x = torch.randn(2, 16)
+    assert torch.equal(ref(x), quantised(x))

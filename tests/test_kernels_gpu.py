@@ -642,3 +642,18 @@ def test_rotating_quantizer(ops):
     xg = x.float().requires_grad_(True)
     q(xg).sum().backward()
     assert torch.allclose(xg.grad, ops.hadamard(torch.ones_like(xg), 1.0 / 128 ** 0.5))
+
+
+@pytest.mark.parametrize(("block_sizes", "rows", "expected"), [
+    ({-1: 2, -2: 2}, 2, [[5.0, 7.0]]),
+    ({-1: 4, -2: 2}, 4, [[7.0], [15.0]]),
+    ({-2: 4}, 4, [[12.0, 13.0, 14.0, 15.0]])])
+def test_reduce_block_amax_over_several_dimensions_like_the_reference_test(block_sizes, rows, expected):
+    """Reference tests/unit/torch/quantization/test_utils.py:26-59 (its comparison is not asserted there; the
+    values are what its ``reduce_block_amax`` returns: one dimension after the other)."""
+    from b200q.utils import reduce_block_amax
+
+    x = torch.arange(rows * 4, dtype=torch.bfloat16, device="cuda").reshape(rows, 4)
+    got = reduce_block_amax(x, block_sizes)
+    want = torch.tensor(expected, dtype=torch.bfloat16, device="cuda")
+    assert got.dtype == torch.bfloat16 and got.shape == want.shape and torch.equal(got, want)

@@ -258,3 +258,58 @@ def test_quantizer_context_restores_everything_but_what_calibration_added(mtq):
     for k, v in model.state_dict().items():
         if "output_quantizer" not in k:
             assert torch.equal(v, state[k]), k
+
+
+def _data_parallel_rank(rank, world, port):
+    import os
+
+    import torch.distributed as dist
+
+    import b200q
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank % torch.cuda.device_count())
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        model = _model()                                     # the same weights on every rank
+        g = torch.Generator(device="cuda").manual_seed(10 + rank)
+        batches = [torch.randn(2, 16, device="cuda", generator=g) * (1 + rank) for _ in range(2)]
+
+        def forward_loop(m):
+            for b in batches:
+                m(b)
+
+        alone = copy.deepcopy(model)
+        b200q.replace_quant_module(alone)
+        b200q.set_quantizer_by_cfg(alone, b200q.INT8_DEFAULT_CFG["quant_cfg"])
+        b200q.model_calib.max_calibrate(alone, forward_loop, distributed_sync=False)
+        b200q.quantize(model, b200q.INT8_DEFAULT_CFG, forward_loop)
+        checked = 0
+        for (name, q), (_, q_alone) in zip(model.named_modules(), alone.named_modules()):
+            if isinstance(q, b200q.nn.TensorQuantizer) and "output_quantizer" not in name:
+                # the reference's check: the amax already is the MAX over the ranks
+                over_ranks = q.amax.clone()
+                dist.all_reduce(over_ranks, op=dist.ReduceOp.MAX)
+                assert torch.equal(over_ranks, q.amax), name
+                # and it is the MAX of what each rank finds on its own batches
+                mine = q_alone.amax.clone()
+                dist.all_reduce(mine, op=dist.ReduceOp.MAX)
+                assert torch.equal(mine, q.amax), name
+                checked += 1
+        assert checked == 6
+    finally:
+        dist.destroy_process_group()
+
+
+def test_data_parallel_max_calibration_over_two_ranks(mtq):
+    """Reference tests/unit/torch/quantization/test_dist.py:28-47 with the tensors on the GPU: two ranks
+    (gloo; one GPU each when there are two, else both on the one GPU) calibrate INT8 on different batches
+    and end with the same amax, the maximum over both."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_data_parallel_rank, args=(2, port), nprocs=2, join=True)
