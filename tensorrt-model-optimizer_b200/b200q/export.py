@@ -11,7 +11,8 @@ from .qtensor import FP8QTensor, NVFP4QTensor, QTensorWrapper
 __all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized_weight",
            "get_quantization_format", "get_weight_block_size", "get_scaling_factor", "get_activation_scaling_factor",
            "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
-           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict",
+           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values",
+           "KV_CACHE_FP8", "KV_CACHE_INT8", "KV_CACHE_NVFP4", "KV_CACHE_NVFP4_AFFINE",
            "QUANTIZATION_FP8", "QUANTIZATION_INT8_SQ", "QUANTIZATION_INT8_WO", "QUANTIZATION_INT4_AWQ",
            "QUANTIZATION_W4A8_AWQ", "QUANTIZATION_NVFP4", "QUANTIZATION_NVFP4_AWQ", "QUANTIZATION_FP8_PB_WO",
            "QUANTIZATION_FP8_PC_PT"]
@@ -163,6 +164,23 @@ def get_weight_block_size(module) -> int:
     return wq.block_sizes[-1]
 
 
+def adjust_attn_amax_values(module):
+    """Give the weight quantisers of the q / k / v projections among ``module``'s children their common
+    maximum amax, as a fused QKV GEMM needs (reference modelopt/torch/export/quant_utils.py:185-211)."""
+    layers = []
+    for name, child in module.named_children():
+        for prefix in ("q", "k", "v"):
+            if prefix in name and hasattr(child, "weight_quantizer") and hasattr(child.weight_quantizer, "amax") \
+                    and child.weight_quantizer.amax is not None:
+                layers.append(child)
+    if not layers:
+        raise ValueError("No projection layers with the specified prefixes ('q', 'k', 'v') have amax attributes")
+    common = torch.stack([layer.weight_quantizer.amax.float().reshape(()) for layer in layers]).max()
+    assert common > 0, "max_amax must be positive."
+    for layer in layers:
+        layer.weight_quantizer.amax.copy_(common)
+
+
 def get_scaling_factor(quantizer):
     """fp32 scaling factor of a quantiser: amax / maxbound (amax / (6 * 448) for NVFP4)."""
     if not quantizer.is_enabled:
@@ -259,19 +277,38 @@ def export_quantized_weight(module, dtype: torch.dtype):
         module.register_buffer("weight_scale", weight_scale)
 
 
-def postprocess_state_dict(state_dict: dict) -> dict:
+KV_CACHE_FP8, KV_CACHE_INT8, KV_CACHE_NVFP4, KV_CACHE_NVFP4_AFFINE = "FP8", "INT8", "NVFP4", "NVFP4_AFFINE"
+
+
+def postprocess_state_dict(state_dict: dict, maxbound: float = 0.0, quantization: str | None = None) -> dict:
     """Drop quantiser state (``_amax``, output quantisers, real-quant scale buffers), rename
-    ``input_quantizer._pre_quant_scale`` to ``pre_quant_scale`` and squeeze ``[1, a, b]`` scales."""
+    ``input_quantizer._pre_quant_scale`` to ``pre_quant_scale``, turn the amax of KV-cache quantisers
+    (``[kv]_bmm_quantizer._amax``) into ``k_proj.k_scale`` / ``v_proj.v_scale`` = amax / ``maxbound`` (at least
+    1 for an FP8 cache, ``quantization`` naming the cache format) and squeeze ``[1, a, b]`` scales
+    (reference modelopt/torch/export/quant_utils.py:860-983)."""
     from .nn import RealQuantLinear
 
     skip = ("output_quantizer", "_amax", "_bias_value", "input_quantizer._pre_quant_scale")
-    old, new = "input_quantizer._pre_quant_scale", "pre_quant_scale"
+    replacements = {"k_bmm_quantizer._amax": "k_proj.k_scale", "v_bmm_quantizer._amax": "v_proj.v_scale",
+                    "k_bmm_quantizer._bias_value": "k_proj.k_bias", "v_bmm_quantizer._bias_value": "v_proj.v_bias",
+                    "input_quantizer._pre_quant_scale": "pre_quant_scale"}
     out = {}
     for key, value in state_dict.items():
         if all(s not in key for s in skip):
             out[key] = value
-        elif key.endswith(old):
+            continue
+        for old, new in replacements.items():
+            if not key.endswith(old):
+                continue
+            if "_amax" in key:
+                assert quantization in (KV_CACHE_FP8, KV_CACHE_NVFP4, KV_CACHE_NVFP4_AFFINE), (
+                    "Invalid KV cache quantization format.")
+                assert maxbound > 0, "Maxbound must be greater than zero."
+                value = _true_div(value.float(), float(maxbound))
+                if quantization == KV_CACHE_FP8:
+                    value = value.clamp(min=1.0)
             out[key[: -len(old)] + new] = value
+            break
     for key, value in list(out.items()):
         if "scale" in key and isinstance(value, torch.Tensor) and value.dim() == 3 and value.shape[0] == 1:
             out[key] = value.squeeze(0)

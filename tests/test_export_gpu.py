@@ -1,0 +1,153 @@
+"""The reference's export-helper tests (tests/gpu/torch/export/test_export.py) on this library: the format a
+quantised model reports, weight block sizes, scaling factors from weights and from quantisers, the common
+amax of q / k / v projections, and the state-dict post-processing with KV-cache scales.  Same toy models,
+configurations and known answers; rows for formats outside this library's path (KV-cache dtype of attention
+plugins, per-layer configuration records of the TensorRT-LLM exporter) are absent."""
+import pytest
+import torch
+from torch import nn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mtq():
+    import b200q
+
+    return b200q
+
+
+@pytest.fixture(scope="module")
+def export():
+    from b200q import export
+
+    return export
+
+
+class ToyModel(nn.Module):
+    def __init__(self, dims=(10, 10, 10, 10)):
+        super().__init__()
+        self.linears = nn.Sequential(*(nn.Linear(dims[i], dims[i + 1]) for i in range(len(dims) - 1)))
+
+    def forward(self, x):
+        return self.linears(x)
+
+
+class SmallLinearModelwithCustomWeight(nn.Module):
+    def __init__(self, weights):
+        super().__init__()
+        for name, w in zip(("q_proj", "k_proj", "v_proj", "o_proj"), weights):
+            layer = nn.Linear(w.shape[1], w.shape[0], bias=False)
+            with torch.no_grad():
+                layer.weight.copy_(w)
+            setattr(self, name, layer)
+
+    def forward(self, x):
+        return self.o_proj(self.v_proj(self.k_proj(self.q_proj(x))))
+
+
+_NVFP4 = {"num_bits": (2, 1), "block_sizes": {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}, "axis": None}
+partial_fp8_config = {"quant_cfg": {"*.1.weight_quantizer": {"num_bits": (4, 3), "axis": None},
+                                    "*.1.input_quantizer": {"num_bits": (4, 3), "axis": None},
+                                    "default": {"num_bits": 8, "enable": False}}, "algorithm": "max"}
+partial_w4a8_config = {
+    "quant_cfg": {"*.2.weight_quantizer": [{"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+                                           {"num_bits": (4, 3), "axis": None, "enable": True}],
+                  "*.2.input_quantizer": {"num_bits": (4, 3), "axis": None, "enable": True},
+                  "default": {"num_bits": 8, "enable": False}}, "algorithm": "awq_lite"}
+partial_nvfp4_config = {"quant_cfg": {"*.1.weight_quantizer": dict(_NVFP4, enable=True),
+                                      "*.1.input_quantizer": dict(_NVFP4, enable=True),
+                                      "default": {"enable": False}}, "algorithm": "max"}
+partial_nvfp4_awq_config = {"quant_cfg": {"*.2.weight_quantizer": dict(_NVFP4, enable=True),
+                                          "*.2.input_quantizer": dict(_NVFP4, enable=True),
+                                          "*.1.weight_quantizer": dict(_NVFP4, enable=False),
+                                          "*.1.input_quantizer": dict(_NVFP4, enable=False),
+                                          "default": {"enable": False}}, "algorithm": "awq_lite"}
+partial_int4_awq_config = {
+    "quant_cfg": {"*.2.weight_quantizer": {"num_bits": 4, "block_sizes": {-1: 128, "type": "static"}, "enable": True},
+                  "*.2.input_quantizer": {"enable": False}, "default": {"enable": False}},
+    "algorithm": {"method": "awq_lite", "alpha_step": 0.1}}
+
+
+def _only(which):
+    return {"quant_cfg": {f"*{name}_quantizer": {"num_bits": (4, 3), "axis": None, "enable": name == which}
+                          for name in ("weight", "input", "output")} | {"default": {"enable": False}},
+            "algorithm": "max"}
+
+
+def _toy(mtq, config):
+    torch.manual_seed(0)
+    model = ToyModel().cuda()
+    mtq.quantize(model, config, lambda m: m(torch.randn(1, 4, 10, device="cuda")))
+    return model
+
+
+@pytest.mark.parametrize(("config", "expected"), [
+    (partial_fp8_config, "fp8"), (partial_w4a8_config, "w4a8_awq"), (partial_nvfp4_config, "nvfp4"),
+    (partial_nvfp4_awq_config, "nvfp4_awq"), (partial_int4_awq_config, "int4_awq")])
+def test_get_quantization_format(mtq, export, config, expected):
+    """Reference test_export.py:68-81."""
+    assert export.get_quantization_format(_toy(mtq, config)) == expected
+
+
+@pytest.mark.parametrize(("weight", "group_size", "expected"), [
+    ([[0.0, 0.35, 0.28, 7.0], [0.49, 0.84, -0.77, 0.07]], 2, [[0.05, 1.0], [0.12, 0.11]]),
+    ([[0.127, 0.0, 1.27, -12.7], [0.0, 127.0, 0.254, 2.54]], 0, [0.1, 1.0]),
+    ([[0.0, 0.0, 0.0, 0.0], [0.0, -0.127, 0.254, 2.54]], 0, [1.0, 0.02]),            # zero replaced with 1.0
+    ([[0.0, 0.84, -0.77, 0.07], [0.0, 0.0, 0.0, 0.0]], 2, [[0.12, 0.11], [1.0, 1.0]])])
+def test_get_scaling_factor_from_weight(export, weight, group_size, expected):
+    """Reference test_export.py:163-196, exact as there: fp32 amax / 7 per group, amax / 127 per row."""
+    weight = torch.tensor(weight, device="cuda")
+    got = export.get_scaling_factor_from_weight(weight, group_size)
+    assert list(got.shape) == ([2, 4 // group_size] if group_size else [2])
+    assert torch.equal(got.cpu(), torch.tensor(expected))
+
+
+_QKVO = ([[0.1, 0.3], [0.22, 0.45]], [[0.44, 0.32], [0.11, 0.95]], [[0.9, 0.03], [0.92, 0.8]],
+         [[0.01, 0.97], [0.29, 0.77]])
+
+
+@pytest.mark.parametrize("negate", [False, True])
+@pytest.mark.parametrize("config_name", ["FP8_DEFAULT_CFG", "NVFP4_DEFAULT_CFG"])
+def test_adjust_attn_amax_values(mtq, export, config_name, negate):
+    """Reference test_export.py:277-320: q, k and v end with their common maximum, o keeps its own."""
+    weights = [torch.tensor(w) for w in _QKVO]
+    if negate:
+        weights[1][1, 1] *= -1
+        weights[3][0, 1] *= -1
+    model = SmallLinearModelwithCustomWeight(weights).cuda()
+    mtq.quantize(model, getattr(mtq, config_name), lambda m: m(torch.randn(1, 4, 2, device="cuda")))
+    export.adjust_attn_amax_values(model)
+    for layer in (model.q_proj, model.k_proj, model.v_proj):
+        assert layer.weight_quantizer.amax.item() == pytest.approx(0.95, rel=1e-6)
+    assert model.o_proj.weight_quantizer.amax.item() == pytest.approx(0.97, rel=1e-6)
+
+
+@pytest.mark.parametrize(("config", "expected"), [
+    ("FP8_DEFAULT_CFG", 0), ("INT8_WEIGHT_ONLY_CFG", 0), ("INT8_SMOOTHQUANT_CFG", 0), ("NVFP4_DEFAULT_CFG", 16),
+    ("NVFP4_AWQ_LITE_CFG", 16), ("W4A8_AWQ_BETA_CFG", 128), ("INT4_AWQ_CFG", 128), (partial_nvfp4_config, 16)])
+def test_get_weight_block_size(mtq, export, config, expected):
+    """Reference test_export.py:323-352."""
+    model = _toy(mtq, getattr(mtq, config) if isinstance(config, str) else config)
+    for module in model.modules():
+        size = export.get_weight_block_size(module)
+        wq = getattr(module, "weight_quantizer", None)
+        if wq is not None and (isinstance(wq, mtq.nn.SequentialQuantizer) or wq.is_enabled):
+            assert size == expected
+        else:
+            assert size == 0
+
+
+@pytest.mark.parametrize(("which", "expected_amax"), [
+    ("weight", [0.45, 0.95, 0.92, 0.97]), ("input", [1.0, 0.67, 0.68, 0.9]), ("output", [0.67, 0.68, 0.9, 0.88])])
+def test_get_scaling_factor(mtq, export, which, expected_amax):
+    """Reference test_export.py:355-390: amax / 448 of every enabled quantiser, in module order."""
+    model = SmallLinearModelwithCustomWeight([torch.tensor(w) for w in _QKVO]).cuda()
+    mtq.quantize(model, _only(which), lambda m: m(torch.ones(1, 2, 2, device="cuda")))
+    expected = list(expected_amax)
+    for module in model.modules():
+        if isinstance(module, mtq.nn.TensorQuantizer) and module.is_enabled:
+            scale = export.get_scaling_factor(module)
+            want = torch.tensor(expected.pop(0) / 448, dtype=scale.dtype, device=scale.device)
+            assert torch.allclose(scale, want, rtol=1e-3, atol=1e-3)
+    assert not expected

@@ -559,3 +559,26 @@ def test_replaced_modules_with_quantisers_off_compute_what_the_originals_do():
     mtq.set_quantizer_attribute(quantised, "*", {"enable": False})
     x = torch.randn(2, 16)
     assert torch.equal(ref(x), quantised(x))
+
+
+@pytest.mark.parametrize(("state_dict", "quantization", "expected"), [
+    ({"layer1.k_bmm_quantizer._amax": torch.tensor([0.128]), "layer1.v_bmm_quantizer._amax": torch.tensor([256.0]),
+      "layer1.input_quantizer._pre_quant_scale": torch.tensor([0.128])}, "FP8",
+     {"layer1.k_proj.k_scale": torch.tensor([1.0]), "layer1.v_proj.v_scale": torch.tensor([2.0]),
+      "layer1.pre_quant_scale": torch.tensor([0.128])}),
+    ({"layer1.q_bmm_quantizer._amax": torch.tensor([0.128]), "layer1.k_bmm_quantizer._amax": torch.tensor([0.128]),
+      "layer1.v_bmm_quantizer._amax": torch.tensor([256])}, "FP8",
+     {"layer1.k_proj.k_scale": torch.tensor([1.0]), "layer1.v_proj.v_scale": torch.tensor([2.0])}),
+    ({"layer1.input_quantizer._pre_quant_scale": torch.tensor([0.128])}, None,
+     {"layer1.pre_quant_scale": torch.tensor([0.128])})])
+def test_postprocess_state_dict_like_the_reference_test(state_dict, quantization, expected):
+    """Reference tests/gpu/torch/export/test_export.py:199-253: KV-cache amax becomes k_scale / v_scale =
+    amax / maxbound, at least 1 for an FP8 cache; other amax entries are dropped."""
+    from b200q import export
+
+    got = export.postprocess_state_dict(state_dict, 128.0, quantization)
+    assert got.keys() == expected.keys()
+    for k, v in expected.items():
+        assert torch.equal(got[k], v), k
+    with pytest.raises(AssertionError, match="Invalid KV cache"):
+        export.postprocess_state_dict({"l.k_bmm_quantizer._amax": torch.tensor([1.0])}, 128.0, None)
