@@ -151,3 +151,41 @@ def test_get_scaling_factor(mtq, export, which, expected_amax):
             want = torch.tensor(expected.pop(0) / 448, dtype=scale.dtype, device=scale.device)
             assert torch.allclose(scale, want, rtol=1e-3, atol=1e-3)
     assert not expected
+
+
+def _quantised_toy(mtq, dims, config):
+    torch.manual_seed(0)
+    model = ToyModel(dims).cuda()
+    mtq.quantize(model, config, lambda m: m(torch.randn(1, 4, dims[0], device="cuda")))
+    return model
+
+
+def test_export_per_tensor_quantized_weight(mtq, export):
+    """Reference tests/unit/torch/export/test_export_weight.py:49-78: a layer whose quantisers are off is
+    left alone; an FP8 layer gets E4M3 weights, ``weight_scale`` and ``input_scale``, no second scale."""
+    model = _quantised_toy(mtq, (32, 256, 32, 128), partial_fp8_config)
+    untouched, fp8 = model.linears[0], model.linears[1]
+    export.export_quantized_weight(untouched, torch.float32)
+    assert untouched.weight.dtype == torch.float32
+    assert not untouched.weight_quantizer.is_enabled and not untouched.input_quantizer.is_enabled
+    assert not untouched.output_quantizer.is_enabled
+    for name in ("weight_scale", "weight_scale_2", "input_scale", "output_scale"):
+        assert not hasattr(untouched, name), name
+    export.export_quantized_weight(fp8, torch.float32)
+    assert fp8.weight.dtype == torch.float8_e4m3fn
+    assert hasattr(fp8, "weight_scale") and hasattr(fp8, "input_scale")
+    assert not hasattr(fp8, "weight_scale_2") and not hasattr(fp8, "output_scale")
+    assert hasattr(fp8, "weight_quantizer") and hasattr(fp8, "input_quantizer")
+    assert not fp8.output_quantizer.is_enabled
+
+
+def test_export_per_block_quantized_weight(mtq, export):
+    """Reference tests/unit/torch/export/test_export_weight.py:81-98 (and its GPU twin): a W4A8 layer gets
+    packed uint8 weights, both weight scales and the input scale."""
+    model = _quantised_toy(mtq, (32, 256, 256, 32), partial_w4a8_config)
+    layer = model.linears[2]
+    export.export_quantized_weight(layer, torch.float32)
+    assert layer.weight.dtype == torch.uint8
+    for name in ("weight_quantizer", "weight_scale", "weight_scale_2", "input_scale", "input_quantizer"):
+        assert hasattr(layer, name), name
+    assert not layer.output_quantizer.is_enabled and not hasattr(layer, "output_scale")
