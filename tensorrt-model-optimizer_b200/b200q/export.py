@@ -12,6 +12,7 @@ __all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized
            "get_quantization_format", "get_weight_block_size", "get_scaling_factor", "get_activation_scaling_factor",
            "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
            "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values",
+           "get_kv_cache_dtype", "get_kv_cache_scaling_factor", "get_kv_cache_bias",
            "KV_CACHE_FP8", "KV_CACHE_INT8", "KV_CACHE_NVFP4", "KV_CACHE_NVFP4_AFFINE",
            "QUANTIZATION_FP8", "QUANTIZATION_INT8_SQ", "QUANTIZATION_INT8_WO", "QUANTIZATION_INT4_AWQ",
            "QUANTIZATION_W4A8_AWQ", "QUANTIZATION_NVFP4", "QUANTIZATION_NVFP4_AWQ", "QUANTIZATION_FP8_PB_WO",
@@ -194,6 +195,43 @@ def get_scaling_factor(quantizer):
         s = _true_div(amax.float(), float(quantizer.maxbound))
     assert torch.all(s > 0), f"scaling factor {s} not positive."
     return s
+
+
+def get_kv_cache_dtype(modules):
+    """"FP8" / "INT8" / "NVFP4" / "NVFP4_AFFINE" from the enabled ``k_bmm_quantizer`` / ``v_bmm_quantizer`` /
+    ``output_quantizer`` of a module or list of modules, None without one (reference
+    modelopt/torch/export/quant_utils.py:373-409)."""
+    if isinstance(modules, torch.nn.Module):
+        modules = [modules]
+    bits, affine = [], True
+    for module in modules:
+        for name in ("k_bmm_quantizer", "v_bmm_quantizer", "output_quantizer"):
+            q = getattr(module, name, None)
+            if q is not None and q.is_enabled:
+                bits.append(q.num_bits)
+                affine &= getattr(q, "_bias_value", None) is not None
+    if (4, 3) in bits:
+        return KV_CACHE_FP8
+    if 8 in bits:
+        return KV_CACHE_INT8
+    if (2, 1) in bits:
+        return KV_CACHE_NVFP4_AFFINE if affine else KV_CACHE_NVFP4
+    return QUANTIZATION_NONE
+
+
+def get_kv_cache_bias(kv_module):
+    return [getattr(getattr(kv_module, name, None), "_bias_value", None) for name in ("k_bmm_quantizer", "v_bmm_quantizer")]
+
+
+def get_kv_cache_scaling_factor(kv_module):
+    """[k scale, v scale] of an attention module with KV-cache quantisers, at least 1 for an FP8 cache
+    (reference modelopt/torch/export/quant_utils.py:348-370); [None, None] without the quantisers."""
+    if not hasattr(kv_module, "k_bmm_quantizer") or not hasattr(kv_module, "v_bmm_quantizer"):
+        return [None, None]
+    factors = [get_scaling_factor(getattr(kv_module, name)) for name in ("k_bmm_quantizer", "v_bmm_quantizer")]
+    if get_kv_cache_dtype(kv_module) == KV_CACHE_FP8:
+        factors = [f.clamp(min=1.0) for f in factors]
+    return factors
 
 
 def get_activation_scaling_factor(module):

@@ -189,3 +189,35 @@ def test_export_per_block_quantized_weight(mtq, export):
     for name in ("weight_quantizer", "weight_scale", "weight_scale_2", "input_scale", "input_quantizer"):
         assert hasattr(layer, name), name
     assert not layer.output_quantizer.is_enabled and not hasattr(layer, "output_scale")
+
+
+@pytest.mark.parametrize(("output_bits", "expected"), [((4, 3), "FP8"), (8, "INT8")])
+def test_get_kv_cache_dtype(mtq, export, output_bits, expected):
+    """Reference test_export.py:256-274: the cache format is read off the enabled output quantisers."""
+    config = {"quant_cfg": {"*.1.weight_quantizer": {"num_bits": (4, 3), "axis": None},
+                            "*.1.input_quantizer": {"num_bits": (4, 3), "axis": None},
+                            "*output_quantizer": {"num_bits": output_bits, "axis": None, "enable": True},
+                            "default": {"enable": False}}, "algorithm": "max"}
+    model = _toy(mtq, config)
+    assert export.get_kv_cache_dtype(list(model.modules())) == expected
+    assert export.get_kv_cache_dtype(_toy(mtq, partial_fp8_config)) is None
+
+
+def test_get_kv_cache_scaling_factor(mtq, export):
+    """Scales of the key / value quantisers of an attention module: amax / 448, at least 1 for an FP8 cache
+    (reference modelopt/torch/export/quant_utils.py:348-370)."""
+    from b200q.config import QuantizerAttributeConfig
+
+    class Attention(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.k_bmm_quantizer = mtq.nn.TensorQuantizer(QuantizerAttributeConfig(num_bits=(4, 3), axis=None))
+            self.v_bmm_quantizer = mtq.nn.TensorQuantizer(QuantizerAttributeConfig(num_bits=(4, 3), axis=None))
+
+    attention = Attention().cuda()
+    attention.k_bmm_quantizer.amax = torch.tensor(0.128, device="cuda")
+    attention.v_bmm_quantizer.amax = torch.tensor(896.0, device="cuda")
+    k, v = export.get_kv_cache_scaling_factor(attention)
+    assert k.item() == 1.0 and v.item() == 2.0
+    assert export.get_kv_cache_scaling_factor(nn.Linear(2, 2)) == [None, None]
+    assert export.get_kv_cache_bias(attention) == [None, None]
