@@ -8,7 +8,7 @@ import torch
 from . import ops
 from .qtensor import FP8QTensor, NVFP4QTensor, QTensorWrapper
 
-__all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized_weight",
+__all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized_weight", "from_quantized_weight",
            "get_quantization_format", "get_weight_block_size", "get_scaling_factor", "get_activation_scaling_factor",
            "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
            "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values",
@@ -105,6 +105,19 @@ def to_quantized_weight(weight, weights_scaling_factor, quantization: str, weigh
             "Weights scaling factor 2 not passed. Unable to quantize to NVFP4 format")
         return NVFP4QTensor.quantize(weight, block_size, weights_scaling_factor,
                                      weights_scaling_factor2)[0]._quantized_data
+    raise NotImplementedError(f"quantization format {quantization} not supported")
+
+
+def from_quantized_weight(weight, weights_scaling_factor, quantization: str, torch_dtype):
+    """Back from the checkpoint form to ``torch_dtype`` for the one-byte formats with one scale per tensor or
+    per row (FP8, INT8); anything wider is only cast (reference modelopt/torch/export/quant_utils.py:837-857,
+    the same two torch operations, so the values are the reference's)."""
+    if weight.element_size() >= 2 or weights_scaling_factor is None or not quantization:
+        return weight.to(torch_dtype)
+    if quantization == QUANTIZATION_FP8:
+        return weight.view(torch.float8_e4m3fn).to(torch_dtype) * weights_scaling_factor.to(torch_dtype)
+    if quantization in (QUANTIZATION_INT8_SQ, QUANTIZATION_INT8_WO):
+        return weight.to(torch_dtype) * weights_scaling_factor[:, None].to(torch_dtype)
     raise NotImplementedError(f"quantization format {quantization} not supported")
 
 

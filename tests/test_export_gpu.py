@@ -221,3 +221,22 @@ def test_get_kv_cache_scaling_factor(mtq, export):
     assert k.item() == 1.0 and v.item() == 2.0
     assert export.get_kv_cache_scaling_factor(nn.Linear(2, 2)) == [None, None]
     assert export.get_kv_cache_bias(attention) == [None, None]
+
+
+@pytest.mark.parametrize("quantization", ["fp8", "int8_sq", "int8_wo"])
+def test_from_quantized_weight_undoes_to_quantized_weight(export, quantization):
+    """Reference modelopt/torch/export/quant_utils.py:741-857: packing then unpacking returns every weight to
+    within half a quantisation step (an eighth of the value for E4M3's three mantissa bits)."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    weight = torch.randn(64, 128, device="cuda", generator=g, dtype=torch.float32)
+    if quantization == "fp8":
+        scale = (weight.abs().max() / 448.0).reshape(1)
+        tolerance = (weight.abs() / 16 + scale * 2.0 ** -10) * (1 + 1e-5)
+    else:
+        scale = weight.abs().amax(dim=1) / 127.0
+        tolerance = (scale / 2)[:, None] * (1 + 1e-6)
+    packed = export.to_quantized_weight(weight, scale, quantization)
+    assert packed.element_size() == 1
+    back = export.from_quantized_weight(packed, scale, quantization, torch.float32)
+    assert back.dtype == torch.float32 and bool(((back - weight).abs() <= tolerance).all())
+    assert export.from_quantized_weight(weight, None, quantization, torch.bfloat16).dtype == torch.bfloat16
