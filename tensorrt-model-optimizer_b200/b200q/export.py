@@ -11,7 +11,8 @@ from .qtensor import FP8QTensor, NVFP4QTensor, QTensorWrapper
 __all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized_weight", "from_quantized_weight",
            "get_quantization_format", "get_weight_block_size", "get_scaling_factor", "get_activation_scaling_factor",
            "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
-           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values",
+           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values", "all_items_same",
+           "preprocess_linear_fusion", "fuse_prequant_layernorm", "requantize_resmooth_fused_llm_layers",
            "get_kv_cache_dtype", "get_kv_cache_scaling_factor", "get_kv_cache_bias",
            "KV_CACHE_FP8", "KV_CACHE_INT8", "KV_CACHE_NVFP4", "KV_CACHE_NVFP4_AFFINE",
            "QUANTIZATION_FP8", "QUANTIZATION_INT8_SQ", "QUANTIZATION_INT8_WO", "QUANTIZATION_INT4_AWQ",
@@ -377,15 +378,147 @@ def postprocess_state_dict(state_dict: dict, maxbound: float = 0.0, quantization
     return out
 
 
+# ------------------------------------------------------------- layers that share their input --
+# Reference: modelopt/torch/export/quant_utils.py:986-1011,1104-1187 and
+# modelopt/torch/export/unified_export_hf.py:90-232.  Linear layers fed the same tensor (q / k / v, gate / up)
+# are served by one fused GEMM at deployment: they must agree on the input scale, on a per-tensor weight scale
+# and on the AWQ pre-quant scale, which can then move into the normalisation layer in front of them.
+
+def all_items_same(item_list):
+    return all(x == item_list[0] for x in item_list)
+
+
 @torch.no_grad()
-def export_hf_state_dict(model, dtype: torch.dtype | None = None) -> dict:
+def _update_pre_quant_scale(module, new_pre_quant_scale):
+    """Re-smooth ``module`` to another pre-quant scale: the weight takes old / new (in fp32), the weight
+    quantiser is calibrated again on the new weight."""
+    from .model_calib import enable_stats_collection, finish_stats_collection
+
+    old = module.input_quantizer._pre_quant_scale
+    dtype, device = module.weight.dtype, module.weight.device
+    module.weight = torch.nn.Parameter(
+        (module.weight.to(torch.float32) * old.to(dtype=torch.float32, device=device)
+         / new_pre_quant_scale.to(dtype=torch.float32, device=device)).to(dtype),
+        requires_grad=module.weight.requires_grad)
+    module.input_quantizer.pre_quant_scale = new_pre_quant_scale
+    module.weight_quantizer.reset_amax()
+    enable_stats_collection(module.weight_quantizer)
+    module.weight_quantizer(module.weight)
+    finish_stats_collection(module.weight_quantizer)
+
+
+@torch.no_grad()
+def preprocess_linear_fusion(modules, resmooth_only=False):
+    """Make the quantised linear layers ``modules`` fusable: the mean of their pre-quant scales for all
+    (weights re-smoothed and re-calibrated), the maximum of their per-tensor input amax and of their
+    per-tensor weight amax (the second quantiser of a sequential pair)."""
+    from .nn import SequentialQuantizer
+
+    assert all_items_same([get_quantization_format(m) for m in modules]), "Modules have different quantization formats"
+    first = modules[0]
+    if hasattr(first, "input_quantizer"):
+        if first.input_quantizer.pre_quant_scale is not None:
+            mean = torch.mean(torch.stack([m.input_quantizer.pre_quant_scale for m in modules]), dim=0)
+            for m in modules:
+                if not torch.equal(m.input_quantizer.pre_quant_scale, mean):
+                    _update_pre_quant_scale(m, mean)
+        if resmooth_only:
+            return
+        if first.input_quantizer.is_enabled and first.input_quantizer.amax is not None:
+            assert first.input_quantizer.amax.numel() == 1, "Only support scalar input quant amax"
+            common = torch.max(torch.stack([m.input_quantizer.amax for m in modules]))
+            for m in modules:
+                m.input_quantizer.amax = common
+    if hasattr(first, "weight_quantizer"):
+        wq = first.weight_quantizer
+        if isinstance(wq, SequentialQuantizer):
+            if wq[-1].is_enabled:
+                assert len(wq) == 2
+                common = torch.max(torch.stack([m.weight_quantizer[-1].amax for m in modules]))
+                for m in modules:
+                    m.weight_quantizer[-1].amax = common
+        elif wq.is_enabled and wq.amax is not None and wq.amax.numel() == 1:
+            common = torch.max(torch.stack([m.weight_quantizer.amax for m in modules]))
+            for m in modules:
+                m.weight_quantizer.amax = common
+
+
+@torch.no_grad()
+def fuse_prequant_layernorm(layernorm_module, modules):
+    """Move the (common) pre-quant scale of ``modules`` into the weight and bias of the normalisation layer
+    that feeds them; the layers lose their ``_pre_quant_scale`` and are marked ``fused_with_prequant``."""
+    scale = modules[0].input_quantizer._pre_quant_scale
+    layernorm_module.weight = torch.nn.Parameter(layernorm_module.weight * scale)
+    if getattr(layernorm_module, "bias", None) is not None:
+        layernorm_module.bias = torch.nn.Parameter(layernorm_module.bias * scale)
+    for m in modules:
+        delattr(m.input_quantizer, "_pre_quant_scale")
+        m.fused_with_prequant = True
+
+
+def _is_layernorm(module) -> bool:
+    name = type(module).__name__
+    return any(key in name for key in ("LayerNorm", "RMSNorm"))
+
+
+@torch.no_grad()
+def requantize_resmooth_fused_llm_layers(model, fake_input=None):
+    """Find the quantised linear layers that are fed the same tensor by one forward pass with every
+    quantiser off, make each such group fusable (``preprocess_linear_fusion``; FP8 layers keep their own
+    scales, as in the reference) and, for AWQ formats, move the group's pre-quant scale into the
+    normalisation layer whose output they read.  ``fake_input`` defaults to the two-token id tensor the
+    reference feeds a causal language model.  Returns {first layer's name: names of its group}."""
+    from .conversion import set_quantizer_by_cfg_context
+    from .nn import is_quantized_linear
+
+    by_input, by_output, handles, names = {}, {}, [], {}
+
+    def saw_input(module, args, output):
+        by_input.setdefault(args[0], []).append(module)
+
+    def saw_output(module, args, output):
+        by_output[output] = module
+
+    for name, module in model.named_modules():
+        names[module] = name
+        if _is_layernorm(module):
+            handles.append(module.register_forward_hook(saw_output))
+        elif is_quantized_linear(module) and (module.input_quantizer.is_enabled or module.weight_quantizer.is_enabled):
+            handles.append(module.register_forward_hook(saw_input))
+    try:
+        if fake_input is None:
+            device = next(model.parameters()).device
+            fake_input = torch.ones([1, 2], dtype=torch.long, device=device)
+        with set_quantizer_by_cfg_context(model, {"*": {"enable": False}}):
+            model(fake_input)
+    finally:
+        for h in handles:
+            h.remove()
+    fused = {}
+    for tensor, modules in by_input.items():
+        fmt = get_quantization_format(modules[0])
+        if len(modules) > 1 and fmt not in (QUANTIZATION_FP8, QUANTIZATION_NONE):
+            preprocess_linear_fusion(modules)
+            fused[names[modules[0]]] = [names[m] for m in modules]
+        if fmt is not QUANTIZATION_NONE and "awq" in fmt and tensor in by_output \
+                and hasattr(modules[0].input_quantizer, "_pre_quant_scale"):
+            fuse_prequant_layernorm(by_output[tensor], modules)
+    return fused
+
+
+@torch.no_grad()
+def export_hf_state_dict(model, dtype: torch.dtype | None = None, fake_input=None) -> dict:
     """Packed state dict of a quantised model with the checkpoint's names (``weight``,
     ``weight_scale``, ``weight_scale_2``, ``input_scale``, ``pre_quant_scale``).  The model's
-    linear layers are converted in place."""
+    linear layers are converted in place.  Layers that share their input are first made fusable
+    (``requantize_resmooth_fused_llm_layers``) when the model is a Hugging Face model (it has a ``config``;
+    the reference's two-token input is used) or when ``fake_input`` gives the tensor to trace it with."""
     from .nn import is_quantized_linear
 
     if dtype is None:
         dtype = next(p.dtype for p in model.parameters() if p.is_floating_point())
+    if fake_input is not None or hasattr(model, "config"):
+        requantize_resmooth_fused_llm_layers(model, fake_input)
     for _, m in model.named_modules():
         if is_quantized_linear(m) and get_quantization_format(m) is not QUANTIZATION_NONE:
             export_quantized_weight(m, dtype)

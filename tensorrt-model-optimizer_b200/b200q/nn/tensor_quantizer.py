@@ -65,6 +65,20 @@ class TensorQuantizer(nn.Module):
         keep_calibrator = None
         if isinstance(attribute_cfg, dict):
             given = dict(attribute_cfg)
+            if hasattr(self, "_num_bits") and not {"axis", "block_sizes", "calibrator"} & set(given):
+                # nothing that shapes the amax is named: the calibrator, its axis and the block view that a
+                # static block quantiser has set up for its input stay as they are
+                c = QuantizerAttributeConfig(**{**self._current_attributes(), **given})     # validates
+                for key in given:
+                    if key == "enable":
+                        self._disabled = not c.enable
+                    elif key == "type":
+                        self._dynamic = c.type == "dynamic"
+                    elif key in ("num_bits", "unsigned"):
+                        setattr(self, key, getattr(c, key))        # the setters carry it to the calibrator
+                    else:
+                        setattr(self, "_" + key, getattr(c, key))
+                return
             if hasattr(self, "_num_bits"):
                 merged = {**self._current_attributes(), **given}
                 if given.get("axis") is not None and "block_sizes" not in given:

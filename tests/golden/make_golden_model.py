@@ -167,6 +167,83 @@ def golden_export_layers(mtq, out):
     np.savez_compressed(out / "export_layers.npz", **cases)
 
 
+class SharedInputBlock(nn.Module):
+    """A normalisation layer feeding three projections, as the attention input of a decoder layer."""
+
+    def __init__(self, hidden=128):
+        super().__init__()
+        self.input_layernorm = nn.LayerNorm(hidden)
+        self.q_proj = nn.Linear(hidden, 128, bias=False)
+        self.k_proj = nn.Linear(hidden, 64, bias=False)
+        self.v_proj = nn.Linear(hidden, 64, bias=False)
+
+    def forward(self, x):
+        h = self.input_layernorm(x)
+        return torch.cat([self.q_proj(h), self.k_proj(h), self.v_proj(h)], dim=-1)
+
+
+def make_shared_input_block(seed, dtype):
+    torch.manual_seed(seed)
+    m = SharedInputBlock()
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if "layernorm" in name:
+                p.copy_(1.0 + 0.1 * torch.randn_like(p) if name.endswith("weight") else 0.05 * torch.randn_like(p))
+            else:
+                p.copy_(torch.randn_like(p) * (0.03 + 0.02 * "qkv".index(name[0])))
+    return m.to(dtype)
+
+
+def golden_export_fusion(mtq, out):
+    """Layers that share their input, made fusable by the reference (preprocess_linear_fusion, then
+    fuse_prequant_layernorm for the AWQ format) and exported layer by layer.  Stored: the state of the
+    block before the fusion step (weights, pre-quant scales, amax) and the exported state dict after it."""
+    from modelopt.torch.export.quant_utils import (fuse_prequant_layernorm, get_quantization_format,
+                                                   postprocess_state_dict, preprocess_linear_fusion)
+    from modelopt.torch.export.unified_export_hf import _export_quantized_weight
+
+    cases = {}
+    dtype = torch.bfloat16
+    batches = make_batches(52, 2, dtype)
+    for i, b in enumerate(batches):
+        cases[f"x{i}"] = bits(b)
+    base = make_shared_input_block(51, dtype)
+    for k, v in base.state_dict().items():
+        cases[f"base_{k}"] = bits(v)
+
+    def loop(m):
+        for b in batches:
+            m(b)
+
+    int4 = copy.deepcopy(mtq.INT4_AWQ_CFG)
+    int4["quant_cfg"]["*weight_quantizer"]["block_sizes"] = {-1: 32, "type": "static"}
+    for tag, cfg in (("nvfp4", mtq.NVFP4_DEFAULT_CFG), ("int4_awq", int4), ("w4a8_awq", mtq.W4A8_AWQ_BETA_CFG),
+                     ("fp8", mtq.FP8_DEFAULT_CFG)):
+        model = copy.deepcopy(base)
+        mtq.quantize(model, copy.deepcopy(cfg), loop)
+        layers = [model.q_proj, model.k_proj, model.v_proj]
+        for name, lin in zip("qkv", layers):      # what the fusion step starts from
+            cases[f"{tag}_pre_{name}_weight"] = bits(lin.weight)
+            if hasattr(lin.input_quantizer, "_pre_quant_scale"):
+                cases[f"{tag}_pre_{name}_pqs"] = bits(lin.input_quantizer._pre_quant_scale)
+            if getattr(lin.input_quantizer, "_amax", None) is not None:
+                cases[f"{tag}_pre_{name}_in_amax"] = bits(lin.input_quantizer._amax.float().reshape(-1))
+        fmt = get_quantization_format(layers[0])
+        cases[f"{tag}_format"] = np.array(str(fmt))
+        if fmt != "fp8":                                          # unified_export_hf.py:186-196
+            preprocess_linear_fusion(layers)
+        if "awq" in fmt:
+            fuse_prequant_layernorm(model.input_layernorm, layers)
+        for lin in layers:
+            _export_quantized_weight(lin, dtype)
+        sd = postprocess_state_dict(model.state_dict(), 448.0, None)
+        cases[f"{tag}_keys"] = np.array(sorted(sd.keys()))
+        for k, v in sd.items():
+            cases[f"{tag}_sd_{k}"] = bits(v)
+            cases[f"{tag}_dt_{k}"] = np.array(str(v.dtype))
+    np.savez_compressed(out / "export_fusion.npz", **cases)
+
+
 def golden_clip_smooth(mtq, out):
     """awq_clip / awq_full on INT4 block-32 weights (losses per clip ratio and block, the chosen
     block amax) and INT8 smoothquant (pre-quant scale, smoothed weight, amax buffers)."""
@@ -229,6 +306,10 @@ def main():
         golden_export_layers(mtq, HERE)
         print("wrote export_layers")
         return
+    if args.only == "export_fusion":
+        golden_export_fusion(mtq, HERE)
+        print("wrote export_fusion")
+        return
     if args.only == "awq128":
         golden_awq(mtq, HERE, "awq128", hidden=256, inter=512, tokens=128)
         print("wrote awq128")
@@ -246,6 +327,8 @@ def main():
     print("wrote clip_smooth")
     golden_export_layers(mtq, HERE)
     print("wrote export_layers")
+    golden_export_fusion(mtq, HERE)
+    print("wrote export_fusion")
 
 
 if __name__ == "__main__":
