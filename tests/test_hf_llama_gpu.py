@@ -68,3 +68,55 @@ def test_quantize_and_compress_a_hugging_face_llama(name):
     fresh.load_state_dict(model.state_dict())
     with torch.no_grad():
         assert torch.equal(fresh(batches[0]).logits, model(batches[0]).logits)
+
+
+@pytest.mark.parametrize("name", ["NVFP4_DEFAULT_CFG", "FP8_DEFAULT_CFG", "INT4_AWQ_CFG"])
+def test_export_a_hugging_face_llama_with_its_shared_input_layers_made_fusable(name):
+    """``export_hf_state_dict`` on the Hugging Face module tree (reference unified_export_hf.py:90-232, 233-392):
+    q / k / v and gate / up read one tensor each and leave with common scales; with AWQ their averaged pre-quant
+    scale moves into the RMSNorm in front of them (o_proj and down_proj keep theirs), and the model still
+    computes what it computed before the layers were re-smoothed."""
+    import b200q as mtq
+    from b200q import export
+
+    model = _tiny_llama()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    batches = [torch.randint(0, 512, (2, 64), generator=g, device="cuda") for _ in range(3)]
+
+    def loop(m):
+        with torch.no_grad():
+            for ids in batches:
+                m(ids)
+
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), loop)
+    with torch.no_grad():
+        before = model(batches[0]).logits.float()
+    norm_before = model.model.layers[0].input_layernorm.weight.clone()
+    fused = export.requantize_resmooth_fused_llm_layers(copy.deepcopy(model))
+    if name == "FP8_DEFAULT_CFG":
+        assert fused == {}
+    else:
+        assert fused == {f"model.layers.{i}.{first}": [f"model.layers.{i}.{first.split('.')[0]}.{p}" for p in group]
+                         for i in range(2) for first, group in (("self_attn.q_proj", ("q_proj", "k_proj", "v_proj")),
+                                                                ("mlp.gate_proj", ("gate_proj", "up_proj")))}
+    if name == "INT4_AWQ_CFG":
+        probe = copy.deepcopy(model)
+        export.requantize_resmooth_fused_llm_layers(probe)
+        with torch.no_grad():
+            after = probe(batches[0]).logits.float()
+        cos = torch.nn.functional.cosine_similarity(after.flatten(), before.flatten(), dim=0)
+        assert cos > 0.98, float(cos)             # the groups leave their own best scale for the average: 4-bit rounding moves
+    sd = export.export_hf_state_dict(model, torch.bfloat16)
+    attn, mlp = "model.layers.0.self_attn.", "model.layers.0.mlp."
+    if name == "NVFP4_DEFAULT_CFG":
+        for key in ("input_scale", "weight_scale_2"):
+            assert torch.equal(sd[attn + "q_proj." + key], sd[attn + "k_proj." + key])
+            assert torch.equal(sd[attn + "q_proj." + key], sd[attn + "v_proj." + key])
+            assert torch.equal(sd[mlp + "gate_proj." + key], sd[mlp + "up_proj." + key])
+        assert sd[attn + "q_proj.weight"].dtype == torch.uint8
+    if name == "INT4_AWQ_CFG":
+        for layer in ("q_proj", "k_proj", "v_proj"):
+            assert attn + layer + ".pre_quant_scale" not in sd
+        assert attn + "o_proj.pre_quant_scale" in sd and mlp + "down_proj.pre_quant_scale" in sd
+        assert not torch.equal(sd["model.layers.0.input_layernorm.weight"], norm_before)
+    assert not any("_amax" in k or "quantizer" in k for k in sd)
