@@ -2,7 +2,7 @@
 quantize / calibrate path.  ``import b200q as mtq`` gives the reference's entry points
 (``quantize``, ``calibrate``, ``compress``, the ``*_CFG`` dictionaries) for this path."""
 from . import _cabi, ops  # noqa: F401  (loading the library is part of importing the package)
-from . import backends, calib, dist, nn, qtensor, tensor_quant, utils  # noqa: F401
+from . import backends, calib, dist, export, nn, qtensor, tensor_quant, utils  # noqa: F401
 from .config import *  # noqa: F401,F403
 from .conversion import (QuantModuleRegistry, register, replace_quant_module, set_quantizer_attribute,  # noqa: F401
                          set_quantizer_by_cfg, set_quantizer_by_cfg_context, unregister)

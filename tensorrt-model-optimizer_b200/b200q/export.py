@@ -11,7 +11,8 @@ from .qtensor import FP8QTensor, NVFP4QTensor, QTensorWrapper
 __all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized_weight", "from_quantized_weight",
            "get_quantization_format", "get_weight_block_size", "get_scaling_factor", "get_activation_scaling_factor",
            "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
-           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values", "all_items_same",
+           "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values", "all_items_same", "process_layer_quant_config", "get_quant_config",
+           "convert_hf_quant_config_format", "export_hf_checkpoint",
            "preprocess_linear_fusion", "fuse_prequant_layernorm", "requantize_resmooth_fused_llm_layers",
            "get_kv_cache_dtype", "get_kv_cache_scaling_factor", "get_kv_cache_bias",
            "KV_CACHE_FP8", "KV_CACHE_INT8", "KV_CACHE_NVFP4", "KV_CACHE_NVFP4_AFFINE",
@@ -506,6 +507,98 @@ def requantize_resmooth_fused_llm_layers(model, fake_input=None):
     return fused
 
 
+# ------------------------------------------------------ the quantisation record of a checkpoint --
+# Reference: modelopt/torch/export/quant_utils.py:536-694 (process_layer_quant_config) and :1190-1290
+# (get_quant_config): what ``hf_quant_config.json`` says beside the packed tensors.
+
+# format name -> (deployment algorithm name, carries a group size, is an AWQ format)
+_ALGORITHM_OF_FORMAT = {
+    QUANTIZATION_FP8: ("FP8", False, False),
+    QUANTIZATION_FP8_PC_PT: ("FP8_PER_CHANNEL_PER_TOKEN", False, False),
+    QUANTIZATION_INT4_AWQ: ("W4A16_AWQ", True, True),
+    QUANTIZATION_W4A8_AWQ: ("W4A8_AWQ", True, True),
+    QUANTIZATION_INT8_WO: ("W8A16", False, False),
+    QUANTIZATION_INT8_SQ: ("W8A8_SQ_PER_CHANNEL", False, False),
+    QUANTIZATION_NVFP4: ("NVFP4", True, False),
+    QUANTIZATION_NVFP4_AWQ: ("NVFP4_AWQ", True, True),
+    "w4a8_nvfp4_fp8": ("W4A8_NVFP4_FP8", True, True),
+    "w4a8_mxfp4_fp8": ("W4A8_MXFP4_FP8", True, False),
+}
+
+
+def _exclusion_patterns(unquantized, quantized):
+    """The fewest-characters description of the unquantised layers by patterns cut at dots: for each layer
+    the shortest ``prefix*`` (else the pair ``prefix`` + ``prefix.*``, else the name itself) that cannot
+    match a quantised layer; a layer already covered by chosen patterns adds nothing."""
+    forbidden = set()
+    for name in quantized:
+        forbidden.add(name)
+        forbidden.update(name[:i] + "*" for i in range(len(name) + 1))
+    chosen = set()
+    for name in unquantized:
+        cuts = [i for i, ch in enumerate(name) if ch == "."]
+        options = [o for i in cuts for o in ([name[:i] + "*"], [name[:i], name[:i] + ".*"])] + [[name]]
+        for option in options:
+            if any(pattern in forbidden for pattern in option):
+                continue
+            if not all(pattern in chosen for pattern in option):
+                chosen.update(option)
+            break
+    return chosen
+
+
+def process_layer_quant_config(layer_config_dict: dict) -> dict:
+    """``{"<layer>.quantization": format, "<layer>.awq_block_size": n}`` -> the record of the whole model: one
+    algorithm with the excluded modules when every quantised layer has the same settings, else
+    ``MIXED_PRECISION`` with the settings layer by layer."""
+    layers, excluded, kinds = {}, [], {}
+    for key, fmt in layer_config_dict.items():
+        if "awq_block_size" in key:
+            continue
+        layer = key.rsplit(".", 1)[0]
+        algorithm, grouped, awq = _ALGORITHM_OF_FORMAT.get(fmt, (fmt, False, False))
+        if algorithm is QUANTIZATION_NONE:
+            excluded.append(layer)
+            continue
+        record = {"quant_algo": algorithm}
+        if grouped:
+            record["group_size"] = layer_config_dict.get(layer + ".awq_block_size", 0)
+        if awq:
+            record.update(has_zero_point=False, pre_quant_scale=True)
+        layers[layer] = record
+        kinds[str(record)] = record
+    out = {"quant_algo": None, "kv_cache_quant_algo": None}
+    if len(kinds) > 1:
+        out["quant_algo"] = "MIXED_PRECISION"
+        out["quantized_layers"] = layers
+    elif len(kinds) == 1:
+        out.update(next(iter(kinds.values())))
+        out["exclude_modules"] = sorted(_exclusion_patterns(excluded, layers.keys()))
+    else:
+        out["quantized_layers"] = {}
+    return out
+
+
+def get_quant_config(model) -> dict:
+    """The quantisation record of a (fully, partly or mixed-precision) quantised model:
+    ``{"producer": {...}, "quantization": {...}}``."""
+    per_layer, kv_format = {}, QUANTIZATION_NONE
+    for name, module in model.named_modules():
+        if hasattr(module, "weight_quantizer") or hasattr(module, "input_quantizer"):
+            per_layer[name + ".quantization"] = get_quantization_format(module)
+            per_layer[name + ".awq_block_size"] = get_weight_block_size(module)
+        if any(getattr(getattr(module, q, None), "is_enabled", False)
+               for q in ("k_bmm_quantizer", "v_bmm_quantizer", "output_quantizer")):
+            mine = get_kv_cache_dtype(module)
+            assert kv_format in (QUANTIZATION_NONE, mine), "Do not support mixed precision kv cache quantization"
+            kv_format = mine
+    quantization = {"quant_algo": None, "kv_cache_quant_algo": None}
+    quantization.update(process_layer_quant_config(per_layer))
+    if kv_format is not QUANTIZATION_NONE:
+        quantization["kv_cache_quant_algo"] = kv_format
+    return {"producer": {"name": "b200q", "version": "0.40"}, "quantization": quantization}
+
+
 @torch.no_grad()
 def export_hf_state_dict(model, dtype: torch.dtype | None = None, fake_input=None) -> dict:
     """Packed state dict of a quantised model with the checkpoint's names (``weight``,
@@ -523,3 +616,57 @@ def export_hf_state_dict(model, dtype: torch.dtype | None = None, fake_input=Non
         if is_quantized_linear(m) and get_quantization_format(m) is not QUANTIZATION_NONE:
             export_quantized_weight(m, dtype)
     return postprocess_state_dict(model.state_dict())
+
+
+def convert_hf_quant_config_format(record: dict) -> dict:
+    """The quantisation record in the shape Hugging Face's ``config.json`` carries as ``quantization_config``
+    (reference modelopt/torch/export/convert_hf_config.py:21-117): the scheme of the one weight / activation
+    group for FP8 and NVFP4, the ignored modules, the KV-cache scheme, ``quant_method`` "modelopt"."""
+    q = record.get("quantization", {})
+    algorithm = q.get("quant_algo")
+    scheme = {"FP8": {"dynamic": False, "num_bits": 8, "type": "float"},
+              "NVFP4": {"dynamic": False, "num_bits": 4, "type": "float", "group_size": q.get("group_size", 16)}}
+    out = {}
+    if algorithm in scheme:
+        out["config_groups"] = {"group_0": {"input_activations": dict(scheme[algorithm]),
+                                            "weights": dict(scheme[algorithm]), "targets": ["Linear"]}}
+    out["ignore"] = q.get("exclude_modules") or []
+    if algorithm:
+        out["quant_algo"] = algorithm
+    kv = q.get("kv_cache_quant_algo")
+    if kv:
+        out["kv_cache_scheme"] = dict(scheme["FP8"]) if kv == "FP8" else kv
+    if record.get("producer"):
+        out["producer"] = record["producer"]
+    out["quant_method"] = "modelopt"
+    return out
+
+
+def export_hf_checkpoint(model, dtype: torch.dtype | None = None, export_dir="exported_model", fake_input=None):
+    """Write the packed checkpoint of a quantised model to ``export_dir``: ``hf_quant_config.json`` (the
+    quantisation record), the tensors under their checkpoint names, and — for a Hugging Face model, saved
+    with its own ``save_pretrained`` — ``config.json`` with the record as ``quantization_config``; any other
+    module is written as ``model.safetensors`` (reference modelopt/torch/export/unified_export_hf.py:556-615).
+    The model's linear layers are converted in place."""
+    import json
+    from pathlib import Path
+
+    export_dir = Path(export_dir)
+    export_dir.mkdir(parents=True, exist_ok=True)
+    record = get_quant_config(model)            # read before the layers are converted
+    state = export_hf_state_dict(model, dtype, fake_input)
+    quantised = record["quantization"]["quant_algo"] is not None
+    if quantised:
+        (export_dir / "hf_quant_config.json").write_text(json.dumps(record, indent=4))
+    if hasattr(model, "save_pretrained"):
+        model.save_pretrained(export_dir, state_dict=dict(state))      # it empties the dictionary it is given
+        config_path = export_dir / "config.json"
+        config = json.loads(config_path.read_text())
+        if quantised:
+            config["quantization_config"] = convert_hf_quant_config_format(record)
+        config_path.write_text(json.dumps(config, indent=4))
+    else:
+        from safetensors.torch import save_file
+
+        save_file({k: v.contiguous() for k, v in state.items()}, str(export_dir / "model.safetensors"))
+    return state, record

@@ -240,3 +240,27 @@ def test_from_quantized_weight_undoes_to_quantized_weight(export, quantization):
     back = export.from_quantized_weight(packed, scale, quantization, torch.float32)
     assert back.dtype == torch.float32 and bool(((back - weight).abs() <= tolerance).all())
     assert export.from_quantized_weight(weight, None, quantization, torch.bfloat16).dtype == torch.bfloat16
+
+
+def _kv_config(output_bits):
+    return {"quant_cfg": {"*.1.weight_quantizer": {"num_bits": (4, 3), "axis": None},
+                          "*.1.input_quantizer": {"num_bits": (4, 3), "axis": None},
+                          "*output_quantizer": {"num_bits": output_bits, "axis": None, "enable": True},
+                          "default": {"enable": False}}, "algorithm": "max"}
+
+
+@pytest.mark.parametrize(("config", "expected"), [
+    (partial_fp8_config, {"exclude_modules": ["linears.0", "linears.2"], "kv_cache_quant_algo": None, "quant_algo": "FP8"}),
+    (partial_w4a8_config, {"exclude_modules": ["linears.0", "linears.1"], "group_size": 128, "has_zero_point": False,
+                           "kv_cache_quant_algo": None, "pre_quant_scale": True, "quant_algo": "W4A8_AWQ"}),
+    (partial_nvfp4_config, {"exclude_modules": ["linears.0", "linears.2"], "group_size": 16,
+                            "kv_cache_quant_algo": None, "quant_algo": "NVFP4"}),
+    (partial_nvfp4_awq_config, {"exclude_modules": ["linears.0", "linears.1"], "group_size": 16, "has_zero_point": False,
+                                "pre_quant_scale": True, "kv_cache_quant_algo": None, "quant_algo": "NVFP4_AWQ"}),
+    (partial_int4_awq_config, {"exclude_modules": ["linears.0", "linears.1"], "group_size": 128, "has_zero_point": False,
+                               "kv_cache_quant_algo": None, "pre_quant_scale": True, "quant_algo": "W4A16_AWQ"}),
+    (_kv_config((4, 3)), {"exclude_modules": ["linears.0", "linears.2"], "quant_algo": "FP8", "kv_cache_quant_algo": "FP8"}),
+    (_kv_config(8), {"exclude_modules": ["linears.0", "linears.2"], "quant_algo": "FP8", "kv_cache_quant_algo": "INT8"})])
+def test_get_quant_config(mtq, export, config, expected):
+    """Reference test_export.py:393-466: the quantisation record written beside an exported checkpoint."""
+    assert export.get_quant_config(_toy(mtq, config))["quantization"] == expected

@@ -120,3 +120,40 @@ def test_export_a_hugging_face_llama_with_its_shared_input_layers_made_fusable(n
         assert attn + "o_proj.pre_quant_scale" in sd and mlp + "down_proj.pre_quant_scale" in sd
         assert not torch.equal(sd["model.layers.0.input_layernorm.weight"], norm_before)
     assert not any("_amax" in k or "quantizer" in k for k in sd)
+
+
+@pytest.mark.parametrize("name", ["NVFP4_DEFAULT_CFG", "FP8_DEFAULT_CFG"])
+def test_export_hf_checkpoint_writes_tensors_record_and_config(name, tmp_path):
+    """Reference modelopt/torch/export/unified_export_hf.py:556-615: the directory holds the packed tensors
+    (read back bit for bit), ``hf_quant_config.json`` and a ``config.json`` that carries the record."""
+    import json
+
+    from safetensors import safe_open
+
+    import b200q as mtq
+    from b200q import export
+
+    model = _tiny_llama()
+    ids = torch.randint(0, 512, (2, 64), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(ids))
+    state, record = export.export_hf_checkpoint(model, torch.bfloat16, tmp_path)
+    algorithm = "NVFP4" if "NVFP4" in name else "FP8"
+    assert record["quantization"]["quant_algo"] == algorithm
+    assert record["quantization"]["exclude_modules"] == ["lm_head"]
+    assert json.loads((tmp_path / "hf_quant_config.json").read_text()) == record
+    config = json.loads((tmp_path / "config.json").read_text())
+    assert config["quantization_config"]["quant_algo"] == algorithm
+    assert config["quantization_config"]["ignore"] == ["lm_head"]
+    files = sorted(p.name for p in tmp_path.glob("*.safetensors"))
+    assert files
+    seen = {}
+    for f in files:
+        with safe_open(str(tmp_path / f), framework="pt") as reader:
+            for key in reader.keys():
+                seen[key] = reader.get_tensor(key)
+    assert set(seen) == set(state)
+    key = "model.layers.0.self_attn.q_proj.weight"
+    assert seen[key].dtype == (torch.uint8 if algorithm == "NVFP4" else torch.float8_e4m3fn)
+    for k, v in state.items():
+        assert torch.equal(seen[k].view(torch.uint8) if v.element_size() == 1 else seen[k],
+                           v.cpu().view(torch.uint8) if v.element_size() == 1 else v.cpu()), k

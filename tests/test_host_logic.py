@@ -582,3 +582,52 @@ def test_postprocess_state_dict_like_the_reference_test(state_dict, quantization
         assert torch.equal(got[k], v), k
     with pytest.raises(AssertionError, match="Invalid KV cache"):
         export.postprocess_state_dict({"l.k_bmm_quantizer._amax": torch.tensor([1.0])}, 128.0, None)
+
+
+def test_process_layer_quant_config_like_the_reference_test():
+    """Reference tests/gpu/torch/export/test_export.py:84-142: several formats give MIXED_PRECISION with the
+    settings layer by layer; one format gives that format with the excluded modules."""
+    from b200q import export
+
+    mixed = export.process_layer_quant_config({
+        "layer1.quantization": "nvfp4", "layer1.awq_block_size": 16, "layer3.quantization": "int4_awq",
+        "layer3.awq_block_size": 8, "layer4.quantization": "w4a8_awq", "layer4.awq_block_size": 64,
+        "layer5.quantization": "int8_sq", "layer6.quantization": "fp8", "layer7.quantization": "xyz",
+        "layer8.quantization": None})
+    assert mixed == {
+        "quant_algo": "MIXED_PRECISION", "kv_cache_quant_algo": None,
+        "quantized_layers": {
+            "layer1": {"quant_algo": "NVFP4", "group_size": 16},
+            "layer3": {"quant_algo": "W4A16_AWQ", "group_size": 8, "has_zero_point": False, "pre_quant_scale": True},
+            "layer4": {"quant_algo": "W4A8_AWQ", "group_size": 64, "has_zero_point": False, "pre_quant_scale": True},
+            "layer5": {"quant_algo": "W8A8_SQ_PER_CHANNEL"}, "layer6": {"quant_algo": "FP8"},
+            "layer7": {"quant_algo": "xyz"}}}
+    single = export.process_layer_quant_config({
+        "layer1.quantization": "nvfp4", "layer1.awq_block_size": 16, "layer2.quantization": "nvfp4",
+        "layer2.awq_block_size": 16, "layer8.quantization": None})
+    assert single == {"quant_algo": "NVFP4", "kv_cache_quant_algo": None, "group_size": 16,
+                      "exclude_modules": ["layer8"]}
+    # excluded modules are summarised by prefixes cut at dots that match no quantised layer
+    summary = export.process_layer_quant_config({
+        **{f"model.layers.{i}.mlp.up.quantization": "fp8" for i in range(2)},
+        **{f"model.layers.{i}.mlp.gate.quantization": None for i in range(2)},
+        "vision.a.quantization": None, "vision.b.quantization": None, "lm_head.quantization": None})
+    assert summary["exclude_modules"] == ["lm_head", "model.layers.0.mlp.gate", "model.layers.1.mlp.gate", "vision*"]
+    for items, same in ((["a", "a", "a"], True), (["b", "a", "a"], False), ([True, False, True], False), ([False], True)):
+        assert export.all_items_same(items) == same
+
+
+def test_quantization_record_in_the_hugging_face_shape():
+    """Reference modelopt/torch/export/convert_hf_config.py:21-117 (its docstring's FP8 example)."""
+    from b200q import export
+
+    got = export.convert_hf_quant_config_format({
+        "producer": {"name": "modelopt", "version": "0.19.0"},
+        "quantization": {"quant_algo": "FP8", "kv_cache_quant_algo": "FP8", "exclude_modules": ["lm_head"]}})
+    eight = {"dynamic": False, "num_bits": 8, "type": "float"}
+    assert got == {"config_groups": {"group_0": {"input_activations": eight, "weights": eight, "targets": ["Linear"]}},
+                   "ignore": ["lm_head"], "quant_algo": "FP8", "kv_cache_scheme": eight,
+                   "producer": {"name": "modelopt", "version": "0.19.0"}, "quant_method": "modelopt"}
+    nvfp4 = export.convert_hf_quant_config_format({"quantization": {"quant_algo": "NVFP4", "group_size": 16}})
+    assert nvfp4["config_groups"]["group_0"]["weights"] == {"dynamic": False, "num_bits": 4, "type": "float", "group_size": 16}
+    assert nvfp4["ignore"] == [] and "kv_cache_scheme" not in nvfp4
