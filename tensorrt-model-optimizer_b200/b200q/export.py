@@ -13,7 +13,7 @@ __all__ = ["get_scaling_factor_from_weight", "pack_int4_in_uint8", "to_quantized
            "get_weight_scaling_factor", "get_weight_scaling_factor_2", "get_prequant_scaling_factor",
            "export_quantized_weight", "postprocess_state_dict", "export_hf_state_dict", "adjust_attn_amax_values", "all_items_same", "process_layer_quant_config", "get_quant_config",
            "convert_hf_quant_config_format", "export_hf_checkpoint",
-           "preprocess_linear_fusion", "fuse_prequant_layernorm", "requantize_resmooth_fused_llm_layers",
+           "preprocess_linear_fusion", "fuse_prequant_layernorm", "fuse_prequant_to_linear", "requantize_resmooth_fused_llm_layers",
            "get_kv_cache_dtype", "get_kv_cache_scaling_factor", "get_kv_cache_bias",
            "KV_CACHE_FP8", "KV_CACHE_INT8", "KV_CACHE_NVFP4", "KV_CACHE_NVFP4_AFFINE",
            "QUANTIZATION_FP8", "QUANTIZATION_INT8_SQ", "QUANTIZATION_INT8_WO", "QUANTIZATION_INT4_AWQ",
@@ -457,6 +457,58 @@ def fuse_prequant_layernorm(layernorm_module, modules):
         m.fused_with_prequant = True
 
 
+# (class-name fragments of the parent, layer that takes the scale, layer that gives it up): the output channels
+# of v_proj are the input channels of o_proj (through the attention average), those of up_proj the input
+# channels of down_proj (through the elementwise product with the gate).
+_PRE_QUANT_SCALE_MOVES = ((("LlamaAttention", "Qwen3Attention", "Qwen3MoeAttention"), "v_proj", "o_proj"),
+                          (("LlamaMLP", "Qwen3MLP", "Qwen3MoeMLP"), "up_proj", "down_proj"))
+
+
+@torch.no_grad()
+def fuse_prequant_to_linear(model, fuse_grouped_heads=False):
+    """Move the pre-quant scale of o_proj / down_proj into the output channels of the layer whose output they
+    read (v_proj / up_proj) where the module classes are known to allow it (reference
+    modelopt/torch/export/quant_utils.py:1013-1102).  With grouped-query attention o_proj has more input
+    channels than v_proj has outputs: with ``fuse_grouped_heads`` the scale is first averaged over the query
+    heads that share a key / value head (o_proj is re-smoothed to the averaged scale), otherwise the pair is
+    skipped.  The taking layer's weight quantiser is calibrated again; the giving layer loses its
+    ``_pre_quant_scale`` and is marked ``fused_with_prequant``."""
+    import warnings
+
+    from .model_calib import enable_stats_collection, finish_stats_collection
+
+    for parent in model.modules():
+        kind = type(parent).__name__
+        for fragments, taker_name, giver_name in _PRE_QUANT_SCALE_MOVES:
+            if not any(f in kind for f in fragments):
+                continue
+            taker, giver = parent.get_submodule(taker_name), parent.get_submodule(giver_name)
+            scale = getattr(getattr(giver, "input_quantizer", None), "_pre_quant_scale", None)
+            if scale is None:
+                continue
+            out_channels = taker.weight.shape[-2]
+            if scale.numel() != out_channels:
+                if not fuse_grouped_heads or "attention" not in kind.lower():
+                    warnings.warn(f"Skipping pattern fuse prequant for {kind}: pre_quant_scale dim {scale.numel()} "
+                                  f"!= out_channel dim {out_channels}")
+                    continue
+                kv_heads = parent.config.num_key_value_heads
+                head_dim = out_channels // kv_heads
+                queries_per_kv = scale.numel() // out_channels
+                per_kv_head = scale.view(kv_heads, queries_per_kv, head_dim).mean(dim=1)
+                _update_pre_quant_scale(giver, per_kv_head.unsqueeze(1).expand(kv_heads, queries_per_kv, head_dim).reshape(-1))
+                scale = per_kv_head.reshape(-1)
+            taker.weight = torch.nn.Parameter(taker.weight * scale.view(-1, 1), requires_grad=taker.weight.requires_grad)
+            if getattr(taker, "bias", None) is not None:
+                taker.bias = torch.nn.Parameter(taker.bias * scale, requires_grad=taker.bias.requires_grad)
+            taker.weight_quantizer.reset_amax()
+            enable_stats_collection(taker.weight_quantizer)
+            taker.weight_quantizer(taker.weight)
+            finish_stats_collection(taker.weight_quantizer)
+            delattr(giver.input_quantizer, "_pre_quant_scale")
+            giver.fused_with_prequant = True
+
+
 def _is_layernorm(module) -> bool:
     name = type(module).__name__
     return any(key in name for key in ("LayerNorm", "RMSNorm"))
@@ -473,6 +525,9 @@ def requantize_resmooth_fused_llm_layers(model, fake_input=None):
     from .nn import is_quantized_linear
 
     by_input, by_output, handles, names = {}, {}, [], {}
+    whole = get_quantization_format(model)
+    if whole is not QUANTIZATION_NONE and "nvfp4_awq" in whole:
+        fuse_prequant_to_linear(model)
 
     def saw_input(module, args, output):
         by_input.setdefault(args[0], []).append(module)

@@ -157,3 +157,33 @@ def test_export_hf_checkpoint_writes_tensors_record_and_config(name, tmp_path):
     for k, v in state.items():
         assert torch.equal(seen[k].view(torch.uint8) if v.element_size() == 1 else seen[k],
                            v.cpu().view(torch.uint8) if v.element_size() == 1 else v.cpu()), k
+
+
+@pytest.mark.parametrize("name", ["INT4_AWQ_CFG", "NVFP4_AWQ_LITE_CFG"])
+@pytest.mark.parametrize("heads", [(4, 4), (4, 2), (4, 1)])      # MHA, GQA, MQA
+def test_pattern_fuse_prequant(name, heads):
+    """Reference tests/gpu/torch/export/test_quant_utils.py:41-101: the pre-quant scales of o_proj and down_proj
+    move into v_proj and up_proj (averaged over the query heads of a key / value head first); the layers that
+    gave them up are marked, and the logits stay within the reference test's tolerance."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    import b200q as mtq
+    from b200q import export
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=heads[0],
+                      num_key_value_heads=heads[1], max_position_embeddings=128, vocab_size=256)
+    model = LlamaForCausalLM(cfg).cuda().eval()
+    ids = torch.randint(0, 256, (1, 16), device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(ids))
+    with torch.no_grad():
+        before = model(ids).logits
+    export.fuse_prequant_to_linear(model, fuse_grouped_heads=True)
+    for target in ("model.layers.0.self_attn.o_proj", "model.layers.0.mlp.down_proj",
+                   "model.layers.1.self_attn.o_proj", "model.layers.1.mlp.down_proj"):
+        layer = model.get_submodule(target)
+        assert not hasattr(layer.input_quantizer, "_pre_quant_scale"), target
+        assert getattr(layer, "fused_with_prequant", False), target
+    with torch.no_grad():
+        after = model(ids).logits
+    assert torch.allclose(before, after, rtol=1e-1, atol=5e-1)
