@@ -147,3 +147,39 @@ def test_compress_switches_the_gemm_on(tmp_path):
     assert fake.net[0]._use_real_quant_gemm is True
     backends.disable_real_quant_gemm(fake)
     assert fake.net[0]._use_real_quant_gemm is False
+
+
+def _calibrated_and_compressed(mtq, model, config, calib_data):
+    def forward_loop(m):
+        for batch in calib_data:
+            m(batch)
+
+    mtq.quantize(model, config, forward_loop)
+    fake = model(calib_data[0].clone())
+    mtq.compress(model)
+    return fake
+
+
+def test_nvfp4_compressed_forward_stays_close_to_the_fake_quantised_one():
+    """Reference tests/gpu/torch/quantization/backends/test_nvfp4_gemm.py:77-101 (its tolerance)."""
+    mtq, config, _ = _case("nvfp4")
+    torch.manual_seed(0)
+    model = OneLayerLinear(64, 32).to(torch.float16).cuda()
+    calib_data = [model.get_input(2).to(torch.float16).cuda() for _ in range(8)]
+    fake = _calibrated_and_compressed(mtq, model, config, calib_data)
+    real = model(calib_data[0].clone())
+    assert torch.allclose(fake, real, atol=0.2), float((fake - real).abs().max())
+
+
+@pytest.mark.parametrize("which", ["fp8", "nvfp4"])
+def test_the_registry_finds_the_gemm_of_a_compressed_layer(which):
+    """Reference tests/gpu/torch/quantization/backends/test_fp8_per_tensor_gemm.py:29-52, and the same for
+    NVFP4: the first layer of a compressed model matches its format's GEMM."""
+    from b200q.backends import gemm_registry
+
+    mtq, config, apply = _case(which)
+    torch.manual_seed(0)
+    model = (SimpleLinear() if which == "fp8" else OneLayerLinear(64, 32)).to(torch.float16).cuda()
+    calib_data = [model.get_input().to(torch.float16).cuda() for _ in range(8)]
+    _calibrated_and_compressed(mtq, model, config, calib_data)
+    assert gemm_registry.find_match(model.net[0], calib_data[0].clone(), [], {}) == apply
