@@ -187,3 +187,41 @@ def test_pattern_fuse_prequant(name, heads):
     with torch.no_grad():
         after = model(ids).logits
     assert torch.allclose(before, after, rtol=1e-1, atol=5e-1)
+
+
+@pytest.mark.parametrize(("name", "fused"), [
+    ("FP8_DEFAULT_CFG", True), ("NVFP4_DEFAULT_CFG", True), ("NVFP4_AWQ_LITE_CFG", True), ("INT4_AWQ_CFG", True),
+    ("W4A8_AWQ_BETA_CFG", True), ("INT8_WEIGHT_ONLY_CFG", False)])
+def test_exported_safetensors_share_scales_across_fused_projections(name, fused, tmp_path):
+    """Reference tests/gpu/torch/export/test_unified_hf_export_and_check_safetensors.py:24-131 without the
+    example script around it: a small Llama is quantised with each format, exported, and the safetensors are
+    read back: gate / up and q / k / v agree on ``input_scale``, ``weight_scale_2`` and ``prequant_scale``."""
+    from safetensors import safe_open
+
+    import b200q as mtq
+    from b200q import export
+
+    model = _tiny_llama()
+    ids = torch.randint(0, 512, (2, 64), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    mtq.quantize(model, copy.deepcopy(getattr(mtq, name)), lambda m: m(ids))
+    export.export_hf_checkpoint(model, torch.bfloat16, tmp_path)
+    files = sorted(tmp_path.glob("*.safetensors"))
+    assert files
+    tensors = {}
+    for f in files:
+        with safe_open(str(f), framework="pt") as reader:
+            for key in reader.keys():
+                tensors[key] = reader.get_tensor(key)
+    assert tensors
+    checked = 0
+    for key, value in tensors.items():
+        if not (fused and key.endswith(("input_scale", "weight_scale_2", "prequant_scale"))):
+            continue
+        for first, second in (("gate_proj", "up_proj"), ("q_proj", "k_proj"), ("q_proj", "v_proj")):
+            if first in key:
+                assert torch.allclose(value.float(), tensors[key.replace(first, second)].float()), key
+                checked += 1
+    if fused and name != "INT4_AWQ_CFG":      # INT4 AWQ has weight-only layers: no such scales to compare
+        assert checked > 0
+    packed = tensors["model.layers.0.mlp.up_proj.weight"]
+    assert packed.element_size() == 1
