@@ -79,6 +79,18 @@ class NVFP4QTensor(BaseQuantizedTensor):
             s2 = weights_scaling_factor_2
         return cls(shape, dtype, packed), scales, s2
 
+    @classmethod
+    def _cast_fp4(cls, weight: torch.Tensor) -> torch.Tensor:
+        """The 4-bit E2M1 code (sign bit 8, magnitude index 0..7) of every element as uint8, ties between two
+        grid values going to the even index (reference qtensor/nvfp4_tensor.py ``_cast_fp4``): the
+        quantisation kernel run with unit scales, its packed pairs taken apart again."""
+        block = 16
+        x = reduce_block_padding(weight, {-1: block})
+        ones = torch.ones(*x.shape[:-1], x.shape[-1] // block, device=x.device).to(torch.float8_e4m3fn)
+        packed = cls.quantize(x, block, ones, torch.ones((), dtype=torch.float32, device=x.device))[0]._quantized_data
+        codes = torch.stack((packed & 0xF, packed >> 4), dim=-1).reshape(x.shape)
+        return codes[..., : weight.shape[-1]].contiguous()
+
     def dequantize(self, dtype=None, fast=False, **kwarg):
         """Needs ``scale`` (E4M3 per block), ``double_scale`` (fp32) and ``block_sizes``."""
         dtype = dtype or self.metadata["dtype"]

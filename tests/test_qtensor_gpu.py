@@ -164,3 +164,44 @@ def test_fp8_with_an_amax_and_block_sizes(dtype, shape, block_sizes):
     deq = q(q(x))
     assert torch.allclose(deq, x, rtol=1e-1, atol=1e-1)
     assert q._scale.numel() > 1
+
+
+@pytest.mark.parametrize("values", [
+    None,
+    [[0.25, 0.75, 1.25], [1.75, 2.5, 3.5]],
+    [[0.1, 2.5, 1.0, 4.8], [1.5, 1.25, 3.25, 5.0]],
+    [[0, 0.75, 1.25], [1.75, 2.5, 5.5]],
+    [[-0.25, -0.75, -1.25], [-1.75, -2.5, -3.5]],
+    [[-0.1, -2.5, -1.0, -4.8], [-1.5, -1.25, -3.25, -5.0]],
+    [[0, -0.75, -1.25], [-1.75, -2.5, -5.5]]])
+def test_cast_fp4_equivalence(values):
+    """Reference tests/gpu/torch/quantization/test_qtensor_cuda.py:398-445: the 4-bit code of each value
+    equals the definition by the E2M1 midpoints, values on a midpoint going to the even code."""
+    from b200q.qtensor import NVFP4QTensor
+
+    x = (torch.randn(32, 16, generator=torch.Generator().manual_seed(0)) if values is None
+         else torch.tensor(values, dtype=torch.float32)).cuda()
+    bounds = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5], device="cuda")
+    up_on_tie = torch.tensor([0, 1, 0, 1, 0, 1, 0], device="cuda")
+    magnitude = (x.abs().unsqueeze(-1) > bounds).sum(-1) + ((x.abs().unsqueeze(-1) == bounds) * up_on_tie).sum(-1)
+    want = ((x < 0).to(torch.uint8) * 8 + magnitude.to(torch.uint8)).to(torch.uint8)
+    got = NVFP4QTensor._cast_fp4(x)
+    assert got.dtype == torch.uint8 and got.shape == x.shape
+    # the sign of a value that rounds to zero is kept by the definition above and by the kernel alike
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("shape", [(128, 64), (64, 128, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_nvfp4_dequantize_fast_equals_the_standard_one(shape, dtype):
+    """Reference tests/gpu/torch/quantization/test_qtensor_cuda.py:534-572: ``fast=True`` changes nothing
+    here (one kernel serves both), and the result stays close to the input."""
+    from b200q.qtensor import NVFP4QTensor
+
+    block_sizes = {-1: 16, "type": "dynamic", "scale_bits": (4, 3)}
+    x = torch.randn(shape, dtype=dtype, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0))
+    q, scale, double_scale = NVFP4QTensor.quantize(x, 16)
+    standard = q.dequantize(dtype=dtype, fast=False, scale=scale, double_scale=double_scale, block_sizes=block_sizes)
+    fast = q.dequantize(dtype=dtype, fast=True, scale=scale, double_scale=double_scale, block_sizes=block_sizes)
+    assert torch.equal(fast, standard)
+    assert torch.allclose(standard, x, atol=0.5, rtol=0.1)
